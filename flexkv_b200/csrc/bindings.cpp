@@ -1,0 +1,339 @@
+// pybind11 surface of flexkv_b200._C. Tensors cross as raw addresses
+// (tensor.data_ptr()) and numpy arrays; no torch headers are involved.
+// Functional counterpart of the reference's c_ext module (csrc/bindings.cpp:428-1365).
+#include <pybind11/numpy.h>
+#include <pybind11/pybind11.h>
+#include <pybind11/stl.h>
+
+#include <cuda_runtime.h>
+
+#include "hasher.h"
+#include "host_mem.h"
+#include "kernels/kv_copy.h"
+#include "radix_index.h"
+#include "ssd_io.h"
+#include "transfer_group.h"
+
+namespace py = pybind11;
+using namespace fkv;
+
+using I64Array = py::array_t<int64_t, py::array::c_style | py::array::forcecast>;
+using U64Array = py::array_t<uint64_t, py::array::c_style | py::array::forcecast>;
+
+void init_kernel_bindings(py::module_& m);     // bindings_kernels.cpp
+void init_layerwise_bindings(py::module_& m);  // bindings_layerwise.cpp
+
+template <typename T>
+static py::array_t<T> to_array(const std::vector<T>& v) {
+  py::array_t<T> a((py::ssize_t)v.size());
+  if (!v.empty()) std::memcpy(a.mutable_data(), v.data(), v.size() * sizeof(T));
+  return a;
+}
+
+static py::object handle_to_py(NodeHandle h) {
+  if (h == kNullHandle) return py::none();
+  return py::int_(h);
+}
+static NodeHandle handle_from_py(const py::object& o) {
+  if (o.is_none()) return kNullHandle;
+  return o.cast<uint64_t>();
+}
+
+struct PyMatch {
+  MatchResult r;
+};
+
+PYBIND11_MODULE(_C, m) {
+  m.doc() = "flexkv_b200 native core (sm_100a kernels + C++ control plane)";
+  m.attr("MAX_GPU_PTRS") = kMaxGpuPtrs;
+
+  // ---------------------------------------------------------------- hashing
+  m.def("xxh64", [](py::buffer b, uint64_t seed) {
+    py::buffer_info info = b.request();
+    return XXH64::hash(info.ptr, (size_t)(info.size * info.itemsize), seed);
+  }, py::arg("data"), py::arg("seed") = 0);
+
+  m.def("gen_hashes", [](I64Array tokens, int tokens_per_block, py::object ns) {
+    if (tokens_per_block <= 0) throw std::invalid_argument("tokens_per_block must be positive");
+    const int64_t n = (int64_t)tokens.size();
+    I64Array nsa;
+    const int64_t* nsp = nullptr;
+    int64_t nsl = 0;
+    if (!ns.is_none()) { nsa = ns.cast<I64Array>(); nsp = nsa.data(); nsl = (int64_t)nsa.size(); }
+    py::array_t<uint64_t> out((py::ssize_t)(n / tokens_per_block));
+    {
+      const int64_t* tp = tokens.data();
+      uint64_t* op = out.mutable_data();
+      py::gil_scoped_release rel;
+      gen_block_hashes(tp, n, tokens_per_block, nsp, nsl, op);
+    }
+    return out;
+  }, py::arg("token_ids"), py::arg("tokens_per_block"), py::arg("namespace_prefix") = py::none());
+
+  m.def("gen_hashes_batch", [](std::vector<I64Array> seqs, int tokens_per_block, py::object ns, int threads) {
+    I64Array nsa;
+    const int64_t* nsp = nullptr;
+    int64_t nsl = 0;
+    if (!ns.is_none()) { nsa = ns.cast<I64Array>(); nsp = nsa.data(); nsl = (int64_t)nsa.size(); }
+    const int64_t n = (int64_t)seqs.size();
+    std::vector<int64_t> off(n + 1, 0), ooff(n + 1, 0);
+    for (int64_t i = 0; i < n; ++i) {
+      off[i + 1] = off[i] + (int64_t)seqs[i].size();
+      ooff[i + 1] = ooff[i] + (int64_t)seqs[i].size() / tokens_per_block;
+    }
+    std::vector<int64_t> flat((size_t)off[n]);
+    for (int64_t i = 0; i < n; ++i)
+      if (seqs[i].size()) std::memcpy(flat.data() + off[i], seqs[i].data(), (size_t)seqs[i].size() * 8);
+    std::vector<uint64_t> out((size_t)ooff[n]);
+    {
+      py::gil_scoped_release rel;
+      gen_block_hashes_batch(flat.data(), off.data(), n, tokens_per_block, nsp, nsl, out.data(), ooff.data(), threads);
+    }
+    py::list res;
+    for (int64_t i = 0; i < n; ++i) {
+      py::array_t<uint64_t> a((py::ssize_t)(ooff[i + 1] - ooff[i]));
+      if (a.size()) std::memcpy(a.mutable_data(), out.data() + ooff[i], (size_t)a.size() * 8);
+      res.append(a);
+    }
+    return res;
+  }, py::arg("seqs"), py::arg("tokens_per_block"), py::arg("namespace_prefix") = py::none(), py::arg("threads") = 4);
+
+  // ---------------------------------------------------------------- radix index
+  py::class_<PyMatch>(m, "MatchResult")
+      .def_property_readonly("num_ready_matched_blocks", [](const PyMatch& p) { return p.r.num_ready_matched; })
+      .def_property_readonly("num_matched_blocks", [](const PyMatch& p) { return p.r.num_matched; })
+      .def_property_readonly("last_node_matched_length", [](const PyMatch& p) { return p.r.last_node_matched_length; })
+      .def_property_readonly("last_ready_node", [](const PyMatch& p) { return handle_to_py(p.r.last_ready_node); })
+      .def_property_readonly("last_node", [](const PyMatch& p) { return handle_to_py(p.r.last_node); })
+      .def_property_readonly("physical_blocks", [](const PyMatch& p) { return to_array(p.r.physical_blocks); });
+
+  py::class_<RadixIndex>(m, "RadixIndex")
+      .def(py::init([](int tpb, int64_t max_blocks, const std::string& policy, double reward, uint32_t slru) {
+             return new RadixIndex(tpb, max_blocks, parse_policy(policy), reward, slru);
+           }),
+           py::arg("tokens_per_block"), py::arg("max_num_blocks") = 0, py::arg("eviction_policy") = "lru",
+           py::arg("hit_reward_seconds") = 0.0, py::arg("slru_threshold") = 2)
+      .def("match_prefix", [](RadixIndex& t, U64Array hashes, int64_t n, bool update) {
+             if (n < 0 || n > (int64_t)hashes.size()) n = (int64_t)hashes.size();
+             PyMatch pm;
+             pm.r = t.match_prefix(hashes.data(), n, update);
+             return pm;
+           }, py::arg("block_hashes"), py::arg("num_blocks") = -1, py::arg("update_cache_info") = true)
+      .def("insert", [](RadixIndex& t, I64Array physical, U64Array hashes, int64_t num_insert, bool ready,
+                        py::object match) {
+             const MatchResult* mr = nullptr;
+             PyMatch pm;
+             if (!match.is_none()) { pm = match.cast<PyMatch>(); mr = &pm.r; }
+             if (num_insert < 0) num_insert = (int64_t)hashes.size();
+             return handle_to_py(t.insert(physical.data(), (int64_t)physical.size(), hashes.data(),
+                                          (int64_t)hashes.size(), num_insert, ready, mr));
+           }, py::arg("physical_block_ids"), py::arg("block_hashes"), py::arg("num_insert_blocks") = -1,
+           py::arg("is_ready") = true, py::arg("match_result") = py::none())
+      .def("evict", [](RadixIndex& t, int64_t n) {
+             EvictResult r = t.evict(n);
+             return py::make_tuple(to_array(r.blocks), to_array(r.hashes));
+           })
+      .def("lock", [](RadixIndex& t, py::object h) { t.lock(handle_from_py(h)); })
+      .def("unlock", [](RadixIndex& t, py::object h) { t.unlock(handle_from_py(h)); })
+      .def("set_ready", [](RadixIndex& t, py::object h, bool ready, int64_t len) {
+             t.set_ready(handle_from_py(h), ready, len);
+           }, py::arg("node"), py::arg("ready") = true, py::arg("ready_length") = -1)
+      .def("remove_unready_leaf", [](RadixIndex& t, py::object h) {
+             return to_array(t.remove_unready_leaf(handle_from_py(h)));
+           })
+      .def("reset", [](RadixIndex& t) { return to_array(t.reset()); })
+      .def("alive", [](RadixIndex& t, py::object h) { return t.alive(handle_from_py(h)); })
+      .def("is_root", [](RadixIndex& t, py::object h) { return t.is_root(handle_from_py(h)); })
+      .def("root", [](RadixIndex& t) { return handle_to_py(t.root_handle()); })
+      .def("node_size", [](RadixIndex& t, py::object h) { return t.node_size(handle_from_py(h)); })
+      .def("node_ready", [](RadixIndex& t, py::object h) { return t.node_ready(handle_from_py(h)); })
+      .def("node_lock_cnt", [](RadixIndex& t, py::object h) { return t.node_lock_cnt(handle_from_py(h)); })
+      .def("node_parent", [](RadixIndex& t, py::object h) { return handle_to_py(t.node_parent(handle_from_py(h))); })
+      .def("node_is_leaf", [](RadixIndex& t, py::object h) { return t.node_is_leaf(handle_from_py(h)); })
+      .def("node_hit_count", [](RadixIndex& t, py::object h) { return t.node_hit_count(handle_from_py(h)); })
+      .def("total_cached_blocks", &RadixIndex::total_cached_blocks)
+      .def("total_ready_blocks", &RadixIndex::total_ready_blocks)
+      .def("num_nodes", &RadixIndex::num_nodes)
+      .def("num_leaves", &RadixIndex::num_leaves)
+      .def("num_evictable_blocks", &RadixIndex::num_evictable_blocks)
+      .def("is_empty", &RadixIndex::is_empty)
+      .def("set_clock_override", &RadixIndex::set_clock_override)
+      .def("set_policy", [](RadixIndex& t, const std::string& p) { t.set_policy(parse_policy(p)); })
+      .def("stats", [](RadixIndex& t) {
+        py::dict d;
+        d["hit"] = t.stat_hit; d["match"] = t.stat_match; d["miss"] = t.stat_miss;
+        d["insert_blocks"] = t.stat_insert_blocks; d["evict_blocks"] = t.stat_evict_blocks;
+        return d;
+      });
+
+  py::class_<BlockPool>(m, "BlockPool")
+      .def(py::init<int64_t>())
+      .def("allocate", [](BlockPool& p, int64_t n, bool strict) { return to_array(p.allocate(n, strict)); },
+           py::arg("num"), py::arg("strict") = true)
+      .def("recycle", [](BlockPool& p, I64Array ids) { p.recycle(ids.data(), (int64_t)ids.size()); })
+      .def("reset", &BlockPool::reset)
+      .def_property_readonly("num_free", &BlockPool::num_free)
+      .def_property_readonly("num_total", &BlockPool::num_total)
+      .def_property_readonly("num_used", &BlockPool::num_used)
+      .def("is_free", &BlockPool::is_free);
+
+  // ---------------------------------------------------------------- host memory
+  py::class_<HostRegion>(m, "HostRegion", py::buffer_protocol())
+      .def_property_readonly("ptr", [](const HostRegion& r) { return (uint64_t)(uintptr_t)r.ptr; })
+      .def_readonly("bytes", &HostRegion::bytes)
+      .def_readonly("map_bytes", &HostRegion::map_bytes)
+      .def_readonly("hugepage", &HostRegion::hugepage)
+      .def_readonly("file_backed", &HostRegion::file_backed)
+      .def_readonly("registered", &HostRegion::registered)
+      .def("register", [](HostRegion& r, size_t chunk) { py::gil_scoped_release rel; host_region_register(r, chunk); },
+           py::arg("chunk_bytes") = 0)
+      .def("unregister", [](HostRegion& r) { host_region_unregister(r); })
+      .def("free", [](HostRegion& r) { host_region_free(r); })
+      .def_buffer([](HostRegion& r) {
+        return py::buffer_info(r.ptr, 1, py::format_descriptor<uint8_t>::format(), 1, {(py::ssize_t)r.bytes}, {1});
+      });
+
+  m.def("host_region_alloc", [](size_t bytes, bool hugepage, size_t hugepage_bytes, int numa_node, bool populate,
+                                int touch_threads, bool cuda_register, size_t register_chunk, std::string file) {
+    HostAllocOptions o;
+    o.hugepage = hugepage; o.hugepage_bytes = hugepage_bytes; o.numa_node = numa_node; o.populate = populate;
+    o.touch_threads = touch_threads; o.cuda_register = cuda_register; o.register_chunk_bytes = register_chunk;
+    o.backing_file = file;
+    py::gil_scoped_release rel;
+    return host_region_alloc(bytes, o);
+  }, py::arg("bytes"), py::arg("hugepage") = false, py::arg("hugepage_bytes") = (size_t)(2u << 20),
+     py::arg("numa_node") = -1, py::arg("populate") = true, py::arg("touch_threads") = 8,
+     py::arg("cuda_register") = false, py::arg("register_chunk_bytes") = (size_t)0, py::arg("backing_file") = "");
+  m.def("host_region_open", &host_region_open, py::arg("file"), py::arg("bytes"), py::arg("hugepage") = false,
+        py::arg("hugepage_bytes") = (size_t)(2u << 20));
+  m.def("gpu_numa_node", &gpu_numa_node);
+  m.def("cuda_device_count", [] {
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess) { (void)cudaGetLastError(); return 0; }
+    return n;
+  });
+
+  // ---------------------------------------------------------------- SSD IO
+  py::class_<SsdIoEngine>(m, "SsdIoEngine")
+      .def(py::init<const std::vector<std::vector<std::string>>&, int64_t, int64_t, bool, bool, int, int>(),
+           py::arg("files"), py::arg("block_bytes"), py::arg("blocks_per_file"), py::arg("create") = true,
+           py::arg("try_direct") = true, py::arg("iouring_entries") = 512, py::arg("num_threads") = 8)
+      .def("transfer", [](SsdIoEngine& e, uint64_t cpu_base, I64Array cpu_blocks, I64Array ssd_blocks, bool is_read,
+                          py::dict lay, int layer_start, int num_layers) {
+             if (cpu_blocks.size() != ssd_blocks.size()) throw std::invalid_argument("block id arrays differ in size");
+             SsdLayout L;
+             L.cpu_layer_stride = lay["cpu_layer_stride"].cast<int64_t>();
+             L.cpu_kv_stride = lay["cpu_kv_stride"].cast<int64_t>();
+             L.cpu_block_stride = lay["cpu_block_stride"].cast<int64_t>();
+             L.ssd_layer_stride = lay["ssd_layer_stride"].cast<int64_t>();
+             L.ssd_kv_stride = lay["ssd_kv_stride"].cast<int64_t>();
+             L.ssd_block_stride = lay["ssd_block_stride"].cast<int64_t>();
+             L.chunk_bytes = lay["chunk_bytes"].cast<int64_t>();
+             L.num_layers_total = lay["num_layers"].cast<int>();
+             L.kv_dim = lay["kv_dim"].cast<int>();
+             L.block_first = lay["block_first"].cast<bool>();
+             const int64_t n = (int64_t)cpu_blocks.size();
+             py::array_t<uint8_t> ok((py::ssize_t)n);
+             int64_t nfail;
+             {
+               const int64_t* cb = cpu_blocks.data();
+               const int64_t* sb = ssd_blocks.data();
+               uint8_t* okp = ok.mutable_data();
+               py::gil_scoped_release rel;
+               nfail = e.transfer((uint8_t*)(uintptr_t)cpu_base, cb, sb, n, is_read, L, layer_start, num_layers, okp);
+             }
+             return py::make_tuple(nfail, ok);
+           })
+      .def("set_fault", [](SsdIoEngine& e, int mode, int64_t nth) { SsdFault f; f.mode = mode; f.nth = nth; e.set_fault(f); })
+      .def("sync_files", &SsdIoEngine::sync_files)
+      .def_property_readonly("using_iouring", &SsdIoEngine::using_iouring)
+      .def_property_readonly("direct_available", &SsdIoEngine::direct_available)
+      .def_property_readonly("capacity_blocks", &SsdIoEngine::capacity_blocks)
+      .def_property_readonly("bytes_read", &SsdIoEngine::bytes_read)
+      .def_property_readonly("bytes_written", &SsdIoEngine::bytes_written);
+
+  // ---------------------------------------------------------------- transfer group
+  py::class_<OpResult>(m, "OpResult")
+      .def_readonly("status", &OpResult::status)
+      .def_readonly("gpu_ms", &OpResult::gpu_ms);
+
+  py::class_<TransferGroup>(m, "TransferGroup")
+      .def(py::init([](py::list gpus, py::dict host, py::dict o) {
+             std::vector<GpuSide> gs;
+             for (auto item : gpus) {
+               py::dict d = item.cast<py::dict>();
+               GpuSide g;
+               g.device = d["device"].cast<int>();
+               g.ptrs = d["ptrs"].cast<std::vector<uint64_t>>();
+               g.idx_layer_mul = d["idx_layer_mul"].cast<int>();
+               g.idx_kv_mul = d["idx_kv_mul"].cast<int>();
+               g.layer_stride = d["layer_stride"].cast<int64_t>();
+               g.kv_stride = d["kv_stride"].cast<int64_t>();
+               g.block_stride = d["block_stride"].cast<int64_t>();
+               g.num_blocks = d["num_blocks"].cast<int64_t>();
+               gs.push_back(std::move(g));
+             }
+             HostSide h;
+             h.base = host["base"].cast<uint64_t>();
+             h.layer_stride = host["layer_stride"].cast<int64_t>();
+             h.kv_stride = host["kv_stride"].cast<int64_t>();
+             h.block_stride = host["block_stride"].cast<int64_t>();
+             h.num_blocks = host["num_blocks"].cast<int64_t>();
+             GroupOptions g;
+             g.num_layers = o["num_layers"].cast<int>();
+             g.kv_dim = o["kv_dim"].cast<int>();
+             g.chunk_bytes = o["chunk_bytes"].cast<int64_t>();
+             g.cpu_tp_stride = o.contains("cpu_tp_stride") ? o["cpu_tp_stride"].cast<int64_t>() : 0;
+             g.shared_kv = o.contains("shared_kv") && o["shared_kv"].cast<bool>();
+             if (o.contains("shared_mode")) g.shared_mode = parse_shared_kv_mode(o["shared_mode"].cast<std::string>());
+             auto launch = [&](const char* k, KvCopyLaunch& l) {
+               if (!o.contains(k)) return;
+               py::dict d = o[k].cast<py::dict>();
+               if (d.contains("num_ctas")) l.num_ctas = d["num_ctas"].cast<int>();
+               if (d.contains("tile_bytes")) l.tile_bytes = d["tile_bytes"].cast<int>();
+               if (d.contains("engine")) l.engine = d["engine"].cast<int>();
+             };
+             launch("h2d", g.h2d);
+             launch("d2h", g.d2h);
+             if (o.contains("ring_slots")) g.ring_slots = o["ring_slots"].cast<int>();
+             if (o.contains("max_blocks_per_op")) g.max_blocks_per_op = o["max_blocks_per_op"].cast<int64_t>();
+             if (o.contains("high_priority_stream")) g.high_priority_stream = o["high_priority_stream"].cast<bool>();
+             py::gil_scoped_release rel;
+             return new TransferGroup(std::move(gs), h, g);
+           }))
+      .def("submit", [](TransferGroup& t, I64Array gb, I64Array cb, bool h2d, int ls, int nl, int engine) {
+             if (gb.size() != cb.size()) throw std::invalid_argument("block id arrays differ in size");
+             const int64_t* g = gb.data();
+             const int64_t* c = cb.data();
+             const int64_t n = (int64_t)gb.size();
+             py::gil_scoped_release rel;
+             return t.submit(g, c, n, h2d, ls, nl, engine);
+           }, py::arg("gpu_blocks"), py::arg("cpu_blocks"), py::arg("h2d"), py::arg("layer_start"),
+           py::arg("num_layers"), py::arg("engine") = -1)
+      .def("wait", [](TransferGroup& t, uint64_t ticket) { py::gil_scoped_release rel; return t.wait(ticket); })
+      .def("poll", &TransferGroup::poll)
+      .def("transfer", [](TransferGroup& t, I64Array gb, I64Array cb, bool h2d, int ls, int nl, int engine) {
+             if (gb.size() != cb.size()) throw std::invalid_argument("block id arrays differ in size");
+             const int64_t* g = gb.data();
+             const int64_t* c = cb.data();
+             const int64_t n = (int64_t)gb.size();
+             py::gil_scoped_release rel;
+             return t.transfer(g, c, n, h2d, ls, nl, engine);
+           }, py::arg("gpu_blocks"), py::arg("cpu_blocks"), py::arg("h2d"), py::arg("layer_start"),
+           py::arg("num_layers"), py::arg("engine") = -1)
+      .def("transfer_refshape", [](TransferGroup& t, I64Array gb, I64Array cb, bool h2d, int ctas) {
+             const int64_t* g = gb.data();
+             const int64_t* c = cb.data();
+             const int64_t n = (int64_t)gb.size();
+             py::gil_scoped_release rel;
+             return t.transfer_refshape(g, c, n, h2d, ctas);
+           }, py::arg("gpu_blocks"), py::arg("cpu_blocks"), py::arg("h2d"), py::arg("num_ctas") = 4)
+      .def("update_gpu_ptrs", &TransferGroup::update_gpu_ptrs)
+      .def("set_launch", [](TransferGroup& t, bool h2d, int ctas, int tile, int engine) {
+             t.set_launch(h2d, KvCopyLaunch{ctas, tile, engine});
+           })
+      .def_property_readonly("num_ranks", &TransferGroup::num_ranks);
+
+  init_kernel_bindings(m);
+  init_layerwise_bindings(m);
+}

@@ -1,0 +1,67 @@
+// Direct launch entry points for the CUDA kernels (used by flexkv_b200.ops and
+// by tests that compare a kernel with a PyTorch reference on one stream).
+#include <pybind11/numpy.h>
+#include <pybind11/pybind11.h>
+#include <pybind11/stl.h>
+
+#include <cuda_runtime.h>
+
+#include "kernels/kv_copy.h"
+
+namespace py = pybind11;
+using namespace fkv;
+
+static void throw_on(cudaError_t e, const char* what) {
+  if (e != cudaSuccess) {
+    (void)cudaGetLastError();
+    throw std::runtime_error(std::string(what) + ": " + cudaGetErrorString(e));
+  }
+}
+
+KvCopyParams kv_params_from_dict(const py::dict& d) {
+  KvCopyParams p;
+  std::memset(&p, 0, sizeof(p));
+  auto ptrs = d["gpu_ptrs"].cast<std::vector<uint64_t>>();
+  if ((int)ptrs.size() > kMaxGpuPtrs) throw std::invalid_argument("too many gpu tensors");
+  for (size_t i = 0; i < ptrs.size(); ++i) p.gpu_ptrs[i] = ptrs[i];
+  auto geti = [&](const char* k, int64_t dflt) { return d.contains(k) ? d[k].cast<int64_t>() : dflt; };
+  p.idx_layer_mul = (int32_t)geti("idx_layer_mul", 1);
+  p.idx_kv_mul = (int32_t)geti("idx_kv_mul", 0);
+  p.g_layer_stride = geti("g_layer_stride", 0);
+  p.g_kv_stride = geti("g_kv_stride", 0);
+  p.g_block_stride = geti("g_block_stride", 0);
+  p.g_off = geti("g_off", 0);
+  p.cpu_base = d["cpu_base"].cast<uint64_t>();
+  p.c_layer_stride = geti("c_layer_stride", 0);
+  p.c_kv_stride = geti("c_kv_stride", 0);
+  p.c_block_stride = geti("c_block_stride", 0);
+  p.c_off = geti("c_off", 0);
+  p.gpu_blocks = (const int64_t*)(uintptr_t)d["gpu_blocks_ptr"].cast<uint64_t>();
+  p.cpu_blocks = (const int64_t*)(uintptr_t)d["cpu_blocks_ptr"].cast<uint64_t>();
+  p.num_pairs = (int32_t)geti("num_pairs", 0);
+  p.layer_start = (int32_t)geti("layer_start", 0);
+  p.num_layers = (int32_t)geti("num_layers", 0);
+  p.kv_dim = (int32_t)geti("kv_dim", 1);
+  p.chunk_bytes = geti("chunk_bytes", 0);
+  p.gpu_num_blocks = geti("gpu_num_blocks", 0);
+  p.cpu_num_blocks = geti("cpu_num_blocks", 0);
+  p.status = (int32_t*)(uintptr_t)(uint64_t)geti("status_ptr", 0);
+  p.h2d = (int32_t)geti("h2d", 0);
+  return p;
+}
+
+void init_kernel_bindings(py::module_& m) {
+  m.def("kv_copy", [](py::dict params, int num_ctas, int tile_bytes, int engine, uint64_t stream) {
+    KvCopyParams p = kv_params_from_dict(params);
+    KvCopyLaunch cfg{num_ctas, tile_bytes, engine};
+    throw_on(launch_kv_copy(p, cfg, (cudaStream_t)(uintptr_t)stream), "kv_copy launch");
+  }, py::arg("params"), py::arg("num_ctas") = 16, py::arg("tile_bytes") = 16384, py::arg("engine") = 0,
+     py::arg("stream") = 0);
+
+  m.def("kv_copy_refshape", [](py::dict params, int num_ctas, uint64_t stream) {
+    KvCopyParams p = kv_params_from_dict(params);
+    throw_on(launch_kv_copy_refshape(p, num_ctas, (cudaStream_t)(uintptr_t)stream), "kv_copy_refshape launch");
+  }, py::arg("params"), py::arg("num_ctas") = 4, py::arg("stream") = 0);
+
+  m.def("kv_copy_tma_eligible", [](py::dict params) { return kv_copy_tma_eligible(kv_params_from_dict(params)); });
+}

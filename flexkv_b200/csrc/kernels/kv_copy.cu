@@ -1,0 +1,320 @@
+// Paged KV gather/scatter kernels (see kv_copy.h for the addressing model).
+//
+// Engine 0 — bulk-copy pipeline. Each persistent CTA is one warp that drives
+// a ring of shared-memory stages through the TMA unit: lane 0 issues a 1-D
+// bulk load (global -> shared, completion on an mbarrier) for tiles up to
+// LOOKAHEAD ahead, and as each tile lands issues the matching bulk store
+// (shared -> global). Either side may be mapped host memory, so the same
+// pipeline does GPU->host and host->GPU with no SM load/store instructions
+// on the data and no registers holding payload; the other lanes only
+// prefetch block ids. Host reads need many bytes in flight to cover the PCIe
+// round trip, so host->GPU runs with LOOKAHEAD = STAGES-1; GPU->host keeps
+// half of the ring for queued posted writes.
+//
+// Engine 1 — SIMT vector copy, warp per tile, 16/8/4/1-byte lanes with an
+// 8-deep unrolled load batch. It serves chunks whose size or alignment rules
+// out 16-byte bulk copies (the reference needs an 8-byte path for the same
+// reason: csrc/transfer.cu:34-92) and is the cross-check for engine 0.
+#include "kv_copy.h"
+#include "ptx_sm100.cuh"
+
+namespace fkv {
+namespace {
+
+constexpr uint64_t kWaitBudgetNs = 2000000000ull;  // 2 s per bulk-copy wait
+
+// The status word may sit in mapped host memory, where device atomics depend
+// on PCIe atomic support; a plain store is enough because any non-zero value
+// fails the op and the individual bits are diagnostic only.
+__device__ __forceinline__ void report_status(int32_t* status, int err) {
+  *reinterpret_cast<volatile int32_t*>(status) = *reinterpret_cast<volatile int32_t*>(status) | err;
+}
+
+struct TileAddr {
+  uint64_t gpu;
+  uint64_t cpu;
+  uint32_t bytes;  // 0 = skip (bad block id)
+};
+
+// Decodes tile index t (warp-uniform) given the pair's block ids.
+__device__ __forceinline__ TileAddr tile_addr(const KvCopyParams& p, int64_t r, int64_t gblk, int64_t cblk,
+                                              int tile_bytes, int tiles_per_chunk) {
+  // r = index inside the pair: ((layer * kv_dim) + kv) * tiles_per_chunk + s
+  const int s = (int)(r % tiles_per_chunk);
+  const int lk = (int)(r / tiles_per_chunk);
+  const int kv = lk % p.kv_dim;
+  const int layer = p.layer_start + lk / p.kv_dim;
+  TileAddr a;
+  const int64_t off = (int64_t)s * tile_bytes;
+  const int64_t left = p.chunk_bytes - off;
+  a.bytes = (uint32_t)(left < tile_bytes ? left : tile_bytes);
+  a.gpu = p.gpu_ptrs[layer * p.idx_layer_mul + kv * p.idx_kv_mul] + layer * p.g_layer_stride +
+          kv * p.g_kv_stride + gblk * p.g_block_stride + p.g_off + off;
+  a.cpu = p.cpu_base + layer * p.c_layer_stride + kv * p.c_kv_stride + cblk * p.c_block_stride + p.c_off + off;
+  return a;
+}
+
+__device__ __forceinline__ bool ids_in_range(const KvCopyParams& p, int64_t g, int64_t c, int& err) {
+  bool ok = true;
+  if (p.gpu_num_blocks > 0 && (g < 0 || g >= p.gpu_num_blocks)) { err |= KV_ERR_GPU_BLOCK_RANGE; ok = false; }
+  if (p.cpu_num_blocks > 0 && (c < 0 || c >= p.cpu_num_blocks)) { err |= KV_ERR_CPU_BLOCK_RANGE; ok = false; }
+  return ok;
+}
+
+template <int STAGES, int LOOKAHEAD>
+__global__ void __launch_bounds__(32, 1)
+kv_copy_bulk_kernel(const __grid_constant__ KvCopyParams p, int tile_bytes, int tiles_per_chunk) {
+  static_assert(LOOKAHEAD >= 1 && LOOKAHEAD < STAGES, "lookahead must leave one stage for stores");
+  extern __shared__ __align__(128) uint8_t ring[];
+  __shared__ __align__(8) uint64_t full[STAGES];
+  __shared__ uint64_t s_dst[STAGES];
+  __shared__ uint32_t s_bytes[STAGES];
+
+  const int lane = threadIdx.x;
+  if (lane == 0) {
+#pragma unroll
+    for (int s = 0; s < STAGES; ++s) ptx::mbar_init(&full[s], 1);
+    ptx::fence_mbar_init();
+  }
+  __syncwarp();
+
+  const int64_t tiles_per_pair = (int64_t)p.num_layers * p.kv_dim * tiles_per_chunk;
+  const int64_t total = tiles_per_pair * p.num_pairs;
+  const int64_t first = blockIdx.x, step = gridDim.x;
+  const int64_t n_mine = first < total ? (total - first + step - 1) / step : 0;
+
+  // Block ids are fetched 32 pairs at a time, one pair per lane, and the next
+  // window is requested as soon as the current one becomes active, so the
+  // round trip to (possibly host-resident) id arrays is off the issue path.
+  int64_t cur_w = -1;
+  int64_t cur_g = 0, cur_c = 0, nxt_g = 0, nxt_c = 0;
+  auto load_window = [&](int64_t w, int64_t& g, int64_t& c) {
+    const int64_t i = (w << 5) + lane;
+    if (i < p.num_pairs) {
+      g = __ldg(p.gpu_blocks + i);
+      c = __ldg(p.cpu_blocks + i);
+    }
+  };
+
+  int err = 0;
+  int dead = 0;         // set after an expired wait: stop issuing, drain, leave
+  uint32_t phases = 0;  // lane 0: parity of the next completion of each stage's barrier
+
+  for (int64_t it = 0; it < n_mine + LOOKAHEAD && !dead; ++it) {
+    const int64_t j = it - LOOKAHEAD;
+    if (j >= 0 && lane == 0) {
+      const int st = (int)(j % STAGES);
+      const uint32_t bytes = s_bytes[st];
+      if (bytes) {
+        if (ptx::mbar_wait_bounded(&full[st], (phases >> st) & 1u, kWaitBudgetNs)) {
+          phases ^= 1u << st;
+          ptx::bulk_s2g(reinterpret_cast<void*>(s_dst[st]), ring + (size_t)st * tile_bytes, bytes);
+        } else {
+          err |= KV_ERR_WAIT_EXPIRED;
+        }
+      }
+      ptx::bulk_commit();  // one group per tile (possibly empty) keeps the wait arithmetic uniform
+    }
+    dead = __shfl_sync(0xffffffffu, (err & KV_ERR_WAIT_EXPIRED) ? 1 : 0, 0);
+    if (dead) break;
+
+    if (it < n_mine) {
+      const int64_t t = first + it * step;
+      const int64_t pair = t / tiles_per_pair;
+      const int64_t r = t - pair * tiles_per_pair;
+      const int64_t w = pair >> 5;
+      if (w != cur_w) {
+        if (w == cur_w + 1 && cur_w >= 0) { cur_g = nxt_g; cur_c = nxt_c; }
+        else load_window(w, cur_g, cur_c);
+        cur_w = w;
+        load_window(w + 1, nxt_g, nxt_c);
+      }
+      const int64_t gblk = __shfl_sync(0xffffffffu, cur_g, (int)(pair & 31));
+      const int64_t cblk = __shfl_sync(0xffffffffu, cur_c, (int)(pair & 31));
+      if (lane == 0) {
+        const int st = (int)(it % STAGES);
+        // the stage was last used by tile it-STAGES; all but the newest
+        // STAGES-LOOKAHEAD store groups must have finished reading smem
+        if (it >= STAGES) ptx::bulk_wait_read<STAGES - LOOKAHEAD>();
+        TileAddr a{0, 0, 0};
+        if (ids_in_range(p, gblk, cblk, err)) a = tile_addr(p, r, gblk, cblk, tile_bytes, tiles_per_chunk);
+        s_bytes[st] = a.bytes;
+        if (a.bytes) {
+          s_dst[st] = p.h2d ? a.gpu : a.cpu;
+          ptx::mbar_expect_tx(&full[st], a.bytes);
+          ptx::bulk_g2s(ring + (size_t)st * tile_bytes, reinterpret_cast<const void*>(p.h2d ? a.cpu : a.gpu),
+                        a.bytes, &full[st]);
+        }
+      }
+    }
+  }
+  if (lane == 0) {
+    ptx::bulk_wait<0>();
+    if (err && p.status) report_status(p.status, err);
+  }
+}
+
+// ---------------------------------------------------------------- SIMT engine
+
+template <typename V> struct VecIO;
+template <> struct VecIO<uint4> {
+  static __device__ __forceinline__ uint4 ld(const void* p) { return ptx::ld_nc_v4(p); }
+  static __device__ __forceinline__ void st(void* p, const uint4& v) { ptx::st_cg_v4(p, v); }
+};
+template <> struct VecIO<uint2> {
+  static __device__ __forceinline__ uint2 ld(const void* p) { return ptx::ld_nc_v2(p); }
+  static __device__ __forceinline__ void st(void* p, const uint2& v) { ptx::st_cg_v2(p, v); }
+};
+template <> struct VecIO<uint32_t> {
+  static __device__ __forceinline__ uint32_t ld(const void* p) { return ptx::ld_nc_u32(p); }
+  static __device__ __forceinline__ void st(void* p, const uint32_t& v) { ptx::st_cg_u32(p, v); }
+};
+template <> struct VecIO<uint8_t> {
+  static __device__ __forceinline__ uint8_t ld(const void* p) { return *reinterpret_cast<const volatile uint8_t*>(p); }
+  static __device__ __forceinline__ void st(void* p, const uint8_t& v) { *reinterpret_cast<volatile uint8_t*>(p) = v; }
+};
+
+template <typename V>
+__global__ void __launch_bounds__(512)
+kv_copy_simt_kernel(const __grid_constant__ KvCopyParams p, int tile_bytes, int tiles_per_chunk) {
+  constexpr int UNROLL = 8;
+  const int lane = threadIdx.x & 31;
+  const int warps_per_cta = blockDim.x >> 5;
+  const int64_t warp0 = (int64_t)blockIdx.x * warps_per_cta + (threadIdx.x >> 5);
+  const int64_t nwarps = (int64_t)gridDim.x * warps_per_cta;
+  const int64_t tiles_per_pair = (int64_t)p.num_layers * p.kv_dim * tiles_per_chunk;
+  const int64_t total = tiles_per_pair * p.num_pairs;
+  int err = 0;
+  for (int64_t t = warp0; t < total; t += nwarps) {
+    const int64_t pair = t / tiles_per_pair;
+    const int64_t r = t - pair * tiles_per_pair;
+    const int64_t gblk = __ldg(p.gpu_blocks + pair);
+    const int64_t cblk = __ldg(p.cpu_blocks + pair);
+    if (!ids_in_range(p, gblk, cblk, err)) continue;
+    const TileAddr a = tile_addr(p, r, gblk, cblk, tile_bytes, tiles_per_chunk);
+    const uint8_t* src = reinterpret_cast<const uint8_t*>(p.h2d ? a.cpu : a.gpu);
+    uint8_t* dst = reinterpret_cast<uint8_t*>(p.h2d ? a.gpu : a.cpu);
+    const int nvec = (int)(a.bytes / sizeof(V));
+    int i = lane;
+    for (; i + 32 * (UNROLL - 1) < nvec; i += 32 * UNROLL) {
+      V v[UNROLL];
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) v[u] = VecIO<V>::ld(src + (size_t)(i + 32 * u) * sizeof(V));
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) VecIO<V>::st(dst + (size_t)(i + 32 * u) * sizeof(V), v[u]);
+    }
+    for (; i < nvec; i += 32) VecIO<V>::st(dst + (size_t)i * sizeof(V), VecIO<V>::ld(src + (size_t)i * sizeof(V)));
+  }
+  if (err && p.status && lane == 0) report_status(p.status, err);
+}
+
+// ---------------------------------------------------------------- baseline shape
+// One warp per (layer, pair); inside, a loop over kv planes with 16-byte lanes.
+__global__ void __launch_bounds__(1024) kv_copy_refshape_kernel(const __grid_constant__ KvCopyParams p) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp0 = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int64_t nwarps = (int64_t)gridDim.x * (blockDim.x >> 5);
+  const int64_t total = (int64_t)p.num_layers * p.num_pairs;
+  const int nvec = (int)(p.chunk_bytes / 16);
+  for (int64_t w = warp0; w < total; w += nwarps) {
+    const int layer = p.layer_start + (int)(w / p.num_pairs);
+    const int64_t pair = w % p.num_pairs;
+    const int64_t gblk = p.gpu_blocks[pair];
+    const int64_t cblk = p.cpu_blocks[pair];
+    for (int kv = 0; kv < p.kv_dim; ++kv) {
+      const uint64_t g = p.gpu_ptrs[layer * p.idx_layer_mul + kv * p.idx_kv_mul] + layer * p.g_layer_stride +
+                         kv * p.g_kv_stride + gblk * p.g_block_stride + p.g_off;
+      const uint64_t c =
+          p.cpu_base + layer * p.c_layer_stride + kv * p.c_kv_stride + cblk * p.c_block_stride + p.c_off;
+      const uint8_t* src = reinterpret_cast<const uint8_t*>(p.h2d ? c : g);
+      uint8_t* dst = reinterpret_cast<uint8_t*>(p.h2d ? g : c);
+      for (int i = lane; i < nvec; i += 32) ptx::st_cg_v4(dst + (size_t)i * 16, ptx::ld_nc_v4(src + (size_t)i * 16));
+    }
+  }
+}
+
+template <typename K>
+cudaError_t ensure_smem(K kernel, int bytes) {
+  // idempotent and cheap; avoids per-device bookkeeping
+  return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+}
+
+template <int STAGES, int LA>
+cudaError_t launch_bulk(const KvCopyParams& p, int ctas, int tile_bytes, int tiles_per_chunk, cudaStream_t s) {
+  const int smem = STAGES * tile_bytes;
+  auto k = kv_copy_bulk_kernel<STAGES, LA>;
+  cudaError_t e = ensure_smem(k, smem);
+  if (e != cudaSuccess) return e;
+  k<<<ctas, 32, smem, s>>>(p, tile_bytes, tiles_per_chunk);
+  return cudaGetLastError();
+}
+
+inline bool all_multiple(const KvCopyParams& p, int64_t m) {
+  auto ok = [m](int64_t v) { return (v % m) == 0; };
+  bool r = ok(p.chunk_bytes) && ok(p.g_layer_stride) && ok(p.g_kv_stride) && ok(p.g_block_stride) && ok(p.g_off) &&
+           ok((int64_t)(p.cpu_base % (uint64_t)m)) && ok(p.c_layer_stride) && ok(p.c_kv_stride) &&
+           ok(p.c_block_stride) && ok(p.c_off);
+  const int nptr = p.idx_layer_mul == 0 && p.idx_kv_mul == 0
+                       ? 1
+                       : (p.layer_start + p.num_layers - 1) * p.idx_layer_mul + (p.kv_dim - 1) * p.idx_kv_mul + 1;
+  for (int i = 0; i < nptr && i < kMaxGpuPtrs; ++i) r = r && (p.gpu_ptrs[i] % (uint64_t)m) == 0;
+  return r;
+}
+
+}  // namespace
+
+bool kv_copy_tma_eligible(const KvCopyParams& p) { return all_multiple(p, 16); }
+
+cudaError_t launch_kv_copy(const KvCopyParams& p, const KvCopyLaunch& cfg, cudaStream_t stream) {
+  if (p.num_pairs <= 0 || p.num_layers <= 0 || p.kv_dim <= 0 || p.chunk_bytes <= 0) return cudaSuccess;
+  int tile = cfg.tile_bytes > 0 ? cfg.tile_bytes : 16384;
+  int engine = cfg.engine;
+  if (engine == 0 && !all_multiple(p, 16)) engine = 1;
+  if (engine == 0) {
+    tile = (tile / 16) * 16;
+    if (tile < 1024) tile = 1024;
+    if (tile > 32768) tile = 32768;
+    if ((int64_t)tile > p.chunk_bytes) tile = (int)p.chunk_bytes;
+    const int tiles_per_chunk = (int)((p.chunk_bytes + tile - 1) / tile);
+    const int64_t total = (int64_t)p.num_pairs * p.num_layers * p.kv_dim * tiles_per_chunk;
+    int ctas = cfg.num_ctas > 0 ? cfg.num_ctas : 16;
+    if ((int64_t)ctas > total) ctas = (int)total;
+    // deepest ring that fits beside the static barriers (limit 227 KiB per CTA)
+    const int budget = 200 * 1024;
+    const int stages = budget / tile;
+    if (p.h2d) {
+      if (stages >= 12) return launch_bulk<12, 11>(p, ctas, tile, tiles_per_chunk, stream);
+      if (stages >= 8) return launch_bulk<8, 7>(p, ctas, tile, tiles_per_chunk, stream);
+      return launch_bulk<6, 5>(p, ctas, tile, tiles_per_chunk, stream);
+    }
+    if (stages >= 12) return launch_bulk<12, 6>(p, ctas, tile, tiles_per_chunk, stream);
+    if (stages >= 8) return launch_bulk<8, 4>(p, ctas, tile, tiles_per_chunk, stream);
+    return launch_bulk<6, 3>(p, ctas, tile, tiles_per_chunk, stream);
+  }
+  // SIMT engine
+  if (tile > p.chunk_bytes) tile = (int)p.chunk_bytes;
+  int vec = all_multiple(p, 16) ? 16 : all_multiple(p, 8) ? 8 : all_multiple(p, 4) ? 4 : 1;
+  tile = (tile / vec) * vec;
+  if (tile <= 0) tile = vec;
+  const int tiles_per_chunk = (int)((p.chunk_bytes + tile - 1) / tile);
+  const int64_t total = (int64_t)p.num_pairs * p.num_layers * p.kv_dim * tiles_per_chunk;
+  int ctas = cfg.num_ctas > 0 ? cfg.num_ctas : 16;
+  const int64_t need = (total + 15) / 16;
+  if ((int64_t)ctas > need) ctas = (int)need;
+  switch (vec) {
+    case 16: kv_copy_simt_kernel<uint4><<<ctas, 512, 0, stream>>>(p, tile, tiles_per_chunk); break;
+    case 8: kv_copy_simt_kernel<uint2><<<ctas, 512, 0, stream>>>(p, tile, tiles_per_chunk); break;
+    case 4: kv_copy_simt_kernel<uint32_t><<<ctas, 512, 0, stream>>>(p, tile, tiles_per_chunk); break;
+    default: kv_copy_simt_kernel<uint8_t><<<ctas, 512, 0, stream>>>(p, tile, tiles_per_chunk); break;
+  }
+  return cudaGetLastError();
+}
+
+cudaError_t launch_kv_copy_refshape(const KvCopyParams& p, int num_ctas, cudaStream_t stream) {
+  if (p.num_pairs <= 0 || p.num_layers <= 0) return cudaSuccess;
+  if (!all_multiple(p, 16)) return cudaErrorInvalidValue;
+  kv_copy_refshape_kernel<<<num_ctas > 0 ? num_ctas : 4, 1024, 0, stream>>>(p);
+  return cudaGetLastError();
+}
+
+}  // namespace fkv

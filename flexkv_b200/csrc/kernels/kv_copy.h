@@ -1,0 +1,73 @@
+// Paged KV gather/scatter between a GPU block table and a host block pool.
+//
+// One launch moves, for every (gpu_block, cpu_block) pair, every layer in
+// [layer_start, layer_start + num_layers) and every kv plane, one contiguous
+// chunk of `chunk_bytes`. The two sides are addressed independently, which is
+// what converts between the engine's paged layout and the host block format:
+//
+//   gpu = gpu_ptrs[layer*idx_layer_mul + kv*idx_kv_mul]
+//         + layer*g_layer_stride + kv*g_kv_stride + gpu_block*g_block_stride + g_off
+//   cpu = cpu_base + layer*c_layer_stride + kv*c_kv_stride + cpu_block*c_block_stride + c_off
+//
+// vLLM (one tensor per layer):      idx_layer_mul=1, idx_kv_mul=0, g_layer_stride=0
+// TensorRT-LLM (one tensor):        idx_*=0, all three g_* strides set
+// SGLang (K tensors then V tensors):idx_layer_mul=1, idx_kv_mul=num_layers, g_kv_stride=g_layer_stride=0
+// (reference addressing rules: csrc/gtensor_handler.cuh:43-67).
+//
+// The block-id arrays may live in mapped pinned host memory: the kernels read
+// them directly, so an op needs no staging copy before the launch.
+#pragma once
+#include <cstdint>
+#include <cuda_runtime.h>
+
+namespace fkv {
+
+constexpr int kMaxGpuPtrs = 256;
+
+enum KvCopyStatus : int {
+  KV_OK = 0,
+  KV_ERR_GPU_BLOCK_RANGE = 1,   // a gpu block id outside [0, gpu_num_blocks)
+  KV_ERR_CPU_BLOCK_RANGE = 2,   // a cpu block id outside [0, cpu_num_blocks)
+  KV_ERR_WAIT_EXPIRED = 4,      // a bounded wait on a bulk copy ran out
+  KV_ERR_BAD_ARGS = 8,
+  KV_ERR_PAYLOAD_OVERFLOW = 16, // compressed payload larger than its slot
+  KV_ERR_PEER_WAIT_EXPIRED = 32,
+};
+
+struct KvCopyParams {
+  uint64_t gpu_ptrs[kMaxGpuPtrs];
+  int32_t idx_layer_mul;
+  int32_t idx_kv_mul;
+  int64_t g_layer_stride, g_kv_stride, g_block_stride, g_off;
+  uint64_t cpu_base;
+  int64_t c_layer_stride, c_kv_stride, c_block_stride, c_off;
+  const int64_t* gpu_blocks;
+  const int64_t* cpu_blocks;
+  int32_t num_pairs;
+  int32_t layer_start, num_layers, kv_dim;
+  int64_t chunk_bytes;
+  int64_t gpu_num_blocks, cpu_num_blocks;  // <= 0 disables the range check
+  int32_t* status;                         // device or mapped word, OR-ed with KvCopyStatus bits; may be null
+  int32_t h2d;                             // 1: host -> gpu, 0: gpu -> host
+};
+
+struct KvCopyLaunch {
+  int32_t num_ctas;     // persistent CTAs (each one bulk-copy pipeline)
+  int32_t tile_bytes;   // multiple of 16, <= 32 KiB
+  int32_t engine;       // 0 = TMA bulk pipeline, 1 = SIMT vector ld/st
+};
+
+// Returns cudaSuccess or the launch error. `chunk_bytes`, all strides and
+// offsets must be multiples of 16 for the TMA engine; the SIMT engine accepts
+// any multiple of 4 (and single bytes through its tail path).
+cudaError_t launch_kv_copy(const KvCopyParams& p, const KvCopyLaunch& cfg, cudaStream_t stream);
+
+// Re-statement of the reference's copy kernel shape for baseline timing only:
+// 4 CTAs x 1024 threads, one warp per (layer, pair), lanes move 16 bytes
+// (reference: csrc/transfer.cu:95-158,176-190).
+cudaError_t launch_kv_copy_refshape(const KvCopyParams& p, int num_ctas, cudaStream_t stream);
+
+// true when every address component allows 16-byte bulk copies
+bool kv_copy_tma_eligible(const KvCopyParams& p);
+
+}  // namespace fkv
