@@ -1,0 +1,535 @@
+"""Control plane: per-tier prefix caches and the planner that turns a get/put
+request into a transfer graph.
+
+Behavioural counterpart of the reference's ``CacheEngine`` /
+``GlobalCacheEngine`` (flexkv/cache/cache_engine.py:272-867 tier engine,
+:1109-1232 get, :1718-1997 local get plan, :2000-2081 put, :2488-2701 local put
+plan, :2919-3020 completion / abort, :480-582 take with eviction). The tiers
+are inclusive and write-through: a put lands in the host pool and, when
+enabled, on SSD; evicting from one tier never writes back to another.
+"""
+from __future__ import annotations
+
+import math
+import threading
+from dataclasses import dataclass, field
+from typing import Any, Callable, Dict, List, Optional, Tuple
+
+import numpy as np
+
+from .. import _native
+from ..common.block import SequenceMeta
+from ..common.config import GLOBAL_CONFIG_FROM_ENV, CacheConfig, ModelConfig
+from ..common.debug import EvictionLogAggregator, flexkv_logger
+from ..common.transfer import DeviceType, TransferOp, TransferOpGraph, TransferType
+from .mempool import Mempool, NotEnoughSpaceError
+from .radixtree import RadixTreeIndex
+
+_EMPTY = np.zeros(0, dtype=np.int64)
+
+
+def slot_mapping_to_block_ids(slot_mapping: np.ndarray, tokens_per_block: int) -> np.ndarray:
+    """One GPU block id per block: the engine's flat token slot is
+    ``block_id * tokens_per_block + offset`` (flexkv/cache/cache_engine.py:3338-3340)."""
+    return np.ascontiguousarray(slot_mapping[::tokens_per_block] // tokens_per_block, dtype=np.int64)
+
+
+class CacheEngine:
+    """Prefix index + block pool of one tier."""
+
+    def __init__(self, device_type: DeviceType, num_total_blocks: int, tokens_per_block: int,
+                 evict_ratio: float = 0.0, hit_reward_seconds: float = 0.0, eviction_policy: str = "lru",
+                 slru_threshold: int = 2, evict_start_threshold: float = 1.0,
+                 accel: Optional[bool] = None) -> None:
+        if num_total_blocks <= 0:
+            raise ValueError(f"invalid num_total_blocks: {num_total_blocks}")
+        if tokens_per_block <= 0 or tokens_per_block & (tokens_per_block - 1):
+            raise ValueError(f"tokens_per_block must be a power of two, got {tokens_per_block}")
+        if not 0.0 <= evict_ratio <= 1.0:
+            raise ValueError("evict_ratio must be in [0, 1]")
+        if not 0.0 < evict_start_threshold <= 1.0:
+            raise ValueError("evict_start_threshold must be in (0, 1]")
+        self.device_type = device_type
+        self.num_total_blocks = int(num_total_blocks)
+        self.tokens_per_block = tokens_per_block
+        self.evict_ratio = evict_ratio
+        self.evict_start_threshold = evict_start_threshold
+        self.accel = GLOBAL_CONFIG_FROM_ENV.index_accel if accel is None else accel
+        if self.accel:
+            self.index = _native.C.RadixIndex(tokens_per_block, self.num_total_blocks, eviction_policy,
+                                              float(hit_reward_seconds), int(slru_threshold))
+        else:
+            self.index = RadixTreeIndex(tokens_per_block, self.num_total_blocks, eviction_policy,
+                                        float(hit_reward_seconds), int(slru_threshold))
+        self.mempool = Mempool(self.num_total_blocks, native=self.accel)
+        self.on_evict: List[Callable[[DeviceType, np.ndarray, np.ndarray], None]] = []
+        self.on_insert: List[Callable[[DeviceType, np.ndarray, np.ndarray], None]] = []
+        self.num_evicted_total = 0
+
+    def reset(self) -> None:
+        self.index.reset()
+        self.mempool.reset()
+
+    def match(self, seq: SequenceMeta, update_cache_info: bool = True):
+        return self.index.match_prefix(seq.block_hashes, seq.num_blocks, update_cache_info)
+
+    def insert(self, seq: SequenceMeta, physical_block_ids: np.ndarray, num_insert_blocks: int = -1,
+               is_ready: bool = True, match_result: Any = None):
+        node = self.index.insert(np.ascontiguousarray(physical_block_ids, dtype=np.int64), seq.block_hashes,
+                                 num_insert_blocks, is_ready, match_result)
+        if node is not None and self.on_insert:
+            n = len(physical_block_ids)
+            end = seq.num_blocks if num_insert_blocks < 0 else num_insert_blocks
+            for cb in self.on_insert:
+                cb(self.device_type, np.asarray(physical_block_ids), seq.block_hashes[end - n:end])
+        return node
+
+    def lock_node(self, node) -> None:
+        self.index.lock(node)
+
+    def unlock(self, node) -> None:
+        if self.index.alive(node):
+            self.index.unlock(node)
+
+    def set_ready(self, node, ready: bool = True, ready_length: int = -1) -> None:
+        if self.index.alive(node):
+            self.index.set_ready(node, ready, ready_length)
+
+    def rollback_unready_insert(self, node) -> int:
+        """Drops a node inserted by a plan that never produced its data; its
+        blocks go back to the pool. Returns the number of blocks released."""
+        if node is None or not self.index.alive(node):
+            return 0
+        blocks = self.index.remove_unready_leaf(node)
+        if len(blocks):
+            self.mempool.recycle_blocks(blocks)
+        return int(len(blocks))
+
+    def take(self, num_required_blocks: int, protected_node=None, strict: bool = True) -> np.ndarray:
+        """Allocates blocks, evicting when the pool is short or past the
+        configured utilisation (flexkv/cache/cache_engine.py:480-582)."""
+        n = int(num_required_blocks)
+        if n <= 0:
+            return _EMPTY
+        total, free = self.num_total_blocks, self.mempool.num_free_blocks
+        used = total - free
+        over = used / total >= self.evict_start_threshold and self.evict_start_threshold < 1.0
+        if n > free or over:
+            to_threshold = max(0, used + n - int(math.floor(total * self.evict_start_threshold)))
+            amount = max(n - free, to_threshold, int(total * self.evict_ratio))
+            if amount > 0:
+                locked = protected_node is not None and self.index.alive(protected_node) \
+                    and not self.index.is_root(protected_node)
+                if locked:
+                    self.index.lock(protected_node)
+                try:
+                    blocks, hashes = self.index.evict(amount)
+                finally:
+                    if locked:
+                        self.index.unlock(protected_node)
+                if len(blocks):
+                    self.mempool.recycle_blocks(blocks)
+                    self.num_evicted_total += int(len(blocks))
+                    for cb in self.on_evict:
+                        cb(self.device_type, blocks, hashes)
+        if n > self.mempool.num_free_blocks and strict:
+            raise NotEnoughSpaceError(f"{self.device_type.name}: need {n} blocks, "
+                                      f"{self.mempool.num_free_blocks} free after eviction")
+        return self.mempool.allocate_blocks(min(n, self.mempool.num_free_blocks), strict=False)
+
+    def recycle(self, block_ids: np.ndarray) -> None:
+        if block_ids is not None and len(block_ids):
+            self.mempool.recycle_blocks(block_ids)
+
+
+class TransferPlanHandle:
+    """Exactly one of ``complete`` / ``abort`` runs, once
+    (flexkv/cache/cache_engine.py:236-264)."""
+
+    def __init__(self, complete: Callable[[], None], abort: Callable[[], None]) -> None:
+        self._complete, self._abort = complete, abort
+        self._done = False
+        self._lock = threading.Lock()
+
+    def _once(self) -> bool:
+        with self._lock:
+            if self._done:
+                return False
+            self._done = True
+            return True
+
+    def complete(self) -> None:
+        if self._once():
+            self._complete()
+
+    def abort(self) -> None:
+        if self._once():
+            self._abort()
+
+    def __call__(self) -> None:
+        self.complete()
+
+    @property
+    def finished(self) -> bool:
+        return self._done
+
+
+@dataclass
+class TransferPlan:
+    graph: TransferOpGraph
+    finished_ops_ids: List[int] = field(default_factory=list)
+    # device -> list of (node, ready_length); ready_length 0 = lock only
+    nodes: Dict[DeviceType, List[Tuple[Any, int]]] = field(default_factory=dict)
+    inserted: Dict[DeviceType, List[Any]] = field(default_factory=dict)   # rollback candidates
+    buffer_to_free: Dict[DeviceType, np.ndarray] = field(default_factory=dict)
+    op_callback_dict: Dict[int, Callable] = field(default_factory=dict)
+    num_gpu_blocks_to_transfer: int = 0
+    skipped_gpu_blocks: int = 0
+
+
+def _block_range(token_mask: np.ndarray, tokens_per_block: int) -> Tuple[int, int]:
+    idx = np.flatnonzero(token_mask)
+    if idx.size == 0:
+        return 0, 0
+    return int(idx[0]) // tokens_per_block, int(idx[-1]) // tokens_per_block + 1
+
+
+class GlobalCacheEngine:
+    def __init__(self, cache_config: CacheConfig, model_config: ModelConfig) -> None:
+        self.cache_config = cache_config
+        self.model_config = model_config
+        self.tokens_per_block = cache_config.tokens_per_block
+        self._cache_tree_lock = threading.RLock()
+        env = GLOBAL_CONFIG_FROM_ENV
+        policy = cache_config.eviction_policy or env.eviction_policy
+        common = dict(tokens_per_block=self.tokens_per_block, evict_ratio=env.evict_ratio,
+                      hit_reward_seconds=env.hit_reward_seconds, eviction_policy=policy,
+                      slru_threshold=env.slru_protected_threshold, evict_start_threshold=env.evict_start_threshold)
+        self.cache_engines: Dict[DeviceType, CacheEngine] = {}
+        self.cpu_cache_engine: Optional[CacheEngine] = None
+        self.ssd_cache_engine: Optional[CacheEngine] = None
+        self.remote_cache_engine: Optional[CacheEngine] = None
+        if cache_config.enable_cpu:
+            self.cpu_cache_engine = CacheEngine(DeviceType.CPU, cache_config.num_cpu_blocks, **common)
+            self.cache_engines[DeviceType.CPU] = self.cpu_cache_engine
+        if cache_config.enable_ssd:
+            self.ssd_cache_engine = CacheEngine(DeviceType.SSD, cache_config.num_ssd_blocks, **common)
+            self.cache_engines[DeviceType.SSD] = self.ssd_cache_engine
+        if cache_config.enable_remote and cache_config.num_remote_blocks:
+            self.remote_cache_engine = CacheEngine(DeviceType.REMOTE, cache_config.num_remote_blocks, **common)
+            self.cache_engines[DeviceType.REMOTE] = self.remote_cache_engine
+        if not self.cache_engines:
+            raise ValueError("at least one cache tier must be enabled")
+        if self.cpu_cache_engine is None:
+            raise ValueError("the host tier is the staging area of every other tier and must be enabled")
+        self.peer_directory = None          # set by parallel.peer_directory when GPU prefix sharing is on
+        self._metrics = None
+        self._evict_log = EvictionLogAggregator()
+        for eng in self.cache_engines.values():
+            eng.on_evict.append(self._on_evict)
+        self.event_listeners: List[Any] = []   # objects with publish_stored / publish_removed
+
+    # ---- observers ------------------------------------------------------------
+    def set_metrics_collector(self, collector) -> None:
+        self._metrics = collector
+        self._update_mempool_metrics()
+
+    def _on_evict(self, device: DeviceType, blocks: np.ndarray, hashes: np.ndarray) -> None:
+        self._evict_log.record(device.name, len(blocks))
+        if self._metrics is not None:
+            self._metrics.record_eviction(device.name, len(blocks))
+        for l in self.event_listeners:
+            l.publish_removed(device, hashes)
+
+    def _update_mempool_metrics(self) -> None:
+        if self._metrics is None:
+            return
+        for d, e in self.cache_engines.items():
+            self._metrics.set_mempool(d.name, e.num_total_blocks, e.mempool.num_free_blocks)
+
+    # ---- public planner entry points -----------------------------------------------
+    def reset(self) -> None:
+        with self._cache_tree_lock:
+            for e in self.cache_engines.values():
+                e.reset()
+            self._update_mempool_metrics()
+
+    def _prepare(self, token_ids: np.ndarray, token_mask: Optional[np.ndarray], slot_mapping: Optional[np.ndarray]
+                 ) -> Tuple[np.ndarray, np.ndarray, int]:
+        if token_ids.ndim != 1:
+            raise ValueError("token_ids must be 1-D")
+        token_ids = np.ascontiguousarray(token_ids, dtype=np.int64)
+        if token_mask is None:
+            token_mask = np.ones(token_ids.shape[0], dtype=np.bool_)
+        else:
+            token_mask = np.array(token_mask, dtype=np.bool_, copy=True)
+        if token_mask.shape != token_ids.shape:
+            raise ValueError(f"token_mask has {token_mask.size} entries for {token_ids.size} tokens")
+        if slot_mapping is not None:
+            if slot_mapping.ndim != 1:
+                raise ValueError("slot_mapping must be 1-D")
+            if slot_mapping.size != int(token_mask.sum()):
+                raise ValueError(f"slot_mapping has {slot_mapping.size} entries, token_mask selects "
+                                 f"{int(token_mask.sum())} tokens")
+        aligned = (token_ids.shape[0] // self.tokens_per_block) * self.tokens_per_block
+        token_mask[aligned:] = False
+        return token_ids, token_mask, aligned
+
+    def _empty(self, token_mask: np.ndarray):
+        handle = TransferPlanHandle(lambda: None, lambda: None)
+        return TransferOpGraph.create_empty_graph(), np.zeros_like(token_mask, dtype=np.bool_), handle, {}, -1
+
+    def _finish(self, plan: TransferPlan, is_put: bool):
+        graph = plan.graph
+        if len(plan.finished_ops_ids) == 1:
+            end_op = plan.finished_ops_ids[0]
+        elif plan.finished_ops_ids:
+            end_op = graph.add_virtual_op(plan.finished_ops_ids)
+        else:
+            end_op = -1
+        for dev, lst in plan.nodes.items():
+            for node, _ in lst:
+                self.cache_engines[dev].lock_node(node)
+        handle = TransferPlanHandle(complete=lambda: self._complete_plan(plan, is_put),
+                                    abort=lambda: self._abort_plan(plan))
+        self._update_mempool_metrics()
+        return graph, handle, plan.op_callback_dict, end_op
+
+    def get(self, request_id: int, token_ids: np.ndarray, token_mask: Optional[np.ndarray],
+            slot_mapping: Optional[np.ndarray], dp_client_id: int = 0, namespace: Optional[List[str]] = None,
+            cpu_only: bool = False, prefetch: bool = False):
+        """Returns ``(graph, return_mask, plan_handle, op_callbacks, task_end_op_id)``."""
+        token_ids, token_mask, aligned = self._prepare(token_ids, token_mask, slot_mapping)
+        if aligned == 0 or not token_mask.any():
+            return self._empty(token_mask)
+        tpb = self.tokens_per_block
+        bstart, bend = _block_range(token_mask, tpb)
+        gpu_blocks = None
+        if slot_mapping is not None:
+            gpu_blocks = slot_mapping_to_block_ids(slot_mapping, tpb)[:bend - bstart]
+        seq = SequenceMeta(token_ids[:aligned], tpb, namespace)
+        with self._cache_tree_lock:
+            plan = self._get_impl_local(seq, bstart, bend, gpu_blocks, dp_client_id, cpu_only, prefetch)
+            if plan is None:
+                return self._empty(token_mask)
+            graph, handle, cbs, end_op = self._finish(plan, is_put=False)
+        mask = np.zeros_like(token_mask, dtype=np.bool_)
+        mask[bstart * tpb:(bstart + plan.num_gpu_blocks_to_transfer) * tpb] = True
+        return graph, mask, handle, cbs, end_op
+
+    def put(self, request_id: int, token_ids: np.ndarray, token_mask: Optional[np.ndarray],
+            slot_mapping: Optional[np.ndarray], dp_client_id: int = 0, namespace: Optional[List[str]] = None):
+        token_ids, token_mask, aligned = self._prepare(token_ids, token_mask, slot_mapping)
+        if aligned == 0 or not token_mask.any():
+            return self._empty(token_mask)
+        tpb = self.tokens_per_block
+        bstart, bend = _block_range(token_mask, tpb)
+        if bstart != 0:
+            raise ValueError("put: token_mask must select a prefix of the sequence")
+        gpu_blocks = None
+        if slot_mapping is not None:
+            gpu_blocks = slot_mapping_to_block_ids(slot_mapping, tpb)[:bend]
+        seq = SequenceMeta(token_ids[:aligned], tpb, namespace)
+        with self._cache_tree_lock:
+            plan = self._put_impl_local(seq, bend, gpu_blocks, dp_client_id)
+            if plan is None:
+                return self._empty(token_mask)
+            graph, handle, cbs, end_op = self._finish(plan, is_put=True)
+        mask = np.zeros_like(token_mask, dtype=np.bool_)
+        lo = plan.skipped_gpu_blocks * tpb
+        mask[lo:lo + plan.num_gpu_blocks_to_transfer * tpb] = True
+        return graph, mask, handle, cbs, end_op
+
+    # ---- GET ------------------------------------------------------------------------
+    def _get_impl_local(self, seq: SequenceMeta, bstart: int, bend: int, gpu_blocks: Optional[np.ndarray],
+                        dp_client_id: int, cpu_only: bool, prefetch: bool) -> Optional[TransferPlan]:
+        cpu, ssd = self.cpu_cache_engine, (None if cpu_only else self.ssd_cache_engine)
+        cpu_m = cpu.match(seq)
+        ssd_m = ssd.match(seq) if ssd is not None else None
+        cpu_hit = min(cpu_m.num_ready_matched_blocks, bend)
+        ssd_hit = min(ssd_m.num_ready_matched_blocks, bend) if ssd_m is not None else 0
+        if ssd_hit <= cpu_hit:
+            ssd_m, ssd_hit = None, 0
+        if self._metrics is not None:
+            self._metrics.record_match("CPU", cpu_hit, bend - cpu_hit)
+            if ssd is not None:
+                self._metrics.record_match("SSD", ssd_hit, bend - ssd_hit)
+        end = max(cpu_hit, ssd_hit)
+        f1 = max(0, cpu_hit - bstart)                     # blocks [bstart, cpu_hit) from the host pool
+        f2_lo = max(bstart, cpu_hit)
+        f2 = max(0, end - f2_lo)                          # blocks [f2_lo, end) from SSD
+        if prefetch:
+            f1 = 0
+        if f1 + f2 == 0:
+            return None
+        graph = TransferOpGraph()
+        plan = TransferPlan(graph)
+        cpu_phys = cpu_m.physical_blocks
+        use_gds = bool(self.cache_config.enable_gds) and not prefetch
+        staging = _EMPTY
+        stage_node = None
+        if f2 > 0 and not use_gds:
+            staging = cpu.take(f2, protected_node=cpu_m.last_node, strict=False)
+            if len(staging) < f2:
+                cpu.recycle(staging)
+                if self._metrics is not None:
+                    self._metrics.record_allocation_failure("CPU")
+                if f1 == 0:
+                    return None
+                f2, staging = 0, _EMPTY
+        ops_done: List[int] = []
+        disk_op = None
+        if f2 > 0:
+            ssd_src = ssd_m.physical_blocks[f2_lo:f2_lo + f2]
+            if use_gds:
+                disk_op = TransferOp(graph.graph_id, TransferType.DISK2D, ssd_src,
+                                     gpu_blocks[f1:f1 + f2] if gpu_blocks is not None else _EMPTY,
+                                     dp_client_id=dp_client_id,
+                                     gpu_side=None if gpu_blocks is not None else "dst", gpu_bind="tail")
+            else:
+                disk_op = TransferOp(graph.graph_id, TransferType.DISK2H, ssd_src, staging, dp_client_id=dp_client_id)
+            graph.add_transfer_op(disk_op)
+            plan.nodes.setdefault(DeviceType.SSD, []).append((ssd_m.last_ready_node, 0))
+            if not use_gds:
+                # keep the staged copy as cache content when it extends a fully ready host prefix
+                contiguous = cpu_m.num_matched_blocks == cpu_m.num_ready_matched_blocks == f2_lo
+                if contiguous:
+                    try:
+                        stage_node = cpu.insert(seq, staging, num_insert_blocks=f2_lo + f2, is_ready=False,
+                                                match_result=cpu_m)
+                    except RuntimeError:
+                        stage_node = None
+                if stage_node is not None:
+                    plan.nodes.setdefault(DeviceType.CPU, []).append((stage_node, 0))
+                    plan.inserted.setdefault(DeviceType.CPU, []).append(stage_node)
+                    node, n = stage_node, f2
+                    plan.op_callback_dict[disk_op.op_id] = lambda node=node, n=n: cpu.set_ready(node, True, n)
+                else:
+                    plan.buffer_to_free[DeviceType.CPU] = staging
+        if prefetch:
+            if disk_op is None:
+                return None
+            plan.finished_ops_ids = [disk_op.op_id]
+            plan.num_gpu_blocks_to_transfer = f2
+            return plan
+        h2d_src = np.concatenate([cpu_phys[bstart:bstart + f1], staging]) if not use_gds else cpu_phys[bstart:bstart + f1]
+        n_h2d = int(h2d_src.size)
+        if n_h2d > 0:
+            h2d = TransferOp(graph.graph_id, TransferType.H2D, h2d_src,
+                             gpu_blocks[:n_h2d] if gpu_blocks is not None else _EMPTY, dp_client_id=dp_client_id,
+                             gpu_side=None if gpu_blocks is not None else "dst", gpu_bind="head")
+            graph.add_transfer_op(h2d)
+            if disk_op is not None and not use_gds:
+                graph.add_dependency(h2d.op_id, disk_op.op_id)
+            ops_done.append(h2d.op_id)
+            if f1 > 0:
+                plan.nodes.setdefault(DeviceType.CPU, []).append((cpu_m.last_ready_node, 0))
+        if disk_op is not None and use_gds:
+            ops_done.append(disk_op.op_id)
+        plan.finished_ops_ids = ops_done
+        plan.num_gpu_blocks_to_transfer = f1 + f2
+        return plan
+
+    # ---- PUT ------------------------------------------------------------------------
+    def _put_impl_local(self, seq: SequenceMeta, nb: int, gpu_blocks: Optional[np.ndarray], dp_client_id: int
+                        ) -> Optional[TransferPlan]:
+        cpu, ssd = self.cpu_cache_engine, self.ssd_cache_engine
+        # matched (ready or still in flight) blocks are never offloaded twice
+        cpu_m = cpu.match(seq)
+        cpu_matched = min(cpu_m.num_matched_blocks, nb)
+        need_cpu = nb - cpu_matched
+        ssd_m, ssd_matched, need_ssd = None, 0, 0
+        if ssd is not None:
+            ssd_m = ssd.match(seq)
+            ssd_matched = min(ssd_m.num_matched_blocks, nb)
+            need_ssd = nb - ssd_matched
+            # host blocks that another task is still filling cannot feed a disk write
+            if need_ssd > 0 and nb - need_ssd < cpu_matched and cpu_m.num_ready_matched_blocks < cpu_matched:
+                need_ssd = 0
+        if need_cpu == 0 and need_ssd == 0:
+            return None
+        cpu_new = cpu.take(need_cpu, protected_node=cpu_m.last_node, strict=False) if need_cpu else _EMPTY
+        if len(cpu_new) < need_cpu:
+            cpu.recycle(cpu_new)
+            if self._metrics is not None:
+                self._metrics.record_allocation_failure("CPU")
+            return None
+        ssd_new = _EMPTY
+        if need_ssd:
+            ssd_new = ssd.take(need_ssd, protected_node=ssd_m.last_node, strict=False)
+            if len(ssd_new) < need_ssd:
+                ssd.recycle(ssd_new)
+                cpu.recycle(cpu_new)
+                if self._metrics is not None:
+                    self._metrics.record_allocation_failure("SSD")
+                return None
+        graph = TransferOpGraph()
+        plan = TransferPlan(graph)
+        d2h = None
+        if need_cpu:
+            late = gpu_blocks is None
+            d2h = TransferOp(graph.graph_id, TransferType.D2H,
+                             _EMPTY if late else gpu_blocks[cpu_matched:nb], cpu_new, dp_client_id=dp_client_id,
+                             gpu_side="src" if late else None, gpu_bind="head")
+            graph.add_transfer_op(d2h)
+            try:
+                cpu_node = cpu.insert(seq, cpu_new, num_insert_blocks=nb, is_ready=False, match_result=cpu_m)
+            except RuntimeError:
+                cpu.recycle(cpu_new)
+                ssd and ssd.recycle(ssd_new)
+                raise
+            plan.nodes.setdefault(DeviceType.CPU, []).append((cpu_node, 0))
+            plan.inserted.setdefault(DeviceType.CPU, []).append(cpu_node)
+            plan.op_callback_dict[d2h.op_id] = lambda node=cpu_node, n=need_cpu: cpu.set_ready(node, True, n)
+        elif not cpu.index.is_root(cpu_m.last_node):
+            plan.nodes.setdefault(DeviceType.CPU, []).append((cpu_m.last_node, 0))
+        if need_ssd:
+            cpu_all = np.concatenate([cpu_m.physical_blocks[:cpu_matched], cpu_new])
+            disk = TransferOp(graph.graph_id, TransferType.H2DISK, cpu_all[nb - need_ssd:nb], ssd_new,
+                              dp_client_id=dp_client_id)
+            graph.add_transfer_op(disk)
+            if d2h is not None:
+                graph.add_dependency(disk.op_id, d2h.op_id)
+            ssd_node = ssd.insert(seq, ssd_new, num_insert_blocks=nb, is_ready=False, match_result=ssd_m)
+            plan.nodes.setdefault(DeviceType.SSD, []).append((ssd_node, 0))
+            plan.inserted.setdefault(DeviceType.SSD, []).append(ssd_node)
+            plan.op_callback_dict[disk.op_id] = lambda node=ssd_node, n=need_ssd: ssd.set_ready(node, True, n)
+            if d2h is None:
+                plan.finished_ops_ids = [disk.op_id]
+        if d2h is not None:
+            plan.finished_ops_ids = [d2h.op_id]     # the caller may see success before the disk write ends
+        plan.skipped_gpu_blocks = cpu_matched
+        plan.num_gpu_blocks_to_transfer = need_cpu
+        return plan
+
+    # ---- plan end --------------------------------------------------------------------
+    def _complete_plan(self, plan: TransferPlan, is_put: bool) -> None:
+        with self._cache_tree_lock:
+            for dev, lst in plan.nodes.items():
+                for node, _ in lst:
+                    self.cache_engines[dev].unlock(node)
+            for dev, ids in plan.buffer_to_free.items():
+                self.cache_engines[dev].recycle(ids)
+            # a node whose op callback never ran (op skipped) stays unready; drop it
+            for dev, lst in plan.inserted.items():
+                for node in lst:
+                    eng = self.cache_engines[dev]
+                    if eng.index.alive(node) and not eng.index.node_ready(node):
+                        eng.rollback_unready_insert(node)
+            self._update_mempool_metrics()
+
+    def _abort_plan(self, plan: TransferPlan) -> None:
+        with self._cache_tree_lock:
+            for dev, lst in plan.nodes.items():
+                for node, _ in lst:
+                    self.cache_engines[dev].unlock(node)
+            for dev, lst in plan.inserted.items():
+                for node in lst:
+                    self.cache_engines[dev].rollback_unready_insert(node)
+            for dev, ids in plan.buffer_to_free.items():
+                self.cache_engines[dev].recycle(ids)
+            self._update_mempool_metrics()
+
+    def run_op_callback(self, cb: Callable) -> None:
+        with self._cache_tree_lock:
+            cb()

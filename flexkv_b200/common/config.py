@@ -1,0 +1,494 @@
+"""Configuration: model/cache dataclasses, the ``FLEXKV_*`` environment table,
+user config files and GB -> block conversion.
+
+Field and variable names match the reference so that existing deployments can
+switch without renaming anything (flexkv/common/config.py:122-427 ModelConfig,
+:430-571 RankInfo, :623-746 CacheConfig, :748-841 environment table,
+:843-944 UserConfig, :946-1246 conversion helpers). Keys that only tuned the
+reference's copy-engine paths are accepted and ignored: every GPU<->host move
+here is one sm_100a kernel.
+"""
+from __future__ import annotations
+
+import json
+import os
+from argparse import Namespace
+from dataclasses import dataclass, field, fields
+from typing import Any, Dict, List, Optional, Tuple, Union
+
+import torch
+
+from .storage import KVCacheLayoutType
+
+_DTYPE_ALIASES = {
+    "bf16": torch.bfloat16, "bfloat16": torch.bfloat16, "fp16": torch.float16, "float16": torch.float16,
+    "half": torch.float16, "fp32": torch.float32, "float32": torch.float32, "float": torch.float32,
+    "fp8": torch.float8_e4m3fn, "fp8_e4m3": torch.float8_e4m3fn, "fp8_e5m2": torch.float8_e5m2,
+    "uint8": torch.uint8, "int8": torch.int8,
+    # byte-exact NVFP4: the packed cache is moved as bytes, never interpreted
+    "nvfp4": torch.uint8, "fp4": torch.uint8, "e2m1": torch.uint8, "fp4_e2m1": torch.uint8,
+}
+NVFP4_NAMES = ("nvfp4", "fp4", "e2m1", "fp4_e2m1")
+
+
+def parse_dtype(name: Union[str, torch.dtype]) -> torch.dtype:
+    if isinstance(name, torch.dtype):
+        return name
+    key = str(name).lower().replace("torch.", "")
+    if key not in _DTYPE_ALIASES:
+        raise ValueError(f"unsupported kv cache dtype: {name}")
+    return _DTYPE_ALIASES[key]
+
+
+def nvfp4_head_bytes(head_size: int) -> int:
+    """Bytes per token per head of a packed NVFP4 cache: e2m1 nibbles plus one
+    e4m3 scale per 16 elements (flexkv/integration/config.py:24-36,142-150)."""
+    return head_size // 2 + head_size // 16
+
+
+@dataclass
+class LayerGroupSpec:
+    """A run of layers with its own KV shape (e.g. an indexer or a compressed-KV group)."""
+    num_layers: int
+    num_kv_heads: int
+    head_size: int
+    kv_dim: int = 2
+    dtype: Optional[torch.dtype] = None
+    compress_ratio: int = 1           # tokens stored per block = tokens_per_block / ratio
+    layer_ids: Optional[List[int]] = None
+    name: str = ""
+
+
+@dataclass
+class ModelConfig:
+    num_layers: int = 1
+    num_kv_heads: int = 1
+    head_size: int = 1
+    kv_dim: int = 2
+    dtype: torch.dtype = torch.bfloat16
+    use_mla: bool = False
+    tp_size: int = 1
+    pp_size: int = 1
+    dp_size: int = 1
+    enable_dp_attention: bool = False
+    attn_cp_size: int = 1
+    cp_size: int = 1
+    nnodes: int = 1
+    master_host: str = "localhost"
+    master_ports: Tuple[str, str, str] = ("5556", "5557", "5558")
+    use_trtllm_subprocess: bool = False
+    trtllm_subprocess_host: str = "localhost"
+    trtllm_subprocess_ports: Tuple[str, str, str] = ("6667", "6668", "6669")
+    instance_num: int = 1
+    layer_groups: Optional[List[LayerGroupSpec]] = None
+    _frozen: bool = field(default=False, init=False, repr=False, compare=False)
+
+    def __post_init__(self) -> None:
+        if self.use_mla:
+            object.__setattr__(self, "kv_dim", 1)
+        elif self.kv_dim == 1 and self.num_kv_heads == 1:
+            object.__setattr__(self, "use_mla", True)
+
+    def __setattr__(self, name: str, value: Any) -> None:
+        if getattr(self, "_frozen", False) and name != "_frozen":
+            raise AttributeError(f"ModelConfig is frozen; cannot set {name}")
+        object.__setattr__(self, name, value)
+
+    def freeze(self) -> None:
+        if self.cp_size == 1 and self.attn_cp_size != 1:
+            self.cp_size = self.attn_cp_size
+        elif self.attn_cp_size == 1 and self.cp_size != 1:
+            self.attn_cp_size = self.cp_size
+        elif self.cp_size != self.attn_cp_size:
+            raise ValueError("cp_size and attn_cp_size disagree")
+        if self.nnodes < 1 or self.total_gpus % self.nnodes:
+            raise ValueError("total GPUs must divide evenly over nnodes")
+        self._validate_layer_groups()
+        object.__setattr__(self, "_frozen", True)
+
+    def _validate_layer_groups(self) -> None:
+        if not self.layer_groups:
+            return
+        for g in self.layer_groups:
+            if g.num_layers <= 0 or g.head_size <= 0 or g.num_kv_heads <= 0:
+                raise ValueError(f"bad layer group {g}")
+            if g.compress_ratio < 1:
+                raise ValueError("compress_ratio must be >= 1")
+
+    # ---- topology -------------------------------------------------------------
+    @property
+    def total_gpus(self) -> int:
+        return self.tp_size * self.cp_size * self.pp_size * self.dp_size
+
+    @property
+    def total_clients(self) -> int:
+        return self.dp_size * self.instance_num
+
+    @property
+    def gpus_per_node(self) -> int:
+        return max(1, self.total_gpus // self.nnodes)
+
+    @property
+    def effective_tp_size(self) -> int:
+        """Slices of one host block: every (cp_rank, tp_rank) pair owns one."""
+        return self.tp_size * self.cp_size
+
+    @property
+    def nnodes_per_tp_group(self) -> int:
+        return max(1, (self.effective_tp_size + self.gpus_per_node - 1) // self.gpus_per_node)
+
+    @property
+    def effective_tp_size_per_node(self) -> int:
+        return self.effective_tp_size // self.nnodes_per_tp_group
+
+    @property
+    def tp_size_per_node(self) -> int:
+        return max(1, self.tp_size // self.nnodes_per_tp_group)
+
+    @property
+    def num_layers_per_pp_stage(self) -> int:
+        return self.num_layers // self.pp_size
+
+    # ---- sizes ----------------------------------------------------------------
+    @property
+    def bytes_per_token_per_layer(self) -> int:
+        return self.kv_dim * self.num_kv_heads * self.head_size * self.dtype.itemsize
+
+    @property
+    def token_size_in_bytes(self) -> int:
+        """Bytes of KV one token occupies across all layers (all TP ranks together)."""
+        if self.layer_groups:
+            total = 0
+            for g in self.layer_groups:
+                dt = g.dtype or self.dtype
+                total += g.num_layers * g.kv_dim * g.num_kv_heads * g.head_size * dt.itemsize // g.compress_ratio
+            return total
+        return self.num_layers * self.bytes_per_token_per_layer
+
+    @property
+    def token_size_in_bytes_per_pp_stage(self) -> int:
+        return self.token_size_in_bytes // self.pp_size
+
+    def block_size_in_bytes(self, tokens_per_block: int) -> int:
+        if self.layer_groups:
+            total = 0
+            for g in self.layer_groups:
+                dt = g.dtype or self.dtype
+                total += g.num_layers * g.kv_dim * (tokens_per_block // g.compress_ratio) * g.num_kv_heads \
+                    * g.head_size * dt.itemsize
+            return total
+        return self.token_size_in_bytes * tokens_per_block
+
+
+@dataclass
+class RankInfo:
+    """Where one engine worker sits in the tp x cp x pp x dp grid
+    (flexkv/common/config.py:430-571)."""
+    model_config: ModelConfig
+    tp_rank: int = 0
+    cp_rank: int = 0
+    pp_rank: int = 0
+    dp_rank: int = 0
+    instance_id: int = 0
+    node_rank: int = 0
+    device_id: int = 0
+
+    @property
+    def dp_client_id(self) -> int:
+        return self.instance_id * self.model_config.dp_size + self.dp_rank
+
+    @property
+    def effective_tp_rank(self) -> int:
+        return self.cp_rank * self.model_config.tp_size + self.tp_rank
+
+    @property
+    def intra_client_id(self) -> int:
+        m = self.model_config
+        return self.pp_rank * m.effective_tp_size + self.effective_tp_rank
+
+
+@dataclass
+class SWAPoolConfig:
+    """Sliding-window side pool (one page per window snapshot)."""
+    enabled: bool = False
+    num_cpu_slots: int = 0
+    num_ssd_slots: int = 0
+    num_remote_slots: int = 0
+    page_bytes: int = 0
+    window_blocks: int = 1
+
+    def for_cache_tier(self, device_type) -> Optional["SWAPoolConfig"]:
+        return self if self.enabled else None
+
+
+@dataclass
+class CacheConfig:
+    tokens_per_block: int = 16
+    eviction_policy: str = "lru"
+    enable_cpu: bool = True
+    enable_ssd: bool = False
+    enable_gds: bool = False
+    enable_nixl: bool = False
+    nixl_extra_config: Optional[Dict[str, Any]] = None
+    enable_remote: bool = False
+    enable_kv_sharing: bool = False
+    enable_p2p_cpu: bool = False
+    enable_p2p_ssd: bool = False
+    enable_3rd_remote: bool = False
+    # B200-native additions: cross-GPU prefix reuse over NVLink and quantised offload
+    enable_p2p_gpu: bool = False
+    offload_quant: str = "none"            # none | fp8_e4m3 (block-scaled, 1 fp32 scale / 128 values)
+    enable_compression: bool = False       # lossless exponent-packing codec on the host tier
+    distributed_node_id: int = -1
+    num_tmp_cpu_blocks: int = 500
+    use_hugepage_cpu_buffer: bool = False
+    use_hugepage_tmp_buffer: bool = False
+    hugepage_size_bytes: int = 2 * 1024 * 1024
+    num_cpu_blocks: int = 1000000
+    num_ssd_blocks: int = 10000000
+    num_remote_blocks: Optional[int] = None
+    num_local_blocks: int = 1000000
+    ssd_cache_dir: Optional[Union[str, List[str]]] = None
+    remote_cache_size_mode: str = "file_size"
+    remote_file_size: Optional[int] = None
+    remote_file_num: Optional[int] = None
+    remote_file_prefix: Optional[str] = None
+    remote_cache_path: Optional[Union[str, List[str]]] = None
+    remote_config_custom: Optional[Dict[str, Any]] = None
+    local_zmq_ip: str = "127.0.0.1"
+    local_zmq_port: int = 5555
+    redis_host: str = "127.0.0.1"
+    redis_port: int = 6379
+    local_ip: str = "127.0.0.1"
+    redis_password: Optional[str] = None
+    node_ttl_seconds: int = 30
+    mooncake_config_path: Optional[str] = None
+    use_mooncake_store_backend: bool = False
+    mooncake_store_config_path: Optional[str] = None
+    _user_cpu_cache_gb: float = 0
+    _user_ssd_cache_gb: float = 0
+    swa: Optional[SWAPoolConfig] = None
+    enable_swa_transfer: bool = False
+
+    def __post_init__(self) -> None:
+        if self.tokens_per_block <= 0 or self.tokens_per_block & (self.tokens_per_block - 1):
+            raise ValueError("tokens_per_block must be a power of two")
+        self.enable_kv_sharing = self.enable_p2p_cpu or self.enable_p2p_ssd or self.enable_3rd_remote
+        self.enable_remote = self.enable_remote or self.enable_3rd_remote or self.use_mooncake_store_backend
+        if self.enable_gds and not self.enable_ssd:
+            raise ValueError("enable_gds requires enable_ssd")
+        if self.offload_quant not in ("none", "fp8_e4m3"):
+            raise ValueError(f"unknown offload_quant {self.offload_quant}")
+
+
+def _env(name: str, default: Any, cast=None) -> Any:
+    v = os.getenv(name)
+    if v is None:
+        return default
+    if cast is bool:
+        return bool(int(v))
+    return (cast or type(default))(v)
+
+
+def load_env_config() -> Namespace:
+    return Namespace(
+        instance_num=_env("FLEXKV_INSTANCE_NUM", 1),
+        instance_id=_env("FLEXKV_INSTANCE_ID", 0),
+        enable_metrics=_env("FLEXKV_ENABLE_METRICS", False, bool),
+        cpp_metrics_port=_env("FLEXKV_CPP_METRICS_PORT", 8081),
+        py_metrics_port=_env("FLEXKV_PY_METRICS_PORT", 8080),
+        server_client_mode=_env("FLEXKV_SERVER_CLIENT_MODE", False, bool),
+        server_launch_mode=_env("FLEXKV_SERVER_LAUNCH_MODE", "embedded").lower(),
+        server_recv_port=_env("FLEXKV_SERVER_RECV_PORT", "ipc:///tmp/flexkv_server"),
+        index_accel=_env("FLEXKV_INDEX_ACCEL", True, bool),
+        cpu_layout_type=KVCacheLayoutType(_env("FLEXKV_CPU_LAYOUT", "BLOCKFIRST").upper()),
+        ssd_layout_type=KVCacheLayoutType(_env("FLEXKV_SSD_LAYOUT", "BLOCKFIRST").upper()),
+        remote_layout_type=KVCacheLayoutType(_env("FLEXKV_REMOTE_LAYOUT", "BLOCKFIRST").upper()),
+        gds_layout_type=KVCacheLayoutType(_env("FLEXKV_GDS_LAYOUT", "BLOCKFIRST").upper()),
+        enable_layerwise_transfer=_env("FLEXKV_ENABLE_LAYERWISE_TRANSFER", False, bool),
+        # copy kernel launch shape; the bulk-copy pipeline wants a CTA per ~4 GB/s of link
+        transfer_num_cta_h2d=_env("FLEXKV_TRANSFER_NUM_CTA_H2D", 16),
+        transfer_num_cta_d2h=_env("FLEXKV_TRANSFER_NUM_CTA_D2H", 16),
+        transfer_tile_bytes=_env("FLEXKV_TRANSFER_TILE_BYTES", 16384),
+        transfer_engine=_env("FLEXKV_TRANSFER_ENGINE", "tma").lower(),   # tma | simt
+        # accepted for compatibility, unused: copy-engine tuning of the reference
+        use_ce_transfer_h2d=_env("FLEXKV_USE_CE_TRANSFER_H2D", False, bool),
+        use_ce_transfer_d2h=_env("FLEXKV_USE_CE_TRANSFER_D2H", False, bool),
+        ce_segment_threshold=_env("FLEXKV_CE_SEGMENT_THRESHOLD", 8),
+        ssd_io_opt=_env("FLEXKV_SSD_IO_OPT", True, bool),
+        ssd_io_threads=_env("FLEXKV_SSD_IO_THREADS", 8),
+        iouring_entries=_env("FLEXKV_IOURING_ENTRIES", 512),
+        iouring_flags=_env("FLEXKV_IOURING_FLAGS", 0),
+        max_file_size_gb=_env("FLEXKV_MAX_FILE_SIZE_GB", -1.0),
+        evict_ratio=_env("FLEXKV_EVICT_RATIO", 0.0),
+        evict_start_threshold=_env("FLEXKV_EVICT_START_THRESHOLD", 1.0),
+        hit_reward_seconds=_env("FLEXKV_HIT_REWARD_SECONDS", 0),
+        eviction_policy=_env("FLEXKV_EVICTION_POLICY", "lru"),
+        slru_protected_threshold=_env("FLEXKV_SLRU_PROTECTED_THRESHOLD", 2),
+        enable_mps=_env("FLEXKV_ENABLE_MPS", False, bool),
+        enable_collective_sync=_env("FLEXKV_ENABLE_COLLECTIVE_SYNC", True, bool),
+        enable_trace=_env("FLEXKV_ENABLE_TRACE", False, bool),
+        trace_file_path=_env("FLEXKV_TRACE_FILE_PATH", "./flexkv_trace.log"),
+        trace_max_file_size_mb=_env("FLEXKV_TRACE_MAX_FILE_SIZE_MB", 100),
+        trace_max_files=_env("FLEXKV_TRACE_MAX_FILES", 5),
+        trace_flush_interval_ms=_env("FLEXKV_TRACE_FLUSH_INTERVAL_MS", 1000),
+        enable_transfer_trace=_env("FLEXKV_TRANSFER_TRACE", False, bool),
+        refresh_batch_size=_env("FLEXKV_REFRESH_BATCH_SIZE", 256),
+        rebuild_interval_ms=_env("FLEXKV_REBUILD_INTERVAL_MS", 2000),
+        idle_sleep_ms=_env("FLEXKV_IDLE_SLEEP_MS", 10),
+        lease_ttl_ms=_env("FLEXKV_LEASE_TTL_MS", 30000),
+        safety_ttl_ms=_env("FLEXKV_SAFETY_TTL_MS", 100),
+        renew_lease_ms=_env("FLEXKV_RENEW_LEASE_MS", 4000),
+        reset_barrier_timeout_ms=_env("FLEXKV_RESET_BARRIER_TIMEOUT_MS", 60000),
+        reset_barrier_poll_ms=_env("FLEXKV_RESET_BARRIER_POLL_MS", 50),
+        enable_compression=_env("FLEXKV_ENABLE_NVCOMP", False, bool),
+        kv_shared_across_ranks_mode=_env("FLEXKV_KV_SHARED_ACROSS_RANKS_MODE", "sharded"),
+        layerwise_notify_mode=_env("FLEXKV_LAYERWISE_NOTIFY_MODE", "hostfunc"),
+        worker_shutdown_timeout_s=_env("FLEXKV_WORKER_SHUTDOWN_TIMEOUT_S", 600.0),
+        transfer_manager_shutdown_timeout_s=_env("FLEXKV_TRANSFER_MANAGER_SHUTDOWN_TIMEOUT_S", 900.0),
+        log_level=_env("FLEXKV_LOG_LEVEL", "INFO"),
+        task_ttl_seconds=_env("FLEXKV_TASK_TTL_SECONDS", 1800),
+    )
+
+
+GLOBAL_CONFIG_FROM_ENV: Namespace = load_env_config()
+
+
+@dataclass
+class UserConfig:
+    """What a deployment sets: sizes in GB, directories and feature switches
+    (file at ``FLEXKV_CONFIG_PATH`` as json or yaml, or ``FLEXKV_*`` variables)."""
+    cpu_cache_gb: float = 16
+    ssd_cache_gb: float = 0
+    ssd_cache_dir: Union[str, List[str]] = "/data/flexkv_ssd/"
+    enable_gds: bool = False
+    use_hugepage_cpu_buffer: bool = False
+    use_hugepage_tmp_buffer: bool = False
+    hugepage_size_bytes: int = 2 * 1024 * 1024
+    enable_p2p_cpu: bool = False
+    enable_p2p_ssd: bool = False
+    enable_p2p_gpu: bool = False
+    redis_host: str = "127.0.0.1"
+    redis_port: int = 6379
+    redis_password: Optional[str] = None
+    local_ip: str = "127.0.0.1"
+    kv_cache_dtype: Optional[str] = None
+    offload_quant: str = "none"
+    overrides: Dict[str, Any] = field(default_factory=dict)
+
+    def __post_init__(self) -> None:
+        if self.cpu_cache_gb <= 0:
+            raise ValueError("cpu_cache_gb must be positive")
+        if self.ssd_cache_gb < 0:
+            raise ValueError("ssd_cache_gb must be non-negative")
+        if 0 < self.ssd_cache_gb <= self.cpu_cache_gb:
+            raise ValueError("ssd_cache_gb must exceed cpu_cache_gb when the SSD tier is on")
+
+
+def parse_path_list(path_str: Union[str, List[str]]) -> List[str]:
+    if isinstance(path_str, (list, tuple)):
+        return [str(p) for p in path_str]
+    return [p.strip() for p in str(path_str).split(";") if p.strip()]
+
+
+def _coerce(value: Any, like: Any) -> Any:
+    if isinstance(like, bool):
+        if isinstance(value, str):
+            return value.strip().lower() in ("1", "true", "yes", "on")
+        return bool(value)
+    if isinstance(like, KVCacheLayoutType):
+        return KVCacheLayoutType(str(value).upper())
+    if isinstance(like, int) and not isinstance(like, bool):
+        return int(value)
+    if isinstance(like, float):
+        return float(value)
+    return value
+
+
+def load_user_config_from_file(path: str) -> UserConfig:
+    with open(path) as f:
+        if path.endswith((".yaml", ".yml")):
+            import yaml
+            raw = yaml.safe_load(f) or {}
+        else:
+            raw = json.load(f)
+    known = {f.name for f in fields(UserConfig)}
+    kw = {k: v for k, v in raw.items() if k in known and k != "overrides"}
+    cfg = UserConfig(**kw)
+    # anything else addresses the environment table by its attribute name
+    cfg.overrides = {k: v for k, v in raw.items() if k not in known}
+    return cfg
+
+
+def load_user_config_from_env() -> UserConfig:
+    path = os.getenv("FLEXKV_CONFIG_PATH")
+    if path:
+        return load_user_config_from_file(path)
+    kw: Dict[str, Any] = {}
+    for f in fields(UserConfig):
+        if f.name == "overrides":
+            continue
+        v = os.getenv("FLEXKV_" + f.name.upper())
+        if v is not None:
+            kw[f.name] = _coerce(v, f.default) if f.default is not None else v
+    return UserConfig(**kw)
+
+
+def apply_overrides(user: UserConfig, env: Optional[Namespace] = None) -> None:
+    env = env if env is not None else GLOBAL_CONFIG_FROM_ENV
+    for k, v in user.overrides.items():
+        key = k[len("override_"):] if k.startswith("override_") else k
+        if not hasattr(env, key):
+            raise ValueError(f"unknown config key: {k}")
+        setattr(env, key, _coerce(v, getattr(env, key)))
+
+
+def convert_to_block_num(size_in_gb: float, block_size_in_bytes: int) -> int:
+    return int(size_in_gb * (1 << 30)) // max(1, block_size_in_bytes)
+
+
+def update_default_config_from_user_config(model_config: ModelConfig, cache_config: CacheConfig,
+                                           user_config: UserConfig) -> None:
+    """Fills block counts and tier switches of ``cache_config`` from sizes in GB."""
+    if user_config.kv_cache_dtype and not model_config._frozen:
+        model_config.dtype = parse_dtype(user_config.kv_cache_dtype)
+    block_bytes = model_config.block_size_in_bytes(cache_config.tokens_per_block)
+    if cache_config.offload_quant == "none" and user_config.offload_quant != "none":
+        cache_config.offload_quant = user_config.offload_quant
+    cache_config._user_cpu_cache_gb = user_config.cpu_cache_gb
+    cache_config._user_ssd_cache_gb = user_config.ssd_cache_gb
+    cache_config.num_cpu_blocks = convert_to_block_num(user_config.cpu_cache_gb, block_bytes)
+    cache_config.enable_cpu = True
+    cache_config.use_hugepage_cpu_buffer = user_config.use_hugepage_cpu_buffer
+    cache_config.use_hugepage_tmp_buffer = user_config.use_hugepage_tmp_buffer
+    cache_config.hugepage_size_bytes = user_config.hugepage_size_bytes
+    if user_config.ssd_cache_gb > 0:
+        dirs = parse_path_list(user_config.ssd_cache_dir)
+        cache_config.enable_ssd = True
+        cache_config.ssd_cache_dir = dirs
+        n = convert_to_block_num(user_config.ssd_cache_gb, block_bytes)
+        cache_config.num_ssd_blocks = n - n % max(1, len(dirs))
+        cache_config.enable_gds = user_config.enable_gds
+    else:
+        cache_config.enable_ssd = False
+        cache_config.num_ssd_blocks = 0
+    cache_config.enable_p2p_cpu = user_config.enable_p2p_cpu
+    cache_config.enable_p2p_ssd = user_config.enable_p2p_ssd
+    cache_config.enable_p2p_gpu = user_config.enable_p2p_gpu
+    cache_config.redis_host = user_config.redis_host
+    cache_config.redis_port = user_config.redis_port
+    cache_config.redis_password = user_config.redis_password
+    cache_config.local_ip = user_config.local_ip
+    cache_config.__post_init__()
+    apply_overrides(user_config)
+
+
+def recompute_block_counts(model_config: ModelConfig, cache_config: CacheConfig) -> None:
+    """Called when layer groups become known after the first sizing."""
+    block_bytes = model_config.block_size_in_bytes(cache_config.tokens_per_block)
+    if cache_config._user_cpu_cache_gb:
+        cache_config.num_cpu_blocks = convert_to_block_num(cache_config._user_cpu_cache_gb, block_bytes)
+    if cache_config._user_ssd_cache_gb and cache_config.enable_ssd:
+        dirs = parse_path_list(cache_config.ssd_cache_dir or [])
+        n = convert_to_block_num(cache_config._user_ssd_cache_gb, block_bytes)
+        cache_config.num_ssd_blocks = n - n % max(1, len(dirs))

@@ -1,0 +1,101 @@
+"""Logging helpers: one package logger honouring ``FLEXKV_LOG_LEVEL`` and
+``FLEXKV_LOGGING_PREFIX``, structured ``key=value`` operation logs, an eviction
+log aggregator and a timing decorator (flexkv/common/debug.py:129-283,360;
+csrc/logging.cpp:50-104)."""
+from __future__ import annotations
+
+import functools
+import logging
+import os
+import threading
+import time
+from typing import Any, Callable, Dict, Optional
+
+_LEVELS = {"TRACE": 5, "DEBUG": logging.DEBUG, "INFO": logging.INFO, "WARN": logging.WARNING,
+           "WARNING": logging.WARNING, "ERROR": logging.ERROR, "CRITICAL": logging.CRITICAL, "OFF": 100}
+
+
+def _make_logger() -> logging.Logger:
+    lg = logging.getLogger("flexkv")
+    if not lg.handlers:
+        h = logging.StreamHandler()
+        prefix = os.getenv("FLEXKV_LOGGING_PREFIX", "FLEXKV")
+        h.setFormatter(logging.Formatter(f"[{prefix}] %(levelname)s %(asctime)s.%(msecs)03d "
+                                         f"[%(filename)s:%(lineno)d] %(message)s", "%m-%d %H:%M:%S"))
+        lg.addHandler(h)
+        lg.propagate = False
+    lg.setLevel(_LEVELS.get(os.getenv("FLEXKV_LOG_LEVEL", "INFO").upper(), logging.INFO))
+    return lg
+
+
+flexkv_logger = _make_logger()
+
+
+def set_log_level(level: str) -> None:
+    flexkv_logger.setLevel(_LEVELS.get(level.upper(), logging.INFO))
+
+
+def format_op_log(operation: str, act: str, status: str, **kv: Any) -> str:
+    """``operation=put act=launch status=ok task_id=3 ...``"""
+    parts = [f"operation={operation}", f"act={act}", f"status={status}"]
+    parts += [f"{k}={v}" for k, v in kv.items()]
+    return " ".join(parts)
+
+
+def log_op(operation: str, act: str, status: str, level: int = logging.DEBUG, **kv: Any) -> None:
+    if flexkv_logger.isEnabledFor(level):
+        flexkv_logger.log(level, format_op_log(operation, act, status, **kv))
+
+
+class EvictionLogAggregator:
+    """Batches eviction events so a storm of small evictions prints one line per interval."""
+
+    def __init__(self, interval_s: float = 5.0) -> None:
+        self.interval_s = interval_s
+        self._lock = threading.Lock()
+        self._counts: Dict[str, int] = {}
+        self._events: Dict[str, int] = {}
+        self._last = time.monotonic()
+
+    def record(self, tier: str, num_blocks: int) -> Optional[str]:
+        with self._lock:
+            self._counts[tier] = self._counts.get(tier, 0) + int(num_blocks)
+            self._events[tier] = self._events.get(tier, 0) + 1
+            now = time.monotonic()
+            if now - self._last < self.interval_s:
+                return None
+            self._last = now
+            msg = " ".join(f"{t}:blocks={self._counts[t]},events={self._events[t]}" for t in sorted(self._counts))
+            self._counts.clear()
+            self._events.clear()
+        line = format_op_log("evict", "aggregate", "ok", detail=msg)
+        flexkv_logger.info(line)
+        return line
+
+    def flush(self) -> Optional[str]:
+        with self._lock:
+            if not self._counts:
+                return None
+            msg = " ".join(f"{t}:blocks={self._counts[t]},events={self._events[t]}" for t in sorted(self._counts))
+            self._counts.clear()
+            self._events.clear()
+        line = format_op_log("evict", "aggregate", "ok", detail=msg)
+        flexkv_logger.info(line)
+        return line
+
+
+def debug_timing(name: Optional[str] = None) -> Callable:
+    def deco(fn: Callable) -> Callable:
+        label = name or fn.__qualname__
+
+        @functools.wraps(fn)
+        def wrapper(*a: Any, **k: Any) -> Any:
+            if not flexkv_logger.isEnabledFor(logging.DEBUG):
+                return fn(*a, **k)
+            t0 = time.perf_counter()
+            try:
+                return fn(*a, **k)
+            finally:
+                flexkv_logger.debug("%s took %.3f ms", label, (time.perf_counter() - t0) * 1e3)
+        return wrapper
+    return deco

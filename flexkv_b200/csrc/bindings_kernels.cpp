@@ -63,5 +63,11 @@ void init_kernel_bindings(py::module_& m) {
     throw_on(launch_kv_copy_refshape(p, num_ctas, (cudaStream_t)(uintptr_t)stream), "kv_copy_refshape launch");
   }, py::arg("params"), py::arg("num_ctas") = 4, py::arg("stream") = 0);
 
+  m.def("host_kv_copy", [](py::dict params, int threads) {
+    KvCopyParams p = kv_params_from_dict(params);
+    py::gil_scoped_release rel;
+    return host_kv_copy(p, threads);
+  }, py::arg("params"), py::arg("threads") = 4);
+
   m.def("kv_copy_tma_eligible", [](py::dict params) { return kv_copy_tma_eligible(kv_params_from_dict(params)); });
 }

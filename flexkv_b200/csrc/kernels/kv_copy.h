@@ -67,6 +67,10 @@ cudaError_t launch_kv_copy(const KvCopyParams& p, const KvCopyLaunch& cfg, cudaS
 // (reference: csrc/transfer.cu:95-158,176-190).
 cudaError_t launch_kv_copy_refshape(const KvCopyParams& p, int num_ctas, cudaStream_t stream);
 
+// Same addressing executed on the CPU with memcpy; every pointer (gpu_ptrs
+// included) is a host address. Returns the OR of KvCopyStatus bits.
+int host_kv_copy(const KvCopyParams& p, int num_threads);
+
 // true when every address component allows 16-byte bulk copies
 bool kv_copy_tma_eligible(const KvCopyParams& p);
 

@@ -1,0 +1,194 @@
+"""Public facade. Same methods and semantics as the reference's ``KVManager``
+(flexkv/kvmanager.py:34-394): tasks are ints, results are ``KVResponse``.
+
+In-process mode owns a ``KVTaskEngine`` whose data plane runs on threads of
+this process. With ``dp_size > 1``, several engine instances or
+``FLEXKV_SERVER_CLIENT_MODE=1`` the manager becomes a client of one
+``KVServer`` that owns the shared index (flexkv/kvmanager.py:69-131).
+"""
+from __future__ import annotations
+
+import os
+import time
+from typing import Dict, List, Optional, Sequence, Tuple, Union
+
+import numpy as np
+import torch
+
+from .common.config import GLOBAL_CONFIG_FROM_ENV, CacheConfig, ModelConfig
+from .common.debug import flexkv_logger
+from .common.request import KVResponse
+from .common.storage import KVCacheLayout
+
+
+def _np(x, dtype=None):
+    if x is None:
+        return None
+    if isinstance(x, torch.Tensor):
+        x = x.detach().cpu().numpy()
+    x = np.asarray(x)
+    return x.astype(dtype, copy=False) if dtype is not None else x
+
+
+class KVManager:
+    def __init__(self, model_config: ModelConfig, cache_config: CacheConfig, dp_client_id: int = 0,
+                 server_recv_port: Optional[str] = None, gpu_register_port: Optional[str] = None,
+                 require_gpu: Optional[bool] = None) -> None:
+        env = GLOBAL_CONFIG_FROM_ENV
+        self.model_config = model_config
+        self.cache_config = cache_config
+        self.dp_client_id = dp_client_id
+        self.server_recv_port = server_recv_port or env.server_recv_port
+        self.gpu_register_port = gpu_register_port
+        safe = {k: ("***" if "password" in k else v) for k, v in vars(cache_config).items() if not k.startswith("_")}
+        flexkv_logger.debug("KVManager config: %s | %s", model_config, safe)
+        self.server_client_mode = bool(env.server_client_mode or model_config.dp_size > 1
+                                       or model_config.instance_num > 1)
+        self.server_handle = None
+        self.dp_client = None
+        self.kv_task_engine = None
+        self.transfer_manager = None
+        self._metrics = None
+        if self.server_client_mode:
+            from .server.client import KVDPClient
+            from .server.server import KVServer
+            # dp client 0 of instance 0 hosts the server unless one is launched externally
+            if dp_client_id == 0 and env.instance_id == 0 and env.server_launch_mode != "external":
+                self.server_handle = KVServer.create_server(model_config, cache_config, self.server_recv_port,
+                                                            gpu_register_port=gpu_register_port)
+            self.dp_client = KVDPClient(self.server_recv_port, model_config, dp_client_id)
+        else:
+            from .kvtask import KVTaskEngine
+            from .transfer_manager import TransferManager
+            if require_gpu is None:
+                require_gpu = torch.cuda.is_available()
+            self.transfer_manager = TransferManager(model_config, cache_config, gpu_register_port,
+                                                    require_gpu=require_gpu)
+            self.kv_task_engine = KVTaskEngine(model_config, cache_config, transfer_handles=[self.transfer_manager])
+            if env.enable_metrics:
+                from .metrics.collector import get_collector
+                self._metrics = get_collector(start_server=True)
+                self.kv_task_engine.set_metrics_collector(self._metrics)
+                self.transfer_manager.set_metrics_collector(self._metrics)
+
+    # ---- in-process registration (engine worker and manager share the process) --------------
+    def register_gpu_tensors(self, tensors: Sequence[torch.Tensor], gpu_layout: KVCacheLayout, tp_rank: int = 0,
+                             pp_rank: int = 0, dp_client_id: Optional[int] = None) -> None:
+        if self.server_client_mode:
+            raise RuntimeError("in server-client mode GPU tensors are registered through KVTPClient")
+        from .storage.gpu_layout import register_tensors
+        reg = register_tensors(tensors, gpu_layout, tp_rank=tp_rank, pp_rank=pp_rank,
+                               dp_client_id=self.dp_client_id if dp_client_id is None else dp_client_id)
+        self.transfer_manager.register_gpu(reg)
+
+    # ---- lifecycle ------------------------------------------------------------
+    def start(self) -> None:
+        if self.server_client_mode:
+            self.dp_client.start_server_and_register()
+        else:
+            self.kv_task_engine.start()
+
+    def is_ready(self) -> bool:
+        if self.server_client_mode:
+            return self.dp_client.is_ready()
+        return self.kv_task_engine.is_ready()
+
+    def wait_ready(self, timeout: float = 600.0) -> None:
+        t0 = time.monotonic()
+        while not self.is_ready():
+            if time.monotonic() - t0 > timeout:
+                raise TimeoutError("KVManager did not become ready")
+            time.sleep(0.01)
+
+    def shutdown(self) -> None:
+        if self.server_client_mode:
+            self.dp_client.shutdown()
+            if self.server_handle is not None:
+                self.server_handle.shutdown()
+                self.server_handle = None
+        else:
+            self.kv_task_engine.shutdown()
+
+    # ---- requests -------------------------------------------------------------
+    def get_async(self, token_ids, slot_mapping, token_mask=None, namespace: Optional[List[str]] = None) -> int:
+        token_ids, slot_mapping, token_mask = _np(token_ids, np.int64), _np(slot_mapping, np.int64), _np(token_mask)
+        if self.server_client_mode:
+            return self.dp_client.get_async(token_ids, slot_mapping, token_mask, namespace=namespace)
+        return self.kv_task_engine.get_async(token_ids, slot_mapping, token_mask, self.dp_client_id, namespace)[0]
+
+    def get_match(self, token_ids, token_mask=None, cpu_only: bool = False, namespace: Optional[List[str]] = None,
+                  swa_aware: bool = False) -> Tuple[int, np.ndarray]:
+        token_ids, token_mask = _np(token_ids, np.int64), _np(token_mask)
+        if self.server_client_mode:
+            return self.dp_client.get_match(token_ids, token_mask, cpu_only=cpu_only, namespace=namespace,
+                                            swa_aware=swa_aware)
+        return self.kv_task_engine.get_match(token_ids, token_mask, self.dp_client_id, cpu_only, namespace, swa_aware)
+
+    def put_async(self, token_ids, slot_mapping, token_mask=None, namespace: Optional[List[str]] = None) -> int:
+        token_ids, slot_mapping, token_mask = _np(token_ids, np.int64), _np(slot_mapping, np.int64), _np(token_mask)
+        if self.server_client_mode:
+            return self.dp_client.put_async(token_ids, slot_mapping, token_mask, namespace=namespace)
+        return self.kv_task_engine.put_async(token_ids, slot_mapping, token_mask, self.dp_client_id, namespace)[0]
+
+    def put_match(self, token_ids, token_mask=None, namespace: Optional[List[str]] = None) -> Tuple[int, np.ndarray]:
+        token_ids, token_mask = _np(token_ids, np.int64), _np(token_mask)
+        if self.server_client_mode:
+            return self.dp_client.put_match(token_ids, token_mask, namespace=namespace)
+        return self.kv_task_engine.put_match(token_ids, token_mask, self.dp_client_id, namespace)
+
+    def prefetch_async(self, token_ids, namespace: Optional[List[str]] = None, swa_aware: bool = False) -> int:
+        token_ids = _np(token_ids, np.int64)
+        if self.server_client_mode:
+            return self.dp_client.prefetch_async(token_ids, namespace=namespace, swa_aware=swa_aware)
+        return self.kv_task_engine.prefetch_async(token_ids, self.dp_client_id, namespace, swa_aware)
+
+    def launch(self, task_ids: Union[int, List[int]], slot_mappings, swa_slot_mappings=None, as_batch: bool = False,
+               layerwise_transfer: bool = False, counter_id: int = 0) -> List[int]:
+        if isinstance(task_ids, int):
+            task_ids = [task_ids]
+        if not isinstance(slot_mappings, (list, tuple)):
+            slot_mappings = [slot_mappings]
+        slot_mappings = [_np(s, np.int64) for s in slot_mappings]
+        if self.server_client_mode:
+            return self.dp_client.launch_tasks(task_ids, slot_mappings, swa_slot_mappings=swa_slot_mappings,
+                                               as_batch=as_batch, layerwise_transfer=layerwise_transfer,
+                                               counter_id=counter_id)
+        return self.kv_task_engine.launch_tasks(task_ids, slot_mappings, swa_slot_mappings=swa_slot_mappings,
+                                                as_batch=as_batch, layerwise_transfer=layerwise_transfer,
+                                                counter_id=counter_id)
+
+    def cancel(self, task_ids: Union[int, List[int]]) -> None:
+        if isinstance(task_ids, int):
+            task_ids = [task_ids]
+        if self.server_client_mode:
+            self.dp_client.cancel_tasks(task_ids)
+        else:
+            self.kv_task_engine.cancel_tasks(task_ids)
+
+    def wait(self, task_ids: Union[int, List[int]], timeout: float = 20.0, completely: bool = False
+             ) -> Dict[int, KVResponse]:
+        if isinstance(task_ids, int):
+            task_ids = [task_ids]
+        if self.server_client_mode:
+            return self.dp_client.wait(task_ids, timeout, completely)
+        return self.kv_task_engine.wait(task_ids, timeout, completely)
+
+    def try_wait(self, task_ids: Union[int, List[int]]) -> Dict[int, KVResponse]:
+        if isinstance(task_ids, int):
+            task_ids = [task_ids]
+        if self.server_client_mode:
+            return self.dp_client.try_wait(task_ids)
+        return self.kv_task_engine.try_wait(task_ids)
+
+    def _clear_cpu_cache(self) -> None:
+        if self.server_client_mode:
+            flexkv_logger.error("clearing the host cache is not supported in server-client mode")
+            return
+        self.kv_task_engine._clear_cpu_cache()  # noqa: SLF001
+
+    def reset(self) -> None:
+        """Drops every tier's index and frees its pool (call after a weight update)."""
+        if self.server_client_mode:
+            self.dp_client.reset()
+        else:
+            self.kv_task_engine.reset_cache()

@@ -1,0 +1,232 @@
+"""Tier storage: the host block pool, SSD cache files and GPU registrations.
+
+Reference counterparts: flexkv/storage/storage_engine.py:40-492 and
+flexkv/storage/allocator.py:190-690. The host pool is one native region
+(hugepage or THP-backed, placed on the NUMA node of the owning GPU, registered
+PORTABLE|MAPPED so kernels can address it); SSD files follow the reference's
+naming and sizing so cache directories are interchangeable:
+``{dir_d}/{prefix}_{d}_{j}.bin``, each pre-sized to
+``num_blocks_per_file * block_bytes``, ``num_ssd_blocks % num_devices == 0``.
+"""
+from __future__ import annotations
+
+import os
+import shutil
+from dataclasses import dataclass
+from typing import Any, Dict, List, Optional, Tuple
+
+import numpy as np
+import torch
+
+from .. import _native
+from ..common.config import GLOBAL_CONFIG_FROM_ENV, CacheConfig, ModelConfig, parse_path_list
+from ..common.debug import flexkv_logger
+from ..common.storage import GroupLayout, KVCacheLayout, KVCacheLayoutType
+from ..common.transfer import DeviceType, WorkerKey
+from .gpu_layout import GpuRegistration
+
+QUANT_GROUP = 128     # values per fp32 scale of the block-scaled fp8 host format
+
+
+def packed_chunk_bytes(chunk_elems: int, quant: str, itemsize: int) -> int:
+    """Bytes one chunk occupies on the host tier."""
+    if quant == "fp8_e4m3":
+        if chunk_elems % QUANT_GROUP:
+            raise ValueError("fp8 offload needs chunk elements divisible by 128")
+        return chunk_elems + (chunk_elems // QUANT_GROUP) * 4
+    return chunk_elems * itemsize
+
+
+@dataclass
+class HostPool:
+    region: Any                 # native HostRegion
+    layout: KVCacheLayout
+    block_bytes: int
+    layer_stride: int           # bytes
+    kv_stride: int
+    chunk_bytes: int            # bytes of one (layer, kv) chunk holding every rank's heads
+    num_blocks: int
+    quant: str = "none"
+
+    @property
+    def base(self) -> int:
+        return int(self.region.ptr)
+
+    def as_numpy(self) -> np.ndarray:
+        return np.frombuffer(self.region, dtype=np.uint8)[: self.num_blocks * self.block_bytes]
+
+    def block_view(self, block_id: int) -> np.ndarray:
+        return self.as_numpy()[block_id * self.block_bytes:(block_id + 1) * self.block_bytes]
+
+
+@dataclass
+class SsdPool:
+    engine: Any                 # native SsdIoEngine
+    files: List[List[str]]
+    block_bytes: int
+    num_blocks: int
+    blocks_per_file: int
+
+
+class StorageEngine:
+    def __init__(self, model_config: ModelConfig, cache_config: CacheConfig, cuda_register: Optional[bool] = None,
+                 numa_node: int = -1) -> None:
+        self.model_config = model_config
+        self.cache_config = cache_config
+        self.env = GLOBAL_CONFIG_FROM_ENV
+        self.gpu_regs: Dict[WorkerKey, Dict[int, GpuRegistration]] = {}
+        self.host: Optional[HostPool] = None
+        self.ssd: Optional[SsdPool] = None
+        self._cuda_register = torch.cuda.is_available() if cuda_register is None else cuda_register
+        self._numa_node = numa_node
+        if cache_config.enable_cpu:
+            self._alloc_host()
+        if cache_config.enable_ssd:
+            self._alloc_ssd()
+
+    # ---- host pool ----------------------------------------------------------------
+    def _host_geometry(self) -> Tuple[int, int, int, int, KVCacheLayout]:
+        m, c = self.model_config, self.cache_config
+        T = c.tokens_per_block
+        layers = m.num_layers_per_pp_stage
+        if m.layer_groups:
+            groups = []
+            for g in m.layer_groups:
+                dt = g.dtype or m.dtype
+                heads_rank = g.num_kv_heads if g.num_kv_heads == 1 else g.num_kv_heads // m.effective_tp_size
+                groups.append(GroupLayout(g.num_layers // m.pp_size, g.kv_dim, T // g.compress_ratio,
+                                          max(1, heads_rank), g.head_size, dt.itemsize))
+            slices = 1 if all(g.num_kv_heads == 1 for g in m.layer_groups) else m.effective_tp_size
+            lay = KVCacheLayout(KVCacheLayoutType.BLOCKFIRST, layers, c.num_cpu_blocks, T, m.num_kv_heads,
+                                m.head_size, is_mla=m.use_mla, groups=groups, tp_slices=slices)
+            return lay.block_bytes_flat, 0, 0, 0, lay
+        lay = KVCacheLayout(self.env.cpu_layout_type, layers, c.num_cpu_blocks, T, m.num_kv_heads, m.head_size,
+                            is_mla=m.use_mla, kv_dim_override=m.kv_dim)
+        chunk = packed_chunk_bytes(lay.get_chunk_size(), c.offload_quant, m.dtype.itemsize)
+        if lay.type == KVCacheLayoutType.BLOCKFIRST:
+            kv_stride, layer_stride = chunk, lay.kv_dim * chunk
+            block_bytes = layers * layer_stride
+        elif lay.type == KVCacheLayoutType.LAYERFIRST:
+            kv_stride = c.num_cpu_blocks * chunk
+            layer_stride = lay.kv_dim * kv_stride
+            block_bytes = chunk          # block stride
+        else:
+            kv_stride = chunk
+            block_bytes = lay.kv_dim * chunk
+            layer_stride = c.num_cpu_blocks * block_bytes
+        return block_bytes, layer_stride, kv_stride, chunk, lay
+
+    def _alloc_host(self) -> None:
+        c = self.cache_config
+        block_bytes, layer_stride, kv_stride, chunk, lay = self._host_geometry()
+        total = self._host_total_bytes(block_bytes, lay)
+        backing = os.environ.get("FLEXKV_HUGEPAGE_FILE", "") if c.use_hugepage_cpu_buffer else ""
+        try:
+            region = _native.C.host_region_alloc(total, hugepage=c.use_hugepage_cpu_buffer,
+                                                 hugepage_bytes=c.hugepage_size_bytes, numa_node=self._numa_node,
+                                                 populate=True, touch_threads=min(16, os.cpu_count() or 4),
+                                                 cuda_register=self._cuda_register,
+                                                 register_chunk_bytes=int(os.environ.get(
+                                                     "FLEXKV_HOST_REGISTER_CHUNK_BYTES", 0)),
+                                                 backing_file=backing)
+        except RuntimeError as e:
+            raise RuntimeError(f"host pool of {total / 2**30:.1f} GiB could not be allocated: {e}") from e
+        self.host = HostPool(region, lay, block_bytes, layer_stride, kv_stride, chunk, c.num_cpu_blocks,
+                             c.offload_quant)
+        flexkv_logger.info("host pool: %d blocks x %d B = %.2f GiB (hugepage=%s, registered=%s, layout=%s)",
+                           c.num_cpu_blocks, block_bytes, total / 2**30, region.hugepage, region.registered,
+                           lay.type.value)
+
+    def _host_total_bytes(self, block_bytes: int, lay: KVCacheLayout) -> int:
+        c = self.cache_config
+        if lay.is_multi_group or lay.type == KVCacheLayoutType.BLOCKFIRST:
+            return c.num_cpu_blocks * block_bytes
+        return self.model_config.num_layers_per_pp_stage * lay.kv_dim * c.num_cpu_blocks * \
+            packed_chunk_bytes(lay.get_chunk_size(), c.offload_quant, self.model_config.dtype.itemsize)
+
+    def host_block_stride(self) -> int:
+        return self.host.block_bytes
+
+    # ---- SSD ----------------------------------------------------------------------
+    def _alloc_ssd(self) -> None:
+        c = self.cache_config
+        dirs = parse_path_list(c.ssd_cache_dir or [])
+        if not dirs:
+            raise ValueError("enable_ssd requires ssd_cache_dir")
+        ndev = len(dirs)
+        if c.num_ssd_blocks % ndev:
+            raise ValueError(f"num_ssd_blocks ({c.num_ssd_blocks}) must be a multiple of the number of "
+                             f"SSD directories ({ndev})")
+        if self.host is None:
+            raise ValueError("the SSD tier needs the host tier as staging")
+        block_bytes = self.host.block_bytes if self.host.layout.type == KVCacheLayoutType.BLOCKFIRST or \
+            self.host.layout.is_multi_group else \
+            self.model_config.num_layers_per_pp_stage * self.host.layout.kv_dim * self.host.chunk_bytes
+        per_dev = c.num_ssd_blocks // ndev
+        max_gb = self.env.max_file_size_gb
+        blocks_per_file = per_dev
+        for d in dirs:
+            os.makedirs(d, exist_ok=True)
+            free = shutil.disk_usage(d).free
+            blocks_per_file = min(blocks_per_file, max(1, free // block_bytes))
+        if max_gb and max_gb > 0:
+            blocks_per_file = min(blocks_per_file, max(1, int(max_gb * 2**30) // block_bytes))
+        files_per_dev = (per_dev + blocks_per_file - 1) // blocks_per_file
+        prefix = f"flexkv_ssd_cache_{os.getpid()}" if os.environ.get("FLEXKV_SSD_FILE_PER_PROCESS", "1") == "1" \
+            else "flexkv_ssd_cache"
+        files = [[os.path.join(d, f"{prefix}_{di}_{j}.bin") for j in range(files_per_dev)]
+                 for di, d in enumerate(dirs)]
+        engine = _native.C.SsdIoEngine(files, block_bytes, blocks_per_file, create=True, try_direct=True,
+                                       iouring_entries=self.env.iouring_entries,
+                                       num_threads=self.env.ssd_io_threads)
+        self.ssd = SsdPool(engine, files, block_bytes, c.num_ssd_blocks, blocks_per_file)
+        flexkv_logger.info("ssd pool: %d blocks x %d B over %d dir(s), %d file(s)/dir, io_uring=%s direct=%s",
+                           c.num_ssd_blocks, block_bytes, ndev, files_per_dev, engine.using_iouring,
+                           engine.direct_available)
+
+    def ssd_layout_dict(self) -> Dict[str, Any]:
+        h = self.host
+        bf = h.layout.type == KVCacheLayoutType.BLOCKFIRST or h.layout.is_multi_group
+        L = self.model_config.num_layers_per_pp_stage
+        if bf:
+            ssd_layer, ssd_kv = h.layer_stride, h.kv_stride
+        else:
+            ssd_kv = h.chunk_bytes
+            ssd_layer = h.layout.kv_dim * h.chunk_bytes
+        if h.layout.is_multi_group:
+            # one run per block: describe the block as a single "layer"
+            return dict(cpu_layer_stride=h.block_bytes, cpu_kv_stride=0, cpu_block_stride=h.block_bytes,
+                        ssd_layer_stride=h.block_bytes, ssd_kv_stride=0, ssd_block_stride=h.block_bytes,
+                        chunk_bytes=h.block_bytes, num_layers=1, kv_dim=1, block_first=True)
+        return dict(cpu_layer_stride=h.layer_stride, cpu_kv_stride=h.kv_stride, cpu_block_stride=h.block_bytes,
+                    ssd_layer_stride=ssd_layer, ssd_kv_stride=ssd_kv, ssd_block_stride=self.ssd.block_bytes,
+                    chunk_bytes=h.chunk_bytes, num_layers=L, kv_dim=h.layout.kv_dim, block_first=bf)
+
+    # ---- GPU ----------------------------------------------------------------------
+    def register_gpu_blocks(self, reg: GpuRegistration) -> None:
+        key = WorkerKey(reg.dp_client_id, reg.pp_rank)
+        self.gpu_regs.setdefault(key, {})[reg.tp_rank] = reg
+
+    def all_registered(self) -> bool:
+        m = self.model_config
+        want_keys = m.total_clients * m.pp_size
+        if len(self.gpu_regs) < want_keys:
+            return False
+        return all(len(r) >= m.effective_tp_size_per_node for r in self.gpu_regs.values())
+
+    def shutdown(self) -> None:
+        if self.host is not None:
+            try:
+                self.host.region.free()
+            except Exception:  # noqa: BLE001
+                pass
+            self.host = None
+        if self.ssd is not None:
+            files = [f for d in self.ssd.files for f in d]
+            self.ssd = None
+            if os.environ.get("FLEXKV_KEEP_SSD_FILES", "0") != "1":
+                for f in files:
+                    try:
+                        os.unlink(f)
+                    except OSError:
+                        pass

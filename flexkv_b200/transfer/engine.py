@@ -1,0 +1,180 @@
+"""Data-plane runtime: a scheduler thread that walks transfer graphs and hands
+ready ops to per-type workers.
+
+The reference runs one *process* per worker type behind two pipe hops
+(flexkv/transfer/transfer_engine.py:443-760,1115-1286; flexkv/transfer/worker.py).
+Here workers are threads of the serving process: the heavy lifting happens in
+native code that releases the GIL (kernel launches joined on CUDA events,
+io_uring submission), so an op costs one queue hand-off instead of pickling
+through pipes, and block ids reach the GPU through a mapped pinned ring with no
+shared-memory slot pool. Failure semantics are the reference's: a failed op
+stops further dispatch of its graph, in-flight ops drain, and the graph is
+reported once as failed (flexkv/transfer/transfer_engine.py:1320-1378).
+"""
+from __future__ import annotations
+
+import queue
+import threading
+import time
+from dataclasses import dataclass
+from typing import Any, Callable, Dict, List, Optional, Tuple
+
+import numpy as np
+
+from ..common.config import GLOBAL_CONFIG_FROM_ENV, CacheConfig, ModelConfig
+from ..common.debug import flexkv_logger
+from ..common.transfer import (CompletedOp, LayerwiseTransferOp, TransferOp, TransferOpGraph, TransferType,
+                               WorkerKey)
+from .trace import TransferTrace
+from .workers import OpOutcome, TransferWorker, build_workers
+
+
+class TransferEngine:
+    def __init__(self, storage, model_config: ModelConfig, cache_config: CacheConfig,
+                 workers: Optional[Dict[Tuple[WorkerKey, TransferType], TransferWorker]] = None) -> None:
+        self.storage = storage
+        self.model_config = model_config
+        self.cache_config = cache_config
+        self._events: "queue.Queue[Tuple[str, Any, Any]]" = queue.Queue()
+        self._completed: "queue.Queue[CompletedOp]" = queue.Queue()
+        self._graphs: Dict[int, TransferOpGraph] = {}
+        self._inflight: Dict[int, int] = {}
+        self._workers = workers
+        self._thread: Optional[threading.Thread] = None
+        self._ready = threading.Event()
+        self._stopping = False
+        self._trace = TransferTrace(enabled=GLOBAL_CONFIG_FROM_ENV.enable_transfer_trace)
+        self._metrics = None
+        self.stats = dict(ops=0, failed_ops=0, graphs=0, failed_graphs=0)
+
+    # ---- lifecycle ------------------------------------------------------------
+    def start(self) -> None:
+        if self._workers is None:
+            self._workers = build_workers(self.storage, self.model_config, self.cache_config)
+        for w in set(self._workers.values()):
+            w.start(self._on_worker_done)
+        self._thread = threading.Thread(target=self._loop, name="flexkv-scheduler", daemon=True)
+        self._thread.start()
+        self._ready.set()
+
+    def is_ready(self) -> bool:
+        return self._ready.is_set()
+
+    def set_metrics_collector(self, collector) -> None:
+        self._metrics = collector
+
+    def shutdown(self) -> None:
+        if self._thread is None:
+            return
+        self._stopping = True
+        self._events.put(("stop", None, None))
+        self._thread.join(timeout=30)
+        self._thread = None
+        for w in set((self._workers or {}).values()):
+            w.stop()
+        self._ready.clear()
+
+    def worker_for(self, key: WorkerKey, tt: TransferType) -> Optional[TransferWorker]:
+        return (self._workers or {}).get((key, tt))
+
+    # ---- submission / completion ----------------------------------------------
+    def submit(self, graph: TransferOpGraph) -> None:
+        self._events.put(("submit", graph, None))
+
+    def submit_batch(self, graphs: List[TransferOpGraph]) -> None:
+        for g in graphs:
+            self._events.put(("submit", g, None))
+
+    def wait(self, timeout: Optional[float] = None) -> List[CompletedOp]:
+        """Completed ops so far; blocks up to ``timeout`` seconds for the first one."""
+        out: List[CompletedOp] = []
+        try:
+            if timeout is None or timeout > 0:
+                out.append(self._completed.get(timeout=timeout))
+            while True:
+                out.append(self._completed.get_nowait())
+        except queue.Empty:
+            pass
+        return out
+
+    get_completed_graphs_and_ops = wait
+
+    # ---- scheduler ------------------------------------------------------------
+    def _on_worker_done(self, op: TransferOp, outcome: OpOutcome) -> None:
+        self._events.put(("done", op, outcome))
+
+    def _loop(self) -> None:
+        while True:
+            kind, a, b = self._events.get()
+            if kind == "stop":
+                break
+            try:
+                if kind == "submit":
+                    self._on_submit(a)
+                elif kind == "done":
+                    self._on_done(a, b)
+            except Exception:  # noqa: BLE001  - the scheduler must survive a bad graph
+                flexkv_logger.exception("transfer scheduler error")
+
+    def _on_submit(self, graph: TransferOpGraph) -> None:
+        self._graphs[graph.graph_id] = graph
+        self._inflight[graph.graph_id] = 0
+        self.stats["graphs"] += 1
+        if graph.num_ops == 0:
+            self._finish_graph(graph)
+            return
+        self._dispatch(graph)
+
+    def _dispatch(self, graph: TransferOpGraph) -> None:
+        if graph.failed:
+            return
+        progress = True
+        while progress:
+            progress = False
+            for op in graph.take_ready_ops():
+                if op.transfer_type == TransferType.VIRTUAL or (op.valid_block_num == 0 and
+                                                                not isinstance(op, LayerwiseTransferOp)):
+                    graph.mark_completed(op.op_id, True)
+                    self._completed.put(CompletedOp(graph.graph_id, op.op_id, True))
+                    progress = True
+                    continue
+                key = WorkerKey(op.dp_client_id, 0)
+                w = self._workers.get((key, op.transfer_type)) or self._workers.get((WorkerKey(0, 0), op.transfer_type))
+                if w is None:
+                    flexkv_logger.error("no worker for %s (dp client %d)", op.transfer_type.value, op.dp_client_id)
+                    graph.mark_completed(op.op_id, False)
+                    self._completed.put(CompletedOp(graph.graph_id, op.op_id, False))
+                    continue
+                self._inflight[graph.graph_id] += 1
+                self._trace.on_submit(op)
+                w.submit(op)
+        if graph.all_transfer_ops_completed() or (graph.failed and self._inflight[graph.graph_id] == 0):
+            self._finish_graph(graph)
+
+    def _on_done(self, op: TransferOp, outcome: OpOutcome) -> None:
+        graph = self._graphs.get(op.graph_id)
+        if graph is None:
+            return
+        self._inflight[graph.graph_id] -= 1
+        self.stats["ops"] += 1
+        if not outcome.success:
+            self.stats["failed_ops"] += 1
+        op.block_results = outcome.block_results
+        self._trace.on_done(op, outcome)
+        if self._metrics is not None:
+            self._metrics.record_transfer(op.transfer_type.value, op.valid_block_num, outcome.num_bytes,
+                                          outcome.success)
+        graph.mark_completed(op.op_id, outcome.success)
+        self._completed.put(CompletedOp(graph.graph_id, op.op_id, outcome.success,
+                                        block_results=outcome.block_results, gpu_ms=outcome.gpu_ms,
+                                        num_bytes=outcome.num_bytes))
+        self._dispatch(graph)
+
+    def _finish_graph(self, graph: TransferOpGraph) -> None:
+        if graph.graph_id not in self._graphs:
+            return
+        del self._graphs[graph.graph_id]
+        del self._inflight[graph.graph_id]
+        if graph.failed:
+            self.stats["failed_graphs"] += 1
+        self._completed.put(CompletedOp.graph_done(graph.graph_id, success=not graph.failed))

@@ -1,0 +1,259 @@
+"""Transfer workers: one thread per (worker key, direction) that executes ops
+of one kind and reports an ``OpOutcome``.
+
+Counterparts in the reference are worker *processes*
+(flexkv/transfer/worker.py:709-1097 GPU<->host, :1099-1529 TP group,
+:1531-1713 host<->SSD, :1948-2244 GDS, :1715-1946 remote file system).
+A worker never drops an op: any exception becomes a failed outcome so that the
+task layer can report FAILED instead of timing out
+(flexkv/transfer/worker.py:612-619).
+"""
+from __future__ import annotations
+
+import queue
+import threading
+import time
+from dataclasses import dataclass
+from typing import Any, Callable, Dict, List, Optional, Tuple
+
+import numpy as np
+
+from .. import _native
+from ..common.config import GLOBAL_CONFIG_FROM_ENV, CacheConfig, ModelConfig
+from ..common.debug import flexkv_logger
+from ..common.storage import KVCacheLayoutType
+from ..common.transfer import LayerwiseTransferOp, TransferOp, TransferType, WorkerKey
+
+
+@dataclass
+class OpOutcome:
+    success: bool
+    block_results: Optional[Tuple[bool, ...]] = None
+    gpu_ms: float = 0.0
+    num_bytes: int = 0
+    error: str = ""
+
+
+class TransferWorker:
+    """Base: a FIFO of ops served by one thread."""
+
+    name = "worker"
+
+    def __init__(self) -> None:
+        self._q: "queue.Queue[Optional[TransferOp]]" = queue.Queue()
+        self._thread: Optional[threading.Thread] = None
+        self._done_cb: Optional[Callable[[TransferOp, OpOutcome], None]] = None
+        self.fail_next = 0          # host-side fault injection for tests: fail this many ops
+
+    def start(self, done_cb: Callable[[TransferOp, OpOutcome], None]) -> None:
+        self._done_cb = done_cb
+        if self._thread is None:
+            self._thread = threading.Thread(target=self._run, name=f"flexkv-{self.name}", daemon=True)
+            self._thread.start()
+
+    def stop(self) -> None:
+        if self._thread is not None:
+            self._q.put(None)
+            self._thread.join(timeout=GLOBAL_CONFIG_FROM_ENV.worker_shutdown_timeout_s)
+            self._thread = None
+        self.close()
+
+    def close(self) -> None:
+        pass
+
+    def submit(self, op: TransferOp) -> None:
+        self._q.put(op)
+
+    def _run(self) -> None:
+        while True:
+            op = self._q.get()
+            if op is None:
+                return
+            try:
+                if self.fail_next > 0:
+                    self.fail_next -= 1
+                    raise RuntimeError("injected worker failure")
+                out = self.execute(op)
+            except Exception as e:  # noqa: BLE001
+                flexkv_logger.error("%s: op %d (%s) failed: %s", self.name, op.op_id, op.transfer_type.value, e)
+                out = OpOutcome(False, error=str(e))
+            self._done_cb(op, out)
+
+    def execute(self, op: TransferOp) -> OpOutcome:
+        raise NotImplementedError
+
+
+# ------------------------------------------------------------------ GPU <-> host
+
+def _launch_cfg(env, h2d: bool) -> Dict[str, int]:
+    return dict(num_ctas=env.transfer_num_cta_h2d if h2d else env.transfer_num_cta_d2h,
+                tile_bytes=env.transfer_tile_bytes, engine=0 if env.transfer_engine == "tma" else 1)
+
+
+def build_transfer_group(storage, model_config: ModelConfig, key: WorkerKey, high_priority: bool = False,
+                         max_blocks_per_op: Optional[int] = None):
+    """One native TransferGroup over every registered rank of ``key``."""
+    env = GLOBAL_CONFIG_FROM_ENV
+    regs = storage.gpu_regs[key]
+    ranks = sorted(regs)
+    host = storage.host
+    reg0 = regs[ranks[0]]
+    shared = model_config.use_mla or model_config.num_kv_heads == 1
+    if host.layout.is_multi_group:
+        raise ValueError("multi-group pools are served by MultiGroupGpuHostWorker")
+    if host.quant != "none":
+        raise ValueError("quantised pools are served by QuantGpuHostWorker")
+    n_slices = 1 if shared else model_config.effective_tp_size
+    if host.layout.type == KVCacheLayoutType.BLOCKFIRST:
+        layer_stride, kv_stride = host.layer_stride // n_slices, host.kv_stride // n_slices
+        tp_stride = host.block_bytes // n_slices
+    else:
+        layer_stride, kv_stride = host.layer_stride, host.kv_stride
+        tp_stride = host.chunk_bytes // n_slices
+    if not shared and host.chunk_bytes // n_slices != reg0.chunk_bytes:
+        raise ValueError(f"host chunk {host.chunk_bytes} B / {n_slices} ranks does not match the GPU chunk "
+                         f"{reg0.chunk_bytes} B")
+    if shared and host.chunk_bytes != reg0.chunk_bytes:
+        raise ValueError(f"host chunk {host.chunk_bytes} B does not match the GPU chunk {reg0.chunk_bytes} B")
+    gpus = []
+    for r in ranks:
+        d = regs[r].as_native()
+        gpus.append(d)
+    host_d = dict(base=host.base, layer_stride=layer_stride, kv_stride=kv_stride, block_stride=host.block_bytes,
+                  num_blocks=host.num_blocks)
+    opts = dict(num_layers=reg0.num_layers, kv_dim=reg0.kv_dim, chunk_bytes=reg0.chunk_bytes,
+                cpu_tp_stride=tp_stride, shared_kv=shared, shared_mode=env.kv_shared_across_ranks_mode,
+                h2d=_launch_cfg(env, True), d2h=_launch_cfg(env, False), high_priority_stream=high_priority,
+                max_blocks_per_op=max_blocks_per_op or max(4096, min(1 << 18, host.num_blocks)))
+    return _native.C.TransferGroup(gpus, host_d, opts)
+
+
+class GpuHostWorker(TransferWorker):
+    """H2D or D2H through the native transfer group (one kernel launch per GPU per op)."""
+
+    def __init__(self, group, h2d: bool, block_bytes_per_rank: int, num_ranks: int) -> None:
+        super().__init__()
+        self.group = group
+        self.h2d = h2d
+        self.name = "h2d" if h2d else "d2h"
+        self._bytes_per_block = block_bytes_per_rank * num_ranks
+
+    def execute(self, op: TransferOp) -> OpOutcome:
+        if self.h2d:
+            cpu, gpu = op.src_block_ids, op.dst_block_ids
+        else:
+            gpu, cpu = op.src_block_ids, op.dst_block_ids
+        if gpu.size != cpu.size:
+            return OpOutcome(False, error=f"unbound GPU blocks: {gpu.size} vs {cpu.size}")
+        nl = self.group_layers if op.num_layers < 0 else op.num_layers
+        max_n = self.max_blocks
+        status, ms = 0, 0.0
+        tickets = []
+        for lo in range(0, int(cpu.size), max_n):
+            tickets.append(self.group.submit(gpu[lo:lo + max_n], cpu[lo:lo + max_n], self.h2d, op.layer_start, nl))
+        for t in tickets:
+            r = self.group.wait(t)
+            status |= r.status if r.status >= 0 else (1 << 30)
+            ms += r.gpu_ms
+        ok = status == 0
+        return OpOutcome(ok, gpu_ms=ms, num_bytes=int(cpu.size) * self._bytes_per_block,
+                         error="" if ok else f"kernel status 0x{status:x}")
+
+    group_layers = 0
+    max_blocks = 1 << 16
+
+
+class HostEmulatedGpuWorker(TransferWorker):
+    """GPU-less data plane: the registered "GPU" tensors are host tensors and
+    the copy runs on CPU threads with the kernels' addressing. Serves CPU-only
+    deployments of the control plane and the CPU test tier."""
+
+    def __init__(self, storage, model_config: ModelConfig, key: WorkerKey, h2d: bool) -> None:
+        super().__init__()
+        self.h2d = h2d
+        self.name = "h2d-host" if h2d else "d2h-host"
+        self.regs = [storage.gpu_regs[key][r] for r in sorted(storage.gpu_regs[key])]
+        host = storage.host
+        self.host = host
+        shared = model_config.use_mla or model_config.num_kv_heads == 1
+        n_slices = 1 if shared else model_config.effective_tp_size
+        if host.layout.type == KVCacheLayoutType.BLOCKFIRST:
+            self.layer_stride, self.kv_stride = host.layer_stride // n_slices, host.kv_stride // n_slices
+            self.tp_stride = host.block_bytes // n_slices
+        else:
+            self.layer_stride, self.kv_stride = host.layer_stride, host.kv_stride
+            self.tp_stride = host.chunk_bytes // n_slices
+        self.shared = shared
+
+    def execute(self, op: TransferOp) -> OpOutcome:
+        if self.h2d:
+            cpu, gpu = op.src_block_ids, op.dst_block_ids
+        else:
+            gpu, cpu = op.src_block_ids, op.dst_block_ids
+        if gpu.size != cpu.size:
+            return OpOutcome(False, error=f"unbound GPU blocks: {gpu.size} vs {cpu.size}")
+        gpu = np.ascontiguousarray(gpu, dtype=np.int64)
+        cpu = np.ascontiguousarray(cpu, dtype=np.int64)
+        status, nbytes = 0, 0
+        for i, reg in enumerate(self.regs):
+            if self.shared and not self.h2d and i > 0:
+                break       # identical KV on every rank: one writer is enough
+            nl = reg.num_layers if op.num_layers < 0 else op.num_layers
+            params = dict(gpu_ptrs=[int(p) for p in reg.ptrs], idx_layer_mul=reg.idx_layer_mul,
+                          idx_kv_mul=reg.idx_kv_mul, g_layer_stride=reg.layer_stride, g_kv_stride=reg.kv_stride,
+                          g_block_stride=reg.block_stride, cpu_base=self.host.base, c_layer_stride=self.layer_stride,
+                          c_kv_stride=self.kv_stride, c_block_stride=self.host.block_bytes,
+                          c_off=0 if self.shared else i * self.tp_stride, gpu_blocks_ptr=gpu.ctypes.data,
+                          cpu_blocks_ptr=cpu.ctypes.data, num_pairs=int(cpu.size), layer_start=op.layer_start,
+                          num_layers=nl, kv_dim=reg.kv_dim, chunk_bytes=reg.chunk_bytes,
+                          gpu_num_blocks=reg.num_blocks, cpu_num_blocks=self.host.num_blocks, h2d=int(self.h2d))
+            status |= _native.C.host_kv_copy(params, 4)
+            nbytes += int(cpu.size) * nl * reg.kv_dim * reg.chunk_bytes
+        return OpOutcome(status == 0, num_bytes=nbytes, error="" if status == 0 else f"copy status 0x{status:x}")
+
+
+# ------------------------------------------------------------------ host <-> SSD
+
+class SsdWorker(TransferWorker):
+    def __init__(self, storage, is_read: bool) -> None:
+        super().__init__()
+        self.storage = storage
+        self.is_read = is_read
+        self.name = "disk2h" if is_read else "h2disk"
+
+    def execute(self, op: TransferOp) -> OpOutcome:
+        st = self.storage
+        if self.is_read:
+            ssd, cpu = op.src_block_ids, op.dst_block_ids
+        else:
+            cpu, ssd = op.src_block_ids, op.dst_block_ids
+        lay = st.ssd_layout_dict()
+        nl = lay["num_layers"] if op.num_layers < 0 else op.num_layers
+        nfail, ok = st.ssd.engine.transfer(st.host.base, cpu, ssd, self.is_read, lay, op.layer_start, nl)
+        return OpOutcome(nfail == 0, block_results=tuple(bool(x) for x in ok),
+                         num_bytes=int((len(ok) - nfail)) * st.ssd.block_bytes,
+                         error="" if nfail == 0 else f"{nfail} block(s) failed")
+
+
+def build_workers(storage, model_config: ModelConfig, cache_config: CacheConfig
+                  ) -> Dict[Tuple[WorkerKey, TransferType], TransferWorker]:
+    workers: Dict[Tuple[WorkerKey, TransferType], TransferWorker] = {}
+    for key, regs in storage.gpu_regs.items():
+        reg0 = regs[sorted(regs)[0]]
+        if reg0.device_id < 0:
+            workers[(key, TransferType.H2D)] = HostEmulatedGpuWorker(storage, model_config, key, True)
+            workers[(key, TransferType.D2H)] = HostEmulatedGpuWorker(storage, model_config, key, False)
+            continue
+        group = build_transfer_group(storage, model_config, key)
+        per_rank_block = reg0.num_layers * reg0.kv_dim * reg0.chunk_bytes
+        shared = model_config.use_mla or model_config.num_kv_heads == 1
+        for h2d in (True, False):
+            w = GpuHostWorker(group, h2d, per_rank_block, len(regs) if (h2d or not shared) else 1)
+            w.group_layers = reg0.num_layers
+            w.max_blocks = max(4096, min(1 << 18, storage.host.num_blocks))
+            workers[(key, TransferType.H2D if h2d else TransferType.D2H)] = w
+    if storage.ssd is not None:
+        k0 = WorkerKey(0, 0)
+        workers[(k0, TransferType.DISK2H)] = SsdWorker(storage, True)
+        workers[(k0, TransferType.H2DISK)] = SsdWorker(storage, False)
+    return workers

@@ -1,0 +1,147 @@
+"""Owner of the data plane: storage tiers, GPU registrations and the transfer
+engine, behind the handle interface the task layer uses
+(``start / is_ready / submit_batch / wait / shutdown``).
+
+The reference spawns this as a separate process and talks to it over pipes
+(flexkv/transfer_manager.py:38-527,970-1272); here it lives in the serving
+process and initialises on a background thread: GPU registrations may arrive
+in-process (``register_gpu``) or from engine worker processes over a ZMQ
+PULL socket carrying exported tensor handles (flexkv/transfer_manager.py:77-83,
+317-357). Graphs submitted before initialisation finished are queued.
+"""
+from __future__ import annotations
+
+import threading
+import time
+from typing import Any, List, Optional
+
+from .common.config import CacheConfig, ModelConfig
+from .common.debug import flexkv_logger
+from .common.transfer import CompletedOp, TransferOpGraph
+from .storage.gpu_layout import GpuRegistration
+from .storage.storage_engine import StorageEngine
+from .transfer.engine import TransferEngine
+
+
+class TransferManager:
+    def __init__(self, model_config: ModelConfig, cache_config: CacheConfig, gpu_register_port: Optional[str] = None,
+                 require_gpu: bool = True, numa_node: int = -1) -> None:
+        self.model_config = model_config
+        self.cache_config = cache_config
+        self.gpu_register_port = gpu_register_port
+        self.require_gpu = require_gpu
+        self.numa_node = numa_node
+        self.storage: Optional[StorageEngine] = None
+        self.engine: Optional[TransferEngine] = None
+        self._pending_regs: List[GpuRegistration] = []
+        self._reg_cv = threading.Condition()
+        self._ready = threading.Event()
+        self._init_error: Optional[BaseException] = None
+        self._init_thread: Optional[threading.Thread] = None
+        self._early: List[TransferOpGraph] = []
+        self._early_lock = threading.Lock()
+        self._listener = None
+        self._metrics = None
+        self._stop = False
+
+    # ---- registration -----------------------------------------------------------
+    def register_gpu(self, reg: GpuRegistration) -> None:
+        with self._reg_cv:
+            self._pending_regs.append(reg)
+            self._reg_cv.notify_all()
+
+    def _expected_registrations(self) -> int:
+        m = self.model_config
+        return m.total_clients * m.pp_size * m.effective_tp_size_per_node if self.require_gpu else 0
+
+    # ---- lifecycle ----------------------------------------------------------------
+    def start(self) -> None:
+        if self._init_thread is not None:
+            return
+        if self.gpu_register_port:
+            from .server.registration import RegistrationListener
+            self._listener = RegistrationListener(self.gpu_register_port, self.register_gpu)
+            self._listener.start()
+        self._init_thread = threading.Thread(target=self._init, name="flexkv-tm-init", daemon=True)
+        self._init_thread.start()
+
+    def _init(self) -> None:
+        try:
+            want = self._expected_registrations()
+            t0 = time.monotonic()
+            warned = False
+            with self._reg_cv:
+                while len(self._pending_regs) < want and not self._stop:
+                    self._reg_cv.wait(timeout=1.0)
+                    if not warned and time.monotonic() - t0 > 60:
+                        warned = True
+                        flexkv_logger.warning("still waiting for GPU registrations: %d of %d arrived",
+                                              len(self._pending_regs), want)
+            if self._stop:
+                return
+            numa = self.numa_node
+            if numa < 0 and self._pending_regs and self._pending_regs[0].device_id >= 0:
+                from . import _native
+                numa = _native.C.gpu_numa_node(self._pending_regs[0].device_id)
+            has_gpu = any(r.device_id >= 0 for r in self._pending_regs)
+            self.storage = StorageEngine(self.model_config, self.cache_config, cuda_register=has_gpu,
+                                         numa_node=numa)
+            for r in self._pending_regs:
+                self.storage.register_gpu_blocks(r)
+            self.engine = TransferEngine(self.storage, self.model_config, self.cache_config)
+            if self._metrics is not None:
+                self.engine.set_metrics_collector(self._metrics)
+            self.engine.start()
+            with self._early_lock:
+                early, self._early = self._early, []
+                self._ready.set()
+            if early:
+                self.engine.submit_batch(early)
+        except BaseException as e:  # noqa: BLE001
+            self._init_error = e
+            flexkv_logger.exception("transfer manager initialisation failed")
+
+    def is_ready(self) -> bool:
+        if self._init_error is not None:
+            raise RuntimeError(f"transfer manager failed to start: {self._init_error}") from self._init_error
+        return self._ready.is_set()
+
+    def set_metrics_collector(self, collector) -> None:
+        self._metrics = collector
+        if self.engine is not None:
+            self.engine.set_metrics_collector(collector)
+
+    def submit(self, graph: TransferOpGraph) -> None:
+        self.submit_batch([graph])
+
+    def submit_batch(self, graphs: List[TransferOpGraph]) -> None:
+        with self._early_lock:
+            if not self._ready.is_set():
+                self._early.extend(graphs)
+                return
+        self.engine.submit_batch(graphs)
+
+    def wait(self, timeout: Optional[float] = None) -> List[CompletedOp]:
+        if not self._ready.is_set():
+            if timeout:
+                self._ready.wait(timeout)
+            if not self._ready.is_set():
+                return []
+        return self.engine.wait(timeout)
+
+    def shutdown(self) -> None:
+        self._stop = True
+        with self._reg_cv:
+            self._reg_cv.notify_all()
+        if self._listener is not None:
+            self._listener.stop()
+            self._listener = None
+        if self._init_thread is not None:
+            self._init_thread.join(timeout=60)
+        if self.engine is not None:
+            self.engine.shutdown()
+            self.engine = None
+        if self.storage is not None:
+            self.storage.shutdown()
+            self.storage = None
+        self._ready.clear()
