@@ -1,0 +1,346 @@
+#!/usr/bin/env python
+"""Headline benchmark: KV put/get throughput between a B200's paged KV cache and
+the pinned host pool, plus p50 get latency of one 8K-token request.
+
+Workload (per GPU, weak scaling): Llama-3-8B KV shape in the vLLM paged layout
+(32 layers, 8 KV heads, head 128, bf16, 16-token blocks = 2 MiB of K+V per
+block), a GPU pool of 32,768 blocks, batches of 32 requests x 8,192 tokens that
+are put (GPU->host) and then got back (host->GPU) against random, non-contiguous
+GPU block ids. One *step* = one batch put + one batch get = 2 x 32 GiB per GPU.
+
+Two numbers are produced:
+  * ``value``  — the data plane alone: the native transfer group is driven
+    directly, one D2H and one H2D op per step; timed with CUDA events.
+  * ``e2e``    — the same bytes through the public API (``KVManager.put_match /
+    get_match / launch / wait``) including token hashing, prefix matching,
+    planning, eviction and completion handling; the KV payload itself is the
+    host<->device traffic (H2D from pinned host memory on get, D2H on put).
+
+Launch: ``python bench.py`` (1 GPU) or
+``python -m torch.distributed.run --nproc-per-node N ... bench.py --gpus N``.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=4)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "refshape"])
+    ap.add_argument("--model", default="llama3-8b")
+    ap.add_argument("--requests", type=int, default=32)
+    ap.add_argument("--tokens", type=int, default=8192)
+    ap.add_argument("--gpu-blocks", type=int, default=32768)
+    ap.add_argument("--host-pool-gib", type=float, default=256.0)
+    ap.add_argument("--ctas", type=int, default=0, help="persistent CTAs per copy kernel (0 = configured default)")
+    ap.add_argument("--tile-bytes", type=int, default=0)
+    ap.add_argument("--engine", default="", choices=["", "tma", "simt"])
+    ap.add_argument("--latency-iters", type=int, default=20)
+    ap.add_argument("--skip-e2e", action="store_true")
+    return ap.parse_args()
+
+
+def reference_unavailable() -> None:
+    # The reference's build aborts offline: its third_party/spdlog, xxHash and prometheus-cpp submodules
+    # are empty and the link line needs libxxhash and liburing, none of which exist on this image.
+    print(json.dumps({"impl": "reference", "unavailable":
+                      "reference does not build offline: setup.py aborts on the empty third_party/spdlog "
+                      "submodule and needs system xxhash/liburing headers that the image lacks"}))
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int) -> None:
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.lines = []
+
+    def start(self) -> None:
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.gpu_index), f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "200"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._pump, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self) -> None:
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for l in self.lines:
+            parts = [p.strip() for p in l.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, parts[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def main() -> None:
+    args = parse_args()
+    if args.impl == "reference":
+        reference_unavailable()
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    from flexkv_b200 import CacheConfig, KVManager, _native
+    from flexkv_b200.common.config import GLOBAL_CONFIG_FROM_ENV as ENV
+    from flexkv_b200.models import alloc_paged_cache, get_shape, make_model_config
+    from flexkv_b200.storage.gpu_layout import register_tensors
+
+    C = _native.C
+    rank = int(os.environ.get("RANK", 0))
+    local_rank = int(os.environ.get("LOCAL_RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    if world != args.gpus:
+        if rank == 0:
+            print(f"warning: --gpus {args.gpus} but WORLD_SIZE={world}; using WORLD_SIZE", file=sys.stderr)
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(x: float) -> float:
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    if args.ctas:
+        ENV.transfer_num_cta_h2d = ENV.transfer_num_cta_d2h = args.ctas
+    if args.tile_bytes:
+        ENV.transfer_tile_bytes = args.tile_bytes
+    if args.engine:
+        ENV.transfer_engine = args.engine
+
+    shape = get_shape(args.model)
+    T = shape.tokens_per_block
+    blocks_per_req = args.tokens // T
+    blocks_per_batch = blocks_per_req * args.requests
+    block_bytes = shape.block_bytes
+    batch_bytes = blocks_per_batch * block_bytes
+    if blocks_per_batch > args.gpu_blocks:
+        raise SystemExit("a batch does not fit in the GPU pool")
+
+    # host pool: the named 256 GiB when the box can pin it for every local rank, else what fits
+    avail = 0
+    with open("/proc/meminfo") as f:
+        for line in f:
+            if line.startswith("MemAvailable"):
+                avail = int(line.split()[1]) * 1024
+    local_world = int(os.environ.get("LOCAL_WORLD_SIZE", world))
+    cap = int(avail * 0.55 / max(1, local_world))
+    pool_bytes = min(int(args.host_pool_gib * 2**30), cap)
+    num_cpu_blocks = max(pool_bytes // block_bytes, 2 * blocks_per_batch + 64)
+    model_cfg = make_model_config(shape)
+    cache_cfg = CacheConfig(tokens_per_block=T, num_cpu_blocks=int(num_cpu_blocks), enable_ssd=False)
+
+    t_setup = time.perf_counter()
+    kv, layout = alloc_paged_cache(shape, args.gpu_blocks, dev, "vllm", fill="normal", seed=1234 + rank)
+    mgr = KVManager(model_cfg, cache_cfg)
+    mgr.register_gpu_tensors(kv, layout)
+    mgr.start()
+    mgr.wait_ready(timeout=1800)
+    setup_s = time.perf_counter() - t_setup
+    from flexkv_b200.common.transfer import TransferType, WorkerKey
+    group = mgr.transfer_manager.engine.worker_for(WorkerKey(0, 0), TransferType.H2D).group
+    rng = np.random.default_rng(99 + rank)
+
+    # ------------------------------------------------------------------ data plane alone
+    def run_direct(steps: int):
+        ms_put = ms_get = 0.0
+        for _ in range(steps):
+            g = rng.permutation(args.gpu_blocks)[:blocks_per_batch].astype(np.int64)
+            c = rng.permutation(int(num_cpu_blocks))[:blocks_per_batch].astype(np.int64)
+            if args.impl == "refshape":
+                r1 = group.transfer_refshape(g, c, False, 4)
+                g2 = rng.permutation(args.gpu_blocks)[:blocks_per_batch].astype(np.int64)
+                r2 = group.transfer_refshape(g2, c, True, 4)
+            else:
+                r1 = group.transfer(g, c, False, 0, shape.num_layers)
+                g2 = rng.permutation(args.gpu_blocks)[:blocks_per_batch].astype(np.int64)
+                r2 = group.transfer(g2, c, True, 0, shape.num_layers)
+            if r1.status or r2.status:
+                raise RuntimeError(f"copy kernel reported status {r1.status}/{r2.status}")
+            ms_put += r1.gpu_ms
+            ms_get += r2.gpu_ms
+        return ms_put, ms_get
+
+    run_direct(args.warmup)
+    barrier()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    torch.cuda.synchronize()
+    ms_put, ms_get = run_direct(args.steps)
+    ev1.record()
+    barrier()
+    region_ms = ev0.elapsed_time(ev1)
+    clocks = sampler.stop()
+    ms_put, ms_get, region_ms = max_over_ranks(ms_put), max_over_ranks(ms_get), max_over_ranks(region_ms)
+    # the kernels' own event time is the device-timed figure; the region adds host-side id shuffling
+    kernel_ms = ms_put + ms_get
+    total_bytes = 2 * batch_bytes * args.steps * world
+    value = total_bytes / (kernel_ms * 1e-3) / 1e9
+    put_gbs = batch_bytes * args.steps / (ms_put * 1e-3) / 1e9
+    get_gbs = batch_bytes * args.steps / (ms_get * 1e-3) / 1e9
+
+    # ------------------------------------------------------------------ public API, end to end
+    e2e = None
+    p50_ms = None
+    if not args.skip_e2e and args.impl == "ours":
+        vocab = 128256
+
+        def one_step(step_seed: int) -> int:
+            r = np.random.default_rng(step_seed)
+            toks = [r.integers(0, vocab, size=args.tokens, dtype=np.int64) for _ in range(args.requests)]
+            g = r.permutation(args.gpu_blocks)[:blocks_per_batch].astype(np.int64)
+            slots = [(np.repeat(g[i * blocks_per_req:(i + 1) * blocks_per_req], T) * T +
+                      np.tile(np.arange(T), blocks_per_req)) for i in range(args.requests)]
+            ids, moved = [], 0
+            for t in toks:
+                tid, mask = mgr.put_match(t)
+                ids.append(tid)
+            bid = mgr.launch(ids, slots, as_batch=True)
+            res = mgr.wait(bid, timeout=600, completely=True)
+            for rsp in res.values():
+                if rsp.status.value != "success":
+                    raise RuntimeError(f"put failed: {rsp.status}")
+                moved += int(sum(m.sum() for m in rsp.return_mask)) if isinstance(rsp.return_mask, list) \
+                    else int(rsp.return_mask.sum())
+            g2 = r.permutation(args.gpu_blocks)[:blocks_per_batch].astype(np.int64)
+            slots2 = [(np.repeat(g2[i * blocks_per_req:(i + 1) * blocks_per_req], T) * T +
+                       np.tile(np.arange(T), blocks_per_req)) for i in range(args.requests)]
+            ids = []
+            for t in toks:
+                tid, mask = mgr.get_match(t)
+                if int(mask.sum()) != args.tokens:
+                    raise RuntimeError("get_match did not find the batch that was just put")
+                ids.append(tid)
+            bid = mgr.launch(ids, slots2, as_batch=True)
+            res = mgr.wait(bid, timeout=600)
+            for rsp in res.values():
+                if rsp.status.value != "success":
+                    raise RuntimeError(f"get failed: {rsp.status}")
+                moved += int(sum(m.sum() for m in rsp.return_mask)) if isinstance(rsp.return_mask, list) \
+                    else int(rsp.return_mask.sum())
+            return moved
+
+        for w in range(args.warmup):
+            one_step(10_000 * (rank + 1) + w)
+        barrier()
+        t0 = time.perf_counter()
+        ev0.record()
+        moved = 0
+        for s in range(args.steps):
+            moved += one_step(20_000 * (rank + 1) + s)
+        ev1.record()
+        barrier()
+        wall_ms = max_over_ranks((time.perf_counter() - t0) * 1e3)
+        tok_bytes = shape.bytes_per_token
+        e2e_val = moved * tok_bytes * world / (wall_ms * 1e-3) / 1e9
+        ids_bytes = 2 * blocks_per_batch * 8
+        e2e = {"value": round(e2e_val, 2), "unit": "GB/s", "ms_per_step": round(wall_ms / args.steps, 2),
+               "h2d_bytes_per_step": batch_bytes + ids_bytes, "d2h_bytes_per_step": batch_bytes + 8,
+               "api": "KVManager.put_match/get_match/launch(as_batch)/wait"}
+
+        # p50 latency of one 8K-token get through the public API
+        lat = []
+        r = np.random.default_rng(777 + rank)
+        n8k = 8192 // T
+        for i in range(args.latency_iters + 3):
+            tok = r.integers(0, vocab, size=8192, dtype=np.int64)
+            g = r.permutation(args.gpu_blocks)[:n8k].astype(np.int64)
+            slot = np.repeat(g, T) * T + np.tile(np.arange(T), n8k)
+            tid = mgr.put_async(tok, slot)
+            mgr.wait(tid, timeout=60, completely=True)
+            torch.cuda.synchronize()
+            t1 = time.perf_counter()
+            tid, mask = mgr.get_match(tok)
+            mgr.launch(tid, slot)
+            rsp = mgr.wait(tid, timeout=60)[tid]
+            dt = (time.perf_counter() - t1) * 1e3
+            if rsp.status.value != "success" or int(rsp.return_mask.sum()) != 8192:
+                raise RuntimeError("latency probe get failed")
+            if i >= 3:
+                lat.append(dt)
+        p50_ms = max_over_ranks(statistics.median(lat))
+
+    launches = 2 * args.steps     # one D2H and one H2D kernel per step and rank
+    mgr.shutdown()
+    if rank == 0:
+        out = {
+            "metric": "KV get/put GB/s per GPU & whole box at 1/2/4/8 B200; p50 get latency/8K tok",
+            "impl": "ours" if args.impl == "ours" else "reference-shaped kernel (4 CTAs x 1024 threads) in this repo",
+            "value": round(value, 2), "unit": "GB/s (put+get bytes / kernel time, all GPUs)",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": round(kernel_ms / args.steps, 3), "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic: uniform token ids, N(0,1) KV, random-init",
+            "put_gbs_per_gpu": round(put_gbs, 2), "get_gbs_per_gpu": round(get_gbs, 2),
+            "region_ms_per_step": round(region_ms / args.steps, 3),
+            "p50_get_latency_ms_8k_tokens": None if p50_ms is None else round(p50_ms, 3),
+            "e2e": e2e, "gpu_launches": launches * world, "clocks": clocks,
+            "config": {"model": f"{shape.name} KV, vLLM paged layout", "global_batch": args.requests * world,
+                       "seq_len": args.tokens, "parallelism": f"dp{world}", "gpu_blocks": args.gpu_blocks,
+                       "host_pool_gib": round(num_cpu_blocks * block_bytes / 2**30, 1),
+                       "host_pool_gib_requested": args.host_pool_gib, "block_bytes": block_bytes,
+                       "bytes_per_step_per_gpu": 2 * batch_bytes,
+                       "l2": "inputs larger than L2 (32 GiB per direction per step)",
+                       "ctas": ENV.transfer_num_cta_h2d, "tile_bytes": ENV.transfer_tile_bytes,
+                       "engine": ENV.transfer_engine, "setup_s": round(setup_s, 1)},
+        }
+        print(json.dumps(out))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

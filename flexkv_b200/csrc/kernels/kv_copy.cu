@@ -23,11 +23,15 @@ namespace {
 
 constexpr uint64_t kWaitBudgetNs = 2000000000ull;  // 2 s per bulk-copy wait
 
-// The status word may sit in mapped host memory, where device atomics depend
-// on PCIe atomic support; a plain store is enough because any non-zero value
-// fails the op and the individual bits are diagnostic only.
+// Error reporting without atomics: `status` is an array of kStatusWords words,
+// one per KvCopyStatus bit, and a CTA that saw error bit b stores 1 to word b.
+// Plain idempotent stores cannot lose a bit when several CTAs report at once,
+// and they work on mapped host memory whether or not the platform offers PCIe
+// atomics. The host ORs the words back into a bit mask.
 __device__ __forceinline__ void report_status(int32_t* status, int err) {
-  *reinterpret_cast<volatile int32_t*>(status) = *reinterpret_cast<volatile int32_t*>(status) | err;
+#pragma unroll
+  for (int b = 0; b < kStatusWords; ++b)
+    if (err & (1 << b)) reinterpret_cast<volatile int32_t*>(status)[b] = 1;
 }
 
 struct TileAddr {

@@ -23,6 +23,7 @@
 namespace fkv {
 
 constexpr int kMaxGpuPtrs = 256;
+constexpr int kStatusWords = 8;   // status arrays hold one int32 per KvCopyStatus bit
 
 enum KvCopyStatus : int {
   KV_OK = 0,
@@ -47,7 +48,8 @@ struct KvCopyParams {
   int32_t layer_start, num_layers, kv_dim;
   int64_t chunk_bytes;
   int64_t gpu_num_blocks, cpu_num_blocks;  // <= 0 disables the range check
-  int32_t* status;                         // device or mapped word, OR-ed with KvCopyStatus bits; may be null
+  int32_t* status;                         // device or mapped int32[kStatusWords], word b set to 1 when bit b
+                                           // of KvCopyStatus occurred; may be null
   int32_t h2d;                             // 1: host -> gpu, 0: gpu -> host
 };
 
@@ -70,6 +72,14 @@ cudaError_t launch_kv_copy_refshape(const KvCopyParams& p, int num_ctas, cudaStr
 // Same addressing executed on the CPU with memcpy; every pointer (gpu_ptrs
 // included) is a host address. Returns the OR of KvCopyStatus bits.
 int host_kv_copy(const KvCopyParams& p, int num_threads);
+
+// folds a status array back into a KvCopyStatus bit mask and clears it
+inline int collect_status(volatile int32_t* words) {
+  int m = 0;
+  for (int b = 0; b < kStatusWords; ++b)
+    if (words[b]) { m |= 1 << b; words[b] = 0; }
+  return m;
+}
 
 // true when every address component allows 16-byte bulk copies
 bool kv_copy_tma_eligible(const KvCopyParams& p);

@@ -53,6 +53,7 @@ int32_t RadixIndex::alloc_node() {
   n.parent = -1;
   int64_t t = now_us();
   n.grace_us = n.last_access_us = n.creation_us = t;
+  n.serial = ++next_serial_;
   ++live_nodes_;
   return idx;
 }
@@ -292,7 +293,7 @@ EvictResult RadixIndex::evict(int64_t num_blocks) {
     const Node& b = nodes_[y];
     if (evict_before(b, a)) return true;
     if (evict_before(a, b)) return false;
-    return x > y;  // deterministic tie-break
+    return a.serial > b.serial;  // deterministic tie-break: older allocation leaves first
   };
   std::priority_queue<int32_t, std::vector<int32_t>, decltype(later)> heap(later);
   for (int32_t l : leaves_)

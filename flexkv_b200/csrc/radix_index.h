@@ -100,6 +100,7 @@ class RadixIndex {
     bool ready = false;
     bool live = false;
     int64_t grace_us = 0, last_access_us = 0, creation_us = 0;
+    uint64_t serial = 0;  // allocation order, the deterministic eviction tie-break
     size_t size() const { return hashes.size(); }
     bool leaf() const { return !children || children->empty(); }
   };
@@ -132,6 +133,7 @@ class RadixIndex {
   std::unordered_set<int32_t> leaves_;
   int64_t total_blocks_ = 0;
   int64_t live_nodes_ = 0;
+  uint64_t next_serial_ = 0;
 };
 
 // Fixed-capacity id pool with duplicate / double-free detection

@@ -136,9 +136,10 @@ void TransferGroup::rank_main(int r) {
       check(cudaEventCreate(&ev0[i]), "cudaEventCreate");
       check(cudaEventCreate(&ev1[i]), "cudaEventCreate");
     }
-    check(cudaHostAlloc((void**)&rk.status, kInflight * sizeof(int32_t), cudaHostAllocPortable | cudaHostAllocMapped),
+    check(cudaHostAlloc((void**)&rk.status, kInflight * kStatusWords * sizeof(int32_t),
+                        cudaHostAllocPortable | cudaHostAllocMapped),
           "cudaHostAlloc(status)");
-    for (int i = 0; i < kInflight; ++i) rk.status[i] = 0;
+    for (int i = 0; i < kInflight * kStatusWords; ++i) rk.status[i] = 0;
   } catch (const std::exception& e) {
     std::lock_guard<std::mutex> g(rk.mu);
     rk.init_error = e.what();
@@ -172,7 +173,7 @@ void TransferGroup::rank_main(int r) {
       KvCopyParams p;
       bool skip = false;
       fill_params(r, t, p, skip);
-      p.status = rk.status + i;
+      p.status = rk.status + i * kStatusWords;
       launched[i] = skip ? 0 : 1;
       lerr[i] = cudaSuccess;
       if (skip) continue;
@@ -194,8 +195,7 @@ void TransferGroup::rank_main(int r) {
         if (e == cudaSuccess) e = cudaEventSynchronize(ev1[i]);
         if (e == cudaSuccess) {
           cudaEventElapsedTime(&ms, ev0[i], ev1[i]);
-          status = rk.status[i];
-          rk.status[i] = 0;
+          status = collect_status(rk.status + i * kStatusWords);
         } else {
           (void)cudaGetLastError();
           status = -(int)e;
