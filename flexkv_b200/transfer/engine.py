@@ -126,9 +126,7 @@ class TransferEngine:
         self._dispatch(graph)
 
     def _dispatch(self, graph: TransferOpGraph) -> None:
-        if graph.failed:
-            return
-        progress = True
+        progress = not graph.failed        # a failed graph gets no new ops; in-flight ones drain
         while progress:
             progress = False
             for op in graph.take_ready_ops():
