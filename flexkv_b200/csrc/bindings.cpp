@@ -13,6 +13,7 @@
 #include "radix_index.h"
 #include "ssd_io.h"
 #include "transfer_group.h"
+#include "bindings_common.h"
 
 namespace py = pybind11;
 using namespace fkv;
@@ -221,17 +222,7 @@ PYBIND11_MODULE(_C, m) {
       .def("transfer", [](SsdIoEngine& e, uint64_t cpu_base, I64Array cpu_blocks, I64Array ssd_blocks, bool is_read,
                           py::dict lay, int layer_start, int num_layers) {
              if (cpu_blocks.size() != ssd_blocks.size()) throw std::invalid_argument("block id arrays differ in size");
-             SsdLayout L;
-             L.cpu_layer_stride = lay["cpu_layer_stride"].cast<int64_t>();
-             L.cpu_kv_stride = lay["cpu_kv_stride"].cast<int64_t>();
-             L.cpu_block_stride = lay["cpu_block_stride"].cast<int64_t>();
-             L.ssd_layer_stride = lay["ssd_layer_stride"].cast<int64_t>();
-             L.ssd_kv_stride = lay["ssd_kv_stride"].cast<int64_t>();
-             L.ssd_block_stride = lay["ssd_block_stride"].cast<int64_t>();
-             L.chunk_bytes = lay["chunk_bytes"].cast<int64_t>();
-             L.num_layers_total = lay["num_layers"].cast<int>();
-             L.kv_dim = lay["kv_dim"].cast<int>();
-             L.block_first = lay["block_first"].cast<bool>();
+             SsdLayout L = parse_ssd_layout(lay);
              const int64_t n = (int64_t)cpu_blocks.size();
              py::array_t<uint8_t> ok((py::ssize_t)n);
              int64_t nfail;
@@ -259,45 +250,9 @@ PYBIND11_MODULE(_C, m) {
 
   py::class_<TransferGroup>(m, "TransferGroup")
       .def(py::init([](py::list gpus, py::dict host, py::dict o) {
-             std::vector<GpuSide> gs;
-             for (auto item : gpus) {
-               py::dict d = item.cast<py::dict>();
-               GpuSide g;
-               g.device = d["device"].cast<int>();
-               g.ptrs = d["ptrs"].cast<std::vector<uint64_t>>();
-               g.idx_layer_mul = d["idx_layer_mul"].cast<int>();
-               g.idx_kv_mul = d["idx_kv_mul"].cast<int>();
-               g.layer_stride = d["layer_stride"].cast<int64_t>();
-               g.kv_stride = d["kv_stride"].cast<int64_t>();
-               g.block_stride = d["block_stride"].cast<int64_t>();
-               g.num_blocks = d["num_blocks"].cast<int64_t>();
-               gs.push_back(std::move(g));
-             }
-             HostSide h;
-             h.base = host["base"].cast<uint64_t>();
-             h.layer_stride = host["layer_stride"].cast<int64_t>();
-             h.kv_stride = host["kv_stride"].cast<int64_t>();
-             h.block_stride = host["block_stride"].cast<int64_t>();
-             h.num_blocks = host["num_blocks"].cast<int64_t>();
-             GroupOptions g;
-             g.num_layers = o["num_layers"].cast<int>();
-             g.kv_dim = o["kv_dim"].cast<int>();
-             g.chunk_bytes = o["chunk_bytes"].cast<int64_t>();
-             g.cpu_tp_stride = o.contains("cpu_tp_stride") ? o["cpu_tp_stride"].cast<int64_t>() : 0;
-             g.shared_kv = o.contains("shared_kv") && o["shared_kv"].cast<bool>();
-             if (o.contains("shared_mode")) g.shared_mode = parse_shared_kv_mode(o["shared_mode"].cast<std::string>());
-             auto launch = [&](const char* k, KvCopyLaunch& l) {
-               if (!o.contains(k)) return;
-               py::dict d = o[k].cast<py::dict>();
-               if (d.contains("num_ctas")) l.num_ctas = d["num_ctas"].cast<int>();
-               if (d.contains("tile_bytes")) l.tile_bytes = d["tile_bytes"].cast<int>();
-               if (d.contains("engine")) l.engine = d["engine"].cast<int>();
-             };
-             launch("h2d", g.h2d);
-             launch("d2h", g.d2h);
-             if (o.contains("ring_slots")) g.ring_slots = o["ring_slots"].cast<int>();
-             if (o.contains("max_blocks_per_op")) g.max_blocks_per_op = o["max_blocks_per_op"].cast<int64_t>();
-             if (o.contains("high_priority_stream")) g.high_priority_stream = o["high_priority_stream"].cast<bool>();
+             std::vector<GpuSide> gs = parse_gpu_sides(gpus);
+             HostSide h = parse_host_side(host);
+             GroupOptions g = parse_group_options(o);
              py::gil_scoped_release rel;
              return new TransferGroup(std::move(gs), h, g);
            }))

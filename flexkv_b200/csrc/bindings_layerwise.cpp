@@ -1,3 +1,86 @@
+// Bindings of the layerwise restore group and the layer stub kernels.
+#include <pybind11/numpy.h>
 #include <pybind11/pybind11.h>
+#include <pybind11/stl.h>
+
+#include "bindings_common.h"
+#include "kernels/layer_sync.h"
+#include "layerwise_group.h"
+
 namespace py = pybind11;
-void init_layerwise_bindings(py::module_& m) { (void)m; }
+using namespace fkv;
+using I64Array = py::array_t<int64_t, py::array::c_style | py::array::forcecast>;
+
+void init_layerwise_bindings(py::module_& m) {
+  py::class_<LayerwiseResult>(m, "LayerwiseResult")
+      .def_readonly("status", &LayerwiseResult::status)
+      .def_readonly("total_ms", &LayerwiseResult::total_ms)
+      .def_readonly("disk_ms", &LayerwiseResult::disk_ms)
+      .def_readonly("layer_done_ms", &LayerwiseResult::layer_done_ms);
+
+  py::class_<LayerwiseGroup>(m, "LayerwiseGroup")
+      .def(py::init([](py::list gpus, py::dict host, py::dict o) {
+             LayerwiseOptions lo;
+             lo.group = parse_group_options(o);
+             if (o.contains("notify_mode")) lo.notify = parse_notify_mode(o["notify_mode"].cast<std::string>());
+             if (o.contains("num_counters")) lo.num_counters = o["num_counters"].cast<int>();
+             if (o.contains("layers_per_batch")) lo.layers_per_batch = o["layers_per_batch"].cast<int>();
+             if (o.contains("create_eventfds")) lo.create_eventfds = o["create_eventfds"].cast<bool>();
+             std::vector<GpuSide> gs = parse_gpu_sides(gpus);
+             HostSide h = parse_host_side(host);
+             py::gil_scoped_release rel;
+             return new LayerwiseGroup(std::move(gs), h, lo);
+           }))
+      .def("restore", [](LayerwiseGroup& g, I64Array gpu_blocks, I64Array cpu_blocks, int counter_id, py::object ssd,
+                         py::object ssd_layout, py::object ssd_src, py::object cpu_dst) {
+             if (gpu_blocks.size() != cpu_blocks.size()) throw std::invalid_argument("block id arrays differ in size");
+             SsdIoEngine* eng = nullptr;
+             SsdLayout lay;
+             I64Array s, c;
+             int64_t nd = 0;
+             if (!ssd.is_none() && !ssd_src.is_none()) {
+               eng = ssd.cast<SsdIoEngine*>();
+               lay = parse_ssd_layout(ssd_layout.cast<py::dict>());
+               s = ssd_src.cast<I64Array>();
+               c = cpu_dst.cast<I64Array>();
+               if (s.size() != c.size()) throw std::invalid_argument("disk id arrays differ in size");
+               nd = (int64_t)s.size();
+             }
+             const int64_t* gp = gpu_blocks.data();
+             const int64_t* cp = cpu_blocks.data();
+             const int64_t n = (int64_t)gpu_blocks.size();
+             const int64_t* sp = nd ? s.data() : nullptr;
+             const int64_t* dp = nd ? c.data() : nullptr;
+             py::gil_scoped_release rel;
+             return g.restore(gp, cp, n, counter_id, eng, nd ? &lay : nullptr, sp, dp, nd);
+           }, py::arg("gpu_blocks"), py::arg("cpu_blocks"), py::arg("counter_id") = 0, py::arg("ssd") = py::none(),
+           py::arg("ssd_layout") = py::none(), py::arg("ssd_src") = py::none(), py::arg("cpu_dst") = py::none())
+      .def("eventfd_of", &LayerwiseGroup::eventfd_of)
+      .def("eventfds_flat", &LayerwiseGroup::eventfds_flat)
+      .def("set_eventfd", &LayerwiseGroup::set_eventfd)
+      .def("device_flags_ptr", &LayerwiseGroup::device_flags_ptr)
+      .def("host_flags_ptr", &LayerwiseGroup::host_flags_ptr)
+      .def("epoch_of", &LayerwiseGroup::epoch_of)
+      .def("stream_wait_layer", [](LayerwiseGroup& g, int rank, int counter, int layer, uint64_t stream) {
+             cudaError_t e = g.stream_wait_layer(rank, counter, layer, (cudaStream_t)(uintptr_t)stream);
+             if (e != cudaSuccess) throw std::runtime_error(cudaGetErrorString(e));
+           })
+      .def_property_readonly("num_ranks", &LayerwiseGroup::num_ranks)
+      .def_property_readonly("num_layers", &LayerwiseGroup::num_layers)
+      .def_property_readonly("num_counters", &LayerwiseGroup::num_counters);
+
+  m.def("layer_stub", [](uint64_t flag_ptr, uint32_t epoch, uint64_t busy_ns, uint64_t budget_ns, uint64_t status_ptr,
+                         uint64_t t_start_ptr, int num_ctas, uint64_t stream) {
+    cudaError_t e = launch_layer_stub((const uint32_t*)(uintptr_t)flag_ptr, epoch, busy_ns, budget_ns,
+                                      (int32_t*)(uintptr_t)status_ptr, (uint64_t*)(uintptr_t)t_start_ptr, num_ctas,
+                                      (cudaStream_t)(uintptr_t)stream);
+    if (e != cudaSuccess) throw std::runtime_error(cudaGetErrorString(e));
+  }, py::arg("flag_ptr"), py::arg("epoch"), py::arg("busy_ns"), py::arg("budget_ns") = (uint64_t)1000000000ull,
+     py::arg("status_ptr") = (uint64_t)0, py::arg("t_start_ptr") = (uint64_t)0, py::arg("num_ctas") = 1,
+     py::arg("stream") = (uint64_t)0);
+
+  m.def("set_flags", [](uint64_t flags_ptr, int n, uint32_t value, uint64_t stream) {
+    cudaError_t e = launch_set_flags((uint32_t*)(uintptr_t)flags_ptr, n, value, (cudaStream_t)(uintptr_t)stream);
+    if (e != cudaSuccess) throw std::runtime_error(cudaGetErrorString(e));
+  });
+}

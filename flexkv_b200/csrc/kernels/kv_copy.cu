@@ -34,6 +34,23 @@ __device__ __forceinline__ void report_status(int32_t* status, int err) {
     if (err & (1 << b)) reinterpret_cast<volatile int32_t*>(status)[b] = 1;
 }
 
+// Last-CTA-out publication of the completion flags (see KvCopyParams). Called by
+// one thread per CTA after all of the CTA's stores are complete.
+__device__ __forceinline__ void signal_done(const KvCopyParams& p) {
+  if (p.done_counter == nullptr) return;
+  ptx::fence_proxy_async_all();  // order the bulk (async proxy) stores before the generic-proxy flag traffic
+  __threadfence();
+  const unsigned prev = atomicAdd(p.done_counter, 1u);
+  if (prev == gridDim.x - 1) {
+    *reinterpret_cast<volatile uint32_t*>(p.done_counter) = 0;
+    __threadfence();
+    for (int l = p.layer_start; l < p.layer_start + p.num_layers; ++l) {
+      if (p.dev_flags) ptx::st_release_gpu(p.dev_flags + l, p.epoch);
+      if (p.host_flags) ptx::st_release_sys(p.host_flags + l, p.epoch);
+    }
+  }
+}
+
 struct TileAddr {
   uint64_t gpu;
   uint64_t cpu;
@@ -155,6 +172,7 @@ kv_copy_bulk_kernel(const __grid_constant__ KvCopyParams p, int tile_bytes, int 
   if (lane == 0) {
     ptx::bulk_wait<0>();
     if (err && p.status) report_status(p.status, err);
+    signal_done(p);
   }
 }
 
@@ -210,6 +228,10 @@ kv_copy_simt_kernel(const __grid_constant__ KvCopyParams p, int tile_bytes, int 
     for (; i < nvec; i += 32) VecIO<V>::st(dst + (size_t)i * sizeof(V), VecIO<V>::ld(src + (size_t)i * sizeof(V)));
   }
   if (err && p.status && lane == 0) report_status(p.status, err);
+  if (p.done_counter) {
+    __syncthreads();
+    if (threadIdx.x == 0) signal_done(p);
+  }
 }
 
 // ---------------------------------------------------------------- baseline shape
@@ -287,10 +309,14 @@ cudaError_t launch_kv_copy(const KvCopyParams& p, const KvCopyLaunch& cfg, cudaS
     const int budget = 200 * 1024;
     const int stages = budget / tile;
     if (p.h2d) {
+      if (stages >= 32) return launch_bulk<32, 31>(p, ctas, tile, tiles_per_chunk, stream);
+      if (stages >= 20) return launch_bulk<20, 19>(p, ctas, tile, tiles_per_chunk, stream);
       if (stages >= 12) return launch_bulk<12, 11>(p, ctas, tile, tiles_per_chunk, stream);
       if (stages >= 8) return launch_bulk<8, 7>(p, ctas, tile, tiles_per_chunk, stream);
       return launch_bulk<6, 5>(p, ctas, tile, tiles_per_chunk, stream);
     }
+    if (stages >= 32) return launch_bulk<32, 16>(p, ctas, tile, tiles_per_chunk, stream);
+    if (stages >= 20) return launch_bulk<20, 10>(p, ctas, tile, tiles_per_chunk, stream);
     if (stages >= 12) return launch_bulk<12, 6>(p, ctas, tile, tiles_per_chunk, stream);
     if (stages >= 8) return launch_bulk<8, 4>(p, ctas, tile, tiles_per_chunk, stream);
     return launch_bulk<6, 3>(p, ctas, tile, tiles_per_chunk, stream);

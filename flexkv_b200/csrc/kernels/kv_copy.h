@@ -51,6 +51,16 @@ struct KvCopyParams {
   int32_t* status;                         // device or mapped int32[kStatusWords], word b set to 1 when bit b
                                            // of KvCopyStatus occurred; may be null
   int32_t h2d;                             // 1: host -> gpu, 0: gpu -> host
+  // Optional completion signal, fused into the copy: every CTA bumps
+  // `done_counter` (device scratch word, zero between launches) after its last
+  // store has landed; the last one resets the counter and publishes `epoch` to
+  // flag words [layer_start, layer_start + num_layers) of `dev_flags` (device
+  // memory, for consumer kernels on this GPU) and `host_flags` (mapped host
+  // memory, for a polling host thread). All three may be null.
+  uint32_t* done_counter;
+  uint32_t* dev_flags;
+  uint32_t* host_flags;
+  uint32_t epoch;
 };
 
 struct KvCopyLaunch {

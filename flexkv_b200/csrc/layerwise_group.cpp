@@ -1,0 +1,297 @@
+#include "layerwise_group.h"
+
+#include <sys/eventfd.h>
+#include <unistd.h>
+
+#include <algorithm>
+#include <chrono>
+#include <cstring>
+#include <stdexcept>
+
+namespace fkv {
+
+NotifyMode parse_notify_mode(const std::string& s) {
+  if (s == "hostfunc") return NotifyMode::HOSTFUNC;
+  if (s == "polling") return NotifyMode::POLLING;
+  if (s == "flag") return NotifyMode::FLAG;
+  throw std::invalid_argument("unknown layerwise notify mode: " + s);
+}
+
+static void check(cudaError_t e, const char* what) {
+  if (e != cudaSuccess) {
+    (void)cudaGetLastError();
+    throw std::runtime_error(std::string(what) + ": " + cudaGetErrorString(e));
+  }
+}
+
+LayerwiseGroup::LayerwiseGroup(std::vector<GpuSide> gpus, HostSide host, LayerwiseOptions opt)
+    : gpus_(std::move(gpus)), host_(host), opt_(opt) {
+  if (gpus_.empty()) throw std::invalid_argument("LayerwiseGroup: no GPUs");
+  if (opt_.num_counters < 1 || opt_.layers_per_batch < 1) throw std::invalid_argument("LayerwiseGroup: bad options");
+  const int L = opt_.group.num_layers, R = (int)gpus_.size(), C = opt_.num_counters;
+  epochs_.assign((size_t)C, 0);
+  if (opt_.create_eventfds) {
+    eventfds_.assign((size_t)C * R * L, -1);
+    for (auto& fd : eventfds_) {
+      fd = eventfd(0, EFD_NONBLOCK | EFD_SEMAPHORE);
+      if (fd < 0) throw std::runtime_error(std::string("eventfd: ") + strerror(errno));
+    }
+  }
+  check(cudaSetDevice(gpus_[0].device), "cudaSetDevice");
+  check(cudaHostAlloc((void**)&id_ring_, 2 * (size_t)opt_.group.max_blocks_per_op * sizeof(int64_t),
+                      cudaHostAllocPortable | cudaHostAllocMapped),
+        "cudaHostAlloc(id ring)");
+  const int batches = (L + opt_.layers_per_batch - 1) / opt_.layers_per_batch;
+  for (int r = 0; r < R; ++r)
+    for (int c = 0; c < C; ++c)
+      for (int b = 0; b < batches; ++b) {
+        auto a = std::make_unique<HostFnArg>();
+        a->self = this; a->rank = r; a->counter = c;
+        a->layer_lo = b * opt_.layers_per_batch;
+        a->layer_hi = std::min(L, a->layer_lo + opt_.layers_per_batch);
+        fn_args_.push_back(std::move(a));
+      }
+  for (int r = 0; r < R; ++r) ranks_.emplace_back(new Rank());
+  for (int r = 0; r < R; ++r) ranks_[(size_t)r]->th = std::thread([this, r] { rank_main(r); });
+  for (auto& rk : ranks_) {
+    std::unique_lock<std::mutex> lk(rk->mu);
+    rk->cv.wait(lk, [&] { return rk->ready; });
+    if (!rk->init_error.empty()) {
+      std::string msg = rk->init_error;
+      lk.unlock();
+      stop_ = true;
+      for (auto& x : ranks_) { x->cv.notify_all(); if (x->th.joinable()) x->th.join(); }
+      throw std::runtime_error("LayerwiseGroup: " + msg);
+    }
+  }
+}
+
+LayerwiseGroup::~LayerwiseGroup() {
+  stop_ = true;
+  for (auto& rk : ranks_) {
+    { std::lock_guard<std::mutex> g(rk->mu); }
+    rk->cv.notify_all();
+  }
+  for (auto& rk : ranks_) if (rk->th.joinable()) rk->th.join();
+  for (int fd : eventfds_) if (fd >= 0) close(fd);
+  if (id_ring_) cudaFreeHost(id_ring_);
+}
+
+int LayerwiseGroup::eventfd_of(int counter, int rank, int layer) const {
+  if (eventfds_.empty()) return -1;
+  const int L = opt_.group.num_layers, R = (int)gpus_.size();
+  return eventfds_[((size_t)counter * R + rank) * L + layer];
+}
+
+void LayerwiseGroup::set_eventfd(int counter, int rank, int layer, int fd) {
+  const int L = opt_.group.num_layers, R = (int)gpus_.size(), C = opt_.num_counters;
+  if (counter < 0 || counter >= C || rank < 0 || rank >= R || layer < 0 || layer >= L)
+    throw std::out_of_range("LayerwiseGroup::set_eventfd: index out of range");
+  std::lock_guard<std::mutex> api(api_mu_);
+  if (eventfds_.empty()) eventfds_.assign((size_t)C * R * L, -1);
+  int& slot = eventfds_[((size_t)counter * R + rank) * L + layer];
+  if (slot >= 0) close(slot);
+  slot = dup(fd);
+  if (slot < 0) throw std::runtime_error(std::string("dup(eventfd): ") + strerror(errno));
+}
+
+uint64_t LayerwiseGroup::device_flags_ptr(int rank, int counter) const {
+  return (uint64_t)(uintptr_t)(ranks_.at((size_t)rank)->dev_flags + (size_t)counter * opt_.group.num_layers);
+}
+uint64_t LayerwiseGroup::host_flags_ptr(int rank, int counter) const {
+  return (uint64_t)(uintptr_t)(ranks_.at((size_t)rank)->host_flags + (size_t)counter * opt_.group.num_layers);
+}
+
+cudaError_t LayerwiseGroup::stream_wait_layer(int rank, int counter, int layer, cudaStream_t stream) {
+  Rank& rk = *ranks_.at((size_t)rank);
+  return cudaStreamWaitEvent(stream, rk.layer_ev[(size_t)counter * opt_.group.num_layers + layer], 0);
+}
+
+void LayerwiseGroup::notify(int rank, int counter, int layer_lo, int layer_hi) {
+  if (eventfds_.empty()) return;
+  const uint64_t one = 1;
+  for (int l = layer_lo; l < layer_hi; ++l) {
+    const int fd = eventfd_of(counter, rank, l);
+    if (fd >= 0) { ssize_t w = write(fd, &one, sizeof(one)); (void)w; }
+  }
+}
+
+void CUDART_CB LayerwiseGroup::host_fn(void* arg) {
+  auto* a = static_cast<HostFnArg*>(arg);
+  a->self->notify(a->rank, a->counter, a->layer_lo, a->layer_hi);
+}
+
+void LayerwiseGroup::rank_main(int r) {
+  Rank& rk = *ranks_[(size_t)r];
+  const int L = opt_.group.num_layers, C = opt_.num_counters;
+  try {
+    check(cudaSetDevice(gpus_[(size_t)r].device), "cudaSetDevice");
+    int lo = 0, hi = 0;
+    check(cudaDeviceGetStreamPriorityRange(&lo, &hi), "cudaDeviceGetStreamPriorityRange");
+    check(cudaStreamCreateWithPriority(&rk.stream, cudaStreamNonBlocking, hi), "cudaStreamCreateWithPriority");
+    check(cudaMalloc((void**)&rk.dev_flags, (size_t)C * L * sizeof(uint32_t)), "cudaMalloc(flags)");
+    check(cudaMemset(rk.dev_flags, 0, (size_t)C * L * sizeof(uint32_t)), "cudaMemset(flags)");
+    check(cudaMalloc((void**)&rk.done_counter, sizeof(uint32_t)), "cudaMalloc(counter)");
+    check(cudaMemset(rk.done_counter, 0, sizeof(uint32_t)), "cudaMemset(counter)");
+    check(cudaHostAlloc((void**)&rk.host_flags, (size_t)C * L * sizeof(uint32_t),
+                        cudaHostAllocPortable | cudaHostAllocMapped), "cudaHostAlloc(flags)");
+    std::memset(rk.host_flags, 0, (size_t)C * L * sizeof(uint32_t));
+    check(cudaHostAlloc((void**)&rk.status, kStatusWords * sizeof(int32_t),
+                        cudaHostAllocPortable | cudaHostAllocMapped), "cudaHostAlloc(status)");
+    std::memset(rk.status, 0, kStatusWords * sizeof(int32_t));
+    rk.layer_ev.resize((size_t)C * L);
+    for (auto& e : rk.layer_ev) check(cudaEventCreate(&e), "cudaEventCreate");
+    check(cudaEventCreate(&rk.ev_begin), "cudaEventCreate");
+    check(cudaDeviceSynchronize(), "cudaDeviceSynchronize");
+  } catch (const std::exception& e) {
+    std::lock_guard<std::mutex> g(rk.mu);
+    rk.init_error = e.what();
+    rk.ready = true;
+    rk.cv.notify_all();
+    return;
+  }
+  { std::lock_guard<std::mutex> g(rk.mu); rk.ready = true; }
+  rk.cv.notify_all();
+  for (;;) {
+    Job j;
+    {
+      std::unique_lock<std::mutex> lk(rk.mu);
+      rk.cv.wait(lk, [&] { return stop_.load() || !rk.q.empty(); });
+      if (rk.q.empty() && stop_.load()) break;
+      j = rk.q.front();
+      rk.q.pop_front();
+    }
+    run_job(r, j);
+    { std::lock_guard<std::mutex> g(done_mu_); rk.done = true; }
+    done_cv_.notify_all();
+  }
+  for (auto& e : rk.layer_ev) cudaEventDestroy(e);
+  if (rk.ev_begin) cudaEventDestroy(rk.ev_begin);
+  if (rk.dev_flags) cudaFree(rk.dev_flags);
+  if (rk.done_counter) cudaFree(rk.done_counter);
+  if (rk.host_flags) cudaFreeHost(rk.host_flags);
+  if (rk.status) cudaFreeHost(rk.status);
+  if (rk.stream) cudaStreamDestroy(rk.stream);
+}
+
+void LayerwiseGroup::run_job(int r, const Job& j) {
+  Rank& rk = *ranks_[(size_t)r];
+  const int L = opt_.group.num_layers, B = opt_.layers_per_batch, R = (int)gpus_.size();
+  const int batches = (L + B - 1) / B;
+  rk.res_status = 0;
+  rk.res_layer_ms.assign((size_t)L, 0.f);
+  cudaEvent_t* ev = rk.layer_ev.data() + (size_t)j.counter * L;
+  uint32_t* hflags = rk.host_flags + (size_t)j.counter * L;
+  cudaError_t err = cudaEventRecord(rk.ev_begin, rk.stream);
+  for (int b = 0; b < batches && err == cudaSuccess; ++b) {
+    const int l0 = b * B, l1 = std::min(L, l0 + B);
+    KvCopyParams p;
+    bool skip = false;
+    fill_kv_params(gpus_[(size_t)r], host_, opt_.group, r, R, j.gpu_blocks, j.cpu_blocks, j.n, true, l0, l1 - l0, 0,
+                   p, skip);
+    p.status = rk.status;
+    p.done_counter = rk.done_counter;
+    p.dev_flags = rk.dev_flags + (size_t)j.counter * L;
+    p.host_flags = hflags;
+    p.epoch = j.epoch;
+    if (j.n > 0) {
+      err = launch_kv_copy(p, opt_.group.h2d, rk.stream);
+    } else {
+      // nothing to restore: publish the flags from the host so waiters are released at once
+      for (int l = l0; l < l1; ++l) hflags[l] = j.epoch;
+      err = cudaMemcpyAsync(rk.dev_flags + (size_t)j.counter * L + l0, hflags + l0, (size_t)(l1 - l0) * 4,
+                            cudaMemcpyHostToDevice, rk.stream);
+    }
+    for (int l = l0; l < l1 && err == cudaSuccess; ++l) err = cudaEventRecord(ev[l], rk.stream);
+    if (err == cudaSuccess && opt_.notify == NotifyMode::HOSTFUNC) {
+      HostFnArg* a = fn_args_[((size_t)r * opt_.num_counters + j.counter) * batches + b].get();
+      err = cudaLaunchHostFunc(rk.stream, host_fn, a);
+    }
+  }
+  if (err == cudaSuccess && opt_.notify != NotifyMode::HOSTFUNC) {
+    // retire the batches in order from this thread
+    const auto t0 = std::chrono::steady_clock::now();
+    for (int b = 0; b < batches; ++b) {
+      const int l0 = b * B, l1 = std::min(L, l0 + B);
+      for (;;) {
+        bool ready;
+        if (opt_.notify == NotifyMode::POLLING) {
+          cudaError_t q = cudaEventQuery(ev[l1 - 1]);
+          if (q != cudaSuccess && q != cudaErrorNotReady) { err = q; break; }
+          ready = q == cudaSuccess;
+        } else {
+          ready = __atomic_load_n(hflags + l1 - 1, __ATOMIC_ACQUIRE) == j.epoch;
+        }
+        if (ready) break;
+        if (std::chrono::steady_clock::now() - t0 > std::chrono::seconds(120)) { err = cudaErrorTimeout; break; }
+      }
+      if (err != cudaSuccess) break;
+      notify(r, j.counter, l0, l1);
+    }
+  }
+  if (err == cudaSuccess) err = cudaStreamSynchronize(rk.stream);
+  if (err != cudaSuccess) {
+    (void)cudaGetLastError();
+    rk.res_status = -(int)err;
+    rk.res_ms = 0.f;
+    return;
+  }
+  rk.res_status = collect_status(rk.status);
+  for (int l = 0; l < L; ++l) cudaEventElapsedTime(&rk.res_layer_ms[(size_t)l], rk.ev_begin, ev[l]);
+  rk.res_ms = rk.res_layer_ms[(size_t)L - 1];
+}
+
+LayerwiseResult LayerwiseGroup::restore(const int64_t* gpu_blocks, const int64_t* cpu_blocks, int64_t n,
+                                        int counter_id, SsdIoEngine* ssd, const SsdLayout* ssd_layout,
+                                        const int64_t* ssd_src, const int64_t* cpu_dst, int64_t n_disk) {
+  if (counter_id < 0 || counter_id >= opt_.num_counters) throw std::invalid_argument("LayerwiseGroup: bad counter id");
+  if (n > opt_.group.max_blocks_per_op) throw std::invalid_argument("LayerwiseGroup: op exceeds max_blocks_per_op");
+  std::lock_guard<std::mutex> api(api_mu_);
+  LayerwiseResult res;
+  if (n_disk > 0) {
+    if (ssd == nullptr || ssd_layout == nullptr) throw std::invalid_argument("LayerwiseGroup: disk blocks without an SSD engine");
+    const auto t0 = std::chrono::steady_clock::now();
+    std::vector<uint8_t> ok((size_t)n_disk, 0);
+    const int64_t nfail = ssd->transfer(reinterpret_cast<uint8_t*>(host_.base), cpu_dst, ssd_src, n_disk, true,
+                                        *ssd_layout, 0, ssd_layout->num_layers_total, ok.data());
+    res.disk_ms = std::chrono::duration<float, std::milli>(std::chrono::steady_clock::now() - t0).count();
+    if (nfail > 0) {
+      res.status = 1 << 29;  // disk stage failed: nothing is restored, nothing is signalled
+      return res;
+    }
+  }
+  if (n > 0) {
+    std::memcpy(id_ring_, gpu_blocks, (size_t)n * sizeof(int64_t));
+    std::memcpy(id_ring_ + opt_.group.max_blocks_per_op, cpu_blocks, (size_t)n * sizeof(int64_t));
+  }
+  Job j;
+  j.n = n;
+  j.counter = counter_id;
+  j.epoch = ++epochs_[(size_t)counter_id];
+  j.gpu_blocks = id_ring_;
+  j.cpu_blocks = id_ring_ + opt_.group.max_blocks_per_op;
+  {
+    std::lock_guard<std::mutex> g(done_mu_);
+    for (auto& rk : ranks_) rk->done = false;
+  }
+  for (auto& rk : ranks_) {
+    { std::lock_guard<std::mutex> g(rk->mu); rk->q.push_back(j); }
+    rk->cv.notify_one();
+  }
+  {
+    std::unique_lock<std::mutex> lk(done_mu_);
+    done_cv_.wait(lk, [&] {
+      for (auto& rk : ranks_) if (!rk->done) return false;
+      return true;
+    });
+  }
+  for (auto& rk : ranks_) {
+    if (rk->res_status < 0) res.status = rk->res_status;
+    else if (res.status >= 0) res.status |= rk->res_status;
+    res.total_ms = std::max(res.total_ms, rk->res_ms);
+  }
+  res.layer_done_ms = ranks_[0]->res_layer_ms;
+  return res;
+}
+
+}  // namespace fkv

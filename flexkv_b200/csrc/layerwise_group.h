@@ -1,0 +1,131 @@
+// Layer-by-layer restore with per-layer completion signals.
+//
+// A restore first brings any SSD-resident blocks into the host pool (all
+// layers), then copies host -> GPU one layer batch at a time on a
+// highest-priority stream per GPU, so that the model's layer l can start as
+// soon as its KV has landed while layers l+1.. are still in flight
+// (reference behaviour: csrc/layerwise.cpp:944-1311, eventfd table
+// [counters][tp][layers] :537-544, host-callback notification :105-137,
+// polling notification :36-68).
+//
+// Each layer batch is one copy kernel whose last CTA publishes the restore's
+// epoch to a device flag (for consumer kernels and CUDA-event waits on the same
+// GPU) and to a mapped host flag. Three ways reach another process's eventfd:
+//   hostfunc : cudaLaunchHostFunc after the kernel writes the eventfd
+//   polling  : a host thread polls cudaEventQuery on per-layer events
+//   flag     : a host thread polls the mapped host flag the kernel wrote
+// Every rank signals its own eventfd as soon as its own copy is done.
+#pragma once
+#include <atomic>
+#include <condition_variable>
+#include <cstdint>
+#include <deque>
+#include <memory>
+#include <mutex>
+#include <string>
+#include <thread>
+#include <vector>
+
+#include <cuda_runtime.h>
+
+#include "ssd_io.h"
+#include "transfer_group.h"
+
+namespace fkv {
+
+enum class NotifyMode : int { HOSTFUNC = 0, POLLING = 1, FLAG = 2 };
+NotifyMode parse_notify_mode(const std::string& s);
+
+struct LayerwiseOptions {
+  GroupOptions group;
+  NotifyMode notify = NotifyMode::HOSTFUNC;
+  int num_counters = 3;       // independent flag / eventfd sets (restores in flight)
+  int layers_per_batch = 1;
+  bool create_eventfds = true;
+};
+
+struct LayerwiseResult {
+  int status = 0;
+  float total_ms = 0.f;              // first launch to last completion, max over ranks (CUDA events)
+  float disk_ms = 0.f;               // host wall time of the SSD -> host stage
+  std::vector<float> layer_done_ms;  // per layer, time since first launch (rank 0)
+};
+
+class LayerwiseGroup {
+ public:
+  LayerwiseGroup(std::vector<GpuSide> gpus, HostSide host, LayerwiseOptions opt);
+  ~LayerwiseGroup();
+
+  // blocking; `ssd` may be null when nothing comes from disk
+  LayerwiseResult restore(const int64_t* gpu_blocks, const int64_t* cpu_blocks, int64_t n, int counter_id,
+                          SsdIoEngine* ssd, const SsdLayout* ssd_layout, const int64_t* ssd_src,
+                          const int64_t* cpu_dst, int64_t n_disk);
+
+  // eventfd of (counter, rank, layer); -1 when eventfds are disabled
+  int eventfd_of(int counter, int rank, int layer) const;
+  std::vector<int> eventfds_flat() const { return eventfds_; }
+  // installs a caller-owned eventfd (e.g. received from the engine over a UNIX
+  // socket); the group takes a dup() of it
+  void set_eventfd(int counter, int rank, int layer, int fd);
+  uint64_t device_flags_ptr(int rank, int counter) const;  // uint32[num_layers] in device memory
+  uint64_t host_flags_ptr(int rank, int counter) const;    // uint32[num_layers] in mapped host memory
+  uint32_t epoch_of(int counter) const { return epochs_[(size_t)counter]; }
+  // makes `stream` (a CUDA stream of rank's device) wait for layer `layer` of the restore in flight on `counter`
+  cudaError_t stream_wait_layer(int rank, int counter, int layer, cudaStream_t stream);
+  int num_ranks() const { return (int)gpus_.size(); }
+  int num_layers() const { return opt_.group.num_layers; }
+  int num_counters() const { return opt_.num_counters; }
+
+ private:
+  struct Job {
+    int64_t n;
+    int counter;
+    uint32_t epoch;
+    const int64_t* gpu_blocks;  // in the id ring
+    const int64_t* cpu_blocks;
+  };
+  struct Rank {
+    std::thread th;
+    std::mutex mu;
+    std::condition_variable cv;
+    std::deque<Job> q;
+    bool ready = false;
+    std::string init_error;
+    cudaStream_t stream = nullptr;
+    uint32_t* dev_flags = nullptr;      // [counters][layers]
+    uint32_t* host_flags = nullptr;     // mapped, [counters][layers]
+    uint32_t* done_counter = nullptr;   // device scratch word
+    int32_t* status = nullptr;          // mapped, kStatusWords
+    std::vector<cudaEvent_t> layer_ev;  // [counters][layers]
+    cudaEvent_t ev_begin = nullptr;
+    // result of the last job
+    int res_status = 0;
+    float res_ms = 0.f;
+    std::vector<float> res_layer_ms;
+    bool done = false;
+  };
+  struct HostFnArg {
+    LayerwiseGroup* self;
+    int rank, counter, layer_lo, layer_hi;
+  };
+
+  void rank_main(int r);
+  void run_job(int r, const Job& j);
+  void notify(int rank, int counter, int layer_lo, int layer_hi);
+  static void CUDART_CB host_fn(void* arg);
+
+  std::vector<GpuSide> gpus_;
+  HostSide host_;
+  LayerwiseOptions opt_;
+  std::vector<std::unique_ptr<Rank>> ranks_;
+  std::atomic<bool> stop_{false};
+  std::vector<int> eventfds_;       // [counters][ranks][layers]
+  std::vector<uint32_t> epochs_;    // per counter
+  int64_t* id_ring_ = nullptr;      // [2][max_blocks], mapped pinned
+  std::mutex api_mu_;               // one restore at a time per group
+  std::mutex done_mu_;
+  std::condition_variable done_cv_;
+  std::vector<std::unique_ptr<HostFnArg>> fn_args_;
+};
+
+}  // namespace fkv

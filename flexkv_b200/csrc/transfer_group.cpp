@@ -73,10 +73,9 @@ void TransferGroup::set_launch(bool h2d, KvCopyLaunch cfg) {
   (h2d ? opt_.h2d : opt_.d2h) = cfg;
 }
 
-void TransferGroup::fill_params(int r, const Task& t, KvCopyParams& p, bool& skip) const {
-  std::lock_guard<std::mutex> g(ptr_mu_);
-  const GpuSide& gs = gpus_[(size_t)r];
-  const int N = (int)gpus_.size();
+void fill_kv_params(const GpuSide& gs, const HostSide& host, const GroupOptions& opt, int r, int N,
+                    const int64_t* gpu_blocks, const int64_t* cpu_blocks, int64_t n, bool h2d, int layer_start,
+                    int num_layers, uint64_t rotate, KvCopyParams& p, bool& skip) {
   std::memset(&p, 0, sizeof(p));
   for (size_t i = 0; i < gs.ptrs.size(); ++i) p.gpu_ptrs[i] = gs.ptrs[i];
   p.idx_layer_mul = gs.idx_layer_mul;
@@ -84,43 +83,51 @@ void TransferGroup::fill_params(int r, const Task& t, KvCopyParams& p, bool& ski
   p.g_layer_stride = gs.layer_stride;
   p.g_kv_stride = gs.kv_stride;
   p.g_block_stride = gs.block_stride;
-  p.cpu_base = host_.base;
-  p.c_layer_stride = host_.layer_stride;
-  p.c_kv_stride = host_.kv_stride;
-  p.c_block_stride = host_.block_stride;
-  p.gpu_blocks = id_ring_ + ((size_t)t.slot * 2 + 0) * (size_t)opt_.max_blocks_per_op;
-  p.cpu_blocks = id_ring_ + ((size_t)t.slot * 2 + 1) * (size_t)opt_.max_blocks_per_op;
-  p.num_pairs = (int32_t)t.n;
-  p.layer_start = t.layer_start;
-  p.num_layers = t.num_layers;
-  p.kv_dim = opt_.kv_dim;
-  p.chunk_bytes = opt_.chunk_bytes;
+  p.cpu_base = host.base;
+  p.c_layer_stride = host.layer_stride;
+  p.c_kv_stride = host.kv_stride;
+  p.c_block_stride = host.block_stride;
+  p.gpu_blocks = gpu_blocks;
+  p.cpu_blocks = cpu_blocks;
+  p.num_pairs = (int32_t)n;
+  p.layer_start = layer_start;
+  p.num_layers = num_layers;
+  p.kv_dim = opt.kv_dim;
+  p.chunk_bytes = opt.chunk_bytes;
   p.gpu_num_blocks = gs.num_blocks;
-  p.cpu_num_blocks = host_.num_blocks;
-  p.h2d = t.h2d ? 1 : 0;
+  p.cpu_num_blocks = host.num_blocks;
+  p.h2d = h2d ? 1 : 0;
   skip = false;
-  if (!opt_.shared_kv) {
-    p.c_off = (int64_t)r * opt_.cpu_tp_stride;
+  if (!opt.shared_kv) {
+    p.c_off = (int64_t)r * opt.cpu_tp_stride;
     return;
   }
-  if (t.h2d || N == 1) return;  // every rank restores the full chunk
-  switch (opt_.shared_mode) {
+  if (h2d || N == 1) return;  // every rank restores the full chunk
+  switch (opt.shared_mode) {
     case SharedKvMode::SHARDED:
-      p.chunk_bytes = opt_.chunk_bytes / N;
+      p.chunk_bytes = opt.chunk_bytes / N;
       p.g_off = p.c_off = (int64_t)r * p.chunk_bytes;
       break;
     case SharedKvMode::ALL_WRITE: break;
     case SharedKvMode::RANK0_ONLY: skip = r != 0; break;
-    case SharedKvMode::RANK_ROTATE: skip = (int)(t.rotate % (uint64_t)N) != r; break;
+    case SharedKvMode::RANK_ROTATE: skip = (int)(rotate % (uint64_t)N) != r; break;
     case SharedKvMode::LAYER_PARALLEL: {
-      const int per = (t.num_layers + N - 1) / N;
-      const int lo = std::min(t.num_layers, r * per), hi = std::min(t.num_layers, (r + 1) * per);
-      p.layer_start = t.layer_start + lo;
+      const int per = (num_layers + N - 1) / N;
+      const int lo = std::min(num_layers, r * per), hi = std::min(num_layers, (r + 1) * per);
+      p.layer_start = layer_start + lo;
       p.num_layers = hi - lo;
       skip = hi <= lo;
       break;
     }
   }
+}
+
+void TransferGroup::fill_params(int r, const Task& t, KvCopyParams& p, bool& skip) const {
+  std::lock_guard<std::mutex> g(ptr_mu_);
+  fill_kv_params(gpus_[(size_t)r], host_, opt_, r, (int)gpus_.size(),
+                 id_ring_ + ((size_t)t.slot * 2 + 0) * (size_t)opt_.max_blocks_per_op,
+                 id_ring_ + ((size_t)t.slot * 2 + 1) * (size_t)opt_.max_blocks_per_op, t.n, t.h2d, t.layer_start,
+                 t.num_layers, t.rotate, p, skip);
 }
 
 void TransferGroup::rank_main(int r) {

@@ -62,6 +62,13 @@ struct OpResult {
   float gpu_ms = 0.f;    // max over ranks, CUDA events on the launching stream
 };
 
+// Fills the addressing part of a launch for rank `r` of `n_ranks` (shared by the
+// transfer group and the layerwise group). `skip` is set when the rank has
+// nothing to do under the shared-KV write mode.
+void fill_kv_params(const GpuSide& gs, const HostSide& host, const GroupOptions& opt, int r, int n_ranks,
+                    const int64_t* gpu_blocks, const int64_t* cpu_blocks, int64_t n, bool h2d, int layer_start,
+                    int num_layers, uint64_t rotate, KvCopyParams& p, bool& skip);
+
 class TransferGroup {
  public:
   TransferGroup(std::vector<GpuSide> gpus, HostSide host, GroupOptions opt);

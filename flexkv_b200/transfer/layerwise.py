@@ -1,0 +1,182 @@
+"""Layerwise restore: the worker that executes LAYERWISE ops and the eventfd
+hand-off with the engine process.
+
+The engine's per-layer hook blocks on one eventfd per (counter, tp_rank, layer);
+the worker signals each exactly once per restore, after that layer's KV has
+landed on that rank's GPU (flexkv/transfer/layerwise.py:756-1059,
+csrc/layerwise.cpp:105-137). The descriptors travel over a UNIX socket with
+SCM_RIGHTS using the reference's framing (flexkv/transfer/layerwise.py:822-860):
+
+    header  ``iiii``  = rank, tp_size, num_layers, num_counters   (16 bytes)
+    then per counter: 4-byte counter id + one SCM_RIGHTS batch of num_layers fds
+    reply   1 byte ACK
+"""
+from __future__ import annotations
+
+import array
+import os
+import select
+import socket
+import struct
+import threading
+from typing import Callable, Dict, List, Optional, Sequence
+
+import numpy as np
+
+from .. import _native
+from ..common.config import GLOBAL_CONFIG_FROM_ENV
+from ..common.debug import flexkv_logger
+from ..common.transfer import LayerwiseTransferOp, TransferOp, WorkerKey
+from .workers import OpOutcome, TransferWorker, _launch_cfg
+
+HEADER = struct.Struct("iiii")
+ACK = b"\x01"
+
+
+def send_eventfds(sock_path: str, rank: int, tp_size: int, fds_per_counter: Sequence[Sequence[int]],
+                  timeout: float = 30.0) -> None:
+    """Engine side: hands this rank's eventfds (``[counter][layer]``) to the worker."""
+    num_counters = len(fds_per_counter)
+    num_layers = len(fds_per_counter[0])
+    with socket.socket(socket.AF_UNIX, socket.SOCK_STREAM) as s:
+        s.settimeout(timeout)
+        s.connect(sock_path)
+        s.sendall(HEADER.pack(rank, tp_size, num_layers, num_counters))
+        for c, fds in enumerate(fds_per_counter):
+            if len(fds) != num_layers:
+                raise ValueError("every counter needs one eventfd per layer")
+            s.sendmsg([struct.pack("i", c)], [(socket.SOL_SOCKET, socket.SCM_RIGHTS, array.array("i", fds))])
+        if s.recv(1) != ACK:
+            raise RuntimeError("layerwise worker did not acknowledge the eventfds")
+
+
+def _recv_exact(conn: socket.socket, n: int) -> bytes:
+    buf = b""
+    while len(buf) < n:
+        part = conn.recv(n - len(buf))
+        if not part:
+            raise ConnectionError("peer closed during the eventfd handshake")
+        buf += part
+    return buf
+
+
+class EventfdReceiver:
+    """Worker side: listens on a UNIX socket and installs received eventfds."""
+
+    def __init__(self, sock_path: str, install: Callable[[int, int, int, int], None]) -> None:
+        self.sock_path = sock_path
+        self._install = install
+        self._stop = threading.Event()
+        self._thread: Optional[threading.Thread] = None
+        self.ranks_seen: Dict[int, int] = {}
+        if os.path.exists(sock_path):
+            os.unlink(sock_path)
+        self._srv = socket.socket(socket.AF_UNIX, socket.SOCK_STREAM)
+        self._srv.bind(sock_path)
+        self._srv.listen(64)
+
+    def start(self) -> None:
+        self._thread = threading.Thread(target=self._loop, name="flexkv-eventfd-recv", daemon=True)
+        self._thread.start()
+
+    def _loop(self) -> None:
+        while not self._stop.is_set():
+            r, _, _ = select.select([self._srv], [], [], 0.2)
+            if not r:
+                continue
+            conn, _ = self._srv.accept()
+            try:
+                self._handle(conn)
+            except Exception as e:  # noqa: BLE001
+                flexkv_logger.error("eventfd handshake failed: %s", e)
+            finally:
+                conn.close()
+
+    def _handle(self, conn: socket.socket) -> None:
+        conn.settimeout(30.0)
+        rank, tp_size, num_layers, num_counters = HEADER.unpack(_recv_exact(conn, HEADER.size))
+        for _ in range(num_counters):
+            fds = array.array("i")
+            msg, anc, _, _ = conn.recvmsg(4, socket.CMSG_LEN(num_layers * fds.itemsize))
+            while len(msg) < 4:
+                msg += _recv_exact(conn, 4 - len(msg))
+            (counter,) = struct.unpack("i", msg)
+            for level, ctype, data in anc:
+                if level == socket.SOL_SOCKET and ctype == socket.SCM_RIGHTS:
+                    fds.frombytes(data[:len(data) - (len(data) % fds.itemsize)])
+            if len(fds) != num_layers:
+                raise RuntimeError(f"expected {num_layers} eventfds for counter {counter}, got {len(fds)}")
+            for layer, fd in enumerate(fds):
+                self._install(counter, rank, layer, fd)     # the native side keeps a dup
+                os.close(fd)
+        self.ranks_seen[rank] = num_counters
+        conn.sendall(ACK)
+
+    def stop(self) -> None:
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join(timeout=5)
+        self._srv.close()
+        try:
+            os.unlink(self.sock_path)
+        except OSError:
+            pass
+
+
+def build_layerwise_group(storage, model_config, key: WorkerKey, notify_mode: Optional[str] = None,
+                          num_counters: int = 3, layers_per_batch: int = 1, create_eventfds: bool = True):
+    from ..common.storage import KVCacheLayoutType
+    env = GLOBAL_CONFIG_FROM_ENV
+    regs = storage.gpu_regs[key]
+    ranks = sorted(regs)
+    host, reg0 = storage.host, regs[ranks[0]]
+    shared = model_config.use_mla or model_config.num_kv_heads == 1
+    n_slices = 1 if shared else model_config.effective_tp_size
+    if host.layout.type == KVCacheLayoutType.BLOCKFIRST:
+        layer_stride, kv_stride, tp_stride = host.layer_stride // n_slices, host.kv_stride // n_slices, \
+            host.block_bytes // n_slices
+    else:
+        layer_stride, kv_stride, tp_stride = host.layer_stride, host.kv_stride, host.chunk_bytes // n_slices
+    host_d = dict(base=host.base, layer_stride=layer_stride, kv_stride=kv_stride, block_stride=host.block_bytes,
+                  num_blocks=host.num_blocks)
+    opts = dict(num_layers=reg0.num_layers, kv_dim=reg0.kv_dim, chunk_bytes=reg0.chunk_bytes,
+                cpu_tp_stride=tp_stride, shared_kv=shared, h2d=_launch_cfg(env, True), d2h=_launch_cfg(env, False),
+                max_blocks_per_op=max(4096, min(1 << 18, host.num_blocks)),
+                notify_mode=notify_mode or env.layerwise_notify_mode, num_counters=num_counters,
+                layers_per_batch=layers_per_batch, create_eventfds=create_eventfds)
+    return _native.C.LayerwiseGroup([regs[r].as_native() for r in ranks], host_d, opts)
+
+
+class LayerwiseWorker(TransferWorker):
+    """Executes LAYERWISE ops: SSD -> host for all layers, then host -> GPU per layer with signals."""
+
+    name = "layerwise"
+
+    def __init__(self, storage, model_config, key: WorkerKey, sock_path: Optional[str] = None, **kw) -> None:
+        super().__init__()
+        self.storage = storage
+        self.group = build_layerwise_group(storage, model_config, key, **kw)
+        self.receiver: Optional[EventfdReceiver] = None
+        if sock_path:
+            self.receiver = EventfdReceiver(sock_path, self.group.set_eventfd)
+            self.receiver.start()
+        self.last_result = None
+
+    def execute(self, op: TransferOp) -> OpOutcome:
+        assert isinstance(op, LayerwiseTransferOp)
+        st = self.storage
+        has_disk = op.src_block_ids_disk2h.size > 0
+        if has_disk and st.ssd is None:
+            return OpOutcome(False, error="layerwise op reads from SSD but no SSD tier is configured")
+        r = self.group.restore(op.dst_block_ids_h2d, op.src_block_ids_h2d, op.counter_id,
+                               st.ssd.engine if has_disk else None, st.ssd_layout_dict() if has_disk else None,
+                               op.src_block_ids_disk2h if has_disk else None,
+                               op.dst_block_ids_disk2h if has_disk else None)
+        self.last_result = r
+        nbytes = int(op.src_block_ids_h2d.size) * st.host.block_bytes
+        return OpOutcome(r.status == 0, gpu_ms=r.total_ms, num_bytes=nbytes,
+                         error="" if r.status == 0 else f"layerwise status 0x{r.status & 0xffffffff:x}")
+
+    def close(self) -> None:
+        if self.receiver is not None:
+            self.receiver.stop()

@@ -10,6 +10,7 @@ task layer can report FAILED instead of timing out
 """
 from __future__ import annotations
 
+import os
 import queue
 import threading
 import time
@@ -252,6 +253,11 @@ def build_workers(storage, model_config: ModelConfig, cache_config: CacheConfig
             w.group_layers = reg0.num_layers
             w.max_blocks = max(4096, min(1 << 18, storage.host.num_blocks))
             workers[(key, TransferType.H2D if h2d else TransferType.D2H)] = w
+        if GLOBAL_CONFIG_FROM_ENV.enable_layerwise_transfer:
+            from .layerwise import LayerwiseWorker
+            sock = os.environ.get("FLEXKV_LAYERWISE_SOCK", "")
+            workers[(key, TransferType.LAYERWISE)] = LayerwiseWorker(
+                storage, model_config, key, sock_path=f"{sock}.{key.dp_client_id}" if sock else None)
     if storage.ssd is not None:
         k0 = WorkerKey(0, 0)
         workers[(k0, TransferType.DISK2H)] = SsdWorker(storage, True)

@@ -1,0 +1,124 @@
+"""Layerwise restore on a GPU: bytes, one eventfd unit per layer per restore and
+none before the transfer, layer completion order, stream waits, device flags
+with a bounded wait (reference: tests/test_layerwise_eventfd_timing.py:342-429)."""
+import os
+import struct
+
+import numpy as np
+import pytest
+import torch
+
+from flexkv_b200 import _native
+from flexkv_b200.models import KVShape, alloc_paged_cache
+from flexkv_b200.storage.gpu_layout import register_tensors
+
+pytestmark = pytest.mark.gpu
+C = _native.C
+
+
+def _setup(shape, NB=128, notify="hostfunc", layers_per_batch=1, engine_layout="vllm"):
+    dev = torch.device("cuda:0")
+    kv, layout = alloc_paged_cache(shape, NB, dev, engine_layout, fill="normal", seed=21)
+    reg = register_tensors(kv, layout)
+    chunk = reg.chunk_bytes
+    bb = shape.num_layers * shape.kv_dim * chunk
+    pool = torch.zeros(NB, shape.num_layers, shape.kv_dim, chunk, dtype=torch.uint8).pin_memory()
+    host = dict(base=pool.data_ptr(), layer_stride=shape.kv_dim * chunk, kv_stride=chunk, block_stride=bb,
+                num_blocks=NB)
+    opts = dict(num_layers=shape.num_layers, kv_dim=shape.kv_dim, chunk_bytes=chunk, max_blocks_per_op=NB,
+                notify_mode=notify, num_counters=3, layers_per_batch=layers_per_batch,
+                h2d=dict(num_ctas=4, tile_bytes=8192, engine=0))
+    grp = C.LayerwiseGroup([reg.as_native()], host, opts)
+    xfer = C.TransferGroup([reg.as_native()], host, dict(num_layers=shape.num_layers, kv_dim=shape.kv_dim,
+                                                         chunk_bytes=chunk, max_blocks_per_op=NB))
+    return kv, reg, pool, grp, xfer
+
+
+def _drain(fd):
+    n = 0
+    while True:
+        try:
+            n += struct.unpack("Q", os.read(fd, 8))[0]
+        except BlockingIOError:
+            return n
+
+
+@pytest.mark.parametrize("notify,lpb", [("hostfunc", 1), ("polling", 1), ("flag", 1), ("hostfunc", 3), ("flag", 4)])
+def test_restore_signals_each_layer_once(notify, lpb):
+    shape = KVShape("lw", 6, 2, 64, tokens_per_block=16)
+    kv, reg, pool, grp, xfer = _setup(shape, notify=notify, layers_per_batch=lpb)
+    rng = np.random.default_rng(3)
+    n = 40
+    src = rng.permutation(128)[:n].astype(np.int64)
+    cpu = rng.permutation(128)[:n].astype(np.int64)
+    assert xfer.transfer(src, cpu, False, 0, shape.num_layers).status == 0
+    want = [t[:, torch.from_numpy(src).cuda()].clone() for t in kv]
+    for t in kv:
+        t.zero_()
+    for counter in (0, 2):
+        fds = [grp.eventfd_of(counter, 0, l) for l in range(shape.num_layers)]
+        assert all(_drain(fd) == 0 for fd in fds)                 # nothing before the transfer
+        dst = rng.permutation(128)[:n].astype(np.int64)
+        r = grp.restore(dst, cpu, counter)
+        assert r.status == 0 and len(r.layer_done_ms) == shape.num_layers
+        assert all(b >= a for a, b in zip(r.layer_done_ms, r.layer_done_ms[1:]))   # layers land in order
+        assert [_drain(fd) for fd in fds] == [1] * shape.num_layers               # exactly one unit per layer
+        other = [grp.eventfd_of(1, 0, l) for l in range(shape.num_layers)]
+        assert all(_drain(fd) == 0 for fd in other)                                # other counters untouched
+        d = torch.from_numpy(dst).cuda()
+        for l in range(shape.num_layers):
+            assert torch.equal(kv[l][:, d], want[l])
+        # device and host flags carry the restore's epoch
+        ep = grp.epoch_of(counter)
+        flags = torch.empty(shape.num_layers, dtype=torch.int32, device="cuda")
+        torch.cuda.synchronize()
+        import ctypes
+        host_flags = (ctypes.c_uint32 * shape.num_layers).from_address(grp.host_flags_ptr(0, counter))
+        assert list(host_flags) == [ep] * shape.num_layers
+
+
+def test_empty_restore_fires_every_layer_immediately():
+    shape = KVShape("lw", 4, 2, 64, tokens_per_block=16)
+    kv, reg, pool, grp, xfer = _setup(shape)
+    e = np.zeros(0, dtype=np.int64)
+    r = grp.restore(e, e, 1)
+    assert r.status == 0
+    assert [_drain(grp.eventfd_of(1, 0, l)) for l in range(4)] == [1, 1, 1, 1]
+
+
+def test_model_stream_can_wait_per_layer_and_device_flags_release_consumers():
+    shape = KVShape("lw", 5, 2, 128, tokens_per_block=16)
+    kv, reg, pool, grp, xfer = _setup(shape, notify="flag")
+    n = 64
+    ids = np.arange(n, dtype=np.int64)
+    assert xfer.transfer(ids, ids, False, 0, shape.num_layers).status == 0
+    grp.restore(ids, ids, 0)                                       # first restore: epoch 1
+    ep = grp.epoch_of(0)
+    model = torch.cuda.Stream()
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    starts = torch.zeros(shape.num_layers, dtype=torch.int64, device="cuda")
+    # consumer kernels that wait (bounded) on the device flag of their layer, already satisfied by epoch `ep`
+    for l in range(shape.num_layers):
+        C.layer_stub(grp.device_flags_ptr(0, 0) + 4 * l, ep, 20_000, 500_000_000, status.data_ptr(),
+                     starts.data_ptr() + 8 * l, 2, model.cuda_stream)
+    model.synchronize()
+    assert status.item() == 0 and bool((starts[1:] >= starts[:-1]).all())
+    # stream-ordered wait on the per-layer event of a finished restore returns at once
+    for l in range(shape.num_layers):
+        grp.stream_wait_layer(0, 0, l, model.cuda_stream)
+    model.synchronize()
+
+
+def test_consumer_wait_runs_out_and_reports_status():
+    """A flag that nothing sets: the wait gives up after its budget, sets the
+    status word and the context stays usable."""
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    C.layer_stub(flag.data_ptr(), 5, 1000, 50_000_000, status.data_ptr(), 0, 1, torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    assert status.item() == 1
+    C.set_flags(flag.data_ptr(), 1, 7, torch.cuda.current_stream().cuda_stream)
+    status.zero_()
+    C.layer_stub(flag.data_ptr(), 5, 1000, 50_000_000, status.data_ptr(), 0, 1, torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    assert status.item() == 0 and flag.item() == 7
