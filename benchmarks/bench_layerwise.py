@@ -29,7 +29,7 @@ from flexkv_b200.storage.gpu_layout import register_tensors  # noqa: E402
 C = _native.C
 
 
-def build(shape, ngpu, gpu_blocks, host_blocks, engine_layout, notify, ctas, tile, tp_split):
+def build(shape, ngpu, gpu_blocks, host_blocks, engine_layout, notify, ctas, tile, tp_split, lpb=1):
     regs, caches = [], []
     for d in range(ngpu):
         kv, layout = alloc_paged_cache(shape, gpu_blocks, torch.device("cuda", d), engine_layout,
@@ -45,7 +45,7 @@ def build(shape, ngpu, gpu_blocks, host_blocks, engine_layout, notify, ctas, til
                 num_blocks=host_blocks)
     opts = dict(num_layers=shape.num_layers, kv_dim=shape.kv_dim, chunk_bytes=chunk,
                 cpu_tp_stride=block_bytes // slices if tp_split else 0, shared_kv=not tp_split,
-                max_blocks_per_op=max(gpu_blocks, 4096), notify_mode=notify, num_counters=3,
+                max_blocks_per_op=max(gpu_blocks, 4096), notify_mode=notify, num_counters=3, layers_per_batch=lpb,
                 h2d=dict(num_ctas=ctas, tile_bytes=tile, engine=0))
     grp = C.LayerwiseGroup([r.as_native() for r in regs], host, opts)
     return grp, region, caches, chunk, block_bytes
@@ -56,9 +56,9 @@ def scenario_notify(a):
     scales = {"small": (8, 16), "medium": (32, 64), "large": (80, 256)}
     for name, (layers, blocks) in scales.items():
         shape = KVShape(name, layers, 1, 512, dtype=torch.float16, use_mla=True, tokens_per_block=16)
-        for notify in ("hostfunc", "polling", "flag"):
+        for notify, lpb in (("hostfunc", 1), ("polling", 1), ("flag", 1), ("flag", 0)):
             grp, region, caches, chunk, bb = build(shape, a.gpus, blocks, blocks, "vllm", notify, a.ctas or 4,
-                                                   a.tile_bytes, tp_split=False)
+                                                   a.tile_bytes, tp_split=False, lpb=lpb)
             ids = np.arange(blocks, dtype=np.int64)
             lat = []
             for i in range(a.iters + 5):
@@ -72,7 +72,7 @@ def scenario_notify(a):
                     lat.append(dt)
             p50 = statistics.median(lat)
             per_gpu = layers * blocks * chunk
-            row = dict(scale=name, notify=notify, gpus=a.gpus, p50_ms=round(p50, 3),
+            row = dict(scale=name, notify=notify + ("+fused" if lpb == 0 else ""), gpus=a.gpus, p50_ms=round(p50, 3),
                        gbs_per_gpu=round(per_gpu / p50 / 1e6, 2), bytes_per_gpu=per_gpu,
                        gpu_ms=round(r.total_ms, 3))
             out.append(row)
@@ -86,7 +86,7 @@ def scenario_overlap(a):
     shape = KVShape("llama3-70b", 80, 8, 128, tokens_per_block=16)
     nblocks = a.requests * a.tokens // 16
     grp, region, caches, chunk, bb = build(shape, a.gpus, nblocks, nblocks, "sglang", a.notify, a.ctas or 8,
-                                           a.tile_bytes, tp_split=a.gpus > 1)
+                                           a.tile_bytes, tp_split=a.gpus > 1, lpb=a.layers_per_batch)
     L = shape.num_layers
     rng = np.random.default_rng(0)
     cpu = rng.permutation(nblocks).astype(np.int64)
@@ -128,7 +128,7 @@ def scenario_overlap(a):
     restore_ms = statistics.median(x[0] for x in rows)
     model_ms = statistics.median(x[1] for x in rows)
     per_rank = nblocks * L * shape.kv_dim * chunk
-    row = dict(scenario="overlap", gpus=a.gpus, notify=a.notify, blocks=nblocks, bytes_per_rank=per_rank,
+    row = dict(scenario="overlap", gpus=a.gpus, notify=a.notify, layers_per_batch=a.layers_per_batch, blocks=nblocks, bytes_per_rank=per_rank,
                restore_ms=round(restore_ms, 2), restore_gbs_per_gpu=round(per_rank / restore_ms / 1e6, 2),
                restore_gbs_box=round(a.gpus * per_rank / restore_ms / 1e6, 2),
                compute_only_ms=round(L * a.layer_us / 1e3, 2), overlapped_total_ms=round(model_ms, 2),
@@ -150,6 +150,7 @@ def main():
     ap.add_argument("--tokens", type=int, default=16384)
     ap.add_argument("--layer-us", type=float, default=200.0)
     ap.add_argument("--stub-ctas", type=int, default=148)
+    ap.add_argument("--layers-per-batch", type=int, default=0, help="0 = one fused launch with per-layer flags")
     ap.add_argument("--out", default="")
     a = ap.parse_args()
     rows = scenario_notify(a) if a.scenario == "notify" else scenario_overlap(a)

@@ -306,9 +306,9 @@ def load_env_config() -> Namespace:
         remote_layout_type=KVCacheLayoutType(_env("FLEXKV_REMOTE_LAYOUT", "BLOCKFIRST").upper()),
         gds_layout_type=KVCacheLayoutType(_env("FLEXKV_GDS_LAYOUT", "BLOCKFIRST").upper()),
         enable_layerwise_transfer=_env("FLEXKV_ENABLE_LAYERWISE_TRANSFER", False, bool),
-        # copy kernel launch shape; the bulk-copy pipeline wants a CTA per ~4 GB/s of link
-        transfer_num_cta_h2d=_env("FLEXKV_TRANSFER_NUM_CTA_H2D", 16),
-        transfer_num_cta_d2h=_env("FLEXKV_TRANSFER_NUM_CTA_D2H", 16),
+        # copy kernel launch shape: four single-warp CTAs with 16 KiB tiles already fill a PCIe Gen5 x16 link
+        transfer_num_cta_h2d=_env("FLEXKV_TRANSFER_NUM_CTA_H2D", 8),
+        transfer_num_cta_d2h=_env("FLEXKV_TRANSFER_NUM_CTA_D2H", 8),
         transfer_tile_bytes=_env("FLEXKV_TRANSFER_TILE_BYTES", 16384),
         transfer_engine=_env("FLEXKV_TRANSFER_ENGINE", "tma").lower(),   # tma | simt
         # accepted for compatibility, unused: copy-engine tuning of the reference

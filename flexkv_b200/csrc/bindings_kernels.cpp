@@ -47,6 +47,11 @@ KvCopyParams kv_params_from_dict(const py::dict& d) {
   p.cpu_num_blocks = geti("cpu_num_blocks", 0);
   p.status = (int32_t*)(uintptr_t)(uint64_t)geti("status_ptr", 0);
   p.h2d = (int32_t)geti("h2d", 0);
+  p.done_counter = (uint32_t*)(uintptr_t)(uint64_t)geti("done_counter_ptr", 0);
+  p.dev_flags = (uint32_t*)(uintptr_t)(uint64_t)geti("dev_flags_ptr", 0);
+  p.host_flags = (uint32_t*)(uintptr_t)(uint64_t)geti("host_flags_ptr", 0);
+  p.epoch = (uint32_t)geti("epoch", 0);
+  p.layer_major = (int32_t)geti("layer_major", 0);
   return p;
 }
 

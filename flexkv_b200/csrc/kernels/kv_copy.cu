@@ -57,21 +57,38 @@ struct TileAddr {
   uint32_t bytes;  // 0 = skip (bad block id)
 };
 
-// Decodes tile index t (warp-uniform) given the pair's block ids.
-__device__ __forceinline__ TileAddr tile_addr(const KvCopyParams& p, int64_t r, int64_t gblk, int64_t cblk,
-                                              int tile_bytes, int tiles_per_chunk) {
-  // r = index inside the pair: ((layer * kv_dim) + kv) * tiles_per_chunk + s
-  const int s = (int)(r % tiles_per_chunk);
-  const int lk = (int)(r / tiles_per_chunk);
-  const int kv = lk % p.kv_dim;
-  const int layer = p.layer_start + lk / p.kv_dim;
+// Position of a tile inside the launch. Tiles are enumerated pair-major
+// (pair, layer, kv, sub-tile: one host block's bytes are visited contiguously)
+// or, for per-layer signalling, layer-major (layer, pair, kv, sub-tile).
+struct TilePos {
+  int32_t pair, layer, kv, s;
+};
+
+__device__ __forceinline__ TilePos decode_tile(const KvCopyParams& p, int32_t major, int32_t r, int tiles_per_chunk) {
+  TilePos t;
+  t.s = r % tiles_per_chunk;
+  const int32_t q = r / tiles_per_chunk;
+  if (p.layer_major) {
+    t.layer = p.layer_start + major;
+    t.kv = q % p.kv_dim;
+    t.pair = q / p.kv_dim;
+  } else {
+    t.pair = major;
+    t.kv = q % p.kv_dim;
+    t.layer = p.layer_start + q / p.kv_dim;
+  }
+  return t;
+}
+
+__device__ __forceinline__ TileAddr tile_addr(const KvCopyParams& p, const TilePos& t, int64_t gblk, int64_t cblk,
+                                              int tile_bytes) {
   TileAddr a;
-  const int64_t off = (int64_t)s * tile_bytes;
+  const int64_t off = (int64_t)t.s * tile_bytes;
   const int64_t left = p.chunk_bytes - off;
   a.bytes = (uint32_t)(left < tile_bytes ? left : tile_bytes);
-  a.gpu = p.gpu_ptrs[layer * p.idx_layer_mul + kv * p.idx_kv_mul] + layer * p.g_layer_stride +
-          kv * p.g_kv_stride + gblk * p.g_block_stride + p.g_off + off;
-  a.cpu = p.cpu_base + layer * p.c_layer_stride + kv * p.c_kv_stride + cblk * p.c_block_stride + p.c_off + off;
+  a.gpu = p.gpu_ptrs[t.layer * p.idx_layer_mul + t.kv * p.idx_kv_mul] + t.layer * p.g_layer_stride +
+          t.kv * p.g_kv_stride + gblk * p.g_block_stride + p.g_off + off;
+  a.cpu = p.cpu_base + t.layer * p.c_layer_stride + t.kv * p.c_kv_stride + cblk * p.c_block_stride + p.c_off + off;
   return a;
 }
 
@@ -82,14 +99,34 @@ __device__ __forceinline__ bool ids_in_range(const KvCopyParams& p, int64_t g, i
   return ok;
 }
 
+// Per-layer publication for layer-major launches: this CTA has finished (and
+// drained) everything it owns in layers [from, to); the last CTA to say so for
+// a layer resets that layer's counter and publishes the flags.
+__device__ __forceinline__ void signal_layers(const KvCopyParams& p, int from, int to) {
+  if (p.done_counter == nullptr || from >= to) return;
+  ptx::fence_proxy_async_all();
+  __threadfence();
+  for (int l = from; l < to; ++l) {
+    const unsigned prev = atomicAdd(p.done_counter + l, 1u);
+    if (prev == gridDim.x - 1) {
+      reinterpret_cast<volatile uint32_t*>(p.done_counter)[l] = 0;
+      __threadfence();
+      if (p.dev_flags) ptx::st_release_gpu(p.dev_flags + p.layer_start + l, p.epoch);
+      if (p.host_flags) ptx::st_release_sys(p.host_flags + p.layer_start + l, p.epoch);
+    }
+  }
+}
+
 template <int STAGES, int LOOKAHEAD>
 __global__ void __launch_bounds__(32, 1)
 kv_copy_bulk_kernel(const __grid_constant__ KvCopyParams p, int tile_bytes, int tiles_per_chunk) {
   static_assert(LOOKAHEAD >= 1 && LOOKAHEAD < STAGES, "lookahead must leave one stage for stores");
+  static_assert(STAGES <= 32, "stage phases are kept in one 32-bit mask");
   extern __shared__ __align__(128) uint8_t ring[];
   __shared__ __align__(8) uint64_t full[STAGES];
   __shared__ uint64_t s_dst[STAGES];
   __shared__ uint32_t s_bytes[STAGES];
+  __shared__ int32_t s_layer[STAGES];   // layer-major launches: layer (relative) of the tile in the stage
 
   const int lane = threadIdx.x;
   if (lane == 0) {
@@ -99,18 +136,23 @@ kv_copy_bulk_kernel(const __grid_constant__ KvCopyParams p, int tile_bytes, int 
   }
   __syncwarp();
 
-  const int64_t tiles_per_pair = (int64_t)p.num_layers * p.kv_dim * tiles_per_chunk;
-  const int64_t total = tiles_per_pair * p.num_pairs;
+  // span = tiles per major unit (a pair, or a layer when layer-major); all counts fit 32 bits
+  const int32_t n_major = p.layer_major ? p.num_layers : p.num_pairs;
+  const int32_t span = (p.layer_major ? p.num_pairs : p.num_layers) * p.kv_dim * tiles_per_chunk;
+  const int64_t total = (int64_t)span * n_major;
   const int64_t first = blockIdx.x, step = gridDim.x;
   const int64_t n_mine = first < total ? (total - first + step - 1) / step : 0;
+  // the walk (major, r) advances by `step` tiles per iteration without divisions
+  const int32_t step_q = (int32_t)(step / span), step_r = (int32_t)(step % span);
+  int32_t major = (int32_t)(first / span), r = (int32_t)(first % span);
 
   // Block ids are fetched 32 pairs at a time, one pair per lane, and the next
   // window is requested as soon as the current one becomes active, so the
   // round trip to (possibly host-resident) id arrays is off the issue path.
-  int64_t cur_w = -1;
+  int32_t cur_w = -1;
   int64_t cur_g = 0, cur_c = 0, nxt_g = 0, nxt_c = 0;
-  auto load_window = [&](int64_t w, int64_t& g, int64_t& c) {
-    const int64_t i = (w << 5) + lane;
+  auto load_window = [&](int32_t w, int64_t& g, int64_t& c) {
+    const int64_t i = ((int64_t)w << 5) + lane;
     if (i < p.num_pairs) {
       g = __ldg(p.gpu_blocks + i);
       c = __ldg(p.cpu_blocks + i);
@@ -118,14 +160,22 @@ kv_copy_bulk_kernel(const __grid_constant__ KvCopyParams p, int tile_bytes, int 
   };
 
   int err = 0;
-  int dead = 0;         // set after an expired wait: stop issuing, drain, leave
-  uint32_t phases = 0;  // lane 0: parity of the next completion of each stage's barrier
+  int dead = 0;          // set after an expired wait: stop issuing, drain, leave
+  uint32_t phases = 0;   // lane 0: parity of the next completion of each stage's barrier
+  int32_t signalled = 0; // lane 0, layer-major: layers [0, signalled) already reported by this CTA
 
   for (int64_t it = 0; it < n_mine + LOOKAHEAD && !dead; ++it) {
     const int64_t j = it - LOOKAHEAD;
     if (j >= 0 && lane == 0) {
       const int st = (int)(j % STAGES);
       const uint32_t bytes = s_bytes[st];
+      if (p.layer_major && p.done_counter && s_layer[st] > signalled) {
+        // first store of a later layer: everything this CTA owned in the earlier layers is committed;
+        // drain those stores (the loads in flight are unaffected) and report the layers
+        ptx::bulk_wait<0>();
+        signal_layers(p, signalled, s_layer[st]);
+        signalled = s_layer[st];
+      }
       if (bytes) {
         if (ptx::mbar_wait_bounded(&full[st], (phases >> st) & 1u, kWaitBudgetNs)) {
           phases ^= 1u << st;
@@ -140,26 +190,25 @@ kv_copy_bulk_kernel(const __grid_constant__ KvCopyParams p, int tile_bytes, int 
     if (dead) break;
 
     if (it < n_mine) {
-      const int64_t t = first + it * step;
-      const int64_t pair = t / tiles_per_pair;
-      const int64_t r = t - pair * tiles_per_pair;
-      const int64_t w = pair >> 5;
+      const TilePos t = decode_tile(p, major, r, tiles_per_chunk);
+      const int32_t w = t.pair >> 5;
       if (w != cur_w) {
         if (w == cur_w + 1 && cur_w >= 0) { cur_g = nxt_g; cur_c = nxt_c; }
         else load_window(w, cur_g, cur_c);
         cur_w = w;
         load_window(w + 1, nxt_g, nxt_c);
       }
-      const int64_t gblk = __shfl_sync(0xffffffffu, cur_g, (int)(pair & 31));
-      const int64_t cblk = __shfl_sync(0xffffffffu, cur_c, (int)(pair & 31));
+      const int64_t gblk = __shfl_sync(0xffffffffu, cur_g, t.pair & 31);
+      const int64_t cblk = __shfl_sync(0xffffffffu, cur_c, t.pair & 31);
       if (lane == 0) {
         const int st = (int)(it % STAGES);
         // the stage was last used by tile it-STAGES; all but the newest
         // STAGES-LOOKAHEAD store groups must have finished reading smem
         if (it >= STAGES) ptx::bulk_wait_read<STAGES - LOOKAHEAD>();
         TileAddr a{0, 0, 0};
-        if (ids_in_range(p, gblk, cblk, err)) a = tile_addr(p, r, gblk, cblk, tile_bytes, tiles_per_chunk);
+        if (ids_in_range(p, gblk, cblk, err)) a = tile_addr(p, t, gblk, cblk, tile_bytes);
         s_bytes[st] = a.bytes;
+        s_layer[st] = major;
         if (a.bytes) {
           s_dst[st] = p.h2d ? a.gpu : a.cpu;
           ptx::mbar_expect_tx(&full[st], a.bytes);
@@ -167,12 +216,16 @@ kv_copy_bulk_kernel(const __grid_constant__ KvCopyParams p, int tile_bytes, int 
                         a.bytes, &full[st]);
         }
       }
+      major += step_q;
+      r += step_r;
+      if (r >= span) { r -= span; ++major; }
     }
   }
   if (lane == 0) {
     ptx::bulk_wait<0>();
     if (err && p.status) report_status(p.status, err);
-    signal_done(p);
+    if (p.layer_major) signal_layers(p, signalled, p.num_layers);
+    else signal_done(p);
   }
 }
 
@@ -204,16 +257,16 @@ kv_copy_simt_kernel(const __grid_constant__ KvCopyParams p, int tile_bytes, int 
   const int warps_per_cta = blockDim.x >> 5;
   const int64_t warp0 = (int64_t)blockIdx.x * warps_per_cta + (threadIdx.x >> 5);
   const int64_t nwarps = (int64_t)gridDim.x * warps_per_cta;
-  const int64_t tiles_per_pair = (int64_t)p.num_layers * p.kv_dim * tiles_per_chunk;
-  const int64_t total = tiles_per_pair * p.num_pairs;
+  const int32_t n_major = p.layer_major ? p.num_layers : p.num_pairs;
+  const int32_t span = (p.layer_major ? p.num_pairs : p.num_layers) * p.kv_dim * tiles_per_chunk;
+  const int64_t total = (int64_t)span * n_major;
   int err = 0;
   for (int64_t t = warp0; t < total; t += nwarps) {
-    const int64_t pair = t / tiles_per_pair;
-    const int64_t r = t - pair * tiles_per_pair;
-    const int64_t gblk = __ldg(p.gpu_blocks + pair);
-    const int64_t cblk = __ldg(p.cpu_blocks + pair);
+    const TilePos pos = decode_tile(p, (int32_t)(t / span), (int32_t)(t % span), tiles_per_chunk);
+    const int64_t gblk = __ldg(p.gpu_blocks + pos.pair);
+    const int64_t cblk = __ldg(p.cpu_blocks + pos.pair);
     if (!ids_in_range(p, gblk, cblk, err)) continue;
-    const TileAddr a = tile_addr(p, r, gblk, cblk, tile_bytes, tiles_per_chunk);
+    const TileAddr a = tile_addr(p, pos, gblk, cblk, tile_bytes);
     const uint8_t* src = reinterpret_cast<const uint8_t*>(p.h2d ? a.cpu : a.gpu);
     uint8_t* dst = reinterpret_cast<uint8_t*>(p.h2d ? a.gpu : a.cpu);
     const int nvec = (int)(a.bytes / sizeof(V));

@@ -57,10 +57,17 @@ struct KvCopyParams {
   // flag words [layer_start, layer_start + num_layers) of `dev_flags` (device
   // memory, for consumer kernels on this GPU) and `host_flags` (mapped host
   // memory, for a polling host thread). All three may be null.
+  //
+  // With `layer_major` set (bulk engine only) the tiles are walked layer by
+  // layer inside ONE launch and the signal is per layer: `done_counter` is then
+  // an array of num_layers words and the flag of layer l is published as soon
+  // as every CTA has drained its share of layers <= l, while later layers are
+  // still in flight.
   uint32_t* done_counter;
   uint32_t* dev_flags;
   uint32_t* host_flags;
   uint32_t epoch;
+  int32_t layer_major;
 };
 
 struct KvCopyLaunch {

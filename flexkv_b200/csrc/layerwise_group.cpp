@@ -1,5 +1,7 @@
 #include "layerwise_group.h"
 
+#include <cuda.h>
+
 #include <sys/eventfd.h>
 #include <unistd.h>
 
@@ -24,10 +26,26 @@ static void check(cudaError_t e, const char* what) {
   }
 }
 
+// cuStreamWaitValue32 through the runtime's driver-entry lookup (no link against libcuda)
+typedef CUresult (*StreamWaitValue32Fn)(CUstream, CUdeviceptr, cuuint32_t, unsigned int);
+static StreamWaitValue32Fn stream_wait_value32() {
+  static StreamWaitValue32Fn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuStreamWaitValue32", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess) {
+      (void)cudaGetLastError();
+      p = nullptr;
+    }
+    return reinterpret_cast<StreamWaitValue32Fn>(p);
+  }();
+  return fn;
+}
+
 LayerwiseGroup::LayerwiseGroup(std::vector<GpuSide> gpus, HostSide host, LayerwiseOptions opt)
     : gpus_(std::move(gpus)), host_(host), opt_(opt) {
   if (gpus_.empty()) throw std::invalid_argument("LayerwiseGroup: no GPUs");
-  if (opt_.num_counters < 1 || opt_.layers_per_batch < 1) throw std::invalid_argument("LayerwiseGroup: bad options");
+  if (opt_.num_counters < 1 || opt_.layers_per_batch < 0) throw std::invalid_argument("LayerwiseGroup: bad options");
   const int L = opt_.group.num_layers, R = (int)gpus_.size(), C = opt_.num_counters;
   epochs_.assign((size_t)C, 0);
   if (opt_.create_eventfds) {
@@ -41,14 +59,15 @@ LayerwiseGroup::LayerwiseGroup(std::vector<GpuSide> gpus, HostSide host, Layerwi
   check(cudaHostAlloc((void**)&id_ring_, 2 * (size_t)opt_.group.max_blocks_per_op * sizeof(int64_t),
                       cudaHostAllocPortable | cudaHostAllocMapped),
         "cudaHostAlloc(id ring)");
-  const int batches = (L + opt_.layers_per_batch - 1) / opt_.layers_per_batch;
+  const int lpb = opt_.layers_per_batch > 0 ? opt_.layers_per_batch : L;
+  const int batches = (L + lpb - 1) / lpb;
   for (int r = 0; r < R; ++r)
     for (int c = 0; c < C; ++c)
       for (int b = 0; b < batches; ++b) {
         auto a = std::make_unique<HostFnArg>();
         a->self = this; a->rank = r; a->counter = c;
-        a->layer_lo = b * opt_.layers_per_batch;
-        a->layer_hi = std::min(L, a->layer_lo + opt_.layers_per_batch);
+        a->layer_lo = b * lpb;
+        a->layer_hi = std::min(L, a->layer_lo + lpb);
         fn_args_.push_back(std::move(a));
       }
   for (int r = 0; r < R; ++r) ranks_.emplace_back(new Rank());
@@ -104,7 +123,15 @@ uint64_t LayerwiseGroup::host_flags_ptr(int rank, int counter) const {
 
 cudaError_t LayerwiseGroup::stream_wait_layer(int rank, int counter, int layer, cudaStream_t stream) {
   Rank& rk = *ranks_.at((size_t)rank);
-  return cudaStreamWaitEvent(stream, rk.layer_ev[(size_t)counter * opt_.group.num_layers + layer], 0);
+  if (opt_.layers_per_batch > 0)
+    return cudaStreamWaitEvent(stream, rk.layer_ev[(size_t)counter * opt_.group.num_layers + layer], 0);
+  // fused launch: no event sits between layers, so the stream waits on the device flag itself
+  StreamWaitValue32Fn fn = stream_wait_value32();
+  if (fn == nullptr) return cudaErrorNotSupported;
+  uint32_t* flag = rk.dev_flags + (size_t)counter * opt_.group.num_layers + layer;
+  const CUresult r = fn((CUstream)stream, (CUdeviceptr)(uintptr_t)flag, epochs_[(size_t)counter],
+                        CU_STREAM_WAIT_VALUE_GEQ);
+  return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorUnknown;
 }
 
 void LayerwiseGroup::notify(int rank, int counter, int layer_lo, int layer_hi) {
@@ -129,10 +156,11 @@ void LayerwiseGroup::rank_main(int r) {
     int lo = 0, hi = 0;
     check(cudaDeviceGetStreamPriorityRange(&lo, &hi), "cudaDeviceGetStreamPriorityRange");
     check(cudaStreamCreateWithPriority(&rk.stream, cudaStreamNonBlocking, hi), "cudaStreamCreateWithPriority");
+    check(cudaStreamCreateWithFlags(&rk.notify_stream, cudaStreamNonBlocking), "cudaStreamCreate(notify)");
     check(cudaMalloc((void**)&rk.dev_flags, (size_t)C * L * sizeof(uint32_t)), "cudaMalloc(flags)");
     check(cudaMemset(rk.dev_flags, 0, (size_t)C * L * sizeof(uint32_t)), "cudaMemset(flags)");
-    check(cudaMalloc((void**)&rk.done_counter, sizeof(uint32_t)), "cudaMalloc(counter)");
-    check(cudaMemset(rk.done_counter, 0, sizeof(uint32_t)), "cudaMemset(counter)");
+    check(cudaMalloc((void**)&rk.done_counter, (size_t)L * sizeof(uint32_t)), "cudaMalloc(counter)");
+    check(cudaMemset(rk.done_counter, 0, (size_t)L * sizeof(uint32_t)), "cudaMemset(counter)");
     check(cudaHostAlloc((void**)&rk.host_flags, (size_t)C * L * sizeof(uint32_t),
                         cudaHostAllocPortable | cudaHostAllocMapped), "cudaHostAlloc(flags)");
     std::memset(rk.host_flags, 0, (size_t)C * L * sizeof(uint32_t));
@@ -172,12 +200,15 @@ void LayerwiseGroup::rank_main(int r) {
   if (rk.host_flags) cudaFreeHost(rk.host_flags);
   if (rk.status) cudaFreeHost(rk.status);
   if (rk.stream) cudaStreamDestroy(rk.stream);
+  if (rk.notify_stream) cudaStreamDestroy(rk.notify_stream);
 }
 
 void LayerwiseGroup::run_job(int r, const Job& j) {
   Rank& rk = *ranks_[(size_t)r];
-  const int L = opt_.group.num_layers, B = opt_.layers_per_batch, R = (int)gpus_.size();
+  const bool fused = opt_.layers_per_batch <= 0;
+  const int L = opt_.group.num_layers, B = fused ? L : opt_.layers_per_batch, R = (int)gpus_.size();
   const int batches = (L + B - 1) / B;
+  const auto t_begin = std::chrono::steady_clock::now();
   rk.res_status = 0;
   rk.res_layer_ms.assign((size_t)L, 0.f);
   cudaEvent_t* ev = rk.layer_ev.data() + (size_t)j.counter * L;
@@ -194,6 +225,7 @@ void LayerwiseGroup::run_job(int r, const Job& j) {
     p.dev_flags = rk.dev_flags + (size_t)j.counter * L;
     p.host_flags = hflags;
     p.epoch = j.epoch;
+    p.layer_major = fused ? 1 : 0;
     if (j.n > 0) {
       err = launch_kv_copy(p, opt_.group.h2d, rk.stream);
     } else {
@@ -203,19 +235,22 @@ void LayerwiseGroup::run_job(int r, const Job& j) {
                             cudaMemcpyHostToDevice, rk.stream);
     }
     for (int l = l0; l < l1 && err == cudaSuccess; ++l) err = cudaEventRecord(ev[l], rk.stream);
-    if (err == cudaSuccess && opt_.notify == NotifyMode::HOSTFUNC) {
+    if (err == cudaSuccess && opt_.notify == NotifyMode::HOSTFUNC && !fused) {
+      // the callback runs on a side stream behind the layer's event, so the copy stream never waits for the host
       HostFnArg* a = fn_args_[((size_t)r * opt_.num_counters + j.counter) * batches + b].get();
-      err = cudaLaunchHostFunc(rk.stream, host_fn, a);
+      err = cudaStreamWaitEvent(rk.notify_stream, ev[l1 - 1], 0);
+      if (err == cudaSuccess) err = cudaLaunchHostFunc(rk.notify_stream, host_fn, a);
     }
   }
-  if (err == cudaSuccess && opt_.notify != NotifyMode::HOSTFUNC) {
-    // retire the batches in order from this thread
+  if (err == cudaSuccess && (opt_.notify != NotifyMode::HOSTFUNC || fused)) {
+    // retire in order from this thread; a fused launch is watched layer by layer through the mapped flags
     const auto t0 = std::chrono::steady_clock::now();
-    for (int b = 0; b < batches; ++b) {
-      const int l0 = b * B, l1 = std::min(L, l0 + B);
+    const int units = fused ? L : batches;
+    for (int b = 0; b < units; ++b) {
+      const int l0 = fused ? b : b * B, l1 = fused ? b + 1 : std::min(L, l0 + B);
       for (;;) {
         bool ready;
-        if (opt_.notify == NotifyMode::POLLING) {
+        if (opt_.notify == NotifyMode::POLLING && !fused) {
           cudaError_t q = cudaEventQuery(ev[l1 - 1]);
           if (q != cudaSuccess && q != cudaErrorNotReady) { err = q; break; }
           ready = q == cudaSuccess;
@@ -227,9 +262,13 @@ void LayerwiseGroup::run_job(int r, const Job& j) {
       }
       if (err != cudaSuccess) break;
       notify(r, j.counter, l0, l1);
+      if (fused)
+        rk.res_layer_ms[(size_t)l0] =
+            std::chrono::duration<float, std::milli>(std::chrono::steady_clock::now() - t_begin).count();
     }
   }
   if (err == cudaSuccess) err = cudaStreamSynchronize(rk.stream);
+  if (err == cudaSuccess) err = cudaStreamSynchronize(rk.notify_stream);
   if (err != cudaSuccess) {
     (void)cudaGetLastError();
     rk.res_status = -(int)err;
@@ -237,8 +276,12 @@ void LayerwiseGroup::run_job(int r, const Job& j) {
     return;
   }
   rk.res_status = collect_status(rk.status);
-  for (int l = 0; l < L; ++l) cudaEventElapsedTime(&rk.res_layer_ms[(size_t)l], rk.ev_begin, ev[l]);
-  rk.res_ms = rk.res_layer_ms[(size_t)L - 1];
+  if (!fused) {
+    for (int l = 0; l < L; ++l) cudaEventElapsedTime(&rk.res_layer_ms[(size_t)l], rk.ev_begin, ev[l]);
+    rk.res_ms = rk.res_layer_ms[(size_t)L - 1];
+  } else {
+    cudaEventElapsedTime(&rk.res_ms, rk.ev_begin, ev[L - 1]);   // whole launch, CUDA events
+  }
 }
 
 LayerwiseResult LayerwiseGroup::restore(const int64_t* gpu_blocks, const int64_t* cpu_blocks, int64_t n,

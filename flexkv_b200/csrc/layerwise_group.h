@@ -40,7 +40,7 @@ struct LayerwiseOptions {
   GroupOptions group;
   NotifyMode notify = NotifyMode::HOSTFUNC;
   int num_counters = 3;       // independent flag / eventfd sets (restores in flight)
-  int layers_per_batch = 1;
+  int layers_per_batch = 1;   // 0 = ONE launch for all layers, flags published per layer from inside the kernel
   bool create_eventfds = true;
 };
 
@@ -92,9 +92,10 @@ class LayerwiseGroup {
     bool ready = false;
     std::string init_error;
     cudaStream_t stream = nullptr;
+    cudaStream_t notify_stream = nullptr;   // carries host callbacks so the copy stream never blocks on them
     uint32_t* dev_flags = nullptr;      // [counters][layers]
     uint32_t* host_flags = nullptr;     // mapped, [counters][layers]
-    uint32_t* done_counter = nullptr;   // device scratch word
+    uint32_t* done_counter = nullptr;   // device scratch, one word per layer, zero between launches
     int32_t* status = nullptr;          // mapped, kStatusWords
     std::vector<cudaEvent_t> layer_ev;  // [counters][layers]
     cudaEvent_t ev_begin = nullptr;

@@ -43,7 +43,8 @@ def _drain(fd):
             return n
 
 
-@pytest.mark.parametrize("notify,lpb", [("hostfunc", 1), ("polling", 1), ("flag", 1), ("hostfunc", 3), ("flag", 4)])
+@pytest.mark.parametrize("notify,lpb", [("hostfunc", 1), ("polling", 1), ("flag", 1), ("hostfunc", 3), ("flag", 4),
+                                        ("flag", 0), ("hostfunc", 0)])   # 0 = one launch, per-layer flags from the kernel
 def test_restore_signals_each_layer_once(notify, lpb):
     shape = KVShape("lw", 6, 2, 64, tokens_per_block=16)
     kv, reg, pool, grp, xfer = _setup(shape, notify=notify, layers_per_batch=lpb)
@@ -86,9 +87,10 @@ def test_empty_restore_fires_every_layer_immediately():
     assert [_drain(grp.eventfd_of(1, 0, l)) for l in range(4)] == [1, 1, 1, 1]
 
 
-def test_model_stream_can_wait_per_layer_and_device_flags_release_consumers():
+@pytest.mark.parametrize("lpb", [1, 0])
+def test_model_stream_can_wait_per_layer_and_device_flags_release_consumers(lpb):
     shape = KVShape("lw", 5, 2, 128, tokens_per_block=16)
-    kv, reg, pool, grp, xfer = _setup(shape, notify="flag")
+    kv, reg, pool, grp, xfer = _setup(shape, notify="flag", layers_per_batch=lpb)
     n = 64
     ids = np.arange(n, dtype=np.int64)
     assert xfer.transfer(ids, ids, False, 0, shape.num_layers).status == 0
