@@ -185,6 +185,7 @@ class TransferPlan:
     op_callback_dict: Dict[int, Callable] = field(default_factory=dict)
     num_gpu_blocks_to_transfer: int = 0
     skipped_gpu_blocks: int = 0
+    peer_leases: Optional[Tuple[np.ndarray, np.ndarray]] = None   # (ranks, gpu blocks) pinned in the peer directory
 
 
 def _block_range(token_mask: np.ndarray, tokens_per_block: int) -> Tuple[int, int]:
@@ -222,7 +223,10 @@ class GlobalCacheEngine:
             raise ValueError("at least one cache tier must be enabled")
         if self.cpu_cache_engine is None:
             raise ValueError("the host tier is the staging area of every other tier and must be enabled")
-        self.peer_directory = None          # set by parallel.peer_directory when GPU prefix sharing is on
+        self.peer_directory = None
+        if cache_config.enable_p2p_gpu:
+            from ..parallel.peer_directory import GpuPeerDirectory
+            self.peer_directory = GpuPeerDirectory()
         self._metrics = None
         self._evict_log = EvictionLogAggregator()
         for eng in self.cache_engines.values():
@@ -354,13 +358,21 @@ class GlobalCacheEngine:
             self._metrics.record_match("CPU", cpu_hit, bend - cpu_hit)
             if ssd is not None:
                 self._metrics.record_match("SSD", ssd_hit, bend - ssd_hit)
-        end = max(cpu_hit, ssd_hit)
-        f1 = max(0, cpu_hit - bstart)                     # blocks [bstart, cpu_hit) from the host pool
-        f2_lo = max(bstart, cpu_hit)
-        f2 = max(0, end - f2_lo)                          # blocks [f2_lo, end) from SSD
+        # Blocks that another rank holds in HBM come over NVLink instead of PCIe:
+        # fragment 0 = [bstart, p_end) from peers, then host and SSD cover the rest.
+        f0, peer_ranks, peer_blocks = 0, None, None
+        if self.peer_directory is not None and not prefetch:
+            f0, peer_ranks, peer_blocks = self.peer_directory.match_prefix(seq.block_hashes[:bend], dp_client_id,
+                                                                           start=bstart, lease=True)
+        p_end = bstart + f0
+        end = max(cpu_hit, ssd_hit, p_end)
+        lo1 = max(bstart, p_end)
+        f1 = max(0, cpu_hit - lo1)                        # blocks [lo1, cpu_hit) from the host pool
+        f2_lo = max(lo1, cpu_hit)
+        f2 = max(0, max(cpu_hit, ssd_hit) - f2_lo)        # blocks [f2_lo, ...) from SSD
         if prefetch:
             f1 = 0
-        if f1 + f2 == 0:
+        if f0 + f1 + f2 == 0:
             return None
         graph = TransferOpGraph()
         plan = TransferPlan(graph)
@@ -374,16 +386,24 @@ class GlobalCacheEngine:
                 cpu.recycle(staging)
                 if self._metrics is not None:
                     self._metrics.record_allocation_failure("CPU")
-                if f1 == 0:
+                if f0 + f1 == 0:
                     return None
                 f2, staging = 0, _EMPTY
         ops_done: List[int] = []
         disk_op = None
+        if f0 > 0:
+            peer_op = TransferOp(graph.graph_id, TransferType.PEERD2D, peer_blocks,
+                                 gpu_blocks[:f0] if gpu_blocks is not None else _EMPTY, dp_client_id=dp_client_id,
+                                 gpu_side=None if gpu_blocks is not None else "dst", gpu_bind="head",
+                                 remote_node_ids=peer_ranks)
+            graph.add_transfer_op(peer_op)
+            ops_done.append(peer_op.op_id)
+            plan.peer_leases = (peer_ranks, peer_blocks)
         if f2 > 0:
             ssd_src = ssd_m.physical_blocks[f2_lo:f2_lo + f2]
             if use_gds:
                 disk_op = TransferOp(graph.graph_id, TransferType.DISK2D, ssd_src,
-                                     gpu_blocks[f1:f1 + f2] if gpu_blocks is not None else _EMPTY,
+                                     gpu_blocks[f0 + f1:f0 + f1 + f2] if gpu_blocks is not None else _EMPTY,
                                      dp_client_id=dp_client_id,
                                      gpu_side=None if gpu_blocks is not None else "dst", gpu_bind="tail")
             else:
@@ -412,12 +432,13 @@ class GlobalCacheEngine:
             plan.finished_ops_ids = [disk_op.op_id]
             plan.num_gpu_blocks_to_transfer = f2
             return plan
-        h2d_src = np.concatenate([cpu_phys[bstart:bstart + f1], staging]) if not use_gds else cpu_phys[bstart:bstart + f1]
+        h2d_src = np.concatenate([cpu_phys[lo1:lo1 + f1], staging]) if not use_gds else cpu_phys[lo1:lo1 + f1]
         n_h2d = int(h2d_src.size)
         if n_h2d > 0:
             h2d = TransferOp(graph.graph_id, TransferType.H2D, h2d_src,
-                             gpu_blocks[:n_h2d] if gpu_blocks is not None else _EMPTY, dp_client_id=dp_client_id,
-                             gpu_side=None if gpu_blocks is not None else "dst", gpu_bind="head")
+                             gpu_blocks[f0:f0 + n_h2d] if gpu_blocks is not None else _EMPTY,
+                             dp_client_id=dp_client_id, gpu_side=None if gpu_blocks is not None else "dst",
+                             gpu_bind="head", gpu_offset=f0)
             graph.add_transfer_op(h2d)
             if disk_op is not None and not use_gds:
                 graph.add_dependency(h2d.op_id, disk_op.op_id)
@@ -427,7 +448,7 @@ class GlobalCacheEngine:
         if disk_op is not None and use_gds:
             ops_done.append(disk_op.op_id)
         plan.finished_ops_ids = ops_done
-        plan.num_gpu_blocks_to_transfer = f1 + f2
+        plan.num_gpu_blocks_to_transfer = f0 + f1 + f2
         return plan
 
     # ---- PUT ------------------------------------------------------------------------
@@ -510,6 +531,7 @@ class GlobalCacheEngine:
                     self.cache_engines[dev].unlock(node)
             for dev, ids in plan.buffer_to_free.items():
                 self.cache_engines[dev].recycle(ids)
+            self._release_peer(plan)
             # a node whose op callback never ran (op skipped) stays unready; drop it
             for dev, lst in plan.inserted.items():
                 for node in lst:
@@ -528,7 +550,28 @@ class GlobalCacheEngine:
                     self.cache_engines[dev].rollback_unready_insert(node)
             for dev, ids in plan.buffer_to_free.items():
                 self.cache_engines[dev].recycle(ids)
+            self._release_peer(plan)
             self._update_mempool_metrics()
+
+    def _release_peer(self, plan: TransferPlan) -> None:
+        if plan.peer_leases is not None and self.peer_directory is not None:
+            self.peer_directory.release(*plan.peer_leases)
+            plan.peer_leases = None
+
+    def publish_gpu_blocks(self, rank: int, token_ids: np.ndarray, gpu_block_ids: np.ndarray,
+                           namespace: Optional[List[str]] = None) -> int:
+        """Announces that `rank`'s GPU blocks hold the leading blocks of this sequence."""
+        if self.peer_directory is None:
+            return 0
+        seq = SequenceMeta(np.ascontiguousarray(token_ids, dtype=np.int64), self.tokens_per_block, namespace)
+        n = min(seq.num_blocks, len(gpu_block_ids))
+        self.peer_directory.publish(rank, seq.block_hashes[:n], np.asarray(gpu_block_ids[:n], dtype=np.int64))
+        return n
+
+    def withdraw_gpu_blocks(self, rank: int, gpu_block_ids: np.ndarray) -> List[int]:
+        if self.peer_directory is None:
+            return []
+        return self.peer_directory.withdraw_blocks(rank, np.asarray(gpu_block_ids, dtype=np.int64))
 
     def run_op_callback(self, cb: Callable) -> None:
         with self._cache_tree_lock:

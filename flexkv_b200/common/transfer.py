@@ -81,6 +81,7 @@ class TransferOp:
     # tail) of the block ids the engine passes at launch
     gpu_side: Optional[str] = None
     gpu_bind: str = "head"
+    gpu_offset: int = 0           # head binding starts this many blocks into the launch-time list
     is_swa: bool = False
     remote_node_ids: Optional[np.ndarray] = None      # owner node / rank per block (peer ops)
     block_hashes: Optional[np.ndarray] = None         # key-addressed remote stores
@@ -196,9 +197,11 @@ class TransferOpGraph:
                 n = int(op.src_block_ids_h2d.size)
             else:
                 n = int(op.dst_block_ids.size if op.gpu_side == "src" else op.src_block_ids.size)
-            if n > gpu_block_ids.size:
-                raise ValueError(f"slot mapping covers {gpu_block_ids.size} blocks, op needs {n}")
-            ids = gpu_block_ids[:n] if op.gpu_bind == "head" else gpu_block_ids[gpu_block_ids.size - n:]
+            if n + (op.gpu_offset if op.gpu_bind == "head" else 0) > gpu_block_ids.size:
+                raise ValueError(f"slot mapping covers {gpu_block_ids.size} blocks, op needs "
+                                 f"{n} at offset {op.gpu_offset}")
+            ids = gpu_block_ids[op.gpu_offset:op.gpu_offset + n] if op.gpu_bind == "head" \
+                else gpu_block_ids[gpu_block_ids.size - n:]
             if op.gpu_side == "src":
                 op.src_block_ids = ids
             else:

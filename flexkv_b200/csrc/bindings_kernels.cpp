@@ -7,6 +7,7 @@
 #include <cuda_runtime.h>
 
 #include "kernels/kv_copy.h"
+#include "kernels/kv_fanout.h"
 
 namespace py = pybind11;
 using namespace fkv;
@@ -31,7 +32,15 @@ KvCopyParams kv_params_from_dict(const py::dict& d) {
   p.g_kv_stride = geti("g_kv_stride", 0);
   p.g_block_stride = geti("g_block_stride", 0);
   p.g_off = geti("g_off", 0);
-  p.cpu_base = d["cpu_base"].cast<uint64_t>();
+  p.cpu_base = d.contains("cpu_base") ? d["cpu_base"].cast<uint64_t>() : 0;
+  if (d.contains("c_ptrs")) {
+    auto cp = d["c_ptrs"].cast<std::vector<uint64_t>>();
+    if ((int)cp.size() > kMaxGpuPtrs) throw std::invalid_argument("too many peer tensors");
+    for (size_t i = 0; i < cp.size(); ++i) p.c_ptrs[i] = cp[i];
+    p.c_use_table = 1;
+    p.c_idx_layer_mul = (int32_t)geti("c_idx_layer_mul", 1);
+    p.c_idx_kv_mul = (int32_t)geti("c_idx_kv_mul", 0);
+  }
   p.c_layer_stride = geti("c_layer_stride", 0);
   p.c_kv_stride = geti("c_kv_stride", 0);
   p.c_block_stride = geti("c_block_stride", 0);
@@ -67,6 +76,17 @@ void init_kernel_bindings(py::module_& m) {
     KvCopyParams p = kv_params_from_dict(params);
     throw_on(launch_kv_copy_refshape(p, num_ctas, (cudaStream_t)(uintptr_t)stream), "kv_copy_refshape launch");
   }, py::arg("params"), py::arg("num_ctas") = 4, py::arg("stream") = 0);
+
+  m.def("kv_fanout", [](py::dict params, int64_t mc_delta, uint64_t mc_flag_ptr, int num_ctas, int tile_bytes,
+                        uint64_t stream) {
+    KvFanoutParams fp;
+    fp.base = kv_params_from_dict(params);
+    fp.base.h2d = 1;
+    fp.mc_delta = mc_delta;
+    fp.mc_flag = (uint32_t*)(uintptr_t)mc_flag_ptr;
+    throw_on(launch_kv_fanout(fp, num_ctas, tile_bytes, (cudaStream_t)(uintptr_t)stream), "kv_fanout launch");
+  }, py::arg("params"), py::arg("mc_delta"), py::arg("mc_flag_ptr") = (uint64_t)0, py::arg("num_ctas") = 8,
+     py::arg("tile_bytes") = 16384, py::arg("stream") = (uint64_t)0);
 
   m.def("host_kv_copy", [](py::dict params, int threads) {
     KvCopyParams p = kv_params_from_dict(params);

@@ -6,6 +6,7 @@
 #include "bindings_common.h"
 #include "kernels/layer_sync.h"
 #include "layerwise_group.h"
+#include "peer_copier.h"
 
 namespace py = pybind11;
 using namespace fkv;
@@ -68,6 +69,26 @@ void init_layerwise_bindings(py::module_& m) {
       .def_property_readonly("num_ranks", &LayerwiseGroup::num_ranks)
       .def_property_readonly("num_layers", &LayerwiseGroup::num_layers)
       .def_property_readonly("num_counters", &LayerwiseGroup::num_counters);
+
+  py::class_<PeerCopier>(m, "PeerCopier")
+      .def(py::init([](py::list ranks, int num_layers, int kv_dim, int64_t chunk_bytes, int ctas, int tile, int engine,
+                       int64_t max_blocks) {
+             return new PeerCopier(parse_gpu_sides(ranks), num_layers, kv_dim, chunk_bytes,
+                                   KvCopyLaunch{ctas, tile, engine}, max_blocks);
+           }), py::arg("ranks"), py::arg("num_layers"), py::arg("kv_dim"), py::arg("chunk_bytes"),
+           py::arg("num_ctas") = 64, py::arg("tile_bytes") = 16384, py::arg("engine") = 0,
+           py::arg("max_blocks_per_op") = (int64_t)65536)
+      .def("pull", [](PeerCopier& c, int dst_rank, int src_rank, I64Array dst_blocks, I64Array src_blocks,
+                      int layer_start, int num_layers) {
+             if (dst_blocks.size() != src_blocks.size()) throw std::invalid_argument("block id arrays differ in size");
+             const int64_t* d = dst_blocks.data();
+             const int64_t* s = src_blocks.data();
+             const int64_t n = (int64_t)dst_blocks.size();
+             py::gil_scoped_release rel;
+             return c.pull(dst_rank, src_rank, d, s, n, layer_start, num_layers);
+           })
+      .def("can_access", &PeerCopier::can_access)
+      .def_property_readonly("num_ranks", &PeerCopier::num_ranks);
 
   m.def("layer_stub", [](uint64_t flag_ptr, uint32_t epoch, uint64_t busy_ns, uint64_t budget_ns, uint64_t status_ptr,
                          uint64_t t_start_ptr, int num_ctas, uint64_t stream) {

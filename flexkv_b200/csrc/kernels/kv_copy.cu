@@ -88,7 +88,8 @@ __device__ __forceinline__ TileAddr tile_addr(const KvCopyParams& p, const TileP
   a.bytes = (uint32_t)(left < tile_bytes ? left : tile_bytes);
   a.gpu = p.gpu_ptrs[t.layer * p.idx_layer_mul + t.kv * p.idx_kv_mul] + t.layer * p.g_layer_stride +
           t.kv * p.g_kv_stride + gblk * p.g_block_stride + p.g_off + off;
-  a.cpu = p.cpu_base + t.layer * p.c_layer_stride + t.kv * p.c_kv_stride + cblk * p.c_block_stride + p.c_off + off;
+  const uint64_t cbase = p.c_use_table ? p.c_ptrs[t.layer * p.c_idx_layer_mul + t.kv * p.c_idx_kv_mul] : p.cpu_base;
+  a.cpu = cbase + t.layer * p.c_layer_stride + t.kv * p.c_kv_stride + cblk * p.c_block_stride + p.c_off + off;
   return a;
 }
 
@@ -337,6 +338,12 @@ inline bool all_multiple(const KvCopyParams& p, int64_t m) {
                        ? 1
                        : (p.layer_start + p.num_layers - 1) * p.idx_layer_mul + (p.kv_dim - 1) * p.idx_kv_mul + 1;
   for (int i = 0; i < nptr && i < kMaxGpuPtrs; ++i) r = r && (p.gpu_ptrs[i] % (uint64_t)m) == 0;
+  if (p.c_use_table) {
+    const int nc = p.c_idx_layer_mul == 0 && p.c_idx_kv_mul == 0
+                       ? 1
+                       : (p.layer_start + p.num_layers - 1) * p.c_idx_layer_mul + (p.kv_dim - 1) * p.c_idx_kv_mul + 1;
+    for (int i = 0; i < nc && i < kMaxGpuPtrs; ++i) r = r && (p.c_ptrs[i] % (uint64_t)m) == 0;
+  }
   return r;
 }
 

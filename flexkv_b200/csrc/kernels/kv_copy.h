@@ -8,6 +8,7 @@
 //   gpu = gpu_ptrs[layer*idx_layer_mul + kv*idx_kv_mul]
 //         + layer*g_layer_stride + kv*g_kv_stride + gpu_block*g_block_stride + g_off
 //   cpu = cpu_base + layer*c_layer_stride + kv*c_kv_stride + cpu_block*c_block_stride + c_off
+//         (cpu_base is replaced by a second tensor table for GPU<->GPU moves, see c_ptrs)
 //
 // vLLM (one tensor per layer):      idx_layer_mul=1, idx_kv_mul=0, g_layer_stride=0
 // TensorRT-LLM (one tensor):        idx_*=0, all three g_* strides set
@@ -42,6 +43,11 @@ struct KvCopyParams {
   int64_t g_layer_stride, g_kv_stride, g_block_stride, g_off;
   uint64_t cpu_base;
   int64_t c_layer_stride, c_kv_stride, c_block_stride, c_off;
+  // The "cpu" side may itself be a table of tensors (a peer GPU's paged cache
+  // reached over NVLink): when c_use_table is set its base is
+  // c_ptrs[layer*c_idx_layer_mul + kv*c_idx_kv_mul] instead of cpu_base.
+  uint64_t c_ptrs[kMaxGpuPtrs];
+  int32_t c_use_table, c_idx_layer_mul, c_idx_kv_mul, pad0_;
   const int64_t* gpu_blocks;
   const int64_t* cpu_blocks;
   int32_t num_pairs;

@@ -28,7 +28,9 @@ int host_kv_copy(const KvCopyParams& p, int num_threads) {
         uint8_t* ga = reinterpret_cast<uint8_t*>(p.gpu_ptrs[layer * p.idx_layer_mul + kv * p.idx_kv_mul] +
                                                  layer * p.g_layer_stride + kv * p.g_kv_stride +
                                                  g * p.g_block_stride + p.g_off);
-        uint8_t* ca = reinterpret_cast<uint8_t*>(p.cpu_base + layer * p.c_layer_stride + kv * p.c_kv_stride +
+        const uint64_t cbase =
+            p.c_use_table ? p.c_ptrs[layer * p.c_idx_layer_mul + kv * p.c_idx_kv_mul] : p.cpu_base;
+        uint8_t* ca = reinterpret_cast<uint8_t*>(cbase + layer * p.c_layer_stride + kv * p.c_kv_stride +
                                                  c * p.c_block_stride + p.c_off);
         if (p.h2d) std::memcpy(ga, ca, (size_t)p.chunk_bytes);
         else std::memcpy(ca, ga, (size_t)p.chunk_bytes);

@@ -33,7 +33,7 @@ def _np(x, dtype=None):
 class KVManager:
     def __init__(self, model_config: ModelConfig, cache_config: CacheConfig, dp_client_id: int = 0,
                  server_recv_port: Optional[str] = None, gpu_register_port: Optional[str] = None,
-                 require_gpu: Optional[bool] = None) -> None:
+                 require_gpu: Optional[bool] = None, in_process: Optional[bool] = None) -> None:
         env = GLOBAL_CONFIG_FROM_ENV
         self.model_config = model_config
         self.cache_config = cache_config
@@ -42,8 +42,10 @@ class KVManager:
         self.gpu_register_port = gpu_register_port
         safe = {k: ("***" if "password" in k else v) for k, v in vars(cache_config).items() if not k.startswith("_")}
         flexkv_logger.debug("KVManager config: %s | %s", model_config, safe)
+        # `in_process=True` keeps everything in this process even with several DP ranks (one process
+        # that sees every GPU, e.g. tests and single-process benchmarks)
         self.server_client_mode = bool(env.server_client_mode or model_config.dp_size > 1
-                                       or model_config.instance_num > 1)
+                                       or model_config.instance_num > 1) if in_process is None else not in_process
         self.server_handle = None
         self.dp_client = None
         self.kv_task_engine = None
@@ -179,6 +181,24 @@ class KVManager:
         if self.server_client_mode:
             return self.dp_client.try_wait(task_ids)
         return self.kv_task_engine.try_wait(task_ids)
+
+    # ---- cross-rank GPU prefix reuse (NVLink) ------------------------------------------
+    def publish_gpu_blocks(self, token_ids, slot_mapping, namespace: Optional[List[str]] = None,
+                           dp_client_id: Optional[int] = None) -> int:
+        """Tells the other ranks that these GPU blocks of this rank hold the prefix's
+        KV, so their gets can pull it over NVLink. Returns the number of blocks published."""
+        token_ids, slot_mapping = _np(token_ids, np.int64), _np(slot_mapping, np.int64)
+        dp = self.dp_client_id if dp_client_id is None else dp_client_id
+        if self.server_client_mode:
+            return self.dp_client.publish_gpu_blocks(token_ids, slot_mapping, namespace=namespace)
+        return self.kv_task_engine.publish_gpu_blocks(token_ids, slot_mapping, dp, namespace)
+
+    def withdraw_gpu_blocks(self, gpu_block_ids, dp_client_id: Optional[int] = None) -> List[int]:
+        """Call before the engine reuses the blocks; returns blocks a peer is still reading."""
+        dp = self.dp_client_id if dp_client_id is None else dp_client_id
+        if self.server_client_mode:
+            return self.dp_client.withdraw_gpu_blocks(_np(gpu_block_ids, np.int64))
+        return self.kv_task_engine.withdraw_gpu_blocks(_np(gpu_block_ids, np.int64), dp)
 
     def _clear_cpu_cache(self) -> None:
         if self.server_client_mode:

@@ -441,6 +441,15 @@ class KVTaskEngine:
         t = self.tasks.get(task_id)
         return None if t is None else t.failed_gpu_blocks
 
+    # ---- GPU prefix sharing --------------------------------------------------------
+    def publish_gpu_blocks(self, token_ids: np.ndarray, slot_mapping: np.ndarray, dp_id: int = 0,
+                           namespace: Optional[List[str]] = None) -> int:
+        ids = slot_mapping_to_block_ids(np.asarray(slot_mapping, dtype=np.int64), self.cache_config.tokens_per_block)
+        return self.cache_engine.publish_gpu_blocks(dp_id, token_ids, ids, namespace)
+
+    def withdraw_gpu_blocks(self, gpu_block_ids: np.ndarray, dp_id: int = 0) -> List[int]:
+        return self.cache_engine.withdraw_gpu_blocks(dp_id, gpu_block_ids)
+
     # ---- maintenance ----------------------------------------------------------
     def _clear_cpu_cache(self) -> None:
         self.cache_engine.cpu_cache_engine.reset()

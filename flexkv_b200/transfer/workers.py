@@ -213,6 +213,48 @@ class HostEmulatedGpuWorker(TransferWorker):
         return OpOutcome(status == 0, num_bytes=nbytes, error="" if status == 0 else f"copy status 0x{status:x}")
 
 
+# ------------------------------------------------------------------ GPU <-> GPU (NVLink)
+
+class PeerD2DWorker(TransferWorker):
+    """Pulls blocks out of other ranks' paged caches over NVLink peer memory
+    (one launch per owner rank; source and destination layouts are independent)."""
+
+    name = "peer-d2d"
+
+    def __init__(self, storage, model_config: ModelConfig, tp_rank: int = 0) -> None:
+        super().__init__()
+        env = GLOBAL_CONFIG_FROM_ENV
+        keys = sorted(k for k in storage.gpu_regs if tp_rank in storage.gpu_regs[k])
+        self.rank_of = {k.dp_client_id: i for i, k in enumerate(keys)}
+        regs = [storage.gpu_regs[k][tp_rank] for k in keys]
+        r0 = regs[0]
+        for r in regs:
+            if (r.chunk_bytes, r.num_layers, r.kv_dim) != (r0.chunk_bytes, r0.num_layers, r0.kv_dim):
+                raise ValueError("peer ranks must share the KV chunk geometry")
+        self.num_layers = r0.num_layers
+        self.bytes_per_block = r0.num_layers * r0.kv_dim * r0.chunk_bytes
+        self.copier = _native.C.PeerCopier([r.as_native() for r in regs], r0.num_layers, r0.kv_dim, r0.chunk_bytes,
+                                           num_ctas=int(os.environ.get("FLEXKV_PEER_NUM_CTA", 64)),
+                                           tile_bytes=env.transfer_tile_bytes, engine=0,
+                                           max_blocks_per_op=max(4096, max(r.num_blocks for r in regs)))
+
+    def execute(self, op: TransferOp) -> OpOutcome:
+        src, dst, owners = op.src_block_ids, op.dst_block_ids, op.remote_node_ids
+        if dst.size != src.size or owners is None or owners.size != src.size:
+            return OpOutcome(False, error="peer op needs bound destination blocks and one owner per block")
+        me = self.rank_of[op.dp_client_id]
+        status, ms = 0, 0.0
+        nl = self.num_layers if op.num_layers < 0 else op.num_layers
+        for owner in np.unique(owners):
+            sel = owners == owner
+            r = self.copier.pull(me, self.rank_of[int(owner)], np.ascontiguousarray(dst[sel]),
+                                 np.ascontiguousarray(src[sel]), op.layer_start, nl)
+            status |= r.status if r.status >= 0 else (1 << 30)
+            ms += r.gpu_ms
+        return OpOutcome(status == 0, gpu_ms=ms, num_bytes=int(src.size) * self.bytes_per_block,
+                         error="" if status == 0 else f"peer copy status 0x{status:x}")
+
+
 # ------------------------------------------------------------------ host <-> SSD
 
 class SsdWorker(TransferWorker):
@@ -258,6 +300,11 @@ def build_workers(storage, model_config: ModelConfig, cache_config: CacheConfig
             sock = os.environ.get("FLEXKV_LAYERWISE_SOCK", "")
             workers[(key, TransferType.LAYERWISE)] = LayerwiseWorker(
                 storage, model_config, key, sock_path=f"{sock}.{key.dp_client_id}" if sock else None)
+    real = [k for k, regs in storage.gpu_regs.items() if regs[sorted(regs)[0]].device_id >= 0]
+    if cache_config.enable_p2p_gpu and len(real) > 1:
+        peer = PeerD2DWorker(storage, model_config)
+        for k in real:
+            workers[(k, TransferType.PEERD2D)] = peer
     if storage.ssd is not None:
         k0 = WorkerKey(0, 0)
         workers[(k0, TransferType.DISK2H)] = SsdWorker(storage, True)
