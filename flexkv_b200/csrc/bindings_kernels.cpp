@@ -8,6 +8,7 @@
 
 #include "kernels/kv_copy.h"
 #include "kernels/kv_fanout.h"
+#include "kernels/kv_quant.h"
 
 namespace py = pybind11;
 using namespace fkv;
@@ -87,6 +88,12 @@ void init_kernel_bindings(py::module_& m) {
     throw_on(launch_kv_fanout(fp, num_ctas, tile_bytes, (cudaStream_t)(uintptr_t)stream), "kv_fanout launch");
   }, py::arg("params"), py::arg("mc_delta"), py::arg("mc_flag_ptr") = (uint64_t)0, py::arg("num_ctas") = 8,
      py::arg("tile_bytes") = 16384, py::arg("stream") = (uint64_t)0);
+
+  m.def("kv_quant_fp8", [](py::dict params, int num_ctas, uint64_t stream) {
+    KvCopyParams p = kv_params_from_dict(params);
+    throw_on(launch_kv_quant_fp8(p, num_ctas, (cudaStream_t)(uintptr_t)stream), "kv_quant_fp8 launch");
+  }, py::arg("params"), py::arg("num_ctas") = 32, py::arg("stream") = (uint64_t)0);
+  m.def("fp8_packed_chunk_bytes", &fp8_packed_chunk_bytes);
 
   m.def("host_kv_copy", [](py::dict params, int threads) {
     KvCopyParams p = kv_params_from_dict(params);

@@ -213,6 +213,73 @@ class HostEmulatedGpuWorker(TransferWorker):
         return OpOutcome(status == 0, num_bytes=nbytes, error="" if status == 0 else f"copy status 0x{status:x}")
 
 
+class QuantGpuHostWorker(TransferWorker):
+    """H2D / D2H for host pools stored as block-scaled fp8: the copy kernel packs on
+    the way out and unpacks on the way in (one launch per rank and op)."""
+
+    def __init__(self, storage, model_config: ModelConfig, key: WorkerKey, h2d: bool) -> None:
+        super().__init__()
+        import torch
+        self.h2d = h2d
+        self.name = "h2d-fp8" if h2d else "d2h-fp8"
+        self.regs = [storage.gpu_regs[key][r] for r in sorted(storage.gpu_regs[key])]
+        host = storage.host
+        if host.layout.type != KVCacheLayoutType.BLOCKFIRST:
+            raise ValueError("fp8 offload uses the BLOCKFIRST host layout")
+        self.shared = model_config.use_mla or model_config.num_kv_heads == 1
+        n = 1 if self.shared else model_config.effective_tp_size
+        self.host = host
+        self.layer_stride, self.kv_stride, self.tp_stride = host.layer_stride // n, host.kv_stride // n, \
+            host.block_bytes // n
+        self.num_ctas = int(os.environ.get("FLEXKV_QUANT_NUM_CTA", 32))
+        self._torch = torch
+        self.streams = {r.device_id: torch.cuda.Stream(device=r.device_id) for r in self.regs}
+        self.status = {r.device_id: torch.zeros(8, dtype=torch.int32, device=f"cuda:{r.device_id}") for r in self.regs}
+
+    def execute(self, op: TransferOp) -> OpOutcome:
+        torch = self._torch
+        if self.h2d:
+            cpu, gpu = op.src_block_ids, op.dst_block_ids
+        else:
+            gpu, cpu = op.src_block_ids, op.dst_block_ids
+        if gpu.size != cpu.size:
+            return OpOutcome(False, error=f"unbound GPU blocks: {gpu.size} vs {cpu.size}")
+        keep, evs, nbytes = [], [], 0
+        g_ids = torch.from_numpy(np.ascontiguousarray(gpu, dtype=np.int64)).pin_memory()
+        c_ids = torch.from_numpy(np.ascontiguousarray(cpu, dtype=np.int64)).pin_memory()
+        for i, reg in enumerate(self.regs):
+            if self.shared and not self.h2d and i > 0:
+                break
+            nl = reg.num_layers if op.num_layers < 0 else op.num_layers
+            params = dict(gpu_ptrs=[int(p) for p in reg.ptrs], idx_layer_mul=reg.idx_layer_mul,
+                          idx_kv_mul=reg.idx_kv_mul, g_layer_stride=reg.layer_stride, g_kv_stride=reg.kv_stride,
+                          g_block_stride=reg.block_stride, cpu_base=self.host.base, c_layer_stride=self.layer_stride,
+                          c_kv_stride=self.kv_stride, c_block_stride=self.host.block_bytes,
+                          c_off=0 if self.shared else i * self.tp_stride, gpu_blocks_ptr=g_ids.data_ptr(),
+                          cpu_blocks_ptr=c_ids.data_ptr(), num_pairs=int(cpu.size), layer_start=op.layer_start,
+                          num_layers=nl, kv_dim=reg.kv_dim, chunk_bytes=reg.chunk_bytes,
+                          gpu_num_blocks=reg.num_blocks, cpu_num_blocks=self.host.num_blocks,
+                          status_ptr=self.status[reg.device_id].data_ptr(), h2d=int(self.h2d))
+            st = self.streams[reg.device_id]
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            with torch.cuda.device(reg.device_id):
+                e0.record(st)
+                _native.C.kv_quant_fp8(params, self.num_ctas, st.cuda_stream)
+                e1.record(st)
+            evs.append((e0, e1, reg.device_id))
+            nbytes += int(cpu.size) * nl * reg.kv_dim * reg.chunk_bytes
+        status, ms = 0, 0.0
+        for e0, e1, dev in evs:
+            e1.synchronize()
+            ms = max(ms, e0.elapsed_time(e1))
+            words = self.status[dev].tolist()
+            status |= sum(1 << b for b, w in enumerate(words) if w)
+            if status:
+                self.status[dev].zero_()
+        return OpOutcome(status == 0, gpu_ms=ms, num_bytes=nbytes,
+                         error="" if status == 0 else f"quant kernel status 0x{status:x}")
+
+
 # ------------------------------------------------------------------ GPU <-> GPU (NVLink)
 
 class PeerD2DWorker(TransferWorker):
@@ -286,6 +353,10 @@ def build_workers(storage, model_config: ModelConfig, cache_config: CacheConfig
         if reg0.device_id < 0:
             workers[(key, TransferType.H2D)] = HostEmulatedGpuWorker(storage, model_config, key, True)
             workers[(key, TransferType.D2H)] = HostEmulatedGpuWorker(storage, model_config, key, False)
+            continue
+        if storage.host.quant != "none":
+            workers[(key, TransferType.H2D)] = QuantGpuHostWorker(storage, model_config, key, True)
+            workers[(key, TransferType.D2H)] = QuantGpuHostWorker(storage, model_config, key, False)
             continue
         group = build_transfer_group(storage, model_config, key)
         per_rank_block = reg0.num_layers * reg0.kv_dim * reg0.chunk_bytes
