@@ -9,6 +9,7 @@
 #include "kernels/kv_copy.h"
 #include "kernels/kv_fanout.h"
 #include "kernels/kv_quant.h"
+#include "ipc.h"
 
 namespace py = pybind11;
 using namespace fkv;
@@ -94,6 +95,13 @@ void init_kernel_bindings(py::module_& m) {
     throw_on(launch_kv_quant_fp8(p, num_ctas, (cudaStream_t)(uintptr_t)stream), "kv_quant_fp8 launch");
   }, py::arg("params"), py::arg("num_ctas") = 32, py::arg("stream") = (uint64_t)0);
   m.def("fp8_packed_chunk_bytes", &fp8_packed_chunk_bytes);
+
+  m.def("ipc_export", [](uint64_t ptr) {
+    IpcExport e = ipc_export(ptr);
+    return py::make_tuple(py::bytes(e.handle), e.offset, e.alloc_bytes);
+  });
+  m.def("ipc_import", &ipc_import);
+  m.def("ipc_close", &ipc_close);
 
   m.def("host_kv_copy", [](py::dict params, int threads) {
     KvCopyParams p = kv_params_from_dict(params);

@@ -1,0 +1,140 @@
+"""Clients of the KV server: ``KVDPClient`` (one per data-parallel rank, mirrors
+the KVManager API) and ``KVTPClient`` (one per engine worker, registers that
+worker's GPU KV tensors) — flexkv/server/client.py:39-288,290-517."""
+from __future__ import annotations
+
+import pickle
+import threading
+import time
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+import zmq
+
+from ..common.config import ModelConfig
+from ..common.debug import flexkv_logger
+from ..common.memory_handle import TensorSharedHandle
+from ..common.request import KVResponse
+from ..common.storage import KVCacheLayout
+from . import request as R
+from .utils import get_zmq_socket, unique_ipc_endpoint
+
+
+class KVDPClient:
+    def __init__(self, server_recv_port: str, model_config: ModelConfig, dp_client_id: int = 0,
+                 request_timeout: float = 120.0) -> None:
+        self.dp_client_id = dp_client_id
+        self.model_config = model_config
+        self.request_timeout = request_timeout
+        self._ctx = zmq.Context.instance()
+        self._send = get_zmq_socket(self._ctx, zmq.PUSH, server_recv_port, bind=False)
+        self._recv_endpoint = unique_ipc_endpoint(f"flexkv_dp{dp_client_id}")
+        self._recv = get_zmq_socket(self._ctx, zmq.PULL, self._recv_endpoint, bind=True)
+        self._seq = 0
+        self._lock = threading.Lock()
+        self._registered = False
+
+    def _call(self, req: R.Request, timeout: Optional[float] = None) -> R.Response:
+        with self._lock:
+            self._seq += 1
+            req.dp_client_id, req.seq = self.dp_client_id, self._seq
+            self._send.send(pickle.dumps(req, protocol=pickle.HIGHEST_PROTOCOL))
+            deadline = time.monotonic() + (timeout if timeout is not None else self.request_timeout)
+            while True:
+                left = deadline - time.monotonic()
+                if left <= 0 or not self._recv.poll(int(left * 1000)):
+                    raise TimeoutError(f"KV server did not answer {type(req).__name__}")
+                rsp: R.Response = pickle.loads(self._recv.recv())
+                if rsp.seq != self._seq:
+                    continue                      # a stale answer to a request that timed out earlier
+                if rsp.error:
+                    raise RuntimeError(f"KV server: {rsp.error}")
+                return rsp
+
+    def start_server_and_register(self) -> None:
+        if not self._registered:
+            self._call(R.RegisterDPClientRequest(client_recv_port=self._recv_endpoint))
+            self._registered = True
+
+    def is_ready(self) -> bool:
+        self.start_server_and_register()
+        return bool(self._call(R.IsReadyRequest()).ready)
+
+    def put_async(self, token_ids, slot_mapping, token_mask=None, namespace=None) -> int:
+        return self._call(R.PutRequest(token_ids=token_ids, slot_mapping=slot_mapping, token_mask=token_mask,
+                                       namespace=namespace)).task_id
+
+    def put_match(self, token_ids, token_mask=None, namespace=None) -> Tuple[int, np.ndarray]:
+        r = self._call(R.PutRequest(token_ids=token_ids, token_mask=token_mask, namespace=namespace, match_only=True))
+        return r.task_id, r.mask
+
+    def get_async(self, token_ids, slot_mapping, token_mask=None, namespace=None) -> int:
+        return self._call(R.GetRequest(token_ids=token_ids, slot_mapping=slot_mapping, token_mask=token_mask,
+                                       namespace=namespace)).task_id
+
+    def get_match(self, token_ids, token_mask=None, cpu_only=False, namespace=None, swa_aware=False):
+        r = self._call(R.GetRequest(token_ids=token_ids, token_mask=token_mask, namespace=namespace, match_only=True,
+                                    cpu_only=cpu_only, swa_aware=swa_aware))
+        return r.task_id, r.mask
+
+    def prefetch_async(self, token_ids, namespace=None, swa_aware=False) -> int:
+        return self._call(R.PrefetchRequest(token_ids=token_ids, namespace=namespace, swa_aware=swa_aware)).task_id
+
+    def launch_tasks(self, task_ids, slot_mappings, swa_slot_mappings=None, as_batch=False, layerwise_transfer=False,
+                     counter_id=0) -> List[int]:
+        return self._call(R.LaunchRequest(task_ids=list(task_ids), slot_mappings=list(slot_mappings),
+                                          as_batch=as_batch, layerwise_transfer=layerwise_transfer,
+                                          counter_id=counter_id)).task_ids
+
+    def cancel_tasks(self, task_ids) -> None:
+        self._call(R.CancelRequest(task_ids=list(task_ids)))
+
+    def wait(self, task_ids, timeout: float = 20.0, completely: bool = False) -> Dict[int, KVResponse]:
+        return self._call(R.WaitRequest(task_ids=list(task_ids), timeout=timeout, completely=completely),
+                          timeout=timeout + self.request_timeout).status
+
+    def try_wait(self, task_ids) -> Dict[int, KVResponse]:
+        return self._call(R.WaitRequest(task_ids=list(task_ids), try_wait=True)).status
+
+    def reset(self) -> None:
+        self._call(R.ResetRequest())
+
+    def publish_gpu_blocks(self, token_ids, slot_mapping, namespace=None) -> int:
+        return self._call(R.PublishGpuBlocksRequest(token_ids=token_ids, slot_mapping=slot_mapping,
+                                                    namespace=namespace)).value
+
+    def withdraw_gpu_blocks(self, gpu_block_ids) -> List[int]:
+        return self._call(R.WithdrawGpuBlocksRequest(gpu_block_ids=gpu_block_ids)).value
+
+    def shutdown(self) -> None:
+        self._send.close()
+        self._recv.close()
+
+
+class KVTPClient:
+    """Registers one engine worker's GPU KV tensors with the process that runs the
+    data plane (address handles in the same process, CUDA IPC across processes)."""
+
+    def __init__(self, gpu_register_port: str, dp_client_id: int = 0, device_id: int = 0,
+                 intra_client_id: Optional[int] = None, tp_rank: int = 0, pp_rank: int = 0) -> None:
+        self.dp_client_id, self.device_id = dp_client_id, device_id
+        self.tp_rank, self.pp_rank = tp_rank, pp_rank
+        self.intra_client_id = tp_rank if intra_client_id is None else intra_client_id
+        if intra_client_id is not None and tp_rank == 0:
+            self.tp_rank = intra_client_id
+        self._ctx = zmq.Context.instance()
+        self._sock = get_zmq_socket(self._ctx, zmq.PUSH, gpu_register_port, bind=False)
+        self._handles: List[TensorSharedHandle] = []
+
+    def register_to_server(self, kv_caches: Sequence[torch.Tensor], kv_layout: KVCacheLayout,
+                           mode: Optional[str] = None) -> None:
+        self._handles = [TensorSharedHandle.export(t, mode) for t in kv_caches]
+        req = R.RegisterTPClientRequest(self.dp_client_id, self.intra_client_id, self.device_id, self._handles,
+                                        kv_layout, pp_rank=self.pp_rank, tp_rank=self.tp_rank)
+        self._sock.send(pickle.dumps(req, protocol=pickle.HIGHEST_PROTOCOL))
+        flexkv_logger.info("sent GPU registration: dp %d rank %d, %d tensors", self.dp_client_id,
+                           self.intra_client_id, len(kv_caches))
+
+    def shutdown(self) -> None:
+        self._sock.close()

@@ -1,0 +1,62 @@
+"""GPU registration over ZeroMQ: engine workers PUSH their tensor handles, the
+data plane's owner PULLs them and opens the memory
+(flexkv/transfer_manager.py:77-83,317-357; flexkv/server/client.py:366-496)."""
+from __future__ import annotations
+
+import pickle
+import threading
+from typing import Callable, Optional
+
+import zmq
+
+from ..common.debug import flexkv_logger
+from ..storage.gpu_layout import GpuRegistration, describe_gpu_tensors
+from .request import RegisterTPClientRequest
+from .utils import get_zmq_socket
+
+
+def registration_from_request(req: RegisterTPClientRequest) -> GpuRegistration:
+    ptrs = [h.open() for h in req.handles]
+    h0 = req.handles[0]
+    reg = describe_gpu_tensors(ptrs, req.gpu_layout, h0.dtype, req.device_id if h0.device_id >= 0 else -1,
+                               [h.shape for h in req.handles], [h.stride for h in req.handles])
+    reg.dp_client_id, reg.pp_rank, reg.tp_rank = req.dp_client_id, req.pp_rank, req.tp_rank
+    reg.keepalive = list(req.handles)
+    return reg
+
+
+class RegistrationListener:
+    def __init__(self, endpoint: str, on_register: Callable[[GpuRegistration], None]) -> None:
+        self.endpoint = endpoint
+        self.on_register = on_register
+        self._ctx = zmq.Context.instance()
+        self._sock = get_zmq_socket(self._ctx, zmq.PULL, endpoint, bind=True)
+        self._stop = threading.Event()
+        self._thread: Optional[threading.Thread] = None
+        self.count = 0
+
+    def start(self) -> None:
+        self._thread = threading.Thread(target=self._loop, name="flexkv-gpu-register", daemon=True)
+        self._thread.start()
+
+    def _loop(self) -> None:
+        poller = zmq.Poller()
+        poller.register(self._sock, zmq.POLLIN)
+        while not self._stop.is_set():
+            if not dict(poller.poll(200)):
+                continue
+            try:
+                req = pickle.loads(self._sock.recv())
+                if isinstance(req, RegisterTPClientRequest):
+                    self.on_register(registration_from_request(req))
+                    self.count += 1
+                    flexkv_logger.info("registered GPU tensors of dp client %d rank %d (device %d)",
+                                       req.dp_client_id, req.intra_client_id, req.device_id)
+            except Exception:  # noqa: BLE001
+                flexkv_logger.exception("bad GPU registration message")
+
+    def stop(self) -> None:
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join(timeout=5)
+        self._sock.close()

@@ -1,0 +1,123 @@
+"""Messages between clients and the KV server (flexkv/server/request.py:15-180)."""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Dict, List, Optional
+
+import numpy as np
+
+from ..common.memory_handle import TensorSharedHandle
+from ..common.storage import KVCacheLayout
+
+
+@dataclass
+class Request:
+    dp_client_id: int = 0
+    seq: int = 0                      # echoed in the response so a client can pair them
+
+
+@dataclass
+class RegisterDPClientRequest(Request):
+    client_recv_port: str = ""
+
+
+@dataclass
+class RegisterTPClientRequest:
+    """One engine worker's KV tensors; key = (dp_client_id, intra_client_id)
+    (flexkv/server/request.py:46-48)."""
+    dp_client_id: int
+    intra_client_id: int              # pp_rank * effective_tp + effective_tp_rank
+    device_id: int
+    handles: List[TensorSharedHandle]
+    gpu_layout: KVCacheLayout
+    pp_rank: int = 0
+    tp_rank: int = 0
+
+
+@dataclass
+class IsReadyRequest(Request):
+    pass
+
+
+@dataclass
+class PutRequest(Request):
+    token_ids: np.ndarray = None
+    slot_mapping: Optional[np.ndarray] = None
+    token_mask: Optional[np.ndarray] = None
+    namespace: Optional[List[str]] = None
+    match_only: bool = False
+
+
+@dataclass
+class GetRequest(Request):
+    token_ids: np.ndarray = None
+    slot_mapping: Optional[np.ndarray] = None
+    token_mask: Optional[np.ndarray] = None
+    namespace: Optional[List[str]] = None
+    match_only: bool = False
+    cpu_only: bool = False
+    swa_aware: bool = False
+
+
+@dataclass
+class PrefetchRequest(Request):
+    token_ids: np.ndarray = None
+    namespace: Optional[List[str]] = None
+    swa_aware: bool = False
+
+
+@dataclass
+class LaunchRequest(Request):
+    task_ids: List[int] = field(default_factory=list)
+    slot_mappings: List[np.ndarray] = field(default_factory=list)
+    as_batch: bool = False
+    layerwise_transfer: bool = False
+    counter_id: int = 0
+
+
+@dataclass
+class CancelRequest(Request):
+    task_ids: List[int] = field(default_factory=list)
+
+
+@dataclass
+class WaitRequest(Request):
+    task_ids: List[int] = field(default_factory=list)
+    timeout: float = 20.0
+    completely: bool = False
+    try_wait: bool = False
+
+
+@dataclass
+class ResetRequest(Request):
+    pass
+
+
+@dataclass
+class PublishGpuBlocksRequest(Request):
+    token_ids: np.ndarray = None
+    slot_mapping: np.ndarray = None
+    namespace: Optional[List[str]] = None
+
+
+@dataclass
+class WithdrawGpuBlocksRequest(Request):
+    gpu_block_ids: np.ndarray = None
+
+
+@dataclass
+class ShutdownRequest(Request):
+    pass
+
+
+@dataclass
+class Response:
+    dp_client_id: int
+    seq: int = 0
+    task_id: Optional[int] = None
+    task_ids: Optional[List[int]] = None
+    mask: Optional[np.ndarray] = None
+    status: Optional[Dict[int, Any]] = None
+    ready: Optional[bool] = None
+    value: Any = None
+    error: Optional[str] = None

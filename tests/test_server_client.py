@@ -1,0 +1,56 @@
+"""Server-client mode on CPU: two data-parallel KVManager front ends share one
+index through the ZeroMQ server; GPU tensors (host stand-ins here) arrive as
+handles over the registration socket (reference: tests/test_kvmanager_client_api.py,
+test_external_server_mode.py, test_registration_key.py)."""
+import os
+import time
+
+import numpy as np
+import pytest
+import torch
+
+from flexkv_b200 import CacheConfig, KVManager, KVTPClient
+from flexkv_b200.models import KVShape, alloc_paged_cache, make_model_config
+from flexkv_b200.server.utils import unique_ipc_endpoint
+
+
+def slots(blocks, T):
+    return np.repeat(np.asarray(blocks, dtype=np.int64), T) * T + np.tile(np.arange(T), len(blocks))
+
+
+def test_two_dp_ranks_share_one_server():
+    shape = KVShape("s", 2, 2, 16, tokens_per_block=4)
+    T = 4
+    model = make_model_config(shape, dp_size=2)
+    cache = CacheConfig(tokens_per_block=T, num_cpu_blocks=32)
+    ep, reg = unique_ipc_endpoint("srv"), unique_ipc_endpoint("reg")
+    m0 = KVManager(model, cache, dp_client_id=0, server_recv_port=ep, gpu_register_port=reg, require_gpu=True)
+    m1 = KVManager(model, cache, dp_client_id=1, server_recv_port=ep, gpu_register_port=reg)
+    assert m0.server_client_mode and m0.server_handle is not None and m1.server_handle is None
+    caches = []
+    for d in range(2):
+        kv, layout = alloc_paged_cache(shape, 32, "cpu", "vllm", fill="normal", seed=70 + d)
+        KVTPClient(reg, dp_client_id=d, device_id=0, tp_rank=0).register_to_server(kv, layout, mode="same_process")
+        caches.append(kv)
+    m0.start(); m1.start()
+    try:
+        m0.wait_ready(30); m1.wait_ready(30)
+        tok = np.arange(6 * T, dtype=np.int64)
+        src = np.array([3, 9, 1, 30, 12, 7])
+        tid = m0.put_async(tok, slots(src, T))
+        assert m0.wait(tid, completely=True)[tid].status.value == "success"
+        # the other rank sees the prefix and restores it into its own cache
+        tid, mask = m1.get_match(tok)
+        assert int(mask.sum()) == 6 * T
+        dst = np.array([0, 1, 2, 3, 4, 5])
+        assert m1.launch(tid, slots(dst, T)) == [tid]
+        assert m1.wait(tid)[tid].status.value == "success"
+        for l in range(2):
+            assert torch.equal(caches[1][l][:, dst], caches[0][l][:, src])
+        assert m1.try_wait(tid)[tid].status.value == "not_found"
+        m1.reset()
+        assert int(m0.get_match(tok)[1].sum()) == 0
+        with pytest.raises(RuntimeError):
+            m0.launch(12345, slots(dst, T))        # server-side errors come back as exceptions
+    finally:
+        m1.shutdown(); m0.shutdown()
