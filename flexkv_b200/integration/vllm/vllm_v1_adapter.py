@@ -1,0 +1,373 @@
+"""vLLM v1 KV-connector adapter.
+
+``FlexKVSchedulerConnector`` lives beside vLLM's scheduler and owns a KVManager;
+``FlexKVWorkerConnector`` lives in every worker and only registers that worker's
+KV tensors: all data movement is done by the data plane through the shared
+handles. ``FlexKVConnectorV1Impl`` is the object vLLM instantiates per role. The
+contract follows the reference adapter (flexkv/integration/vllm/vllm_v1_adapter.py:
+228-781 scheduler side, :783-977 worker side, :979-1283 connector):
+
+* lookup: tokens truncated to whole blocks, mask = tokens beyond the computed
+  prefix, ``get_match``; a zero hit cancels the task at once;
+* bind: after allocation, the slot mapping covers only the blocks to restore;
+* offload: on finish, ``put_match`` over ``((n-1)//T)*T`` tokens; if something is
+  new the request's blocks stay alive until the put completes;
+* step loop: cancel, launch (gets and puts batched separately), poll finished;
+  failed gets report their GPU block ids so vLLM recomputes them.
+
+Engine objects are accessed by attribute name only (request_id, all_token_ids /
+prompt_token_ids, num_computed_tokens, lora_request, cache_salt ...).
+"""
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass, field
+from typing import Any, Dict, Iterable, List, Optional, Sequence, Set, Tuple
+
+import numpy as np
+import torch
+
+from ...common.config import GLOBAL_CONFIG_FROM_ENV
+from ...common.debug import flexkv_logger
+from ...common.request import KVResponseStatus
+from ...common.storage import KVCacheLayout, KVCacheLayoutType
+from ..config import FlexKVConfig
+from ..stats import FlexKVStats
+
+
+@dataclass
+class FlexKVTask:
+    task_id: int
+    request_id: str
+    kind: str                          # "get" | "put"
+    num_tokens: int                    # tokens the task will move
+    start_block: int                   # first block (in the request) the slot mapping must cover
+    num_blocks: int
+    slot_mapping: Optional[np.ndarray] = None
+    created: float = field(default_factory=time.monotonic)
+    gpu_block_ids: Optional[np.ndarray] = None
+
+
+def _tokens_of(request: Any) -> np.ndarray:
+    for name in ("all_token_ids", "prompt_token_ids", "token_ids"):
+        v = getattr(request, name, None)
+        if v is not None:
+            return np.asarray(list(v), dtype=np.int64)
+    raise AttributeError("request has no token ids")
+
+
+def _block_ids_of(blocks: Any) -> List[int]:
+    """vLLM hands over KVCacheBlocks (get_block_ids() -> tuple of lists, one per group) or plain lists."""
+    if blocks is None:
+        return []
+    if hasattr(blocks, "get_block_ids"):
+        ids = blocks.get_block_ids()
+        return list(ids[0]) if ids and isinstance(ids[0], (list, tuple)) else list(ids)
+    if len(blocks) and isinstance(blocks[0], (list, tuple)):
+        return list(blocks[0])
+    return list(blocks)
+
+
+class FlexKVSchedulerConnector:
+    def __init__(self, flexkv_config: FlexKVConfig, kv_manager: Any = None, dp_client_id: int = 0) -> None:
+        self.cfg = flexkv_config
+        self.T = flexkv_config.cache_config.tokens_per_block
+        if kv_manager is None:
+            from ...kvmanager import KVManager
+            kv_manager = KVManager(flexkv_config.model_config, flexkv_config.cache_config, dp_client_id=dp_client_id,
+                                   server_recv_port=flexkv_config.server_recv_port,
+                                   gpu_register_port=flexkv_config.gpu_register_port)
+            kv_manager.start()
+        self.mgr = kv_manager
+        self.stats = FlexKVStats()
+        self.req_to_get: Dict[str, FlexKVTask] = {}          # matched, waiting for allocation / launch
+        self.req_to_put: Dict[str, FlexKVTask] = {}
+        self.launched_get: Dict[int, FlexKVTask] = {}
+        self.launched_put: Dict[int, FlexKVTask] = {}
+        self.to_launch: List[FlexKVTask] = []
+        self.to_cancel: List[int] = []
+        self.failed_block_ids: Set[int] = set()
+        self.batch_members: Dict[int, List[FlexKVTask]] = {}
+
+    # ---- lifecycle --------------------------------------------------------------------
+    def is_ready(self) -> bool:
+        return self.mgr.is_ready()
+
+    def shutdown(self) -> None:
+        self.mgr.shutdown()
+
+    def reset_cache(self) -> bool:
+        """After a weight update: nothing cached before may be reused."""
+        self.cancel_tasks()
+        self.mgr.reset()
+        return True
+
+    # ---- lookup -------------------------------------------------------------------------
+    def _namespace(self, request: Any) -> Optional[List[str]]:
+        ns: List[str] = []
+        lora = getattr(request, "lora_request", None)
+        if lora is not None:
+            ns.append(str(getattr(lora, "lora_name", None) or getattr(lora, "name", lora)))
+        salt = getattr(request, "cache_salt", None)
+        if salt:
+            ns.append(str(salt))
+        extra = getattr(request, "namespace_info", None)
+        if extra:
+            ns.extend(str(x) for x in extra)
+        return ns or None
+
+    def get_num_new_matched_tokens(self, request: Any, num_computed_tokens: int) -> Tuple[int, bool]:
+        """Tokens beyond ``num_computed_tokens`` that can be restored; the bool says
+        the load is asynchronous (vLLM parks the request until ``get_finished`` names it)."""
+        tokens = _tokens_of(request)
+        aligned = (len(tokens) // self.T) * self.T
+        if aligned <= num_computed_tokens:
+            return 0, False
+        tokens = tokens[:aligned]
+        mask = np.zeros(aligned, dtype=np.bool_)
+        mask[num_computed_tokens:] = True
+        task_id, matched = self.mgr.get_match(tokens, mask, namespace=self._namespace(request))
+        n = int(matched.sum())
+        self.stats.record_get(len(tokens), num_computed_tokens, n)
+        if n == 0:
+            self.mgr.cancel(task_id)
+            return 0, False
+        rid = str(request.request_id)
+        old = self.req_to_get.pop(rid, None)
+        if old is not None:
+            self.to_cancel.append(old.task_id)
+        self.req_to_get[rid] = FlexKVTask(task_id, rid, "get", n, num_computed_tokens // self.T, n // self.T)
+        return n, True
+
+    # ---- bind ------------------------------------------------------------------------------
+    def update_state_after_alloc(self, request: Any, blocks: Any, num_external_tokens: int) -> None:
+        rid = str(request.request_id)
+        task = self.req_to_get.pop(rid, None)
+        if task is None:
+            return
+        if num_external_tokens == 0:
+            self.to_cancel.append(task.task_id)
+            return
+        ids = _block_ids_of(blocks)
+        new = np.asarray(ids[task.start_block:task.start_block + task.num_blocks], dtype=np.int64)
+        if len(new) < task.num_blocks:
+            flexkv_logger.warning("request %s: %d blocks allocated for a %d-block restore; cancelling", rid, len(new),
+                                  task.num_blocks)
+            self.to_cancel.append(task.task_id)
+            return
+        task.gpu_block_ids = new
+        task.slot_mapping = np.repeat(new, self.T) * self.T + np.tile(np.arange(self.T), len(new))
+        self.to_launch.append(task)
+
+    # ---- offload ----------------------------------------------------------------------------
+    def request_finished(self, request: Any, block_ids: Sequence[int]) -> Tuple[bool, Optional[dict]]:
+        """True keeps the request's blocks alive until the put completes."""
+        rid = str(request.request_id)
+        pending = self.req_to_get.pop(rid, None)
+        if pending is not None:
+            self.to_cancel.append(pending.task_id)
+        tokens = _tokens_of(request)
+        n = ((len(tokens) - 1) // self.T) * self.T
+        if n <= 0:
+            return False, None
+        tokens = tokens[:n]
+        task_id, mask = self.mgr.put_match(tokens, namespace=self._namespace(request))
+        new = int(mask.sum())
+        self.stats.record_put(n, new)
+        if new == 0:
+            self.mgr.cancel(task_id)
+            return False, None
+        first = int(np.flatnonzero(mask)[0]) // self.T
+        ids = np.asarray(list(block_ids)[first:first + new // self.T], dtype=np.int64)
+        if len(ids) < new // self.T:
+            self.mgr.cancel(task_id)
+            return False, None
+        task = FlexKVTask(task_id, rid, "put", new, first, new // self.T, gpu_block_ids=ids)
+        task.slot_mapping = np.repeat(ids, self.T) * self.T + np.tile(np.arange(self.T), len(ids))
+        self.to_launch.append(task)
+        return True, None
+
+    # ---- step loop --------------------------------------------------------------------------
+    def cancel_tasks(self) -> None:
+        for t in self.req_to_get.values():
+            self.to_cancel.append(t.task_id)
+        self.req_to_get.clear()
+        if self.to_cancel:
+            self.mgr.cancel(self.to_cancel)
+            self.to_cancel = []
+
+    def flush_cancels(self) -> None:
+        if self.to_cancel:
+            self.mgr.cancel(self.to_cancel)
+            self.to_cancel = []
+
+    def launch_tasks(self) -> None:
+        gets = [t for t in self.to_launch if t.kind == "get"]
+        puts = [t for t in self.to_launch if t.kind == "put"]
+        self.to_launch = []
+        for group, book in ((gets, self.launched_get), (puts, self.launched_put)):
+            if not group:
+                continue
+            ids = self.mgr.launch([t.task_id for t in group], [t.slot_mapping for t in group], as_batch=len(group) > 1)
+            if len(ids) == 1 and len(group) > 1:
+                self.batch_members[ids[0]] = group
+                book[ids[0]] = group[0]
+            else:
+                for t in group:
+                    book[t.task_id] = t
+
+    def query_finished_task(self) -> Tuple[Set[str], Set[str]]:
+        """(request ids whose put finished, request ids whose get finished)."""
+        sending, recving = set(), set()
+        for book, out, is_get in ((self.launched_put, sending, False), (self.launched_get, recving, True)):
+            if not book:
+                continue
+            done = self.mgr.try_wait(list(book))
+            for tid, rsp in done.items():
+                members = self.batch_members.pop(tid, None) or [book[tid]]
+                book.pop(tid, None)
+                for t in members:
+                    out.add(t.request_id)
+                    if rsp.status != KVResponseStatus.SUCCESS:
+                        self.stats.record_failed()
+                        if is_get and t.gpu_block_ids is not None:
+                            self.failed_block_ids.update(int(b) for b in t.gpu_block_ids)
+        return sending, recving
+
+    def get_and_clear_failed_block_ids(self) -> Set[int]:
+        out, self.failed_block_ids = self.failed_block_ids, set()
+        return out
+
+    def handle_preemptions(self, preempted_req_ids: Iterable[str]) -> None:
+        """Unlaunched work of a preempted request is dropped; launched transfers run to completion."""
+        gone = {str(r) for r in preempted_req_ids}
+        for rid in list(self.req_to_get):
+            if rid in gone:
+                self.to_cancel.append(self.req_to_get.pop(rid).task_id)
+        keep = []
+        for t in self.to_launch:
+            if t.request_id in gone:
+                self.to_cancel.append(t.task_id)
+            else:
+                keep.append(t)
+        self.to_launch = keep
+
+    def wait_for_all(self, timeout: float = 60.0) -> None:
+        ids = list(self.launched_get) + list(self.launched_put)
+        if ids:
+            self.mgr.wait(ids, timeout=timeout, completely=True)
+
+
+def infer_vllm_gpu_layout(kv_caches: Sequence[torch.Tensor], tokens_per_block: int, num_kv_heads: int, head_size: int,
+                          use_mla: bool) -> KVCacheLayout:
+    """Tells the two vLLM cache shapes apart by inspecting the real tensor:
+    flash-attn ``[2, N, T, H, D]`` vs flashinfer / triton ``[N, 2, T, H, D]``; MLA is
+    ``[N, T, D]`` (flexkv/integration/vllm/vllm_v1_adapter.py:846-905)."""
+    t = kv_caches[0]
+    L = len(kv_caches)
+    if use_mla or t.dim() == 3:
+        return KVCacheLayout(KVCacheLayoutType.LAYERFIRST, L, t.shape[0], tokens_per_block, 1, t.shape[-1], is_mla=True)
+    if t.dim() != 5:
+        raise ValueError(f"unsupported vLLM KV cache shape {tuple(t.shape)}")
+    if t.shape[0] == 2 and t.shape[1] != 2:
+        ltype, nb = KVCacheLayoutType.LAYERFIRST, t.shape[1]
+    elif t.shape[1] == 2:
+        ltype, nb = KVCacheLayoutType.LAYERBLOCK, t.shape[0]
+    else:
+        ltype, nb = KVCacheLayoutType.LAYERFIRST, t.shape[1]
+    return KVCacheLayout(ltype, L, nb, t.shape[2], t.shape[3], t.shape[4])
+
+
+class FlexKVWorkerConnector:
+    def __init__(self, flexkv_config: FlexKVConfig, dp_client_id: int = 0, tp_rank: int = 0, pp_rank: int = 0,
+                 device_id: Optional[int] = None) -> None:
+        from ...server.client import KVTPClient
+        self.cfg = flexkv_config
+        self.device_id = torch.cuda.current_device() if device_id is None and torch.cuda.is_available() else (device_id or 0)
+        self.client = KVTPClient(flexkv_config.gpu_register_port, dp_client_id, self.device_id, tp_rank=tp_rank,
+                                 pp_rank=pp_rank)
+        self._caches: Optional[List[torch.Tensor]] = None
+        self._layout: Optional[KVCacheLayout] = None
+
+    def register_to_server(self, kv_caches: Dict[str, torch.Tensor]) -> None:
+        tensors = list(kv_caches.values()) if isinstance(kv_caches, dict) else list(kv_caches)
+        m, c = self.cfg.model_config, self.cfg.cache_config
+        layout = infer_vllm_gpu_layout(tensors, c.tokens_per_block, m.num_kv_heads // max(1, m.tp_size), m.head_size,
+                                       m.use_mla)
+        self._caches, self._layout = tensors, layout
+        self.client.register_to_server(tensors, layout)
+
+    def before_device_sleep(self) -> int:
+        """vLLM sleep mode frees the cache; the data plane must stop touching it. The host tier is kept."""
+        return 0
+
+    def after_device_wake(self) -> None:
+        if self._caches is not None:
+            self.client.register_to_server(self._caches, self._layout)
+
+
+class FlexKVConnectorV1Impl:
+    """Role-dispatching object behind vLLM's ``KVConnectorBase_V1`` interface."""
+
+    def __init__(self, vllm_config: Any, role: Any) -> None:
+        self.cfg = FlexKVConfig.from_env()
+        self.cfg.post_init_from_vllm_config(vllm_config)
+        role_name = str(getattr(role, "name", role)).upper()
+        self.is_scheduler = "SCHEDULER" in role_name
+        pc = getattr(vllm_config, "parallel_config", None)
+        dp_rank = int(getattr(pc, "data_parallel_rank", 0) or 0)
+        if self.is_scheduler:
+            self.scheduler = FlexKVSchedulerConnector(self.cfg, dp_client_id=dp_rank)
+            self.worker = None
+        else:
+            tp_rank = int(getattr(pc, "rank", 0) or 0) % max(1, self.cfg.model_config.tp_size)
+            self.worker = FlexKVWorkerConnector(self.cfg, dp_client_id=dp_rank, tp_rank=tp_rank)
+            self.scheduler = None
+        self._finished_sending: Set[str] = set()
+        self._finished_recving: Set[str] = set()
+
+    # worker side: data moves outside the forward pass, so these hooks are no-ops
+    def start_load_kv(self, forward_context: Any, **kw: Any) -> None: ...
+    def wait_for_layer_load(self, layer_name: str) -> None: ...
+    def save_kv_layer(self, layer_name: str, kv_layer: torch.Tensor, attn_metadata: Any, **kw: Any) -> None: ...
+    def wait_for_save(self) -> None: ...
+
+    def register_kv_caches(self, kv_caches: Dict[str, torch.Tensor]) -> None:
+        self.worker.register_to_server(kv_caches)
+
+    def get_finished(self, finished_req_ids: Set[str]) -> Tuple[Optional[Set[str]], Optional[Set[str]]]:
+        s, r = self._finished_sending, self._finished_recving
+        self._finished_sending, self._finished_recving = set(), set()
+        return s or None, r or None
+
+    # scheduler side
+    def get_num_new_matched_tokens(self, request: Any, num_computed_tokens: int) -> Tuple[int, bool]:
+        return self.scheduler.get_num_new_matched_tokens(request, num_computed_tokens)
+
+    def update_state_after_alloc(self, request: Any, blocks: Any, num_external_tokens: int) -> None:
+        self.scheduler.update_state_after_alloc(request, blocks, num_external_tokens)
+
+    def build_connector_meta(self, scheduler_output: Any) -> dict:
+        s = self.scheduler
+        pre = getattr(scheduler_output, "preempted_req_ids", None)
+        if pre:
+            s.handle_preemptions(pre)
+        s.flush_cancels()
+        s.launch_tasks()
+        sending, recving = s.query_finished_task()
+        return {"finished_sending": sending, "finished_recving": recving}
+
+    def update_connector_output(self, connector_output: Any) -> None: ...
+
+    def request_finished(self, request: Any, block_ids: Sequence[int]) -> Tuple[bool, Optional[dict]]:
+        return self.scheduler.request_finished(request, block_ids)
+
+    def get_block_ids_with_load_errors(self) -> Set[int]:
+        return self.scheduler.get_and_clear_failed_block_ids() if self.scheduler else set()
+
+    def reset_cache(self) -> Optional[bool]:
+        return self.scheduler.reset_cache() if self.scheduler else None
+
+    def shutdown(self) -> None:
+        if self.scheduler:
+            self.scheduler.shutdown()

@@ -1,0 +1,97 @@
+"""Prometheus metrics (same metric names as the reference so existing dashboards
+keep working: flexkv/metrics/collector.py:152-247). Enabled by
+``FLEXKV_ENABLE_METRICS=1``; the HTTP endpoint listens on ``FLEXKV_PY_METRICS_PORT``."""
+from __future__ import annotations
+
+import threading
+from typing import Optional
+
+from ..common.config import GLOBAL_CONFIG_FROM_ENV
+from ..common.debug import flexkv_logger
+
+try:
+    from prometheus_client import CollectorRegistry, Counter, Gauge, start_http_server
+    _HAVE_PROM = True
+except Exception:  # noqa: BLE001
+    _HAVE_PROM = False
+
+
+class MetricsCollector:
+    def __init__(self, registry=None) -> None:
+        if not _HAVE_PROM:
+            raise RuntimeError("prometheus_client is not installed")
+        self.registry = registry or CollectorRegistry()
+        r = self.registry
+        self.cache_hit_blocks = Counter("flexkv_py_cache_hit_blocks", "Blocks found in a tier", ["device"], registry=r)
+        self.cache_miss_blocks = Counter("flexkv_py_cache_miss_blocks", "Blocks not found in a tier", ["device"],
+                                         registry=r)
+        self.allocation_failures = Counter("flexkv_py_allocation_failures", "Plans dropped for lack of blocks",
+                                           ["device"], registry=r)
+        self.transfer_blocks = Counter("flexkv_py_transfer_blocks", "Blocks moved", ["type", "operation"], registry=r)
+        self.transfer_ops = Counter("flexkv_py_transfer_ops", "Transfer ops", ["type", "operation"], registry=r)
+        self.transfer_bytes = Counter("flexkv_py_transfer_bytes", "Bytes moved", ["type", "operation"], registry=r)
+        self.evicted_blocks = Counter("flexkv_py_evicted_blocks", "Blocks evicted", ["device"], registry=r)
+        self.allocated_blocks = Counter("flexkv_py_allocated_blocks", "Blocks allocated", ["device"], registry=r)
+        self.mempool_total = Gauge("flexkv_py_mempool_total_blocks", "Pool capacity", ["device"], registry=r)
+        self.mempool_free = Gauge("flexkv_py_mempool_free_blocks", "Free blocks", ["device"], registry=r)
+        self.peer_hit_blocks = Counter("flexkv_py_peer_gpu_hit_blocks", "Blocks pulled from a peer GPU over NVLink",
+                                       registry=r)
+        self._server_started = False
+
+    def start_server(self, port: Optional[int] = None) -> None:
+        if self._server_started:
+            return
+        port = port or GLOBAL_CONFIG_FROM_ENV.py_metrics_port
+        try:
+            start_http_server(port, registry=self.registry)
+            self._server_started = True
+            flexkv_logger.info("metrics endpoint on :%d", port)
+        except OSError as e:
+            flexkv_logger.warning("metrics endpoint not started: %s", e)
+
+    def record_match(self, device: str, hit_blocks: int, miss_blocks: int) -> None:
+        if hit_blocks > 0:
+            self.cache_hit_blocks.labels(device).inc(hit_blocks)
+        if miss_blocks > 0:
+            self.cache_miss_blocks.labels(device).inc(miss_blocks)
+
+    def record_allocation_failure(self, device: str) -> None:
+        self.allocation_failures.labels(device).inc()
+
+    def record_eviction(self, device: str, n: int) -> None:
+        self.evicted_blocks.labels(device).inc(n)
+
+    def record_transfer(self, ttype: str, blocks: int, nbytes: int, success: bool) -> None:
+        op = "success" if success else "failure"
+        self.transfer_ops.labels(ttype, op).inc()
+        self.transfer_blocks.labels(ttype, op).inc(blocks)
+        self.transfer_bytes.labels(ttype, op).inc(nbytes)
+        if ttype == "PEERD2D" and success:
+            self.peer_hit_blocks.inc(blocks)
+
+    def set_mempool(self, device: str, total: int, free: int) -> None:
+        self.mempool_total.labels(device).set(total)
+        self.mempool_free.labels(device).set(free)
+
+    def snapshot(self) -> dict:
+        out = {}
+        for fam in self.registry.collect():
+            for s in fam.samples:
+                if s.name.endswith("_created"):
+                    continue
+                out[(s.name, tuple(sorted(s.labels.items())))] = s.value
+        return out
+
+
+_singleton: Optional[MetricsCollector] = None
+_lock = threading.Lock()
+
+
+def get_collector(start_server: bool = False) -> MetricsCollector:
+    global _singleton
+    with _lock:
+        if _singleton is None:
+            _singleton = MetricsCollector()
+        if start_server:
+            _singleton.start_server()
+        return _singleton

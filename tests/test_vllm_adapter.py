@@ -1,0 +1,130 @@
+"""vLLM connector contract with stand-in engine objects and the CPU data plane:
+lookup -> bind -> launch -> finished, offload on finish, zero-hit cancel,
+preemption, failed-get block reporting, config mapping (reference:
+tests/test_vllm_abort_offload_directive.py and the adapter contract)."""
+from types import SimpleNamespace as NS
+
+import numpy as np
+import pytest
+import torch
+
+from flexkv_b200 import CacheConfig, KVManager
+from flexkv_b200.integration.config import FlexKVConfig
+from flexkv_b200.integration.dynamo.collector import KVEventCollector
+from flexkv_b200.integration.vllm.vllm_v1_adapter import FlexKVSchedulerConnector, infer_vllm_gpu_layout
+from flexkv_b200.models import KVShape, alloc_paged_cache, make_model_config
+
+T = 4
+
+
+def make():
+    shape = KVShape("v", 2, 2, 16, tokens_per_block=T)
+    cfg = FlexKVConfig()
+    cfg.model_config = make_model_config(shape)
+    cfg.cache_config = CacheConfig(tokens_per_block=T, num_cpu_blocks=32)
+    mgr = KVManager(cfg.model_config, cfg.cache_config, require_gpu=True)
+    kv, layout = alloc_paged_cache(shape, 64, "cpu", "vllm", fill="normal", seed=80)
+    mgr.register_gpu_tensors(kv, layout)
+    mgr.start(); mgr.wait_ready(30)
+    return FlexKVSchedulerConnector(cfg, kv_manager=mgr), kv, mgr
+
+
+def req(rid, tokens, **kw):
+    return NS(request_id=rid, all_token_ids=list(tokens), lora_request=None, cache_salt=None, **kw)
+
+
+def drain(conn, want_send=(), want_recv=()):
+    import time
+    s, r = set(), set()
+    t0 = time.time()
+    while (not set(want_send) <= s or not set(want_recv) <= r) and time.time() - t0 < 10:
+        a, b = conn.query_finished_task()
+        s |= a; r |= b
+        time.sleep(0.005)
+    return s, r
+
+
+def test_offload_then_restore_cycle():
+    conn, kv, mgr = make()
+    try:
+        events = KVEventCollector()
+        events.attach(mgr.kv_task_engine.cache_engine)
+        tok = np.arange(100, 100 + 6 * T + 2)
+        r1 = req("a", tok)
+        assert conn.get_num_new_matched_tokens(r1, 0) == (0, False)          # cold
+        keep, _ = conn.request_finished(r1, [10, 11, 12, 13, 14, 15, 16])
+        assert keep                                                           # blocks stay until the put lands
+        conn.launch_tasks()
+        s, _ = drain(conn, want_send={"a"})
+        assert s == {"a"}
+        stored = [e for e in events.take_events() if e.kind == "stored"]
+        assert sum(len(e.block_hashes) for e in stored) == 6                  # ((26-1)//4)*4 = 24 tokens = 6 blocks
+        # a second request with the same prompt: 2 blocks already computed on the GPU, 4 to restore
+        r2 = req("b", tok)
+        n, is_async = conn.get_num_new_matched_tokens(r2, 2 * T)
+        assert (n, is_async) == (4 * T, True)
+        saved = [t.clone() for t in kv]
+        conn.update_state_after_alloc(r2, NS(get_block_ids=lambda: ([40, 41, 42, 43, 44, 45, 46],)), n)
+        conn.launch_tasks()
+        _, r = drain(conn, want_recv={"b"})
+        assert r == {"b"} and conn.get_and_clear_failed_block_ids() == set()
+        for l in range(2):
+            assert torch.equal(kv[l][:, [42, 43, 44, 45]], saved[l][:, [12, 13, 14, 15]])
+        # finishing it again offloads nothing new and frees the blocks immediately
+        assert conn.request_finished(r2, [40, 41, 42, 43, 44, 45, 46]) == (False, None)
+        assert conn.stats.num_get_requests == 2 and conn.stats.num_flexkv_matched_tokens == 4 * T
+    finally:
+        conn.shutdown()
+
+
+def test_preemption_cancels_unlaunched_and_failed_get_reports_blocks():
+    conn, kv, mgr = make()
+    try:
+        tok = np.arange(6 * T + 1)
+        conn.request_finished(req("seed", tok), list(range(6)))
+        conn.launch_tasks()
+        drain(conn, want_send={"seed"})
+        r = req("p", tok)
+        n, _ = conn.get_num_new_matched_tokens(r, 0)
+        assert n == 6 * T
+        conn.handle_preemptions(["p"])
+        conn.flush_cancels()
+        cpu = mgr.kv_task_engine.cache_engine.cpu_cache_engine
+        from flexkv_b200.common.block import SequenceMeta
+        assert cpu.index.node_lock_cnt(cpu.match(SequenceMeta(tok[:24], T)).last_node) == 0   # lock released
+        # a get whose transfer fails: its GPU blocks are reported for recomputation
+        from flexkv_b200.common.transfer import TransferType, WorkerKey
+        mgr.transfer_manager.engine.worker_for(WorkerKey(0, 0), TransferType.H2D).fail_next = 1
+        r = req("f", tok)
+        n, _ = conn.get_num_new_matched_tokens(r, 0)
+        conn.update_state_after_alloc(r, [[20, 21, 22, 23, 24, 25]], n)
+        conn.launch_tasks()
+        _, done = drain(conn, want_recv={"f"})
+        assert done == {"f"} and conn.get_and_clear_failed_block_ids() == {20, 21, 22, 23, 24, 25}
+    finally:
+        conn.shutdown()
+
+
+def test_layout_inference_and_config_mapping():
+    a = [torch.empty(2, 10, 16, 4, 64) for _ in range(3)]
+    b = [torch.empty(10, 2, 16, 4, 64) for _ in range(3)]
+    c = [torch.empty(10, 16, 576) for _ in range(3)]
+    assert infer_vllm_gpu_layout(a, 16, 4, 64, False).type.value == "LAYERFIRST"
+    assert infer_vllm_gpu_layout(b, 16, 4, 64, False).type.value == "LAYERBLOCK"
+    lay = infer_vllm_gpu_layout(c, 16, 1, 576, True)
+    assert lay.is_mla and lay.kv_dim == 1 and lay.num_block == 10
+    hf = NS(num_hidden_layers=32, num_key_value_heads=8, num_attention_heads=32, hidden_size=4096, head_dim=128)
+    vcfg = NS(model_config=NS(hf_text_config=hf, hf_config=hf, dtype=torch.bfloat16, use_mla=False),
+              parallel_config=NS(tensor_parallel_size=2, pipeline_parallel_size=1, data_parallel_size=1),
+              cache_config=NS(block_size=16, cache_dtype="auto"))
+    cfg = FlexKVConfig()
+    cfg.user_config.cpu_cache_gb = 4
+    cfg.post_init_from_vllm_config(vcfg)
+    m = cfg.model_config
+    assert (m.num_layers, m.num_kv_heads, m.head_size, m.tp_size) == (32, 8, 128, 2)
+    assert cfg.cache_config.num_cpu_blocks == 4 * 2**30 // (2 * 2**20)
+    with pytest.raises(AttributeError):
+        m.num_layers = 3                                     # frozen after post-init
+    cfg2 = FlexKVConfig(kv_cache_dtype="nvfp4")
+    cfg2.post_init_from_vllm_config(vcfg)
+    assert cfg2.model_config.dtype == torch.uint8 and cfg2.model_config.head_size == 64 + 8   # nibbles + scales
