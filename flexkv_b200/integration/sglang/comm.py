@@ -1,0 +1,178 @@
+"""Rank coordination for the SGLang connector and the engine-side layer hook.
+
+``FlexKVComm``: only the sync leader of a replica owns a KVManager; it scatters
+per-request manifests (matched lengths, task ids, slot mappings) to the other
+TP / CP / PP ranks, and block counts are agreed with an all-reduce(MIN), over a
+CPU (gloo) process group (flexkv/integration/sglang/comm.py:81-560).
+
+``FlexKVLayerDoneCounter``: ``num_counters`` sets of per-layer eventfds (triple
+buffering, so a new restore can be prepared while the previous one is being
+consumed). The model's layer hook calls ``wait_until(layer)``, which blocks on
+that layer's eventfd of the consumer set once per restore in flight
+(flexkv/integration/sglang/comm.py:611-983).
+"""
+from __future__ import annotations
+
+import os
+import pickle
+import select
+import struct
+import threading
+import time
+from typing import Any, Dict, List, Optional
+
+import torch
+import torch.distributed as dist
+
+
+class FlexKVComm:
+    def __init__(self, world_group=None, tp_size: int = 1, cp_size: int = 1, pp_size: int = 1,
+                 rank: Optional[int] = None) -> None:
+        self.group = world_group
+        self.enabled = dist.is_available() and dist.is_initialized()
+        self.rank = rank if rank is not None else (dist.get_rank(self.group) if self.enabled else 0)
+        self.world = dist.get_world_size(self.group) if self.enabled else 1
+        self.tp_size, self.cp_size, self.pp_size = tp_size, cp_size, pp_size
+        self.leader = 0
+        if self.enabled and dist.get_backend(self.group) != "gloo":
+            # manifests are CPU objects: coordination needs a CPU-capable group
+            self.group = dist.new_group(backend="gloo")
+
+    @property
+    def is_leader(self) -> bool:
+        return self.rank == self.leader
+
+    def scatter(self, data: Optional[List[Any]] = None) -> Any:
+        """Leader passes one payload per rank; every rank returns its own."""
+        if not self.enabled or self.world == 1:
+            return data[0] if data is not None else None
+        out: List[Any] = [None]
+        dist.scatter_object_list(out, data if self.is_leader else None, src=self.leader, group=self.group)
+        return out[0]
+
+    def broadcast(self, data: Any = None) -> Any:
+        if not self.enabled or self.world == 1:
+            return data
+        box = [data if self.is_leader else None]
+        dist.broadcast_object_list(box, src=self.leader, group=self.group)
+        return box[0]
+
+    def all_reduce_min(self, value: int) -> int:
+        if not self.enabled or self.world == 1:
+            return int(value)
+        t = torch.tensor([int(value)], dtype=torch.int64)
+        dist.all_reduce(t, op=dist.ReduceOp.MIN, group=self.group)
+        return int(t.item())
+
+    def barrier(self) -> None:
+        if self.enabled and self.world > 1:
+            dist.barrier(group=self.group)
+
+
+class FlexKVLayerLoadingEvent:
+    """One set of per-layer eventfds plus the number of restores that will signal it."""
+
+    def __init__(self, num_layers: int) -> None:
+        self.num_layers = num_layers
+        self.fds = [os.eventfd(0, os.EFD_NONBLOCK | os.EFD_SEMAPHORE) for _ in range(num_layers)]
+        self._pending = 0
+        self._lock = threading.Lock()
+
+    def _drain(self) -> None:
+        for fd in self.fds:
+            while True:
+                try:
+                    os.read(fd, 8)
+                except BlockingIOError:
+                    break
+
+    def reset_for_new_transfer(self) -> None:
+        with self._lock:
+            self._drain()
+            self._pending = 0
+
+    def add_transfer(self) -> None:
+        with self._lock:
+            self._pending += 1
+
+    def remove_transfer(self) -> None:
+        with self._lock:
+            self._pending = max(0, self._pending - 1)
+
+    def pending_transfers(self) -> int:
+        return self._pending
+
+    def wait(self, layer: int, timeout: float = 240.0) -> None:
+        """Blocks until every restore registered on this set has signalled `layer`."""
+        need = self._pending
+        fd = self.fds[layer]
+        deadline = time.monotonic() + timeout
+        got = 0
+        while got < need:
+            left = deadline - time.monotonic()
+            if left <= 0:
+                raise TimeoutError(f"layer {layer}: {got} of {need} restores signalled within {timeout} s")
+            r, _, _ = select.select([fd], [], [], min(left, 1.0))
+            if r:
+                try:
+                    os.read(fd, 8)      # semaphore mode: one unit per read
+                    got += 1
+                except BlockingIOError:
+                    pass
+
+    def close(self) -> None:
+        for fd in self.fds:
+            try:
+                os.close(fd)
+            except OSError:
+                pass
+        self.fds = []
+
+
+class FlexKVLayerDoneCounter:
+    def __init__(self, num_layers: int, num_counters: int = 3, world_rank: int = -1) -> None:
+        self.num_layers, self.num_counters, self.world_rank = num_layers, num_counters, world_rank
+        self.events = [FlexKVLayerLoadingEvent(num_layers) for _ in range(num_counters)]
+        self._producer = -1
+        self._consumer = -1
+        self._task_to_counter: Dict[int, int] = {}
+
+    def fds_per_counter(self) -> List[List[int]]:
+        return [list(e.fds) for e in self.events]
+
+    def update_producer(self) -> int:
+        """Chooses the next set for a new restore and clears it."""
+        self._producer = (self._producer + 1) % self.num_counters
+        self.events[self._producer].reset_for_new_transfer()
+        return self._producer
+
+    def register_task(self, task_id: int, producer_id: int) -> None:
+        self._task_to_counter[task_id] = producer_id
+        self.events[producer_id].add_transfer()
+
+    def rollback_prepared_transfer(self, task_id: int) -> None:
+        c = self._task_to_counter.pop(task_id, None)
+        if c is not None:
+            self.events[c].remove_transfer()
+
+    def set_consumer(self, task_id: int) -> None:
+        """The forward pass that is about to run consumes the set this task signals."""
+        self._consumer = self._task_to_counter.pop(task_id, self._consumer)
+
+    def wait_until(self, layer: int, timeout: float = 240.0) -> None:
+        if self._consumer < 0:
+            return
+        self.events[self._consumer].wait(layer, timeout)
+        if layer == self.num_layers - 1:
+            self.events[self._consumer].reset_for_new_transfer()
+            self._consumer = -1
+
+    def reset(self) -> None:
+        for e in self.events:
+            e.reset_for_new_transfer()
+        self._producer = self._consumer = -1
+        self._task_to_counter.clear()
+
+    def close(self) -> None:
+        for e in self.events:
+            e.close()

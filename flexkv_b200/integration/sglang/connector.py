@@ -1,0 +1,258 @@
+"""SGLang HiCache-style connector.
+
+Every rank owns a ``KVTPClient`` (registers its ``2L`` K/V buffers); only the sync
+leader owns a ``KVManager``. Lookups, stores and loads are decided on the leader
+and scattered to the other ranks as manifests so that all ranks act on the same
+matched length (flexkv/integration/sglang/connector.py:116-2291, start-up
+:190-333, lookup :460-586, retrieve :605-694, layerwise load :696-955, store
+:1011-1182, prefetch :1281-1406, reset :1424).
+"""
+from __future__ import annotations
+
+import atexit
+import os
+import signal
+import time
+from dataclasses import dataclass, field
+from typing import Any, Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from ...common.config import GLOBAL_CONFIG_FROM_ENV
+from ...common.debug import flexkv_logger
+from ...common.request import KVResponseStatus
+from ...common.storage import KVCacheLayout, KVCacheLayoutType
+from ..config import FlexKVConfig
+from ..stats import FlexKVStats
+from .comm import FlexKVComm, FlexKVLayerDoneCounter
+
+
+@dataclass
+class _PendingLoad:
+    rid: str
+    task_id: int
+    matched_tokens: int
+    start_block: int
+
+
+def sglang_gpu_layout(k_buffers: Sequence[torch.Tensor], page_size: int, use_mla: bool) -> KVCacheLayout:
+    t = k_buffers[0]
+    L = len(k_buffers)
+    tokens = t.shape[0]
+    if use_mla:
+        return KVCacheLayout(KVCacheLayoutType.LAYERFIRST, L, tokens // page_size, page_size, 1, t.shape[-1],
+                             is_mla=True)
+    return KVCacheLayout(KVCacheLayoutType.LAYERFIRST, L, tokens // page_size, page_size, t.shape[-2], t.shape[-1])
+
+
+class FlexKVConnector:
+    def __init__(self, flexkv_config: FlexKVConfig, page_size: int, tp_rank: int = 0, tp_size: int = 1,
+                 pp_rank: int = 0, pp_size: int = 1, dp_rank: int = 0, cp_rank: int = 0, cp_size: int = 1,
+                 comm: Optional[FlexKVComm] = None, kv_manager: Any = None, register: bool = True) -> None:
+        self.cfg = flexkv_config
+        self.T = page_size
+        self.tp_rank, self.tp_size, self.pp_rank, self.dp_rank = tp_rank, tp_size, pp_rank, dp_rank
+        self.comm = comm or FlexKVComm(tp_size=tp_size, cp_size=cp_size, pp_size=pp_size)
+        self.is_leader = self.comm.is_leader
+        self.stats = FlexKVStats()
+        self.layerwise = bool(GLOBAL_CONFIG_FROM_ENV.enable_layerwise_transfer)
+        self.layer_counter: Optional[FlexKVLayerDoneCounter] = None
+        self.mgr = kv_manager
+        if self.is_leader and self.mgr is None:
+            from ...kvmanager import KVManager
+            self.mgr = KVManager(flexkv_config.model_config, flexkv_config.cache_config, dp_client_id=dp_rank,
+                                 server_recv_port=flexkv_config.server_recv_port,
+                                 gpu_register_port=flexkv_config.gpu_register_port)
+            self.mgr.start()
+        self._pending_loads: Dict[str, _PendingLoad] = {}
+        self._stores: Dict[str, int] = {}
+        self._prefetch: Dict[str, int] = {}
+        self._client = None
+        if register:
+            from ...server.client import KVTPClient
+            dev = torch.cuda.current_device() if torch.cuda.is_available() else 0
+            self._client = KVTPClient(flexkv_config.gpu_register_port, dp_rank, dev, tp_rank=cp_rank * tp_size + tp_rank,
+                                      pp_rank=pp_rank)
+        atexit.register(self.shutdown)
+
+    # ---- start-up ---------------------------------------------------------------------
+    def register_kv_buffers(self, k_buffers: Sequence[torch.Tensor], v_buffers: Optional[Sequence[torch.Tensor]] = None
+                            ) -> None:
+        use_mla = v_buffers is None or self.cfg.model_config.use_mla
+        layout = sglang_gpu_layout(k_buffers, self.T, use_mla)
+        # every rank must agree on the number of pages it can address
+        nb = self.comm.all_reduce_min(layout.num_block)
+        layout = layout._replace(num_block=nb)
+        tensors = list(k_buffers) + ([] if use_mla else list(v_buffers))
+        if self._client is not None:
+            self._client.register_to_server(tensors, layout)
+
+    def register_layer_transfer_counter(self, kvcache: Any) -> None:
+        """Installs the per-layer wait hook on SGLang's KV pool object."""
+        L = self.cfg.model_config.num_layers_per_pp_stage
+        self.layer_counter = FlexKVLayerDoneCounter(L, num_counters=3, world_rank=self.comm.rank)
+        if hasattr(kvcache, "register_layer_transfer_counter"):
+            kvcache.register_layer_transfer_counter(self.layer_counter)
+        sock = os.environ.get("FLEXKV_LAYERWISE_SOCK", "")
+        if sock:
+            from ...transfer.layerwise import send_eventfds
+            send_eventfds(f"{sock}.{self.dp_rank}", self.tp_rank, self.tp_size, self.layer_counter.fds_per_counter())
+
+    def wait_ready(self, timeout: float = 600.0) -> None:
+        if self.is_leader:
+            self.mgr.wait_ready(timeout)
+        self.comm.barrier()
+
+    # ---- lookup / load -------------------------------------------------------------------
+    def lookup_kv(self, rid: str, token_ids: Sequence[int], num_computed_tokens: int = 0,
+                  namespace: Optional[List[str]] = None) -> int:
+        """Tokens beyond the GPU-resident prefix that can be restored (same on every rank)."""
+        matched = 0
+        if self.is_leader:
+            tok = np.asarray(token_ids, dtype=np.int64)
+            aligned = (len(tok) // self.T) * self.T
+            if aligned > num_computed_tokens:
+                mask = np.zeros(aligned, dtype=np.bool_)
+                mask[num_computed_tokens:] = True
+                tid, m = self.mgr.get_match(tok[:aligned], mask, namespace=namespace)
+                matched = int(m.sum())
+                if matched == 0:
+                    self.mgr.cancel(tid)
+                else:
+                    old = self._pending_loads.pop(rid, None)
+                    if old is not None:
+                        self.mgr.cancel(old.task_id)
+                    self._pending_loads[rid] = _PendingLoad(rid, tid, matched, num_computed_tokens // self.T)
+            self.stats.record_get(len(tok), num_computed_tokens, matched)
+        return int(self.comm.broadcast(matched))
+
+    def release_pending(self, rid: str) -> None:
+        p = self._pending_loads.pop(rid, None)
+        if p is not None and self.is_leader:
+            self.mgr.cancel(p.task_id)
+
+    def retrieve_kv(self, rid: str, slot_mapping: Any, timeout: float = 60.0) -> int:
+        """Blocking load of the matched tokens into the pages named by `slot_mapping`
+        (one entry per matched token). Returns the number of tokens restored."""
+        done = 0
+        if self.is_leader:
+            p = self._pending_loads.pop(rid, None)
+            if p is not None:
+                sm = torch.as_tensor(slot_mapping).cpu().numpy().astype(np.int64)[:p.matched_tokens]
+                self.mgr.launch(p.task_id, sm)
+                rsp = self.mgr.wait(p.task_id, timeout=timeout)[p.task_id]
+                done = p.matched_tokens if rsp.status == KVResponseStatus.SUCCESS else 0
+                if not done:
+                    self.stats.record_failed()
+        return int(self.comm.broadcast(done))
+
+    def start_load_kv_layerwise(self, rids: Sequence[str], slot_mappings: Sequence[Any]) -> List[int]:
+        """Launches the loads of a batch as ONE layerwise restore that signals per
+        layer; the forward pass waits in the KV pool's layer hook."""
+        ids: List[int] = []
+        counter = 0
+        if self.is_leader:
+            pend = [self._pending_loads.pop(r, None) for r in rids]
+            pairs = [(p, sm) for p, sm in zip(pend, slot_mappings) if p is not None]
+            if pairs:
+                counter = self.layer_counter.update_producer() if self.layer_counter else 0
+                sms = [torch.as_tensor(sm).cpu().numpy().astype(np.int64)[:p.matched_tokens] for p, sm in pairs]
+                ids = self.mgr.launch([p.task_id for p, _ in pairs], sms, as_batch=True,
+                                      layerwise_transfer=self.layerwise, counter_id=counter)
+        manifest = self.comm.broadcast({"ids": ids, "counter": counter})
+        if self.layer_counter is not None and manifest["ids"]:
+            if not self.is_leader:
+                self.layer_counter.update_producer()
+            for t in manifest["ids"]:
+                self.layer_counter.register_task(t, manifest["counter"])
+            self.layer_counter.set_consumer(manifest["ids"][0])
+        return manifest["ids"]
+
+    def drain_launched_loads(self, task_ids: Sequence[int], timeout: float = 60.0) -> bool:
+        ok = True
+        if self.is_leader and task_ids:
+            res = self.mgr.wait(list(task_ids), timeout=timeout)
+            ok = all(r.status == KVResponseStatus.SUCCESS for r in res.values())
+        return bool(self.comm.broadcast(ok))
+
+    # ---- store -----------------------------------------------------------------------------
+    def store_kv(self, rid: str, token_ids: Sequence[int], slot_mapping: Any,
+                 namespace: Optional[List[str]] = None) -> int:
+        """Asynchronous offload of the request's full pages; returns the tokens that will move."""
+        moved = 0
+        if self.is_leader:
+            tok = np.asarray(token_ids, dtype=np.int64)
+            aligned = (len(tok) // self.T) * self.T
+            if aligned > 0:
+                sm = torch.as_tensor(slot_mapping).cpu().numpy().astype(np.int64)[:aligned]
+                tid, mask = self.mgr.put_match(tok[:aligned], namespace=namespace)
+                moved = int(mask.sum())
+                if moved == 0:
+                    self.mgr.cancel(tid)
+                else:
+                    self.mgr.launch(tid, sm[mask])
+                    self._stores[rid] = tid
+                self.stats.record_put(aligned, moved)
+        return int(self.comm.broadcast(moved))
+
+    def check_completed_stores(self) -> List[str]:
+        done: List[str] = []
+        if self.is_leader and self._stores:
+            res = self.mgr.try_wait(list(self._stores.values()))
+            for rid, tid in list(self._stores.items()):
+                if tid in res:
+                    done.append(rid)
+                    del self._stores[rid]
+        return list(self.comm.broadcast(done))
+
+    def wait_store(self, rid: str, timeout: float = 30.0) -> bool:
+        ok = True
+        if self.is_leader and rid in self._stores:
+            tid = self._stores.pop(rid)
+            ok = self.mgr.wait(tid, timeout=timeout, completely=True)[tid].status == KVResponseStatus.SUCCESS
+        return bool(self.comm.broadcast(ok))
+
+    # ---- prefetch ---------------------------------------------------------------------------
+    def prefetch_async(self, rid: str, token_ids: Sequence[int], namespace: Optional[List[str]] = None) -> None:
+        if self.is_leader:
+            self._prefetch[rid] = self.mgr.prefetch_async(np.asarray(token_ids, dtype=np.int64), namespace=namespace)
+
+    def check_prefetch_progress(self, rid: str) -> bool:
+        done = True
+        if self.is_leader and rid in self._prefetch:
+            res = self.mgr.try_wait(self._prefetch[rid])
+            done = self._prefetch[rid] in res
+            if done:
+                del self._prefetch[rid]
+        return bool(self.comm.broadcast(done))
+
+    def cancel_prefetch(self, rid: str) -> None:
+        tid = self._prefetch.pop(rid, None)
+        if tid is not None and self.is_leader:
+            self.mgr.cancel(tid)
+
+    # ---- maintenance -------------------------------------------------------------------------
+    def reset(self) -> None:
+        if self.is_leader:
+            for p in self._pending_loads.values():
+                self.mgr.cancel(p.task_id)
+            self.mgr.reset()
+        self._pending_loads.clear()
+        self._stores.clear()
+        self._prefetch.clear()
+        if self.layer_counter is not None:
+            self.layer_counter.reset()
+        self.comm.barrier()
+
+    def shutdown(self) -> None:
+        if getattr(self, "_closed", False):
+            return
+        self._closed = True
+        if self.layer_counter is not None:
+            self.layer_counter.close()
+        if self.is_leader and self.mgr is not None:
+            try:
+                self.mgr.shutdown()
+            except Exception:  # noqa: BLE001
+                pass

@@ -1,0 +1,128 @@
+"""SGLang connector on CPU: single rank end to end, the layer-done counter, and
+the store protocol across two gloo ranks (reference: tests/test_sglang_connector.py,
+test_sglang_store_protocol.py, run_sglang_store_protocol_distributed.py)."""
+import os
+import struct
+import subprocess
+import sys
+import threading
+
+import numpy as np
+import torch
+
+from flexkv_b200 import CacheConfig, KVManager
+from flexkv_b200.integration.config import FlexKVConfig
+from flexkv_b200.integration.sglang.comm import FlexKVLayerDoneCounter
+from flexkv_b200.integration.sglang.connector import FlexKVConnector
+from flexkv_b200.models import KVShape, alloc_paged_cache, make_model_config
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+T = 4
+
+
+def test_single_rank_store_lookup_retrieve():
+    shape = KVShape("sg", 2, 2, 16, tokens_per_block=T)
+    cfg = FlexKVConfig()
+    cfg.model_config = make_model_config(shape)
+    cfg.cache_config = CacheConfig(tokens_per_block=T, num_cpu_blocks=32)
+    mgr = KVManager(cfg.model_config, cfg.cache_config, require_gpu=True)
+    kv, layout = alloc_paged_cache(shape, 64, "cpu", "sglang", fill="normal", seed=90)
+    mgr.register_gpu_tensors(kv, layout)
+    mgr.start(); mgr.wait_ready(30)
+    conn = FlexKVConnector(cfg, page_size=T, kv_manager=mgr, register=False)
+    try:
+        tok = list(range(300, 300 + 5 * T + 3))
+        pages = np.array([9, 2, 33, 4, 17])
+        slot = np.concatenate([np.repeat(pages, T) * T + np.tile(np.arange(T), 5), [0, 1, 2]])
+        assert conn.store_kv("r1", tok, slot) == 5 * T
+        assert conn.wait_store("r1") and conn.check_completed_stores() == []
+        saved = [t.clone() for t in kv]
+        for t in kv:
+            t.zero_()
+        assert conn.lookup_kv("r2", tok, num_computed_tokens=T) == 4 * T
+        dst = np.array([40, 41, 42, 43])
+        assert conn.retrieve_kv("r2", np.repeat(dst, T) * T + np.tile(np.arange(T), 4)) == 4 * T
+        for i in range(4):          # K buffers then V buffers
+            assert torch.equal(kv[i][dst], saved[i][pages[1:]])
+        assert conn.lookup_kv("r3", list(range(9000, 9016))) == 0
+        conn.reset()
+        assert conn.lookup_kv("r4", tok) == 0
+    finally:
+        conn.shutdown()
+
+
+def test_layer_done_counter_counts_one_unit_per_restore_per_layer():
+    c = FlexKVLayerDoneCounter(num_layers=3, num_counters=3)
+    try:
+        p = c.update_producer()
+        c.register_task(11, p)
+        c.register_task(12, p)                         # two restores feed the same forward pass
+        c.set_consumer(11)
+        fds = c.fds_per_counter()[p]
+
+        def worker():
+            for l in range(3):
+                for _ in range(2):
+                    os.write(fds[l], struct.pack("Q", 1))
+
+        th = threading.Thread(target=worker)
+        th.start()
+        for l in range(3):
+            c.wait_until(l, timeout=5)                 # returns only after both units of the layer arrived
+        th.join()
+        q = c.update_producer()
+        assert q != p
+        c.register_task(13, q)
+        c.rollback_prepared_transfer(13)
+        assert c.events[q].pending_transfers() == 0
+    finally:
+        c.close()
+
+
+WORKER = r"""
+import os, sys
+sys.path.insert(0, %(root)r)
+import numpy as np, torch, torch.distributed as dist
+from flexkv_b200 import CacheConfig, KVManager
+from flexkv_b200.integration.config import FlexKVConfig
+from flexkv_b200.integration.sglang.connector import FlexKVConnector
+from flexkv_b200.integration.sglang.comm import FlexKVComm
+from flexkv_b200.models import KVShape, alloc_paged_cache, make_model_config
+dist.init_process_group("gloo")
+rank = dist.get_rank()
+T = 4
+shape = KVShape("sg", 2, 2, 16, tokens_per_block=T)
+cfg = FlexKVConfig()
+cfg.model_config = make_model_config(shape)
+cfg.cache_config = CacheConfig(tokens_per_block=T, num_cpu_blocks=32)
+mgr = None
+if rank == 0:
+    mgr = KVManager(cfg.model_config, cfg.cache_config, require_gpu=True)
+    kv, layout = alloc_paged_cache(shape, 64, "cpu", "sglang", fill="normal", seed=1)
+    mgr.register_gpu_tensors(kv, layout)
+    mgr.start(); mgr.wait_ready(30)
+conn = FlexKVConnector(cfg, page_size=T, comm=FlexKVComm(tp_size=2), kv_manager=mgr, register=False)
+tok = list(range(5 * T))
+slot = np.repeat(np.arange(5), T) * T + np.tile(np.arange(T), 5)
+moved = conn.store_kv("a", tok, slot)            # decided on the leader, identical on both ranks
+ok = conn.wait_store("a")
+hit = conn.lookup_kv("b", tok, num_computed_tokens=T)
+got = conn.retrieve_kv("b", slot[T:] + 100)
+assert (moved, ok, hit, got) == (5 * T, True, 4 * T, 4 * T), (rank, moved, ok, hit, got)
+assert conn.comm.all_reduce_min(10 + rank) == 10
+conn.reset()
+conn.shutdown()
+dist.barrier()
+dist.destroy_process_group()
+sys.stdout.write("rank%d-ok\n" % rank); sys.stdout.flush()
+"""
+
+
+def test_store_protocol_across_two_gloo_ranks(tmp_path):
+    script = tmp_path / "w.py"
+    script.write_text(WORKER % {"root": ROOT})
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+           "127.0.0.1", "--master-port", "29621", str(script)]
+    p = subprocess.run(cmd, capture_output=True, text=True, timeout=180, env=dict(os.environ, PYTHONPATH=ROOT))
+    assert p.returncode == 0, p.stdout[-1500:] + p.stderr[-1500:]
+    assert "rank0-ok" in p.stdout and "rank1-ok" in p.stdout
