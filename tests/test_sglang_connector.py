@@ -120,7 +120,7 @@ sys.stdout.write("rank%d-ok\n" % rank); sys.stdout.flush()
 
 def test_store_protocol_across_two_gloo_ranks(tmp_path):
     script = tmp_path / "w.py"
-    script.write_text(WORKER % {"root": ROOT})
+    script.write_text(WORKER.replace("%(root)r", repr(ROOT)))
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
            "127.0.0.1", "--master-port", "29621", str(script)]
     p = subprocess.run(cmd, capture_output=True, text=True, timeout=180, env=dict(os.environ, PYTHONPATH=ROOT))
