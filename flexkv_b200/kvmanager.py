@@ -57,7 +57,10 @@ class KVManager:
             # dp client 0 of instance 0 hosts the server unless one is launched externally
             if dp_client_id == 0 and env.instance_id == 0 and env.server_launch_mode != "external":
                 self.server_handle = KVServer.create_server(model_config, cache_config, self.server_recv_port,
-                                                            gpu_register_port=gpu_register_port)
+                                                            gpu_register_port=gpu_register_port,
+                                                            mode=env.server_launch_mode if env.server_launch_mode
+                                                            in ("thread", "process") else "thread",
+                                                            require_gpu=require_gpu)
             self.dp_client = KVDPClient(self.server_recv_port, model_config, dp_client_id)
         else:
             from .kvtask import KVTaskEngine

@@ -137,7 +137,12 @@ class TransferEngine:
                     progress = True
                     continue
                 key = WorkerKey(op.dp_client_id, 0)
-                w = self._workers.get((key, op.transfer_type)) or self._workers.get((WorkerKey(0, 0), op.transfer_type))
+                w = self._workers.get((key, op.transfer_type))
+                if w is None and op.transfer_type not in (TransferType.H2D, TransferType.D2H, TransferType.LAYERWISE,
+                                                          TransferType.PEERD2D, TransferType.DISK2D,
+                                                          TransferType.D2DISK):
+                    # tier-to-tier workers (SSD, remote) are shared by every data-parallel client
+                    w = self._workers.get((WorkerKey(0, 0), op.transfer_type))
                 if w is None:
                     flexkv_logger.error("no worker for %s (dp client %d)", op.transfer_type.value, op.dp_client_id)
                     graph.mark_completed(op.op_id, False)
