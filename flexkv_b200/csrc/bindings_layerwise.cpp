@@ -7,6 +7,7 @@
 #include "kernels/layer_sync.h"
 #include "layerwise_group.h"
 #include "peer_copier.h"
+#include "gds_engine.h"
 
 namespace py = pybind11;
 using namespace fkv;
@@ -89,6 +90,29 @@ void init_layerwise_bindings(py::module_& m) {
            })
       .def("can_access", &PeerCopier::can_access)
       .def_property_readonly("num_ranks", &PeerCopier::num_ranks);
+
+  py::class_<GdsEngine>(m, "GdsEngine")
+      .def(py::init<const std::vector<std::vector<std::string>>&, int64_t, int64_t, int>(), py::arg("files"),
+           py::arg("block_bytes"), py::arg("blocks_per_file"), py::arg("num_threads") = 8)
+      .def_property_readonly("available", &GdsEngine::available)
+      .def_property_readonly("why_unavailable", &GdsEngine::why_unavailable)
+      .def("register_buffer", &GdsEngine::register_buffer)
+      .def("deregister_buffer", &GdsEngine::deregister_buffer)
+      .def("transfer", [](GdsEngine& e, uint64_t dev_base, I64Array dev_offsets, I64Array ssd_blocks, bool is_read,
+                          int64_t slice_off, int64_t slice_bytes) {
+             if (dev_offsets.size() != ssd_blocks.size()) throw std::invalid_argument("arrays differ in size");
+             const int64_t n = (int64_t)ssd_blocks.size();
+             py::array_t<uint8_t> ok((py::ssize_t)n);
+             const int64_t* dp = dev_offsets.data();
+             const int64_t* sp = ssd_blocks.data();
+             uint8_t* okp = ok.mutable_data();
+             int64_t nfail;
+             {
+               py::gil_scoped_release rel;
+               nfail = e.transfer(dev_base, dp, sp, n, is_read, slice_off, slice_bytes, okp);
+             }
+             return py::make_tuple(nfail, ok);
+           });
 
   m.def("layer_stub", [](uint64_t flag_ptr, uint32_t epoch, uint64_t busy_ns, uint64_t budget_ns, uint64_t status_ptr,
                          uint64_t t_start_ptr, int num_ctas, uint64_t stream) {

@@ -345,6 +345,118 @@ class SsdWorker(TransferWorker):
                          error="" if nfail == 0 else f"{nfail} block(s) failed")
 
 
+class GdsWorker(TransferWorker):
+    """DISK2D / D2DISK: SSD blocks move to or from the paged GPU cache without
+    passing through the host pool. With GPUDirect Storage (cuFile) a block is read
+    straight into a device bounce buffer; otherwise it is staged through a small
+    pinned buffer with O_DIRECT io_uring reads. Either way the scatter into the
+    paged layout is the ordinary copy kernel with the bounce buffer as its flat side
+    (flexkv/transfer/worker.py:1948-2244; csrc/gds/gds_manager.cpp:596-795)."""
+
+    def __init__(self, storage, model_config: ModelConfig, key: WorkerKey, to_gpu: bool, slots: int = 64) -> None:
+        super().__init__()
+        import torch
+        self._torch = torch
+        self.to_gpu = to_gpu
+        self.name = "disk2d" if to_gpu else "d2disk"
+        self.storage = storage
+        self.regs = [storage.gpu_regs[key][r] for r in sorted(storage.gpu_regs[key])]
+        host = storage.host
+        self.shared = model_config.use_mla or model_config.num_kv_heads == 1
+        n = 1 if self.shared else model_config.effective_tp_size
+        self.slice_bytes = host.block_bytes // n
+        self.layer_stride, self.kv_stride = host.layer_stride // n, host.kv_stride // n
+        self.slots = slots
+        ssd = storage.ssd
+        self.gds = _native.C.GdsEngine(ssd.files, ssd.block_bytes, ssd.blocks_per_file,
+                                       int(os.environ.get("FLEXKV_GDS_THREADS", 8)))
+        self.direct = bool(self.gds.available) and os.environ.get("FLEXKV_GDS_FORCE_STAGED", "0") != "1"
+        if not self.direct:
+            flexkv_logger.info("GDS direct path unavailable (%s): staging through pinned memory",
+                               self.gds.why_unavailable or "disabled")
+        self.bounce, self.streams, self.status = {}, {}, {}
+        for reg in self.regs:
+            dev = f"cuda:{reg.device_id}"
+            self.bounce[reg.device_id] = torch.empty(slots * self.slice_bytes, dtype=torch.uint8, device=dev)
+            self.streams[reg.device_id] = torch.cuda.Stream(device=reg.device_id)
+            self.status[reg.device_id] = torch.zeros(8, dtype=torch.int32, device=dev)
+            if self.direct:
+                self.gds.register_buffer(self.bounce[reg.device_id].data_ptr(), slots * self.slice_bytes)
+        self.stage = None if self.direct else torch.empty(slots * host.block_bytes, dtype=torch.uint8).pin_memory()
+        self.slot_ids = torch.arange(slots, dtype=torch.int64).pin_memory()
+
+    def _scatter(self, reg, gpu_ids, n: int, base_ptr: int, block_stride: int, off: int, h2d: bool) -> int:
+        torch = self._torch
+        g = torch.from_numpy(np.ascontiguousarray(gpu_ids, dtype=np.int64)).pin_memory()
+        params = dict(gpu_ptrs=[int(p) for p in reg.ptrs], idx_layer_mul=reg.idx_layer_mul, idx_kv_mul=reg.idx_kv_mul,
+                      g_layer_stride=reg.layer_stride, g_kv_stride=reg.kv_stride, g_block_stride=reg.block_stride,
+                      cpu_base=base_ptr, c_layer_stride=self.layer_stride, c_kv_stride=self.kv_stride,
+                      c_block_stride=block_stride, c_off=off, gpu_blocks_ptr=g.data_ptr(),
+                      cpu_blocks_ptr=self.slot_ids.data_ptr(), num_pairs=n, layer_start=0, num_layers=reg.num_layers,
+                      kv_dim=reg.kv_dim, chunk_bytes=reg.chunk_bytes, gpu_num_blocks=reg.num_blocks,
+                      cpu_num_blocks=self.slots, status_ptr=self.status[reg.device_id].data_ptr(), h2d=int(h2d))
+        st = self.streams[reg.device_id]
+        with torch.cuda.device(reg.device_id):
+            _native.C.kv_copy(params, 16, 16384, 0, st.cuda_stream)
+            st.synchronize()
+        words = self.status[reg.device_id].tolist()
+        bad = sum(1 << b for b, w in enumerate(words) if w)
+        if bad:
+            self.status[reg.device_id].zero_()
+        return bad
+
+    def execute(self, op: TransferOp) -> OpOutcome:
+        ssd_ids, gpu_ids = (op.src_block_ids, op.dst_block_ids) if self.to_gpu else (op.dst_block_ids, op.src_block_ids)
+        if ssd_ids.size != gpu_ids.size:
+            return OpOutcome(False, error="unbound GPU blocks")
+        st = self.storage
+        failed = np.zeros(ssd_ids.size, dtype=bool)
+        status = 0
+        for lo in range(0, int(ssd_ids.size), self.slots):
+            s_chunk = np.ascontiguousarray(ssd_ids[lo:lo + self.slots], dtype=np.int64)
+            g_chunk = gpu_ids[lo:lo + self.slots]
+            n = int(s_chunk.size)
+            if not self.direct:
+                slot_ids = np.arange(n, dtype=np.int64)
+                if self.to_gpu:
+                    lay = dict(st.ssd_layout_dict(), cpu_block_stride=st.host.block_bytes)
+                    nfail, ok = st.ssd.engine.transfer(self.stage.data_ptr(), slot_ids, s_chunk, True, lay, 0,
+                                                       lay["num_layers"])
+                    failed[lo:lo + n] |= ~ok.astype(bool)
+            for i, reg in enumerate(self.regs):
+                if self.shared and not self.to_gpu and i > 0:
+                    break
+                off = 0 if self.shared else i * self.slice_bytes
+                if self.direct:
+                    offs = np.arange(n, dtype=np.int64) * self.slice_bytes
+                    base = self.bounce[reg.device_id].data_ptr()
+                    if self.to_gpu:
+                        nfail, ok = self.gds.transfer(base, offs, s_chunk, True, off, self.slice_bytes)
+                        failed[lo:lo + n] |= ~ok.astype(bool)
+                        status |= self._scatter(reg, g_chunk, n, base, self.slice_bytes, 0, True)
+                    else:
+                        status |= self._scatter(reg, g_chunk, n, base, self.slice_bytes, 0, False)
+                        nfail, ok = self.gds.transfer(base, offs, s_chunk, False, off, self.slice_bytes)
+                        failed[lo:lo + n] |= ~ok.astype(bool)
+                else:
+                    status |= self._scatter(reg, g_chunk, n, self.stage.data_ptr(), st.host.block_bytes, off,
+                                            self.to_gpu)
+            if not self.direct and not self.to_gpu:
+                lay = dict(st.ssd_layout_dict(), cpu_block_stride=st.host.block_bytes)
+                nfail, ok = st.ssd.engine.transfer(self.stage.data_ptr(), np.arange(n, dtype=np.int64), s_chunk, False,
+                                                   lay, 0, lay["num_layers"])
+                failed[lo:lo + n] |= ~ok.astype(bool)
+        good = status == 0 and not failed.any()
+        return OpOutcome(good, block_results=tuple(bool(x) for x in ~failed),
+                         num_bytes=int((~failed).sum()) * st.ssd.block_bytes,
+                         error="" if good else f"gds: status 0x{status:x}, {int(failed.sum())} block(s) failed")
+
+    def close(self) -> None:
+        if self.direct:
+            for t in self.bounce.values():
+                self.gds.deregister_buffer(t.data_ptr())
+
+
 def build_workers(storage, model_config: ModelConfig, cache_config: CacheConfig
                   ) -> Dict[Tuple[WorkerKey, TransferType], TransferWorker]:
     workers: Dict[Tuple[WorkerKey, TransferType], TransferWorker] = {}
@@ -376,6 +488,10 @@ def build_workers(storage, model_config: ModelConfig, cache_config: CacheConfig
         peer = PeerD2DWorker(storage, model_config)
         for k in real:
             workers[(k, TransferType.PEERD2D)] = peer
+    if storage.ssd is not None and cache_config.enable_gds and storage.host.quant == "none":
+        for k in real:
+            workers[(k, TransferType.DISK2D)] = GdsWorker(storage, model_config, k, True)
+            workers[(k, TransferType.D2DISK)] = GdsWorker(storage, model_config, k, False)
     if storage.ssd is not None:
         k0 = WorkerKey(0, 0)
         workers[(k0, TransferType.DISK2H)] = SsdWorker(storage, True)
