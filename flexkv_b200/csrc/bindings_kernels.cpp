@@ -9,6 +9,7 @@
 #include "kernels/kv_copy.h"
 #include "kernels/kv_fanout.h"
 #include "kernels/kv_quant.h"
+#include "kernels/kv_compress.h"
 #include "ipc.h"
 
 namespace py = pybind11;
@@ -95,6 +96,18 @@ void init_kernel_bindings(py::module_& m) {
     throw_on(launch_kv_quant_fp8(p, num_ctas, (cudaStream_t)(uintptr_t)stream), "kv_quant_fp8 launch");
   }, py::arg("params"), py::arg("num_ctas") = 32, py::arg("stream") = (uint64_t)0);
   m.def("fp8_packed_chunk_bytes", &fp8_packed_chunk_bytes);
+
+  m.def("kv_compress_bf16", [](py::dict params, uint64_t size_table_ptr, int layers_total, int num_ctas,
+                               uint64_t stream) {
+    KvCopyParams p = kv_params_from_dict(params);
+    throw_on(launch_kv_compress_bf16(p, (uint32_t*)(uintptr_t)size_table_ptr, layers_total, num_ctas,
+                                     (cudaStream_t)(uintptr_t)stream), "kv_compress_bf16 launch");
+  }, py::arg("params"), py::arg("size_table_ptr"), py::arg("layers_total"), py::arg("num_ctas") = 32,
+     py::arg("stream") = (uint64_t)0);
+  m.def("compress_chunk_slot_bytes", &compress_chunk_slot_bytes);
+  m.def("compress_tiles_per_chunk", &compress_tiles_per_chunk);
+  m.attr("COMPRESS_TILE_SLOT") = kCompressTileSlot;
+  m.attr("COMPRESS_TILE_ELEMS") = kCompressTileElems;
 
   m.def("ipc_export", [](uint64_t ptr) {
     IpcExport e = ipc_export(ptr);

@@ -28,8 +28,16 @@ from .gpu_layout import GpuRegistration
 QUANT_GROUP = 128     # values per fp32 scale of the block-scaled fp8 host format
 
 
+COMPRESS_TILE_ELEMS = 8192
+COMPRESS_TILE_SLOT = 2 * COMPRESS_TILE_ELEMS + 128
+
+
 def packed_chunk_bytes(chunk_elems: int, quant: str, itemsize: int) -> int:
     """Bytes one chunk occupies on the host tier."""
+    if quant == "bf16_xp":
+        if chunk_elems % 1024:
+            raise ValueError("the exponent-packing codec needs chunk elements divisible by 1024")
+        return (chunk_elems + COMPRESS_TILE_ELEMS - 1) // COMPRESS_TILE_ELEMS * COMPRESS_TILE_SLOT
     if quant == "fp8_e4m3":
         if chunk_elems % QUANT_GROUP:
             raise ValueError("fp8 offload needs chunk elements divisible by 128")
@@ -46,7 +54,9 @@ class HostPool:
     kv_stride: int
     chunk_bytes: int            # bytes of one (layer, kv) chunk holding every rank's heads
     num_blocks: int
-    quant: str = "none"
+    quant: str = "none"         # host codec: none | fp8_e4m3 (lossy, block-scaled) | bf16_xp (lossless)
+    size_table: Any = None      # bf16_xp: pinned int32 tensor, one entry per (block, layer, kv, tile)
+    tiles_per_chunk: int = 1
 
     @property
     def base(self) -> int:
@@ -77,6 +87,7 @@ class StorageEngine:
         self.gpu_regs: Dict[WorkerKey, Dict[int, GpuRegistration]] = {}
         self.host: Optional[HostPool] = None
         self.ssd: Optional[SsdPool] = None
+        self.ssd_size_table: Optional[np.ndarray] = None
         self._cuda_register = torch.cuda.is_available() if cuda_register is None else cuda_register
         self._numa_node = numa_node
         if cache_config.enable_cpu:
@@ -102,7 +113,10 @@ class StorageEngine:
             return lay.block_bytes_flat, 0, 0, 0, lay
         lay = KVCacheLayout(self.env.cpu_layout_type, layers, c.num_cpu_blocks, T, m.num_kv_heads, m.head_size,
                             is_mla=m.use_mla, kv_dim_override=m.kv_dim)
-        chunk = packed_chunk_bytes(lay.get_chunk_size(), c.offload_quant, m.dtype.itemsize)
+        self._codec = self._choose_codec(lay)
+        slices = 1 if (m.use_mla or m.num_kv_heads == 1) else m.effective_tp_size
+        # every rank's slice of a chunk is packed on its own, so the host chunk is `slices` packed slices
+        chunk = slices * packed_chunk_bytes(lay.get_chunk_size() // slices, self._codec, m.dtype.itemsize)
         if lay.type == KVCacheLayoutType.BLOCKFIRST:
             kv_stride, layer_stride = chunk, lay.kv_dim * chunk
             block_bytes = layers * layer_stride
@@ -115,6 +129,31 @@ class StorageEngine:
             block_bytes = lay.kv_dim * chunk
             layer_stride = c.num_cpu_blocks * block_bytes
         return block_bytes, layer_stride, kv_stride, chunk, lay
+
+    def _choose_codec(self, lay: KVCacheLayout) -> str:
+        """fp8 when asked for; else the lossless codec when compression is on and the cache qualifies
+        (bf16, BLOCKFIRST host layout, chunk elements % 1024 == 0, no layerwise restore: the layerwise
+        kernel consumes raw host blocks — the reference applies the same all-or-nothing rule,
+        flexkv/transfer/compression/ans/ans_utils.py:51-118)."""
+        m, c = self.model_config, self.cache_config
+        if c.offload_quant != "none":
+            return c.offload_quant
+        if not (c.enable_compression or self.env.enable_compression):
+            return "none"
+        slices = 1 if (m.use_mla or m.num_kv_heads == 1) else m.effective_tp_size
+        why = None
+        if m.dtype != torch.bfloat16:
+            why = f"dtype {m.dtype} is not bf16"
+        elif lay.type != KVCacheLayoutType.BLOCKFIRST:
+            why = "host layout is not BLOCKFIRST"
+        elif (lay.get_chunk_size() // slices) % 1024:
+            why = "chunk elements per rank are not a multiple of 1024"
+        elif self.env.enable_layerwise_transfer:
+            why = "layerwise restore is enabled"
+        if why:
+            flexkv_logger.warning("compression requested but refused: %s; every tier runs uncompressed", why)
+            return "none"
+        return "bf16_xp"
 
     def _alloc_host(self) -> None:
         c = self.cache_config
@@ -132,7 +171,15 @@ class StorageEngine:
         except RuntimeError as e:
             raise RuntimeError(f"host pool of {total / 2**30:.1f} GiB could not be allocated: {e}") from e
         self.host = HostPool(region, lay, block_bytes, layer_stride, kv_stride, chunk, c.num_cpu_blocks,
-                             c.offload_quant)
+                             getattr(self, "_codec", c.offload_quant))
+        if self.host.quant == "bf16_xp":
+            m = self.model_config
+            slices = 1 if (m.use_mla or m.num_kv_heads == 1) else m.effective_tp_size
+            tpc = (lay.get_chunk_size() // slices + COMPRESS_TILE_ELEMS - 1) // COMPRESS_TILE_ELEMS
+            self.host.tiles_per_chunk = tpc
+            n = c.num_cpu_blocks * m.num_layers_per_pp_stage * lay.kv_dim * tpc * slices
+            table = torch.zeros(n, dtype=torch.int32)
+            self.host.size_table = table.pin_memory() if self._cuda_register else table
         flexkv_logger.info("host pool: %d blocks x %d B = %.2f GiB (hugepage=%s, registered=%s, layout=%s)",
                            c.num_cpu_blocks, block_bytes, total / 2**30, region.hugepage, region.registered,
                            lay.type.value)
@@ -142,7 +189,8 @@ class StorageEngine:
         if lay.is_multi_group or lay.type == KVCacheLayoutType.BLOCKFIRST:
             return c.num_cpu_blocks * block_bytes
         return self.model_config.num_layers_per_pp_stage * lay.kv_dim * c.num_cpu_blocks * \
-            packed_chunk_bytes(lay.get_chunk_size(), c.offload_quant, self.model_config.dtype.itemsize)
+            packed_chunk_bytes(lay.get_chunk_size(), getattr(self, "_codec", c.offload_quant),
+                               self.model_config.dtype.itemsize)
 
     def host_block_stride(self) -> int:
         return self.host.block_bytes
@@ -180,6 +228,9 @@ class StorageEngine:
                                        iouring_entries=self.env.iouring_entries,
                                        num_threads=self.env.ssd_io_threads)
         self.ssd = SsdPool(engine, files, block_bytes, c.num_ssd_blocks, blocks_per_file)
+        if self.host.size_table is not None:
+            per_block = self.host.size_table.numel() // self.host.num_blocks
+            self.ssd_size_table = np.zeros((c.num_ssd_blocks, per_block), dtype=np.int32)
         flexkv_logger.info("ssd pool: %d blocks x %d B over %d dir(s), %d file(s)/dir, io_uring=%s direct=%s",
                            c.num_ssd_blocks, block_bytes, ndev, files_per_dev, engine.using_iouring,
                            engine.direct_available)

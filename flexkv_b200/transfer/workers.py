@@ -214,8 +214,10 @@ class HostEmulatedGpuWorker(TransferWorker):
 
 
 class QuantGpuHostWorker(TransferWorker):
-    """H2D / D2H for host pools stored as block-scaled fp8: the copy kernel packs on
-    the way out and unpacks on the way in (one launch per rank and op)."""
+    """H2D / D2H for host pools kept in a packed form: block-scaled fp8 (lossy) or
+    the lossless exponent-packing codec. The copy kernel packs on the way out and
+    unpacks on the way in, one launch per rank and op
+    (reference strategy plug-in point: flexkv/transfer/compression/common/strategy.py:13-51)."""
 
     def __init__(self, storage, model_config: ModelConfig, key: WorkerKey, h2d: bool) -> None:
         super().__init__()
@@ -225,7 +227,9 @@ class QuantGpuHostWorker(TransferWorker):
         self.regs = [storage.gpu_regs[key][r] for r in sorted(storage.gpu_regs[key])]
         host = storage.host
         if host.layout.type != KVCacheLayoutType.BLOCKFIRST:
-            raise ValueError("fp8 offload uses the BLOCKFIRST host layout")
+            raise ValueError("packed host pools use the BLOCKFIRST host layout")
+        self.codec = host.quant
+        self.layers_total = self.regs[0].num_layers
         self.shared = model_config.use_mla or model_config.num_kv_heads == 1
         n = 1 if self.shared else model_config.effective_tp_size
         self.host = host
@@ -264,7 +268,15 @@ class QuantGpuHostWorker(TransferWorker):
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             with torch.cuda.device(reg.device_id):
                 e0.record(st)
-                _native.C.kv_quant_fp8(params, self.num_ctas, st.cuda_stream)
+                if self.codec == "bf16_xp":
+                    # size table layout [block][rank][layer][kv][tile]: a rank sees it as a table of
+                    # R*L "layers" and starts r*L*K*tiles entries in
+                    R = 1 if self.shared else len(self.regs)
+                    r_off = 0 if self.shared else i * self.layers_total * reg.kv_dim * self.host.tiles_per_chunk
+                    _native.C.kv_compress_bf16(params, self.host.size_table.data_ptr() + 4 * r_off,
+                                               R * self.layers_total, self.num_ctas, st.cuda_stream)
+                else:
+                    _native.C.kv_quant_fp8(params, self.num_ctas, st.cuda_stream)
                 e1.record(st)
             evs.append((e0, e1, reg.device_id))
             nbytes += int(cpu.size) * nl * reg.kv_dim * reg.chunk_bytes
@@ -331,6 +343,19 @@ class SsdWorker(TransferWorker):
         self.is_read = is_read
         self.name = "disk2h" if is_read else "h2disk"
 
+    def _move_size_tables(self, cpu: np.ndarray, ssd: np.ndarray, ok: np.ndarray) -> None:
+        """Packed pools: a block's tile sizes travel with it between the host and SSD tables
+        (flexkv/transfer/compression/ans/ans_utils.py:215-218)."""
+        st = self.storage
+        if st.ssd_size_table is None:
+            return
+        good = ok.astype(bool)
+        ht = st.host.size_table.view(st.host.num_blocks, -1).numpy()
+        if self.is_read:
+            ht[cpu[good]] = st.ssd_size_table[ssd[good]]
+        else:
+            st.ssd_size_table[ssd[good]] = ht[cpu[good]]
+
     def execute(self, op: TransferOp) -> OpOutcome:
         st = self.storage
         if self.is_read:
@@ -340,6 +365,7 @@ class SsdWorker(TransferWorker):
         lay = st.ssd_layout_dict()
         nl = lay["num_layers"] if op.num_layers < 0 else op.num_layers
         nfail, ok = st.ssd.engine.transfer(st.host.base, cpu, ssd, self.is_read, lay, op.layer_start, nl)
+        self._move_size_tables(cpu, ssd, ok)
         return OpOutcome(nfail == 0, block_results=tuple(bool(x) for x in ok),
                          num_bytes=int((len(ok) - nfail)) * st.ssd.block_bytes,
                          error="" if nfail == 0 else f"{nfail} block(s) failed")

@@ -1,0 +1,129 @@
+"""Lossless exponent-packing codec: packed bytes equal a PyTorch reference of the
+format, every bit pattern round-trips, sizes land in the table, ratio on N(0,1)."""
+import numpy as np
+import pytest
+import torch
+
+from flexkv_b200.models import KVShape, alloc_paged_cache
+from flexkv_b200.ops.kv_compress import (TILE_ELEMS, TILE_SLOT, chunk_slot_bytes, kv_compress,
+                                         reference_compress_tile, size_table_entries, tiles_per_chunk)
+from flexkv_b200.ops.kv_copy import HostSide, decode_status, new_status
+from flexkv_b200.storage.gpu_layout import register_tensors
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("shape", [KVShape("c1", 2, 8, 128, tokens_per_block=16),                 # 16384-element chunks
+                                   KVShape("c2", 2, 1, 576, use_mla=True, tokens_per_block=64),   # 36864: ragged tile
+                                   KVShape("c3", 3, 1, 128, tokens_per_block=8)])                 # 1024-element chunks
+def test_roundtrip_is_bit_exact_and_bytes_match_reference(shape):
+    dev = torch.device("cuda:0")
+    NB, n = 24, 13
+    kv, layout = alloc_paged_cache(shape, NB, dev, "vllm", fill="normal", seed=71)
+    # adversarial content: zeros, denormals, huge, NaN/Inf patterns, and a constant group (w = 0)
+    flat = kv[0].view(-1).view(torch.int16)
+    flat[:128] = 0
+    flat[128:256] = torch.randint(-32768, 32767, (128,), dtype=torch.int16, device=dev)
+    flat[256:384] = 0x3F80                      # all 1.0
+    flat[384:388] = torch.tensor([0x7F80, -128, 0x7FC0, 1], dtype=torch.int16, device=dev)   # inf, -inf, nan, denormal
+    reg = register_tensors(kv, layout)
+    E = reg.chunk_bytes // 2
+    L, K, tpc = shape.num_layers, shape.kv_dim, tiles_per_chunk(E)
+    slot = chunk_slot_bytes(E)
+    pool = torch.zeros(NB, L, K, slot, dtype=torch.uint8).pin_memory()
+    host = HostSide(pool.data_ptr(), K * slot, slot, L * K * slot, NB)
+    table = torch.zeros(size_table_entries(NB, L, K, E), dtype=torch.int32).pin_memory()
+    rng = np.random.default_rng(5)
+    g = np.concatenate([[0], rng.permutation(np.arange(1, NB))[:n - 1]]).astype(np.int64)
+    c = rng.permutation(NB)[:n].astype(np.int64)
+    status = new_status(dev)
+    keep = kv_compress(reg, host, table, g, c, h2d=False, num_ctas=5, status=status)
+    torch.cuda.synchronize()
+    assert decode_status(status) == 0
+    tv = table.view(NB, L, K, tpc)
+    total_packed, total_raw = 0, 0
+    for i in (0, 1, n - 1):                                  # byte-level check of a few blocks, all layers
+        for l in range(L):
+            for k in range(K):
+                x = (kv[l][int(g[i])] if shape.use_mla else kv[l][k][int(g[i])]).reshape(-1).cpu()
+                for t in range(tpc):
+                    tile = x[t * TILE_ELEMS:(t + 1) * TILE_ELEMS]
+                    want = reference_compress_tile(tile)
+                    size = int(tv[int(c[i]), l, k, t])
+                    assert size == want.numel(), (i, l, k, t, size, want.numel())
+                    got = pool[int(c[i]), l, k, t * TILE_SLOT:t * TILE_SLOT + size]
+                    assert torch.equal(got, want), (i, l, k, t)
+    for i in range(n):
+        total_packed += int(tv[int(c[i])].sum())
+        total_raw += L * K * E * 2
+    assert total_packed < 0.80 * total_raw                   # N(0,1) packs to about 0.76
+    saved = [t.clone() for t in kv]
+    for t in kv:
+        t.zero_()
+    g2 = rng.permutation(NB)[:n].astype(np.int64)
+    keep += kv_compress(reg, host, table, g2, c, h2d=True, num_ctas=3, status=status)
+    torch.cuda.synchronize()
+    assert decode_status(status) == 0
+    gi, g2i = torch.from_numpy(g).to(dev), torch.from_numpy(g2).to(dev)
+    for l in range(L):
+        a = saved[l][gi] if shape.use_mla else saved[l][:, gi]
+        b = kv[l][g2i] if shape.use_mla else kv[l][:, g2i]
+        assert torch.equal(a.view(torch.int16), b.view(torch.int16))
+
+
+def test_unwritten_slot_is_reported_not_decoded():
+    dev = torch.device("cuda:0")
+    shape = KVShape("c4", 2, 8, 128, tokens_per_block=16)
+    kv, layout = alloc_paged_cache(shape, 8, dev, "vllm", fill="zeros")
+    reg = register_tensors(kv, layout)
+    E = reg.chunk_bytes // 2
+    slot = chunk_slot_bytes(E)
+    pool = torch.zeros(8, 2, 2, slot, dtype=torch.uint8).pin_memory()
+    host = HostSide(pool.data_ptr(), 2 * slot, slot, 4 * slot, 8)
+    table = torch.zeros(size_table_entries(8, 2, 2, E), dtype=torch.int32).pin_memory()
+    status = new_status(dev)
+    ids = np.array([1, 2], dtype=np.int64)
+    kv_compress(reg, host, table, ids, ids, h2d=True, status=status)        # nothing was ever compressed there
+    torch.cuda.synchronize()
+    assert decode_status(status) == 16
+
+
+def test_kvmanager_with_lossless_codec_host_and_ssd(tmp_path):
+    from flexkv_b200 import CacheConfig, KVManager
+    from flexkv_b200.models import make_model_config
+    dev = torch.device("cuda:0")
+    shape = KVShape("c5", 3, 8, 128, tokens_per_block=16)
+    T, NB, n = 16, 64, 18
+    kv, layout = alloc_paged_cache(shape, NB, dev, "vllm", fill="normal", seed=72)
+    mgr = KVManager(make_model_config(shape), CacheConfig(tokens_per_block=T, num_cpu_blocks=40, enable_compression=True,
+                                                          enable_ssd=True, num_ssd_blocks=96,
+                                                          ssd_cache_dir=str(tmp_path)))
+    mgr.register_gpu_tensors(kv, layout)
+    mgr.start()
+    mgr.wait_ready(120)
+    try:
+        host = mgr.transfer_manager.storage.host
+        assert host.quant == "bf16_xp" and host.size_table is not None
+        rng = np.random.default_rng(9)
+        tok = rng.integers(0, 1000, size=n * T, dtype=np.int64)
+        src = rng.permutation(NB)[:n].astype(np.int64)
+        slot = np.repeat(src, T) * T + np.tile(np.arange(T), n)
+        tid = mgr.put_async(tok, slot)
+        assert mgr.wait(tid, completely=True)[tid].status.value == "success"
+        saved = [t.clone() for t in kv]
+        for rounds, clear in ((0, False), (1, True)):       # host hit, then SSD hit after dropping the host tier
+            if clear:
+                mgr._clear_cpu_cache()
+                host.size_table.zero_()                      # sizes must come back from the SSD table
+            for t in kv:
+                t.zero_()
+            dst = rng.permutation(NB)[:n].astype(np.int64)
+            tid = mgr.get_async(tok, np.repeat(dst, T) * T + np.tile(np.arange(T), n))
+            r = mgr.wait(tid)[tid]
+            assert r.status.value == "success" and int(r.return_mask.sum()) == n * T
+            torch.cuda.synchronize()
+            si, di = torch.from_numpy(src).to(dev), torch.from_numpy(dst).to(dev)
+            for l in range(shape.num_layers):
+                assert torch.equal(kv[l][:, di].view(torch.int16), saved[l][:, si].view(torch.int16))
+    finally:
+        mgr.shutdown()
