@@ -371,6 +371,43 @@ class SsdWorker(TransferWorker):
                          error="" if nfail == 0 else f"{nfail} block(s) failed")
 
 
+_GDS_PROBE: Optional[Tuple[bool, str]] = None
+
+
+def gds_probe(timeout_s: float = 30.0) -> Tuple[bool, str]:
+    """Opens the cuFile driver in a child process first: on hosts without a working
+    GPUDirect Storage stack the driver open may block for a long time, and a child can
+    be abandoned where a call in this process cannot."""
+    global _GDS_PROBE
+    if _GDS_PROBE is not None:
+        return _GDS_PROBE
+    import subprocess
+    import sys
+    import tempfile
+    code = ("import sys, os, tempfile\n"
+            "sys.path.insert(0, %r)\n"
+            "from flexkv_b200 import _native\n"
+            "d = tempfile.mkdtemp()\n"
+            "p = os.path.join(d, 'probe.bin')\n"
+            "open(p, 'wb').truncate(1 << 20)\n"
+            "e = _native.C.GdsEngine([[p]], 1 << 20, 1, 1)\n"
+            "print('GDS_OK' if e.available else 'GDS_NO ' + e.why_unavailable)\n"
+            ) % os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    try:
+        out = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=timeout_s,
+                             cwd=tempfile.gettempdir())
+        if "GDS_OK" in out.stdout:
+            _GDS_PROBE = (True, "")
+        else:
+            tail = (out.stdout.strip().splitlines() or out.stderr.strip().splitlines() or ["no output"])[-1]
+            _GDS_PROBE = (False, tail[:200])
+    except subprocess.TimeoutExpired:
+        _GDS_PROBE = (False, f"cuFile driver open did not return within {timeout_s:.0f} s")
+    except OSError as e:
+        _GDS_PROBE = (False, str(e))
+    return _GDS_PROBE
+
+
 class GdsWorker(TransferWorker):
     """DISK2D / D2DISK: SSD blocks move to or from the paged GPU cache without
     passing through the host pool. With GPUDirect Storage (cuFile) a block is read
@@ -394,12 +431,18 @@ class GdsWorker(TransferWorker):
         self.layer_stride, self.kv_stride = host.layer_stride // n, host.kv_stride // n
         self.slots = slots
         ssd = storage.ssd
-        self.gds = _native.C.GdsEngine(ssd.files, ssd.block_bytes, ssd.blocks_per_file,
-                                       int(os.environ.get("FLEXKV_GDS_THREADS", 8)))
-        self.direct = bool(self.gds.available) and os.environ.get("FLEXKV_GDS_FORCE_STAGED", "0") != "1"
+        self.gds = None
+        why = "disabled by FLEXKV_GDS_FORCE_STAGED"
+        if os.environ.get("FLEXKV_GDS_FORCE_STAGED", "0") != "1":
+            ok, why = gds_probe()
+            if ok:
+                self.gds = _native.C.GdsEngine(ssd.files, ssd.block_bytes, ssd.blocks_per_file,
+                                               int(os.environ.get("FLEXKV_GDS_THREADS", 8)))
+                if not self.gds.available:
+                    why, self.gds = self.gds.why_unavailable, None
+        self.direct = self.gds is not None
         if not self.direct:
-            flexkv_logger.info("GDS direct path unavailable (%s): staging through pinned memory",
-                               self.gds.why_unavailable or "disabled")
+            flexkv_logger.info("GDS direct path unavailable (%s): staging through pinned memory", why)
         self.bounce, self.streams, self.status = {}, {}, {}
         for reg in self.regs:
             dev = f"cuda:{reg.device_id}"

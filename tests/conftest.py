@@ -3,6 +3,8 @@ import sys
 
 import pytest
 
+# a stuck worker must not stall a test run for the production shutdown budget (600 s per worker)
+os.environ.setdefault("FLEXKV_WORKER_SHUTDOWN_TIMEOUT_S", "15")
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
