@@ -39,13 +39,17 @@ def kv_quant_fp8(reg: GpuRegistration, host: HostSide, gpu_blocks, cpu_blocks, h
 
 def reference_pack(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
     """fp32 reference of the pack: ``x`` bf16 ``[..., E]`` -> (uint8 payload ``[..., E]``, fp32 scales ``[..., E/128]``)."""
-    xf = x.float().reshape(*x.shape[:-1], -1, GROUP)
+    # computed on the CPU with tensor / tensor divisions: IEEE round-to-nearest fp32 division, which is what
+    # the kernel's fdiv_rn does (a GPU division by a Python scalar may be turned into a reciprocal multiply)
+    dev = x.device
+    xf = x.detach().cpu().float().reshape(*x.shape[:-1], -1, GROUP)
     amax = xf.abs().amax(dim=-1, keepdim=True)
-    scale = torch.where(amax > 0, amax / 448.0, torch.ones_like(amax))
+    scale = torch.where(amax > 0, amax / torch.full_like(amax, 448.0), torch.ones_like(amax))
     q = (xf / scale).clamp(-448.0, 448.0).to(torch.float8_e4m3fn)
-    return q.view(torch.uint8).reshape(*x.shape), scale.squeeze(-1)
+    return q.view(torch.uint8).reshape(*x.shape).to(dev), scale.squeeze(-1).to(dev)
 
 
 def reference_unpack(payload: torch.Tensor, scales: torch.Tensor) -> torch.Tensor:
-    q = payload.view(torch.float8_e4m3fn).float().reshape(*payload.shape[:-1], -1, GROUP)
-    return (q * scales.unsqueeze(-1)).to(torch.bfloat16).reshape(*payload.shape)
+    dev = payload.device
+    q = payload.detach().cpu().view(torch.float8_e4m3fn).float().reshape(*payload.shape[:-1], -1, GROUP)
+    return (q * scales.detach().cpu().unsqueeze(-1)).to(torch.bfloat16).reshape(*payload.shape).to(dev)
