@@ -216,13 +216,18 @@ class GlobalCacheEngine:
         if cache_config.enable_ssd:
             self.ssd_cache_engine = CacheEngine(DeviceType.SSD, cache_config.num_ssd_blocks, **common)
             self.cache_engines[DeviceType.SSD] = self.ssd_cache_engine
-        if cache_config.enable_remote and cache_config.num_remote_blocks:
+        if cache_config.enable_remote and cache_config.num_remote_blocks and \
+                not cache_config.use_mooncake_store_backend:
             self.remote_cache_engine = CacheEngine(DeviceType.REMOTE, cache_config.num_remote_blocks, **common)
             self.cache_engines[DeviceType.REMOTE] = self.remote_cache_engine
         if not self.cache_engines:
             raise ValueError("at least one cache tier must be enabled")
         if self.cpu_cache_engine is None:
             raise ValueError("the host tier is the staging area of every other tier and must be enabled")
+        self.remote_backend = None          # key-addressed store; None = block-addressed index or no remote tier
+        if cache_config.enable_remote and cache_config.use_mooncake_store_backend:
+            from ..external.remote_store import get_backend
+            self.set_remote_backend(get_backend(cache_config))
         self.peer_directory = None
         if cache_config.enable_p2p_gpu:
             from ..parallel.peer_directory import GpuPeerDirectory
@@ -372,7 +377,15 @@ class GlobalCacheEngine:
         f2 = max(0, max(cpu_hit, ssd_hit) - f2_lo)        # blocks [f2_lo, ...) from SSD
         if prefetch:
             f1 = 0
-        if f0 + f1 + f2 == 0:
+        # fragment 3: blocks only the remote tier has, beyond everything local
+        f3, f3_lo, remote_m = 0, 0, None
+        use_gds_early = bool(self.cache_config.enable_gds) and not prefetch
+        if (self.remote_backend is not None or self.remote_cache_engine is not None) and not cpu_only \
+                and not use_gds_early:
+            r_hit, remote_m = self._remote_hit(seq, bend)
+            f3_lo = max(bstart, end)
+            f3 = max(0, r_hit - f3_lo)
+        if f0 + f1 + f2 + f3 == 0:
             return None
         graph = TransferOpGraph()
         plan = TransferPlan(graph)
@@ -426,13 +439,46 @@ class GlobalCacheEngine:
                     plan.op_callback_dict[disk_op.op_id] = lambda node=node, n=n: cpu.set_ready(node, True, n)
                 else:
                     plan.buffer_to_free[DeviceType.CPU] = staging
+        remote_op, staging3 = None, _EMPTY
+        if f3 > 0:
+            staging3 = cpu.take(f3, protected_node=cpu_m.last_node, strict=False)
+            if len(staging3) < f3:
+                cpu.recycle(staging3)
+                f3, staging3 = 0, _EMPTY
+        if f3 > 0:
+            hashes3 = seq.block_hashes[f3_lo:f3_lo + f3]
+            src3 = remote_m.physical_blocks[f3_lo:f3_lo + f3] if remote_m is not None else np.zeros(f3, dtype=np.int64)
+            remote_op = TransferOp(graph.graph_id, TransferType.REMOTE2H, src3, staging3, dp_client_id=dp_client_id,
+                                   block_hashes=hashes3)
+            graph.add_transfer_op(remote_op)
+            if remote_m is not None:
+                plan.nodes.setdefault(DeviceType.REMOTE, []).append((remote_m.last_ready_node, 0))
+            # the pulled blocks become host cache content when they extend what the host tier holds contiguously
+            node3 = None
+            tail_ok = (stage_node is not None and f2_lo + f2 == f3_lo) or \
+                (f2 == 0 and cpu_m.num_matched_blocks == cpu_m.num_ready_matched_blocks == f3_lo)
+            if tail_ok:
+                try:
+                    node3 = cpu.insert(seq, staging3, num_insert_blocks=f3_lo + f3, is_ready=False,
+                                       match_result=None if stage_node is not None else cpu_m)
+                except (RuntimeError, ValueError):
+                    node3 = None
+            if node3 is not None:
+                plan.nodes.setdefault(DeviceType.CPU, []).append((node3, 0))
+                plan.inserted.setdefault(DeviceType.CPU, []).append(node3)
+                plan.op_callback_dict[remote_op.op_id] = lambda node=node3, n=f3: cpu.set_ready(node, True, n)
+            else:
+                prev = plan.buffer_to_free.get(DeviceType.CPU, _EMPTY)
+                plan.buffer_to_free[DeviceType.CPU] = np.concatenate([prev, staging3])
         if prefetch:
-            if disk_op is None:
+            done = [o.op_id for o in (disk_op, remote_op) if o is not None]
+            if not done:
                 return None
-            plan.finished_ops_ids = [disk_op.op_id]
-            plan.num_gpu_blocks_to_transfer = f2
+            plan.finished_ops_ids = done
+            plan.num_gpu_blocks_to_transfer = f2 + f3
             return plan
-        h2d_src = np.concatenate([cpu_phys[lo1:lo1 + f1], staging]) if not use_gds else cpu_phys[lo1:lo1 + f1]
+        h2d_src = np.concatenate([cpu_phys[lo1:lo1 + f1], staging, staging3]) if not use_gds \
+            else cpu_phys[lo1:lo1 + f1]
         n_h2d = int(h2d_src.size)
         if n_h2d > 0:
             h2d = TransferOp(graph.graph_id, TransferType.H2D, h2d_src,
@@ -442,13 +488,15 @@ class GlobalCacheEngine:
             graph.add_transfer_op(h2d)
             if disk_op is not None and not use_gds:
                 graph.add_dependency(h2d.op_id, disk_op.op_id)
+            if remote_op is not None:
+                graph.add_dependency(h2d.op_id, remote_op.op_id)
             ops_done.append(h2d.op_id)
             if f1 > 0:
                 plan.nodes.setdefault(DeviceType.CPU, []).append((cpu_m.last_ready_node, 0))
         if disk_op is not None and use_gds:
             ops_done.append(disk_op.op_id)
         plan.finished_ops_ids = ops_done
-        plan.num_gpu_blocks_to_transfer = f0 + f1 + f2
+        plan.num_gpu_blocks_to_transfer = f0 + f1 + f2 + f3
         return plan
 
     # ---- PUT ------------------------------------------------------------------------
@@ -517,11 +565,48 @@ class GlobalCacheEngine:
             plan.op_callback_dict[disk.op_id] = lambda node=ssd_node, n=need_ssd: ssd.set_ready(node, True, n)
             if d2h is None:
                 plan.finished_ops_ids = [disk.op_id]
+        self._put_remote(seq, nb, cpu_m, cpu_matched, cpu_new, d2h, graph, plan, dp_client_id)
         if d2h is not None:
             plan.finished_ops_ids = [d2h.op_id]     # the caller may see success before the disk write ends
         plan.skipped_gpu_blocks = cpu_matched
         plan.num_gpu_blocks_to_transfer = need_cpu
         return plan
+
+    def _put_remote(self, seq, nb, cpu_m, cpu_matched, cpu_new, d2h, graph, plan, dp_client_id) -> None:
+        """Write-through of the blocks the remote tier lacks (H2REMOTE after the GPU->host copy)."""
+        if self.remote_backend is None and self.remote_cache_engine is None:
+            return
+        if cpu_m.num_ready_matched_blocks < cpu_matched:
+            return                                   # host blocks of another in-flight put cannot be a source
+        cpu_all = np.concatenate([cpu_m.physical_blocks[:cpu_matched], cpu_new])
+        if self.remote_backend is not None:
+            have = min(self.remote_backend.prefix_hit(seq.block_hashes[:nb]), nb)
+            if have >= nb:
+                return
+            op = TransferOp(graph.graph_id, TransferType.H2REMOTE, cpu_all[have:nb],
+                            np.zeros(nb - have, dtype=np.int64), dp_client_id=dp_client_id,
+                            block_hashes=seq.block_hashes[have:nb])
+        else:
+            rem = self.remote_cache_engine
+            rm = rem.match(seq)
+            have = min(rm.num_matched_blocks, nb)
+            if have >= nb:
+                return
+            new = rem.take(nb - have, protected_node=rm.last_node, strict=False)
+            if len(new) < nb - have:
+                rem.recycle(new)
+                return
+            op = TransferOp(graph.graph_id, TransferType.H2REMOTE, cpu_all[have:nb], new, dp_client_id=dp_client_id,
+                            block_hashes=seq.block_hashes[have:nb])
+            node = rem.insert(seq, new, num_insert_blocks=nb, is_ready=False, match_result=rm)
+            plan.nodes.setdefault(DeviceType.REMOTE, []).append((node, 0))
+            plan.inserted.setdefault(DeviceType.REMOTE, []).append(node)
+            plan.op_callback_dict[op.op_id] = lambda node=node, n=nb - have: rem.set_ready(node, True, n)
+        graph.add_transfer_op(op)
+        if d2h is not None:
+            graph.add_dependency(op.op_id, d2h.op_id)
+        elif not plan.finished_ops_ids:
+            plan.finished_ops_ids = [op.op_id]
 
     # ---- plan end --------------------------------------------------------------------
     def _complete_plan(self, plan: TransferPlan, is_put: bool) -> None:
@@ -557,6 +642,19 @@ class GlobalCacheEngine:
         if plan.peer_leases is not None and self.peer_directory is not None:
             self.peer_directory.release(*plan.peer_leases)
             plan.peer_leases = None
+
+    def set_remote_backend(self, backend) -> None:
+        """Key-addressed remote stores are probed by content key instead of a local index."""
+        self.remote_backend = backend if backend is not None and backend.key_addressed else None
+
+    def _remote_hit(self, seq: SequenceMeta, bend: int):
+        """(blocks available remotely from block 0, remote block ids or None for key-addressed)."""
+        if self.remote_backend is not None:
+            return min(self.remote_backend.prefix_hit(seq.block_hashes[:bend]), bend), None
+        if self.remote_cache_engine is not None:
+            m = self.remote_cache_engine.match(seq)
+            return min(m.num_ready_matched_blocks, bend), m
+        return 0, None
 
     def publish_gpu_blocks(self, rank: int, token_ids: np.ndarray, gpu_block_ids: np.ndarray,
                            namespace: Optional[List[str]] = None) -> int:

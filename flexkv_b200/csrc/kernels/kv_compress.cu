@@ -5,7 +5,7 @@
 namespace fkv {
 namespace {
 
-constexpr int kThreads = 128;
+constexpr int kThreads = 256;
 constexpr int kWarps = kThreads / 32;
 constexpr int kGroup = 128;
 constexpr int kGroupsPerTile = kCompressTileElems / kGroup;   // 64
@@ -48,18 +48,35 @@ kv_compress_kernel(const __grid_constant__ KvCopyParams p, uint32_t* __restrict_
   const int64_t chunk_elems = p.chunk_bytes / 2;
   const int32_t span = p.num_layers * p.kv_dim * tiles_per_chunk;
   const int64_t total = (int64_t)span * p.num_pairs;
-  const int64_t first = blockIdx.x, step = gridDim.x;
-  const int64_t n_mine = first < total ? (total - first + step - 1) / step : 0;
+  // every CTA owns one contiguous run of tiles: consecutive tiles share their block ids (fetched
+  // once per pair, possibly over PCIe) and their size-table neighbourhood
+  const int64_t per_cta = (total + gridDim.x - 1) / gridDim.x;
+  const int64_t first = (int64_t)blockIdx.x * per_cta, step = 1;
+  const int64_t n_mine = first < total ? (total - first < per_cta ? total - first : per_cta) : 0;
+  // thread 0 keeps the ids of the pair it is working on and asks for the next pair's early
+  int32_t id_pair = -1;
+  int64_t id_g = 0, id_c = 0, nx_g = 0, nx_c = 0;
+  auto pair_ids = [&](int32_t pair, int64_t& g, int64_t& c) {
+    if (pair != id_pair) {
+      if (pair == id_pair + 1 && id_pair >= 0) { id_g = nx_g; id_c = nx_c; }
+      else { id_g = __ldg(p.gpu_blocks + pair); id_c = __ldg(p.cpu_blocks + pair); }
+      id_pair = pair;
+      if (pair + 1 < p.num_pairs) { nx_g = __ldg(p.gpu_blocks + pair + 1); nx_c = __ldg(p.cpu_blocks + pair + 1); }
+    }
+    g = id_g; c = id_c;
+  };
   int err = 0;
   uint32_t phases = 0;
 
   // decodes tile `it` of this CTA; returns false for a pair whose ids are out of range
-  auto locate = [&](int64_t it, uint64_t& g, uint64_t& c, uint64_t& tidx, int32_t& elems) -> bool {
+  auto locate = [&](int64_t it, uint64_t& g, uint64_t& c, uint64_t& tidx, int32_t& elems, bool cached) -> bool {
     const int64_t t = first + it * step;
     const int32_t pair = (int32_t)(t / span), r = (int32_t)(t % span);
     const int s_ = r % tiles_per_chunk, q = r / tiles_per_chunk;
     const int kv = q % p.kv_dim, layer = p.layer_start + q / p.kv_dim;
-    const int64_t gblk = __ldg(p.gpu_blocks + pair), cblk = __ldg(p.cpu_blocks + pair);
+    int64_t gblk, cblk;
+    if (cached) pair_ids(pair, gblk, cblk);
+    else { gblk = __ldg(p.gpu_blocks + pair); cblk = __ldg(p.cpu_blocks + pair); }
     bool ok = true;
     if (p.gpu_num_blocks > 0 && (gblk < 0 || gblk >= p.gpu_num_blocks)) { err |= KV_ERR_GPU_BLOCK_RANGE; ok = false; }
     if (p.cpu_num_blocks > 0 && (cblk < 0 || cblk >= p.cpu_num_blocks)) { err |= KV_ERR_CPU_BLOCK_RANGE; ok = false; }
@@ -78,7 +95,7 @@ kv_compress_kernel(const __grid_constant__ KvCopyParams p, uint32_t* __restrict_
     const int st = (int)(it % kInStages);
     uint64_t g, c, tidx;
     int32_t elems;
-    const bool ok = locate(it, g, c, tidx, elems);
+    const bool ok = locate(it, g, c, tidx, elems, true);
     s_table_idx[st] = tidx;
     if (!ok) {
       s_elems[st] = 0;
@@ -111,7 +128,7 @@ kv_compress_kernel(const __grid_constant__ KvCopyParams p, uint32_t* __restrict_
       uint64_t g, c, tidx;
       int32_t elems;
       int keep = err;
-      locate(it, g, c, tidx, elems);
+      locate(it, g, c, tidx, elems, false);
       err = keep;                      // range errors are reported once, by thread 0 at issue time
       s_sizes[it % kEpoch] = __ldg(size_table + tidx);
     }

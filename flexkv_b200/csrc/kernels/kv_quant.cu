@@ -48,8 +48,23 @@ __global__ void __launch_bounds__(kThreads, 1) kv_quant_fp8_kernel(const __grid_
   const int64_t chunk_elems = p.chunk_bytes / 2;
   const int32_t span = p.num_layers * p.kv_dim * tiles_per_chunk;
   const int64_t total = (int64_t)span * p.num_pairs;
-  const int64_t first = blockIdx.x, step = gridDim.x;
-  const int64_t n_mine = first < total ? (total - first + step - 1) / step : 0;
+  // every CTA owns one contiguous run of tiles: consecutive tiles share their block ids (fetched
+  // once per pair, possibly over PCIe) and their size-table neighbourhood
+  const int64_t per_cta = (total + gridDim.x - 1) / gridDim.x;
+  const int64_t first = (int64_t)blockIdx.x * per_cta, step = 1;
+  const int64_t n_mine = first < total ? (total - first < per_cta ? total - first : per_cta) : 0;
+  // thread 0 keeps the ids of the pair it is working on and asks for the next pair's early
+  int32_t id_pair = -1;
+  int64_t id_g = 0, id_c = 0, nx_g = 0, nx_c = 0;
+  auto pair_ids = [&](int32_t pair, int64_t& g, int64_t& c) {
+    if (pair != id_pair) {
+      if (pair == id_pair + 1 && id_pair >= 0) { id_g = nx_g; id_c = nx_c; }
+      else { id_g = __ldg(p.gpu_blocks + pair); id_c = __ldg(p.cpu_blocks + pair); }
+      id_pair = pair;
+      if (pair + 1 < p.num_pairs) { nx_g = __ldg(p.gpu_blocks + pair + 1); nx_c = __ldg(p.cpu_blocks + pair + 1); }
+    }
+    g = id_g; c = id_c;
+  };
   int err = 0;
   uint32_t phases = 0;   // every thread tracks the parity of each stage's next completion
 
@@ -60,7 +75,8 @@ __global__ void __launch_bounds__(kThreads, 1) kv_quant_fp8_kernel(const __grid_
     const int32_t pair = (int32_t)(t / span), r = (int32_t)(t % span);
     const int s_ = r % tiles_per_chunk, q = r / tiles_per_chunk;
     const int kv = q % p.kv_dim, layer = p.layer_start + q / p.kv_dim;
-    const int64_t gblk = __ldg(p.gpu_blocks + pair), cblk = __ldg(p.cpu_blocks + pair);
+    int64_t gblk, cblk;
+    pair_ids(pair, gblk, cblk);
     bool ok = true;
     if (p.gpu_num_blocks > 0 && (gblk < 0 || gblk >= p.gpu_num_blocks)) { err |= KV_ERR_GPU_BLOCK_RANGE; ok = false; }
     if (p.cpu_num_blocks > 0 && (cblk < 0 || cblk >= p.cpu_num_blocks)) { err |= KV_ERR_CPU_BLOCK_RANGE; ok = false; }

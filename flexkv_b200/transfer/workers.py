@@ -371,6 +371,32 @@ class SsdWorker(TransferWorker):
                          error="" if nfail == 0 else f"{nfail} block(s) failed")
 
 
+class RemoteWorker(TransferWorker):
+    """H2REMOTE / REMOTE2H through a remote back end (shared files or a key-addressed
+    store). Reports a per-block result list; any failed block fails the op
+    (flexkv/transfer/worker.py:1715-1946,3875-4092)."""
+
+    def __init__(self, storage, backend, to_host: bool) -> None:
+        super().__init__()
+        self.storage, self.backend, self.to_host = storage, backend, to_host
+        self.name = "remote2h" if to_host else "h2remote"
+
+    def execute(self, op: TransferOp) -> OpOutcome:
+        host = self.storage.host
+        if self.to_host:
+            rids, cpu = op.src_block_ids, op.dst_block_ids
+        else:
+            cpu, rids = op.src_block_ids, op.dst_block_ids
+        ids = op.block_hashes if self.backend.key_addressed else rids
+        if ids is None or len(ids) != len(cpu):
+            return OpOutcome(False, error="remote op without matching ids")
+        views = [host.block_view(int(b)) for b in cpu]
+        res = self.backend.get(list(ids), views) if self.to_host else self.backend.put(list(ids), views)
+        ok = all(res)
+        return OpOutcome(ok, block_results=tuple(bool(r) for r in res), num_bytes=sum(res) * host.block_bytes,
+                         error="" if ok else f"{len(res) - sum(res)} remote block(s) failed")
+
+
 _GDS_PROBE: Optional[Tuple[bool, str]] = None
 
 
@@ -561,6 +587,12 @@ def build_workers(storage, model_config: ModelConfig, cache_config: CacheConfig
         for k in real:
             workers[(k, TransferType.DISK2D)] = GdsWorker(storage, model_config, k, True)
             workers[(k, TransferType.D2DISK)] = GdsWorker(storage, model_config, k, False)
+    if cache_config.enable_remote and storage.host is not None:
+        from ..external.remote_store import get_backend
+        backend = get_backend(cache_config, storage.host.block_bytes)
+        if backend is not None:
+            workers[(WorkerKey(0, 0), TransferType.REMOTE2H)] = RemoteWorker(storage, backend, True)
+            workers[(WorkerKey(0, 0), TransferType.H2REMOTE)] = RemoteWorker(storage, backend, False)
     if storage.ssd is not None:
         k0 = WorkerKey(0, 0)
         workers[(k0, TransferType.DISK2H)] = SsdWorker(storage, True)

@@ -1,0 +1,99 @@
+"""Remote tier on CPU: block-addressed files and the key-addressed store, write-through on
+put, three-fragment get, prefetch, host-side fault injection (reference: tests/test_mooncake_*.py)."""
+import numpy as np
+import pytest
+import torch
+
+from flexkv_b200 import CacheConfig, KVManager
+from flexkv_b200.external.remote_store import FaultInjector, KVStoreBackend, LoopbackKVStore
+from flexkv_b200.models import KVShape, alloc_paged_cache, make_model_config
+
+T = 4
+
+
+def slots(blocks):
+    return np.repeat(np.asarray(blocks, dtype=np.int64), T) * T + np.tile(np.arange(T), len(blocks))
+
+
+def start(cache_kw):
+    shape = KVShape("r", 2, 2, 16, tokens_per_block=T)
+    mgr = KVManager(make_model_config(shape), CacheConfig(tokens_per_block=T, num_cpu_blocks=24, **cache_kw),
+                    require_gpu=True)
+    kv, layout = alloc_paged_cache(shape, 64, "cpu", "vllm", fill="normal", seed=5)
+    mgr.register_gpu_tensors(kv, layout)
+    mgr.start(); mgr.wait_ready(30)
+    return mgr, kv
+
+
+@pytest.mark.parametrize("kind", ["files", "kvstore"])
+def test_remote_write_through_and_restore(tmp_path, kind):
+    kw = dict(enable_remote=True, num_remote_blocks=64)
+    if kind == "files":
+        kw.update(remote_cache_path=str(tmp_path), remote_file_num=3)
+    else:
+        kw.update(use_mooncake_store_backend=True, mooncake_store_config_path="loopback",
+                  remote_config_custom={"store": LoopbackKVStore()})
+    mgr, kv = start(kw)
+    try:
+        tok = np.arange(8 * T, dtype=np.int64)
+        src = np.array([3, 9, 1, 30, 12, 7, 50, 2])
+        tid = mgr.put_async(tok, slots(src))
+        assert mgr.wait(tid, completely=True)[tid].status.value == "success"
+        saved = [t.clone() for t in kv]
+        mgr._clear_cpu_cache()                       # only the remote tier still has the blocks
+        for t in kv:
+            t.zero_()
+        tid, mask = mgr.get_match(tok)
+        assert int(mask.sum()) == 8 * T
+        kinds = sorted(o.transfer_type.value for o in mgr.kv_task_engine.tasks[tid].graph.ops())
+        assert kinds == ["H2D", "REMOTE2H"]
+        dst = np.arange(40, 48)
+        mgr.launch(tid, slots(dst))
+        assert mgr.wait(tid)[tid].status.value == "success"
+        for l in range(2):
+            assert torch.equal(kv[l][:, dst], saved[l][:, src])
+        # the pulled blocks were adopted by the host tier: the next get is host-only
+        tid, mask = mgr.get_match(tok)
+        assert [o.transfer_type.value for o in mgr.kv_task_engine.tasks[tid].graph.ops()] == ["H2D"]
+        mgr.cancel(tid)
+        # prefetch pulls remote blocks into the host pool ahead of time
+        mgr._clear_cpu_cache()
+        pid = mgr.prefetch_async(tok)
+        r = mgr.wait(pid, completely=True)[pid]
+        assert r.status.value == "success" and int(r.return_mask.sum()) == 8 * T
+        tid, mask = mgr.get_match(tok, cpu_only=True)
+        assert int(mask.sum()) == 8 * T
+        mgr.cancel(tid)
+    finally:
+        mgr.shutdown()
+
+
+def test_injected_remote_failure_fails_the_get_and_rolls_back(monkeypatch):
+    monkeypatch.setenv("FLEXKV_MOONCAKE_FAULT_MODE", "tail")
+    monkeypatch.setenv("FLEXKV_MOONCAKE_FAULT_OP", "get")
+    monkeypatch.setenv("FLEXKV_MOONCAKE_FAULT_TAIL_N", "2")
+    mgr, kv = start(dict(enable_remote=True, use_mooncake_store_backend=True, mooncake_store_config_path="loopback",
+                         remote_config_custom={"store": LoopbackKVStore()}))
+    try:
+        tok = np.arange(6 * T, dtype=np.int64)
+        tid = mgr.put_async(tok, slots(range(6)))
+        assert mgr.wait(tid, completely=True)[tid].status.value == "success"
+        mgr._clear_cpu_cache()
+        tid = mgr.get_async(tok, slots(range(10, 16)))
+        assert mgr.wait(tid, timeout=5)[tid].status.value == "failed"       # two tail blocks did not arrive
+        cpu = mgr.kv_task_engine.cache_engine.cpu_cache_engine
+        assert cpu.mempool.num_used_blocks == 0 and cpu.index.is_empty()    # staging returned, nothing adopted
+    finally:
+        mgr.shutdown()
+
+
+def test_fault_injector_modes():
+    assert FaultInjector("none").apply("get", [True, True]) == [True, True]
+    assert FaultInjector("all").apply("get", [True, True]) == [False, False]
+    assert FaultInjector("tail", tail_n=1).apply("put", [True, True, True]) == [True, True, False]
+    assert FaultInjector("tail", op="get").apply("put", [True, True]) == [True, True]
+    r = FaultInjector("random", seed=1, random_ratio=0.5).apply("get", [True] * 8)
+    assert r.count(False) == 4
+    s = KVStoreBackend(LoopbackKVStore())
+    blk = np.arange(16, dtype=np.uint8)
+    assert s.put([7, 8], [blk, blk]) == [True, True] and s.prefix_hit(np.array([7, 8, 9], dtype=np.uint64)) == 2
