@@ -46,6 +46,7 @@ class TransferEngine:
         self._trace = TransferTrace(enabled=GLOBAL_CONFIG_FROM_ENV.enable_transfer_trace)
         self._metrics = None
         self.stats = dict(ops=0, failed_ops=0, graphs=0, failed_graphs=0)
+        self.stats_by_type: Dict[str, List[float]] = {}     # type -> [ops, blocks, bytes, kernel or IO ms]
 
     # ---- lifecycle ------------------------------------------------------------
     def start(self) -> None:
@@ -163,6 +164,11 @@ class TransferEngine:
         if not outcome.success:
             self.stats["failed_ops"] += 1
         op.block_results = outcome.block_results
+        acc = self.stats_by_type.setdefault(op.transfer_type.value, [0, 0, 0, 0.0])
+        acc[0] += 1
+        acc[1] += op.valid_block_num
+        acc[2] += outcome.num_bytes
+        acc[3] += outcome.gpu_ms
         self._trace.on_done(op, outcome)
         if self._metrics is not None:
             self._metrics.record_transfer(op.transfer_type.value, op.valid_block_num, outcome.num_bytes,

@@ -235,7 +235,8 @@ class QuantGpuHostWorker(TransferWorker):
         self.host = host
         self.layer_stride, self.kv_stride, self.tp_stride = host.layer_stride // n, host.kv_stride // n, \
             host.block_bytes // n
-        self.num_ctas = int(os.environ.get("FLEXKV_QUANT_NUM_CTA", 32))
+        # measured on B200 (Llama-3-8B blocks): unpacking fills the link with 16 CTAs, packing needs ~48
+        self.num_ctas = int(os.environ.get("FLEXKV_QUANT_NUM_CTA", 24 if h2d else 48))
         self._torch = torch
         self.streams = {r.device_id: torch.cuda.Stream(device=r.device_id) for r in self.regs}
         self.status = {r.device_id: torch.zeros(8, dtype=torch.int32, device=f"cuda:{r.device_id}") for r in self.regs}
