@@ -74,7 +74,10 @@ class TransferWorker:
                 if self.fail_next > 0:
                     self.fail_next -= 1
                     raise RuntimeError("injected worker failure")
+                t0 = time.perf_counter()
                 out = self.execute(op)
+                if out.gpu_ms <= 0:            # IO workers have no device timing: report the time spent in the call
+                    out.gpu_ms = (time.perf_counter() - t0) * 1e3
             except Exception as e:  # noqa: BLE001
                 flexkv_logger.error("%s: op %d (%s) failed: %s", self.name, op.op_id, op.transfer_type.value, e)
                 out = OpOutcome(False, error=str(e))
@@ -236,7 +239,7 @@ class QuantGpuHostWorker(TransferWorker):
         self.layer_stride, self.kv_stride, self.tp_stride = host.layer_stride // n, host.kv_stride // n, \
             host.block_bytes // n
         # measured on B200 (Llama-3-8B blocks): unpacking fills the link with 16 CTAs, packing needs ~48
-        self.num_ctas = int(os.environ.get("FLEXKV_QUANT_NUM_CTA", 24 if h2d else 48))
+        self.num_ctas = int(os.environ.get("FLEXKV_QUANT_NUM_CTA", 32 if h2d else 48))
         self._torch = torch
         self.streams = {r.device_id: torch.cuda.Stream(device=r.device_id) for r in self.regs}
         self.status = {r.device_id: torch.zeros(8, dtype=torch.int32, device=f"cuda:{r.device_id}") for r in self.regs}
