@@ -8,12 +8,14 @@
 #include <cuda_runtime.h>
 
 #include "hasher.h"
+#include "native_log.h"
 #include "host_mem.h"
 #include "kernels/kv_copy.h"
 #include "radix_index.h"
 #include "ssd_io.h"
 #include "transfer_group.h"
 #include "bindings_common.h"
+#include "native_log.h"
 
 namespace py = pybind11;
 using namespace fkv;
@@ -47,6 +49,30 @@ struct PyMatch {
 PYBIND11_MODULE(_C, m) {
   m.doc() = "flexkv_b200 native core (sm_100a kernels + C++ control plane)";
   m.attr("MAX_GPU_PTRS") = kMaxGpuPtrs;
+
+  // ------------------------------------------------- native logging / counters
+  m.def("configure_cpp_metrics", [](bool enabled) { configure_metrics(enabled); }, py::arg("enabled"));
+  m.def("reset_cpp_metrics", [] { reset_metrics(); });
+  m.def("cpp_metrics_snapshot", [] {
+    py::dict ops, blocks;
+    auto& c = cache_counters();
+    for (int i = 0; i < kNumCacheOps; ++i) {
+      ops[kCacheOpNames[i]] = c.ops[i].load();
+      blocks[kCacheOpNames[i]] = c.blocks[i].load();
+    }
+    py::dict d;
+    d["enabled"] = metrics_enabled();
+    d["ops"] = ops;
+    d["blocks"] = blocks;
+    return d;
+  });
+  m.def("set_log_level", [](const std::string& name) { set_log_level(name); });
+  m.def("get_log_level", [] { return (int)log_level(); });
+  m.def("set_log_prefix", [](const std::string& p) { set_log_prefix(p); });
+  m.def("native_log", [](int level, const std::string& msg) {
+    FKV_LOG((LogLevel)level, "%s", msg.c_str());
+  });
+  m.def("native_log_recent", [](size_t n) { return log_recent(n); }, py::arg("max_lines") = 64);
 
   // ---------------------------------------------------------------- hashing
   m.def("xxh64", [](py::buffer b, uint64_t seed) {

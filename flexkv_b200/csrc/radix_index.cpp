@@ -1,4 +1,5 @@
 #include "radix_index.h"
+#include "native_log.h"
 
 #include <algorithm>
 #include <chrono>
@@ -125,7 +126,7 @@ void RadixIndex::remove_child(int32_t parent, uint64_t head) {
   if (p.leaf() && parent != 0) leaves_.insert(parent);
 }
 
-MatchResult RadixIndex::match_prefix(const uint64_t* hashes, int64_t n, bool update_cache_info) {
+MatchResult RadixIndex::match_prefix(const uint64_t* hashes, int64_t n, bool update_cache_info, bool count_stats) {
   MatchResult r;
   r.last_node = root_handle();
   r.last_ready_node = root_handle();
@@ -167,8 +168,9 @@ MatchResult RadixIndex::match_prefix(const uint64_t* hashes, int64_t n, bool upd
     cur = c;
   }
   r.num_matched = prefix;
-  if (n > 0) {
+  if (n > 0 && count_stats) {
     if (prefix == n) ++stat_hit; else if (prefix > 0) ++stat_match; else ++stat_miss;
+    count_cache_op(prefix == n ? kOpHit : (prefix > 0 ? kOpMatch : kOpMiss), (uint64_t)(prefix > 0 ? prefix : n));
   }
   return r;
 }
@@ -234,7 +236,7 @@ NodeHandle RadixIndex::insert(const int64_t* physical, int64_t num_physical, con
   if (num_insert > n) throw std::invalid_argument("radix index insert: num_insert exceeds hash count");
   MatchResult local;
   if (match == nullptr) {
-    local = match_prefix(hashes, num_insert, false);
+    local = match_prefix(hashes, num_insert, false, false);
     match = &local;
   }
   if (num_insert <= match->num_matched) return kNullHandle;
@@ -258,6 +260,7 @@ NodeHandle RadixIndex::insert(const int64_t* physical, int64_t num_physical, con
   leaves_.insert(nn);
   total_blocks_ += num_physical;
   stat_insert_blocks += (uint64_t)num_physical;
+  count_cache_op(kOpInsert, (uint64_t)num_physical);
   return make_handle(nn);
 }
 
@@ -325,6 +328,7 @@ EvictResult RadixIndex::evict(int64_t num_blocks) {
     if (evictable(parent)) heap.push(parent);
   }
   stat_evict_blocks += (uint64_t)out.blocks.size();
+  if (!out.blocks.empty()) count_cache_op(kOpEvict, (uint64_t)out.blocks.size());
   return out;
 }
 

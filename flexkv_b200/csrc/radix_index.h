@@ -44,7 +44,8 @@ class RadixIndex {
   RadixIndex(int tokens_per_block, int64_t max_num_blocks, EvictPolicy policy,
              double hit_reward_seconds = 0.0, uint32_t slru_threshold = 2);
 
-  MatchResult match_prefix(const uint64_t* hashes, int64_t n, bool update_cache_info);
+  // count_stats=false for lookups the index makes on its own behalf (inside insert).
+  MatchResult match_prefix(const uint64_t* hashes, int64_t n, bool update_cache_info, bool count_stats = true);
 
   // Adds hashes[num_matched:num_insert) with the given physical blocks below
   // the match point. `match` may be null (the call re-matches). Throws

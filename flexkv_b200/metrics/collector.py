@@ -37,6 +37,34 @@ class MetricsCollector:
         self.peer_hit_blocks = Counter("flexkv_py_peer_gpu_hit_blocks", "Blocks pulled from a peer GPU over NVLink",
                                        registry=r)
         self._server_started = False
+        self._attach_native_counters()
+
+    def _attach_native_counters(self) -> None:
+        """Expose the C++ index counters under the reference's native metric names
+        (csrc/monitoring/metrics_manager.cpp:104-110); values are read at scrape time."""
+        try:
+            from .. import _native
+            C = _native.C
+        except Exception:  # noqa: BLE001
+            return
+        from prometheus_client.core import CounterMetricFamily
+
+        class _Native:
+            def collect(self_inner):
+                snap = C.cpp_metrics_snapshot()
+                ops = CounterMetricFamily("flexkv_cpp_cache_ops", "Index operations counted in native code",
+                                          labels=["operation"])
+                blocks = CounterMetricFamily("flexkv_cpp_cache_blocks", "Blocks touched by native index operations",
+                                             labels=["operation"])
+                for k, v in snap["ops"].items():
+                    ops.add_metric([k], v)
+                for k, v in snap["blocks"].items():
+                    blocks.add_metric([k], v)
+                yield ops
+                yield blocks
+
+        C.configure_cpp_metrics(True)
+        self.registry.register(_Native())
 
     def start_server(self, port: Optional[int] = None) -> None:
         if self._server_started:
