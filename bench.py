@@ -50,7 +50,7 @@ def parse_args():
     ap.add_argument("--host-pool-gib", type=float, default=256.0)
     ap.add_argument("--ctas", type=int, default=0, help="persistent CTAs per copy kernel (0 = configured default)")
     ap.add_argument("--tile-bytes", type=int, default=0)
-    ap.add_argument("--engine", default="", choices=["", "tma", "simt"])
+    ap.add_argument("--engine", default="", choices=["", "tma", "simt", "ce", "auto"])
     ap.add_argument("--latency-iters", type=int, default=20)
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--codec", default="bf16_xp", choices=["none", "bf16_xp", "fp8_e4m3"],

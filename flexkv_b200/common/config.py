@@ -4,9 +4,9 @@ user config files and GB -> block conversion.
 Field and variable names match the reference so that existing deployments can
 switch without renaming anything (flexkv/common/config.py:122-427 ModelConfig,
 :430-571 RankInfo, :623-746 CacheConfig, :748-841 environment table,
-:843-944 UserConfig, :946-1246 conversion helpers). Keys that only tuned the
-reference's copy-engine paths are accepted and ignored: every GPU<->host move
-here is one sm_100a kernel.
+:843-944 UserConfig, :946-1246 conversion helpers). GPU<->host moves default to one
+sm_100a kernel per op; the copy-engine switches select the adaptive router that
+sends long contiguous runs to the DMA engines instead.
 """
 from __future__ import annotations
 
@@ -310,8 +310,9 @@ def load_env_config() -> Namespace:
         transfer_num_cta_h2d=_env("FLEXKV_TRANSFER_NUM_CTA_H2D", 8),
         transfer_num_cta_d2h=_env("FLEXKV_TRANSFER_NUM_CTA_D2H", 8),
         transfer_tile_bytes=_env("FLEXKV_TRANSFER_TILE_BYTES", 16384),
-        transfer_engine=_env("FLEXKV_TRANSFER_ENGINE", "tma").lower(),   # tma | simt
-        # accepted for compatibility, unused: copy-engine tuning of the reference
+        transfer_engine=_env("FLEXKV_TRANSFER_ENGINE", "tma").lower(),   # tma | simt | ce | auto
+        # copy-engine router: the two switches turn on "auto" per direction; the segment
+        # threshold is accepted for compatibility (routing here is by bytes per driver call)
         use_ce_transfer_h2d=_env("FLEXKV_USE_CE_TRANSFER_H2D", False, bool),
         use_ce_transfer_d2h=_env("FLEXKV_USE_CE_TRANSFER_D2H", False, bool),
         ce_segment_threshold=_env("FLEXKV_CE_SEGMENT_THRESHOLD", 8),

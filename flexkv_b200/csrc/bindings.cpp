@@ -313,6 +313,7 @@ PYBIND11_MODULE(_C, m) {
       .def("set_launch", [](TransferGroup& t, bool h2d, int ctas, int tile, int engine) {
              t.set_launch(h2d, KvCopyLaunch{ctas, tile, engine});
            })
+      .def_property_readonly("ce_ops", &TransferGroup::ce_ops)
       .def_property_readonly("num_ranks", &TransferGroup::num_ranks);
 
   init_kernel_bindings(m);

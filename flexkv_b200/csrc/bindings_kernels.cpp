@@ -10,6 +10,7 @@
 #include "kernels/kv_fanout.h"
 #include "kernels/kv_quant.h"
 #include "kernels/kv_compress.h"
+#include "ce_copy.h"
 #include "ipc.h"
 
 namespace py = pybind11;
@@ -121,6 +122,27 @@ void init_kernel_bindings(py::module_& m) {
     py::gil_scoped_release rel;
     return host_kv_copy(p, threads);
   }, py::arg("params"), py::arg("threads") = 4);
+
+  // Copy-engine planning, exposed for inspection and CPU tests: returns the runs as an
+  // [R, 3] array (gpu block, cpu block, length), the chosen path, the number of driver
+  // copies that path would issue, and the range-error bits of dropped ids.
+  m.def("ce_plan", [](py::dict params, int64_t max_copies, int64_t min_bytes_per_copy) {
+    KvCopyParams p = kv_params_from_dict(params);
+    CeAnalysis a = ce_analyze(p.gpu_blocks, p.cpu_blocks, p.num_pairs, p.gpu_num_blocks, p.cpu_num_blocks);
+    CePolicy pol;
+    pol.max_copies = max_copies;
+    pol.min_bytes_per_copy = min_bytes_per_copy;
+    CePath path = ce_choose(a, p, pol);
+    py::array_t<int64_t> runs(std::vector<py::ssize_t>{(py::ssize_t)a.runs.size(), 3});
+    auto r = runs.mutable_unchecked<2>();
+    for (size_t i = 0; i < a.runs.size(); ++i) {
+      r(i, 0) = a.runs[i].gpu_block;
+      r(i, 1) = a.runs[i].cpu_block;
+      r(i, 2) = a.runs[i].len;
+    }
+    static const char* names[] = {"kernel", "contig_blocks", "segment_2d"};
+    return py::make_tuple(runs, std::string(names[(int)path]), ce_num_copies(a, p, path), a.status);
+  }, py::arg("params"), py::arg("max_copies") = 4096, py::arg("min_bytes_per_copy") = 256 << 10);
 
   m.def("kv_copy_tma_eligible", [](py::dict params) { return kv_copy_tma_eligible(kv_params_from_dict(params)); });
 }

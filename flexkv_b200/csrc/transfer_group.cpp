@@ -1,5 +1,9 @@
 #include "transfer_group.h"
 
+#include <climits>
+
+#include "ce_copy.h"
+
 #include <algorithm>
 #include <cstring>
 #include <stdexcept>
@@ -185,12 +189,28 @@ void TransferGroup::rank_main(int r) {
       lerr[i] = cudaSuccess;
       if (skip) continue;
       cudaEventRecord(ev0[i], rk.stream);
-      if (t.engine == 2) {
+      if (t.engine == kEngineRefshape) {
         lerr[i] = launch_kv_copy_refshape(p, t.refshape_ctas, rk.stream);
       } else {
         KvCopyLaunch cfg = t.h2d ? opt_.h2d : opt_.d2h;
         if (t.engine >= 0) cfg.engine = t.engine;
-        lerr[i] = launch_kv_copy(p, cfg, rk.stream);
+        bool done = false;
+        if (cfg.engine == kEngineCe || cfg.engine == kEngineAuto) {
+          // the id ring is mapped pinned memory: the same pointers are readable here
+          CeAnalysis a = ce_analyze(p.gpu_blocks, p.cpu_blocks, p.num_pairs, p.gpu_num_blocks, p.cpu_num_blocks);
+          CePath path = ce_choose(a, p, cfg.engine == kEngineCe ? CePolicy{INT64_MAX, 0} : opt_.ce_policy);
+          if (path != CePath::KERNEL) {
+            lerr[i] = ce_copy(p, a, path, rk.stream);
+            for (int b = 0; b < kStatusWords; ++b)
+              if (a.status & (1 << b)) p.status[b] = 1;
+            ce_ops_.fetch_add(1, std::memory_order_relaxed);
+            done = true;
+          }
+        }
+        if (!done) {
+          if (cfg.engine >= kEngineCe) cfg.engine = 0;
+          lerr[i] = launch_kv_copy(p, cfg, rk.stream);
+        }
       }
       cudaEventRecord(ev1[i], rk.stream);
     }
@@ -302,7 +322,7 @@ OpResult TransferGroup::transfer_refshape(const int64_t* gpu_blocks, const int64
   }
   std::memcpy(id_ring_ + ((size_t)t.slot * 2 + 0) * (size_t)opt_.max_blocks_per_op, gpu_blocks, (size_t)n * 8);
   std::memcpy(id_ring_ + ((size_t)t.slot * 2 + 1) * (size_t)opt_.max_blocks_per_op, cpu_blocks, (size_t)n * 8);
-  t.n = n; t.h2d = h2d; t.layer_start = 0; t.num_layers = opt_.num_layers; t.engine = 2; t.refshape_ctas = num_ctas;
+  t.n = n; t.h2d = h2d; t.layer_start = 0; t.num_layers = opt_.num_layers; t.engine = kEngineRefshape; t.refshape_ctas = num_ctas;
   for (auto& rk : ranks_) {
     { std::lock_guard<std::mutex> g(rk->mu); rk->q.push_back(t); }
     rk->cv.notify_one();

@@ -22,6 +22,7 @@
 
 #include <cuda_runtime.h>
 
+#include "ce_copy.h"
 #include "kernels/kv_copy.h"
 
 namespace fkv {
@@ -55,7 +56,11 @@ struct GroupOptions {
   int ring_slots = 8;
   int64_t max_blocks_per_op = 1 << 16;
   bool high_priority_stream = false;
+  CePolicy ce_policy;
 };
+
+// Engine selectors of an op (KvCopyLaunch::engine or a per-op override).
+constexpr int kEngineTma = 0, kEngineSimt = 1, kEngineCe = 2, kEngineAuto = 3, kEngineRefshape = 9;
 
 struct OpResult {
   int status = 0;        // OR of KvCopyStatus bits over ranks; negative = CUDA error code
@@ -89,6 +94,7 @@ class TransferGroup {
   void update_gpu_ptrs(int rank, const std::vector<uint64_t>& ptrs);  // sleep/wake re-registration
   void set_launch(bool h2d, KvCopyLaunch cfg);
   int num_ranks() const { return (int)gpus_.size(); }
+  uint64_t ce_ops() const { return ce_ops_.load(); }   // ops that went through the copy engines
   const GroupOptions& options() const { return opt_; }
 
  private:
@@ -98,7 +104,7 @@ class TransferGroup {
     int64_t n;
     bool h2d;
     int layer_start, num_layers;
-    int engine;        // -1 default, 0/1 override, 2 = refshape
+    int engine;        // -1 default, else one of the kEngine* selectors
     int refshape_ctas;
     uint64_t rotate;   // op counter for RANK_ROTATE
   };
@@ -136,6 +142,7 @@ class TransferGroup {
   std::unordered_map<uint64_t, Pending> pending_;
   uint64_t next_ticket_ = 1;
   uint64_t op_counter_ = 0;
+  std::atomic<uint64_t> ce_ops_{0};
   mutable std::mutex ptr_mu_;
 };
 

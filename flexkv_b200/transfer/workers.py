@@ -89,9 +89,18 @@ class TransferWorker:
 
 # ------------------------------------------------------------------ GPU <-> host
 
+_ENGINE_IDS = {"tma": 0, "simt": 1, "ce": 2, "auto": 3}
+
+
 def _launch_cfg(env, h2d: bool) -> Dict[str, int]:
+    """Engine per direction: FLEXKV_TRANSFER_ENGINE (tma | simt | ce | auto); the reference's
+    FLEXKV_USE_CE_TRANSFER_H2D/D2H switches select the adaptive copy-engine router ("auto")
+    for that direction (csrc/transfer.cu:164-313 chooses kernel vs copy engine the same way)."""
+    engine = _ENGINE_IDS.get(env.transfer_engine, 0)
+    if (env.use_ce_transfer_h2d if h2d else env.use_ce_transfer_d2h) and engine in (0, 1):
+        engine = 3
     return dict(num_ctas=env.transfer_num_cta_h2d if h2d else env.transfer_num_cta_d2h,
-                tile_bytes=env.transfer_tile_bytes, engine=0 if env.transfer_engine == "tma" else 1)
+                tile_bytes=env.transfer_tile_bytes, engine=engine)
 
 
 def build_transfer_group(storage, model_config: ModelConfig, key: WorkerKey, high_priority: bool = False,
