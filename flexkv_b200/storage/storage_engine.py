@@ -135,25 +135,18 @@ class StorageEngine:
         (bf16, BLOCKFIRST host layout, chunk elements % 1024 == 0, no layerwise restore: the layerwise
         kernel consumes raw host blocks — the reference applies the same all-or-nothing rule,
         flexkv/transfer/compression/ans/ans_utils.py:51-118)."""
+        from ..transfer.compression.policy import choose_codec
         m, c = self.model_config, self.cache_config
-        if c.offload_quant != "none":
-            return c.offload_quant
-        if not (c.enable_compression or self.env.enable_compression):
-            return "none"
         slices = 1 if (m.use_mla or m.num_kv_heads == 1) else m.effective_tp_size
-        why = None
-        if m.dtype != torch.bfloat16:
-            why = f"dtype {m.dtype} is not bf16"
-        elif lay.type != KVCacheLayoutType.BLOCKFIRST:
-            why = "host layout is not BLOCKFIRST"
-        elif (lay.get_chunk_size() // slices) % 1024:
-            why = "chunk elements per rank are not a multiple of 1024"
-        elif self.env.enable_layerwise_transfer:
-            why = "layerwise restore is enabled"
-        if why:
-            flexkv_logger.warning("compression requested but refused: %s; every tier runs uncompressed", why)
-            return "none"
-        return "bf16_xp"
+        d = choose_codec(requested_quant=c.offload_quant,
+                         compression_enabled=bool(c.enable_compression or self.env.enable_compression),
+                         dtype=m.dtype, host_layout_type=lay.type, chunk_elems_per_rank=lay.get_chunk_size() // slices,
+                         itemsize=m.dtype.itemsize, layerwise=bool(self.env.enable_layerwise_transfer))
+        if d.reason:
+            flexkv_logger.warning("host codec refused: %s; every tier runs uncompressed", d.reason)
+        if d.warning:
+            flexkv_logger.warning("%s", d.warning)
+        return d.codec
 
     def _alloc_host(self) -> None:
         c = self.cache_config

@@ -235,7 +235,7 @@ class QuantGpuHostWorker(TransferWorker):
         super().__init__()
         import torch
         self.h2d = h2d
-        self.name = "h2d-fp8" if h2d else "d2h-fp8"
+        self.name = ("h2d-" if h2d else "d2h-") + storage.host.quant
         self.regs = [storage.gpu_regs[key][r] for r in sorted(storage.gpu_regs[key])]
         host = storage.host
         if host.layout.type != KVCacheLayoutType.BLOCKFIRST:
@@ -243,6 +243,9 @@ class QuantGpuHostWorker(TransferWorker):
         self.codec = host.quant
         self.layers_total = self.regs[0].num_layers
         self.shared = model_config.use_mla or model_config.num_kv_heads == 1
+        from .compression import build_compressors
+        self.strategy = build_compressors(host, self.layers_total, self.regs[0].kv_dim, len(self.regs), self.shared)
+        self.strategy.attach(self)
         n = 1 if self.shared else model_config.effective_tp_size
         self.host = host
         self.layer_stride, self.kv_stride, self.tp_stride = host.layer_stride // n, host.kv_stride // n, \
@@ -281,15 +284,7 @@ class QuantGpuHostWorker(TransferWorker):
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             with torch.cuda.device(reg.device_id):
                 e0.record(st)
-                if self.codec == "bf16_xp":
-                    # size table layout [block][rank][layer][kv][tile]: a rank sees it as a table of
-                    # R*L "layers" and starts r*L*K*tiles entries in
-                    R = 1 if self.shared else len(self.regs)
-                    r_off = 0 if self.shared else i * self.layers_total * reg.kv_dim * self.host.tiles_per_chunk
-                    _native.C.kv_compress_bf16(params, self.host.size_table.data_ptr() + 4 * r_off,
-                                               R * self.layers_total, self.num_ctas, st.cuda_stream)
-                else:
-                    _native.C.kv_quant_fp8(params, self.num_ctas, st.cuda_stream)
+                self.strategy.run(params, i, self.num_ctas, st.cuda_stream)
                 e1.record(st)
             evs.append((e0, e1, reg.device_id))
             nbytes += int(cpu.size) * nl * reg.kv_dim * reg.chunk_bytes
