@@ -20,31 +20,9 @@
 namespace py = pybind11;
 using namespace fkv;
 
-using I64Array = py::array_t<int64_t, py::array::c_style | py::array::forcecast>;
-using U64Array = py::array_t<uint64_t, py::array::c_style | py::array::forcecast>;
-
 void init_kernel_bindings(py::module_& m);     // bindings_kernels.cpp
 void init_layerwise_bindings(py::module_& m);  // bindings_layerwise.cpp
-
-template <typename T>
-static py::array_t<T> to_array(const std::vector<T>& v) {
-  py::array_t<T> a((py::ssize_t)v.size());
-  if (!v.empty()) std::memcpy(a.mutable_data(), v.data(), v.size() * sizeof(T));
-  return a;
-}
-
-static py::object handle_to_py(NodeHandle h) {
-  if (h == kNullHandle) return py::none();
-  return py::int_(h);
-}
-static NodeHandle handle_from_py(const py::object& o) {
-  if (o.is_none()) return kNullHandle;
-  return o.cast<uint64_t>();
-}
-
-struct PyMatch {
-  MatchResult r;
-};
+void init_dist_bindings(py::module_& m);       // bindings_dist.cpp
 
 PYBIND11_MODULE(_C, m) {
   m.doc() = "flexkv_b200 native core (sm_100a kernels + C++ control plane)";
@@ -318,4 +296,5 @@ PYBIND11_MODULE(_C, m) {
 
   init_kernel_bindings(m);
   init_layerwise_bindings(m);
+  init_dist_bindings(m);
 }

@@ -1,13 +1,42 @@
 // dict -> native struct helpers shared by the binding translation units
 #pragma once
+#include <pybind11/numpy.h>
 #include <pybind11/pybind11.h>
 #include <pybind11/stl.h>
+
+#include <cstring>
 
 #include "ssd_io.h"
 #include "transfer_group.h"
 
+#include "radix_index.h"
+
 namespace fkv {
 namespace py = pybind11;
+
+using I64Array = py::array_t<int64_t, py::array::c_style | py::array::forcecast>;
+using U64Array = py::array_t<uint64_t, py::array::c_style | py::array::forcecast>;
+
+template <typename T>
+inline py::array_t<T> to_array(const std::vector<T>& v) {
+  py::array_t<T> a((py::ssize_t)v.size());
+  if (!v.empty()) std::memcpy(a.mutable_data(), v.data(), v.size() * sizeof(T));
+  return a;
+}
+
+inline py::object handle_to_py(NodeHandle h) {
+  if (h == kNullHandle) return py::none();
+  return py::int_(h);
+}
+inline NodeHandle handle_from_py(const py::object& o) {
+  if (o.is_none()) return kNullHandle;
+  return o.cast<uint64_t>();
+}
+
+// MatchResult as Python sees it (shared by the plain and the lease-aware index bindings)
+struct PyMatch {
+  MatchResult r;
+};
 
 inline std::vector<GpuSide> parse_gpu_sides(const py::list& gpus) {
   std::vector<GpuSide> gs;

@@ -11,7 +11,6 @@
 
 namespace py = pybind11;
 using namespace fkv;
-using I64Array = py::array_t<int64_t, py::array::c_style | py::array::forcecast>;
 
 void init_layerwise_bindings(py::module_& m) {
   py::class_<LayerwiseResult>(m, "LayerwiseResult")

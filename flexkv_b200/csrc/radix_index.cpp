@@ -264,11 +264,42 @@ NodeHandle RadixIndex::insert(const int64_t* physical, int64_t num_physical, con
   return make_handle(nn);
 }
 
-bool RadixIndex::evictable(int32_t idx) const {
+bool RadixIndex::evictable_ignoring_veto(int32_t idx) const {
   if (idx == 0) return false;
   const Node& n = nodes_[idx];
   return n.live && n.leaf() && n.lock_cnt == 0 && n.ready;
 }
+
+bool RadixIndex::evictable(int32_t idx) const {
+  if (!evictable_ignoring_veto(idx)) return false;
+  const Node& n = nodes_[idx];
+  return !veto_ || !veto_(n.hashes.data(), n.hashes.size());
+}
+
+std::vector<std::vector<uint64_t>> RadixIndex::vetoed_leaves(int64_t min_blocks) const {
+  std::vector<int32_t> cand;
+  if (!veto_) return {};
+  for (int32_t l : leaves_)
+    if (evictable_ignoring_veto(l) && !evictable(l)) cand.push_back(l);
+  std::sort(cand.begin(), cand.end(), [this](int32_t x, int32_t y) {
+    const Node& a = nodes_[x];
+    const Node& b = nodes_[y];
+    if (evict_before(a, b)) return true;
+    if (evict_before(b, a)) return false;
+    return a.serial < b.serial;
+  });
+  std::vector<std::vector<uint64_t>> out;
+  int64_t got = 0;
+  for (int32_t idx : cand) {
+    if (got >= min_blocks) break;
+    out.push_back(nodes_[idx].hashes);
+    got += (int64_t)nodes_[idx].size();
+  }
+  return out;
+}
+
+const std::vector<uint64_t>& RadixIndex::node_hashes(NodeHandle h) const { return nodes_[resolve_or_throw(h)].hashes; }
+const std::vector<int64_t>& RadixIndex::node_blocks(NodeHandle h) const { return nodes_[resolve_or_throw(h)].blocks; }
 
 bool RadixIndex::evict_before(const Node& a, const Node& b) const {
   switch (policy_) {

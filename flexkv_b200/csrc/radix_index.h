@@ -9,6 +9,7 @@
 // O(1) instead of by walking parent links.
 #pragma once
 #include <cstdint>
+#include <functional>
 #include <memory>
 #include <mutex>
 #include <stdexcept>
@@ -55,6 +56,17 @@ class RadixIndex {
                     int64_t num_insert, bool ready, const MatchResult* match);
 
   EvictResult evict(int64_t num_blocks);
+
+  // Optional veto consulted for every eviction candidate: return true to keep the node
+  // (used by the lease layer: blocks a peer may still be reading must stay). The callback
+  // sees the node's block hashes and must not call back into the index.
+  using EvictVeto = std::function<bool(const uint64_t* hashes, size_t n)>;
+  void set_evict_veto(EvictVeto v) { veto_ = std::move(v); }
+  // Hash lists of leaves that only the veto keeps alive, in eviction order, until they
+  // cover at least min_blocks blocks (no cascading to parents).
+  std::vector<std::vector<uint64_t>> vetoed_leaves(int64_t min_blocks) const;
+  const std::vector<uint64_t>& node_hashes(NodeHandle h) const;
+  const std::vector<int64_t>& node_blocks(NodeHandle h) const;
 
   void lock(NodeHandle h);
   void unlock(NodeHandle h);
@@ -118,6 +130,7 @@ class RadixIndex {
   void remove_child(int32_t parent, uint64_t head);
   int32_t split(int32_t idx, int64_t prefix_len);  // returns the new prefix node
   bool evictable(int32_t idx) const;
+  bool evictable_ignoring_veto(int32_t idx) const;
   bool evict_before(const Node& a, const Node& b) const;  // a leaves before b
   void validate_insert_target(const uint64_t* hashes, int64_t n, int64_t num_insert, const MatchResult& m,
                               int32_t idx) const;
@@ -135,6 +148,7 @@ class RadixIndex {
   int64_t total_blocks_ = 0;
   int64_t live_nodes_ = 0;
   uint64_t next_serial_ = 0;
+  EvictVeto veto_;
 };
 
 // Fixed-capacity id pool with duplicate / double-free detection
