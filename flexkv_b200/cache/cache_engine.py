@@ -210,7 +210,15 @@ class GlobalCacheEngine:
         self.cpu_cache_engine: Optional[CacheEngine] = None
         self.ssd_cache_engine: Optional[CacheEngine] = None
         self.remote_cache_engine: Optional[CacheEngine] = None
-        if cache_config.enable_cpu:
+        self.node_registry = None
+        if cache_config.enable_cpu and cache_config.enable_p2p_cpu:
+            # host blocks are published to the other nodes of the registry and theirs can be pulled
+            from .hie_cache_engine import HierarchyLRCacheEngine, get_node_registry
+            self.node_registry = get_node_registry(cache_config, model_config)
+            self.cpu_cache_engine = HierarchyLRCacheEngine(DeviceType.CPU, cache_config.num_cpu_blocks,
+                                                           registry=self.node_registry, **common)
+            self.cache_engines[DeviceType.CPU] = self.cpu_cache_engine
+        elif cache_config.enable_cpu:
             self.cpu_cache_engine = CacheEngine(DeviceType.CPU, cache_config.num_cpu_blocks, **common)
             self.cache_engines[DeviceType.CPU] = self.cpu_cache_engine
         if cache_config.enable_ssd:
@@ -262,6 +270,15 @@ class GlobalCacheEngine:
             for e in self.cache_engines.values():
                 e.reset()
             self._update_mempool_metrics()
+
+    def shutdown(self) -> None:
+        """Leaves the cross-node registry (withdraws published blocks, stops the heartbeat)."""
+        for e in self.cache_engines.values():
+            if hasattr(e, "shutdown"):
+                e.shutdown()
+        if self.node_registry is not None:
+            self.node_registry.stop(unregister=True)
+            self.node_registry = None
 
     def _prepare(self, token_ids: np.ndarray, token_mask: Optional[np.ndarray], slot_mapping: Optional[np.ndarray]
                  ) -> Tuple[np.ndarray, np.ndarray, int]:
@@ -385,6 +402,16 @@ class GlobalCacheEngine:
             r_hit, remote_m = self._remote_hit(seq, bend)
             f3_lo = max(bstart, end)
             f3 = max(0, r_hit - f3_lo)
+        # fragment 3 may instead come from another node's host pool when that node holds a longer prefix
+        peer_host_nids = None
+        if self.node_registry is not None and not cpu_only and not use_gds_early:
+            pm = cpu.match_remote(seq, bend)
+            if pm.num_matched_blocks > max(end, f3_lo + f3):
+                f3_lo = max(bstart, end)
+                f3 = pm.num_matched_blocks - f3_lo
+                peer_host_nids = pm.node_ids[f3_lo:f3_lo + f3]
+                peer_host_src = pm.physical_blocks[f3_lo:f3_lo + f3]
+                remote_m = None
         if f0 + f1 + f2 + f3 == 0:
             return None
         graph = TransferOpGraph()
@@ -448,8 +475,13 @@ class GlobalCacheEngine:
         if f3 > 0:
             hashes3 = seq.block_hashes[f3_lo:f3_lo + f3]
             src3 = remote_m.physical_blocks[f3_lo:f3_lo + f3] if remote_m is not None else np.zeros(f3, dtype=np.int64)
-            remote_op = TransferOp(graph.graph_id, TransferType.REMOTE2H, src3, staging3, dp_client_id=dp_client_id,
-                                   block_hashes=hashes3)
+            if peer_host_nids is not None:
+                remote_op = TransferOp(graph.graph_id, TransferType.PEERH2H, peer_host_src, staging3,
+                                       dp_client_id=dp_client_id, block_hashes=hashes3,
+                                       remote_node_ids=peer_host_nids)
+            else:
+                remote_op = TransferOp(graph.graph_id, TransferType.REMOTE2H, src3, staging3,
+                                       dp_client_id=dp_client_id, block_hashes=hashes3)
             graph.add_transfer_op(remote_op)
             if remote_m is not None:
                 plan.nodes.setdefault(DeviceType.REMOTE, []).append((remote_m.last_ready_node, 0))

@@ -139,6 +139,7 @@ class KVTaskEngine:
     def shutdown(self) -> None:
         for h in self.transfer_handles:
             h.shutdown()
+        self.cache_engine.shutdown()
         self.tracer.close()
 
     def set_metrics_collector(self, collector) -> None:

@@ -153,6 +153,13 @@ class StorageEngine:
         block_bytes, layer_stride, kv_stride, chunk, lay = self._host_geometry()
         total = self._host_total_bytes(block_bytes, lay)
         backing = os.environ.get("FLEXKV_HUGEPAGE_FILE", "") if c.use_hugepage_cpu_buffer else ""
+        self._owned_backing = ""
+        if c.enable_p2p_cpu and not backing:
+            # other nodes of the box map this pool to pull blocks out of it
+            import uuid
+            backing = f"/dev/shm/flexkv_host_{os.getpid()}_{uuid.uuid4().hex[:8]}"
+            self._owned_backing = backing
+        self.host_backing_file = backing
         try:
             region = _native.C.host_region_alloc(total, hugepage=c.use_hugepage_cpu_buffer,
                                                  hugepage_bytes=c.hugepage_size_bytes, numa_node=self._numa_node,
@@ -265,6 +272,11 @@ class StorageEngine:
             except Exception:  # noqa: BLE001
                 pass
             self.host = None
+            if getattr(self, "_owned_backing", ""):
+                try:
+                    os.unlink(self._owned_backing)
+                except OSError:
+                    pass
         if self.ssd is not None:
             files = [f for d in self.ssd.files for f in d]
             self.ssd = None

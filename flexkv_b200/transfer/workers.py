@@ -405,6 +405,67 @@ class RemoteWorker(TransferWorker):
                          error="" if ok else f"{len(res) - sum(res)} remote block(s) failed")
 
 
+class PeerHostWorker(TransferWorker):
+    """PEERH2H: pulls blocks out of other nodes' host pools into this node's pool.
+    Inside one box every pool is a shared-memory file whose name the owner published in
+    the registry; blocks are grouped by owner and contiguous segment and copied with
+    plain memcpy (the reference moves them with RDMA reads, flexkv/transfer/worker.py:
+    2920-3029, segment grouping flexkv/transfer/utils.py:41-98). The owner's lease keeps
+    the blocks in place while they are read."""
+
+    name = "peerh2h"
+
+    def __init__(self, storage, registry) -> None:
+        super().__init__()
+        self.storage, self.registry = storage, registry
+        self._maps: Dict[int, Tuple[np.ndarray, int, int]] = {}
+
+    def _pool_of(self, nid: int):
+        ent = self._maps.get(nid)
+        if ent is not None:
+            return ent
+        meta = self.registry.get_node_meta(nid)
+        if not meta or not meta.get("pool_file"):
+            raise RuntimeError(f"node {nid} has no host pool in the registry")
+        if int(meta["block_bytes"]) != self.storage.host.block_bytes or \
+                meta.get("codec", "none") != self.storage.host.quant:
+            raise RuntimeError(f"node {nid} uses a different host block format")
+        mm = np.memmap(meta["pool_file"], dtype=np.uint8, mode="r",
+                       shape=(int(meta["num_blocks"]) * int(meta["block_bytes"]),))
+        ent = (mm, int(meta["block_bytes"]), int(meta["num_blocks"]))
+        self._maps[nid] = ent
+        return ent
+
+    def execute(self, op: TransferOp) -> OpOutcome:
+        src, dst, nids = op.src_block_ids, op.dst_block_ids, op.remote_node_ids
+        if nids is None or len(nids) != len(src) or len(src) != len(dst):
+            return OpOutcome(False, error="peer host op without owner ids")
+        host = self.storage.host
+        mine = host.as_numpy()
+        bb = host.block_bytes
+        results = [False] * len(src)
+        i, n = 0, len(src)
+        err = ""
+        while i < n:
+            j = i + 1
+            while j < n and nids[j] == nids[i] and src[j] == src[j - 1] + 1 and dst[j] == dst[j - 1] + 1:
+                j += 1
+            try:
+                pool, _, nblk = self._pool_of(int(nids[i]))
+                if src[i] < 0 or src[j - 1] >= nblk:
+                    raise RuntimeError(f"block {int(src[j - 1])} outside node {int(nids[i])}'s pool")
+                mine[int(dst[i]) * bb:int(dst[j - 1] + 1) * bb] = pool[int(src[i]) * bb:int(src[j - 1] + 1) * bb]
+                for k in range(i, j):
+                    results[k] = True
+            except (RuntimeError, OSError, ValueError) as e:
+                err = str(e)
+                self._maps.pop(int(nids[i]), None)
+            i = j
+        ok = all(results)
+        return OpOutcome(ok, block_results=tuple(results), num_bytes=sum(results) * bb,
+                         error="" if ok else f"{n - sum(results)} peer block(s) failed: {err}")
+
+
 _GDS_PROBE: Optional[Tuple[bool, str]] = None
 
 
@@ -601,6 +662,10 @@ def build_workers(storage, model_config: ModelConfig, cache_config: CacheConfig
         if backend is not None:
             workers[(WorkerKey(0, 0), TransferType.REMOTE2H)] = RemoteWorker(storage, backend, True)
             workers[(WorkerKey(0, 0), TransferType.H2REMOTE)] = RemoteWorker(storage, backend, False)
+    if cache_config.enable_p2p_cpu and storage.host is not None:
+        from ..cache.hie_cache_engine import get_node_registry
+        workers[(WorkerKey(0, 0), TransferType.PEERH2H)] = PeerHostWorker(
+            storage, get_node_registry(cache_config, model_config))
     if storage.ssd is not None:
         k0 = WorkerKey(0, 0)
         workers[(k0, TransferType.DISK2H)] = SsdWorker(storage, True)

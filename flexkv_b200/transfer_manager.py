@@ -11,6 +11,7 @@ PULL socket carrying exported tensor handles (flexkv/transfer_manager.py:77-83,
 """
 from __future__ import annotations
 
+import os
 import threading
 import time
 from typing import Any, List, Optional
@@ -88,6 +89,14 @@ class TransferManager:
                                          numa_node=numa)
             for r in self._pending_regs:
                 self.storage.register_gpu_blocks(r)
+            if self.cache_config.enable_p2p_cpu and self.storage.host is not None:
+                # what a peer needs to read this node's host pool
+                from .cache.hie_cache_engine import get_node_registry
+                reg = get_node_registry(self.cache_config, self.model_config)
+                reg.set_node_meta(dict(pool_file=self.storage.host_backing_file,
+                                       block_bytes=self.storage.host.block_bytes,
+                                       num_blocks=self.storage.host.num_blocks, pid=os.getpid(),
+                                       codec=self.storage.host.quant))
             self.engine = TransferEngine(self.storage, self.model_config, self.cache_config)
             if self._metrics is not None:
                 self.engine.set_metrics_collector(self._metrics)

@@ -1,0 +1,157 @@
+"""Two nodes of one box share prefixes through the registry: node B restores blocks that
+only node A's host pool holds (PEERH2H), node liveness, stale-node cleanup and the
+registry served over ZeroMQ (reference flow: flexkv/cache/hie_cache_engine.py:239-334,
+flexkv/cache/redis_meta.py:296-430,514-617; worker flexkv/transfer/worker.py:2920-3029)."""
+import time
+import uuid
+
+import numpy as np
+import pytest
+import torch
+
+from flexkv_b200 import CacheConfig, KVManager
+from flexkv_b200.cache.registry import (NodeRegistry, RegistryClient, RegistryMetaChannel, RegistryServer,
+                                        RegistryStore)
+from flexkv_b200.models import KVShape, alloc_paged_cache, make_model_config
+
+T = 4
+
+
+def slots(blocks):
+    return np.repeat(np.asarray(blocks, dtype=np.int64), T) * T + np.tile(np.arange(T), len(blocks))
+
+
+def start_node(name, seed):
+    shape = KVShape("p", 2, 2, 16, tokens_per_block=T)
+    cfg = CacheConfig(tokens_per_block=T, num_cpu_blocks=24, enable_p2p_cpu=True, redis_host=f"inproc:{name}")
+    mgr = KVManager(make_model_config(shape), cfg, require_gpu=True)
+    kv, layout = alloc_paged_cache(shape, 64, "cpu", "vllm", fill="normal", seed=seed)
+    mgr.register_gpu_tensors(kv, layout)
+    mgr.start(); mgr.wait_ready(30)
+    return mgr, kv
+
+
+def test_node_b_restores_from_node_a_host_pool():
+    name = uuid.uuid4().hex
+    a, kva = start_node(name, 1)
+    b, kvb = start_node(name, 2)
+    try:
+        ea = a.kv_task_engine.cache_engine.cpu_cache_engine
+        eb = b.kv_task_engine.cache_engine.cpu_cache_engine
+        assert ea.node_id != eb.node_id
+        tok = np.arange(10 * T, dtype=np.int64) + 1000
+        src = np.array([5, 6, 7, 20, 21, 3, 40, 41, 42, 43])
+        tid = a.put_async(tok, slots(src))
+        assert a.wait(tid, completely=True)[tid].status.value == "success"
+        # B already holds the first 3 blocks itself (different bytes do not matter: same tokens)
+        for l in range(2):
+            kvb[l][:, src[:3]] = kva[l][:, src[:3]]
+        tid = b.put_async(tok[:3 * T], slots(src[:3]))
+        assert b.wait(tid, completely=True)[tid].status.value == "success"
+        ea.refresh(); eb.refresh()
+        from flexkv_b200.common.block import SequenceMeta
+        local, remote, winner = eb.match_all(SequenceMeta(tok, T))
+        assert winner == "remote" and remote.num_matched_blocks == 10 and local.num_ready_matched_blocks == 3
+        assert set(remote.node_ids.tolist()) == {ea.node_id}
+
+        tid, mask = b.get_match(tok)
+        assert int(mask.sum()) == 10 * T
+        kinds = sorted(o.transfer_type.value for o in b.kv_task_engine.tasks[tid].graph.ops())
+        assert kinds == ["H2D", "PEERH2H"]
+        dst = np.arange(50, 60)
+        for t in kvb:
+            t[:, dst] = 0
+        b.launch(tid, slots(dst))
+        assert b.wait(tid)[tid].status.value == "success"
+        for l in range(2):
+            assert torch.equal(kvb[l][:, dst], kva[l][:, src])
+        # the pulled blocks were adopted by B's host tier: the next get needs no peer
+        tid, mask = b.get_match(tok)
+        assert [o.transfer_type.value for o in b.kv_task_engine.tasks[tid].graph.ops()] == ["H2D"]
+        b.cancel(tid)
+    finally:
+        a.shutdown()
+        b.shutdown()
+
+
+def test_peer_that_left_is_not_offered_and_a_vanished_pool_fails_cleanly():
+    name = uuid.uuid4().hex
+    a, kva = start_node(name, 1)
+    b, kvb = start_node(name, 2)
+    try:
+        ea = a.kv_task_engine.cache_engine.cpu_cache_engine
+        eb = b.kv_task_engine.cache_engine.cpu_cache_engine
+        tok = np.arange(6 * T, dtype=np.int64) + 5000
+        tid = a.put_async(tok, slots(range(6)))
+        assert a.wait(tid, completely=True)[tid].status.value == "success"
+        ea.refresh(); eb.refresh()
+        tid, mask = b.get_match(tok)
+        assert int(mask.sum()) == 6 * T
+        # the owner's pool disappears between planning and the copy (host-side fault): the op
+        # fails per block, the get reports failure and B's staging blocks return to its pool
+        w = next(w for (k, tt), w in b.transfer_manager.engine._workers.items() if tt.value == "PEERH2H")
+        real = w.registry.get_node_meta
+        w.registry.get_node_meta = lambda nid, pp_rank=None: {}
+        free_before = eb.mempool.num_free_blocks
+        b.launch(tid, slots(range(30, 36)))
+        r = b.wait(tid)[tid]
+        assert r.status.value == "failed"
+        w.registry.get_node_meta = real
+        assert eb.mempool.num_free_blocks == free_before + 6
+        # A leaves the box: its records are withdrawn and B stops offering them
+        a.shutdown()
+        eb.refresh()
+        tid, mask = b.get_match(tok)
+        assert int(mask.sum()) == 0
+        b.cancel(tid)
+    finally:
+        a.shutdown()
+        b.shutdown()
+
+
+def test_registry_liveness_and_stale_cleanup_with_a_fake_clock():
+    now = [1000.0]
+    store = RegistryStore(clock=lambda: now[0])
+    c = RegistryClient(store)
+    n1 = NodeRegistry(c, ip="10.0.0.1", node_ttl_seconds=5, instance_uuid="u1")
+    n2 = NodeRegistry(c, ip="10.0.0.2", node_ttl_seconds=5, instance_uuid="u2")
+    id1, id2 = n1.register(), n2.register()
+    assert (id1, id2) == (1, 2) and n1.active_nodes() == [1, 2]
+    ch = RegistryMetaChannel(c)
+    ch.publish(id1, [(0, 7, id1, 0xABC, 99999, 0)])
+    n1.set_node_meta(dict(pool_file="/dev/shm/x", block_bytes=4096, num_blocks=8))
+    assert n2.get_node_meta(id1)["pool_file"] == "/dev/shm/x"
+    assert store.scan("CPUB:block:1:") == ["CPUB:block:1:0000000000000abc"]
+    now[0] += 4
+    assert c.expire(f"node:{id2}", 5)              # node 2 heartbeats, node 1 does not
+    now[0] += 2
+    assert n2.active_nodes() == [2] and ch.list_nodes() == [2]
+    assert not c.expire(f"node:{id1}", 5)          # an expired node is not resurrected
+    # the same instance registers again: new id, old records swept
+    c.hset(f"node:{id1}", dict(node_id=id1, ip="10.0.0.1", uuid="u1", status="active"))
+    id1b = n1.register()
+    assert id1b == 3 and store.scan("CPUB:block:1:") == [] and n1.active_nodes() == [2, 3]
+    # reset barrier: both live nodes must acknowledge
+    assert not n1.reset_barrier(1, timeout=0.05)
+    n2.client.hset("reset:1", {str(id2): 1})
+    assert n1.reset_barrier(1, timeout=0.5)
+
+
+def test_registry_over_zeromq(tmp_path):
+    pytest.importorskip("zmq")
+    ep = f"ipc://{tmp_path}/reg.sock"
+    srv = RegistryServer(ep)
+    try:
+        c1, c2 = RegistryClient(ep), RegistryClient(ep)
+        assert c1.incr("global:node_id") == 1 and c2.incr("global:node_id") == 2
+        c1.hset("node:1", dict(node_id=1, status="active"), ttl=0.2)
+        assert c2.hgetall("node:1")["status"] == "active"
+        ch = RegistryMetaChannel(c1)
+        ch.publish(1, [(0, 1, 1, 11, 5000, 0), (11, 2, 1, 12, 5000, 0)])
+        assert sorted(r[3] for r in RegistryMetaChannel(c2).load(1)) == [11, 12]
+        time.sleep(0.3)
+        assert c2.hgetall("node:1") == {}
+        with pytest.raises(RuntimeError):
+            c1._call("no_such_command")
+    finally:
+        srv.close()
