@@ -110,7 +110,10 @@ PYBIND11_MODULE(_C, m) {
       .def_property_readonly("last_node_matched_length", [](const PyMatch& p) { return p.r.last_node_matched_length; })
       .def_property_readonly("last_ready_node", [](const PyMatch& p) { return handle_to_py(p.r.last_ready_node); })
       .def_property_readonly("last_node", [](const PyMatch& p) { return handle_to_py(p.r.last_node); })
-      .def_property_readonly("physical_blocks", [](const PyMatch& p) { return to_array(p.r.physical_blocks); });
+      .def_property_readonly("physical_blocks", [](const PyMatch& p) { return to_array(p.r.physical_blocks); })
+      .def_property_readonly("last_swa_node", [](const PyMatch& p) { return handle_to_py(p.r.last_swa_node); })
+      .def_property_readonly("swa_hit_blocks", [](const PyMatch& p) { return p.r.swa_hit_blocks; })
+      .def_property_readonly("swa_slot", [](const PyMatch& p) { return p.r.swa_slot; });
 
   py::class_<RadixIndex>(m, "RadixIndex")
       .def(py::init([](int tpb, int64_t max_blocks, const std::string& policy, double reward, uint32_t slru) {
@@ -138,6 +141,20 @@ PYBIND11_MODULE(_C, m) {
              EvictResult r = t.evict(n);
              return py::make_tuple(to_array(r.blocks), to_array(r.hashes));
            })
+      .def("set_swa", [](RadixIndex& t, py::object h, int32_t slot) { t.set_swa(handle_from_py(h), slot); })
+      .def("has_swa", [](RadixIndex& t, py::object h) { return t.has_swa(handle_from_py(h)); })
+      .def("swa_slot", [](RadixIndex& t, py::object h) { return t.swa_slot(handle_from_py(h)); })
+      .def("swa_lock_cnt", [](RadixIndex& t, py::object h) { return t.swa_lock_cnt(handle_from_py(h)); })
+      .def("lock_swa", [](RadixIndex& t, py::object h) { t.lock_swa(handle_from_py(h)); })
+      .def("unlock_swa", [](RadixIndex& t, py::object h) { t.unlock_swa(handle_from_py(h)); })
+      .def("evict_swa", [](RadixIndex& t, int64_t n) {
+             std::vector<int64_t> blocks;
+             std::vector<uint64_t> hashes;
+             int64_t freed = t.evict_swa(n, &blocks, &hashes);
+             return py::make_tuple(to_array(blocks), to_array(hashes), freed);
+           })
+      .def("drain_freed_swa_slots", [](RadixIndex& t) { return to_array(t.drain_freed_swa_slots()); })
+      .def("total_swa_slots", &RadixIndex::total_swa_slots)
       .def("lock", [](RadixIndex& t, py::object h) { t.lock(handle_from_py(h)); })
       .def("unlock", [](RadixIndex& t, py::object h) { t.unlock(handle_from_py(h)); })
       .def("set_ready", [](RadixIndex& t, py::object h, bool ready, int64_t len) {

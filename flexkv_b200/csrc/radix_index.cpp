@@ -52,6 +52,9 @@ int32_t RadixIndex::alloc_node() {
   n.hit_count = 0;
   n.ready = false;
   n.parent = -1;
+  n.swa_slot = -1;
+  n.swa_lock = 0;
+  n.on_swa_lru = false;
   int64_t t = now_us();
   n.grace_us = n.last_access_us = n.creation_us = t;
   n.serial = ++next_serial_;
@@ -60,6 +63,7 @@ int32_t RadixIndex::alloc_node() {
 }
 
 void RadixIndex::free_node(int32_t idx) {
+  drop_swa(idx);
   Node& n = nodes_[idx];
   n.live = false;
   ++n.gen;  // invalidates every outstanding handle
@@ -161,6 +165,13 @@ MatchResult RadixIndex::match_prefix(const uint64_t* hashes, int64_t n, bool upd
     if (ready_chain && node.ready) {
       r.num_ready_matched = prefix;
       r.last_ready_node = make_handle(c);
+      // a snapshot sits at the node's trailing block: only a fully matched node exposes it
+      if (node.swa_slot >= 0 && m == (int64_t)node.size()) {
+        r.last_swa_node = make_handle(c);
+        r.swa_hit_blocks = prefix;
+        r.swa_slot = node.swa_slot;
+        if (update_cache_info) swa_touch(c);
+      }
     } else {
       ready_chain = false;
     }
@@ -339,7 +350,8 @@ EvictResult RadixIndex::evict(int64_t num_blocks) {
     Node& node = nodes_[idx];
     int64_t sz = (int64_t)node.size();
     if (sz > need) {
-      // partial shrink: drop the tail, the node stays a leaf
+      // partial shrink: drop the tail, the node stays a leaf; its snapshot described the dropped tail
+      drop_swa(idx);
       out.blocks.insert(out.blocks.end(), node.blocks.end() - need, node.blocks.end());
       out.hashes.insert(out.hashes.end(), node.hashes.end() - need, node.hashes.end());
       node.blocks.resize((size_t)(sz - need));
@@ -409,8 +421,94 @@ std::vector<int64_t> RadixIndex::reset() {
   }
   nodes_[0].children.reset();
   leaves_.clear();
+  swa_lru_.clear();
+  freed_swa_.clear();  // the owner re-arms its slot pool as a whole on reset
   total_blocks_ = 0;
   return all;
+}
+
+// ---- sliding-window snapshots ---------------------------------------------------
+
+void RadixIndex::drop_swa(int32_t idx) {
+  Node& n = nodes_[idx];
+  if (n.swa_slot >= 0) freed_swa_.push_back(n.swa_slot);
+  n.swa_slot = -1;
+  n.swa_lock = 0;
+  if (n.on_swa_lru) {
+    swa_lru_.erase(n.swa_it);
+    n.on_swa_lru = false;
+  }
+}
+
+void RadixIndex::swa_touch(int32_t idx) {
+  Node& n = nodes_[idx];
+  if (n.on_swa_lru) swa_lru_.erase(n.swa_it);
+  swa_lru_.push_back(idx);
+  n.swa_it = std::prev(swa_lru_.end());
+  n.on_swa_lru = true;
+}
+
+void RadixIndex::set_swa(NodeHandle h, int32_t slot) {
+  int32_t idx = resolve_or_throw(h);
+  if (idx == 0) throw std::invalid_argument("radix index: the root carries no window snapshot");
+  if (slot < 0) throw std::invalid_argument("radix index: negative snapshot slot");
+  Node& n = nodes_[idx];
+  if (n.swa_slot >= 0 && n.swa_slot != slot) freed_swa_.push_back(n.swa_slot);
+  n.swa_slot = slot;
+  swa_touch(idx);
+}
+
+bool RadixIndex::has_swa(NodeHandle h) const {
+  int32_t idx = resolve(h);
+  return idx > 0 && nodes_[idx].swa_slot >= 0;
+}
+int32_t RadixIndex::swa_slot(NodeHandle h) const { return nodes_[resolve_or_throw(h)].swa_slot; }
+int RadixIndex::swa_lock_cnt(NodeHandle h) const { return nodes_[resolve_or_throw(h)].swa_lock; }
+
+void RadixIndex::lock_swa(NodeHandle h) {
+  Node& n = nodes_[resolve_or_throw(h)];
+  if (n.swa_slot < 0) throw std::runtime_error("radix index: node has no window snapshot to lock");
+  ++n.lock_cnt;
+  ++n.swa_lock;
+}
+
+void RadixIndex::unlock_swa(NodeHandle h) {
+  int32_t idx = resolve(h);
+  if (idx < 0) return;
+  Node& n = nodes_[idx];
+  if (n.swa_lock > 0) --n.swa_lock;
+  if (n.lock_cnt > 0) --n.lock_cnt;
+}
+
+int64_t RadixIndex::evict_swa(int64_t want, std::vector<int64_t>* freed_full, std::vector<uint64_t>* freed_hashes) {
+  int64_t freed = 0;
+  for (auto it = swa_lru_.begin(); it != swa_lru_.end() && freed < want;) {
+    int32_t idx = *it;
+    ++it;  // the entry may be erased below
+    Node& n = nodes_[idx];
+    if (n.swa_lock > 0) continue;
+    if (n.leaf() && n.lock_cnt == 0 && n.ready && (!veto_ || !veto_(n.hashes.data(), n.hashes.size()))) {
+      // a leaf is only worth keeping for its snapshot: delete it whole
+      if (freed_full) freed_full->insert(freed_full->end(), n.blocks.begin(), n.blocks.end());
+      if (freed_hashes) freed_hashes->insert(freed_hashes->end(), n.hashes.begin(), n.hashes.end());
+      total_blocks_ -= (int64_t)n.size();
+      stat_evict_blocks += n.size();
+      int32_t parent = n.parent;
+      uint64_t head = n.hashes.front();
+      free_node(idx);  // drops the snapshot too
+      remove_child(parent, head);
+    } else {
+      drop_swa(idx);
+    }
+    ++freed;
+  }
+  return freed;
+}
+
+std::vector<int32_t> RadixIndex::drain_freed_swa_slots() {
+  std::vector<int32_t> out;
+  out.swap(freed_swa_);
+  return out;
 }
 
 int64_t RadixIndex::total_ready_blocks() const {

@@ -10,6 +10,7 @@
 #pragma once
 #include <cstdint>
 #include <functional>
+#include <list>
 #include <memory>
 #include <mutex>
 #include <stdexcept>
@@ -33,6 +34,10 @@ struct MatchResult {
   NodeHandle last_ready_node = kNullHandle;
   NodeHandle last_node = kNullHandle;   // deepest node with a match (root if none)
   std::vector<int64_t> physical_blocks; // size num_matched
+  // sliding-window state: deepest fully matched ready node that carries a window snapshot
+  NodeHandle last_swa_node = kNullHandle;
+  int64_t swa_hit_blocks = 0;           // prefix length (blocks) that snapshot covers
+  int32_t swa_slot = -1;
 };
 
 struct EvictResult {
@@ -65,6 +70,25 @@ class RadixIndex {
   // Hash lists of leaves that only the veto keeps alive, in eviction order, until they
   // cover at least min_blocks blocks (no cascading to parents).
   std::vector<std::vector<uint64_t>> vetoed_leaves(int64_t min_blocks) const;
+  // ---- sliding-window snapshots mounted on nodes --------------------------------
+  // A node carries at most one snapshot, valid at its trailing block (the window state
+  // after the node's last token). Snapshots are a subset of full KV: freeing a node's
+  // blocks frees its slot; a split leaves the snapshot on the suffix half. Slots that
+  // the index gave up are buffered until drain_freed_swa_slots()
+  // (reference: csrc/radix_tree.h:32-46, csrc/radix_tree.cpp:541-582).
+  void set_swa(NodeHandle h, int32_t slot);
+  bool has_swa(NodeHandle h) const;
+  int32_t swa_slot(NodeHandle h) const;
+  int swa_lock_cnt(NodeHandle h) const;
+  void lock_swa(NodeHandle h);     // takes a full lock as well: full locks >= window locks
+  void unlock_swa(NodeHandle h);
+  // Frees up to n snapshots, least recently used first. Interior nodes and fully locked
+  // leaves only lose the snapshot; an unlocked ready leaf is deleted whole (its blocks
+  // are returned). Returns the number of snapshots freed.
+  int64_t evict_swa(int64_t n, std::vector<int64_t>* freed_full_blocks, std::vector<uint64_t>* freed_hashes);
+  std::vector<int32_t> drain_freed_swa_slots();
+  int64_t total_swa_slots() const { return (int64_t)swa_lru_.size(); }
+
   const std::vector<uint64_t>& node_hashes(NodeHandle h) const;
   const std::vector<int64_t>& node_blocks(NodeHandle h) const;
 
@@ -114,6 +138,10 @@ class RadixIndex {
     bool live = false;
     int64_t grace_us = 0, last_access_us = 0, creation_us = 0;
     uint64_t serial = 0;  // allocation order, the deterministic eviction tie-break
+    int32_t swa_slot = -1;
+    int32_t swa_lock = 0;
+    bool on_swa_lru = false;
+    std::list<int32_t>::iterator swa_it;
     size_t size() const { return hashes.size(); }
     bool leaf() const { return !children || children->empty(); }
   };
@@ -149,6 +177,10 @@ class RadixIndex {
   int64_t live_nodes_ = 0;
   uint64_t next_serial_ = 0;
   EvictVeto veto_;
+  void drop_swa(int32_t idx);           // frees the node's snapshot, if any
+  void swa_touch(int32_t idx);          // moves the node to the recently-used end
+  std::list<int32_t> swa_lru_;          // front = least recently used
+  std::vector<int32_t> freed_swa_;
 };
 
 // Fixed-capacity id pool with duplicate / double-free detection

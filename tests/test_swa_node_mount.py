@@ -1,0 +1,108 @@
+"""Window snapshots mounted on radix nodes (invariants pinned by the reference's
+tests/test_swa_node_mount.py: one snapshot per node at its trailing block, snapshots are
+a subset of full KV, snapshot-only eviction prefers interior nodes, full locks >= window
+locks, match returns the deepest fully matched ready node with a live snapshot)."""
+import numpy as np
+import pytest
+
+from flexkv_b200 import _native
+
+C = _native.C
+
+
+def _h(*v):
+    return np.array(v, dtype=np.uint64)
+
+
+def _p(*v):
+    return np.array(v, dtype=np.int64)
+
+
+def _idx():
+    return C.RadixIndex(2, 64, "lru", 0.0)
+
+
+def test_match_returns_deepest_snapshot():
+    idx = _idx()
+    n1 = idx.insert(_p(0, 1, 2, 3), _h(1, 2, 3, 4), 4, True, None)
+    idx.set_swa(n1, 100)
+    assert idx.has_swa(n1) and idx.swa_slot(n1) == 100 and idx.total_swa_slots() == 1
+    m = idx.match_prefix(_h(1, 2, 3, 4))
+    assert m.num_matched_blocks == 4 and m.last_swa_node == n1 and m.swa_hit_blocks == 4 and m.swa_slot == 100
+    # a partial match of the node must not expose its trailing-block snapshot
+    m = idx.match_prefix(_h(1, 2, 3))
+    assert m.num_matched_blocks == 3 and m.last_swa_node is None and m.swa_hit_blocks == 0
+
+
+def test_split_keeps_snapshot_on_the_suffix_half():
+    idx = _idx()
+    n1 = idx.insert(_p(0, 1, 2, 3), _h(1, 2, 3, 4), 4, True, None)
+    idx.set_swa(n1, 200)
+    h2 = _h(1, 2, 55, 66)
+    m = idx.match_prefix(h2)
+    assert m.num_matched_blocks == 2
+    idx.insert(_p(8, 9), h2, 4, True, m)
+    assert idx.has_swa(n1) and idx.swa_slot(n1) == 200 and idx.node_size(n1) == 2
+    parent = idx.node_parent(n1)
+    assert not idx.is_root(parent) and not idx.has_swa(parent)
+    assert idx.drain_freed_swa_slots().tolist() == []
+    m = idx.match_prefix(_h(1, 2, 3, 4))
+    assert m.last_swa_node == n1 and m.swa_hit_blocks == 4
+    # the prefix half can get its own snapshot; the deeper one still wins on a full match
+    idx.set_swa(parent, 201)
+    assert idx.match_prefix(_h(1, 2, 3, 4)).swa_slot == 200
+    assert idx.match_prefix(_h(1, 2, 77)).swa_slot == 201
+
+
+def test_full_eviction_frees_the_snapshot_slot():
+    idx = _idx()
+    na = idx.insert(_p(0, 1), _h(1, 2), 2, True, None)
+    idx.set_swa(na, 300)
+    blocks, _ = idx.evict(2)
+    assert len(blocks) == 2
+    assert idx.drain_freed_swa_slots().tolist() == [300] and idx.total_swa_slots() == 0
+    # partial shrink drops the trailing block, so the snapshot goes too
+    nb = idx.insert(_p(4, 5, 6), _h(11, 12, 13), 3, True, None)
+    idx.set_swa(nb, 301)
+    blocks, _ = idx.evict(1)
+    assert blocks.tolist() == [6] and idx.drain_freed_swa_slots().tolist() == [301] and not idx.has_swa(nb)
+
+
+def test_snapshot_eviction_prefers_interior_and_deletes_unlocked_leaves():
+    idx = _idx()
+    leaf = idx.insert(_p(0, 1, 2, 3), _h(1, 2, 3, 4), 4, True, None)
+    h2 = _h(1, 2, 99, 98)
+    idx.insert(_p(8, 9), h2, 4, True, idx.match_prefix(h2))
+    inner = idx.node_parent(leaf)
+    idx.set_swa(inner, 401)          # older
+    idx.set_swa(leaf, 400)           # newer
+    blocks, hashes, freed = idx.evict_swa(1)
+    assert freed == 1 and blocks.size == 0
+    assert idx.drain_freed_swa_slots().tolist() == [401]
+    assert not idx.has_swa(inner) and idx.node_size(inner) == 2 and idx.has_swa(leaf)
+    # an unlocked leaf that loses its snapshot is deleted whole
+    blocks, hashes, freed = idx.evict_swa(1)
+    assert freed == 1 and sorted(blocks.tolist()) == [2, 3] and hashes.tolist() == [3, 4]
+    assert idx.drain_freed_swa_slots().tolist() == [400] and not idx.alive(leaf)
+
+
+def test_locks():
+    idx = _idx()
+    n = idx.insert(_p(0, 1), _h(1, 2), 2, True, None)
+    with pytest.raises(RuntimeError):
+        idx.lock_swa(n)                       # nothing to lock yet
+    idx.set_swa(n, 600)
+    idx.lock_swa(n)
+    assert idx.swa_lock_cnt(n) == 1 and idx.node_lock_cnt(n) == 1     # full locks >= window locks
+    assert idx.evict_swa(1)[2] == 0                                   # window-locked: untouched
+    idx.unlock_swa(n)
+    idx.lock(n)                               # full lock only: the node stays, the snapshot goes
+    blocks, _, freed = idx.evict_swa(1)
+    assert freed == 1 and blocks.size == 0 and idx.alive(n) and not idx.has_swa(n)
+    idx.unlock(n)
+    # replacing a snapshot returns the old slot; reset forgets everything
+    idx.set_swa(n, 601)
+    idx.set_swa(n, 602)
+    assert idx.drain_freed_swa_slots().tolist() == [600, 601]
+    idx.reset()
+    assert idx.total_swa_slots() == 0 and idx.drain_freed_swa_slots().tolist() == []
