@@ -69,6 +69,52 @@ class CacheEngine:
     def reset(self) -> None:
         self.index.reset()
         self.mempool.reset()
+        if self.swa_pool is not None:
+            self.swa_pool.reset()
+
+    # ---- sliding-window snapshots (node-mounted; native index only) ---------------------
+    swa_pool = None
+
+    @property
+    def swa_enabled(self) -> bool:
+        return self.swa_pool is not None
+
+    def attach_swa(self, pool) -> None:
+        if not hasattr(self.index, "set_swa"):
+            raise ValueError("window snapshots need the native index (FLEXKV_INDEX_ACCEL=1)")
+        self.swa_pool = pool
+
+    def _drain_swa(self) -> None:
+        if self.swa_pool is not None:
+            self.swa_pool.free_many(self.index.drain_freed_swa_slots().tolist())
+
+    def alloc_swa_slot(self) -> Optional[int]:
+        """A free window slot, evicting least-recently-used snapshots when the pool is full
+        (unlocked leaves that only a snapshot keeps alive go with their blocks)."""
+        if self.swa_pool is None:
+            return None
+        self._drain_swa()
+        slot = self.swa_pool.allocate()
+        if slot is not None:
+            return slot
+        want = max(1, int(self.swa_pool.num_slots * self.swa_pool.config.evict_ratio))
+        blocks, hashes, _ = self.index.evict_swa(want)
+        if len(blocks):
+            self.mempool.recycle_blocks(blocks)
+            self.num_evicted_total += int(len(blocks))
+            for cb in self.on_evict:
+                cb(self.device_type, blocks, hashes)
+        self._drain_swa()
+        return self.swa_pool.allocate()
+
+    def mount_swa(self, node, slot: int) -> bool:
+        """Attaches the snapshot in ``slot`` to ``node`` (valid at its last block)."""
+        if node is None or not self.index.alive(node) or self.index.is_root(node):
+            self.swa_pool.free(slot)
+            return False
+        self.index.set_swa(node, int(slot))
+        self._drain_swa()               # a replaced snapshot returns its slot
+        return True
 
     def match(self, seq: SequenceMeta, update_cache_info: bool = True):
         return self.index.match_prefix(seq.block_hashes, seq.num_blocks, update_cache_info)
@@ -132,6 +178,7 @@ class CacheEngine:
                     self.num_evicted_total += int(len(blocks))
                     for cb in self.on_evict:
                         cb(self.device_type, blocks, hashes)
+                    self._drain_swa()
         if n > self.mempool.num_free_blocks and strict:
             raise NotEnoughSpaceError(f"{self.device_type.name}: need {n} blocks, "
                                       f"{self.mempool.num_free_blocks} free after eviction")

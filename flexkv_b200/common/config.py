@@ -209,16 +209,28 @@ class RankInfo:
 
 @dataclass
 class SWAPoolConfig:
-    """Sliding-window side pool (one page per window snapshot)."""
+    """Sliding-window side pool: one slot holds the window state of one cache page
+    (``tokens_per_block`` tokens) for every sliding-window layer
+    (reference: flexkv/common/config.py:573-620)."""
     enabled: bool = False
-    num_cpu_slots: int = 0
-    num_ssd_slots: int = 0
-    num_remote_slots: int = 0
-    page_bytes: int = 0
-    window_blocks: int = 1
+    num_slots: int = 1024              # host slots
+    num_ssd_slots: int = 0             # accepted; an SSD window tier is not built
+    num_remote_slots: int = 0          # accepted; a remote window tier is not built
+    num_swa_layers: int = 61
+    bytes_per_token_per_layer: int = 584
+    multi_group: bool = False
+    evict_ratio: float = 0.1           # share of the pool freed when it runs full
+    pin_memory: bool = True
+
+    def page_bytes_per_layer(self, tokens_per_block: int) -> int:
+        return int(tokens_per_block) * int(self.bytes_per_token_per_layer)
+
+    def slot_bytes(self, tokens_per_block: int) -> int:
+        return self.page_bytes_per_layer(tokens_per_block) * int(self.num_swa_layers)
 
     def for_cache_tier(self, device_type) -> Optional["SWAPoolConfig"]:
-        return self if self.enabled else None
+        name = getattr(device_type, "name", str(device_type))
+        return self if (self.enabled and name == "CPU") else None
 
 
 @dataclass

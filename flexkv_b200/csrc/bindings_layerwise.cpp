@@ -26,6 +26,7 @@ void init_layerwise_bindings(py::module_& m) {
              if (o.contains("notify_mode")) lo.notify = parse_notify_mode(o["notify_mode"].cast<std::string>());
              if (o.contains("num_counters")) lo.num_counters = o["num_counters"].cast<int>();
              if (o.contains("layers_per_batch")) lo.layers_per_batch = o["layers_per_batch"].cast<int>();
+             if (o.contains("fused_max_bytes")) lo.fused_max_bytes = o["fused_max_bytes"].cast<int64_t>();
              if (o.contains("create_eventfds")) lo.create_eventfds = o["create_eventfds"].cast<bool>();
              std::vector<GpuSide> gs = parse_gpu_sides(gpus);
              HostSide h = parse_host_side(host);

@@ -45,7 +45,7 @@ static StreamWaitValue32Fn stream_wait_value32() {
 LayerwiseGroup::LayerwiseGroup(std::vector<GpuSide> gpus, HostSide host, LayerwiseOptions opt)
     : gpus_(std::move(gpus)), host_(host), opt_(opt) {
   if (gpus_.empty()) throw std::invalid_argument("LayerwiseGroup: no GPUs");
-  if (opt_.num_counters < 1 || opt_.layers_per_batch < 0) throw std::invalid_argument("LayerwiseGroup: bad options");
+  if (opt_.num_counters < 1 || opt_.layers_per_batch < -1) throw std::invalid_argument("LayerwiseGroup: bad options");
   const int L = opt_.group.num_layers, R = (int)gpus_.size(), C = opt_.num_counters;
   epochs_.assign((size_t)C, 0);
   if (opt_.create_eventfds) {
@@ -59,7 +59,7 @@ LayerwiseGroup::LayerwiseGroup(std::vector<GpuSide> gpus, HostSide host, Layerwi
   check(cudaHostAlloc((void**)&id_ring_, 2 * (size_t)opt_.group.max_blocks_per_op * sizeof(int64_t),
                       cudaHostAllocPortable | cudaHostAllocMapped),
         "cudaHostAlloc(id ring)");
-  const int lpb = opt_.layers_per_batch > 0 ? opt_.layers_per_batch : L;
+  const int lpb = opt_.layers_per_batch > 0 ? opt_.layers_per_batch : (opt_.layers_per_batch < 0 ? 1 : L);
   const int batches = (L + lpb - 1) / lpb;
   for (int r = 0; r < R; ++r)
     for (int c = 0; c < C; ++c)
@@ -205,8 +205,12 @@ void LayerwiseGroup::rank_main(int r) {
 
 void LayerwiseGroup::run_job(int r, const Job& j) {
   Rank& rk = *ranks_[(size_t)r];
-  const bool fused = opt_.layers_per_batch <= 0;
-  const int L = opt_.group.num_layers, B = fused ? L : opt_.layers_per_batch, R = (int)gpus_.size();
+  const int L = opt_.group.num_layers, R = (int)gpus_.size();
+  // adaptive mode: small restores are launch-bound and go out as one fused launch, large ones keep
+  // one launch per layer (measured on B200: fused 0.14 vs 0.22 ms for 2 MiB, 11.2 vs 9.0 ms for 320 MiB)
+  const int64_t job_bytes = j.n * (int64_t)L * opt_.group.kv_dim * opt_.group.chunk_bytes;
+  const bool fused = opt_.layers_per_batch == 0 || (opt_.layers_per_batch < 0 && job_bytes <= opt_.fused_max_bytes);
+  const int B = fused ? L : (opt_.layers_per_batch > 0 ? opt_.layers_per_batch : 1);
   const int batches = (L + B - 1) / B;
   const auto t_begin = std::chrono::steady_clock::now();
   rk.res_status = 0;

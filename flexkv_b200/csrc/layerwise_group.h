@@ -40,7 +40,9 @@ struct LayerwiseOptions {
   GroupOptions group;
   NotifyMode notify = NotifyMode::HOSTFUNC;
   int num_counters = 3;       // independent flag / eventfd sets (restores in flight)
-  int layers_per_batch = 1;   // 0 = ONE launch for all layers, flags published per layer from inside the kernel
+  int layers_per_batch = 1;   // 0 = ONE launch for all layers, flags published per layer from inside the kernel;
+                              // -1 = decide per restore: fused up to fused_max_bytes, else one launch per layer
+  int64_t fused_max_bytes = 64ll << 20;
   bool create_eventfds = true;
 };
 

@@ -124,9 +124,13 @@ class EventfdReceiver:
 
 
 def build_layerwise_group(storage, model_config, key: WorkerKey, notify_mode: Optional[str] = None,
-                          num_counters: int = 3, layers_per_batch: int = 1, create_eventfds: bool = True):
+                          num_counters: int = 3, layers_per_batch: Optional[int] = None,
+                          create_eventfds: bool = True):
     from ..common.storage import KVCacheLayoutType
     env = GLOBAL_CONFIG_FROM_ENV
+    if layers_per_batch is None:
+        # -1: one fused launch for small restores, one launch per layer for large ones
+        layers_per_batch = int(os.environ.get("FLEXKV_LAYERWISE_LAYERS_PER_BATCH", -1))
     regs = storage.gpu_regs[key]
     ranks = sorted(regs)
     host, reg0 = storage.host, regs[ranks[0]]
