@@ -233,6 +233,8 @@ class TransferPlan:
     num_gpu_blocks_to_transfer: int = 0
     skipped_gpu_blocks: int = 0
     peer_leases: Optional[Tuple[np.ndarray, np.ndarray]] = None   # (ranks, gpu blocks) pinned in the peer directory
+    swa_locked: List[Any] = field(default_factory=list)            # nodes whose window snapshot this plan reads
+    swa_pending: Dict[int, int] = field(default_factory=dict)      # side op id -> slot not yet mounted
 
 
 def _block_range(token_mask: np.ndarray, tokens_per_block: int) -> Tuple[int, int]:
@@ -287,6 +289,14 @@ class GlobalCacheEngine:
         if cache_config.enable_p2p_gpu:
             from ..parallel.peer_directory import GpuPeerDirectory
             self.peer_directory = GpuPeerDirectory()
+        # sliding-window snapshots ride on the host tier's nodes
+        self.swa_ops = None
+        swa_cfg = cache_config.swa.for_cache_tier(DeviceType.CPU) if cache_config.swa is not None else None
+        if swa_cfg is not None and self.cpu_cache_engine is not None:
+            from ..swa import SWAHostPool
+            from .swa_cache_engine import SWAOpConstructor
+            self.cpu_cache_engine.attach_swa(SWAHostPool(swa_cfg))
+            self.swa_ops = SWAOpConstructor(self)
         self._metrics = None
         self._evict_log = EvictionLogAggregator()
         for eng in self.cache_engines.values():
@@ -370,7 +380,7 @@ class GlobalCacheEngine:
 
     def get(self, request_id: int, token_ids: np.ndarray, token_mask: Optional[np.ndarray],
             slot_mapping: Optional[np.ndarray], dp_client_id: int = 0, namespace: Optional[List[str]] = None,
-            cpu_only: bool = False, prefetch: bool = False):
+            cpu_only: bool = False, prefetch: bool = False, swa_aware: bool = False):
         """Returns ``(graph, return_mask, plan_handle, op_callbacks, task_end_op_id)``."""
         token_ids, token_mask, aligned = self._prepare(token_ids, token_mask, slot_mapping)
         if aligned == 0 or not token_mask.any():
@@ -382,9 +392,30 @@ class GlobalCacheEngine:
             gpu_blocks = slot_mapping_to_block_ids(slot_mapping, tpb)[:bend - bstart]
         seq = SequenceMeta(token_ids[:aligned], tpb, namespace)
         with self._cache_tree_lock:
+            swa_src = None
+            if swa_aware and self.swa_ops is not None and self.swa_ops.enabled and not prefetch:
+                # joint gate: only a prefix that ends where a window snapshot sits can be resumed
+                m = self.cpu_cache_engine.match(seq)
+                bend = min(bend, int(m.swa_hit_blocks))
+                if bend <= bstart:
+                    return self._empty(token_mask)
+                swa_src = (m.last_swa_node, int(m.swa_slot))
+                cpu_only = True                     # window state lives on the host tier only
+                if gpu_blocks is not None:
+                    gpu_blocks = gpu_blocks[:bend - bstart]
             plan = self._get_impl_local(seq, bstart, bend, gpu_blocks, dp_client_id, cpu_only, prefetch)
             if plan is None:
                 return self._empty(token_mask)
+            if swa_src is not None:
+                if plan.num_gpu_blocks_to_transfer < bend - bstart:
+                    # the full-KV plan fell short of the snapshot's position: the snapshot is useless
+                    self._discard_plan(plan)
+                    return self._empty(token_mask)
+                op = self.swa_ops.build_get_chain(plan.graph, swa_src[1], dp_client_id)
+                if op is not None:
+                    self.cpu_cache_engine.index.lock_swa(swa_src[0])
+                    plan.swa_locked.append(swa_src[0])
+                    plan.finished_ops_ids = list(plan.finished_ops_ids) + [op.op_id]
             graph, handle, cbs, end_op = self._finish(plan, is_put=False)
         mask = np.zeros_like(token_mask, dtype=np.bool_)
         mask[bstart * tpb:(bstart + plan.num_gpu_blocks_to_transfer) * tpb] = True
@@ -647,6 +678,25 @@ class GlobalCacheEngine:
         self._put_remote(seq, nb, cpu_m, cpu_matched, cpu_new, d2h, graph, plan, dp_client_id)
         if d2h is not None:
             plan.finished_ops_ids = [d2h.op_id]     # the caller may see success before the disk write ends
+        if d2h is not None and self.swa_ops is not None and self.swa_ops.enabled:
+            # snapshot of the window state after the last offloaded block, mounted on the new node
+            slot = cpu.alloc_swa_slot()
+            if slot is not None:
+                chain = self.swa_ops.build_put_chain(graph, slot, dp_client_id)
+                if chain.d2h_id is None:
+                    cpu.swa_pool.free(slot)
+                else:
+                    swa_op = graph.get_op(chain.d2h_id)
+                    plan.swa_pending[chain.d2h_id] = slot
+
+                    def _mount(node=cpu_node, slot=slot, op=swa_op, oid=chain.d2h_id):
+                        plan.swa_pending.pop(oid, None)
+                        if op.transfer_type == TransferType.VIRTUAL or not cpu.index.alive(node):
+                            cpu.swa_pool.free(slot)
+                        else:
+                            cpu.mount_swa(node, slot)
+                    plan.op_callback_dict[chain.d2h_id] = _mount
+                    plan.finished_ops_ids = list(plan.finished_ops_ids) + [chain.d2h_id]
         plan.skipped_gpu_blocks = cpu_matched
         plan.num_gpu_blocks_to_transfer = need_cpu
         return plan
@@ -696,6 +746,7 @@ class GlobalCacheEngine:
             for dev, ids in plan.buffer_to_free.items():
                 self.cache_engines[dev].recycle(ids)
             self._release_peer(plan)
+            self._release_swa(plan)
             # a node whose op callback never ran (op skipped) stays unready; drop it
             for dev, lst in plan.inserted.items():
                 for node in lst:
@@ -715,7 +766,26 @@ class GlobalCacheEngine:
             for dev, ids in plan.buffer_to_free.items():
                 self.cache_engines[dev].recycle(ids)
             self._release_peer(plan)
+            self._release_swa(plan)
             self._update_mempool_metrics()
+
+    def _discard_plan(self, plan: TransferPlan) -> None:
+        """Gives back what a plan reserved before its nodes were locked (it never launches)."""
+        for dev, lst in plan.inserted.items():
+            for node in lst:
+                self.cache_engines[dev].rollback_unready_insert(node)
+        for dev, ids in plan.buffer_to_free.items():
+            self.cache_engines[dev].recycle(ids)
+        self._release_peer(plan)
+
+    def _release_swa(self, plan: TransferPlan) -> None:
+        cpu = self.cpu_cache_engine
+        for node in plan.swa_locked:
+            cpu.index.unlock_swa(node)
+        plan.swa_locked = []
+        for slot in plan.swa_pending.values():      # side ops that never completed
+            cpu.swa_pool.free(slot)
+        plan.swa_pending = {}
 
     def _release_peer(self, plan: TransferPlan) -> None:
         if plan.peer_leases is not None and self.peer_directory is not None:

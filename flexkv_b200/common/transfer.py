@@ -168,7 +168,7 @@ class TransferOpGraph:
         self._ops[op.op_id] = op
         self._ready.add(op.op_id)
         self._unfinished += 1
-        if op.gpu_side is not None:
+        if op.gpu_side is not None and not op.is_swa:   # window side ops are bound (or dropped) at launch
             self._gpu_bound = False
         return op.op_id
 
@@ -191,7 +191,7 @@ class TransferOpGraph:
     def set_gpu_blocks(self, gpu_block_ids: np.ndarray) -> None:
         gpu_block_ids = _ids(gpu_block_ids)
         for op in self._ops.values():
-            if op.gpu_side is None:
+            if op.gpu_side is None or op.is_swa:
                 continue
             if isinstance(op, LayerwiseTransferOp):
                 n = int(op.src_block_ids_h2d.size)
@@ -213,6 +213,27 @@ class TransferOpGraph:
     @property
     def gpu_bound(self) -> bool:
         return self._gpu_bound
+
+    def set_swa_pages(self, page_ids: Optional[np.ndarray]) -> None:
+        """Binds the GPU side of sliding-window side ops to the caller's window pages. With
+        ``None`` the side ops are turned into no-ops (the caller moves no window state)."""
+        for op in self._ops.values():
+            if not op.is_swa or op.gpu_side is None:
+                continue
+            n = int(op.dst_block_ids.size if op.gpu_side == "src" else op.src_block_ids.size)
+            if page_ids is None:
+                op.transfer_type = TransferType.VIRTUAL
+                op.src_block_ids = op.dst_block_ids = _EMPTY
+                op.gpu_side = None
+                continue
+            ids = _ids(page_ids)
+            if ids.size < n:
+                raise ValueError(f"window side op needs {n} page(s), {ids.size} given")
+            if op.gpu_side == "src":
+                op.src_block_ids = ids[:n]
+            else:
+                op.dst_block_ids = ids[:n]
+            op.gpu_side = None
 
     # ---- execution ------------------------------------------------------------
     def take_ready_ops(self) -> List[TransferOp]:

@@ -171,10 +171,11 @@ class KVTaskEngine:
             self.graph_to_task[graph.graph_id] = tid
         return task
 
-    def _create_get(self, token_ids, token_mask, slot_mapping, dp_id, namespace, cpu_only=False) -> KVTask:
+    def _create_get(self, token_ids, token_mask, slot_mapping, dp_id, namespace, cpu_only=False,
+                    swa_aware=False) -> KVTask:
         with nvtx_range("flexkv.get.plan"):
             planned = self.cache_engine.get(-1, token_ids, token_mask, slot_mapping, dp_id, namespace,
-                                            cpu_only=cpu_only)
+                                            cpu_only=cpu_only, swa_aware=swa_aware)
         return self._new_task(TaskType.GET, token_ids, token_mask, slot_mapping, dp_id, planned)
 
     def _create_put(self, token_ids, token_mask, slot_mapping, dp_id, namespace) -> KVTask:
@@ -188,6 +189,7 @@ class KVTaskEngine:
         self._update_tasks(timeout=0)
         task = self._create_get(token_ids, token_mask, slot_mapping, dp_id, namespace)
         self.tracer.trace_request("GET", task.task_id, token_ids, slot_mapping, token_mask, namespace)
+        task.graph.set_swa_pages(None)      # the one-call API carries no window pages
         self._launch([task])
         return task.task_id, task.return_mask
 
@@ -196,6 +198,7 @@ class KVTaskEngine:
         self._update_tasks(timeout=0)
         task = self._create_put(token_ids, token_mask, slot_mapping, dp_id, namespace)
         self.tracer.trace_request("PUT", task.task_id, token_ids, slot_mapping, token_mask, namespace)
+        task.graph.set_swa_pages(None)
         self._launch([task])
         return task.task_id, task.return_mask
 
@@ -203,7 +206,7 @@ class KVTaskEngine:
                   cpu_only: bool = False, namespace: Optional[List[str]] = None, swa_aware: bool = False
                   ) -> Tuple[int, np.ndarray]:
         self._update_tasks(timeout=0)
-        task = self._create_get(token_ids, token_mask, None, dp_id, namespace, cpu_only=cpu_only)
+        task = self._create_get(token_ids, token_mask, None, dp_id, namespace, cpu_only=cpu_only, swa_aware=swa_aware)
         self.tracer.trace_request("GET_MATCH", task.task_id, token_ids, None, token_mask, namespace)
         return task.task_id, task.return_mask
 
@@ -233,13 +236,18 @@ class KVTaskEngine:
         self.tracer.trace_launch(task_ids, slot_mappings, as_batch, layerwise_transfer, counter_id)
         tasks: List[KVTask] = []
         with self._lock:
-            for tid, sm in zip(task_ids, slot_mappings):
+            for i, (tid, sm) in enumerate(zip(task_ids, slot_mappings)):
                 task = self.tasks.get(tid)
                 if task is None:
                     raise KeyError(f"unknown task {tid}")
                 if task.status == TaskStatus.UNREADY:
                     ids = slot_mapping_to_block_ids(np.asarray(sm, dtype=np.int64), self.cache_config.tokens_per_block)
                     task.graph.set_gpu_blocks(ids)
+                    # window side ops: one page of window slots per task, or none (side ops become no-ops)
+                    swa_sm = swa_slot_mappings[i] if swa_slot_mappings is not None and i < len(swa_slot_mappings) \
+                        else None
+                    task.graph.set_swa_pages(None if swa_sm is None else slot_mapping_to_block_ids(
+                        np.asarray(swa_sm, dtype=np.int64), self.cache_config.tokens_per_block))
                     task.slot_mapping = sm
                     task.status = TaskStatus.READY
                 tasks.append(task)

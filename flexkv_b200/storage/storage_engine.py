@@ -70,6 +70,20 @@ class HostPool:
 
 
 @dataclass
+class SwaPool:
+    """Host side of the sliding-window pool: [slot][rank][layer][page bytes]."""
+    region: Any
+    num_slots: int
+    slot_bytes: int             # all ranks
+    rank_slot_bytes: int
+    page_bytes: int             # one layer of one rank
+
+    @property
+    def base(self) -> int:
+        return int(self.region.ptr)
+
+
+@dataclass
 class SsdPool:
     engine: Any                 # native SsdIoEngine
     files: List[List[str]]
@@ -88,6 +102,8 @@ class StorageEngine:
         self.host: Optional[HostPool] = None
         self.ssd: Optional[SsdPool] = None
         self.ssd_size_table: Optional[np.ndarray] = None
+        self.swa_regs: Dict[WorkerKey, Dict[int, GpuRegistration]] = {}
+        self.swa_host: Optional[SwaPool] = None
         self._cuda_register = torch.cuda.is_available() if cuda_register is None else cuda_register
         self._numa_node = numa_node
         if cache_config.enable_cpu:
@@ -254,6 +270,30 @@ class StorageEngine:
                     chunk_bytes=h.chunk_bytes, num_layers=L, kv_dim=h.layout.kv_dim, block_first=bf)
 
     # ---- GPU ----------------------------------------------------------------------
+    # ---- sliding-window side pool ------------------------------------------------------
+    def register_swa_blocks(self, reg: GpuRegistration) -> None:
+        """GPU window pages of one rank: ``num_layers`` tensors of [pages, page_bytes]."""
+        key = WorkerKey(reg.dp_client_id, reg.pp_rank)
+        self.swa_regs.setdefault(key, {})[reg.tp_rank] = reg
+        if self.swa_host is None:
+            self._alloc_swa(reg)
+
+    def _alloc_swa(self, reg: GpuRegistration) -> None:
+        cfg = self.cache_config.swa
+        if cfg is None or not cfg.enabled:
+            raise ValueError("window pages registered but CacheConfig.swa is not enabled")
+        ranks = 1 if (self.model_config.use_mla or self.model_config.num_kv_heads == 1) else \
+            self.model_config.effective_tp_size
+        rank_slot = reg.num_layers * reg.chunk_bytes
+        total = cfg.num_slots * ranks * rank_slot
+        region = _native.C.host_region_alloc(total, hugepage=False, hugepage_bytes=2 << 20, numa_node=self._numa_node,
+                                             populate=True, touch_threads=4,
+                                             cuda_register=self._cuda_register and cfg.pin_memory,
+                                             register_chunk_bytes=0, backing_file="")
+        self.swa_host = SwaPool(region, cfg.num_slots, ranks * rank_slot, rank_slot, reg.chunk_bytes)
+        flexkv_logger.info("window pool: %d slots x %d B (%d layers x %d B per rank, %d rank(s))", cfg.num_slots,
+                           ranks * rank_slot, reg.num_layers, reg.chunk_bytes, ranks)
+
     def register_gpu_blocks(self, reg: GpuRegistration) -> None:
         key = WorkerKey(reg.dp_client_id, reg.pp_rank)
         self.gpu_regs.setdefault(key, {})[reg.tp_rank] = reg
@@ -277,6 +317,12 @@ class StorageEngine:
                     os.unlink(self._owned_backing)
                 except OSError:
                     pass
+        if self.swa_host is not None:
+            try:
+                self.swa_host.region.free()
+            except Exception:  # noqa: BLE001
+                pass
+            self.swa_host = None
         if self.ssd is not None:
             files = [f for d in self.ssd.files for f in d]
             self.ssd = None

@@ -138,8 +138,8 @@ class TransferEngine:
                     progress = True
                     continue
                 key = WorkerKey(op.dp_client_id, 0)
-                w = self._workers.get((key, op.transfer_type))
-                if w is None and op.transfer_type not in (TransferType.H2D, TransferType.D2H, TransferType.LAYERWISE,
+                w = self._workers.get((key, "SWA" if op.is_swa else op.transfer_type))
+                if w is None and not op.is_swa and op.transfer_type not in (TransferType.H2D, TransferType.D2H, TransferType.LAYERWISE,
                                                           TransferType.PEERD2D, TransferType.DISK2D,
                                                           TransferType.D2DISK):
                     # tier-to-tier workers (SSD, remote) are shared by every data-parallel client

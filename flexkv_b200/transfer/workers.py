@@ -405,6 +405,80 @@ class RemoteWorker(TransferWorker):
                          error="" if ok else f"{len(res) - sum(res)} remote block(s) failed")
 
 
+class SwaWorker(TransferWorker):
+    """Moves sliding-window pages between the GPU window pool and the host window pool
+    (ops flagged ``is_swa``; ids are window page ids on the GPU side and slot ids on the
+    host side). Pages are small and few, so one plain copy-kernel launch per rank and op
+    on its own stream is enough; host-resident stand-ins go through the CPU oracle."""
+
+    name = "swa"
+
+    def __init__(self, storage, model_config: ModelConfig, key: WorkerKey) -> None:
+        super().__init__()
+        self.storage = storage
+        self.regs = [storage.swa_regs[key][r] for r in sorted(storage.swa_regs[key])]
+        self.shared = model_config.use_mla or model_config.num_kv_heads == 1
+        self.on_gpu = self.regs[0].device_id >= 0
+        self._streams, self._status = {}, {}
+        if self.on_gpu:
+            import torch
+            self._torch = torch
+            for r in self.regs:
+                self._streams[r.device_id] = torch.cuda.Stream(device=r.device_id)
+                self._status[r.device_id] = torch.zeros(8, dtype=torch.int32, device=f"cuda:{r.device_id}")
+
+    def execute(self, op: TransferOp) -> OpOutcome:
+        h2d = op.transfer_type == TransferType.H2D
+        if op.transfer_type not in (TransferType.H2D, TransferType.D2H):
+            return OpOutcome(False, error=f"window ops on {op.transfer_type.value} are not built")
+        slots, pages = (op.src_block_ids, op.dst_block_ids) if h2d else (op.dst_block_ids, op.src_block_ids)
+        if slots.size != pages.size or slots.size == 0:
+            return OpOutcome(False, error=f"unbound window pages: {pages.size} vs {slots.size} slots")
+        pool = self.storage.swa_host
+        nbytes, status, ms = 0, 0, 0.0
+        if self.on_gpu:
+            g_ids = self._torch.from_numpy(np.ascontiguousarray(pages, dtype=np.int64)).pin_memory()
+            c_ids = self._torch.from_numpy(np.ascontiguousarray(slots, dtype=np.int64)).pin_memory()
+            g_ptr, c_ptr = g_ids.data_ptr(), c_ids.data_ptr()
+        else:
+            g_ids = np.ascontiguousarray(pages, dtype=np.int64)
+            c_ids = np.ascontiguousarray(slots, dtype=np.int64)
+            g_ptr, c_ptr = g_ids.ctypes.data, c_ids.ctypes.data
+        evs = []
+        for i, reg in enumerate(self.regs):
+            if self.shared and not h2d and i > 0:
+                break
+            params = dict(gpu_ptrs=[int(p) for p in reg.ptrs], idx_layer_mul=reg.idx_layer_mul,
+                          idx_kv_mul=reg.idx_kv_mul, g_layer_stride=reg.layer_stride, g_kv_stride=reg.kv_stride,
+                          g_block_stride=reg.block_stride, cpu_base=pool.base, c_layer_stride=pool.page_bytes,
+                          c_kv_stride=0, c_block_stride=pool.slot_bytes,
+                          c_off=0 if self.shared else i * pool.rank_slot_bytes, gpu_blocks_ptr=g_ptr,
+                          cpu_blocks_ptr=c_ptr, num_pairs=int(slots.size), layer_start=0, num_layers=reg.num_layers,
+                          kv_dim=1, chunk_bytes=reg.chunk_bytes, gpu_num_blocks=reg.num_blocks,
+                          cpu_num_blocks=pool.num_slots, h2d=int(h2d))
+            nbytes += int(slots.size) * reg.num_layers * reg.chunk_bytes
+            if not self.on_gpu:
+                status |= _native.C.host_kv_copy(params, 2)
+                continue
+            st = self._streams[reg.device_id]
+            params["status_ptr"] = self._status[reg.device_id].data_ptr()
+            e0, e1 = self._torch.cuda.Event(enable_timing=True), self._torch.cuda.Event(enable_timing=True)
+            with self._torch.cuda.device(reg.device_id):
+                e0.record(st)
+                _native.C.kv_copy(params, 4, 16384, 0, st.cuda_stream)
+                e1.record(st)
+            evs.append((e0, e1, reg.device_id))
+        for e0, e1, dev in evs:
+            e1.synchronize()
+            ms = max(ms, e0.elapsed_time(e1))
+            words = self._status[dev].tolist()
+            status |= sum(1 << b for b, w in enumerate(words) if w)
+            if status:
+                self._status[dev].zero_()
+        return OpOutcome(status == 0, gpu_ms=ms, num_bytes=nbytes,
+                         error="" if status == 0 else f"window copy status 0x{status:x}")
+
+
 class PeerHostWorker(TransferWorker):
     """PEERH2H: pulls blocks out of other nodes' host pools into this node's pool.
     Inside one box every pool is a shared-memory file whose name the owner published in
@@ -647,6 +721,8 @@ def build_workers(storage, model_config: ModelConfig, cache_config: CacheConfig
             sock = os.environ.get("FLEXKV_LAYERWISE_SOCK", "")
             workers[(key, TransferType.LAYERWISE)] = LayerwiseWorker(
                 storage, model_config, key, sock_path=f"{sock}.{key.dp_client_id}" if sock else None)
+    for key in storage.swa_regs:
+        workers[(key, "SWA")] = SwaWorker(storage, model_config, key)
     real = [k for k, regs in storage.gpu_regs.items() if regs[sorted(regs)[0]].device_id >= 0]
     if cache_config.enable_p2p_gpu and len(real) > 1:
         peer = PeerD2DWorker(storage, model_config)

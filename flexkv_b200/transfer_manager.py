@@ -35,6 +35,7 @@ class TransferManager:
         self.storage: Optional[StorageEngine] = None
         self.engine: Optional[TransferEngine] = None
         self._pending_regs: List[GpuRegistration] = []
+        self._pending_swa: List[GpuRegistration] = []
         self._reg_cv = threading.Condition()
         self._ready = threading.Event()
         self._init_error: Optional[BaseException] = None
@@ -50,6 +51,11 @@ class TransferManager:
         with self._reg_cv:
             self._pending_regs.append(reg)
             self._reg_cv.notify_all()
+
+    def register_swa(self, reg: GpuRegistration) -> None:
+        """Window pages of one rank; must arrive before start() completes initialisation."""
+        with self._reg_cv:
+            self._pending_swa.append(reg)
 
     def _expected_registrations(self) -> int:
         m = self.model_config
@@ -89,6 +95,8 @@ class TransferManager:
                                          numa_node=numa)
             for r in self._pending_regs:
                 self.storage.register_gpu_blocks(r)
+            for r in self._pending_swa:
+                self.storage.register_swa_blocks(r)
             if self.cache_config.enable_p2p_cpu and self.storage.host is not None:
                 # what a peer needs to read this node's host pool
                 from .cache.hie_cache_engine import get_node_registry

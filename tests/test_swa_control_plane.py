@@ -1,0 +1,125 @@
+"""Sliding-window snapshots end to end on the CPU tier: a put mounts the window page of the
+sequence end on the new host node, a window-aware get is gated to the deepest snapshot and
+restores full KV plus the page, snapshots are evicted LRU-first when the pool is full
+(reference behaviour: flexkv/cache/swa_cache_engine.py:142-239, tests/test_swa_control_plane_e2e.py)."""
+import numpy as np
+import torch
+
+from flexkv_b200 import CacheConfig, KVManager
+from flexkv_b200.common.config import SWAPoolConfig
+from flexkv_b200.models import KVShape, alloc_paged_cache, make_model_config
+from flexkv_b200.swa import SWAHostPool
+
+T = 4
+SWA_LAYERS, PAGE_BYTES = 3, 64
+
+
+def slots(blocks):
+    return np.repeat(np.asarray(blocks, dtype=np.int64), T) * T + np.tile(np.arange(T), len(blocks))
+
+
+def start(num_slots=4):
+    shape = KVShape("s", 2, 2, 16, tokens_per_block=T)
+    cfg = CacheConfig(tokens_per_block=T, num_cpu_blocks=32, enable_swa_transfer=True,
+                      swa=SWAPoolConfig(enabled=True, num_slots=num_slots, num_swa_layers=SWA_LAYERS,
+                                        bytes_per_token_per_layer=PAGE_BYTES // T, evict_ratio=0.25))
+    mgr = KVManager(make_model_config(shape), cfg, require_gpu=True)
+    kv, layout = alloc_paged_cache(shape, 64, "cpu", "vllm", fill="normal", seed=5)
+    mgr.register_gpu_tensors(kv, layout)
+    g = torch.Generator().manual_seed(9)
+    swa = [torch.randint(0, 256, (16, PAGE_BYTES), dtype=torch.uint8, generator=g) for _ in range(SWA_LAYERS)]
+    mgr.register_swa_tensors(swa)
+    mgr.start(); mgr.wait_ready(30)
+    return mgr, kv, swa
+
+
+def put(mgr, tok, blocks, page):
+    tid, mask = mgr.put_match(tok)
+    mgr.launch(tid, slots(blocks)[mask[:len(blocks) * T]] if mask.any() else slots(blocks)[:0],
+               swa_slot_mappings=[slots([page])])
+    return mgr.wait(tid, completely=True)[tid]
+
+
+def test_put_mounts_and_window_aware_get_restores_page_and_blocks():
+    mgr, kv, swa = start()
+    try:
+        tok = np.arange(6 * T, dtype=np.int64) + 100
+        src = np.array([3, 9, 1, 30, 12, 7])
+        assert put(mgr, tok, src, page=5).status.value == "success"
+        cpu = mgr.kv_task_engine.cache_engine.cpu_cache_engine
+        assert cpu.index.total_swa_slots() == 1 and cpu.swa_pool.num_used == 1
+        want_page = [t[5].clone() for t in swa]
+        want_kv = [t[:, src].clone() for t in kv]
+        # a longer query still only resumes at the snapshot (6 blocks), and a shorter one finds nothing
+        long_tok = np.concatenate([tok, np.arange(2 * T) + 9000])
+        tid, mask = mgr.get_match(long_tok, swa_aware=True)
+        assert int(mask.sum()) == 6 * T
+        kinds = sorted((o.transfer_type.value, o.is_swa) for o in mgr.kv_task_engine.tasks[tid].graph.ops()
+                       if o.transfer_type.value != "Virtual")
+        assert kinds == [("H2D", False), ("H2D", True)]
+        dst = np.arange(40, 46)
+        for t in swa:
+            t[11] = 0
+        mgr.launch(tid, slots(dst), swa_slot_mappings=[slots([11])])
+        assert mgr.wait(tid)[tid].status.value == "success"
+        for l in range(2):
+            assert torch.equal(kv[l][:, dst], want_kv[l])
+        for l in range(SWA_LAYERS):
+            assert torch.equal(swa[l][11], want_page[l])
+        tid, mask = mgr.get_match(tok[:4 * T], swa_aware=True)
+        assert int(mask.sum()) == 0
+        mgr.cancel(tid)
+        # without window awareness the plain prefix match is unchanged
+        tid, mask = mgr.get_match(tok[:4 * T])
+        assert int(mask.sum()) == 4 * T
+        mgr.cancel(tid)
+        # the node stays window-locked only while the get runs
+        m = cpu.match(__import__("flexkv_b200.common.block", fromlist=["SequenceMeta"]).SequenceMeta(tok, T))
+        assert cpu.index.swa_lock_cnt(m.last_swa_node) == 0
+    finally:
+        mgr.shutdown()
+
+
+def test_launch_without_window_pages_drops_the_side_ops_and_returns_the_slot():
+    mgr, kv, swa = start()
+    try:
+        tok = np.arange(3 * T, dtype=np.int64) + 500
+        tid, mask = mgr.put_match(tok)
+        mgr.launch(tid, slots([1, 2, 3]))
+        assert mgr.wait(tid, completely=True)[tid].status.value == "success"
+        cpu = mgr.kv_task_engine.cache_engine.cpu_cache_engine
+        assert cpu.index.total_swa_slots() == 0 and cpu.swa_pool.num_used == 0
+        tid = mgr.put_async(tok + 1, slots([4, 5, 6]))
+        assert mgr.wait(tid, completely=True)[tid].status.value == "success"
+        assert cpu.swa_pool.num_used == 0
+    finally:
+        mgr.shutdown()
+
+
+def test_full_pool_evicts_least_recently_used_snapshots():
+    mgr, kv, swa = start(num_slots=2)
+    try:
+        cpu = mgr.kv_task_engine.cache_engine.cpu_cache_engine
+        seqs = [np.arange(2 * T, dtype=np.int64) + 1000 * (i + 1) for i in range(3)]
+        for i, tok in enumerate(seqs):
+            assert put(mgr, tok, [2 * i, 2 * i + 1], page=i).status.value == "success"
+        assert cpu.swa_pool.num_used <= 2 and cpu.index.total_swa_slots() == cpu.swa_pool.num_used
+        # the oldest sequence lost its snapshot (an unlocked leaf goes with its blocks)
+        tid, mask = mgr.get_match(seqs[0], swa_aware=True)
+        assert int(mask.sum()) == 0
+        mgr.cancel(tid)
+        tid, mask = mgr.get_match(seqs[2], swa_aware=True)
+        assert int(mask.sum()) == 2 * T
+        mgr.cancel(tid)
+    finally:
+        mgr.shutdown()
+
+
+def test_slot_pool():
+    p = SWAHostPool(SWAPoolConfig(enabled=True, num_slots=3))
+    a, b, c = p.allocate(), p.allocate(), p.allocate()
+    assert (a, b, c) == (0, 1, 2) and p.allocate() is None and p.num_used == 3
+    p.free(b); p.free(b)
+    assert p.num_free == 1 and p.allocate() == 1
+    p.reset()
+    assert p.num_free == 3
