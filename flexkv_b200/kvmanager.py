@@ -33,7 +33,8 @@ def _np(x, dtype=None):
 class KVManager:
     def __init__(self, model_config: ModelConfig, cache_config: CacheConfig, dp_client_id: int = 0,
                  server_recv_port: Optional[str] = None, gpu_register_port: Optional[str] = None,
-                 require_gpu: Optional[bool] = None, in_process: Optional[bool] = None) -> None:
+                 require_gpu: Optional[bool] = None, in_process: Optional[bool] = None,
+                 remote_transfer_endpoints: Optional[Sequence[Tuple[str, str, str]]] = None) -> None:
         env = GLOBAL_CONFIG_FROM_ENV
         self.model_config = model_config
         self.cache_config = cache_config
@@ -69,7 +70,13 @@ class KVManager:
                 require_gpu = torch.cuda.is_available()
             self.transfer_manager = TransferManager(model_config, cache_config, gpu_register_port,
                                                     require_gpu=require_gpu)
-            self.kv_task_engine = KVTaskEngine(model_config, cache_config, transfer_handles=[self.transfer_manager])
+            handles = [self.transfer_manager]
+            # other nodes of a TP/PP group: one handle per (command, result, query) endpoint triple; a graph
+            # is finished when every node reported it
+            for cmd, res, qry in (remote_transfer_endpoints or []):
+                from .transfer_manager import TransferManagerMultiNodeHandle
+                handles.append(TransferManagerMultiNodeHandle(cmd, res, qry))
+            self.kv_task_engine = KVTaskEngine(model_config, cache_config, transfer_handles=handles)
             if env.enable_metrics:
                 from .metrics.collector import get_collector
                 self._metrics = get_collector(start_server=True)

@@ -54,7 +54,8 @@ def get_shape(name: str) -> KVShape:
     return SHAPES[name]
 
 
-def make_model_config(shape: KVShape, tp_size: int = 1, dp_size: int = 1, pp_size: int = 1) -> ModelConfig:
+def make_model_config(shape: KVShape, tp_size: int = 1, dp_size: int = 1, pp_size: int = 1, nnodes: int = 1
+                      ) -> ModelConfig:
     return ModelConfig(num_layers=shape.num_layers, num_kv_heads=shape.num_kv_heads, head_size=shape.head_size,
                        kv_dim=shape.kv_dim, use_mla=shape.use_mla, dtype=shape.dtype, tp_size=tp_size,
-                       dp_size=dp_size, pp_size=pp_size)
+                       dp_size=dp_size, pp_size=pp_size, nnodes=nnodes)

@@ -157,7 +157,8 @@ class StorageEngine:
         d = choose_codec(requested_quant=c.offload_quant,
                          compression_enabled=bool(c.enable_compression or self.env.enable_compression),
                          dtype=m.dtype, host_layout_type=lay.type, chunk_elems_per_rank=lay.get_chunk_size() // slices,
-                         itemsize=m.dtype.itemsize, layerwise=bool(self.env.enable_layerwise_transfer))
+                         itemsize=m.dtype.itemsize, layerwise=bool(self.env.enable_layerwise_transfer),
+                         peer_host_sharing=bool(c.enable_p2p_cpu))
         if d.reason:
             flexkv_logger.warning("host codec refused: %s; every tier runs uncompressed", d.reason)
         if d.warning:

@@ -26,7 +26,7 @@ class CodecDecision:
 
 
 def choose_codec(*, requested_quant: str, compression_enabled: bool, dtype, host_layout_type, chunk_elems_per_rank: int,
-                 itemsize: int, layerwise: bool) -> CodecDecision:
+                 itemsize: int, layerwise: bool, peer_host_sharing: bool = False) -> CodecDecision:
     """``requested_quant`` is the explicit lossy choice (CacheConfig.offload_quant); the
     lossless codec is picked when compression is enabled and the cache qualifies."""
     if requested_quant not in ("none", "fp8_e4m3", "bf16_xp"):
@@ -55,6 +55,8 @@ def choose_codec(*, requested_quant: str, compression_enabled: bool, dtype, host
         why = f"chunk elements per rank are not a multiple of {XP_ELEM_MULTIPLE}"
     elif layerwise:
         why = "layerwise restore is enabled"
+    elif peer_host_sharing:
+        why = "host blocks are shared with other nodes (the size table is not)"
     if why:
         return CodecDecision("none", why)
     warn = ""

@@ -162,3 +162,138 @@ class TransferManager:
             self.storage.shutdown()
             self.storage = None
         self._ready.clear()
+
+
+# ------------------------------------------------------------------ other nodes / processes
+
+class TransferManagerOnRemote:
+    """Runs a TransferManager for this node's GPUs on behalf of a master node: graphs
+    arrive on a ZeroMQ PULL socket, completions go back on a PUSH socket, readiness is
+    answered on a REP socket (reference: flexkv/transfer_manager.py:529-908, ports
+    5556-5558 at :1314-1343). The node keeps its own host pool; block ids in the graphs
+    are the master's, applied to the same positions here."""
+
+    def __init__(self, model_config: ModelConfig, cache_config: CacheConfig, command_endpoint: str,
+                 result_endpoint: str, query_endpoint: str, require_gpu: bool = True) -> None:
+        import zmq
+        self.tm = TransferManager(model_config, cache_config, require_gpu=require_gpu)
+        self._ctx = zmq.Context.instance()
+        self._cmd = self._ctx.socket(zmq.PULL)
+        self._cmd.setsockopt(zmq.LINGER, 0)
+        self._cmd.bind(command_endpoint)
+        self._res = self._ctx.socket(zmq.PUSH)
+        self._res.setsockopt(zmq.LINGER, 0)
+        self._res.connect(result_endpoint)
+        self._qry = self._ctx.socket(zmq.REP)
+        self._qry.setsockopt(zmq.LINGER, 0)
+        self._qry.bind(query_endpoint)
+        self._stop = threading.Event()
+
+    def register_gpu(self, reg: GpuRegistration) -> None:
+        self.tm.register_gpu(reg)
+
+    def serve_forever(self) -> None:
+        import pickle
+        import zmq
+        self.tm.start()
+        pump = threading.Thread(target=self._pump_results, name="flexkv-remote-results", daemon=True)
+        pump.start()
+        poller = zmq.Poller()
+        poller.register(self._cmd, zmq.POLLIN)
+        poller.register(self._qry, zmq.POLLIN)
+        while not self._stop.is_set():
+            for sock, _ in poller.poll(100):
+                if sock is self._qry:
+                    q = pickle.loads(self._qry.recv())
+                    try:
+                        ans = self.tm.is_ready() if q == "ready" else None
+                    except RuntimeError as e:
+                        ans = repr(e)
+                    self._qry.send(pickle.dumps(ans))
+                    continue
+                kind, payload = pickle.loads(self._cmd.recv())
+                if kind == "submit":
+                    self.tm.submit_batch(payload)
+                elif kind == "shutdown":
+                    self._stop.set()
+        pump.join(timeout=2)
+        self.tm.shutdown()
+        for s in (self._cmd, self._res, self._qry):
+            s.close()
+
+    def _pump_results(self) -> None:
+        import pickle
+        while not self._stop.is_set():
+            done = self.tm.wait(timeout=0.05)
+            if done:
+                self._res.send(pickle.dumps(done))
+
+
+class TransferManagerMultiNodeHandle:
+    """Master-side handle of a TransferManagerOnRemote: same interface as an in-process
+    TransferManager, so the task layer counts it as one more handle whose completions
+    must arrive before a graph is finished (flexkv/transfer_manager.py:1279-1468)."""
+
+    def __init__(self, command_endpoint: str, result_endpoint: str, query_endpoint: str) -> None:
+        import zmq
+        self._ctx = zmq.Context.instance()
+        self._cmd = self._ctx.socket(zmq.PUSH)
+        self._cmd.setsockopt(zmq.LINGER, 0)
+        self._cmd.connect(command_endpoint)
+        self._res = self._ctx.socket(zmq.PULL)
+        self._res.setsockopt(zmq.LINGER, 0)
+        self._res.bind(result_endpoint)
+        self._query_endpoint = query_endpoint
+        self._lock = threading.Lock()
+
+    def start(self) -> None:
+        pass
+
+    def is_ready(self) -> bool:
+        import pickle
+        import zmq
+        q = self._ctx.socket(zmq.REQ)
+        q.setsockopt(zmq.LINGER, 0)
+        q.setsockopt(zmq.RCVTIMEO, 500)
+        q.setsockopt(zmq.SNDTIMEO, 500)
+        try:
+            q.connect(self._query_endpoint)
+            q.send(pickle.dumps("ready"))
+            ans = pickle.loads(q.recv())
+        except zmq.ZMQError:
+            return False
+        finally:
+            q.close()
+        if isinstance(ans, str):
+            raise RuntimeError(f"remote transfer manager failed to start: {ans}")
+        return bool(ans)
+
+    def submit(self, graph: TransferOpGraph) -> None:
+        self.submit_batch([graph])
+
+    def submit_batch(self, graphs: List[TransferOpGraph]) -> None:
+        import pickle
+        with self._lock:
+            self._cmd.send(pickle.dumps(("submit", graphs)))
+
+    def wait(self, timeout: Optional[float] = None) -> List[CompletedOp]:
+        import pickle
+        if not self._res.poll(int((timeout or 0) * 1000)):
+            return []
+        out: List[CompletedOp] = []
+        while self._res.poll(0):
+            out.extend(pickle.loads(self._res.recv()))
+        return out
+
+    def set_metrics_collector(self, collector) -> None:
+        pass
+
+    def shutdown(self) -> None:
+        import pickle
+        try:
+            with self._lock:
+                self._cmd.send(pickle.dumps(("shutdown", None)))
+        except Exception:  # noqa: BLE001
+            pass
+        self._cmd.close()
+        self._res.close()
