@@ -1,0 +1,82 @@
+#!/usr/bin/env python
+"""Copy-engine ceiling of the box: every rank copies one contiguous pinned buffer to and from
+its GPU at the same time (`cudaMemcpyAsync` through torch), CUDA events, max over ranks.
+This is what the PCIe links and the host memory system give N GPUs at once, the denominator
+for the multi-GPU numbers of bench.py. Launch with torchrun (one rank per GPU) or plain for one GPU.
+"""
+import argparse
+import json
+import os
+
+import numpy as np
+import torch
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gib", type=float, default=4.0)
+    ap.add_argument("--iters", type=int, default=5)
+    a = ap.parse_args()
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    rank = int(os.environ.get("RANK", 0))
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+    n = int(a.gib * 2**30)
+    host = torch.empty(n, dtype=torch.uint8).pin_memory()
+    host.fill_(1)
+    gpu = torch.empty(n, dtype=torch.uint8, device=dev)
+    out = {}
+    for name, (dst, src) in (("d2h", (host, gpu)), ("h2d", (gpu, host))):
+        ms = []
+        for i in range(a.iters + 3):
+            torch.cuda.synchronize()
+            if dist is not None:
+                dist.barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            dst.copy_(src, non_blocking=True)
+            e1.record()
+            torch.cuda.synchronize()
+            t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+            if dist is not None:
+                dist.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+            if i >= 3:
+                ms.append(float(t.item()))
+        out[name + "_gbs_per_gpu"] = round(n / float(np.median(ms)) / 1e6, 2)
+    # both directions at once (a put on one stream, a get on another)
+    s1, s2 = torch.cuda.Stream(), torch.cuda.Stream()
+    host2 = torch.empty(n, dtype=torch.uint8).pin_memory()
+    gpu2 = torch.empty(n, dtype=torch.uint8, device=dev)
+    ms = []
+    for i in range(a.iters + 3):
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+        e0, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+        e0.record()
+        s1.wait_event(e0); s2.wait_event(e0)
+        with torch.cuda.stream(s1):
+            host.copy_(gpu, non_blocking=True); e1.record(s1)
+        with torch.cuda.stream(s2):
+            gpu2.copy_(host2, non_blocking=True); e2.record(s2)
+        torch.cuda.synchronize()
+        t = torch.tensor([max(e0.elapsed_time(e1), e0.elapsed_time(e2))], dtype=torch.float64, device=dev)
+        if dist is not None:
+            dist.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        if i >= 3:
+            ms.append(float(t.item()))
+    out["bidirectional_gbs_per_gpu_sum"] = round(2 * n / float(np.median(ms)) / 1e6, 2)
+    if rank == 0:
+        print(json.dumps(dict(benchmark="memcpy_baseline", gpus=world, gib_per_copy=a.gib, **out)))
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
