@@ -160,7 +160,9 @@ def mode_fanout(a):
             t = timed_max(e0.elapsed_time(e1))
             if i >= 3:
                 ms.append(t)
-        assert decode_status(status) == 0
+        errors = []
+        if decode_status(status) != 0:
+            errors.append(f"copy status {decode_status(status)}")
         t_ind = float(np.median(ms))
         want = kv[L - 1][torch.from_numpy(gpu_blocks).to(dev)].clone()
         # one reader, NVSwitch multicast
@@ -181,12 +183,18 @@ def mode_fanout(a):
                 ok = wait_flag(sym, epoch, timeout_s=20.0)
                 wall = (time.perf_counter() - t0) * 1e3
                 torch.cuda.synchronize()
-                assert ok, "completion flag never arrived"
+                if not ok:
+                    errors.append("completion flag never arrived")
                 t = timed_max(e0.elapsed_time(e1) if rank == 0 else 0.0)
                 w = timed_max(wall)
                 if i >= 3:
                     ms.append((t, w))
-            assert torch.equal(kv[L - 1][torch.from_numpy(gpu_blocks).to(dev)], want), f"rank {rank}: bytes differ"
+            # every rank walks the same collective sequence whatever it found: a rank must not leave
+            # while its memory is bound to the multicast object
+            if not torch.equal(kv[L - 1][torch.from_numpy(gpu_blocks).to(dev)], want):
+                errors.append("bytes differ")
+            bad = torch.tensor([len(errors)], dtype=torch.float64, device=dev)
+            dist.all_reduce(bad, op=dist.ReduceOp.SUM)
             t_fan = float(np.median([m[0] for m in ms]))
             w_fan = float(np.median([m[1] for m in ms]))
             if rank == 0:
@@ -195,7 +203,8 @@ def mode_fanout(a):
                                  fanout_until_flag_seen_ms_host_clock=round(w_fan, 3),
                                  host_bytes_read_independent=total * world, host_bytes_read_fanout=total,
                                  delivered_gbs_fanout=round(total * world / t_fan / 1e6, 1),
-                                 delivered_gbs_independent=round(total * world / t_ind / 1e6, 1)))
+                                 delivered_gbs_independent=round(total * world / t_ind / 1e6, 1),
+                                 errors_over_ranks=int(bad.item()), rank0_errors=errors[:3]))
                 print(json.dumps(rows[-1]), flush=True)
             dist.barrier()
         return rows
