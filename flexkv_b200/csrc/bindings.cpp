@@ -76,29 +76,27 @@ PYBIND11_MODULE(_C, m) {
   }, py::arg("token_ids"), py::arg("tokens_per_block"), py::arg("namespace_prefix") = py::none());
 
   m.def("gen_hashes_batch", [](std::vector<I64Array> seqs, int tokens_per_block, py::object ns, int threads) {
+    if (tokens_per_block <= 0) throw std::invalid_argument("tokens_per_block must be positive");
     I64Array nsa;
     const int64_t* nsp = nullptr;
     int64_t nsl = 0;
     if (!ns.is_none()) { nsa = ns.cast<I64Array>(); nsp = nsa.data(); nsl = (int64_t)nsa.size(); }
     const int64_t n = (int64_t)seqs.size();
-    std::vector<int64_t> off(n + 1, 0), ooff(n + 1, 0);
-    for (int64_t i = 0; i < n; ++i) {
-      off[i + 1] = off[i] + (int64_t)seqs[i].size();
-      ooff[i + 1] = ooff[i] + (int64_t)seqs[i].size() / tokens_per_block;
-    }
-    std::vector<int64_t> flat((size_t)off[n]);
-    for (int64_t i = 0; i < n; ++i)
-      if (seqs[i].size()) std::memcpy(flat.data() + off[i], seqs[i].data(), (size_t)seqs[i].size() * 8);
-    std::vector<uint64_t> out((size_t)ooff[n]);
-    {
-      py::gil_scoped_release rel;
-      gen_block_hashes_batch(flat.data(), off.data(), n, tokens_per_block, nsp, nsl, out.data(), ooff.data(), threads);
-    }
+    // hash straight from the callers' arrays into the result arrays: no flattening copies
+    std::vector<const int64_t*> in((size_t)n);
+    std::vector<int64_t> len((size_t)n);
+    std::vector<uint64_t*> out((size_t)n);
     py::list res;
     for (int64_t i = 0; i < n; ++i) {
-      py::array_t<uint64_t> a((py::ssize_t)(ooff[i + 1] - ooff[i]));
-      if (a.size()) std::memcpy(a.mutable_data(), out.data() + ooff[i], (size_t)a.size() * 8);
+      in[(size_t)i] = seqs[(size_t)i].data();
+      len[(size_t)i] = (int64_t)seqs[(size_t)i].size();
+      py::array_t<uint64_t> a((py::ssize_t)(len[(size_t)i] / tokens_per_block));
+      out[(size_t)i] = a.mutable_data();
       res.append(a);
+    }
+    {
+      py::gil_scoped_release rel;
+      gen_block_hashes_ptrs(in.data(), len.data(), n, tokens_per_block, nsp, nsl, out.data(), threads);
     }
     return res;
   }, py::arg("seqs"), py::arg("tokens_per_block"), py::arg("namespace_prefix") = py::none(), py::arg("threads") = 4);

@@ -29,5 +29,8 @@ inline int64_t gen_block_hashes(const int64_t* tokens, int64_t num_tokens, int t
 void gen_block_hashes_batch(const int64_t* tokens, const int64_t* offsets, int64_t n, int tokens_per_block,
                             const int64_t* ns_prefix, int64_t ns_len, uint64_t* out, const int64_t* out_offsets,
                             int num_threads);
+// Same, over separately stored sequences and result buffers (no flattening).
+void gen_block_hashes_ptrs(const int64_t* const* seqs, const int64_t* lens, int64_t n, int tokens_per_block,
+                           const int64_t* ns_prefix, int64_t ns_len, uint64_t* const* outs, int num_threads);
 
 }  // namespace fkv
