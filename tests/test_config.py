@@ -1,0 +1,96 @@
+"""Configuration: environment table, user config files, GB -> block conversion, model geometry
+(reference tests: test_config_hugepage.py, test_recompute_block_counts.py; code
+flexkv/common/config.py:748-841,843-944,946-1246)."""
+import json
+import os
+
+import pytest
+import torch
+
+from flexkv_b200.common import config as cfgmod
+from flexkv_b200.common.config import (CacheConfig, ModelConfig, UserConfig, apply_overrides, convert_to_block_num,
+                                       load_env_config, load_user_config_from_file, parse_path_list,
+                                       recompute_block_counts, update_default_config_from_user_config)
+
+
+def _llama():
+    return ModelConfig(num_layers=32, num_kv_heads=8, head_size=128, dtype=torch.bfloat16)
+
+
+def test_block_geometry_and_gb_conversion():
+    m = _llama()
+    assert m.token_size_in_bytes == 32 * 2 * 8 * 128 * 2            # 128 KiB per token
+    assert m.block_size_in_bytes(16) == 2 << 20
+    assert convert_to_block_num(1.0, 2 << 20) == 512
+    mla = ModelConfig(num_layers=61, num_kv_heads=1, head_size=576, use_mla=True, dtype=torch.bfloat16)
+    assert mla.block_size_in_bytes(64) == 61 * 64 * 576 * 2
+
+
+def test_user_config_fills_tiers_and_rounds_ssd_blocks_to_directories(tmp_path):
+    m, c = _llama(), CacheConfig(tokens_per_block=16)
+    u = UserConfig(cpu_cache_gb=2, ssd_cache_gb=9, ssd_cache_dir=f"{tmp_path}/a;{tmp_path}/b;{tmp_path}/c",
+                   enable_gds=True, enable_p2p_gpu=True)
+    update_default_config_from_user_config(m, c, u)
+    assert c.num_cpu_blocks == 1024 and c.enable_ssd and c.enable_gds and c.enable_p2p_gpu
+    assert c.ssd_cache_dir == [f"{tmp_path}/a", f"{tmp_path}/b", f"{tmp_path}/c"]
+    assert c.num_ssd_blocks == 4608 - 4608 % 3 and c.num_ssd_blocks % 3 == 0
+    # a later change of the KV geometry re-derives the counts from the remembered sizes
+    m2 = ModelConfig(num_layers=64, num_kv_heads=8, head_size=128, dtype=torch.bfloat16)
+    recompute_block_counts(m2, c)
+    assert c.num_cpu_blocks == 512
+
+
+def test_user_config_validation():
+    with pytest.raises(ValueError):
+        UserConfig(cpu_cache_gb=0)
+    with pytest.raises(ValueError):
+        UserConfig(cpu_cache_gb=8, ssd_cache_gb=4)
+    with pytest.raises(ValueError):
+        CacheConfig(tokens_per_block=12)
+    with pytest.raises(ValueError):
+        CacheConfig(enable_gds=True, enable_ssd=False)
+
+
+def test_files_json_yaml_and_overrides(tmp_path):
+    pj = tmp_path / "c.json"
+    pj.write_text(json.dumps({"cpu_cache_gb": 3, "override_evict_ratio": 0.25, "eviction_policy": "lfu"}))
+    u = load_user_config_from_file(str(pj))
+    assert u.cpu_cache_gb == 3 and u.overrides == {"override_evict_ratio": 0.25, "eviction_policy": "lfu"}
+    env = load_env_config()
+    apply_overrides(u, env)
+    assert env.evict_ratio == 0.25 and env.eviction_policy == "lfu"
+    py = tmp_path / "c.yml"
+    py.write_text("cpu_cache_gb: 5\nenable_p2p_cpu: true\nno_such_key: 1\n")
+    u = load_user_config_from_file(str(py))
+    assert u.cpu_cache_gb == 5 and u.enable_p2p_cpu
+    with pytest.raises(ValueError):
+        apply_overrides(u, load_env_config())
+    assert parse_path_list("/a; /b ;") == ["/a", "/b"] and parse_path_list(["/x"]) == ["/x"]
+
+
+def test_environment_table(monkeypatch):
+    monkeypatch.setenv("FLEXKV_TRANSFER_NUM_CTA_H2D", "12")
+    monkeypatch.setenv("FLEXKV_INDEX_ACCEL", "0")
+    monkeypatch.setenv("FLEXKV_LEASE_TTL_MS", "1234")
+    monkeypatch.setenv("FLEXKV_TRANSFER_ENGINE", "AUTO")
+    monkeypatch.setenv("FLEXKV_USE_CE_TRANSFER_H2D", "1")
+    env = load_env_config()
+    assert env.transfer_num_cta_h2d == 12 and env.index_accel is False and env.lease_ttl_ms == 1234
+    assert env.transfer_engine == "auto" and env.use_ce_transfer_h2d is True
+    from flexkv_b200.transfer.workers import _launch_cfg
+    assert _launch_cfg(env, True)["engine"] == 3
+    env.transfer_engine = "tma"
+    assert _launch_cfg(env, True)["engine"] == 3 and _launch_cfg(env, False)["engine"] == 0
+
+
+def test_model_config_parallel_layout():
+    m = ModelConfig(num_layers=80, num_kv_heads=8, head_size=128, tp_size=8, pp_size=2, dp_size=2, nnodes=4)
+    assert m.total_gpus == 32 and m.gpus_per_node == 8 and m.num_layers_per_pp_stage == 40
+    assert m.effective_tp_size == 8 and m.effective_tp_size_per_node == 8
+    two = ModelConfig(num_layers=8, num_kv_heads=8, head_size=64, tp_size=16, nnodes=2)
+    assert two.nnodes_per_tp_group == 2 and two.effective_tp_size_per_node == 8
+    with pytest.raises(ValueError):
+        ModelConfig(num_layers=8, num_kv_heads=8, head_size=64, tp_size=1, dp_size=3, nnodes=2)
+    m.freeze()
+    with pytest.raises(Exception):
+        m.num_layers = 1
