@@ -90,7 +90,7 @@ def test_model_config_parallel_layout():
     two = ModelConfig(num_layers=8, num_kv_heads=8, head_size=64, tp_size=16, nnodes=2)
     assert two.nnodes_per_tp_group == 2 and two.effective_tp_size_per_node == 8
     with pytest.raises(ValueError):
-        ModelConfig(num_layers=8, num_kv_heads=8, head_size=64, tp_size=1, dp_size=3, nnodes=2)
+        ModelConfig(num_layers=8, num_kv_heads=8, head_size=64, tp_size=1, dp_size=3, nnodes=2).freeze()
     m.freeze()
     with pytest.raises(Exception):
         m.num_layers = 1
