@@ -247,6 +247,13 @@ class TransferOpGraph:
         self._ready.clear()
         return out
 
+    def requeue(self, op_id: int) -> None:
+        """Hands an op that was taken but not started back to the ready set."""
+        op = self._ops[op_id]
+        if op.status == TransferOpStatus.RUNNING:
+            op.status = TransferOpStatus.PENDING
+            self._ready.add(op_id)
+
     def mark_completed(self, op_id: int, success: bool = True) -> List[int]:
         """Returns ids of ops that became ready."""
         op = self._ops[op_id]

@@ -112,6 +112,28 @@ class KVManager:
                               pp_rank=pp_rank, tp_rank=tp_rank, keepalive=list(tensors))
         self.transfer_manager.register_swa(reg)
 
+    # ---- sleep / wake of the engine's GPU memory ---------------------------------------
+    def suspend_gpu_mappings(self, dp_client_id: Optional[int] = None, timeout: float = 60.0) -> bool:
+        """Returns once no transfer touches this client's GPU tensors; later GPU ops wait for
+        ``resume_gpu_mappings``. The host cache stays intact."""
+        if self.server_client_mode:
+            raise RuntimeError("in server-client mode use KVTPClient.suspend_gpu_mappings")
+        return self.transfer_manager.suspend_gpu_mappings(self.dp_client_id if dp_client_id is None else dp_client_id,
+                                                          timeout)
+
+    def resume_gpu_mappings(self, tensors: Optional[Sequence[torch.Tensor]] = None,
+                            gpu_layout: Optional[KVCacheLayout] = None, tp_rank: int = 0, pp_rank: int = 0,
+                            dp_client_id: Optional[int] = None) -> None:
+        """Pass the re-created tensors when the engine re-allocated its cache on wake."""
+        if self.server_client_mode:
+            raise RuntimeError("in server-client mode use KVTPClient.resume_gpu_mappings")
+        dp = self.dp_client_id if dp_client_id is None else dp_client_id
+        regs = []
+        if tensors is not None:
+            from .storage.gpu_layout import register_tensors
+            regs.append(register_tensors(tensors, gpu_layout, tp_rank=tp_rank, pp_rank=pp_rank, dp_client_id=dp))
+        self.transfer_manager.resume_gpu_mappings(dp, regs)
+
     # ---- lifecycle ------------------------------------------------------------
     def start(self) -> None:
         if self.server_client_mode:

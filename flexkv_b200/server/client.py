@@ -136,5 +136,37 @@ class KVTPClient:
         flexkv_logger.info("sent GPU registration: dp %d rank %d, %d tensors", self.dp_client_id,
                            self.intra_client_id, len(kv_caches))
 
+    # ---- sleep / wake (vLLM sleep mode) ----------------------------------------------------
+    def _control(self, action: str, registration=None, timeout: float = 60.0) -> bool:
+        import os
+        import uuid
+        ep = f"ipc:///tmp/flexkv_ctl_{os.getpid()}_{uuid.uuid4().hex[:8]}"
+        reply = get_zmq_socket(self._ctx, zmq.PULL, ep, bind=True)
+        try:
+            req = R.GpuControlRequest(self.dp_client_id, action, ep, registration, timeout)
+            self._sock.send(pickle.dumps(req, protocol=pickle.HIGHEST_PROTOCOL))
+            if not reply.poll(int((timeout + 5) * 1000)):
+                return False
+            return bool(pickle.loads(reply.recv()))
+        finally:
+            reply.close()
+            try:
+                os.unlink(ep[len("ipc://"):])
+            except OSError:
+                pass
+
+    def suspend_gpu_mappings(self, timeout: float = 60.0) -> bool:
+        """Blocks until the data plane no longer touches (or maps) this client's KV tensors."""
+        return self._control("suspend", None, timeout)
+
+    def resume_gpu_mappings(self, kv_caches: Optional[Sequence[torch.Tensor]] = None,
+                            kv_layout: Optional[KVCacheLayout] = None, mode: Optional[str] = None) -> bool:
+        reg = None
+        if kv_caches is not None:
+            self._handles = [TensorSharedHandle.export(t, mode) for t in kv_caches]
+            reg = R.RegisterTPClientRequest(self.dp_client_id, self.intra_client_id, self.device_id, self._handles,
+                                            kv_layout, pp_rank=self.pp_rank, tp_rank=self.tp_rank)
+        return self._control("resume", reg)
+
     def shutdown(self) -> None:
         self._sock.close()

@@ -11,7 +11,7 @@ import zmq
 
 from ..common.debug import flexkv_logger
 from ..storage.gpu_layout import GpuRegistration, describe_gpu_tensors
-from .request import RegisterTPClientRequest
+from .request import GpuControlRequest, RegisterTPClientRequest
 from .utils import get_zmq_socket
 
 
@@ -26,9 +26,11 @@ def registration_from_request(req: RegisterTPClientRequest) -> GpuRegistration:
 
 
 class RegistrationListener:
-    def __init__(self, endpoint: str, on_register: Callable[[GpuRegistration], None]) -> None:
+    def __init__(self, endpoint: str, on_register: Callable[[GpuRegistration], None],
+                 on_control: Optional[Callable[[GpuControlRequest], bool]] = None) -> None:
         self.endpoint = endpoint
         self.on_register = on_register
+        self.on_control = on_control
         self._ctx = zmq.Context.instance()
         self._sock = get_zmq_socket(self._ctx, zmq.PULL, endpoint, bind=True)
         self._stop = threading.Event()
@@ -52,6 +54,15 @@ class RegistrationListener:
                     self.count += 1
                     flexkv_logger.info("registered GPU tensors of dp client %d rank %d (device %d)",
                                        req.dp_client_id, req.intra_client_id, req.device_id)
+                elif isinstance(req, GpuControlRequest):
+                    ok = False
+                    try:
+                        ok = bool(self.on_control(req)) if self.on_control is not None else False
+                    finally:
+                        if req.reply_endpoint:
+                            rs = get_zmq_socket(self._ctx, zmq.PUSH, req.reply_endpoint, bind=False)
+                            rs.send(pickle.dumps(ok))
+                            rs.close(linger=1000)
             except Exception:  # noqa: BLE001
                 flexkv_logger.exception("bad GPU registration message")
 

@@ -35,6 +35,18 @@ class RegisterTPClientRequest:
 
 
 @dataclass
+class GpuControlRequest:
+    """Sleep / wake of one engine worker's GPU memory, sent on the registration channel
+    (the reference uses a dedicated REP socket: flexkv/transfer_manager.py:167-245).
+    ``registration`` carries the handles of the re-created tensors on resume."""
+    dp_client_id: int
+    action: str                        # "suspend" | "resume"
+    reply_endpoint: str = ""
+    registration: Optional[RegisterTPClientRequest] = None
+    timeout: float = 60.0
+
+
+@dataclass
 class IsReadyRequest(Request):
     pass
 

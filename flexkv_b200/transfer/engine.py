@@ -29,6 +29,10 @@ from .trace import TransferTrace
 from .workers import OpOutcome, TransferWorker, build_workers
 
 
+_GPU_TYPES = (TransferType.H2D, TransferType.D2H, TransferType.LAYERWISE, TransferType.PEERD2D, TransferType.DISK2D,
+              TransferType.D2DISK)
+
+
 class TransferEngine:
     def __init__(self, storage, model_config: ModelConfig, cache_config: CacheConfig,
                  workers: Optional[Dict[Tuple[WorkerKey, TransferType], TransferWorker]] = None) -> None:
@@ -45,6 +49,11 @@ class TransferEngine:
         self._stopping = False
         self._trace = TransferTrace(enabled=GLOBAL_CONFIG_FROM_ENV.enable_transfer_trace)
         self._metrics = None
+        # sleep/wake of the engine's GPU memory: ops that touch a suspended client's GPU are parked
+        self._suspended: set = set()
+        self._parked: List[Tuple[TransferOpGraph, TransferOp]] = []
+        self._gpu_inflight: Dict[WorkerKey, int] = {}
+        self._drain_waiters: List[Tuple[set, threading.Event]] = []
         self.stats = dict(ops=0, failed_ops=0, graphs=0, failed_graphs=0)
         self.stats_by_type: Dict[str, List[float]] = {}     # type -> [ops, blocks, bytes, kernel or IO ms]
 
@@ -114,6 +123,10 @@ class TransferEngine:
                     self._on_submit(a)
                 elif kind == "done":
                     self._on_done(a, b)
+                elif kind == "suspend":
+                    self._on_suspend(a, b)
+                elif kind == "resume":
+                    self._on_resume(a, b)
             except Exception:  # noqa: BLE001  - the scheduler must survive a bad graph
                 flexkv_logger.exception("transfer scheduler error")
 
@@ -138,6 +151,9 @@ class TransferEngine:
                     progress = True
                     continue
                 key = WorkerKey(op.dp_client_id, 0)
+                if key in self._suspended and op.transfer_type in _GPU_TYPES:
+                    self._parked.append((graph, op))       # runs after resume_gpu_mappings
+                    continue
                 w = self._workers.get((key, "SWA" if op.is_swa else op.transfer_type))
                 if w is None and not op.is_swa and op.transfer_type not in (TransferType.H2D, TransferType.D2H, TransferType.LAYERWISE,
                                                           TransferType.PEERD2D, TransferType.DISK2D,
@@ -150,12 +166,86 @@ class TransferEngine:
                     self._completed.put(CompletedOp(graph.graph_id, op.op_id, False))
                     continue
                 self._inflight[graph.graph_id] += 1
+                if op.transfer_type in _GPU_TYPES:
+                    self._gpu_inflight[key] = self._gpu_inflight.get(key, 0) + 1
                 self._trace.on_submit(op)
                 w.submit(op)
         if graph.all_transfer_ops_completed() or (graph.failed and self._inflight[graph.graph_id] == 0):
             self._finish_graph(graph)
 
+    # ---- sleep / wake -----------------------------------------------------------
+    def suspend_gpu_mappings(self, dp_client_id: Optional[int] = None, timeout: float = 60.0) -> bool:
+        """Stops touching the GPU memory of one data-parallel client (all when None): ops that
+        need it are parked, and the call returns once none is in flight, so the engine may
+        release or remap that memory (vLLM sleep mode; flexkv/transfer/transfer_engine.py:1661-1716).
+        The host, SSD and remote tiers keep working."""
+        keys = {k for k in (self.storage.gpu_regs if self.storage is not None else {})
+                if dp_client_id is None or k.dp_client_id == dp_client_id}
+        ev = threading.Event()
+        self._events.put(("suspend", keys, ev))
+        return ev.wait(timeout)
+
+    def resume_gpu_mappings(self, dp_client_id: Optional[int] = None, new_registrations=None) -> None:
+        """``new_registrations``: GpuRegistration objects of the re-created tensors (same geometry,
+        new addresses); omitted when the memory came back at the old addresses."""
+        keys = {k for k in (self.storage.gpu_regs if self.storage is not None else {})
+                if dp_client_id is None or k.dp_client_id == dp_client_id}
+        done = threading.Event()
+        self._events.put(("resume", (keys, list(new_registrations or [])), done))
+        done.wait(60.0)
+
+    def _on_suspend(self, keys: set, ev: threading.Event) -> None:
+        self._suspended |= keys
+        if all(self._gpu_inflight.get(k, 0) == 0 for k in keys):
+            ev.set()
+        else:
+            self._drain_waiters.append((keys, ev))
+
+    def _on_resume(self, arg, done: threading.Event) -> None:
+        keys, regs = arg
+        try:
+            for reg in regs:
+                key = WorkerKey(reg.dp_client_id, reg.pp_rank)
+                old = self.storage.gpu_regs.get(key, {}).get(reg.tp_rank)
+                if old is None:
+                    raise ValueError(f"resume: no registration for {key} rank {reg.tp_rank}")
+                if (old.chunk_bytes, old.num_layers, old.kv_dim, len(old.ptrs)) != \
+                        (reg.chunk_bytes, reg.num_layers, reg.kv_dim, len(reg.ptrs)):
+                    raise ValueError("resume: the re-registered tensors have a different geometry")
+                old.ptrs = list(reg.ptrs)
+                old.num_blocks = reg.num_blocks
+                old.keepalive = reg.keepalive
+                rank_index = sorted(self.storage.gpu_regs[key]).index(reg.tp_rank)
+                for (k, _), w in self._workers.items():
+                    if k == key and hasattr(w, "update_gpu_ptrs"):
+                        w.update_gpu_ptrs(rank_index, [int(p) for p in reg.ptrs])
+            self._suspended -= keys
+            parked, self._parked = self._parked, []
+            touched = []
+            for graph, op in parked:
+                if WorkerKey(op.dp_client_id, 0) in self._suspended:
+                    self._parked.append((graph, op))
+                    continue
+                graph.requeue(op.op_id)
+                if graph not in touched:
+                    touched.append(graph)
+            for g in touched:
+                self._dispatch(g)
+        finally:
+            done.set()
+
     def _on_done(self, op: TransferOp, outcome: OpOutcome) -> None:
+        if op.transfer_type in _GPU_TYPES:
+            key = WorkerKey(op.dp_client_id, 0)
+            self._gpu_inflight[key] = max(0, self._gpu_inflight.get(key, 0) - 1)
+            if self._drain_waiters:
+                still = []
+                for keys, ev in self._drain_waiters:
+                    if all(self._gpu_inflight.get(k, 0) == 0 for k in keys):
+                        ev.set()
+                    else:
+                        still.append((keys, ev))
+                self._drain_waiters = still
         graph = self._graphs.get(op.graph_id)
         if graph is None:
             return

@@ -175,6 +175,9 @@ class GpuHostWorker(TransferWorker):
     group_layers = 0
     max_blocks = 1 << 16
 
+    def update_gpu_ptrs(self, rank_index: int, ptrs) -> None:
+        self.group.update_gpu_ptrs(rank_index, list(ptrs))
+
 
 class HostEmulatedGpuWorker(TransferWorker):
     """GPU-less data plane: the registered "GPU" tensors are host tensors and

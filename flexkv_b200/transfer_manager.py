@@ -67,7 +67,7 @@ class TransferManager:
             return
         if self.gpu_register_port:
             from .server.registration import RegistrationListener
-            self._listener = RegistrationListener(self.gpu_register_port, self.register_gpu)
+            self._listener = RegistrationListener(self.gpu_register_port, self.register_gpu, self._on_gpu_control)
             self._listener.start()
         self._init_thread = threading.Thread(target=self._init, name="flexkv-tm-init", daemon=True)
         self._init_thread.start()
@@ -127,6 +127,36 @@ class TransferManager:
         self._metrics = collector
         if self.engine is not None:
             self.engine.set_metrics_collector(collector)
+
+    def suspend_gpu_mappings(self, dp_client_id: Optional[int] = None, timeout: float = 60.0) -> bool:
+        if self.engine is None:
+            return True
+        return self.engine.suspend_gpu_mappings(dp_client_id, timeout)
+
+    def resume_gpu_mappings(self, dp_client_id: Optional[int] = None, new_registrations=None) -> None:
+        if self.engine is not None:
+            self.engine.resume_gpu_mappings(dp_client_id, new_registrations)
+
+    def _on_gpu_control(self, req) -> bool:
+        """Sleep / wake requests of engine worker processes (their tensors are IPC mappings here)."""
+        from .server.registration import registration_from_request
+        if req.action == "suspend":
+            ok = self.suspend_gpu_mappings(req.dp_client_id, req.timeout)
+            if ok and self.storage is not None:
+                # drop this process's view of the memory so that the owner can really free it
+                for key, ranks in self.storage.gpu_regs.items():
+                    if key.dp_client_id != req.dp_client_id:
+                        continue
+                    for reg in ranks.values():
+                        for h in (reg.keepalive or []):
+                            if hasattr(h, "close"):
+                                h.close()
+            return ok
+        if req.action == "resume":
+            regs = [registration_from_request(req.registration)] if req.registration is not None else []
+            self.resume_gpu_mappings(req.dp_client_id, regs)
+            return True
+        return False
 
     def submit(self, graph: TransferOpGraph) -> None:
         self.submit_batch([graph])

@@ -54,3 +54,43 @@ def test_two_dp_ranks_share_one_server():
             m0.launch(12345, slots(dst, T))        # server-side errors come back as exceptions
     finally:
         m1.shutdown(); m0.shutdown()
+
+
+def test_tp_client_sleep_and_wake_over_the_registration_channel():
+    """An engine worker asks the data plane to let go of its tensors, re-creates them and
+    re-registers; a get issued while asleep completes into the new tensors."""
+    shape = KVShape("s", 2, 2, 16, tokens_per_block=4)
+    T = 4
+    model = make_model_config(shape, dp_size=2)
+    cache = CacheConfig(tokens_per_block=T, num_cpu_blocks=32)
+    ep, reg = unique_ipc_endpoint("srv"), unique_ipc_endpoint("reg")
+    m0 = KVManager(model, cache, dp_client_id=0, server_recv_port=ep, gpu_register_port=reg, require_gpu=True)
+    m1 = KVManager(model, cache, dp_client_id=1, server_recv_port=ep, gpu_register_port=reg)
+    clients, caches = [], []
+    for d in range(2):
+        kv, layout = alloc_paged_cache(shape, 32, "cpu", "vllm", fill="normal", seed=90 + d)
+        c = KVTPClient(reg, dp_client_id=d, device_id=0, tp_rank=0)
+        c.register_to_server(kv, layout, mode="same_process")
+        clients.append(c); caches.append((kv, layout))
+    m0.start(); m1.start()
+    try:
+        m0.wait_ready(30); m1.wait_ready(30)
+        tok = np.arange(4 * T, dtype=np.int64) + 40
+        tid = m0.put_async(tok, slots([5, 6, 7, 8], T))
+        assert m0.wait(tid, completely=True)[tid].status.value == "success"
+        want = [t[:, 5:9].clone() for t in caches[0][0]]
+        assert clients[1].suspend_gpu_mappings(timeout=10)
+        tid = m1.get_async(tok, slots([20, 21, 22, 23], T))
+        time.sleep(0.2)
+        assert m1.wait(tid, timeout=0.2)[tid].status.value != "success"          # parked
+        tid0 = m0.put_async(tok + 1000, slots([1, 2, 3, 4], T))                  # the other client is unaffected
+        assert m0.wait(tid0, completely=True)[tid0].status.value == "success"
+        kv2, layout2 = alloc_paged_cache(shape, 32, "cpu", "vllm", fill="zeros")
+        assert clients[1].resume_gpu_mappings(kv2, layout2, mode="same_process")
+        assert m1.wait(tid, timeout=10)[tid].status.value == "success"
+        for l in range(2):
+            assert torch.equal(kv2[l][:, 20:24], want[l])
+    finally:
+        for c in clients:
+            c.shutdown()
+        m1.shutdown(); m0.shutdown()
