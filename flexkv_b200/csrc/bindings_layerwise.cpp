@@ -33,6 +33,7 @@ void init_layerwise_bindings(py::module_& m) {
              py::gil_scoped_release rel;
              return new LayerwiseGroup(std::move(gs), h, lo);
            }))
+      .def("update_gpu_ptrs", &LayerwiseGroup::update_gpu_ptrs)
       .def("restore", [](LayerwiseGroup& g, I64Array gpu_blocks, I64Array cpu_blocks, int counter_id, py::object ssd,
                          py::object ssd_layout, py::object ssd_src, py::object cpu_dst) {
              if (gpu_blocks.size() != cpu_blocks.size()) throw std::invalid_argument("block id arrays differ in size");
@@ -88,6 +89,7 @@ void init_layerwise_bindings(py::module_& m) {
              py::gil_scoped_release rel;
              return c.pull(dst_rank, src_rank, d, s, n, layer_start, num_layers);
            })
+      .def("update_gpu_ptrs", &PeerCopier::update_gpu_ptrs)
       .def("can_access", &PeerCopier::can_access)
       .def_property_readonly("num_ranks", &PeerCopier::num_ranks);
 

@@ -203,6 +203,12 @@ void LayerwiseGroup::rank_main(int r) {
   if (rk.notify_stream) cudaStreamDestroy(rk.notify_stream);
 }
 
+void LayerwiseGroup::update_gpu_ptrs(int rank, const std::vector<uint64_t>& ptrs) {
+  if ((int)ptrs.size() > kMaxGpuPtrs) throw std::invalid_argument("too many GPU tensors");
+  std::lock_guard<std::mutex> api(api_mu_);
+  gpus_.at((size_t)rank).ptrs = ptrs;
+}
+
 void LayerwiseGroup::run_job(int r, const Job& j) {
   Rank& rk = *ranks_[(size_t)r];
   const int L = opt_.group.num_layers, R = (int)gpus_.size();

@@ -75,6 +75,8 @@ class LayerwiseGroup {
   // makes `stream` (a CUDA stream of rank's device) wait for layer `layer` of the restore in flight on `counter`
   cudaError_t stream_wait_layer(int rank, int counter, int layer, cudaStream_t stream);
   int num_ranks() const { return (int)gpus_.size(); }
+  // new tensor addresses after the engine re-created its cache; call with no restore in flight
+  void update_gpu_ptrs(int rank, const std::vector<uint64_t>& ptrs);
   int num_layers() const { return opt_.group.num_layers; }
   int num_counters() const { return opt_.num_counters; }
 

@@ -76,6 +76,11 @@ bool PeerCopier::can_access(int dst_rank, int src_rank) {
   return true;
 }
 
+void PeerCopier::update_gpu_ptrs(int rank, const std::vector<uint64_t>& ptrs) {
+  if ((int)ptrs.size() > kMaxGpuPtrs) throw std::invalid_argument("too many GPU tensors");
+  ranks_.at((size_t)rank).ptrs = ptrs;
+}
+
 OpResult PeerCopier::pull(int dst_rank, int src_rank, const int64_t* dst_blocks, const int64_t* src_blocks, int64_t n,
                           int layer_start, int num_layers) {
   OpResult res;

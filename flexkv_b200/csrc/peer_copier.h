@@ -31,6 +31,7 @@ class PeerCopier {
                 int layer_start, int num_layers);
   bool can_access(int dst_rank, int src_rank);
   int num_ranks() const { return (int)ranks_.size(); }
+  void update_gpu_ptrs(int rank, const std::vector<uint64_t>& ptrs);  // with no pull in flight for that rank
 
  private:
   struct PerDst {

@@ -118,8 +118,11 @@ class KVManager:
         ``resume_gpu_mappings``. The host cache stays intact."""
         if self.server_client_mode:
             raise RuntimeError("in server-client mode use KVTPClient.suspend_gpu_mappings")
-        return self.transfer_manager.suspend_gpu_mappings(self.dp_client_id if dp_client_id is None else dp_client_id,
-                                                          timeout)
+        dp = self.dp_client_id if dp_client_id is None else dp_client_id
+        pd = self.kv_task_engine.cache_engine.peer_directory
+        if pd is not None:
+            pd.clear_rank(dp)           # nobody may plan a pull out of memory that is about to go away
+        return self.transfer_manager.suspend_gpu_mappings(dp, timeout)
 
     def resume_gpu_mappings(self, tensors: Optional[Sequence[torch.Tensor]] = None,
                             gpu_layout: Optional[KVCacheLayout] = None, tp_rank: int = 0, pp_rank: int = 0,

@@ -219,6 +219,8 @@ class TransferEngine:
                 for (k, _), w in self._workers.items():
                     if k == key and hasattr(w, "update_gpu_ptrs"):
                         w.update_gpu_ptrs(rank_index, [int(p) for p in reg.ptrs])
+                    if hasattr(w, "update_gpu_ptrs_for") and reg.tp_rank == 0 and key.dp_client_id in w.rank_of:
+                        w.update_gpu_ptrs_for(key.dp_client_id, [int(p) for p in reg.ptrs])
             self._suspended -= keys
             parked, self._parked = self._parked, []
             touched = []

@@ -181,6 +181,9 @@ class LayerwiseWorker(TransferWorker):
         return OpOutcome(r.status == 0, gpu_ms=r.total_ms, num_bytes=nbytes,
                          error="" if r.status == 0 else f"layerwise status 0x{r.status & 0xffffffff:x}")
 
+    def update_gpu_ptrs(self, rank_index: int, ptrs) -> None:
+        self.group.update_gpu_ptrs(rank_index, list(ptrs))
+
     def close(self) -> None:
         if self.receiver is not None:
             self.receiver.stop()

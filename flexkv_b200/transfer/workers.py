@@ -328,6 +328,9 @@ class PeerD2DWorker(TransferWorker):
                                            tile_bytes=env.transfer_tile_bytes, engine=0,
                                            max_blocks_per_op=max(4096, max(r.num_blocks for r in regs)))
 
+    def update_gpu_ptrs_for(self, dp_client_id: int, ptrs) -> None:
+        self.copier.update_gpu_ptrs(self.rank_of[dp_client_id], list(ptrs))
+
     def execute(self, op: TransferOp) -> OpOutcome:
         src, dst, owners = op.src_block_ids, op.dst_block_ids, op.remote_node_ids
         if dst.size != src.size or owners is None or owners.size != src.size:
