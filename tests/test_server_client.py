@@ -11,6 +11,7 @@ import torch
 
 from flexkv_b200 import CacheConfig, KVManager, KVTPClient
 from flexkv_b200.models import KVShape, alloc_paged_cache, make_model_config
+from flexkv_b200.common.memory_handle import alloc_shared_host_tensor
 from flexkv_b200.server.utils import unique_ipc_endpoint
 
 
@@ -94,3 +95,63 @@ def test_tp_client_sleep_and_wake_over_the_registration_channel():
         for c in clients:
             c.shutdown()
         m1.shutdown(); m0.shutdown()
+
+
+def test_external_server_process(tmp_path, monkeypatch):
+    """The server runs as its own process; the manager only creates clients."""
+    import json
+    import subprocess
+    import sys
+    from flexkv_b200.common.config import GLOBAL_CONFIG_FROM_ENV
+    T = 4
+    shape = KVShape("x", 2, 2, 16, tokens_per_block=T)
+    ep, reg = unique_ipc_endpoint("xsrv"), unique_ipc_endpoint("xreg")
+    mcfg = dict(num_layers=2, num_kv_heads=2, head_size=16, dtype="bfloat16", dp_size=2)
+    ccfg = dict(tokens_per_block=T, num_cpu_blocks=16)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    proc = subprocess.Popen([sys.executable, "-m", "flexkv_b200.server", "--model-config", json.dumps(mcfg),
+                             "--cache-config", json.dumps(ccfg), "--recv-endpoint", ep, "--gpu-register-port", reg,
+                             "--no-gpu"], cwd=root, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    monkeypatch.setattr(GLOBAL_CONFIG_FROM_ENV, "server_launch_mode", "external")
+    mgrs, tp_clients = [], []
+    t0 = time.time()
+    while not os.path.exists(reg[len("ipc://"):]) and time.time() - t0 < 60:      # the server binds its sockets
+        time.sleep(0.1)
+    try:
+        model = make_model_config(shape, dp_size=2)
+        cache = CacheConfig(**ccfg)
+        keep = []
+        for d in range(2):
+            mgrs.append(KVManager(model, cache, dp_client_id=d, server_recv_port=ep, gpu_register_port=reg))
+            assert mgrs[-1].server_handle is None
+            src_kv, layout = alloc_paged_cache(shape, 16, "cpu", "vllm", fill="normal", seed=d)
+            # another process cannot open host stand-ins by address: put them in shared files
+            kv = []
+            for i, t in enumerate(src_kv):
+                s = alloc_shared_host_tensor(t.shape, t.dtype, str(tmp_path / f"kv_{d}_{i}.bin"))
+                s.copy_(t)
+                kv.append(s)
+            tp_clients.append(KVTPClient(reg, dp_client_id=d, device_id=0, tp_rank=0))
+            tp_clients[-1].register_to_server(kv, layout)
+            keep.append(kv)
+        for m in mgrs:
+            m.start()
+        for m in mgrs:
+            m.wait_ready(60)
+        tok = np.arange(3 * T, dtype=np.int64)
+        tid = mgrs[0].put_async(tok, slots([1, 2, 3], T))
+        assert mgrs[0].wait(tid, completely=True)[tid].status.value == "success"
+        tid = mgrs[1].get_async(tok, slots([5, 6, 7], T))
+        assert mgrs[1].wait(tid)[tid].status.value == "success"
+        for l in range(2):
+            assert torch.equal(keep[1][l][:, 5:8], keep[0][l][:, 1:4])
+    finally:
+        for m in mgrs:
+            m.shutdown()
+        proc.terminate()
+        try:
+            out, _ = proc.communicate(timeout=20)
+        except subprocess.TimeoutExpired:
+            proc.kill()
+            out, _ = proc.communicate()
+    assert proc.returncode in (0, -15), out[-2000:]
