@@ -1,0 +1,43 @@
+"""Child process standing in for an engine worker: owns the paged KV cache on cuda:0, exports it
+to the process that runs the data plane through CUDA IPC handles, and checks afterwards that the
+bytes the manager moved landed where they should."""
+import json
+import os
+import sys
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, ROOT)
+
+from flexkv_b200 import KVTPClient  # noqa: E402
+from flexkv_b200.models import KVShape, alloc_paged_cache  # noqa: E402
+
+
+def main() -> int:
+    reg_ep, workdir = sys.argv[1], sys.argv[2]
+    dev = torch.device("cuda", 0)
+    shape = KVShape("ipc", 4, 4, 64, tokens_per_block=16)
+    kv, layout = alloc_paged_cache(shape, 64, dev, "vllm", fill="normal", seed=11)
+    before = [t.clone() for t in kv]
+    client = KVTPClient(reg_ep, dp_client_id=0, device_id=0, tp_rank=0)
+    client.register_to_server(kv, layout)             # cuda_ipc handles: the consumer is another process
+    open(os.path.join(workdir, "registered"), "w").close()
+    t0 = time.time()
+    while not os.path.exists(os.path.join(workdir, "moved")) and time.time() - t0 < 120:
+        time.sleep(0.05)
+    torch.cuda.synchronize()
+    src, dst = [3, 9, 1, 30, 12], [40, 41, 42, 43, 44]
+    ok = all(torch.equal(kv[l][:, dst], before[l][:, src]) for l in range(4))
+    untouched = all(torch.equal(kv[l][:, 50:60], before[l][:, 50:60]) for l in range(4))
+    with open(os.path.join(workdir, "result.json"), "w") as f:
+        json.dump({"ok": bool(ok), "untouched": bool(untouched)}, f)
+    while not os.path.exists(os.path.join(workdir, "exit")) and time.time() - t0 < 180:
+        time.sleep(0.05)
+    client.shutdown()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
