@@ -45,11 +45,11 @@ def test_manager_moves_blocks_of_a_cache_owned_by_another_process(tmp_path):
         res = json.loads((tmp_path / "result.json").read_text())
         assert res == {"ok": True, "untouched": True}
     finally:
+        mgr.shutdown()                                  # the importer lets go before the owner frees
         open(tmp_path / "exit", "w").close()
         try:
             out, _ = child.communicate(timeout=60)
         except subprocess.TimeoutExpired:
             child.kill()
             out, _ = child.communicate()
-        mgr.shutdown()
     assert child.returncode == 0, out[-2000:]
