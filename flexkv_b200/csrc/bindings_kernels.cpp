@@ -142,7 +142,7 @@ void init_kernel_bindings(py::module_& m) {
     }
     static const char* names[] = {"kernel", "contig_blocks", "segment_2d"};
     return py::make_tuple(runs, std::string(names[(int)path]), ce_num_copies(a, p, path), a.status);
-  }, py::arg("params"), py::arg("max_copies") = 4096, py::arg("min_bytes_per_copy") = 256 << 10);
+  }, py::arg("params"), py::arg("max_copies") = 4096, py::arg("min_bytes_per_copy") = 8 << 20);
 
   m.def("kv_copy_tma_eligible", [](py::dict params) { return kv_copy_tma_eligible(kv_params_from_dict(params)); });
 }

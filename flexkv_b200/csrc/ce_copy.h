@@ -38,7 +38,9 @@ enum class CePath : int {
 
 struct CePolicy {
   int64_t max_copies = 4096;         // driver calls per op above which the kernel wins
-  int64_t min_bytes_per_copy = 256 << 10;
+  // measured on B200 (2 MiB blocks, 32 KiB chunks): 16 MiB per driver copy gives 54.6 GB/s against the
+  // kernel's 52.0; 2 MiB per copy gives 50.5, below the kernel
+  int64_t min_bytes_per_copy = 8 << 20;
 };
 
 // `gpu_blocks`/`cpu_blocks` must be host-readable. Out-of-range ids are skipped and

@@ -36,7 +36,9 @@ def test_long_run_layerfirst_gpu_goes_2d_and_blockfirst_goes_contiguous():
     n = 512
     d, keep = _params(np.arange(n) + 7, np.arange(n) + 99)
     runs, path, copies, _ = C.ce_plan(d)
-    assert runs.tolist() == [[7, 99, n]] and path == "segment_2d" and copies == 8
+    assert runs.tolist() == [[7, 99, n]] and path == "segment_2d" and copies == 8      # 16 MiB per copy
+    d, keep = _params(np.arange(64) + 7, np.arange(64) + 99)
+    assert C.ce_plan(d)[1] == "kernel"                                                  # 2 MiB per copy: not worth it
     d, keep = _params(np.arange(n) + 7, np.arange(n) + 99, gpu_blockfirst=True)
     runs, path, copies, _ = C.ce_plan(d)
     assert path == "contig_blocks" and copies == 1
