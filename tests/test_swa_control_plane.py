@@ -18,16 +18,17 @@ def slots(blocks):
     return np.repeat(np.asarray(blocks, dtype=np.int64), T) * T + np.tile(np.arange(T), len(blocks))
 
 
-def start(num_slots=4):
+def start(num_slots=4, device="cpu"):
     shape = KVShape("s", 2, 2, 16, tokens_per_block=T)
     cfg = CacheConfig(tokens_per_block=T, num_cpu_blocks=32, enable_swa_transfer=True,
                       swa=SWAPoolConfig(enabled=True, num_slots=num_slots, num_swa_layers=SWA_LAYERS,
                                         bytes_per_token_per_layer=PAGE_BYTES // T, evict_ratio=0.25))
     mgr = KVManager(make_model_config(shape), cfg, require_gpu=True)
-    kv, layout = alloc_paged_cache(shape, 64, "cpu", "vllm", fill="normal", seed=5)
+    dev = "cpu" if device == "cpu" else torch.device(device)
+    kv, layout = alloc_paged_cache(shape, 64, dev, "vllm", fill="normal", seed=5)
     mgr.register_gpu_tensors(kv, layout)
     g = torch.Generator().manual_seed(9)
-    swa = [torch.randint(0, 256, (16, PAGE_BYTES), dtype=torch.uint8, generator=g) for _ in range(SWA_LAYERS)]
+    swa = [torch.randint(0, 256, (16, PAGE_BYTES), dtype=torch.uint8, generator=g).to(dev) for _ in range(SWA_LAYERS)]
     mgr.register_swa_tensors(swa)
     mgr.start(); mgr.wait_ready(30)
     return mgr, kv, swa
@@ -40,8 +41,12 @@ def put(mgr, tok, blocks, page):
     return mgr.wait(tid, completely=True)[tid]
 
 
-def test_put_mounts_and_window_aware_get_restores_page_and_blocks():
-    mgr, kv, swa = start()
+import pytest
+
+
+@pytest.mark.parametrize("device", ["cpu", pytest.param("cuda:0", marks=pytest.mark.gpu)])
+def test_put_mounts_and_window_aware_get_restores_page_and_blocks(device):
+    mgr, kv, swa = start(device=device)
     try:
         tok = np.arange(6 * T, dtype=np.int64) + 100
         src = np.array([3, 9, 1, 30, 12, 7])
