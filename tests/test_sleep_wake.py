@@ -4,6 +4,7 @@ tier keeps its contents, and transfers continue into re-created tensors after wa
 import time
 
 import numpy as np
+import pytest
 import torch
 
 from flexkv_b200 import CacheConfig, KVManager
@@ -16,10 +17,12 @@ def slots(blocks):
     return np.repeat(np.asarray(blocks, dtype=np.int64), T) * T + np.tile(np.arange(T), len(blocks))
 
 
-def test_gets_park_while_suspended_and_land_in_the_new_tensors():
+@pytest.mark.parametrize("device", ["cpu", pytest.param("cuda:0", marks=pytest.mark.gpu)])
+def test_gets_park_while_suspended_and_land_in_the_new_tensors(device):
+    dev = "cpu" if device == "cpu" else torch.device(device)
     shape = KVShape("z", 2, 2, 16, tokens_per_block=T)
     mgr = KVManager(make_model_config(shape), CacheConfig(tokens_per_block=T, num_cpu_blocks=16), require_gpu=True)
-    kv, layout = alloc_paged_cache(shape, 32, "cpu", "vllm", fill="normal", seed=4)
+    kv, layout = alloc_paged_cache(shape, 32, dev, "vllm", fill="normal", seed=4)
     mgr.register_gpu_tensors(kv, layout)
     mgr.start(); mgr.wait_ready(30)
     try:
@@ -36,7 +39,7 @@ def test_gets_park_while_suspended_and_land_in_the_new_tensors():
         r = mgr.wait(tid, timeout=0.2)[tid]
         assert r.status.value in ("timeout", "unready", "running"), r
         # wake with freshly allocated tensors of the same geometry
-        kv2, layout2 = alloc_paged_cache(shape, 32, "cpu", "vllm", fill="zeros")
+        kv2, layout2 = alloc_paged_cache(shape, 32, dev, "vllm", fill="zeros")
         mgr.resume_gpu_mappings(kv2, layout2)
         assert mgr.wait(tid, timeout=10)[tid].status.value == "success"
         for l in range(2):
