@@ -85,12 +85,15 @@ class KVManager:
 
     # ---- in-process registration (engine worker and manager share the process) --------------
     def register_gpu_tensors(self, tensors: Sequence[torch.Tensor], gpu_layout: KVCacheLayout, tp_rank: int = 0,
-                             pp_rank: int = 0, dp_client_id: Optional[int] = None) -> None:
+                             pp_rank: int = 0, dp_client_id: Optional[int] = None, group_id: int = -1) -> None:
+        """``group_id`` names the layer group of a multi-group cache (``ModelConfig.layer_groups``): call once
+        per group with that group's tensors and layout."""
         if self.server_client_mode:
             raise RuntimeError("in server-client mode GPU tensors are registered through KVTPClient")
         from .storage.gpu_layout import register_tensors
         reg = register_tensors(tensors, gpu_layout, tp_rank=tp_rank, pp_rank=pp_rank,
-                               dp_client_id=self.dp_client_id if dp_client_id is None else dp_client_id)
+                               dp_client_id=self.dp_client_id if dp_client_id is None else dp_client_id,
+                               group_id=group_id)
         self.transfer_manager.register_gpu(reg)
 
     def register_swa_tensors(self, tensors: Sequence[torch.Tensor], tp_rank: int = 0, pp_rank: int = 0,

@@ -40,6 +40,7 @@ class GpuRegistration:
     dp_client_id: int = 0
     pp_rank: int = 0
     tp_rank: int = 0                # effective rank inside the host block (cp_rank * tp + tp_rank)
+    group_id: int = -1              # layer group of a multi-group cache (-1: the only group)
     keepalive: Any = field(default=None, repr=False)   # tensors or opened handles
 
     def as_native(self) -> Dict[str, Any]:

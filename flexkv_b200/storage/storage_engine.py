@@ -103,6 +103,7 @@ class StorageEngine:
         self.ssd: Optional[SsdPool] = None
         self.ssd_size_table: Optional[np.ndarray] = None
         self.swa_regs: Dict[WorkerKey, Dict[int, GpuRegistration]] = {}
+        self.gpu_group_regs: Dict[WorkerKey, Dict[int, Dict[int, GpuRegistration]]] = {}
         self.swa_host: Optional[SwaPool] = None
         self._cuda_register = torch.cuda.is_available() if cuda_register is None else cuda_register
         self._numa_node = numa_node
@@ -297,6 +298,12 @@ class StorageEngine:
 
     def register_gpu_blocks(self, reg: GpuRegistration) -> None:
         key = WorkerKey(reg.dp_client_id, reg.pp_rank)
+        if reg.group_id >= 0:
+            # multi-group cache: one registration per (rank, layer group); the first group also stands
+            # for the rank in the per-rank table
+            self.gpu_group_regs.setdefault(key, {}).setdefault(reg.tp_rank, {})[reg.group_id] = reg
+            self.gpu_regs.setdefault(key, {}).setdefault(reg.tp_rank, reg)
+            return
         self.gpu_regs.setdefault(key, {})[reg.tp_rank] = reg
 
     def all_registered(self) -> bool:

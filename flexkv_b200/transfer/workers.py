@@ -228,6 +228,105 @@ class HostEmulatedGpuWorker(TransferWorker):
         return OpOutcome(status == 0, num_bytes=nbytes, error="" if status == 0 else f"copy status 0x{status:x}")
 
 
+class MultiGroupGpuHostWorker(TransferWorker):
+    """H2D / D2H for caches made of several layer groups with different KV shapes (an indexer
+    beside the main cache, compressed-KV groups storing fewer tokens per block). A host block is
+    byte-flat: ``[rank slice][group][layer][kv][chunk]`` with per-group offsets; every group shares
+    the op's block ids and is moved by its own launch per rank
+    (reference format: flexkv/common/storage.py:87-127,249-286, flexkv/transfer/worker.py:886-921)."""
+
+    def __init__(self, storage, model_config: ModelConfig, key: WorkerKey, h2d: bool) -> None:
+        super().__init__()
+        self.h2d = h2d
+        self.name = "h2d-groups" if h2d else "d2h-groups"
+        host = storage.host
+        lay = host.layout
+        per_rank = storage.gpu_group_regs.get(key, {})
+        if not per_rank:
+            raise ValueError("multi-group host pool but no per-group GPU registrations")
+        self.ranks = sorted(per_rank)
+        self.host = host
+        self.slice_bytes = host.block_bytes // lay.tp_slices
+        self.shared = lay.tp_slices == 1 and len(self.ranks) > 1
+        self.groups = lay.groups
+        self.regs = []                       # [rank index][group] -> registration
+        for r in self.ranks:
+            row = []
+            for gid, g in enumerate(lay.groups):
+                reg = per_rank[r].get(gid)
+                if reg is None:
+                    raise ValueError(f"rank {r} did not register layer group {gid}")
+                if (reg.chunk_bytes, reg.num_layers, reg.kv_dim) != (g.chunk_bytes, g.num_layers, g.kv_dim):
+                    raise ValueError(f"layer group {gid}: GPU tensors ({reg.num_layers} layers x {reg.kv_dim} x "
+                                     f"{reg.chunk_bytes} B) do not match the host format ({g.num_layers} x "
+                                     f"{g.kv_dim} x {g.chunk_bytes} B)")
+                row.append(reg)
+            self.regs.append(row)
+        self.on_gpu = self.regs[0][0].device_id >= 0
+        self.num_ctas = GLOBAL_CONFIG_FROM_ENV.transfer_num_cta_h2d if h2d else GLOBAL_CONFIG_FROM_ENV.transfer_num_cta_d2h
+        self._streams, self._status = {}, {}
+        if self.on_gpu:
+            import torch
+            self._torch = torch
+            for row in self.regs:
+                d = row[0].device_id
+                self._streams[d] = torch.cuda.Stream(device=d)
+                self._status[d] = torch.zeros(8, dtype=torch.int32, device=f"cuda:{d}")
+
+    def execute(self, op: TransferOp) -> OpOutcome:
+        cpu, gpu = (op.src_block_ids, op.dst_block_ids) if self.h2d else (op.dst_block_ids, op.src_block_ids)
+        if gpu.size != cpu.size:
+            return OpOutcome(False, error=f"unbound GPU blocks: {gpu.size} vs {cpu.size}")
+        if self.on_gpu:
+            g_ids = self._torch.from_numpy(np.ascontiguousarray(gpu, dtype=np.int64)).pin_memory()
+            c_ids = self._torch.from_numpy(np.ascontiguousarray(cpu, dtype=np.int64)).pin_memory()
+            g_ptr, c_ptr = g_ids.data_ptr(), c_ids.data_ptr()
+        else:
+            g_ids = np.ascontiguousarray(gpu, dtype=np.int64)
+            c_ids = np.ascontiguousarray(cpu, dtype=np.int64)
+            g_ptr, c_ptr = g_ids.ctypes.data, c_ids.ctypes.data
+        status, nbytes, ms, evs = 0, 0, 0.0, []
+        for i, row in enumerate(self.regs):
+            if self.shared and not self.h2d and i > 0:
+                break
+            dev = row[0].device_id
+            st = self._streams.get(dev)
+            if self.on_gpu:
+                e0, e1 = self._torch.cuda.Event(enable_timing=True), self._torch.cuda.Event(enable_timing=True)
+                e0.record(st)
+            for g, reg in zip(self.groups, row):
+                params = dict(gpu_ptrs=[int(p) for p in reg.ptrs], idx_layer_mul=reg.idx_layer_mul,
+                              idx_kv_mul=reg.idx_kv_mul, g_layer_stride=reg.layer_stride, g_kv_stride=reg.kv_stride,
+                              g_block_stride=reg.block_stride, cpu_base=self.host.base,
+                              c_layer_stride=g.layer_stride_bytes, c_kv_stride=g.chunk_bytes,
+                              c_block_stride=self.host.block_bytes,
+                              c_off=g.offset_bytes + (0 if self.host.layout.tp_slices == 1
+                                                      else self.ranks[i] * self.slice_bytes),
+                              gpu_blocks_ptr=g_ptr, cpu_blocks_ptr=c_ptr, num_pairs=int(cpu.size), layer_start=0,
+                              num_layers=g.num_layers, kv_dim=g.kv_dim, chunk_bytes=g.chunk_bytes,
+                              gpu_num_blocks=reg.num_blocks, cpu_num_blocks=self.host.num_blocks, h2d=int(self.h2d))
+                nbytes += int(cpu.size) * g.bytes
+                if self.on_gpu:
+                    params["status_ptr"] = self._status[dev].data_ptr()
+                    with self._torch.cuda.device(dev):
+                        _native.C.kv_copy(params, self.num_ctas, GLOBAL_CONFIG_FROM_ENV.transfer_tile_bytes, 0,
+                                          st.cuda_stream)
+                else:
+                    status |= _native.C.host_kv_copy(params, 4)
+            if self.on_gpu:
+                e1.record(st)
+                evs.append((e0, e1, dev))
+        for e0, e1, dev in evs:
+            e1.synchronize()
+            ms = max(ms, e0.elapsed_time(e1))
+            words = self._status[dev].tolist()
+            status |= sum(1 << b for b, w in enumerate(words) if w)
+            if status:
+                self._status[dev].zero_()
+        return OpOutcome(status == 0, gpu_ms=ms, num_bytes=nbytes,
+                         error="" if status == 0 else f"copy status 0x{status:x}")
+
+
 class QuantGpuHostWorker(TransferWorker):
     """H2D / D2H for host pools kept in a packed form: block-scaled fp8 (lossy) or
     the lossless exponent-packing codec. The copy kernel packs on the way out and
@@ -706,6 +805,10 @@ def build_workers(storage, model_config: ModelConfig, cache_config: CacheConfig
     workers: Dict[Tuple[WorkerKey, TransferType], TransferWorker] = {}
     for key, regs in storage.gpu_regs.items():
         reg0 = regs[sorted(regs)[0]]
+        if storage.host.layout.is_multi_group:
+            workers[(key, TransferType.H2D)] = MultiGroupGpuHostWorker(storage, model_config, key, True)
+            workers[(key, TransferType.D2H)] = MultiGroupGpuHostWorker(storage, model_config, key, False)
+            continue
         if reg0.device_id < 0:
             workers[(key, TransferType.H2D)] = HostEmulatedGpuWorker(storage, model_config, key, True)
             workers[(key, TransferType.D2H)] = HostEmulatedGpuWorker(storage, model_config, key, False)
