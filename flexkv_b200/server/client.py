@@ -128,10 +128,12 @@ class KVTPClient:
         self._handles: List[TensorSharedHandle] = []
 
     def register_to_server(self, kv_caches: Sequence[torch.Tensor], kv_layout: KVCacheLayout,
-                           mode: Optional[str] = None) -> None:
-        self._handles = [TensorSharedHandle.export(t, mode) for t in kv_caches]
-        req = R.RegisterTPClientRequest(self.dp_client_id, self.intra_client_id, self.device_id, self._handles,
-                                        kv_layout, pp_rank=self.pp_rank, tp_rank=self.tp_rank)
+                           mode: Optional[str] = None, group_id: int = -1) -> None:
+        """``group_id``: layer group of a multi-group cache; call once per group."""
+        handles = [TensorSharedHandle.export(t, mode) for t in kv_caches]
+        self._handles = self._handles + handles if group_id > 0 else handles
+        req = R.RegisterTPClientRequest(self.dp_client_id, self.intra_client_id, self.device_id, handles,
+                                        kv_layout, pp_rank=self.pp_rank, tp_rank=self.tp_rank, group_id=group_id)
         self._sock.send(pickle.dumps(req, protocol=pickle.HIGHEST_PROTOCOL))
         flexkv_logger.info("sent GPU registration: dp %d rank %d, %d tensors", self.dp_client_id,
                            self.intra_client_id, len(kv_caches))

@@ -21,6 +21,7 @@ def registration_from_request(req: RegisterTPClientRequest) -> GpuRegistration:
     reg = describe_gpu_tensors(ptrs, req.gpu_layout, h0.dtype, req.device_id if h0.device_id >= 0 else -1,
                                [h.shape for h in req.handles], [h.stride for h in req.handles])
     reg.dp_client_id, reg.pp_rank, reg.tp_rank = req.dp_client_id, req.pp_rank, req.tp_rank
+    reg.group_id = getattr(req, "group_id", -1)
     reg.keepalive = list(req.handles)
     return reg
 

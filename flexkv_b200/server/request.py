@@ -32,6 +32,7 @@ class RegisterTPClientRequest:
     gpu_layout: KVCacheLayout
     pp_rank: int = 0
     tp_rank: int = 0
+    group_id: int = -1               # layer group of a multi-group cache
 
 
 @dataclass
