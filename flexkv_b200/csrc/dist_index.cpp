@@ -260,14 +260,17 @@ void LocalRadixTree::refresh_once(int64_t now) {
 
 void LocalRadixTree::thread_main() {
   std::unique_lock<std::mutex> lk(mu_);
+  int64_t backoff_ms = 0;   // grows while the channel keeps failing (registry down), so the log is not flooded
   while (!stop_) {
-    cv_.wait_for(lk, std::chrono::milliseconds(opt_.refresh_interval_ms));
+    cv_.wait_for(lk, std::chrono::milliseconds(opt_.refresh_interval_ms + backoff_ms));
     if (stop_) break;
     lk.unlock();
     try {
       refresh_once(-1);
+      backoff_ms = 0;
     } catch (const std::exception& e) {
-      FKV_WARN("local index refresh failed: %s", e.what());
+      if (backoff_ms == 0) FKV_WARN("local index refresh failed: %s", e.what());
+      backoff_ms = std::min<int64_t>(5000, std::max<int64_t>(100, backoff_ms * 2));
     }
     lk.lock();
   }
@@ -340,14 +343,19 @@ int64_t DistributedRadixTree::num_remote_blocks() {
 
 void DistributedRadixTree::thread_main() {
   std::unique_lock<std::mutex> lk(sleep_mu_);
+  int64_t backoff_ms = 0;
   while (!stop_) {
-    cv_.wait_for(lk, std::chrono::milliseconds(refresh_ms_));
+    cv_.wait_for(lk, std::chrono::milliseconds(refresh_ms_ + backoff_ms));
     if (stop_) break;
     lk.unlock();
     try {
       refresh_once();
+      backoff_ms = 0;
     } catch (const std::exception& e) {
-      FKV_WARN("distributed index refresh failed: %s", e.what());
+      if (backoff_ms == 0) FKV_WARN("distributed index refresh failed: %s", e.what());
+      backoff_ms = std::min<int64_t>(5000, std::max<int64_t>(100, backoff_ms * 2));
+      // a view that cannot be refreshed must not keep offering blocks whose leases it cannot see renewed:
+      // entries simply age out through the lease check in match_prefix
     }
     lk.lock();
   }
