@@ -10,6 +10,7 @@
 #include "kernels/kv_fanout.h"
 #include "kernels/kv_quant.h"
 #include "kernels/kv_compress.h"
+#include "kernels/kv_hash.h"
 #include "ce_copy.h"
 #include "ipc.h"
 
@@ -116,6 +117,17 @@ void init_kernel_bindings(py::module_& m) {
   });
   m.def("ipc_import", &ipc_import);
   m.def("ipc_close", &ipc_close);
+
+  // Batched block keys on the GPU; every pointer is a device (or mapped host) address.
+  m.def("kv_block_hashes", [](uint64_t tokens, uint64_t offsets, int64_t num_seqs, int tokens_per_block, uint64_t ns,
+                              int64_t ns_len, uint64_t out, uint64_t out_offsets, uint64_t stream) {
+    throw_on(launch_kv_block_hashes((const int64_t*)(uintptr_t)tokens, (const int64_t*)(uintptr_t)offsets, num_seqs,
+                                    tokens_per_block, (const int64_t*)(uintptr_t)ns, ns_len,
+                                    (uint64_t*)(uintptr_t)out, (const int64_t*)(uintptr_t)out_offsets,
+                                    (cudaStream_t)(uintptr_t)stream),
+             "kv_block_hashes launch");
+  }, py::arg("tokens"), py::arg("offsets"), py::arg("num_seqs"), py::arg("tokens_per_block"), py::arg("ns_prefix") = 0,
+     py::arg("ns_len") = 0, py::arg("out") = 0, py::arg("out_offsets") = 0, py::arg("stream") = 0);
 
   m.def("host_kv_copy", [](py::dict params, int threads) {
     KvCopyParams p = kv_params_from_dict(params);
