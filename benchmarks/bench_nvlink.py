@@ -164,7 +164,27 @@ def mode_fanout(a):
         if decode_status(status) != 0:
             errors.append(f"copy status {decode_status(status)}")
         t_ind = float(np.median(ms))
-        want = kv[L - 1][torch.from_numpy(gpu_blocks).to(dev)].clone()
+        gidx = torch.from_numpy(gpu_blocks).to(dev)
+        check_layers = sorted({0, 1, L // 2, L - 1})
+        want = {l: kv[l][gidx].clone() for l in check_layers}
+
+        def compare():
+            """(mismatching blocks per checked layer, description of the first mismatch)"""
+            bad, first = {}, ""
+            for l in check_layers:
+                got = kv[l][gidx]
+                neq = (got.view(torch.int16) != want[l].view(torch.int16)).reshape(n, -1)
+                per_block = neq.any(dim=1)
+                k = int(per_block.sum())
+                if k:
+                    bad[l] = k
+                    if not first:
+                        b = int(per_block.nonzero()[0])
+                        off = int(neq[b].nonzero()[0])
+                        zero = bool((got[b].view(torch.int16) == 0).all())
+                        first = (f"layer {l} pair {b} (gpu block {int(gpu_blocks[b])}) first differing element {off} "
+                                 f"of {neq.shape[1]}, {int(neq[b].sum())} elements differ, block all zero: {zero}")
+            return bad, first
         # one reader, NVSwitch multicast
         for ctas in a.ctas:
             ms = []
@@ -191,8 +211,11 @@ def mode_fanout(a):
                     ms.append((t, w))
             # every rank walks the same collective sequence whatever it found: a rank must not leave
             # while its memory is bound to the multicast object
-            if not torch.equal(kv[L - 1][torch.from_numpy(gpu_blocks).to(dev)], want):
-                errors.append("bytes differ")
+            bad, first = compare()
+            if bad:
+                errors.append(f"bytes differ on rank {rank}: blocks per layer {bad}; {first}")
+                if rank <= 1 or rank == world - 1:
+                    print(json.dumps({"mode": "fanout", "rank": rank, "ctas": ctas, "mismatch": errors[-1]}), flush=True)
             bad = torch.tensor([len(errors)], dtype=torch.float64, device=dev)
             dist.all_reduce(bad, op=dist.ReduceOp.SUM)
             t_fan = float(np.median([m[0] for m in ms]))
