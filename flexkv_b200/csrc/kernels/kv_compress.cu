@@ -22,6 +22,8 @@ __device__ __forceinline__ int bits_for(int range) {   // smallest w with range 
   return range == 0 ? 0 : 32 - __clz(range);
 }
 
+constexpr int kTblBatch = 32;   // size-table entries written per bulk store (128 bytes)
+
 template <bool COMPRESS>
 __global__ void __launch_bounds__(kThreads, 1)
 kv_compress_kernel(const __grid_constant__ KvCopyParams p, uint32_t* __restrict__ size_table, int layers_total,
@@ -31,6 +33,7 @@ kv_compress_kernel(const __grid_constant__ KvCopyParams p, uint32_t* __restrict_
   __shared__ __align__(8) uint64_t full[kInStages];
   __shared__ uint64_t s_dst[kInStages];
   __shared__ uint64_t s_table_idx[kInStages];
+  __shared__ __align__(128) uint32_t s_tbl[3][kTblBatch];
   __shared__ int32_t s_elems[kInStages];
   __shared__ int32_t s_w[kGroupsPerTile];
   __shared__ int32_t s_off[kGroupsPerTile + 1];
@@ -132,6 +135,22 @@ kv_compress_kernel(const __grid_constant__ KvCopyParams p, uint32_t* __restrict_
       err = keep;                      // range errors are reported once, by thread 0 at issue time
       s_sizes[it % kEpoch] = __ldg(size_table + tidx);
     }
+  };
+
+  // thread 0, compress: pending size-table entries. Three buffers in rotation: a flushed buffer is read by
+  // the bulk copy of the tile's commit group, and the per-tile wait below lets one group stay in flight.
+  uint64_t tbl_start = 0;
+  int tbl_n = 0, tbl_buf = 0;
+  auto flush_table = [&]() {
+    uint32_t* dst = size_table + tbl_start;
+    if ((reinterpret_cast<uintptr_t>(dst) & 15) == 0 && (tbl_n & 3) == 0) {
+      ptx::fence_proxy_async_smem();      // this thread's plain stores to s_tbl before the bulk read
+      ptx::bulk_s2g(dst, s_tbl[tbl_buf], (uint32_t)tbl_n * 4);
+    } else {
+      for (int i = 0; i < tbl_n; ++i) dst[i] = s_tbl[tbl_buf][i];
+    }
+    tbl_buf = tbl_buf == 2 ? 0 : tbl_buf + 1;
+    tbl_n = 0;
   };
 
   if (!COMPRESS) { fetch_sizes(0); __syncthreads(); }
@@ -262,12 +281,20 @@ kv_compress_kernel(const __grid_constant__ KvCopyParams p, uint32_t* __restrict_
     if (tid == 0) {
       if (elems > 0 && out_bytes > 0) {
         ptx::bulk_s2g(reinterpret_cast<void*>(s_dst[st]), sm.out[ob], out_bytes);
-        if (COMPRESS) size_table[s_table_idx[st]] = out_bytes;
+        if (COMPRESS) {
+          // Table entries of consecutive tiles are consecutive words: collect them and write 128 bytes
+          // at a time instead of one 4-byte PCIe write per tile.
+          const uint64_t tidx = s_table_idx[st];
+          if (tbl_n > 0 && (tidx != tbl_start + (uint64_t)tbl_n || (tidx & (kTblBatch - 1)) == 0)) flush_table();
+          if (tbl_n == 0) tbl_start = tidx;
+          s_tbl[tbl_buf][tbl_n++] = out_bytes;
+        }
       }
       ptx::bulk_commit();
     }
   }
   if (tid == 0) {
+    if (COMPRESS && tbl_n > 0) { flush_table(); ptx::bulk_commit(); }
     ptx::bulk_wait<0>();
     if (s_abort) err |= KV_ERR_WAIT_EXPIRED;
     if (err && p.status)
