@@ -64,6 +64,22 @@ class FlexKVSchedulerConnector:
         s, r = self.core.query_finished_task()
         return {"finished_sending": s, "finished_recving": r}
 
+    # the step-loop pieces, for engines that drive them separately
+    def launch_tasks(self) -> None:
+        self.core.launch_tasks()
+
+    def cancel_tasks(self) -> None:
+        self.core.flush_cancels()
+
+    def query_finished_task(self) -> Tuple[Set[str], Set[str]]:
+        return self.core.query_finished_task()
+
+    def wait_for_all_get_tasks(self):
+        return self.core.wait_for_all_get_tasks()
+
+    def wait_for_all_put_tasks(self):
+        return self.core.wait_for_all_put_tasks()
+
     def shutdown(self) -> None:
         self.core.shutdown()
 

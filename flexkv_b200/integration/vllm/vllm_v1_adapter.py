@@ -46,6 +46,22 @@ class FlexKVTask:
     slot_mapping: Optional[np.ndarray] = None
     created: float = field(default_factory=time.monotonic)
     gpu_block_ids: Optional[np.ndarray] = None
+    match_start_time: float = 0.0
+    match_end_time: float = 0.0
+    task_launch_time: float = 0.0
+    task_finished_time: float = 0.0
+
+    @property
+    def task_type(self) -> str:
+        return self.kind
+
+    @property
+    def match_cost(self) -> float:
+        return self.match_end_time - self.match_start_time
+
+    @property
+    def task_execute_cost(self) -> float:
+        return self.task_finished_time - self.task_launch_time
 
 
 def _tokens_of(request: Any) -> np.ndarray:
@@ -88,6 +104,18 @@ class FlexKVSchedulerConnector:
         self.to_cancel: List[int] = []
         self.failed_block_ids: Set[int] = set()
         self.batch_members: Dict[int, List[FlexKVTask]] = {}
+        self.collector = None            # KV-cache events, see enable_kv_events()
+
+    def enable_kv_events(self, publisher=None):
+        """Buffers (or publishes) "stored" / "removed" events of the index for cache-aware routers.
+        Needs the index in this process (not the client side of a separate server)."""
+        eng = getattr(self.mgr, "kv_task_engine", None)
+        if eng is None:
+            raise RuntimeError("KV events are collected where the index lives (in-process manager or the server)")
+        from ..dynamo.collector import KVEventCollector
+        self.collector = KVEventCollector(publisher)
+        self.collector.attach(eng.cache_engine)
+        return self.collector
 
     # ---- lifecycle --------------------------------------------------------------------
     def is_ready(self) -> bool:
@@ -234,6 +262,27 @@ class FlexKVSchedulerConnector:
                             self.failed_block_ids.update(int(b) for b in t.gpu_block_ids)
         return sending, recving
 
+    def _blocking_wait(self, book: Dict[int, FlexKVTask], timeout: float = 120.0) -> List[Any]:
+        """Waits for every launched task of ``book``; used at engine shutdown and by synchronous callers."""
+        out: List[Any] = []
+        ids = list(book)
+        if not ids:
+            return out
+        done = self.mgr.wait(ids, timeout=timeout, completely=True)
+        for tid, rsp in done.items():
+            book.pop(tid, None)
+            self.batch_members.pop(tid, None)
+            out.append(rsp)
+        return out
+
+    def wait_for_all_get_tasks(self) -> List[Any]:
+        self.launch_tasks()
+        return self._blocking_wait(self.launched_get)
+
+    def wait_for_all_put_tasks(self) -> List[Any]:
+        self.launch_tasks()
+        return self._blocking_wait(self.launched_put)
+
     def get_and_clear_failed_block_ids(self) -> Set[int]:
         out, self.failed_block_ids = self.failed_block_ids, set()
         return out
@@ -298,12 +347,16 @@ class FlexKVWorkerConnector:
         self.client.register_to_server(tensors, layout)
 
     def before_device_sleep(self) -> int:
-        """vLLM sleep mode frees the cache; the data plane must stop touching it. The host tier is kept."""
-        return 0
+        """vLLM sleep mode frees the cache; the data plane must stop touching (and mapping) it first.
+        The host tier is kept. Returns 0 when the data plane confirmed."""
+        return 0 if self.client.suspend_gpu_mappings() else 1
 
-    def after_device_wake(self) -> None:
+    def after_device_wake(self, kv_caches: Optional[Dict[str, torch.Tensor]] = None) -> None:
+        """Pass the re-created tensors when the engine allocated a new cache on wake."""
+        if kv_caches is not None:
+            self._caches = list(kv_caches.values()) if isinstance(kv_caches, dict) else list(kv_caches)
         if self._caches is not None:
-            self.client.register_to_server(self._caches, self._layout)
+            self.client.resume_gpu_mappings(self._caches, self._layout)
 
 
 class FlexKVConnectorV1Impl:
@@ -361,6 +414,22 @@ class FlexKVConnectorV1Impl:
 
     def request_finished(self, request: Any, block_ids: Sequence[int]) -> Tuple[bool, Optional[dict]]:
         return self.scheduler.request_finished(request, block_ids)
+
+    def take_events(self) -> List[Any]:
+        """Buffered KV-cache events (stored / removed) for routers that track cache contents."""
+        col = getattr(self.scheduler, "collector", None) if self.scheduler else None
+        return col.take_events() if col is not None else []
+
+    def get_kv_connector_stats(self) -> Optional[dict]:
+        """Counters of the last interval. The worker side returns an empty (non-None) record so that the
+        engine keeps polling for finished transfers on steps that schedule no tokens."""
+        if not self.is_scheduler:
+            return {}
+        st = self.scheduler.stats
+        return dict(num_get_requests=st.num_get_requests, num_get_query_tokens=st.num_get_query_tokens,
+                    num_gpu_matched_tokens=st.num_gpu_matched_tokens,
+                    num_flexkv_matched_tokens=st.num_flexkv_matched_tokens, num_put_requests=st.num_put_requests,
+                    num_put_unmatched_tokens=st.num_put_unmatched_tokens, num_failed_requests=st.num_failed_requests)
 
     def get_block_ids_with_load_errors(self) -> Set[int]:
         return self.scheduler.get_and_clear_failed_block_ids() if self.scheduler else set()

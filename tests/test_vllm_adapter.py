@@ -128,3 +128,24 @@ def test_layout_inference_and_config_mapping():
     cfg2 = FlexKVConfig(kv_cache_dtype="nvfp4")
     cfg2.post_init_from_vllm_config(vcfg)
     assert cfg2.model_config.dtype == torch.uint8 and cfg2.model_config.head_size == 64 + 8   # nibbles + scales
+
+
+def test_blocking_waits_events_and_stats():
+    conn, kv, mgr = make()
+    try:
+        conn.enable_kv_events()
+        tok = np.arange(900, 900 + 4 * T + 1)
+        keep, _ = conn.request_finished(req("p", tok), [1, 2, 3, 4, 5])
+        assert keep
+        rsp = conn.wait_for_all_put_tasks()
+        assert len(rsp) == 1 and rsp[0].status.value == "success" and not conn.launched_put
+        n, _ = conn.get_num_new_matched_tokens(req("g", tok), 0)
+        assert n == 4 * T
+        conn.update_state_after_alloc(req("g", tok), [20, 21, 22, 23, 24], n)
+        rsp = conn.wait_for_all_get_tasks()
+        assert len(rsp) == 1 and rsp[0].status.value == "success"
+        ev = conn.collector.take_events()
+        assert sum(len(e.block_hashes) for e in ev if e.kind == "stored") == 4
+        assert conn.stats.num_put_requests == 1 and conn.stats.num_get_requests == 1
+    finally:
+        conn.shutdown()
