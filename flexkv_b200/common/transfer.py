@@ -208,6 +208,7 @@ class TransferOpGraph:
                 op.dst_block_ids = ids
             if isinstance(op, LayerwiseTransferOp):
                 op.dst_block_ids_h2d = ids
+            op._late_side = op.gpu_side
         self._gpu_bound = True
 
     @property
@@ -236,6 +237,37 @@ class TransferOpGraph:
             op.gpu_side = None
 
     # ---- execution ------------------------------------------------------------
+    set_swa_gpu_blocks = set_swa_pages      # the reference's name for the same binding step
+
+    def clear_gpu_blocks(self) -> None:
+        """Forgets the bound GPU side of every late-bound op so that another pipeline stage (whose
+        engine uses its own block ids) can bind the same plan again (flexkv/kvtask.py:438-444)."""
+        for op in self._ops.values():
+            side = getattr(op, "_late_side", None)
+            if side is None or op.is_swa:
+                continue
+            if side == "src":
+                op.src_block_ids = _EMPTY
+            else:
+                op.dst_block_ids = _EMPTY
+            op.gpu_side = side
+            self._gpu_bound = False
+
+    def is_graph_failed(self) -> bool:
+        return bool(self.failed)
+
+    def visualize(self) -> str:
+        """Text dump of the DAG: one line per op with type, block counts, state and predecessors."""
+        lines = [f"graph {self.graph_id}: {len(self._ops)} ops, {self._unfinished} unfinished"
+                 f"{', FAILED' if self.failed else ''}"]
+        for oid in sorted(self._ops):
+            op = self._ops[oid]
+            dep = ",".join(str(p) for p in sorted(op.predecessors)) or "-"
+            lines.append(f"  op {oid:>5} {op.transfer_type.value:<10} src={op.src_block_ids.size:<6} "
+                         f"dst={op.dst_block_ids.size:<6} {op.status.name:<9} after [{dep}]"
+                         f"{' swa' if op.is_swa else ''}{' late:' + op.gpu_side if op.gpu_side else ''}")
+        return "\n".join(lines)
+
     def take_ready_ops(self) -> List[TransferOp]:
         """Ops whose predecessors are all done and that were not handed out yet."""
         out = []

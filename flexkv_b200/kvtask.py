@@ -183,6 +183,23 @@ class KVTaskEngine:
             planned = self.cache_engine.put(-1, token_ids, token_mask, slot_mapping, dp_id, namespace)
         return self._new_task(TaskType.PUT, token_ids, token_mask, slot_mapping, dp_id, planned)
 
+    # names of the reference's task manager for the same steps (flexkv/kvtask.py:305-425)
+    def create_get_task(self, token_ids, token_mask=None, slot_mapping=None, dp_id: int = 0, namespace=None,
+                        cpu_only: bool = False, swa_aware: bool = False) -> KVTask:
+        return self._create_get(token_ids, token_mask, slot_mapping, dp_id, namespace, cpu_only, swa_aware)
+
+    def create_put_task(self, token_ids, token_mask=None, slot_mapping=None, dp_id: int = 0, namespace=None) -> KVTask:
+        return self._create_put(token_ids, token_mask, slot_mapping, dp_id, namespace)
+
+    def check_completed(self, task_id: int) -> bool:
+        self._update_tasks(timeout=0)
+        t = self.tasks.get(task_id)
+        return t is None or t.status in (TaskStatus.COMPLETED, TaskStatus.CANCELLED, TaskStatus.FAILED)
+
+    def check_task_ready(self, task_id: int) -> bool:
+        t = self.tasks.get(task_id)
+        return t is not None and t.status != TaskStatus.UNREADY
+
     # ---- API ------------------------------------------------------------------
     def get_async(self, token_ids: np.ndarray, slot_mapping: np.ndarray, token_mask: Optional[np.ndarray] = None,
                   dp_id: int = 0, namespace: Optional[List[str]] = None) -> Tuple[int, np.ndarray]:
