@@ -57,6 +57,24 @@ class FlexKVComm:
         dist.broadcast_object_list(box, src=self.leader, group=self.group)
         return box[0]
 
+    def scatter_pp(self, data: Any = None) -> Any:
+        """Pipeline-only fan-out: the leader of stage 0 hands ``data`` to the leader of every other
+        stage; ranks that lead no stage return None (flexkv/integration/sglang/comm.py:342-352).
+        Ranks are laid out stage-major: stage s owns ranks [s * world / pp, (s + 1) * world / pp)."""
+        if not self.enabled or self.pp_size <= 1 or self.world == 1:
+            return data
+        per_stage = self.world // self.pp_size
+        leaders = [s * per_stage for s in range(self.pp_size)]
+        if self.rank not in leaders:
+            return None
+        if self.rank == leaders[0]:
+            for r in leaders[1:]:
+                dist.send_object_list([data], dst=r, group=self.group)
+            return data
+        box: List[Any] = [None]
+        dist.recv_object_list(box, src=leaders[0], group=self.group)
+        return box[0]
+
     def all_reduce_min(self, value: int) -> int:
         if not self.enabled or self.world == 1:
             return int(value)

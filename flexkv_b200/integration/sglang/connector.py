@@ -245,6 +245,10 @@ class FlexKVConnector:
             self.layer_counter.reset()
         self.comm.barrier()
 
+    def destroy(self) -> None:
+        """Name used by engines that tear the connector down with the cache controller."""
+        self.shutdown()
+
     def shutdown(self) -> None:
         if getattr(self, "_closed", False):
             return

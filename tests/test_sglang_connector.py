@@ -126,3 +126,28 @@ def test_store_protocol_across_two_gloo_ranks(tmp_path):
     p = subprocess.run(cmd, capture_output=True, text=True, timeout=180, env=dict(os.environ, PYTHONPATH=ROOT))
     assert p.returncode == 0, p.stdout[-1500:] + p.stderr[-1500:]
     assert "rank0-ok" in p.stdout and "rank1-ok" in p.stdout
+
+
+PP_WORKER = r'''
+import sys
+sys.path.insert(0, "ROOT")
+import torch.distributed as dist
+from flexkv_b200.integration.sglang.comm import FlexKVComm
+dist.init_process_group("gloo")
+c = FlexKVComm(tp_size=2, pp_size=2)
+got = c.scatter_pp({"plan": 42} if c.rank == 0 else None)
+assert got == ({"plan": 42} if c.rank in (0, 2) else None), (c.rank, got)
+assert c.all_reduce_min(10 + c.rank) == 10
+sys.stdout.write("PP_OK %d\n" % c.rank)
+dist.destroy_process_group()
+'''
+
+
+def test_pipeline_stage_leaders_receive_the_plan(tmp_path):
+    script = tmp_path / "pp_worker.py"
+    script.write_text(PP_WORKER.replace("ROOT", ROOT))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "4", "--master-addr",
+           "127.0.0.1", "--master-port", "29567", str(script)]
+    p = subprocess.run(cmd, capture_output=True, text=True, timeout=180, env=dict(os.environ, PYTHONPATH=ROOT))
+    assert p.returncode == 0, p.stdout[-2000:] + p.stderr[-2000:]
+    assert p.stdout.count("PP_OK") == 4
