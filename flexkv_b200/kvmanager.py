@@ -52,6 +52,11 @@ class KVManager:
         self.kv_task_engine = None
         self.transfer_manager = None
         self._metrics = None
+        self._shut = False
+        import atexit
+        import weakref
+        ref = weakref.ref(self)
+        atexit.register(lambda: ref() is not None and ref().shutdown())
         if self.server_client_mode:
             from .server.client import KVDPClient
             from .server.server import KVServer
@@ -160,6 +165,11 @@ class KVManager:
             time.sleep(0.01)
 
     def shutdown(self) -> None:
+        """Stops the data plane, unpins host memory and leaves the registry; safe to call twice.
+        Also runs at interpreter exit for managers that were never shut down."""
+        if self._shut:
+            return
+        self._shut = True
         if self.server_client_mode:
             self.dp_client.shutdown()
             if self.server_handle is not None:
