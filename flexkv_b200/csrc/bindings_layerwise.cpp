@@ -126,6 +126,16 @@ void init_layerwise_bindings(py::module_& m) {
      py::arg("status_ptr") = (uint64_t)0, py::arg("t_start_ptr") = (uint64_t)0, py::arg("num_ctas") = 1,
      py::arg("stream") = (uint64_t)0);
 
+  m.def("layer_probe", [](uint64_t flag_ptr, uint32_t epoch, uint64_t data_ptr, int64_t num_bytes, uint64_t budget_ns,
+                          uint64_t status_ptr, uint64_t out_sum_ptr, int num_ctas, uint64_t stream) {
+    cudaError_t e = launch_layer_probe((const uint32_t*)(uintptr_t)flag_ptr, epoch, (const void*)(uintptr_t)data_ptr,
+                                       num_bytes, budget_ns, (int32_t*)(uintptr_t)status_ptr,
+                                       (uint64_t*)(uintptr_t)out_sum_ptr, num_ctas, (cudaStream_t)(uintptr_t)stream);
+    if (e != cudaSuccess) throw std::runtime_error(cudaGetErrorString(e));
+  }, py::arg("flag_ptr"), py::arg("epoch"), py::arg("data_ptr"), py::arg("num_bytes"),
+     py::arg("budget_ns") = (uint64_t)2000000000ull, py::arg("status_ptr") = (uint64_t)0, py::arg("out_sum_ptr") = (uint64_t)0,
+     py::arg("num_ctas") = 4, py::arg("stream") = (uint64_t)0);
+
   m.def("set_flags", [](uint64_t flags_ptr, int n, uint32_t value, uint64_t stream) {
     cudaError_t e = launch_set_flags((uint32_t*)(uintptr_t)flags_ptr, n, value, (cudaStream_t)(uintptr_t)stream);
     if (e != cudaSuccess) throw std::runtime_error(cudaGetErrorString(e));

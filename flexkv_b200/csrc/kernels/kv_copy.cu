@@ -105,7 +105,9 @@ __device__ __forceinline__ bool ids_in_range(const KvCopyParams& p, int64_t g, i
 // a layer resets that layer's counter and publishes the flags.
 __device__ __forceinline__ void signal_layers(const KvCopyParams& p, int from, int to) {
   if (p.done_counter == nullptr || from >= to) return;
-  ptx::fence_proxy_async_all();
+  // The caller has waited for its bulk stores of these layers (wait_group 0: the writes are performed).
+  // No async-proxy fence here: it would also wait for the loads in flight and drain the pipeline at every
+  // layer boundary; the release below orders the completed stores before the counter and flag updates.
   __threadfence();
   for (int l = from; l < to; ++l) {
     const unsigned prev = atomicAdd(p.done_counter + l, 1u);

@@ -124,3 +124,32 @@ def test_consumer_wait_runs_out_and_reports_status():
     C.layer_stub(flag.data_ptr(), 5, 1000, 50_000_000, status.data_ptr(), 0, 1, torch.cuda.current_stream().cuda_stream)
     torch.cuda.synchronize()
     assert status.item() == 0 and flag.item() == 7
+
+
+@pytest.mark.parametrize("lpb", [0, 1])
+def test_a_layer_flag_is_never_seen_before_the_layer_bytes(lpb):
+    """Consumer kernels are launched BEFORE the restore, spin (bounded) on their layer's device flag and sum
+    the layer's bytes the moment they see it: a flag published ahead of its data would give a stale sum."""
+    shape = KVShape("lw", 6, 2, 128, tokens_per_block=16)
+    NB = 128
+    kv, reg, pool, grp, xfer = _setup(shape, NB=NB, notify="flag", layers_per_batch=lpb)
+    ids = np.arange(NB, dtype=np.int64)
+    assert xfer.transfer(ids, ids, False, 0, shape.num_layers).status == 0
+    want = [int(t.view(torch.int64).sum().item()) & ((1 << 64) - 1) for t in kv]
+    for rep in range(3):
+        for t in kv:
+            t.zero_()
+        torch.cuda.synchronize()
+        ep = grp.epoch_of(0) + 1                                   # the epoch the next restore on counter 0 publishes
+        sums = torch.zeros(shape.num_layers, dtype=torch.int64, device="cuda")
+        status = torch.zeros(1, dtype=torch.int32, device="cuda")
+        streams = [torch.cuda.Stream() for _ in range(shape.num_layers)]
+        for l, s in enumerate(streams):                            # 6 layers x 2 CTAs: all resident at once
+            C.layer_probe(grp.device_flags_ptr(0, 0) + 4 * l, ep, kv[l].data_ptr(), kv[l].numel() * 2, 2_000_000_000,
+                          status.data_ptr(), sums.data_ptr() + 8 * l, 2, s.cuda_stream)
+        r = grp.restore(ids, ids, 0)
+        assert r.status == 0
+        torch.cuda.synchronize()
+        assert status.item() == 0
+        got = [int(v) & ((1 << 64) - 1) for v in sums.tolist()]
+        assert got == want, (rep, lpb)
