@@ -22,6 +22,7 @@ namespace fkv {
 namespace {
 
 constexpr uint64_t kWaitBudgetNs = 2000000000ull;  // 2 s per bulk-copy wait
+constexpr uint64_t kSignalBudgetNs = 60000000000ull;  // signaller warp: longer than any restore, still finite
 
 // Error reporting without atomics: `status` is an array of kStatusWords words,
 // one per KvCopyStatus bit, and a CTA that saw error bit b stores 1 to word b.
@@ -120,8 +121,12 @@ __device__ __forceinline__ void signal_layers(const KvCopyParams& p, int from, i
   }
 }
 
+// Layer-major launches run a second warp per CTA whose only job is the per-layer publication: fences, the
+// counter atomic and the system-scope flag store issued by the copy thread itself would wait for that
+// thread's loads in flight and drain the pipeline at every layer boundary. The copy thread only waits for
+// its bulk stores and posts "layers [0, n) done" to a shared-memory mailbox.
 template <int STAGES, int LOOKAHEAD>
-__global__ void __launch_bounds__(32, 1)
+__global__ void __launch_bounds__(64, 1)
 kv_copy_bulk_kernel(const __grid_constant__ KvCopyParams p, int tile_bytes, int tiles_per_chunk) {
   static_assert(LOOKAHEAD >= 1 && LOOKAHEAD < STAGES, "lookahead must leave one stage for stores");
   static_assert(STAGES <= 32, "stage phases are kept in one 32-bit mask");
@@ -131,13 +136,37 @@ kv_copy_bulk_kernel(const __grid_constant__ KvCopyParams p, int tile_bytes, int 
   __shared__ uint32_t s_bytes[STAGES];
   __shared__ int32_t s_layer[STAGES];   // layer-major launches: layer (relative) of the tile in the stage
 
-  const int lane = threadIdx.x;
-  if (lane == 0) {
+  __shared__ int s_layers_done;         // mailbox: this CTA finished (stores included) layers [0, n)
+  const int lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
 #pragma unroll
     for (int s = 0; s < STAGES; ++s) ptx::mbar_init(&full[s], 1);
     ptx::fence_mbar_init();
+    s_layers_done = 0;
   }
-  __syncwarp();
+  __syncthreads();
+  if (threadIdx.x >= 32) {
+    // ---- signaller warp (present only on layer-major launches with signalling)
+    if (lane != 0 || !p.layer_major || p.done_counter == nullptr) return;
+    int sig = 0;
+    const uint64_t t0 = ptx::globaltimer_ns();
+    while (sig < p.num_layers) {
+      const int d = *reinterpret_cast<volatile int*>(&s_layers_done);
+      if (d > sig) {
+        __threadfence_block();            // acquire side of the mailbox
+        signal_layers(p, sig, d);
+        sig = d;
+      } else {
+        if (ptx::globaltimer_ns() - t0 > kSignalBudgetNs) {   // the copy warp always posts the last layer; belt and braces
+          if (p.status) report_status(p.status, KV_ERR_WAIT_EXPIRED);
+          return;
+        }
+        __nanosleep(64);
+      }
+    }
+    return;
+  }
+  const bool has_signaller = blockDim.x > 32;
 
   // span = tiles per major unit (a pair, or a layer when layer-major); all counts fit 32 bits
   const int32_t n_major = p.layer_major ? p.num_layers : p.num_pairs;
@@ -176,7 +205,12 @@ kv_copy_bulk_kernel(const __grid_constant__ KvCopyParams p, int tile_bytes, int 
         // first store of a later layer: everything this CTA owned in the earlier layers is committed;
         // drain those stores (the loads in flight are unaffected) and report the layers
         ptx::bulk_wait<0>();
-        signal_layers(p, signalled, s_layer[st]);
+        if (has_signaller) {
+          __threadfence_block();
+          *reinterpret_cast<volatile int*>(&s_layers_done) = s_layer[st];
+        } else {
+          signal_layers(p, signalled, s_layer[st]);
+        }
         signalled = s_layer[st];
       }
       if (bytes) {
@@ -227,8 +261,16 @@ kv_copy_bulk_kernel(const __grid_constant__ KvCopyParams p, int tile_bytes, int 
   if (lane == 0) {
     ptx::bulk_wait<0>();
     if (err && p.status) report_status(p.status, err);
-    if (p.layer_major) signal_layers(p, signalled, p.num_layers);
-    else signal_done(p);
+    if (p.layer_major) {
+      if (has_signaller) {
+        __threadfence_block();
+        *reinterpret_cast<volatile int*>(&s_layers_done) = p.num_layers;   // every exit path ends here
+      } else {
+        signal_layers(p, signalled, p.num_layers);
+      }
+    } else {
+      signal_done(p);
+    }
   }
 }
 
@@ -327,7 +369,8 @@ cudaError_t launch_bulk(const KvCopyParams& p, int ctas, int tile_bytes, int til
   auto k = kv_copy_bulk_kernel<STAGES, LA>;
   cudaError_t e = ensure_smem(k, smem);
   if (e != cudaSuccess) return e;
-  k<<<ctas, 32, smem, s>>>(p, tile_bytes, tiles_per_chunk);
+  const int threads = (p.layer_major && p.done_counter != nullptr) ? 64 : 32;   // second warp = layer signaller
+  k<<<ctas, threads, smem, s>>>(p, tile_bytes, tiles_per_chunk);
   return cudaGetLastError();
 }
 
