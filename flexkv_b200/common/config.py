@@ -149,6 +149,16 @@ class ModelConfig:
     def num_layers_per_pp_stage(self) -> int:
         return self.num_layers // self.pp_size
 
+    @property
+    def local_pp_stages(self) -> int:
+        """Pipeline stages whose GPUs one manager serves: all of them on a single node (their layers share
+        one host block, stage s at layer offset s * layers_per_stage); one per node otherwise."""
+        return self.pp_size if self.nnodes == 1 else 1
+
+    @property
+    def num_layers_local(self) -> int:
+        return self.num_layers_per_pp_stage * self.local_pp_stages
+
     # ---- sizes ----------------------------------------------------------------
     @property
     def bytes_per_token_per_layer(self) -> int:

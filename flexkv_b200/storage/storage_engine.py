@@ -116,7 +116,7 @@ class StorageEngine:
     def _host_geometry(self) -> Tuple[int, int, int, int, KVCacheLayout]:
         m, c = self.model_config, self.cache_config
         T = c.tokens_per_block
-        layers = m.num_layers_per_pp_stage
+        layers = m.num_layers_local
         if m.layer_groups:
             groups = []
             for g in m.layer_groups:
@@ -159,7 +159,7 @@ class StorageEngine:
                          compression_enabled=bool(c.enable_compression or self.env.enable_compression),
                          dtype=m.dtype, host_layout_type=lay.type, chunk_elems_per_rank=lay.get_chunk_size() // slices,
                          itemsize=m.dtype.itemsize, layerwise=bool(self.env.enable_layerwise_transfer),
-                         peer_host_sharing=bool(c.enable_p2p_cpu))
+                         peer_host_sharing=bool(c.enable_p2p_cpu), pipeline_stages=m.local_pp_stages)
         if d.reason:
             flexkv_logger.warning("host codec refused: %s; every tier runs uncompressed", d.reason)
         if d.warning:
@@ -195,7 +195,7 @@ class StorageEngine:
             slices = 1 if (m.use_mla or m.num_kv_heads == 1) else m.effective_tp_size
             tpc = (lay.get_chunk_size() // slices + COMPRESS_TILE_ELEMS - 1) // COMPRESS_TILE_ELEMS
             self.host.tiles_per_chunk = tpc
-            n = c.num_cpu_blocks * m.num_layers_per_pp_stage * lay.kv_dim * tpc * slices
+            n = c.num_cpu_blocks * m.num_layers_local * lay.kv_dim * tpc * slices
             table = torch.zeros(n, dtype=torch.int32)
             self.host.size_table = table.pin_memory() if self._cuda_register else table
         flexkv_logger.info("host pool: %d blocks x %d B = %.2f GiB (hugepage=%s, registered=%s, layout=%s)",
@@ -206,9 +206,17 @@ class StorageEngine:
         c = self.cache_config
         if lay.is_multi_group or lay.type == KVCacheLayoutType.BLOCKFIRST:
             return c.num_cpu_blocks * block_bytes
-        return self.model_config.num_layers_per_pp_stage * lay.kv_dim * c.num_cpu_blocks * \
+        return self.model_config.num_layers_local * lay.kv_dim * c.num_cpu_blocks * \
             packed_chunk_bytes(lay.get_chunk_size(), getattr(self, "_codec", c.offload_quant),
                                self.model_config.dtype.itemsize)
+
+    def pp_stage_offset(self, pp_rank: int) -> int:
+        """Byte offset of pipeline stage ``pp_rank``'s first layer inside the host pool's layer axis
+        (stages served by this manager share one host block: stage s owns layers [s*Lp, (s+1)*Lp))."""
+        m = self.model_config
+        if m.local_pp_stages <= 1 or pp_rank <= 0:
+            return 0
+        return pp_rank * m.num_layers_per_pp_stage * self.host.layer_stride
 
     def host_block_stride(self) -> int:
         return self.host.block_bytes
@@ -227,7 +235,7 @@ class StorageEngine:
             raise ValueError("the SSD tier needs the host tier as staging")
         block_bytes = self.host.block_bytes if self.host.layout.type == KVCacheLayoutType.BLOCKFIRST or \
             self.host.layout.is_multi_group else \
-            self.model_config.num_layers_per_pp_stage * self.host.layout.kv_dim * self.host.chunk_bytes
+            self.model_config.num_layers_local * self.host.layout.kv_dim * self.host.chunk_bytes
         per_dev = c.num_ssd_blocks // ndev
         max_gb = self.env.max_file_size_gb
         blocks_per_file = per_dev
@@ -256,7 +264,7 @@ class StorageEngine:
     def ssd_layout_dict(self) -> Dict[str, Any]:
         h = self.host
         bf = h.layout.type == KVCacheLayoutType.BLOCKFIRST or h.layout.is_multi_group
-        L = self.model_config.num_layers_per_pp_stage
+        L = self.model_config.num_layers_local
         if bf:
             ssd_layer, ssd_kv = h.layer_stride, h.kv_stride
         else:
@@ -308,7 +316,7 @@ class StorageEngine:
 
     def all_registered(self) -> bool:
         m = self.model_config
-        want_keys = m.total_clients * m.pp_size
+        want_keys = m.total_clients * m.local_pp_stages
         if len(self.gpu_regs) < want_keys:
             return False
         return all(len(r) >= m.effective_tp_size_per_node for r in self.gpu_regs.values())

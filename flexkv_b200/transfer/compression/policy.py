@@ -26,12 +26,15 @@ class CodecDecision:
 
 
 def choose_codec(*, requested_quant: str, compression_enabled: bool, dtype, host_layout_type, chunk_elems_per_rank: int,
-                 itemsize: int, layerwise: bool, peer_host_sharing: bool = False) -> CodecDecision:
+                 itemsize: int, layerwise: bool, peer_host_sharing: bool = False,
+                 pipeline_stages: int = 1) -> CodecDecision:
     """``requested_quant`` is the explicit lossy choice (CacheConfig.offload_quant); the
     lossless codec is picked when compression is enabled and the cache qualifies."""
     if requested_quant not in ("none", "fp8_e4m3", "bf16_xp"):
         raise ValueError(f"unknown host codec {requested_quant!r}")
     chunk_bytes = chunk_elems_per_rank * itemsize
+    if pipeline_stages > 1 and (requested_quant != "none" or compression_enabled):
+        return CodecDecision("none", "several pipeline stages share one host block (codecs address whole blocks)")
     if requested_quant == "fp8_e4m3":
         if dtype not in (torch.bfloat16, torch.float16):
             return CodecDecision("none", f"fp8 offload needs a 16-bit cache, got {dtype}")

@@ -54,6 +54,7 @@ class TransferEngine:
         self._parked: List[Tuple[TransferOpGraph, TransferOp]] = []
         self._gpu_inflight: Dict[WorkerKey, int] = {}
         self._drain_waiters: List[Tuple[set, threading.Event]] = []
+        self._pp_acc: Dict[int, list] = {}      # op id -> [all ok, bytes, max ms, first error, -] over pipeline stages
         self.stats = dict(ops=0, failed_ops=0, graphs=0, failed_graphs=0)
         self.stats_by_type: Dict[str, List[float]] = {}     # type -> [ops, blocks, bytes, kernel or IO ms]
 
@@ -169,7 +170,21 @@ class TransferEngine:
                 if op.transfer_type in _GPU_TYPES:
                     self._gpu_inflight[key] = self._gpu_inflight.get(key, 0) + 1
                 self._trace.on_submit(op)
-                w.submit(op)
+                # pipeline stages served by this manager each hold their own layers of the same blocks: the op
+                # goes to every stage's worker and counts as done when the last of them reports
+                # (flexkv/transfer/transfer_engine.py:1434-1492,1562-1613)
+                siblings = [w]
+                if op.transfer_type in (TransferType.H2D, TransferType.D2H) and not op.is_swa \
+                        and self.model_config.local_pp_stages > 1:
+                    for r in range(1, self.model_config.local_pp_stages):
+                        sw = self._workers.get((WorkerKey(op.dp_client_id, r), op.transfer_type))
+                        if sw is not None:
+                            siblings.append(sw)
+                op.pending_count = len(siblings)
+                if len(siblings) > 1:
+                    self._pp_acc[op.op_id] = [True, 0, 0.0, "", None]
+                for sw in siblings:
+                    sw.submit(op)
         if graph.all_transfer_ops_completed() or (graph.failed and self._inflight[graph.graph_id] == 0):
             self._finish_graph(graph)
 
@@ -237,6 +252,18 @@ class TransferEngine:
             done.set()
 
     def _on_done(self, op: TransferOp, outcome: OpOutcome) -> None:
+        acc = self._pp_acc.get(op.op_id)
+        if acc is not None:
+            # one report per pipeline stage: fold, and go on only with the last one
+            acc[0] = acc[0] and outcome.success
+            acc[1] += outcome.num_bytes
+            acc[2] = max(acc[2], outcome.gpu_ms)
+            acc[3] = acc[3] or outcome.error
+            op.pending_count -= 1
+            if op.pending_count > 0:
+                return
+            del self._pp_acc[op.op_id]
+            outcome = OpOutcome(acc[0], gpu_ms=acc[2], num_bytes=acc[1], error=acc[3])
         if op.transfer_type in _GPU_TYPES:
             key = WorkerKey(op.dp_client_id, 0)
             self._gpu_inflight[key] = max(0, self._gpu_inflight.get(key, 0) - 1)

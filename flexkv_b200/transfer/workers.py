@@ -132,8 +132,8 @@ def build_transfer_group(storage, model_config: ModelConfig, key: WorkerKey, hig
     for r in ranks:
         d = regs[r].as_native()
         gpus.append(d)
-    host_d = dict(base=host.base, layer_stride=layer_stride, kv_stride=kv_stride, block_stride=host.block_bytes,
-                  num_blocks=host.num_blocks)
+    host_d = dict(base=host.base + storage.pp_stage_offset(key.pp_rank), layer_stride=layer_stride,
+                  kv_stride=kv_stride, block_stride=host.block_bytes, num_blocks=host.num_blocks)
     opts = dict(num_layers=reg0.num_layers, kv_dim=reg0.kv_dim, chunk_bytes=reg0.chunk_bytes,
                 cpu_tp_stride=tp_stride, shared_kv=shared, shared_mode=env.kv_shared_across_ranks_mode,
                 h2d=_launch_cfg(env, True), d2h=_launch_cfg(env, False), high_priority_stream=high_priority,
@@ -200,6 +200,7 @@ class HostEmulatedGpuWorker(TransferWorker):
             self.layer_stride, self.kv_stride = host.layer_stride, host.kv_stride
             self.tp_stride = host.chunk_bytes // n_slices
         self.shared = shared
+        self.pp_off = storage.pp_stage_offset(key.pp_rank)
 
     def execute(self, op: TransferOp) -> OpOutcome:
         if self.h2d:
@@ -219,7 +220,7 @@ class HostEmulatedGpuWorker(TransferWorker):
                           idx_kv_mul=reg.idx_kv_mul, g_layer_stride=reg.layer_stride, g_kv_stride=reg.kv_stride,
                           g_block_stride=reg.block_stride, cpu_base=self.host.base, c_layer_stride=self.layer_stride,
                           c_kv_stride=self.kv_stride, c_block_stride=self.host.block_bytes,
-                          c_off=0 if self.shared else i * self.tp_stride, gpu_blocks_ptr=gpu.ctypes.data,
+                          c_off=self.pp_off + (0 if self.shared else i * self.tp_stride), gpu_blocks_ptr=gpu.ctypes.data,
                           cpu_blocks_ptr=cpu.ctypes.data, num_pairs=int(cpu.size), layer_start=op.layer_start,
                           num_layers=nl, kv_dim=reg.kv_dim, chunk_bytes=reg.chunk_bytes,
                           gpu_num_blocks=reg.num_blocks, cpu_num_blocks=self.host.num_blocks, h2d=int(self.h2d))

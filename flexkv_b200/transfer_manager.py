@@ -60,7 +60,7 @@ class TransferManager:
     def _expected_registrations(self) -> int:
         m = self.model_config
         groups = len(m.layer_groups) if m.layer_groups else 1      # one registration per rank and layer group
-        return m.total_clients * m.pp_size * m.effective_tp_size_per_node * groups if self.require_gpu else 0
+        return m.total_clients * m.local_pp_stages * m.effective_tp_size_per_node * groups if self.require_gpu else 0
 
     # ---- lifecycle ----------------------------------------------------------------
     def start(self) -> None:
