@@ -19,7 +19,7 @@ _U32_MAX = 0xFFFFFFFF
 
 class PyNode:
     __slots__ = ("hashes", "blocks", "children", "parent", "ready", "lock_cnt", "hit_count", "grace_us",
-                 "last_access_us", "creation_us", "live", "serial")
+                 "last_access_us", "creation_us", "live", "serial", "swa_slot", "swa_lock")
 
     def __init__(self, serial: int, now: int) -> None:
         self.hashes: List[int] = []
@@ -32,6 +32,8 @@ class PyNode:
         self.grace_us = self.last_access_us = self.creation_us = now
         self.live = True
         self.serial = serial
+        self.swa_slot = -1          # window snapshot valid at this node's last block (-1: none)
+        self.swa_lock = 0
 
     def size(self) -> int:
         return len(self.hashes)
@@ -48,6 +50,9 @@ class PyMatchResult:
     last_ready_node: Optional[PyNode] = None
     last_node: Optional[PyNode] = None
     physical_blocks: np.ndarray = field(default_factory=lambda: np.zeros(0, dtype=np.int64))
+    last_swa_node: Optional[PyNode] = None
+    swa_hit_blocks: int = 0
+    swa_slot: int = -1
 
 
 class RadixTreeIndex:
@@ -69,6 +74,8 @@ class RadixTreeIndex:
         self._root = self._new_node()
         self._root.ready = True
         self._stats = dict(hit=0, match=0, miss=0, insert_blocks=0, evict_blocks=0)
+        self._swa_lru: List[PyNode] = []       # least recently used first
+        self._freed_swa: List[int] = []
 
     # ---- helpers ----------------------------------------------------------------
     def _now(self) -> int:
@@ -80,6 +87,7 @@ class RadixTreeIndex:
         return PyNode(self._serial, self._now())
 
     def _free(self, n: PyNode) -> None:
+        self._drop_swa(n)
         n.live = False
         n.children = {}
         self._nodes -= 1
@@ -127,6 +135,10 @@ class RadixTreeIndex:
             r.last_node, r.last_node_matched_length = c, m
             if ready_chain and c.ready:
                 r.num_ready_matched_blocks, r.last_ready_node = prefix, c
+                if c.swa_slot >= 0 and m == c.size():      # only a fully matched node exposes its snapshot
+                    r.last_swa_node, r.swa_hit_blocks, r.swa_slot = c, prefix, c.swa_slot
+                    if update_cache_info:
+                        self._swa_touch(c)
             else:
                 ready_chain = False
             if m < c.size():
@@ -249,6 +261,7 @@ class RadixTreeIndex:
                 _, _, node = heapq.heappop(heap)
                 sz = node.size()
                 if sz > need:
+                    self._drop_swa(node)        # the snapshot described the dropped tail
                     blocks.extend(node.blocks[sz - need:])
                     hashes.extend(node.hashes[sz - need:])
                     node.blocks, node.hashes = node.blocks[:sz - need], node.hashes[:sz - need]
@@ -305,7 +318,82 @@ class RadixTreeIndex:
             self._free(x)
         self._root.children = {}
         self._total_blocks = 0
+        self._swa_lru, self._freed_swa = [], []
         return np.asarray(all_blocks, dtype=np.int64)
+
+    # ---- window snapshots mounted on nodes (same rules as the native index) ---------------
+    def _drop_swa(self, n: PyNode) -> None:
+        if n.swa_slot >= 0:
+            self._freed_swa.append(n.swa_slot)
+            self._swa_lru = [x for x in self._swa_lru if x is not n]
+        n.swa_slot, n.swa_lock = -1, 0
+
+    def _swa_touch(self, n: PyNode) -> None:
+        self._swa_lru = [x for x in self._swa_lru if x is not n]
+        self._swa_lru.append(n)
+
+    def set_swa(self, h: PyNode, slot: int) -> None:
+        n = self._check(h)
+        if n is self._root:
+            raise ValueError("radix index: the root carries no window snapshot")
+        if slot < 0:
+            raise ValueError("radix index: negative snapshot slot")
+        if n.swa_slot >= 0 and n.swa_slot != slot:
+            self._freed_swa.append(n.swa_slot)
+        n.swa_slot = int(slot)
+        self._swa_touch(n)
+
+    def has_swa(self, h) -> bool:
+        return h is not None and h.live and h is not self._root and h.swa_slot >= 0
+
+    def swa_slot(self, h) -> int:
+        return self._check(h).swa_slot
+
+    def swa_lock_cnt(self, h) -> int:
+        return self._check(h).swa_lock
+
+    def lock_swa(self, h) -> None:
+        n = self._check(h)
+        if n.swa_slot < 0:
+            raise RuntimeError("radix index: node has no window snapshot to lock")
+        n.lock_cnt += 1
+        n.swa_lock += 1
+
+    def unlock_swa(self, h) -> None:
+        if h is None or not h.live:
+            return
+        if h.swa_lock > 0:
+            h.swa_lock -= 1
+        if h.lock_cnt > 0:
+            h.lock_cnt -= 1
+
+    def evict_swa(self, n: int):
+        blocks: List[int] = []
+        hashes: List[int] = []
+        freed = 0
+        for node in list(self._swa_lru):
+            if freed >= n:
+                break
+            if node.swa_lock > 0:
+                continue
+            if node.is_leaf() and node.lock_cnt == 0 and node.ready:
+                blocks.extend(node.blocks)
+                hashes.extend(node.hashes)
+                self._total_blocks -= node.size()
+                self._stats["evict_blocks"] += node.size()
+                del node.parent.children[node.hashes[0]]
+                self._free(node)
+            else:
+                self._drop_swa(node)
+            freed += 1
+        return np.asarray(blocks, dtype=np.int64), np.asarray(hashes, dtype=np.uint64), freed
+
+    def drain_freed_swa_slots(self) -> np.ndarray:
+        out, self._freed_swa = self._freed_swa, []
+        return np.asarray(out, dtype=np.int32)
+
+    def total_swa_slots(self) -> int:
+        return len(self._swa_lru)
 
     # ---- introspection (mirrors the native class) -------------------------------------
     def alive(self, h) -> bool:

@@ -106,3 +106,61 @@ def test_locks():
     assert idx.drain_freed_swa_slots().tolist() == [600, 601]
     idx.reset()
     assert idx.total_swa_slots() == 0 and idx.drain_freed_swa_slots().tolist() == []
+
+
+def test_python_specification_and_native_index_agree_on_random_snapshot_workloads():
+    """Same random script of inserts, snapshot mounts, matches, full and snapshot-only evictions and locks
+    on the native index and on the Python specification; every observable must agree."""
+    from flexkv_b200.cache.radixtree import RadixTreeIndex
+    for seed in range(6):
+        rng = np.random.default_rng(seed)
+        nat, py = C.RadixIndex(2, 0, "lru", 0.0), RadixTreeIndex(2, 0, "lru", 0.0)
+        nat.set_clock_override(1000)
+        py._clock_override = 1000
+        seqs, handles, next_block, next_slot, clock = [], [], 0, 0, 1000
+        for step in range(300):
+            clock += 1
+            nat.set_clock_override(clock)
+            py._clock_override = clock
+            op = int(rng.integers(0, 10))
+            if op < 4 or not seqs:
+                if seqs and rng.random() < 0.5:
+                    base = seqs[int(rng.integers(len(seqs)))]
+                    k = int(rng.integers(1, len(base) + 1))
+                    h = np.concatenate([base[:k], rng.integers(1, 2**62, size=int(rng.integers(1, 5)), dtype=np.uint64)])
+                else:
+                    h = rng.integers(1, 2**62, size=int(rng.integers(1, 6)), dtype=np.uint64)
+                mn, mp = nat.match_prefix(h), py.match_prefix(h)
+                assert mn.num_matched_blocks == mp.num_matched_blocks
+                need = len(h) - mn.num_matched_blocks
+                if need:
+                    phys = np.arange(next_block, next_block + need, dtype=np.int64)
+                    next_block += need
+                    hn, hp = nat.insert(phys, h, len(h), True, mn), py.insert(phys, h, len(h), True, mp)
+                    handles.append((hn, hp))
+                    seqs.append(h)
+            elif op < 6 and handles:
+                hn, hp = handles[int(rng.integers(len(handles)))]
+                if nat.alive(hn):
+                    assert py.alive(hp)
+                    nat.set_swa(hn, next_slot); py.set_swa(hp, next_slot)
+                    next_slot += 1
+            elif op < 8:
+                h = seqs[int(rng.integers(len(seqs)))]
+                k = int(rng.integers(1, len(h) + 1))
+                mn, mp = nat.match_prefix(h[:k]), py.match_prefix(h[:k])
+                assert (mn.num_matched_blocks, mn.swa_hit_blocks, mn.swa_slot) == \
+                    (mp.num_matched_blocks, mp.swa_hit_blocks, mp.swa_slot), (seed, step)
+            elif op == 8:
+                n = int(rng.integers(1, 4))
+                bn, hn_, fn = nat.evict_swa(n)
+                bp, hp_, fp = py.evict_swa(n)
+                assert fn == fp and sorted(bn.tolist()) == sorted(bp.tolist()), (seed, step)
+            else:
+                n = int(rng.integers(1, 6))
+                bn, _ = nat.evict(n)
+                bp, _ = py.evict(n)
+                assert sorted(bn.tolist()) == sorted(bp.tolist()), (seed, step)
+            assert sorted(nat.drain_freed_swa_slots().tolist()) == sorted(py.drain_freed_swa_slots().tolist()), (seed, step)
+            assert nat.total_swa_slots() == py.total_swa_slots()
+            assert nat.total_cached_blocks() == py._total_blocks
