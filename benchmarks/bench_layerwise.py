@@ -54,9 +54,14 @@ def build(shape, ngpu, gpu_blocks, host_blocks, engine_layout, notify, ctas, til
 def scenario_notify(a):
     out = []
     scales = {"small": (8, 16), "medium": (32, 64), "large": (80, 256)}
+    modes = [("hostfunc", 1), ("polling", 1), ("flag", 1), ("flag", 0)]
+    if a.modes:
+        modes = [m for m in modes if (m[0] + ("+fused" if m[1] == 0 else "")) in a.modes]
     for name, (layers, blocks) in scales.items():
+        if a.scales and name not in a.scales:
+            continue
         shape = KVShape(name, layers, 1, 512, dtype=torch.float16, use_mla=True, tokens_per_block=16)
-        for notify, lpb in (("hostfunc", 1), ("polling", 1), ("flag", 1), ("flag", 0)):
+        for notify, lpb in modes:
             grp, region, caches, chunk, bb = build(shape, a.gpus, blocks, blocks, "vllm", notify, a.ctas or 4,
                                                    a.tile_bytes, tp_split=False, lpb=lpb)
             ids = np.arange(blocks, dtype=np.int64)
@@ -152,6 +157,8 @@ def main():
     ap.add_argument("--stub-ctas", type=int, default=148)
     ap.add_argument("--layers-per-batch", type=int, default=0, help="0 = one fused launch with per-layer flags")
     ap.add_argument("--out", default="")
+    ap.add_argument("--scales", nargs="*", default=[], help="notify: subset of small medium large")
+    ap.add_argument("--modes", nargs="*", default=[], help="notify: subset of hostfunc polling flag flag+fused")
     a = ap.parse_args()
     rows = scenario_notify(a) if a.scenario == "notify" else scenario_overlap(a)
     if a.out:
