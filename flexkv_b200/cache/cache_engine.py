@@ -235,6 +235,7 @@ class TransferPlan:
     peer_leases: Optional[Tuple[np.ndarray, np.ndarray]] = None   # (ranks, gpu blocks) pinned in the peer directory
     swa_locked: List[Any] = field(default_factory=list)            # nodes whose window snapshot this plan reads
     swa_pending: Dict[int, int] = field(default_factory=dict)      # side op id -> slot not yet mounted
+    partial_blocks: Optional[int] = None                           # prefetch: blocks (from bstart) that really arrived
 
 
 def _block_range(token_mask: np.ndarray, tokens_per_block: int) -> Tuple[int, int]:
@@ -375,6 +376,7 @@ class GlobalCacheEngine:
                 self.cache_engines[dev].lock_node(node)
         handle = TransferPlanHandle(complete=lambda: self._complete_plan(plan, is_put),
                                     abort=lambda: self._abort_plan(plan))
+        handle.plan = plan        # the task layer reads plan.partial_blocks of a prefetch
         self._update_mempool_metrics()
         return graph, handle, plan.op_callback_dict, end_op
 
@@ -573,7 +575,24 @@ class GlobalCacheEngine:
                                        match_result=None if stage_node is not None else cpu_m)
                 except (RuntimeError, ValueError):
                     node3 = None
-            if node3 is not None:
+            if node3 is not None and prefetch and remote_op.transfer_type == TransferType.REMOTE2H:
+                # a prefetch may succeed for a prefix only: the staged node is replaced by one that holds the
+                # blocks that arrived, the rest goes back to the pool, and the response mask shrinks
+                remote_op.allow_partial = True
+                plan.inserted.setdefault(DeviceType.CPU, []).append(node3)
+
+                def _adopt(c, node=node3, lo=f3_lo, n=f3):
+                    res = getattr(c, "block_results", None)
+                    k = n if res is None else next((i for i, ok in enumerate(res) if not ok), n)
+                    if k < n:
+                        tail = cpu.index.truncate_unready_leaf(node, k)
+                        cpu.recycle(tail)
+                        plan.partial_blocks = (lo - bstart) + k
+                    if k > 0:
+                        cpu.set_ready(node, True, k)
+                _adopt.wants_result = True
+                plan.op_callback_dict[remote_op.op_id] = _adopt
+            elif node3 is not None:
                 plan.nodes.setdefault(DeviceType.CPU, []).append((node3, 0))
                 plan.inserted.setdefault(DeviceType.CPU, []).append(node3)
                 plan.op_callback_dict[remote_op.op_id] = lambda node=node3, n=f3: cpu.set_ready(node, True, n)
@@ -820,6 +839,10 @@ class GlobalCacheEngine:
             return []
         return self.peer_directory.withdraw_blocks(rank, np.asarray(gpu_block_ids, dtype=np.int64))
 
-    def run_op_callback(self, cb: Callable) -> None:
+    def run_op_callback(self, cb: Callable, completed: Any = None) -> None:
+        """Callbacks marked ``wants_result`` receive the completed op (per-block results)."""
         with self._cache_tree_lock:
-            cb()
+            if getattr(cb, "wants_result", False):
+                cb(completed)
+            else:
+                cb()

@@ -308,6 +308,17 @@ class RadixTreeIndex:
         self._free(h)
         return out
 
+    def truncate_unready_leaf(self, h: Optional[PyNode], keep: int) -> np.ndarray:
+        if keep <= 0:
+            return self.remove_unready_leaf(h)
+        if h is None or not h.live or h is self._root or not h.is_leaf() or h.ready or h.lock_cnt > 0 \
+                or keep >= h.size():
+            return np.zeros(0, dtype=np.int64)
+        out = np.asarray(h.blocks[keep:], dtype=np.int64)
+        h.blocks, h.hashes = h.blocks[:keep], h.hashes[:keep]
+        self._total_blocks -= len(out)
+        return out
+
     def reset(self) -> np.ndarray:
         all_blocks: List[int] = []
         stack = list(self._root.children.values())

@@ -83,6 +83,7 @@ class TransferOp:
     gpu_bind: str = "head"
     gpu_offset: int = 0           # head binding starts this many blocks into the launch-time list
     is_swa: bool = False
+    allow_partial: bool = False   # a per-block failure does not fail the op: the planner adopts the good prefix
     remote_node_ids: Optional[np.ndarray] = None      # owner node / rank per block (peer ops)
     block_hashes: Optional[np.ndarray] = None         # key-addressed remote stores
     layer_start: int = 0

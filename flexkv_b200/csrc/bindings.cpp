@@ -161,6 +161,9 @@ PYBIND11_MODULE(_C, m) {
       .def("remove_unready_leaf", [](RadixIndex& t, py::object h) {
              return to_array(t.remove_unready_leaf(handle_from_py(h)));
            })
+      .def("truncate_unready_leaf", [](RadixIndex& t, py::object h, int64_t keep) {
+             return to_array(t.truncate_unready_leaf(handle_from_py(h), keep));
+           })
       .def("reset", [](RadixIndex& t) { return to_array(t.reset()); })
       .def("alive", [](RadixIndex& t, py::object h) { return t.alive(handle_from_py(h)); })
       .def("is_root", [](RadixIndex& t, py::object h) { return t.is_root(handle_from_py(h)); })

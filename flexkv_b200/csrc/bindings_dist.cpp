@@ -146,6 +146,9 @@ void init_dist_bindings(py::module_& m) {
       .def("remove_unready_leaf", [](LocalRadixTree& t, py::object h) {
              return to_array(t.remove_unready_leaf(handle_from_py(h)));
            })
+      .def("truncate_unready_leaf", [](LocalRadixTree& t, py::object h, int64_t keep) {
+             return to_array(t.truncate_unready_leaf(handle_from_py(h), keep));
+           })
       .def("reset", [](LocalRadixTree& t) {
              std::vector<int64_t> v;
              { py::gil_scoped_release rel; v = t.reset(); }

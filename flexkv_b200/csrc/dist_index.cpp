@@ -192,6 +192,10 @@ std::vector<int64_t> LocalRadixTree::remove_unready_leaf(NodeHandle h) {
   std::lock_guard<std::mutex> g(mu_);
   return index_.remove_unready_leaf(h);
 }
+std::vector<int64_t> LocalRadixTree::truncate_unready_leaf(NodeHandle h, int64_t keep) {
+  std::lock_guard<std::mutex> g(mu_);
+  return index_.truncate_unready_leaf(h, keep);
+}
 std::vector<int64_t> LocalRadixTree::reset() {
   std::vector<int64_t> out;
   {

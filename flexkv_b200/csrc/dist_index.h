@@ -99,6 +99,7 @@ class LocalRadixTree {
   void unlock(NodeHandle h);
   void set_ready(NodeHandle h, bool ready, int64_t ready_length);
   std::vector<int64_t> remove_unready_leaf(NodeHandle h);
+  std::vector<int64_t> truncate_unready_leaf(NodeHandle h, int64_t keep);
   std::vector<int64_t> reset();
   int64_t total_cached_blocks();
   int64_t num_evictable_blocks();

@@ -410,6 +410,20 @@ std::vector<int64_t> RadixIndex::remove_unready_leaf(NodeHandle h) {
   return out;
 }
 
+std::vector<int64_t> RadixIndex::truncate_unready_leaf(NodeHandle h, int64_t keep) {
+  if (keep <= 0) return remove_unready_leaf(h);
+  std::vector<int64_t> out;
+  int32_t idx = resolve(h);
+  if (idx <= 0) return out;
+  Node& n = nodes_[idx];
+  if (!n.leaf() || n.ready || n.lock_cnt > 0 || keep >= (int64_t)n.size()) return out;
+  out.assign(n.blocks.begin() + keep, n.blocks.end());
+  n.blocks.resize((size_t)keep);
+  n.hashes.resize((size_t)keep);
+  total_blocks_ -= (int64_t)out.size();
+  return out;
+}
+
 std::vector<int64_t> RadixIndex::reset() {
   std::vector<int64_t> all;
   all.reserve((size_t)total_blocks_);

@@ -98,6 +98,8 @@ class RadixIndex {
   void set_ready(NodeHandle h, bool ready, int64_t ready_length);
   // detaches h when it is still an unready, unlocked leaf; returns its blocks
   std::vector<int64_t> remove_unready_leaf(NodeHandle h);
+  // keeps the first `keep` blocks of an unready, unlocked leaf and returns the rest (keep <= 0 removes it)
+  std::vector<int64_t> truncate_unready_leaf(NodeHandle h, int64_t keep);
   std::vector<int64_t> reset();  // returns every physical block that was indexed
 
   bool alive(NodeHandle h) const;

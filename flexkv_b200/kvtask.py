@@ -377,11 +377,11 @@ class KVTaskEngine:
                 for m in members:
                     for old, new in task.op_remap.items():
                         if new == c.op_id and old in m.op_callback_dict:
-                            self.cache_engine.run_op_callback(m.op_callback_dict.pop(old))
+                            self.cache_engine.run_op_callback(m.op_callback_dict.pop(old), c)
             else:
                 cb = task.op_callback_dict.pop(c.op_id, None)
                 if cb is not None:
-                    self.cache_engine.run_op_callback(cb)
+                    self.cache_engine.run_op_callback(cb, c)
             if c.op_id == task.task_end_op_id:
                 task.task_end_op_finished = True
                 for m in members:
@@ -395,6 +395,12 @@ class KVTaskEngine:
             m.task_end_op_finished = True
             if m.plan_handle is not None:
                 (m.plan_handle.complete if success else m.plan_handle.abort)()
+                part = getattr(getattr(m.plan_handle, "plan", None), "partial_blocks", None)
+                if success and part is not None and isinstance(m.return_mask, np.ndarray) and m.return_mask.any():
+                    # only the longest prefix that really arrived is reported (flexkv/kvtask.py:615-698)
+                    first = int(np.flatnonzero(m.return_mask)[0])
+                    m.return_mask = m.return_mask.copy()
+                    m.return_mask[first + part * self.cache_config.tokens_per_block:] = False
             if not success and m.task_type == TaskType.GET and m.slot_mapping is not None:
                 m.failed_gpu_blocks = slot_mapping_to_block_ids(np.asarray(m.slot_mapping, dtype=np.int64),
                                                                 self.cache_config.tokens_per_block)

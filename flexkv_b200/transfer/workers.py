@@ -507,6 +507,9 @@ class RemoteWorker(TransferWorker):
         views = [host.block_view(int(b)) for b in cpu]
         res = self.backend.get(list(ids), views) if self.to_host else self.backend.put(list(ids), views)
         ok = all(res)
+        if not ok and op.allow_partial and self.to_host and res and res[0]:
+            # the planner keeps the longest successful prefix (prefetch); the op itself counts as done
+            return OpOutcome(True, block_results=tuple(bool(r) for r in res), num_bytes=sum(res) * host.block_bytes)
         return OpOutcome(ok, block_results=tuple(bool(r) for r in res), num_bytes=sum(res) * host.block_bytes,
                          error="" if ok else f"{len(res) - sum(res)} remote block(s) failed")
 

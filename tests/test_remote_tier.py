@@ -97,3 +97,32 @@ def test_fault_injector_modes():
     s = KVStoreBackend(LoopbackKVStore())
     blk = np.arange(16, dtype=np.uint8)
     assert s.put([7, 8], [blk, blk]) == [True, True] and s.prefix_hit(np.array([7, 8, 9], dtype=np.uint64)) == 2
+
+
+def test_prefetch_reports_the_longest_prefix_that_arrived(monkeypatch):
+    """Per-block failures injected on the host: a prefetch keeps the blocks before the first failure."""
+    monkeypatch.setenv("FLEXKV_MOONCAKE_FAULT_MODE", "tail")
+    monkeypatch.setenv("FLEXKV_MOONCAKE_FAULT_OP", "get")
+    monkeypatch.setenv("FLEXKV_MOONCAKE_FAULT_TAIL_N", "2")
+    mgr, kv = start(dict(enable_remote=True, use_mooncake_store_backend=True, mooncake_store_config_path="loopback",
+                         remote_config_custom={"store": LoopbackKVStore()}))
+    try:
+        tok = np.arange(6 * T, dtype=np.int64)
+        tid = mgr.put_async(tok, slots(range(6)))
+        assert mgr.wait(tid, completely=True)[tid].status.value == "success"
+        saved = [t.clone() for t in kv]
+        mgr._clear_cpu_cache()
+        pid = mgr.prefetch_async(tok)
+        r = mgr.wait(pid, completely=True)[pid]
+        assert r.status.value == "success" and int(r.return_mask.sum()) == 4 * T      # 6 asked, last 2 failed
+        cpu = mgr.kv_task_engine.cache_engine.cpu_cache_engine
+        assert cpu.mempool.num_used_blocks == 4
+        # the adopted prefix serves a host-only get with the right bytes
+        tid, mask = mgr.get_match(tok, cpu_only=True)
+        assert int(mask.sum()) == 4 * T
+        mgr.launch(tid, slots(range(20, 24)))
+        assert mgr.wait(tid)[tid].status.value == "success"
+        for l in range(2):
+            assert torch.equal(kv[l][:, 20:24], saved[l][:, 0:4])
+    finally:
+        mgr.shutdown()
