@@ -165,6 +165,19 @@ PYBIND11_MODULE(_C, m) {
              return to_array(t.truncate_unready_leaf(handle_from_py(h), keep));
            })
       .def("reset", [](RadixIndex& t) { return to_array(t.reset()); })
+      .def("export_ready", [](RadixIndex& t) {
+             IndexSnapshot s = t.export_ready();
+             return py::make_tuple(to_array(s.parents), to_array(s.sizes), to_array(s.hashes), to_array(s.blocks));
+           })
+      .def("import_snapshot", [](RadixIndex& t, py::array_t<int32_t, py::array::c_style | py::array::forcecast> parents,
+                                 I64Array sizes, U64Array hashes, I64Array blocks) {
+             IndexSnapshot s;
+             s.parents.assign(parents.data(), parents.data() + parents.size());
+             s.sizes.assign(sizes.data(), sizes.data() + sizes.size());
+             s.hashes.assign(hashes.data(), hashes.data() + hashes.size());
+             s.blocks.assign(blocks.data(), blocks.data() + blocks.size());
+             return t.import_snapshot(s);
+           })
       .def("alive", [](RadixIndex& t, py::object h) { return t.alive(handle_from_py(h)); })
       .def("is_root", [](RadixIndex& t, py::object h) { return t.is_root(handle_from_py(h)); })
       .def("root", [](RadixIndex& t) { return handle_to_py(t.root_handle()); })
@@ -194,6 +207,7 @@ PYBIND11_MODULE(_C, m) {
       .def("allocate", [](BlockPool& p, int64_t n, bool strict) { return to_array(p.allocate(n, strict)); },
            py::arg("num"), py::arg("strict") = true)
       .def("recycle", [](BlockPool& p, I64Array ids) { p.recycle(ids.data(), (int64_t)ids.size()); })
+      .def("reserve", [](BlockPool& p, I64Array ids) { p.reserve(ids.data(), (int64_t)ids.size()); })
       .def("reset", &BlockPool::reset)
       .def_property_readonly("num_free", &BlockPool::num_free)
       .def_property_readonly("num_total", &BlockPool::num_total)

@@ -212,10 +212,14 @@ void LayerwiseGroup::update_gpu_ptrs(int rank, const std::vector<uint64_t>& ptrs
 void LayerwiseGroup::run_job(int r, const Job& j) {
   Rank& rk = *ranks_[(size_t)r];
   const int L = opt_.group.num_layers, R = (int)gpus_.size();
-  // adaptive mode: small restores are launch-bound and go out as one fused launch, large ones keep
-  // one launch per layer (measured on B200: fused 0.14 vs 0.22 ms for 2 MiB, 11.2 vs 9.0 ms for 320 MiB)
+  // adaptive mode: a fused launch saves L-1 launches and wins at every size once the grid has
+  // enough single-warp CTAs to keep the link busy (measured on B200, 2 MiB / 32 MiB / 320 MiB:
+  // 8 CTAs 0.165 / 1.03 / 8.32 ms fused against 0.217 / 1.31 / 8.87 ms per layer; 4 CTAs 0.119 /
+  // 1.11 / 10.9 against 0.21 / 1.33 / 8.93). Narrow grids keep one launch per layer above fused_max_bytes.
   const int64_t job_bytes = j.n * (int64_t)L * opt_.group.kv_dim * opt_.group.chunk_bytes;
-  const bool fused = opt_.layers_per_batch == 0 || (opt_.layers_per_batch < 0 && job_bytes <= opt_.fused_max_bytes);
+  const bool wide_grid = opt_.group.h2d.num_ctas >= 8;
+  const bool fused = opt_.layers_per_batch == 0 ||
+                     (opt_.layers_per_batch < 0 && (wide_grid || job_bytes <= opt_.fused_max_bytes));
   const int B = fused ? L : (opt_.layers_per_batch > 0 ? opt_.layers_per_batch : 1);
   const int batches = (L + B - 1) / B;
   const auto t_begin = std::chrono::steady_clock::now();

@@ -4,6 +4,7 @@
 #include <algorithm>
 #include <chrono>
 #include <queue>
+#include <unordered_set>
 
 namespace fkv {
 
@@ -441,6 +442,85 @@ std::vector<int64_t> RadixIndex::reset() {
   return all;
 }
 
+// ---- warm restart ---------------------------------------------------------------
+
+IndexSnapshot RadixIndex::export_ready() const {
+  IndexSnapshot snap;
+  // explicit stack of (node, position of its parent in the image); children in key order
+  // so that the image of a given tree is deterministic
+  std::vector<std::pair<int32_t, int32_t>> stack;
+  auto push_children = [&](const Node& n, int32_t pos) {
+    if (!n.children) return;
+    std::vector<std::pair<uint64_t, int32_t>> kids(n.children->begin(), n.children->end());
+    std::sort(kids.begin(), kids.end(), [](const auto& a, const auto& b) { return a.first > b.first; });
+    for (const auto& kv : kids) stack.emplace_back(kv.second, pos);
+  };
+  push_children(nodes_[0], -1);
+  while (!stack.empty()) {
+    auto [idx, parent_pos] = stack.back();
+    stack.pop_back();
+    const Node& n = nodes_[idx];
+    if (!n.live || !n.ready) continue;
+    int32_t pos = (int32_t)snap.parents.size();
+    snap.parents.push_back(parent_pos);
+    snap.sizes.push_back((int64_t)n.size());
+    snap.hashes.insert(snap.hashes.end(), n.hashes.begin(), n.hashes.end());
+    snap.blocks.insert(snap.blocks.end(), n.blocks.begin(), n.blocks.end());
+    push_children(n, pos);
+  }
+  return snap;
+}
+
+int64_t RadixIndex::import_snapshot(const IndexSnapshot& snap) {
+  if (!is_empty()) throw std::invalid_argument("radix index import: the index is not empty");
+  const size_t nn = snap.parents.size();
+  if (snap.sizes.size() != nn) throw std::invalid_argument("radix index import: parents / sizes differ in length");
+  int64_t total = 0;
+  for (size_t i = 0; i < nn; ++i) {
+    if (snap.sizes[i] <= 0) throw std::invalid_argument("radix index import: empty node");
+    if (snap.parents[i] < -1 || snap.parents[i] >= (int32_t)i)
+      throw std::invalid_argument("radix index import: a node is listed before its parent");
+    total += snap.sizes[i];
+  }
+  if ((int64_t)snap.hashes.size() != total || (int64_t)snap.blocks.size() != total)
+    throw std::invalid_argument("radix index import: hashes / blocks do not cover the nodes");
+  if (max_num_blocks_ > 0 && total > max_num_blocks_)
+    throw std::invalid_argument("radix index import: more blocks than this index may hold");
+  {
+    std::vector<uint8_t> seen((size_t)std::max<int64_t>(max_num_blocks_, 0), 0);
+    std::unordered_set<int64_t> seen_sparse;
+    for (int64_t b : snap.blocks) {
+      if (b < 0 || (max_num_blocks_ > 0 && b >= max_num_blocks_))
+        throw std::invalid_argument("radix index import: block id out of range");
+      bool dup = max_num_blocks_ > 0 ? seen[(size_t)b]++ != 0 : !seen_sparse.insert(b).second;
+      if (dup) throw std::invalid_argument("radix index import: a block id is listed twice");
+    }
+  }
+  // replay as inserts: the image is in pre-order, so the path of the node being added is
+  // the path of the previous one cut back to the common ancestor
+  std::vector<uint64_t> path;
+  std::vector<std::pair<int32_t, size_t>> open;  // (position in the image, path length with that node)
+  std::vector<size_t> offset(nn + 1, 0);
+  for (size_t i = 0; i < nn; ++i) offset[i + 1] = offset[i] + (size_t)snap.sizes[i];
+  try {
+    for (size_t i = 0; i < nn; ++i) {
+      while (!open.empty() && open.back().first != snap.parents[i]) open.pop_back();
+      if (open.empty() && snap.parents[i] != -1)
+        throw std::invalid_argument("radix index import: the image is not in pre-order");
+      path.resize(open.empty() ? 0 : open.back().second);
+      path.insert(path.end(), snap.hashes.begin() + (ptrdiff_t)offset[i], snap.hashes.begin() + (ptrdiff_t)offset[i + 1]);
+      NodeHandle h = insert(snap.blocks.data() + offset[i], snap.sizes[i], path.data(), (int64_t)path.size(),
+                            (int64_t)path.size(), true, nullptr);
+      if (h == kNullHandle) throw std::invalid_argument("radix index import: two nodes share a path");
+      open.emplace_back((int32_t)i, path.size());
+    }
+  } catch (...) {
+    reset();
+    throw;
+  }
+  return total;
+}
+
 // ---- sliding-window snapshots ---------------------------------------------------
 
 void RadixIndex::drop_swa(int32_t idx) {
@@ -587,6 +667,24 @@ std::vector<int64_t> BlockPool::allocate(int64_t n, bool strict) {
     out[(size_t)i] = id;
   }
   return out;
+}
+
+void BlockPool::reserve(const int64_t* ids, int64_t n) {
+  for (int64_t i = 0; i < n; ++i) {
+    int64_t id = ids[i];
+    bool in_range = id >= 0 && id < total_;
+    if (!in_range || used_[(size_t)id]) {
+      for (int64_t j = 0; j < i; ++j) used_[(size_t)ids[j]] = 0;  // roll back
+      if (!in_range) throw std::out_of_range("BlockPool: block id out of range");
+      throw std::runtime_error("BlockPool: block already in use or listed twice");
+    }
+    used_[(size_t)id] = 1;
+  }
+  if (n == 0) return;
+  size_t w = 0;
+  for (size_t r = 0; r < free_.size(); ++r)
+    if (!used_[(size_t)free_[r]]) free_[w++] = free_[r];
+  free_.resize(w);
 }
 
 void BlockPool::recycle(const int64_t* ids, int64_t n) {

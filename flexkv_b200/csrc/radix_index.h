@@ -45,6 +45,15 @@ struct EvictResult {
   std::vector<uint64_t> hashes;
 };
 
+// Flat image of the ready part of an index, parents before children: node i hangs below
+// node parents[i] (-1 = the root) and owns sizes[i] consecutive entries of hashes / blocks.
+struct IndexSnapshot {
+  std::vector<int32_t> parents;
+  std::vector<int64_t> sizes;
+  std::vector<uint64_t> hashes;
+  std::vector<int64_t> blocks;
+};
+
 class RadixIndex {
  public:
   RadixIndex(int tokens_per_block, int64_t max_num_blocks, EvictPolicy policy,
@@ -101,6 +110,14 @@ class RadixIndex {
   // keeps the first `keep` blocks of an unready, unlocked leaf and returns the rest (keep <= 0 removes it)
   std::vector<int64_t> truncate_unready_leaf(NodeHandle h, int64_t keep);
   std::vector<int64_t> reset();  // returns every physical block that was indexed
+
+  // Warm restart of a tier whose bytes outlive the process (SSD files, a shared mount):
+  // export_ready() lists every ready node (subtrees below an unready node are left out,
+  // their data was still in flight); import_snapshot() rebuilds them in an empty index and
+  // returns the number of blocks restored. A malformed image (forward parent, size mismatch,
+  // block id out of range or listed twice) throws std::invalid_argument and leaves the index empty.
+  IndexSnapshot export_ready() const;
+  int64_t import_snapshot(const IndexSnapshot& snap);
 
   bool alive(NodeHandle h) const;
   bool is_root(NodeHandle h) const { return h == root_handle(); }
@@ -193,6 +210,9 @@ class BlockPool {
   // returns fewer than n ids only when strict == false and the pool is short
   std::vector<int64_t> allocate(int64_t n, bool strict);
   void recycle(const int64_t* ids, int64_t n);
+  // takes these specific free ids out of the pool (blocks restored from a saved index);
+  // throws and changes nothing when one is out of range, listed twice or already in use
+  void reserve(const int64_t* ids, int64_t n);
   void reset();
   int64_t num_free() const { return (int64_t)free_.size(); }
   int64_t num_total() const { return total_; }
