@@ -22,6 +22,7 @@ from ..common.block import SequenceMeta
 from ..common.config import GLOBAL_CONFIG_FROM_ENV, CacheConfig, ModelConfig
 from ..common.debug import EvictionLogAggregator, flexkv_logger
 from ..common.transfer import DeviceType, TransferOp, TransferOpGraph, TransferType
+from . import persist
 from .mempool import Mempool, NotEnoughSpaceError
 from .radixtree import RadixTreeIndex
 
@@ -246,6 +247,8 @@ def _block_range(token_mask: np.ndarray, tokens_per_block: int) -> Tuple[int, in
 
 
 class GlobalCacheEngine:
+    _index_saved = False
+
     def __init__(self, cache_config: CacheConfig, model_config: ModelConfig) -> None:
         self.cache_config = cache_config
         self.model_config = model_config
@@ -302,6 +305,10 @@ class GlobalCacheEngine:
         self._evict_log = EvictionLogAggregator()
         for eng in self.cache_engines.values():
             eng.on_evict.append(self._on_evict)
+        # warm restart: mount the SSD index that the last clean shutdown left beside the files
+        self.ssd_blocks_restored = 0
+        if self.ssd_cache_engine is not None and persist.persist_enabled(cache_config):
+            self.ssd_blocks_restored = persist.load_index(cache_config, model_config, self.ssd_cache_engine)
         self.event_listeners: List[Any] = []   # objects with publish_stored / publish_removed
 
     # ---- observers ------------------------------------------------------------
@@ -330,7 +337,14 @@ class GlobalCacheEngine:
             self._update_mempool_metrics()
 
     def shutdown(self) -> None:
-        """Leaves the cross-node registry (withdraws published blocks, stops the heartbeat)."""
+        """Saves the SSD index when the tier persists (the data plane has stopped by now, so every
+        ready block is on disk) and leaves the cross-node registry (withdraws published blocks,
+        stops the heartbeat)."""
+        if self.ssd_cache_engine is not None and persist.persist_enabled(self.cache_config) and \
+                not self._index_saved:
+            self._index_saved = True
+            with self._cache_tree_lock:
+                persist.save_index(self.cache_config, self.model_config, self.ssd_cache_engine)
         for e in self.cache_engines.values():
             if hasattr(e, "shutdown"):
                 e.shutdown()

@@ -62,6 +62,21 @@ class Mempool:
         self._free_mask[block_ids] = True
         self._num_free += int(block_ids.size)
 
+    def reserve_blocks(self, block_ids: np.ndarray) -> None:
+        """Takes these specific free blocks out of the pool (blocks of an index mounted from disk)."""
+        block_ids = np.ascontiguousarray(block_ids, dtype=np.int64)
+        if block_ids.size == 0:
+            return
+        if self._native is not None:
+            self._native.reserve(block_ids)
+            return
+        if block_ids.min() < 0 or block_ids.max() >= self.num_total_blocks:
+            raise IndexError("block id out of range")
+        if np.unique(block_ids).size != block_ids.size or not self._free_mask[block_ids].all():
+            raise RuntimeError("block already in use or listed twice")
+        self._free_mask[block_ids] = False
+        self._num_free -= int(block_ids.size)
+
     @property
     def num_free_blocks(self) -> int:
         return self._native.num_free if self._native is not None else self._num_free

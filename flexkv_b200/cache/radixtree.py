@@ -332,6 +332,71 @@ class RadixTreeIndex:
         self._swa_lru, self._freed_swa = [], []
         return np.asarray(all_blocks, dtype=np.int64)
 
+    # ---- warm restart (same image as the native index) -------------------------------------
+    def export_ready(self):
+        """Flat pre-order image of the ready nodes: ``(parents, sizes, hashes, blocks)``; node ``i``
+        hangs below ``parents[i]`` (-1 = root). Subtrees below an unready node are left out."""
+        parents: List[int] = []
+        sizes: List[int] = []
+        hashes: List[int] = []
+        blocks: List[int] = []
+        stack = [(c, -1) for _, c in sorted(self._root.children.items(), reverse=True)]
+        while stack:
+            n, parent_pos = stack.pop()
+            if not n.live or not n.ready:
+                continue
+            pos = len(parents)
+            parents.append(parent_pos)
+            sizes.append(n.size())
+            hashes.extend(n.hashes)
+            blocks.extend(n.blocks)
+            stack.extend((c, pos) for _, c in sorted(n.children.items(), reverse=True))
+        return (np.asarray(parents, dtype=np.int32), np.asarray(sizes, dtype=np.int64),
+                np.asarray(hashes, dtype=np.uint64), np.asarray(blocks, dtype=np.int64))
+
+    def import_snapshot(self, parents, sizes, hashes, blocks) -> int:
+        """Rebuilds an exported image in an empty index; returns the number of blocks restored.
+        A malformed image raises ValueError and leaves the index empty."""
+        if not self.is_empty():
+            raise ValueError("radix index import: the index is not empty")
+        parents = np.asarray(parents, dtype=np.int64)
+        sizes = np.asarray(sizes, dtype=np.int64)
+        hashes = np.asarray(hashes, dtype=np.uint64)
+        blocks = np.asarray(blocks, dtype=np.int64)
+        nn = len(parents)
+        if len(sizes) != nn:
+            raise ValueError("radix index import: parents / sizes differ in length")
+        if nn and (sizes.min() <= 0 or (parents < -1).any() or (parents >= np.arange(nn)).any()):
+            raise ValueError("radix index import: empty node or a node listed before its parent")
+        total = int(sizes.sum())
+        if len(hashes) != total or len(blocks) != total:
+            raise ValueError("radix index import: hashes / blocks do not cover the nodes")
+        if self.max_num_blocks > 0 and total > self.max_num_blocks:
+            raise ValueError("radix index import: more blocks than this index may hold")
+        if total and (blocks.min() < 0 or (self.max_num_blocks > 0 and blocks.max() >= self.max_num_blocks)):
+            raise ValueError("radix index import: block id out of range")
+        if np.unique(blocks).size != total:
+            raise ValueError("radix index import: a block id is listed twice")
+        off = np.concatenate([[0], np.cumsum(sizes)])
+        path: List[int] = []
+        open_: List[Tuple[int, int]] = []
+        try:
+            for i in range(nn):
+                while open_ and open_[-1][0] != parents[i]:
+                    open_.pop()
+                if not open_ and parents[i] != -1:
+                    raise ValueError("radix index import: the image is not in pre-order")
+                del path[open_[-1][1] if open_ else 0:]
+                path.extend(hashes[off[i]:off[i + 1]].tolist())
+                h = self.insert(blocks[off[i]:off[i + 1]], np.asarray(path, dtype=np.uint64), len(path), True, None)
+                if h is None:
+                    raise ValueError("radix index import: two nodes share a path")
+                open_.append((i, len(path)))
+        except Exception:
+            self.reset()
+            raise
+        return total
+
     # ---- window snapshots mounted on nodes (same rules as the native index) ---------------
     def _drop_swa(self, n: PyNode) -> None:
         if n.swa_slot >= 0:

@@ -271,6 +271,7 @@ class CacheConfig:
     num_remote_blocks: Optional[int] = None
     num_local_blocks: int = 1000000
     ssd_cache_dir: Optional[Union[str, List[str]]] = None
+    ssd_persist: bool = False              # keep the SSD files and their index across restarts (FLEXKV_SSD_PERSIST)
     remote_cache_size_mode: str = "file_size"
     remote_file_size: Optional[int] = None
     remote_file_num: Optional[int] = None
@@ -343,6 +344,7 @@ def load_env_config() -> Namespace:
         iouring_entries=_env("FLEXKV_IOURING_ENTRIES", 512),
         iouring_flags=_env("FLEXKV_IOURING_FLAGS", 0),
         max_file_size_gb=_env("FLEXKV_MAX_FILE_SIZE_GB", -1.0),
+        ssd_persist=_env("FLEXKV_SSD_PERSIST", False, bool),
         evict_ratio=_env("FLEXKV_EVICT_RATIO", 0.0),
         evict_start_threshold=_env("FLEXKV_EVICT_START_THRESHOLD", 1.0),
         hit_reward_seconds=_env("FLEXKV_HIT_REWARD_SECONDS", 0),

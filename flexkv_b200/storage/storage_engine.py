@@ -239,15 +239,24 @@ class StorageEngine:
         per_dev = c.num_ssd_blocks // ndev
         max_gb = self.env.max_file_size_gb
         blocks_per_file = per_dev
-        for d in dirs:
+        from ..cache import persist
+        self._ssd_persist = persist.persist_enabled(c)
+        for di, d in enumerate(dirs):
             os.makedirs(d, exist_ok=True)
             free = shutil.disk_usage(d).free
+            if self._ssd_persist:
+                # the files of the previous run are this tier's own space: the split into files
+                # (and with it the place of every block) must come out the same again
+                for name in os.listdir(d):
+                    if name.startswith(f"flexkv_ssd_cache_{di}_") and name.endswith(".bin"):
+                        free += os.stat(os.path.join(d, name)).st_blocks * 512
             blocks_per_file = min(blocks_per_file, max(1, free // block_bytes))
         if max_gb and max_gb > 0:
             blocks_per_file = min(blocks_per_file, max(1, int(max_gb * 2**30) // block_bytes))
         files_per_dev = (per_dev + blocks_per_file - 1) // blocks_per_file
-        prefix = f"flexkv_ssd_cache_{os.getpid()}" if os.environ.get("FLEXKV_SSD_FILE_PER_PROCESS", "1") == "1" \
-            else "flexkv_ssd_cache"
+        # a persistent tier keeps fixed file names so that the next process finds its blocks
+        prefix = f"flexkv_ssd_cache_{os.getpid()}" if not self._ssd_persist and \
+            os.environ.get("FLEXKV_SSD_FILE_PER_PROCESS", "1") == "1" else "flexkv_ssd_cache"
         files = [[os.path.join(d, f"{prefix}_{di}_{j}.bin") for j in range(files_per_dev)]
                  for di, d in enumerate(dirs)]
         engine = _native.C.SsdIoEngine(files, block_bytes, blocks_per_file, create=True, try_direct=True,
@@ -257,6 +266,8 @@ class StorageEngine:
         if self.host.size_table is not None:
             per_block = self.host.size_table.numel() // self.host.num_blocks
             self.ssd_size_table = np.zeros((c.num_ssd_blocks, per_block), dtype=np.int32)
+            if self._ssd_persist and persist.load_size_table(c, self.ssd_size_table):
+                flexkv_logger.info("ssd size table loaded from the previous run")
         flexkv_logger.info("ssd pool: %d blocks x %d B over %d dir(s), %d file(s)/dir, io_uring=%s direct=%s",
                            c.num_ssd_blocks, block_bytes, ndev, files_per_dev, engine.using_iouring,
                            engine.direct_available)
@@ -342,7 +353,10 @@ class StorageEngine:
         if self.ssd is not None:
             files = [f for d in self.ssd.files for f in d]
             self.ssd = None
-            if os.environ.get("FLEXKV_KEEP_SSD_FILES", "0") != "1":
+            if getattr(self, "_ssd_persist", False):
+                from ..cache import persist
+                persist.save_size_table(self.cache_config, self.ssd_size_table)
+            elif os.environ.get("FLEXKV_KEEP_SSD_FILES", "0") != "1":
                 for f in files:
                     try:
                         os.unlink(f)
