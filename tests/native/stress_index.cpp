@@ -93,6 +93,26 @@ static void single_thread_index(uint64_t seed) {
     }
     CHECK(idx.total_cached_blocks() == pool.num_used());
     CHECK(idx.total_cached_blocks() <= cap);
+    if (it % 500 == 499) {
+      // warm-restart image: a second index and pool rebuilt from it agree with the first
+      IndexSnapshot snap = idx.export_ready();
+      RadixIndex copy(16, cap, EvictPolicy::LRU, 0.0);
+      BlockPool pool2(cap);
+      CHECK(copy.import_snapshot(snap) == idx.total_ready_blocks());
+      pool2.reserve(snap.blocks.data(), (int64_t)snap.blocks.size());
+      CHECK(pool2.num_used() == copy.total_cached_blocks());
+      for (const auto& h : seen) {
+        MatchResult a = idx.match_prefix(h.data(), (int64_t)h.size(), false, false);
+        MatchResult b = copy.match_prefix(h.data(), (int64_t)h.size(), false, false);
+        CHECK(b.num_matched == b.num_ready_matched);
+        CHECK(b.num_ready_matched >= a.num_ready_matched);  // ready nodes below an unready gap cannot exist
+        CHECK(b.num_ready_matched == a.num_ready_matched);
+        for (int64_t k = 0; k < b.num_matched; ++k) CHECK(a.physical_blocks[(size_t)k] == b.physical_blocks[(size_t)k]);
+      }
+      IndexSnapshot again = copy.export_ready();
+      CHECK(again.parents == snap.parents && again.sizes == snap.sizes && again.hashes == snap.hashes &&
+            again.blocks == snap.blocks);
+    }
   }
   for (NodeHandle h : locked) idx.unlock(h);
   auto all = idx.reset();
