@@ -19,21 +19,54 @@ void init_layerwise_bindings(py::module_& m) {
       .def_readonly("disk_ms", &LayerwiseResult::disk_ms)
       .def_readonly("layer_done_ms", &LayerwiseResult::layer_done_ms);
 
+  auto parse_options = [](py::dict o) {
+    LayerwiseOptions lo;
+    lo.group = parse_group_options(o);
+    if (o.contains("notify_mode")) lo.notify = parse_notify_mode(o["notify_mode"].cast<std::string>());
+    if (o.contains("num_counters")) lo.num_counters = o["num_counters"].cast<int>();
+    if (o.contains("layers_per_batch")) lo.layers_per_batch = o["layers_per_batch"].cast<int>();
+    if (o.contains("fused_max_bytes")) lo.fused_max_bytes = o["fused_max_bytes"].cast<int64_t>();
+    if (o.contains("create_eventfds")) lo.create_eventfds = o["create_eventfds"].cast<bool>();
+    return lo;
+  };
+
   py::class_<LayerwiseGroup>(m, "LayerwiseGroup")
-      .def(py::init([](py::list gpus, py::dict host, py::dict o) {
-             LayerwiseOptions lo;
-             lo.group = parse_group_options(o);
-             if (o.contains("notify_mode")) lo.notify = parse_notify_mode(o["notify_mode"].cast<std::string>());
-             if (o.contains("num_counters")) lo.num_counters = o["num_counters"].cast<int>();
-             if (o.contains("layers_per_batch")) lo.layers_per_batch = o["layers_per_batch"].cast<int>();
-             if (o.contains("fused_max_bytes")) lo.fused_max_bytes = o["fused_max_bytes"].cast<int64_t>();
-             if (o.contains("create_eventfds")) lo.create_eventfds = o["create_eventfds"].cast<bool>();
+      .def(py::init([parse_options](py::list gpus, py::dict host, py::dict o) {
+             LayerwiseOptions lo = parse_options(o);
              std::vector<GpuSide> gs = parse_gpu_sides(gpus);
              HostSide h = parse_host_side(host);
              py::gil_scoped_release rel;
              return new LayerwiseGroup(std::move(gs), h, lo);
            }))
+      // multi-group form: groups = [{"gpus": [...], "host": {...}, "options": {num_layers, kv_dim, chunk_bytes,
+      // cpu_tp_stride, shared_kv}}], members[l] = [(group, local_layer), ...], host = the whole block pool
+      .def_static("multi_group", [parse_options](py::list groups, py::list members, py::dict host, py::dict o) {
+             LayerwiseOptions lo = parse_options(o);
+             std::vector<LayerwiseMemberGroup> gs;
+             for (py::handle gh : groups) {
+               py::dict g = gh.cast<py::dict>();
+               LayerwiseMemberGroup mg;
+               mg.gpus = parse_gpu_sides(g["gpus"].cast<py::list>());
+               mg.host = parse_host_side(g["host"].cast<py::dict>());
+               mg.group = parse_group_options(g["options"].cast<py::dict>());
+               gs.push_back(std::move(mg));
+             }
+             std::vector<std::vector<LayerMember>> ms;
+             for (py::handle lh : members) {
+               std::vector<LayerMember> layer;
+               for (py::handle mh : lh.cast<py::list>()) {
+                 py::tuple t = mh.cast<py::tuple>();
+                 layer.push_back(LayerMember{t[0].cast<int>(), t[1].cast<int>()});
+               }
+               ms.push_back(std::move(layer));
+             }
+             HostSide h = parse_host_side(host);
+             py::gil_scoped_release rel;
+             return new LayerwiseGroup(std::move(gs), std::move(ms), h, lo);
+           }, py::arg("groups"), py::arg("members"), py::arg("host"), py::arg("options"))
       .def("update_gpu_ptrs", &LayerwiseGroup::update_gpu_ptrs)
+      .def("update_group_gpu_ptrs", &LayerwiseGroup::update_group_gpu_ptrs)
+      .def_property_readonly("is_multi_group", &LayerwiseGroup::multi_group)
       .def("restore", [](LayerwiseGroup& g, I64Array gpu_blocks, I64Array cpu_blocks, int counter_id, py::object ssd,
                          py::object ssd_layout, py::object ssd_src, py::object cpu_dst) {
              if (gpu_blocks.size() != cpu_blocks.size()) throw std::invalid_argument("block id arrays differ in size");

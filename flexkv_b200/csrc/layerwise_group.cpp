@@ -44,6 +44,40 @@ static StreamWaitValue32Fn stream_wait_value32() {
 
 LayerwiseGroup::LayerwiseGroup(std::vector<GpuSide> gpus, HostSide host, LayerwiseOptions opt)
     : gpus_(std::move(gpus)), host_(host), opt_(opt) {
+  start_ranks();
+}
+
+LayerwiseGroup::LayerwiseGroup(std::vector<LayerwiseMemberGroup> groups, std::vector<std::vector<LayerMember>> members,
+                               HostSide host_block, LayerwiseOptions opt)
+    : host_(host_block), opt_(opt), mgroups_(std::move(groups)), members_(std::move(members)) {
+  if (mgroups_.empty() || members_.empty()) throw std::invalid_argument("LayerwiseGroup: no layer groups or no layers");
+  const size_t R = mgroups_[0].gpus.size();
+  for (const auto& g : mgroups_) {
+    if (g.gpus.size() != R || R == 0) throw std::invalid_argument("LayerwiseGroup: every group needs one GPU side per rank");
+    for (size_t r = 0; r < R; ++r)
+      if (g.gpus[r].device != mgroups_[0].gpus[r].device)
+        throw std::invalid_argument("LayerwiseGroup: a rank's groups live on different devices");
+  }
+  std::vector<std::vector<uint8_t>> seen;
+  for (const auto& g : mgroups_) seen.emplace_back((size_t)g.group.num_layers, 0);
+  for (const auto& layer : members_)
+    for (const LayerMember& m : layer) {
+      if (m.group < 0 || m.group >= (int)mgroups_.size() || m.local_layer < 0 ||
+          m.local_layer >= mgroups_[(size_t)m.group].group.num_layers)
+        throw std::invalid_argument("LayerwiseGroup: layer member out of range");
+      if (seen[(size_t)m.group][(size_t)m.local_layer]++)
+        throw std::invalid_argument("LayerwiseGroup: a group layer is a member of two model layers");
+    }
+  for (size_t g = 0; g < seen.size(); ++g)
+    for (uint8_t s : seen[g])
+      if (!s) throw std::invalid_argument("LayerwiseGroup: a group layer belongs to no model layer and would never be restored");
+  gpus_ = mgroups_[0].gpus;                 // devices and rank count
+  opt_.group.num_layers = (int)members_.size();
+  opt_.layers_per_batch = 1;                // one model layer per signal; members are separate launches
+  start_ranks();
+}
+
+void LayerwiseGroup::start_ranks() {
   if (gpus_.empty()) throw std::invalid_argument("LayerwiseGroup: no GPUs");
   if (opt_.num_counters < 1 || opt_.layers_per_batch < -1) throw std::invalid_argument("LayerwiseGroup: bad options");
   const int L = opt_.group.num_layers, R = (int)gpus_.size(), C = opt_.num_counters;
@@ -209,7 +243,88 @@ void LayerwiseGroup::update_gpu_ptrs(int rank, const std::vector<uint64_t>& ptrs
   gpus_.at((size_t)rank).ptrs = ptrs;
 }
 
+void LayerwiseGroup::update_group_gpu_ptrs(int group, int rank, const std::vector<uint64_t>& ptrs) {
+  if ((int)ptrs.size() > kMaxGpuPtrs) throw std::invalid_argument("too many GPU tensors");
+  std::lock_guard<std::mutex> api(api_mu_);
+  mgroups_.at((size_t)group).gpus.at((size_t)rank).ptrs = ptrs;
+}
+
+// Multi-group restore of one rank: model layer by model layer, one launch per member; the last
+// member's launch carries the completion signal of the model layer (same stream, so the earlier
+// members have landed when its last CTA publishes the flag).
+void LayerwiseGroup::run_job_members(int r, const Job& j) {
+  Rank& rk = *ranks_[(size_t)r];
+  const int L = (int)members_.size(), R = (int)gpus_.size();
+  rk.res_status = 0;
+  rk.res_layer_ms.assign((size_t)L, 0.f);
+  cudaEvent_t* ev = rk.layer_ev.data() + (size_t)j.counter * L;
+  uint32_t* hflags = rk.host_flags + (size_t)j.counter * L;
+  uint32_t* dflags = rk.dev_flags + (size_t)j.counter * L;
+  cudaError_t err = cudaEventRecord(rk.ev_begin, rk.stream);
+  for (int l = 0; l < L && err == cudaSuccess; ++l) {
+    const auto& ms = members_[(size_t)l];
+    bool signalled = false;
+    for (size_t k = 0; k < ms.size() && err == cudaSuccess && j.n > 0; ++k) {
+      const LayerwiseMemberGroup& g = mgroups_[(size_t)ms[k].group];
+      KvCopyParams p;
+      bool skip = false;
+      fill_kv_params(g.gpus[(size_t)r], g.host, g.group, r, R, j.gpu_blocks, j.cpu_blocks, j.n, true,
+                     ms[k].local_layer, 1, 0, p, skip);
+      p.status = rk.status;
+      if (k + 1 == ms.size()) {
+        // the kernel publishes flag word [layer_start]: bias the arrays so that this is model layer l
+        const intptr_t bias = ((intptr_t)l - (intptr_t)ms[k].local_layer) * (intptr_t)sizeof(uint32_t);
+        p.done_counter = rk.done_counter;
+        p.dev_flags = reinterpret_cast<uint32_t*>((intptr_t)dflags + bias);
+        p.host_flags = reinterpret_cast<uint32_t*>((intptr_t)hflags + bias);
+        p.epoch = j.epoch;
+        signalled = true;
+      }
+      err = launch_kv_copy(p, opt_.group.h2d, rk.stream);
+    }
+    if (!signalled && err == cudaSuccess) {
+      // a layer without members, or an empty restore: publish from the host, in stream order
+      hflags[l] = j.epoch;
+      err = cudaMemcpyAsync(dflags + l, hflags + l, sizeof(uint32_t), cudaMemcpyHostToDevice, rk.stream);
+    }
+    if (err == cudaSuccess) err = cudaEventRecord(ev[l], rk.stream);
+    if (err == cudaSuccess && opt_.notify == NotifyMode::HOSTFUNC) {
+      HostFnArg* a = fn_args_[((size_t)r * opt_.num_counters + j.counter) * L + l].get();
+      err = cudaStreamWaitEvent(rk.notify_stream, ev[l], 0);
+      if (err == cudaSuccess) err = cudaLaunchHostFunc(rk.notify_stream, host_fn, a);
+    }
+  }
+  if (err == cudaSuccess && opt_.notify != NotifyMode::HOSTFUNC) {
+    const auto t0 = std::chrono::steady_clock::now();
+    for (int l = 0; l < L && err == cudaSuccess; ++l) {
+      for (;;) {
+        // events in both modes: a host-published flag of an empty layer is set before the stream reaches it
+        cudaError_t q = cudaEventQuery(ev[l]);
+        if (q == cudaSuccess) break;
+        if (q != cudaErrorNotReady) { err = q; break; }
+        if (std::chrono::steady_clock::now() - t0 > std::chrono::seconds(120)) { err = cudaErrorTimeout; break; }
+      }
+      if (err == cudaSuccess) notify(r, j.counter, l, l + 1);
+    }
+  }
+  if (err == cudaSuccess) err = cudaStreamSynchronize(rk.stream);
+  if (err == cudaSuccess) err = cudaStreamSynchronize(rk.notify_stream);
+  if (err != cudaSuccess) {
+    (void)cudaGetLastError();
+    rk.res_status = -(int)err;
+    rk.res_ms = 0.f;
+    return;
+  }
+  rk.res_status = collect_status(rk.status);
+  for (int l = 0; l < L; ++l) cudaEventElapsedTime(&rk.res_layer_ms[(size_t)l], rk.ev_begin, ev[l]);
+  rk.res_ms = rk.res_layer_ms[(size_t)L - 1];
+}
+
 void LayerwiseGroup::run_job(int r, const Job& j) {
+  if (!mgroups_.empty()) {
+    run_job_members(r, j);
+    return;
+  }
   Rank& rk = *ranks_[(size_t)r];
   const int L = opt_.group.num_layers, R = (int)gpus_.size();
   // adaptive mode: a fused launch saves L-1 launches and wins at every size once the grid has

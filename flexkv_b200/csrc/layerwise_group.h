@@ -53,9 +53,29 @@ struct LayerwiseResult {
   std::vector<float> layer_done_ms;  // per layer, time since first launch (rank 0)
 };
 
+// Caches made of several layer groups with different KV shapes (an indexer beside the main
+// cache, compressed-KV groups): every group has its own tensors, chunk size and place inside
+// the byte-flat host block, and a model layer is complete when each of its members
+// (group, layer inside the group) has landed
+// (reference behaviour: csrc/layerwise.cpp:1313-1682, layer_members[orig] = [(group, local_layer)]).
+struct LayerMember {
+  int group;
+  int local_layer;
+};
+struct LayerwiseMemberGroup {
+  std::vector<GpuSide> gpus;   // one per rank, same rank order in every group
+  HostSide host;               // strides of this group inside the host block; `base` already at the group's offset
+  GroupOptions group;          // num_layers / kv_dim / chunk_bytes / cpu_tp_stride / shared_kv of this group
+};
+
 class LayerwiseGroup {
  public:
   LayerwiseGroup(std::vector<GpuSide> gpus, HostSide host, LayerwiseOptions opt);
+  // Multi-group form: `members[l]` lists what model layer l consists of (may be empty: the layer is
+  // signalled at once, in order). opt.group supplies the launch shapes and max_blocks_per_op; its
+  // num_layers is replaced by members.size(). One launch per member, flags from the layer's last one.
+  LayerwiseGroup(std::vector<LayerwiseMemberGroup> groups, std::vector<std::vector<LayerMember>> members,
+                 HostSide host_block, LayerwiseOptions opt);
   ~LayerwiseGroup();
 
   // blocking; `ssd` may be null when nothing comes from disk
@@ -77,6 +97,8 @@ class LayerwiseGroup {
   int num_ranks() const { return (int)gpus_.size(); }
   // new tensor addresses after the engine re-created its cache; call with no restore in flight
   void update_gpu_ptrs(int rank, const std::vector<uint64_t>& ptrs);
+  void update_group_gpu_ptrs(int group, int rank, const std::vector<uint64_t>& ptrs);   // multi-group form
+  bool multi_group() const { return !mgroups_.empty(); }
   int num_layers() const { return opt_.group.num_layers; }
   int num_counters() const { return opt_.num_counters; }
 
@@ -114,13 +136,17 @@ class LayerwiseGroup {
     int rank, counter, layer_lo, layer_hi;
   };
 
+  void start_ranks();
   void rank_main(int r);
   void run_job(int r, const Job& j);
+  void run_job_members(int r, const Job& j);
   void notify(int rank, int counter, int layer_lo, int layer_hi);
   static void CUDART_CB host_fn(void* arg);
 
   std::vector<GpuSide> gpus_;
   HostSide host_;
+  std::vector<LayerwiseMemberGroup> mgroups_;            // empty for the uniform form
+  std::vector<std::vector<LayerMember>> members_;        // [model layer]
   LayerwiseOptions opt_;
   std::vector<std::unique_ptr<Rank>> ranks_;
   std::atomic<bool> stop_{false};

@@ -221,7 +221,9 @@ class TransferEngine:
         try:
             for reg in regs:
                 key = WorkerKey(reg.dp_client_id, reg.pp_rank)
-                old = self.storage.gpu_regs.get(key, {}).get(reg.tp_rank)
+                gid = int(getattr(reg, "group_id", 0) or 0)
+                by_group = self.storage.gpu_group_regs.get(key, {}).get(reg.tp_rank)
+                old = by_group.get(gid) if by_group else self.storage.gpu_regs.get(key, {}).get(reg.tp_rank)
                 if old is None:
                     raise ValueError(f"resume: no registration for {key} rank {reg.tp_rank}")
                 if (old.chunk_bytes, old.num_layers, old.kv_dim, len(old.ptrs)) != \
@@ -233,7 +235,10 @@ class TransferEngine:
                 rank_index = sorted(self.storage.gpu_regs[key]).index(reg.tp_rank)
                 for (k, _), w in self._workers.items():
                     if k == key and hasattr(w, "update_gpu_ptrs"):
-                        w.update_gpu_ptrs(rank_index, [int(p) for p in reg.ptrs])
+                        if by_group:      # per-group tensors: only the layerwise worker keeps native copies
+                            w.update_gpu_ptrs(rank_index, [int(p) for p in reg.ptrs], gid)
+                        else:
+                            w.update_gpu_ptrs(rank_index, [int(p) for p in reg.ptrs])
                     if hasattr(w, "update_gpu_ptrs_for") and reg.tp_rank == 0 and key.dp_client_id in w.rank_of:
                         w.update_gpu_ptrs_for(key.dp_client_id, [int(p) for p in reg.ptrs])
             self._suspended -= keys

@@ -131,6 +131,8 @@ def build_layerwise_group(storage, model_config, key: WorkerKey, notify_mode: Op
     if layers_per_batch is None:
         # -1: one fused launch for small restores, one launch per layer for large ones
         layers_per_batch = int(os.environ.get("FLEXKV_LAYERWISE_LAYERS_PER_BATCH", -1))
+    if storage.host.layout.is_multi_group:
+        return _build_multi_group(storage, model_config, key, env, notify_mode, num_counters, create_eventfds)
     regs = storage.gpu_regs[key]
     ranks = sorted(regs)
     host, reg0 = storage.host, regs[ranks[0]]
@@ -149,6 +151,60 @@ def build_layerwise_group(storage, model_config, key: WorkerKey, notify_mode: Op
                 notify_mode=notify_mode or env.layerwise_notify_mode, num_counters=num_counters,
                 layers_per_batch=layers_per_batch, create_eventfds=create_eventfds)
     return _native.C.LayerwiseGroup([regs[r].as_native() for r in ranks], host_d, opts)
+
+
+def layer_members(model_config, groups) -> List[List[tuple]]:
+    """``members[l]`` = the (group, layer inside the group) pairs that make up model layer ``l``.
+    A group lists its model layers in ``LayerGroupSpec.layer_ids``; without the list its layers
+    are model layers 0 .. n-1 (an indexer or a compressed copy beside every main-cache layer)
+    (reference: csrc/layerwise.cpp:1313-1340)."""
+    specs = model_config.layer_groups or []
+    num_model_layers = int(model_config.num_layers)
+    for g, spec in zip(groups, specs):
+        ids = spec.layer_ids if spec.layer_ids is not None else range(g.num_layers)
+        num_model_layers = max(num_model_layers, max(ids, default=-1) + 1)
+    members: List[List[tuple]] = [[] for _ in range(num_model_layers)]
+    for gid, g in enumerate(groups):
+        spec = specs[gid] if gid < len(specs) else None
+        ids = list(spec.layer_ids) if spec is not None and spec.layer_ids is not None else list(range(g.num_layers))
+        if len(ids) != g.num_layers:
+            raise ValueError(f"layer group {gid}: {len(ids)} layer ids for {g.num_layers} layers")
+        for local, l in enumerate(ids):
+            members[int(l)].append((gid, local))
+    return members
+
+
+def _build_multi_group(storage, model_config, key: WorkerKey, env, notify_mode, num_counters, create_eventfds):
+    host = storage.host
+    lay = host.layout
+    per_rank = storage.gpu_group_regs.get(key, {})
+    if not per_rank:
+        raise ValueError("multi-group host pool but no per-group GPU registrations")
+    ranks = sorted(per_rank)
+    slice_bytes = host.block_bytes // lay.tp_slices
+    shared = lay.tp_slices == 1
+    groups = []
+    for gid, g in enumerate(lay.groups):
+        regs = []
+        for r in ranks:
+            reg = per_rank[r].get(gid)
+            if reg is None:
+                raise ValueError(f"rank {r} did not register layer group {gid}")
+            regs.append(reg.as_native())
+        groups.append(dict(
+            gpus=regs,
+            host=dict(base=host.base + g.offset_bytes, layer_stride=g.layer_stride_bytes, kv_stride=g.chunk_bytes,
+                      block_stride=host.block_bytes, num_blocks=host.num_blocks),
+            options=dict(num_layers=g.num_layers, kv_dim=g.kv_dim, chunk_bytes=g.chunk_bytes,
+                         cpu_tp_stride=0 if shared else slice_bytes, shared_kv=shared)))
+    members = layer_members(model_config, lay.groups)
+    opts = dict(num_layers=len(members), kv_dim=1, chunk_bytes=16, h2d=_launch_cfg(env, True),
+                d2h=_launch_cfg(env, False), max_blocks_per_op=max(4096, min(1 << 18, host.num_blocks)),
+                notify_mode=notify_mode or env.layerwise_notify_mode, num_counters=num_counters,
+                layers_per_batch=1, create_eventfds=create_eventfds)
+    host_d = dict(base=host.base, layer_stride=host.block_bytes, kv_stride=0, block_stride=host.block_bytes,
+                  num_blocks=host.num_blocks)
+    return _native.C.LayerwiseGroup.multi_group(groups, [list(m) for m in members], host_d, opts)
 
 
 class LayerwiseWorker(TransferWorker):
@@ -181,8 +237,11 @@ class LayerwiseWorker(TransferWorker):
         return OpOutcome(r.status == 0, gpu_ms=r.total_ms, num_bytes=nbytes,
                          error="" if r.status == 0 else f"layerwise status 0x{r.status & 0xffffffff:x}")
 
-    def update_gpu_ptrs(self, rank_index: int, ptrs) -> None:
-        self.group.update_gpu_ptrs(rank_index, list(ptrs))
+    def update_gpu_ptrs(self, rank_index: int, ptrs, group_id: int = -1) -> None:
+        if self.group.is_multi_group:
+            self.group.update_group_gpu_ptrs(max(0, int(group_id)), rank_index, list(ptrs))
+        else:
+            self.group.update_gpu_ptrs(rank_index, list(ptrs))
 
     def close(self) -> None:
         if self.receiver is not None:

@@ -812,6 +812,11 @@ def build_workers(storage, model_config: ModelConfig, cache_config: CacheConfig
         if storage.host.layout.is_multi_group:
             workers[(key, TransferType.H2D)] = MultiGroupGpuHostWorker(storage, model_config, key, True)
             workers[(key, TransferType.D2H)] = MultiGroupGpuHostWorker(storage, model_config, key, False)
+            if GLOBAL_CONFIG_FROM_ENV.enable_layerwise_transfer and reg0.device_id >= 0:
+                from .layerwise import LayerwiseWorker
+                sock = os.environ.get("FLEXKV_LAYERWISE_SOCK", "")
+                workers[(key, TransferType.LAYERWISE)] = LayerwiseWorker(
+                    storage, model_config, key, sock_path=f"{sock}.{key.dp_client_id}" if sock else None)
             continue
         if reg0.device_id < 0:
             workers[(key, TransferType.H2D)] = HostEmulatedGpuWorker(storage, model_config, key, True)
