@@ -234,8 +234,9 @@ class TransferPlan:
     num_gpu_blocks_to_transfer: int = 0
     skipped_gpu_blocks: int = 0
     peer_leases: Optional[Tuple[np.ndarray, np.ndarray]] = None   # (ranks, gpu blocks) pinned in the peer directory
-    swa_locked: List[Any] = field(default_factory=list)            # nodes whose window snapshot this plan reads
-    swa_pending: Dict[int, int] = field(default_factory=dict)      # side op id -> slot not yet mounted
+    swa_locked: List[Any] = field(default_factory=list)            # (tier engine, node) pairs this plan window-locked
+    swa_pending: Dict[int, int] = field(default_factory=dict)      # side op id -> host slot not yet mounted
+    swa_pending_ssd: Dict[int, int] = field(default_factory=dict)  # side op id -> SSD window slot not yet mounted
     partial_blocks: Optional[int] = None                           # prefetch: blocks (from bstart) that really arrived
 
 
@@ -301,6 +302,10 @@ class GlobalCacheEngine:
             from .swa_cache_engine import SWAOpConstructor
             self.cpu_cache_engine.attach_swa(SWAHostPool(swa_cfg))
             self.swa_ops = SWAOpConstructor(self)
+            ssd_cfg = cache_config.swa.for_cache_tier(DeviceType.SSD)
+            if ssd_cfg is not None and self.ssd_cache_engine is not None:
+                # second window tier: snapshots are written through beside the SSD blocks
+                self.ssd_cache_engine.attach_swa(SWAHostPool(ssd_cfg))
         self._metrics = None
         self._evict_log = EvictionLogAggregator()
         for eng in self.cache_engines.values():
@@ -412,11 +417,17 @@ class GlobalCacheEngine:
             if swa_aware and self.swa_ops is not None and self.swa_ops.enabled and not prefetch:
                 # joint gate: only a prefix that ends where a window snapshot sits can be resumed
                 m = self.cpu_cache_engine.match(seq)
-                bend = min(bend, int(m.swa_hit_blocks))
+                swa_src = (self.cpu_cache_engine, m.last_swa_node, int(m.swa_slot), int(m.swa_hit_blocks))
+                ssd = self.ssd_cache_engine
+                if ssd is not None and ssd.swa_enabled and not cpu_only:
+                    ms = ssd.match(seq)
+                    if int(ms.swa_hit_blocks) > swa_src[3]:      # a deeper snapshot sits on the SSD tier
+                        swa_src = (ssd, ms.last_swa_node, int(ms.swa_slot), int(ms.swa_hit_blocks))
+                bend = min(bend, swa_src[3])
                 if bend <= bstart:
                     return self._empty(token_mask)
-                swa_src = (m.last_swa_node, int(m.swa_slot))
-                cpu_only = True                     # window state lives on the host tier only
+                if swa_src[0] is self.cpu_cache_engine:
+                    cpu_only = True                 # the host snapshot needs no deeper tier
                 if gpu_blocks is not None:
                     gpu_blocks = gpu_blocks[:bend - bstart]
             plan = self._get_impl_local(seq, bstart, bend, gpu_blocks, dp_client_id, cpu_only, prefetch)
@@ -427,10 +438,23 @@ class GlobalCacheEngine:
                     # the full-KV plan fell short of the snapshot's position: the snapshot is useless
                     self._discard_plan(plan)
                     return self._empty(token_mask)
-                op = self.swa_ops.build_get_chain(plan.graph, swa_src[1], dp_client_id)
+                src_eng, src_node, src_slot, _ = swa_src
+                host_slot, stage_in = src_slot, None
+                if src_eng is not self.cpu_cache_engine:
+                    # SSD snapshot: staged through a host slot that the plan gives back at its end
+                    host_slot = self.cpu_cache_engine.alloc_swa_slot()
+                    if host_slot is None:
+                        self._discard_plan(plan)
+                        return self._empty(token_mask)
+                    stage_in = self.swa_ops.build_swa_op(plan.graph, TransferType.DISK2H, [src_slot], [host_slot],
+                                                         dp_client_id)
+                    plan.swa_pending[stage_in.op_id] = host_slot
+                op = self.swa_ops.build_get_chain(plan.graph, host_slot, dp_client_id)
                 if op is not None:
-                    self.cpu_cache_engine.index.lock_swa(swa_src[0])
-                    plan.swa_locked.append(swa_src[0])
+                    if stage_in is not None:
+                        plan.graph.add_dependency(op.op_id, stage_in.op_id)
+                    src_eng.index.lock_swa(src_node)
+                    plan.swa_locked.append((src_eng, src_node))
                     plan.finished_ops_ids = list(plan.finished_ops_ids) + [op.op_id]
             graph, handle, cbs, end_op = self._finish(plan, is_put=False)
         mask = np.zeros_like(token_mask, dtype=np.bool_)
@@ -722,14 +746,34 @@ class GlobalCacheEngine:
                     swa_op = graph.get_op(chain.d2h_id)
                     plan.swa_pending[chain.d2h_id] = slot
 
-                    def _mount(node=cpu_node, slot=slot, op=swa_op, oid=chain.d2h_id):
+                    # write-through to the SSD window tier, onto the SSD node this put created
+                    ssd_slot, disk_op = None, None
+                    if ssd is not None and ssd.swa_enabled and plan.inserted.get(DeviceType.SSD):
+                        ssd_slot = ssd.alloc_swa_slot()
+                        if ssd_slot is not None:
+                            disk_op = self.swa_ops.build_swa_op(graph, TransferType.H2DISK, [slot], [ssd_slot],
+                                                                dp_client_id)
+                            graph.add_dependency(disk_op.op_id, chain.d2h_id)
+                            plan.swa_pending_ssd[disk_op.op_id] = ssd_slot
+
+                    def _mount(node=cpu_node, slot=slot, op=swa_op, oid=chain.d2h_id, chained=disk_op is not None):
                         plan.swa_pending.pop(oid, None)
                         if op.transfer_type == TransferType.VIRTUAL or not cpu.index.alive(node):
                             cpu.swa_pool.free(slot)
-                        else:
-                            cpu.mount_swa(node, slot)
+                        elif cpu.mount_swa(node, slot) and chained:
+                            # the slot feeds the SSD write: it must not be evicted and reused before that ends
+                            cpu.index.lock_swa(node)
+                            plan.swa_locked.append((cpu, node))
                     plan.op_callback_dict[chain.d2h_id] = _mount
                     plan.finished_ops_ids = list(plan.finished_ops_ids) + [chain.d2h_id]
+                    if disk_op is not None:
+                        def _mount_ssd(node=plan.inserted[DeviceType.SSD][-1], s_=ssd_slot, op=disk_op):
+                            plan.swa_pending_ssd.pop(op.op_id, None)
+                            if op.transfer_type == TransferType.VIRTUAL or not ssd.index.alive(node):
+                                ssd.swa_pool.free(s_)
+                            else:
+                                ssd.mount_swa(node, s_)
+                        plan.op_callback_dict[disk_op.op_id] = _mount_ssd
         plan.skipped_gpu_blocks = cpu_matched
         plan.num_gpu_blocks_to_transfer = need_cpu
         return plan
@@ -813,12 +857,16 @@ class GlobalCacheEngine:
 
     def _release_swa(self, plan: TransferPlan) -> None:
         cpu = self.cpu_cache_engine
-        for node in plan.swa_locked:
-            cpu.index.unlock_swa(node)
+        for eng, node in plan.swa_locked:
+            if eng.index.alive(node):
+                eng.index.unlock_swa(node)
         plan.swa_locked = []
-        for slot in plan.swa_pending.values():      # side ops that never completed
+        for slot in plan.swa_pending.values():      # side ops that never completed, staging slots of gets
             cpu.swa_pool.free(slot)
         plan.swa_pending = {}
+        for slot in plan.swa_pending_ssd.values():
+            self.ssd_cache_engine.swa_pool.free(slot)
+        plan.swa_pending_ssd = {}
 
     def _release_peer(self, plan: TransferPlan) -> None:
         if plan.peer_leases is not None and self.peer_directory is not None:

@@ -13,7 +13,7 @@ from __future__ import annotations
 import json
 import os
 from argparse import Namespace
-from dataclasses import dataclass, field, fields
+from dataclasses import replace, dataclass, field, fields
 from typing import Any, Dict, List, Optional, Tuple, Union
 
 import torch
@@ -224,7 +224,7 @@ class SWAPoolConfig:
     (reference: flexkv/common/config.py:573-620)."""
     enabled: bool = False
     num_slots: int = 1024              # host slots
-    num_ssd_slots: int = 0             # accepted; an SSD window tier is not built
+    num_ssd_slots: int = 0             # SSD window tier (0 = none): snapshots written through beside the SSD blocks
     num_remote_slots: int = 0          # accepted; a remote window tier is not built
     num_swa_layers: int = 61
     bytes_per_token_per_layer: int = 584
@@ -240,7 +240,13 @@ class SWAPoolConfig:
 
     def for_cache_tier(self, device_type) -> Optional["SWAPoolConfig"]:
         name = getattr(device_type, "name", str(device_type))
-        return self if (self.enabled and name == "CPU") else None
+        if not self.enabled:
+            return None
+        if name == "CPU":
+            return self
+        if name == "SSD" and self.num_ssd_slots > 0:
+            return replace(self, num_slots=self.num_ssd_slots, pin_memory=False)
+        return None
 
 
 @dataclass

@@ -220,14 +220,18 @@ class TransferOpGraph:
         """Binds the GPU side of sliding-window side ops to the caller's window pages. With
         ``None`` the side ops are turned into no-ops (the caller moves no window state)."""
         for op in self._ops.values():
-            if not op.is_swa or op.gpu_side is None:
+            if not op.is_swa:
                 continue
-            n = int(op.dst_block_ids.size if op.gpu_side == "src" else op.src_block_ids.size)
-            if page_ids is None:
+            if page_ids is None and (op.gpu_side is not None or
+                                     op.transfer_type in (TransferType.H2DISK, TransferType.DISK2H)):
+                # the whole window chain goes, tier-to-tier hops included: their source never arrives
                 op.transfer_type = TransferType.VIRTUAL
                 op.src_block_ids = op.dst_block_ids = _EMPTY
                 op.gpu_side = None
                 continue
+            if op.gpu_side is None:
+                continue
+            n = int(op.dst_block_ids.size if op.gpu_side == "src" else op.src_block_ids.size)
             ids = _ids(page_ids)
             if ids.size < n:
                 raise ValueError(f"window side op needs {n} page(s), {ids.size} given")
@@ -427,4 +431,9 @@ def merge_to_batch_graph(graphs: List[TransferOpGraph], layerwise: bool = False,
         clone.merged_from = [op.op_id]
         remap[op.op_id] = clone.op_id
         merged.add_transfer_op(clone)
+    # a window chain (tier hop, then the GPU copy) keeps its order inside the merged graph
+    for op in swa_ops:
+        for pred in op.predecessors:
+            if pred in remap and remap[pred] != remap[op.op_id]:
+                merged.add_dependency(remap[op.op_id], remap[pred])
     return merged, remap

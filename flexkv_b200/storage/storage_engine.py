@@ -105,6 +105,7 @@ class StorageEngine:
         self.swa_regs: Dict[WorkerKey, Dict[int, GpuRegistration]] = {}
         self.gpu_group_regs: Dict[WorkerKey, Dict[int, Dict[int, GpuRegistration]]] = {}
         self.swa_host: Optional[SwaPool] = None
+        self.swa_ssd: Optional[SsdPool] = None
         self._cuda_register = torch.cuda.is_available() if cuda_register is None else cuda_register
         self._numa_node = numa_node
         if cache_config.enable_cpu:
@@ -290,7 +291,12 @@ class StorageEngine:
                     ssd_layer_stride=ssd_layer, ssd_kv_stride=ssd_kv, ssd_block_stride=self.ssd.block_bytes,
                     chunk_bytes=h.chunk_bytes, num_layers=L, kv_dim=h.layout.kv_dim, block_first=bf)
 
-    # ---- GPU ----------------------------------------------------------------------
+    def swa_ssd_layout_dict(self) -> Dict[str, Any]:
+        """A window slot is one run of bytes on both sides."""
+        b = self.swa_ssd.block_bytes
+        return dict(cpu_layer_stride=b, cpu_kv_stride=0, cpu_block_stride=b, ssd_layer_stride=b, ssd_kv_stride=0,
+                    ssd_block_stride=b, chunk_bytes=b, num_layers=1, kv_dim=1, block_first=True)
+
     # ---- sliding-window side pool ------------------------------------------------------
     def register_swa_blocks(self, reg: GpuRegistration) -> None:
         """GPU window pages of one rank: ``num_layers`` tensors of [pages, page_bytes]."""
@@ -312,6 +318,15 @@ class StorageEngine:
                                              cuda_register=self._cuda_register and cfg.pin_memory,
                                              register_chunk_bytes=0, backing_file="")
         self.swa_host = SwaPool(region, cfg.num_slots, ranks * rank_slot, rank_slot, reg.chunk_bytes)
+        if cfg.num_ssd_slots > 0 and self.cache_config.enable_ssd:
+            # SSD window tier: one file of whole slots in the first cache directory
+            d = parse_path_list(self.cache_config.ssd_cache_dir or [])[0]
+            os.makedirs(d, exist_ok=True)
+            path = os.path.join(d, f"flexkv_swa_cache_{os.getpid()}.bin")
+            engine = _native.C.SsdIoEngine([[path]], ranks * rank_slot, cfg.num_ssd_slots, create=True,
+                                           try_direct=True, iouring_entries=self.env.iouring_entries,
+                                           num_threads=2)
+            self.swa_ssd = SsdPool(engine, [[path]], ranks * rank_slot, cfg.num_ssd_slots, cfg.num_ssd_slots)
         flexkv_logger.info("window pool: %d slots x %d B (%d layers x %d B per rank, %d rank(s))", cfg.num_slots,
                            ranks * rank_slot, reg.num_layers, reg.chunk_bytes, ranks)
 
@@ -350,6 +365,14 @@ class StorageEngine:
             except Exception:  # noqa: BLE001
                 pass
             self.swa_host = None
+        if self.swa_ssd is not None:
+            files = [f for d in self.swa_ssd.files for f in d]
+            self.swa_ssd = None
+            for f in files:
+                try:
+                    os.unlink(f)
+                except OSError:
+                    pass
         if self.ssd is not None:
             files = [f for d in self.ssd.files for f in d]
             self.ssd = None

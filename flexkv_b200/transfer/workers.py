@@ -538,6 +538,8 @@ class SwaWorker(TransferWorker):
 
     def execute(self, op: TransferOp) -> OpOutcome:
         h2d = op.transfer_type == TransferType.H2D
+        if op.transfer_type in (TransferType.H2DISK, TransferType.DISK2H):
+            return self._disk(op)
         if op.transfer_type not in (TransferType.H2D, TransferType.D2H):
             return OpOutcome(False, error=f"window ops on {op.transfer_type.value} are not built")
         slots, pages = (op.src_block_ids, op.dst_block_ids) if h2d else (op.dst_block_ids, op.src_block_ids)
@@ -586,6 +588,22 @@ class SwaWorker(TransferWorker):
                 self._status[dev].zero_()
         return OpOutcome(status == 0, gpu_ms=ms, num_bytes=nbytes,
                          error="" if status == 0 else f"window copy status 0x{status:x}")
+
+
+    def _disk(self, op: TransferOp) -> OpOutcome:
+        """Host window slots <-> slots of the SSD window file (whole slots, the SSD tier's IO engine)."""
+        st = self.storage
+        if st.swa_ssd is None or st.swa_host is None:
+            return OpOutcome(False, error="window op on the SSD tier but no SSD window pool is configured")
+        read = op.transfer_type == TransferType.DISK2H
+        host, disk = (op.dst_block_ids, op.src_block_ids) if read else (op.src_block_ids, op.dst_block_ids)
+        if host.size != disk.size or host.size == 0:
+            return OpOutcome(False, error=f"window disk op with {host.size} host and {disk.size} SSD slots")
+        nfail, ok = st.swa_ssd.engine.transfer(st.swa_host.base, np.ascontiguousarray(host, dtype=np.int64),
+                                               np.ascontiguousarray(disk, dtype=np.int64), read,
+                                               st.swa_ssd_layout_dict(), 0, 1)
+        return OpOutcome(nfail == 0, num_bytes=int(len(ok) - nfail) * st.swa_ssd.block_bytes,
+                         error="" if nfail == 0 else f"{nfail} window slot(s) failed")
 
 
 class PeerHostWorker(TransferWorker):

@@ -128,3 +128,76 @@ def test_slot_pool():
     assert p.num_free == 1 and p.allocate() == 1
     p.reset()
     assert p.num_free == 3
+
+
+def start_tiered(tmp_path, num_slots=4, num_ssd_slots=8, device="cpu"):
+    shape = KVShape("s", 2, 2, 16, tokens_per_block=T)
+    cfg = CacheConfig(tokens_per_block=T, num_cpu_blocks=32, enable_ssd=True, num_ssd_blocks=64,
+                      ssd_cache_dir=str(tmp_path), enable_swa_transfer=True,
+                      swa=SWAPoolConfig(enabled=True, num_slots=num_slots, num_ssd_slots=num_ssd_slots,
+                                        num_swa_layers=SWA_LAYERS, bytes_per_token_per_layer=PAGE_BYTES // T,
+                                        evict_ratio=0.25))
+    mgr = KVManager(make_model_config(shape), cfg, require_gpu=True)
+    dev = "cpu" if device == "cpu" else torch.device(device)
+    kv, layout = alloc_paged_cache(shape, 64, dev, "vllm", fill="normal", seed=5)
+    mgr.register_gpu_tensors(kv, layout)
+    g = torch.Generator().manual_seed(9)
+    swa = [torch.randint(0, 256, (16, PAGE_BYTES), dtype=torch.uint8, generator=g).to(dev) for _ in range(SWA_LAYERS)]
+    mgr.register_swa_tensors(swa)
+    mgr.start(); mgr.wait_ready(30)
+    return mgr, kv, swa
+
+
+@pytest.mark.parametrize("device", ["cpu", pytest.param("cuda:0", marks=pytest.mark.gpu)])
+def test_ssd_window_tier_serves_the_snapshot_after_the_host_copy_is_gone(tmp_path, device):
+    """A put writes the window page through to the SSD window file and mounts it on the SSD node; once the
+    host tier has lost the sequence, a window-aware get reads full KV and the page back from SSD."""
+    mgr, kv, swa = start_tiered(tmp_path, device=device)
+    try:
+        gce = mgr.kv_task_engine.cache_engine
+        cpu, ssd = gce.cpu_cache_engine, gce.ssd_cache_engine
+        tok = np.arange(5 * T, dtype=np.int64) + 700
+        src = np.array([3, 9, 1, 30, 12])
+        tid, mask = mgr.put_match(tok)
+        kinds = sorted((o.transfer_type.value, o.is_swa) for o in mgr.kv_task_engine.tasks[tid].graph.ops()
+                       if o.transfer_type.value != "Virtual")
+        assert kinds == [("D2H", False), ("D2H", True), ("H2DISK", False), ("H2DISK", True)]
+        mgr.launch(tid, slots(src), swa_slot_mappings=[slots([5])])
+        assert mgr.wait(tid, completely=True)[tid].status.value == "success"
+        assert cpu.index.total_swa_slots() == 1 and ssd.index.total_swa_slots() == 1
+        assert cpu.swa_pool.num_used == 1 and ssd.swa_pool.num_used == 1
+        want_page = [t[5].clone() for t in swa]
+        want_kv = [t[:, src].clone() for t in kv]
+        from flexkv_b200.common.block import SequenceMeta
+        m = cpu.match(SequenceMeta(tok, T))
+        assert cpu.index.swa_lock_cnt(m.last_swa_node) == 0          # the write-through lock is gone
+        # the host tier forgets everything (its snapshot slot comes back), the SSD tier keeps both
+        mgr._clear_cpu_cache()
+        assert cpu.swa_pool.num_used == 0 and ssd.index.total_swa_slots() == 1
+        tid, mask = mgr.get_match(tok, swa_aware=True)
+        assert int(mask.sum()) == 5 * T
+        kinds = sorted((o.transfer_type.value, o.is_swa) for o in mgr.kv_task_engine.tasks[tid].graph.ops()
+                       if o.transfer_type.value != "Virtual")
+        assert kinds == [("DISK2H", False), ("DISK2H", True), ("H2D", False), ("H2D", True)]
+        dst = np.arange(40, 45)
+        for t in kv:
+            t[:, dst] = 0
+        for t in swa:
+            t[11] = 0
+        mgr.launch(tid, slots(dst), swa_slot_mappings=[slots([11])])
+        assert mgr.wait(tid)[tid].status.value == "success"
+        for l in range(2):
+            assert torch.equal(kv[l][:, dst], want_kv[l])
+        for l in range(SWA_LAYERS):
+            assert torch.equal(swa[l][11], want_page[l])
+        assert cpu.swa_pool.num_used == 0                               # the staging slot went back
+        ms = ssd.match(SequenceMeta(tok, T))
+        assert ssd.index.swa_lock_cnt(ms.last_swa_node) == 0
+        # a launch without window pages drops the whole chain, SSD hop included
+        tok2 = tok + 1
+        tid, mask = mgr.put_match(tok2)
+        mgr.launch(tid, slots([20, 21, 22, 23, 24]))
+        assert mgr.wait(tid, completely=True)[tid].status.value == "success"
+        assert ssd.swa_pool.num_used == 1 and ssd.index.total_swa_slots() == 1
+    finally:
+        mgr.shutdown()
