@@ -13,6 +13,7 @@
 #include "kernels/kv_hash.h"
 #include "ce_copy.h"
 #include "ipc.h"
+#include "vmm_handle.h"
 
 namespace py = pybind11;
 using namespace fkv;
@@ -117,6 +118,34 @@ void init_kernel_bindings(py::module_& m) {
   });
   m.def("ipc_import", &ipc_import);
   m.def("ipc_close", &ipc_close);
+
+  // Memory from the virtual-memory API (cuMemCreate): shareable handles instead of legacy IPC
+  m.def("vmm_is_vmm_pointer", &vmm_is_vmm_pointer);
+  m.def("vmm_export", [](uint64_t ptr, bool prefer_fabric) {
+    VmmExport e = vmm_export(ptr, prefer_fabric);
+    py::dict d;
+    d["kind"] = e.kind == VmmHandleKind::FABRIC ? "fabric" : "posix_fd";
+    d["fd"] = e.fd;
+    d["fabric"] = py::bytes(e.fabric);
+    d["base"] = e.base;
+    d["size"] = e.size;
+    d["offset"] = e.offset;
+    return d;
+  }, py::arg("device_ptr"), py::arg("prefer_fabric") = true);
+  m.def("vmm_import_fd", [](int fd, uint64_t size, int device) {
+    VmmMapping mp = vmm_import_fd(fd, size, device);
+    return py::make_tuple(mp.va, mp.size);
+  });
+  m.def("vmm_import_fabric", [](const std::string& fabric, uint64_t size, int device) {
+    VmmMapping mp = vmm_import_fabric(fabric, size, device);
+    return py::make_tuple(mp.va, mp.size);
+  });
+  m.def("vmm_unmap", &vmm_unmap);
+  m.def("vmm_alloc", [](uint64_t bytes, int device, bool fabric) {
+    VmmMapping mp = vmm_alloc(bytes, device, fabric);
+    return py::make_tuple(mp.va, mp.size);
+  }, py::arg("bytes"), py::arg("device"), py::arg("fabric") = false);
+  m.def("vmm_free", &vmm_free);
 
   // Batched block keys on the GPU; every pointer is a device (or mapped host) address.
   m.def("kv_block_hashes", [](uint64_t tokens, uint64_t offsets, int64_t num_seqs, int tokens_per_block, uint64_t ns,

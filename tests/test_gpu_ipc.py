@@ -23,14 +23,15 @@ def slots(blocks):
     return np.repeat(np.asarray(blocks, dtype=np.int64), T) * T + np.tile(np.arange(T), len(blocks))
 
 
-def test_manager_moves_blocks_of_a_cache_owned_by_another_process(tmp_path):
+@pytest.mark.parametrize("alloc", ["cuda_ipc", "vmm"])
+def test_manager_moves_blocks_of_a_cache_owned_by_another_process(tmp_path, alloc):
     reg = unique_ipc_endpoint("ipcreg")
     shape = KVShape("ipc", 4, 4, 64, tokens_per_block=T)
     mgr = KVManager(make_model_config(shape), CacheConfig(tokens_per_block=T, num_cpu_blocks=32),
                     gpu_register_port=reg, require_gpu=True)
     mgr.start()
     child = subprocess.Popen([sys.executable, os.path.join(HERE, "mp_workers", "ipc_engine_worker.py"), reg,
-                              str(tmp_path)], stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+                              str(tmp_path), alloc], stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
     try:
         mgr.wait_ready(120)
         tok = np.arange(5 * T, dtype=np.int64)
