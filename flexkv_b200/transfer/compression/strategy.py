@@ -61,8 +61,9 @@ class Fp8BlockScaleStrategy(CompressionStrategy):
 
 
 class ExponentPackStrategy(CompressionStrategy):
-    """Lossless bf16 codec: sign+mantissa bytes stay raw, exponents are re-coded per
-    tile with a 16-entry dictionary (about 0.75x bytes on unit-normal data)."""
+    """Lossless bf16 codec: sign+mantissa bytes stay raw, every group of 128 values stores its
+    largest exponent once and each value's distance to it in w bits, w chosen per group
+    (about 0.75x bytes on unit-normal data)."""
     name = "bf16_xp"
     TILE_ELEMS = 8192
     TILE_SLOT = 2 * TILE_ELEMS + 128
