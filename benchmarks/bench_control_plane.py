@@ -101,7 +101,6 @@ def bench_index(a):
 
 
 def bench_planner(a):
-    import torch
     from flexkv_b200 import CacheConfig, KVManager
     from flexkv_b200.models import alloc_paged_cache, KVShape, make_model_config
     shape = KVShape("tiny", 1, 1, 8, tokens_per_block=T)     # 256 B blocks: the data plane costs nothing

@@ -19,7 +19,6 @@ import tempfile
 import time
 
 import numpy as np
-import torch
 
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 from flexkv_b200 import CacheConfig, KVManager  # noqa: E402

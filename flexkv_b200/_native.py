@@ -8,7 +8,6 @@ from __future__ import annotations
 
 import importlib
 import os
-import sys
 
 
 def _load():

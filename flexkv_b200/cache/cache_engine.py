@@ -20,7 +20,7 @@ import numpy as np
 from .. import _native
 from ..common.block import SequenceMeta
 from ..common.config import GLOBAL_CONFIG_FROM_ENV, CacheConfig, ModelConfig
-from ..common.debug import EvictionLogAggregator, flexkv_logger
+from ..common.debug import EvictionLogAggregator
 from ..common.transfer import DeviceType, TransferOp, TransferOpGraph, TransferType
 from . import persist
 from .mempool import Mempool, NotEnoughSpaceError

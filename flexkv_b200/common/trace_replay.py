@@ -14,7 +14,7 @@ from __future__ import annotations
 import argparse
 import json
 import time
-from typing import Any, Dict, Iterable, List, Optional
+from typing import Any, Dict, Iterable, Optional
 
 import numpy as np
 import torch

@@ -9,7 +9,7 @@ import json
 import os
 import threading
 import time
-from typing import Any, List, Optional
+from typing import List, Optional
 
 import numpy as np
 

@@ -10,10 +10,9 @@ many tasks into one op per tier hop (flexkv/common/transfer.py:761-1042).
 from __future__ import annotations
 
 import itertools
-import threading
 from dataclasses import dataclass, field
 from enum import Enum, IntEnum
-from typing import Callable, Dict, Iterable, List, NamedTuple, Optional, Sequence, Set, Tuple
+from typing import Dict, Iterable, List, NamedTuple, Optional, Sequence, Set, Tuple
 
 import numpy as np
 

@@ -5,13 +5,12 @@ with the real classes and with stand-ins in tests."""
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Any, List, Optional
+from typing import Any, Optional
 
 import torch
 
 from ..common.config import (NVFP4_NAMES, CacheConfig, ModelConfig, UserConfig, load_user_config_from_env,
                              nvfp4_head_bytes, parse_dtype, update_default_config_from_user_config)
-from ..common.debug import flexkv_logger
 
 
 def _attr(obj: Any, *names: str, default: Any = None) -> Any:

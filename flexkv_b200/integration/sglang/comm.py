@@ -14,9 +14,7 @@ that layer's eventfd of the consumer set once per restore in flight
 from __future__ import annotations
 
 import os
-import pickle
 import select
-import struct
 import threading
 import time
 from typing import Any, Dict, List, Optional

@@ -11,16 +11,13 @@ from __future__ import annotations
 
 import atexit
 import os
-import signal
-import time
-from dataclasses import dataclass, field
-from typing import Any, Dict, List, Optional, Sequence, Tuple
+from dataclasses import dataclass
+from typing import Any, Dict, List, Optional, Sequence
 
 import numpy as np
 import torch
 
 from ...common.config import GLOBAL_CONFIG_FROM_ENV
-from ...common.debug import flexkv_logger
 from ...common.request import KVResponseStatus
 from ...common.storage import KVCacheLayout, KVCacheLayoutType
 from ..config import FlexKVConfig

@@ -27,7 +27,6 @@ from typing import Any, Dict, Iterable, List, Optional, Sequence, Set, Tuple
 import numpy as np
 import torch
 
-from ...common.config import GLOBAL_CONFIG_FROM_ENV
 from ...common.debug import flexkv_logger
 from ...common.request import KVResponseStatus
 from ...common.storage import KVCacheLayout, KVCacheLayoutType

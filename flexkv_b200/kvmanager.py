@@ -8,7 +8,6 @@ this process. With ``dp_size > 1``, several engine instances or
 """
 from __future__ import annotations
 
-import os
 import time
 from typing import Dict, List, Optional, Sequence, Tuple, Union
 

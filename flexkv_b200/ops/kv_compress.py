@@ -2,9 +2,8 @@
 the format) — launcher and a bit-exact PyTorch reference of the packed bytes."""
 from __future__ import annotations
 
-from typing import Any, List, Optional, Tuple
+from typing import Any, List, Optional
 
-import numpy as np
 import torch
 
 from .. import _native

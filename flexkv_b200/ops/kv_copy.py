@@ -9,7 +9,7 @@ module must be present.
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Any, Dict, List, Optional, Sequence, Union
+from typing import Any, Dict, List, Optional
 
 import numpy as np
 import torch

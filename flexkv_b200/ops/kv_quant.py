@@ -8,7 +8,6 @@ from __future__ import annotations
 
 from typing import Any, List, Optional, Tuple
 
-import numpy as np
 import torch
 
 from .. import _native

@@ -12,7 +12,7 @@ from __future__ import annotations
 
 import threading
 from collections import defaultdict
-from typing import Dict, List, Optional, Set, Tuple
+from typing import Dict, List, Set, Tuple
 
 import numpy as np
 

@@ -22,7 +22,7 @@ from .. import _native
 from ..common.config import GLOBAL_CONFIG_FROM_ENV, CacheConfig, ModelConfig, parse_path_list
 from ..common.debug import flexkv_logger
 from ..common.storage import GroupLayout, KVCacheLayout, KVCacheLayoutType
-from ..common.transfer import DeviceType, WorkerKey
+from ..common.transfer import WorkerKey
 from .gpu_layout import GpuRegistration
 
 QUANT_GROUP = 128     # values per fp32 scale of the block-scaled fp8 host format

@@ -9,7 +9,7 @@ second pass, the copy kernel itself reads GPU pages and writes packed host tiles
 """
 from __future__ import annotations
 
-from typing import Any, Dict, Optional
+from typing import Any, Dict
 
 from ... import _native
 

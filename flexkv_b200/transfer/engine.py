@@ -15,11 +15,8 @@ from __future__ import annotations
 
 import queue
 import threading
-import time
-from dataclasses import dataclass
-from typing import Any, Callable, Dict, List, Optional, Tuple
+from typing import Dict, List, Optional, Tuple
 
-import numpy as np
 
 from ..common.config import GLOBAL_CONFIG_FROM_ENV, CacheConfig, ModelConfig
 from ..common.debug import flexkv_logger

@@ -21,7 +21,6 @@ import struct
 import threading
 from typing import Callable, Dict, List, Optional, Sequence
 
-import numpy as np
 
 from .. import _native
 from ..common.config import GLOBAL_CONFIG_FROM_ENV

@@ -15,7 +15,7 @@ import queue
 import threading
 import time
 from dataclasses import dataclass
-from typing import Any, Callable, Dict, List, Optional, Tuple
+from typing import Callable, Dict, Optional, Tuple
 
 import numpy as np
 
@@ -23,7 +23,7 @@ from .. import _native
 from ..common.config import GLOBAL_CONFIG_FROM_ENV, CacheConfig, ModelConfig
 from ..common.debug import flexkv_logger
 from ..common.storage import KVCacheLayoutType
-from ..common.transfer import LayerwiseTransferOp, TransferOp, TransferType, WorkerKey
+from ..common.transfer import TransferOp, TransferType, WorkerKey
 
 
 @dataclass

@@ -14,7 +14,7 @@ from __future__ import annotations
 import os
 import threading
 import time
-from typing import Any, List, Optional
+from typing import List, Optional
 
 from .common.config import CacheConfig, ModelConfig
 from .common.debug import flexkv_logger
