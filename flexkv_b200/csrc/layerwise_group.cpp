@@ -49,7 +49,7 @@ LayerwiseGroup::LayerwiseGroup(std::vector<GpuSide> gpus, HostSide host, Layerwi
 
 LayerwiseGroup::LayerwiseGroup(std::vector<LayerwiseMemberGroup> groups, std::vector<std::vector<LayerMember>> members,
                                HostSide host_block, LayerwiseOptions opt)
-    : host_(host_block), opt_(opt), mgroups_(std::move(groups)), members_(std::move(members)) {
+    : host_(host_block), mgroups_(std::move(groups)), members_(std::move(members)), opt_(opt) {
   if (mgroups_.empty() || members_.empty()) throw std::invalid_argument("LayerwiseGroup: no layer groups or no layers");
   const size_t R = mgroups_[0].gpus.size();
   for (const auto& g : mgroups_) {
