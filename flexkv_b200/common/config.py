@@ -231,12 +231,23 @@ class SWAPoolConfig:
     multi_group: bool = False
     evict_ratio: float = 0.1           # share of the pool freed when it runs full
     pin_memory: bool = True
+    # state that rides in the same slot as the window KV (e.g. compressor states of an indexer): one
+    # (num_layers, page_bytes_per_layer) pair per sidecar group; the group's tensors are registered with
+    # group_id = 1 + its position here
+    sidecar_groups: List[Tuple[int, int]] = field(default_factory=list)
+    # engine ranks register their window pages from other processes: start-up waits for all of them
+    wait_for_registration: bool = False
 
     def page_bytes_per_layer(self, tokens_per_block: int) -> int:
         return int(tokens_per_block) * int(self.bytes_per_token_per_layer)
 
     def slot_bytes(self, tokens_per_block: int) -> int:
-        return self.page_bytes_per_layer(tokens_per_block) * int(self.num_swa_layers)
+        return sum(n * b for n, b in self.group_geometry(tokens_per_block))
+
+    def group_geometry(self, tokens_per_block: int) -> List[Tuple[int, int]]:
+        """(layers, page bytes per layer) of the window KV followed by the sidecar groups."""
+        return [(int(self.num_swa_layers), self.page_bytes_per_layer(tokens_per_block))] + \
+            [(int(n), int(b)) for n, b in self.sidecar_groups]
 
     def for_cache_tier(self, device_type) -> Optional["SWAPoolConfig"]:
         name = getattr(device_type, "name", str(device_type))

@@ -23,6 +23,8 @@ from ...common.storage import KVCacheLayout, KVCacheLayoutType
 from ..config import FlexKVConfig
 from ..stats import FlexKVStats
 from .comm import FlexKVComm, FlexKVLayerDoneCounter
+from .pools import (ResolvedPool, build_swa_slot_mapping, layer_group_specs, resolve_kv_pool,
+                    window_pool_config)
 
 
 @dataclass
@@ -74,8 +76,8 @@ class FlexKVConnector:
         atexit.register(self.shutdown)
 
     # ---- start-up ---------------------------------------------------------------------
-    def register_kv_buffers(self, k_buffers: Sequence[torch.Tensor], v_buffers: Optional[Sequence[torch.Tensor]] = None
-                            ) -> None:
+    def register_kv_buffers(self, k_buffers: Sequence[torch.Tensor], v_buffers: Optional[Sequence[torch.Tensor]] = None,
+                            group_id: int = -1) -> None:
         use_mla = v_buffers is None or self.cfg.model_config.use_mla
         layout = sglang_gpu_layout(k_buffers, self.T, use_mla)
         # every rank must agree on the number of pages it can address
@@ -83,7 +85,80 @@ class FlexKVConnector:
         layout = layout._replace(num_block=nb)
         tensors = list(k_buffers) + ([] if use_mla else list(v_buffers))
         if self._client is not None:
-            self._client.register_to_server(tensors, layout)
+            self._client.register_to_server(tensors, layout, group_id=group_id)
+
+    @staticmethod
+    def configure_for_pool(flexkv_config: FlexKVConfig, kvcache: Any, page_size: int,
+                           include_state: Optional[bool] = None) -> ResolvedPool:
+        """Call BEFORE constructing the connector: reads the engine's KV pool object and, when it is made of
+        several layer groups (indexer keys beside the cache, split compressed pools) or carries a
+        sliding-window pool, writes the matching ``layer_groups`` / window-pool geometry into the config and
+        sizes the tiers again for the new block size (flexkv/integration/sglang/connector.py:1840-1874).
+        ``include_state=False`` leaves the compressor-state sidecars out of the window slot."""
+        import dataclasses
+        from ...common.config import recompute_block_counts
+        pool = resolve_kv_pool(kvcache, page_size, include_state)
+        specs = layer_group_specs(pool, page_size)
+        if specs is not None and flexkv_config.model_config.layer_groups is None:
+            m = dataclasses.replace(flexkv_config.model_config, layer_groups=specs)     # the old one may be frozen
+            m.freeze()
+            flexkv_config.model_config = m
+            recompute_block_counts(m, flexkv_config.cache_config)
+        swa = window_pool_config(pool, page_size, flexkv_config.cache_config.swa)
+        if swa is not None:
+            flexkv_config.cache_config.swa = swa
+            flexkv_config.cache_config.enable_swa_transfer = True
+        return pool
+
+    def register_kv_pool(self, kvcache: Any, pool: Optional[ResolvedPool] = None) -> ResolvedPool:
+        """Registers everything this rank holds of the engine's KV pool: the plain K/V (or MLA) buffers, every
+        layer group of a multi-group pool, the window pages and their sidecar groups."""
+        pool = pool if pool is not None else resolve_kv_pool(kvcache, self.T)
+        self._kvcache = kvcache
+        if not pool.multi_group:
+            self.register_kv_buffers(pool.k_buffers, pool.v_buffers)
+            return pool
+        gid = 0
+        if pool.kind == "indexer":
+            self.register_kv_buffers(pool.k_buffers, pool.v_buffers, group_id=0)
+            gid = 1
+        for g in pool.groups:
+            b0 = g.buffers[0]
+            page_bytes = b0.shape[1] * b0.element_size()
+            nb = self.comm.all_reduce_min(int(b0.shape[0]))
+            layout = KVCacheLayout(KVCacheLayoutType.LAYERFIRST, len(g.buffers), nb, g.sub_page_size, 1,
+                                   page_bytes // g.sub_page_size, is_mla=True)
+            if self._client is not None:
+                self._client.register_to_server([b.view(torch.uint8) for b in g.buffers], layout, group_id=gid)
+            gid += 1
+        if pool.swa_buffers and self._client is not None:
+            self._client.register_swa_to_server(pool.swa_buffers, group_id=0)
+            for i, g in enumerate(pool.state_groups):
+                self._client.register_swa_to_server(g.buffers, group_id=1 + i)
+        return pool
+
+    def _window_aware(self) -> bool:
+        kvcache = getattr(self, "_kvcache", None)
+        return kvcache is not None and getattr(kvcache, "swa_kv_pool", None) is not None
+
+    def _window_page(self, slot_mapping: np.ndarray):
+        """The window page of the sequence end, as the one-page slot mapping that ``launch`` binds the window
+        side ops to (None: the engine keeps no window state, or the tail slid out of the window)."""
+        if not self._window_aware() or len(slot_mapping) < self.T:
+            return None
+        m = self.swa_slot_mapping(slot_mapping)
+        if m is None or len(m) < self.T:
+            return None
+        return [np.asarray(m[-self.T:], dtype=np.int64)]
+
+    def swa_slot_mapping(self, full_indices: Any) -> Optional[np.ndarray]:
+        """Window-pool slots for ``launch(..., swa_slot_mappings=...)``; None when the engine has no window pool
+        or none of the tokens is still inside the window."""
+        kvcache = getattr(self, "_kvcache", None)
+        if kvcache is None:
+            return None
+        m = build_swa_slot_mapping(kvcache, torch.as_tensor(full_indices))
+        return None if m is None else m.numpy()
 
     def register_layer_transfer_counter(self, kvcache: Any) -> None:
         """Installs the per-layer wait hook on SGLang's KV pool object."""
@@ -112,7 +187,8 @@ class FlexKVConnector:
             if aligned > num_computed_tokens:
                 mask = np.zeros(aligned, dtype=np.bool_)
                 mask[num_computed_tokens:] = True
-                tid, m = self.mgr.get_match(tok[:aligned], mask, namespace=namespace)
+                tid, m = self.mgr.get_match(tok[:aligned], mask, namespace=namespace,
+                                            swa_aware=self._window_aware())
                 matched = int(m.sum())
                 if matched == 0:
                     self.mgr.cancel(tid)
@@ -137,7 +213,7 @@ class FlexKVConnector:
             p = self._pending_loads.pop(rid, None)
             if p is not None:
                 sm = torch.as_tensor(slot_mapping).cpu().numpy().astype(np.int64)[:p.matched_tokens]
-                self.mgr.launch(p.task_id, sm)
+                self.mgr.launch(p.task_id, sm, swa_slot_mappings=self._window_page(sm))
                 rsp = self.mgr.wait(p.task_id, timeout=timeout)[p.task_id]
                 done = p.matched_tokens if rsp.status == KVResponseStatus.SUCCESS else 0
                 if not done:
@@ -188,7 +264,7 @@ class FlexKVConnector:
                 if moved == 0:
                     self.mgr.cancel(tid)
                 else:
-                    self.mgr.launch(tid, sm[mask])
+                    self.mgr.launch(tid, sm[mask], swa_slot_mappings=self._window_page(sm))
                     self._stores[rid] = tid
                 self.stats.record_put(aligned, moved)
         return int(self.comm.broadcast(moved))

@@ -387,6 +387,16 @@ class FlexKVConnectorV1Impl:
     def register_kv_caches(self, kv_caches: Dict[str, torch.Tensor]) -> None:
         self.worker.register_to_server(kv_caches)
 
+    # sleep mode: the engine releases (and later re-creates) its cache memory around these two calls
+    # (flexkv/integration/vllm/vllm_v1_adapter.py:1115-1125); a scheduler-role object has nothing to do
+    def before_device_sleep(self) -> None:
+        if self.worker is not None:
+            self.worker.before_device_sleep()
+
+    def after_device_wake(self, kv_caches: Optional[Dict[str, torch.Tensor]] = None) -> None:
+        if self.worker is not None:
+            self.worker.after_device_wake(kv_caches)
+
     def get_finished(self, finished_req_ids: Set[str]) -> Tuple[Optional[Set[str]], Optional[Set[str]]]:
         s, r = self._finished_sending, self._finished_recving
         self._finished_sending, self._finished_recving = set(), set()

@@ -101,22 +101,19 @@ class KVManager:
         self.transfer_manager.register_gpu(reg)
 
     def register_swa_tensors(self, tensors: Sequence[torch.Tensor], tp_rank: int = 0, pp_rank: int = 0,
-                             dp_client_id: Optional[int] = None) -> None:
+                             dp_client_id: Optional[int] = None, group_id: int = 0) -> None:
         """Sliding-window pages of one rank: one tensor per window layer, shaped
-        [num_pages, ...] with a contiguous page; call before ``start()``."""
+        [num_pages, ...] with a contiguous page; call before ``start()``. ``group_id`` g >= 1 registers
+        the g-th sidecar group of ``SWAPoolConfig.sidecar_groups`` (state saved with the same slot).
+        Engine ranks in other processes use ``KVTPClient.register_swa_to_server``."""
         if self.server_client_mode:
-            raise RuntimeError("window pages are registered in-process only")
-        from .storage.gpu_layout import GpuRegistration
-        t0 = tensors[0]
-        page_bytes = t0[0].numel() * t0.element_size()
-        for t in tensors:
-            if not t.is_contiguous() or t.shape != t0.shape or t.dtype != t0.dtype:
-                raise ValueError("window page tensors must be contiguous and identically shaped")
-        dev = t0.device.index if t0.is_cuda else -1
-        reg = GpuRegistration(dev if dev is not None else 0, [int(t.data_ptr()) for t in tensors], "vllm", 1, 0, 0, 0,
-                              page_bytes, page_bytes, int(t0.shape[0]), len(tensors), 1, t0.dtype,
-                              dp_client_id=self.dp_client_id if dp_client_id is None else dp_client_id,
-                              pp_rank=pp_rank, tp_rank=tp_rank, keepalive=list(tensors))
+            raise RuntimeError("in server-client mode the engine ranks register their window pages themselves")
+        from .storage.gpu_layout import swa_registration
+        reg = swa_registration([int(t.data_ptr()) for t in tensors], [tuple(t.shape) for t in tensors],
+                               [tuple(t.stride()) for t in tensors], tensors[0].dtype,
+                               (tensors[0].device.index or 0) if tensors[0].is_cuda else -1)
+        reg.dp_client_id = self.dp_client_id if dp_client_id is None else dp_client_id
+        reg.pp_rank, reg.tp_rank, reg.group_id, reg.keepalive = pp_rank, tp_rank, int(group_id), list(tensors)
         self.transfer_manager.register_swa(reg)
 
     # ---- sleep / wake of the engine's GPU memory ---------------------------------------

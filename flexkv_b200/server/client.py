@@ -138,6 +138,18 @@ class KVTPClient:
         flexkv_logger.info("sent GPU registration: dp %d rank %d, %d tensors", self.dp_client_id,
                            self.intra_client_id, len(kv_caches))
 
+    def register_swa_to_server(self, page_tensors: Sequence[torch.Tensor], group_id: int = 0,
+                               mode: Optional[str] = None) -> None:
+        """Sliding-window pages of this rank (one ``[num_pages, ...]`` tensor per window layer); ``group_id``
+        g >= 1 names the g-th sidecar group of ``SWAPoolConfig.sidecar_groups``. The data plane waits for
+        these when ``SWAPoolConfig.wait_for_registration`` is set."""
+        handles = [TensorSharedHandle.export(t, mode) for t in page_tensors]
+        self._swa_handles = getattr(self, "_swa_handles", []) + handles
+        req = R.RegisterTPClientRequest(self.dp_client_id, self.intra_client_id, self.device_id, handles, None,
+                                        pp_rank=self.pp_rank, tp_rank=self.tp_rank, group_id=int(group_id),
+                                        is_swa=True)
+        self._sock.send(pickle.dumps(req, protocol=pickle.HIGHEST_PROTOCOL))
+
     # ---- sleep / wake (vLLM sleep mode) ----------------------------------------------------
     def _control(self, action: str, registration=None, timeout: float = 60.0) -> bool:
         import os

@@ -18,6 +18,14 @@ from .utils import get_zmq_socket
 def registration_from_request(req: RegisterTPClientRequest) -> GpuRegistration:
     ptrs = [h.open() for h in req.handles]
     h0 = req.handles[0]
+    if getattr(req, "is_swa", False):
+        from ..storage.gpu_layout import swa_registration
+        reg = swa_registration(ptrs, [h.shape for h in req.handles], [h.stride for h in req.handles], h0.dtype,
+                               req.device_id if h0.device_id >= 0 else -1)
+        reg.dp_client_id, reg.pp_rank, reg.tp_rank = req.dp_client_id, req.pp_rank, req.tp_rank
+        reg.group_id = max(0, int(getattr(req, "group_id", 0)))
+        reg.keepalive = list(req.handles)
+        return reg
     reg = describe_gpu_tensors(ptrs, req.gpu_layout, h0.dtype, req.device_id if h0.device_id >= 0 else -1,
                                [h.shape for h in req.handles], [h.stride for h in req.handles])
     reg.dp_client_id, reg.pp_rank, reg.tp_rank = req.dp_client_id, req.pp_rank, req.tp_rank

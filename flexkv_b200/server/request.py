@@ -32,7 +32,8 @@ class RegisterTPClientRequest:
     gpu_layout: KVCacheLayout
     pp_rank: int = 0
     tp_rank: int = 0
-    group_id: int = -1               # layer group of a multi-group cache
+    group_id: int = -1               # layer group of a multi-group cache (window pages: group of the window pool)
+    is_swa: bool = False             # the tensors are sliding-window pages ([pages, page bytes] per layer)
 
 
 @dataclass

@@ -41,6 +41,7 @@ class GpuRegistration:
     pp_rank: int = 0
     tp_rank: int = 0                # effective rank inside the host block (cp_rank * tp + tp_rank)
     group_id: int = -1              # layer group of a multi-group cache (-1: the only group)
+    is_swa: bool = False            # sliding-window pages (group_id then names the window pool's group)
     keepalive: Any = field(default=None, repr=False)   # tensors or opened handles
 
     def as_native(self) -> Dict[str, Any]:
@@ -113,3 +114,23 @@ def register_tensors(tensors: Sequence[torch.Tensor], gpu_layout: KVCacheLayout,
     for k, v in ids.items():
         setattr(reg, k, v)
     return reg
+
+
+def swa_registration(ptrs: Sequence[int], shapes: Sequence[Sequence[int]], strides: Sequence[Sequence[int]],
+                     dtype: torch.dtype, device_id: int) -> GpuRegistration:
+    """Window pages of one rank: one tensor per layer, ``[num_pages, ...]`` with a contiguous page."""
+    s0 = tuple(int(d) for d in shapes[0])
+    page_elems = 1
+    for d in s0[1:]:
+        page_elems *= d
+    for shp, st in zip(shapes, strides):
+        expect = 1
+        for d, s in zip(reversed(list(shp)), reversed(list(st))):
+            if int(d) != 1 and int(s) != expect:
+                raise ValueError("window page tensors must be contiguous")
+            expect *= int(d)
+        if tuple(int(d) for d in shp) != s0:
+            raise ValueError("window page tensors must be identically shaped")
+    page_bytes = page_elems * dtype.itemsize
+    return GpuRegistration(device_id, [int(p) for p in ptrs], "vllm", 1, 0, 0, 0, page_bytes, page_bytes, s0[0],
+                           len(ptrs), 1, dtype, is_swa=True)

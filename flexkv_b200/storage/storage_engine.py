@@ -76,7 +76,10 @@ class SwaPool:
     num_slots: int
     slot_bytes: int             # all ranks
     rank_slot_bytes: int
-    page_bytes: int             # one layer of one rank
+    page_bytes: int             # one layer of one rank (window KV group)
+    group_layers: List[int] = None          # per group inside a rank's slot: layers,
+    group_page_bytes: List[int] = None      # bytes of one layer's page,
+    group_offsets: List[int] = None         # and where the group starts
 
     @property
     def base(self) -> int:
@@ -103,6 +106,7 @@ class StorageEngine:
         self.ssd: Optional[SsdPool] = None
         self.ssd_size_table: Optional[np.ndarray] = None
         self.swa_regs: Dict[WorkerKey, Dict[int, GpuRegistration]] = {}
+        self.swa_group_regs: Dict[WorkerKey, Dict[int, Dict[int, GpuRegistration]]] = {}    # [key][rank][group]
         self.gpu_group_regs: Dict[WorkerKey, Dict[int, Dict[int, GpuRegistration]]] = {}
         self.swa_host: Optional[SwaPool] = None
         self.swa_ssd: Optional[SsdPool] = None
@@ -299,25 +303,44 @@ class StorageEngine:
 
     # ---- sliding-window side pool ------------------------------------------------------
     def register_swa_blocks(self, reg: GpuRegistration) -> None:
-        """GPU window pages of one rank: ``num_layers`` tensors of [pages, page_bytes]."""
+        """GPU window pages of one rank: ``num_layers`` tensors of [pages, page_bytes]. ``group_id``
+        0 (or -1) is the window KV itself, g >= 1 the g-th sidecar group of ``SWAPoolConfig.sidecar_groups``
+        (state that is saved and restored with the same slot)."""
         key = WorkerKey(reg.dp_client_id, reg.pp_rank)
-        self.swa_regs.setdefault(key, {})[reg.tp_rank] = reg
+        g = max(0, int(reg.group_id))
         if self.swa_host is None:
-            self._alloc_swa(reg)
+            self._alloc_swa(reg if g == 0 else None)
+        pool = self.swa_host
+        if g >= len(pool.group_layers):
+            raise ValueError(f"window sidecar group {g} is not configured (SWAPoolConfig.sidecar_groups)")
+        if (reg.num_layers, reg.chunk_bytes) != (pool.group_layers[g], pool.group_page_bytes[g]):
+            raise ValueError(f"window group {g}: registered {reg.num_layers} layers x {reg.chunk_bytes} B, the pool "
+                             f"expects {pool.group_layers[g]} x {pool.group_page_bytes[g]} B")
+        self.swa_group_regs.setdefault(key, {}).setdefault(reg.tp_rank, {})[g] = reg
+        if g == 0:
+            self.swa_regs.setdefault(key, {})[reg.tp_rank] = reg
 
-    def _alloc_swa(self, reg: GpuRegistration) -> None:
+    def _alloc_swa(self, reg: Optional[GpuRegistration]) -> None:
         cfg = self.cache_config.swa
         if cfg is None or not cfg.enabled:
             raise ValueError("window pages registered but CacheConfig.swa is not enabled")
         ranks = 1 if (self.model_config.use_mla or self.model_config.num_kv_heads == 1) else \
             self.model_config.effective_tp_size
-        rank_slot = reg.num_layers * reg.chunk_bytes
+        geometry = cfg.group_geometry(self.cache_config.tokens_per_block)
+        if reg is not None and not cfg.sidecar_groups:
+            geometry = [(reg.num_layers, reg.chunk_bytes)]      # a lone window group is sized by its tensors
+        layers = [n for n, _ in geometry]
+        pages = [b for _, b in geometry]
+        offsets = [0]
+        for n, b in geometry[:-1]:
+            offsets.append(offsets[-1] + n * b)
+        rank_slot = sum(n * b for n, b in geometry)
         total = cfg.num_slots * ranks * rank_slot
         region = _native.C.host_region_alloc(total, hugepage=False, hugepage_bytes=2 << 20, numa_node=self._numa_node,
                                              populate=True, touch_threads=4,
                                              cuda_register=self._cuda_register and cfg.pin_memory,
                                              register_chunk_bytes=0, backing_file="")
-        self.swa_host = SwaPool(region, cfg.num_slots, ranks * rank_slot, rank_slot, reg.chunk_bytes)
+        self.swa_host = SwaPool(region, cfg.num_slots, ranks * rank_slot, rank_slot, pages[0], layers, pages, offsets)
         if cfg.num_ssd_slots > 0 and self.cache_config.enable_ssd:
             # SSD window tier: one file of whole slots in the first cache directory
             d = parse_path_list(self.cache_config.ssd_cache_dir or [])[0]
@@ -327,8 +350,8 @@ class StorageEngine:
                                            try_direct=True, iouring_entries=self.env.iouring_entries,
                                            num_threads=2)
             self.swa_ssd = SsdPool(engine, [[path]], ranks * rank_slot, cfg.num_ssd_slots, cfg.num_ssd_slots)
-        flexkv_logger.info("window pool: %d slots x %d B (%d layers x %d B per rank, %d rank(s))", cfg.num_slots,
-                           ranks * rank_slot, reg.num_layers, reg.chunk_bytes, ranks)
+        flexkv_logger.info("window pool: %d slots x %d B (groups of layers x page bytes per rank: %s, %d rank(s))",
+                           cfg.num_slots, ranks * rank_slot, geometry, ranks)
 
     def register_gpu_blocks(self, reg: GpuRegistration) -> None:
         key = WorkerKey(reg.dp_client_id, reg.pp_rank)

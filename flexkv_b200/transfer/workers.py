@@ -526,6 +526,9 @@ class SwaWorker(TransferWorker):
         super().__init__()
         self.storage = storage
         self.regs = [storage.swa_regs[key][r] for r in sorted(storage.swa_regs[key])]
+        # every group of a rank's slot (window KV first, then sidecar state) moves with its own launch
+        self.group_regs = [[storage.swa_group_regs[key][r][g] for g in sorted(storage.swa_group_regs[key][r])]
+                           for r in sorted(storage.swa_regs[key])]
         self.shared = model_config.use_mla or model_config.num_kv_heads == 1
         self.on_gpu = self.regs[0].device_id >= 0
         self._streams, self._status = {}, {}
@@ -556,29 +559,34 @@ class SwaWorker(TransferWorker):
             c_ids = np.ascontiguousarray(slots, dtype=np.int64)
             g_ptr, c_ptr = g_ids.ctypes.data, c_ids.ctypes.data
         evs = []
-        for i, reg in enumerate(self.regs):
+        for i, groups in enumerate(self.group_regs):
             if self.shared and not h2d and i > 0:
                 break
-            params = dict(gpu_ptrs=[int(p) for p in reg.ptrs], idx_layer_mul=reg.idx_layer_mul,
-                          idx_kv_mul=reg.idx_kv_mul, g_layer_stride=reg.layer_stride, g_kv_stride=reg.kv_stride,
-                          g_block_stride=reg.block_stride, cpu_base=pool.base, c_layer_stride=pool.page_bytes,
-                          c_kv_stride=0, c_block_stride=pool.slot_bytes,
-                          c_off=0 if self.shared else i * pool.rank_slot_bytes, gpu_blocks_ptr=g_ptr,
-                          cpu_blocks_ptr=c_ptr, num_pairs=int(slots.size), layer_start=0, num_layers=reg.num_layers,
-                          kv_dim=1, chunk_bytes=reg.chunk_bytes, gpu_num_blocks=reg.num_blocks,
-                          cpu_num_blocks=pool.num_slots, h2d=int(h2d))
-            nbytes += int(slots.size) * reg.num_layers * reg.chunk_bytes
-            if not self.on_gpu:
-                status |= _native.C.host_kv_copy(params, 2)
-                continue
-            st = self._streams[reg.device_id]
-            params["status_ptr"] = self._status[reg.device_id].data_ptr()
-            e0, e1 = self._torch.cuda.Event(enable_timing=True), self._torch.cuda.Event(enable_timing=True)
-            with self._torch.cuda.device(reg.device_id):
+            dev_id = groups[0].device_id
+            if self.on_gpu:
+                st = self._streams[dev_id]
+                e0, e1 = self._torch.cuda.Event(enable_timing=True), self._torch.cuda.Event(enable_timing=True)
                 e0.record(st)
-                _native.C.kv_copy(params, 4, 16384, 0, st.cuda_stream)
+            for reg in groups:
+                g = max(0, int(reg.group_id))
+                params = dict(gpu_ptrs=[int(p) for p in reg.ptrs], idx_layer_mul=reg.idx_layer_mul,
+                              idx_kv_mul=reg.idx_kv_mul, g_layer_stride=reg.layer_stride, g_kv_stride=reg.kv_stride,
+                              g_block_stride=reg.block_stride, cpu_base=pool.base,
+                              c_layer_stride=pool.group_page_bytes[g], c_kv_stride=0, c_block_stride=pool.slot_bytes,
+                              c_off=(0 if self.shared else i * pool.rank_slot_bytes) + pool.group_offsets[g],
+                              gpu_blocks_ptr=g_ptr, cpu_blocks_ptr=c_ptr, num_pairs=int(slots.size), layer_start=0,
+                              num_layers=reg.num_layers, kv_dim=1, chunk_bytes=reg.chunk_bytes,
+                              gpu_num_blocks=reg.num_blocks, cpu_num_blocks=pool.num_slots, h2d=int(h2d))
+                nbytes += int(slots.size) * reg.num_layers * reg.chunk_bytes
+                if not self.on_gpu:
+                    status |= _native.C.host_kv_copy(params, 2)
+                    continue
+                params["status_ptr"] = self._status[dev_id].data_ptr()
+                with self._torch.cuda.device(dev_id):
+                    _native.C.kv_copy(params, 4, 16384, 0, st.cuda_stream)
+            if self.on_gpu:
                 e1.record(st)
-            evs.append((e0, e1, reg.device_id))
+                evs.append((e0, e1, dev_id))
         for e0, e1, dev in evs:
             e1.synchronize()
             ms = max(ms, e0.elapsed_time(e1))

@@ -48,6 +48,9 @@ class TransferManager:
 
     # ---- registration -----------------------------------------------------------
     def register_gpu(self, reg: GpuRegistration) -> None:
+        if getattr(reg, "is_swa", False):
+            self.register_swa(reg)
+            return
         with self._reg_cv:
             self._pending_regs.append(reg)
             self._reg_cv.notify_all()
@@ -56,6 +59,15 @@ class TransferManager:
         """Window pages of one rank; must arrive before start() completes initialisation."""
         with self._reg_cv:
             self._pending_swa.append(reg)
+            self._reg_cv.notify_all()
+
+    def _expected_swa_registrations(self) -> int:
+        """Window registrations that start-up waits for: every rank, every group of the window pool."""
+        swa = self.cache_config.swa
+        if swa is None or not swa.enabled or not swa.wait_for_registration or not self.require_gpu:
+            return 0
+        m = self.model_config
+        return m.total_clients * m.local_pp_stages * m.effective_tp_size_per_node * (1 + len(swa.sidecar_groups))
 
     def _expected_registrations(self) -> int:
         m = self.model_config
@@ -75,16 +87,17 @@ class TransferManager:
 
     def _init(self) -> None:
         try:
-            want = self._expected_registrations()
+            want, want_swa = self._expected_registrations(), self._expected_swa_registrations()
             t0 = time.monotonic()
             warned = False
             with self._reg_cv:
-                while len(self._pending_regs) < want and not self._stop:
+                while (len(self._pending_regs) < want or len(self._pending_swa) < want_swa) and not self._stop:
                     self._reg_cv.wait(timeout=1.0)
                     if not warned and time.monotonic() - t0 > 60:
                         warned = True
-                        flexkv_logger.warning("still waiting for GPU registrations: %d of %d arrived",
-                                              len(self._pending_regs), want)
+                        flexkv_logger.warning("still waiting for GPU registrations: %d of %d arrived (window pages: "
+                                              "%d of %d)", len(self._pending_regs), want, len(self._pending_swa),
+                                              want_swa)
             if self._stop:
                 return
             numa = self.numa_node

@@ -201,3 +201,87 @@ def test_ssd_window_tier_serves_the_snapshot_after_the_host_copy_is_gone(tmp_pat
         assert ssd.swa_pool.num_used == 1 and ssd.index.total_swa_slots() == 1
     finally:
         mgr.shutdown()
+
+
+STATE_LAYERS, STATE_BYTES = 2, 32
+
+
+def _state_tensors(dev, seed):
+    g = torch.Generator().manual_seed(seed)
+    return [torch.randint(0, 256, (16, STATE_BYTES), dtype=torch.uint8, generator=g).to(dev) for _ in range(STATE_LAYERS)]
+
+
+@pytest.mark.parametrize("device", ["cpu", pytest.param("cuda:0", marks=pytest.mark.gpu)])
+@pytest.mark.parametrize("remote_registration", [False, True])
+def test_sidecar_state_travels_in_the_same_slot(device, remote_registration):
+    """A sidecar group (state kept beside the window KV, other layer count and page size) is saved and restored
+    with the slot; the window tensors may be registered by the engine rank over the registration channel."""
+    from flexkv_b200 import KVTPClient
+    from flexkv_b200.server.utils import unique_ipc_endpoint
+    shape = KVShape("s", 2, 2, 16, tokens_per_block=T)
+    cfg = CacheConfig(tokens_per_block=T, num_cpu_blocks=32, enable_swa_transfer=True,
+                      swa=SWAPoolConfig(enabled=True, num_slots=4, num_swa_layers=SWA_LAYERS,
+                                        bytes_per_token_per_layer=PAGE_BYTES // T, evict_ratio=0.25,
+                                        sidecar_groups=[(STATE_LAYERS, STATE_BYTES)],
+                                        wait_for_registration=remote_registration))
+    dev = "cpu" if device == "cpu" else torch.device(device)
+    reg = unique_ipc_endpoint("swareg") if remote_registration else None
+    mgr = KVManager(make_model_config(shape), cfg, require_gpu=True, gpu_register_port=reg)
+    kv, layout = alloc_paged_cache(shape, 64, dev, "vllm", fill="normal", seed=5)
+    g = torch.Generator().manual_seed(9)
+    swa = [torch.randint(0, 256, (16, PAGE_BYTES), dtype=torch.uint8, generator=g).to(dev) for _ in range(SWA_LAYERS)]
+    state = _state_tensors(dev, 13)
+    client = None
+    if remote_registration:
+        mgr.start()
+        client = KVTPClient(reg, dp_client_id=0, device_id=0, tp_rank=0)
+        client.register_to_server(kv, layout, mode="same_process")
+        client.register_swa_to_server(state, group_id=1, mode="same_process")      # any order
+        client.register_swa_to_server(swa, group_id=0, mode="same_process")
+    else:
+        mgr.register_gpu_tensors(kv, layout)
+        mgr.register_swa_tensors(swa)
+        mgr.register_swa_tensors(state, group_id=1)
+        mgr.start()
+    mgr.wait_ready(30)
+    try:
+        pool = mgr.transfer_manager.storage.swa_host
+        assert pool.rank_slot_bytes == SWA_LAYERS * PAGE_BYTES + STATE_LAYERS * STATE_BYTES
+        assert pool.group_offsets == [0, SWA_LAYERS * PAGE_BYTES]
+        tok = np.arange(4 * T, dtype=np.int64) + 300
+        assert put(mgr, tok, np.array([3, 9, 1, 30]), page=5).status.value == "success"
+        want_page = [t[5].clone() for t in swa]
+        want_state = [t[5].clone() for t in state]
+        for t in swa + state:
+            t[11] = 0
+            t[5] = 0
+        tid, mask = mgr.get_match(tok, swa_aware=True)
+        assert int(mask.sum()) == 4 * T
+        mgr.launch(tid, slots(np.arange(40, 44)), swa_slot_mappings=[slots([11])])
+        assert mgr.wait(tid)[tid].status.value == "success"
+        for l in range(SWA_LAYERS):
+            assert torch.equal(swa[l][11], want_page[l])
+        for l in range(STATE_LAYERS):
+            assert torch.equal(state[l][11], want_state[l])
+    finally:
+        mgr.shutdown()
+
+
+def test_sidecar_registration_must_match_the_configured_geometry():
+    shape = KVShape("s", 2, 2, 16, tokens_per_block=T)
+    cfg = CacheConfig(tokens_per_block=T, num_cpu_blocks=32, enable_swa_transfer=True,
+                      swa=SWAPoolConfig(enabled=True, num_slots=4, num_swa_layers=SWA_LAYERS,
+                                        bytes_per_token_per_layer=PAGE_BYTES // T,
+                                        sidecar_groups=[(STATE_LAYERS, STATE_BYTES)]))
+    mgr = KVManager(make_model_config(shape), cfg, require_gpu=True)
+    kv, layout = alloc_paged_cache(shape, 64, "cpu", "vllm", fill="normal", seed=5)
+    mgr.register_gpu_tensors(kv, layout)
+    mgr.register_swa_tensors([torch.zeros(16, PAGE_BYTES, dtype=torch.uint8) for _ in range(SWA_LAYERS)])
+    mgr.register_swa_tensors([torch.zeros(16, STATE_BYTES * 2, dtype=torch.uint8) for _ in range(STATE_LAYERS)],
+                             group_id=1)
+    mgr.start()
+    try:
+        with pytest.raises(RuntimeError, match="window group 1"):
+            mgr.wait_ready(30)
+    finally:
+        mgr.shutdown()
