@@ -338,12 +338,34 @@ class FlexKVWorkerConnector:
         self._layout: Optional[KVCacheLayout] = None
 
     def register_to_server(self, kv_caches: Dict[str, torch.Tensor]) -> None:
-        tensors = list(kv_caches.values()) if isinstance(kv_caches, dict) else list(kv_caches)
+        """Registers the worker's KV tensors. Layers whose name contains ``.k_cache`` are indexer key caches
+        (``[blocks, tokens, dim]`` beside every attention layer): they become a second layer group, and the
+        group list travels with the registration because only the worker sees these tensors
+        (flexkv/integration/vllm/vllm_v1_adapter.py:826-960)."""
         m, c = self.cfg.model_config, self.cfg.cache_config
-        layout = infer_vllm_gpu_layout(tensors, c.tokens_per_block, m.num_kv_heads // max(1, m.tp_size), m.head_size,
+        named = kv_caches if isinstance(kv_caches, dict) else {str(i): t for i, t in enumerate(kv_caches)}
+        main = [t for n, t in named.items() if ".k_cache" not in n]
+        indexer = [t for n, t in named.items() if ".k_cache" in n]
+        layout = infer_vllm_gpu_layout(main, c.tokens_per_block, m.num_kv_heads // max(1, m.tp_size), m.head_size,
                                        m.use_mla)
-        self._caches, self._layout = tensors, layout
-        self.client.register_to_server(tensors, layout)
+        self._caches, self._layout = main, layout
+        if not indexer:
+            self.client.register_to_server(main, layout)
+            return
+        from ...common.config import LayerGroupSpec
+        t0 = indexer[0]
+        if t0.dim() != 3:
+            raise ValueError(f"indexer caches are [blocks, tokens, dim], got {tuple(t0.shape)}")
+        idx_layout = KVCacheLayout(KVCacheLayoutType.LAYERFIRST, len(indexer), t0.shape[0], t0.shape[1], 1, t0.shape[2],
+                                   is_mla=True)
+        groups = [LayerGroupSpec(num_layers=len(main), num_kv_heads=layout.num_head, head_size=layout.head_size,
+                                 kv_dim=layout.kv_dim, dtype=main[0].dtype, layer_ids=list(range(len(main))), name="kv"),
+                  LayerGroupSpec(num_layers=len(indexer), num_kv_heads=1, head_size=int(t0.shape[2]), kv_dim=1,
+                                 dtype=t0.dtype, compress_ratio=max(1, layout.tokens_per_block // int(t0.shape[1])),
+                                 layer_ids=list(range(len(indexer))), name="indexer")]
+        self._indexer, self._idx_layout, self._groups = indexer, idx_layout, groups
+        self.client.register_to_server(main, layout, group_id=0, layer_groups=groups)
+        self.client.register_to_server(indexer, idx_layout, group_id=1, layer_groups=groups)
 
     def before_device_sleep(self) -> int:
         """vLLM sleep mode frees the cache; the data plane must stop touching (and mapping) it first.

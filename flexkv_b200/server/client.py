@@ -128,12 +128,16 @@ class KVTPClient:
         self._handles: List[TensorSharedHandle] = []
 
     def register_to_server(self, kv_caches: Sequence[torch.Tensor], kv_layout: KVCacheLayout,
-                           mode: Optional[str] = None, group_id: int = -1) -> None:
-        """``group_id``: layer group of a multi-group cache; call once per group."""
+                           mode: Optional[str] = None, group_id: int = -1, layer_groups=None) -> None:
+        """``group_id``: layer group of a multi-group cache; call once per group. ``layer_groups``: the
+        ``LayerGroupSpec`` list, for engines whose worker only learns the groups from its tensors (the data
+        plane adopts the first list it receives when its own configuration names none;
+        flexkv/transfer_manager.py:154-161)."""
         handles = [TensorSharedHandle.export(t, mode) for t in kv_caches]
         self._handles = self._handles + handles if group_id > 0 else handles
         req = R.RegisterTPClientRequest(self.dp_client_id, self.intra_client_id, self.device_id, handles,
-                                        kv_layout, pp_rank=self.pp_rank, tp_rank=self.tp_rank, group_id=group_id)
+                                        kv_layout, pp_rank=self.pp_rank, tp_rank=self.tp_rank, group_id=group_id,
+                                        layer_groups=layer_groups)
         self._sock.send(pickle.dumps(req, protocol=pickle.HIGHEST_PROTOCOL))
         flexkv_logger.info("sent GPU registration: dp %d rank %d, %d tensors", self.dp_client_id,
                            self.intra_client_id, len(kv_caches))

@@ -30,6 +30,7 @@ def registration_from_request(req: RegisterTPClientRequest) -> GpuRegistration:
                                [h.shape for h in req.handles], [h.stride for h in req.handles])
     reg.dp_client_id, reg.pp_rank, reg.tp_rank = req.dp_client_id, req.pp_rank, req.tp_rank
     reg.group_id = getattr(req, "group_id", -1)
+    reg.layer_groups = getattr(req, "layer_groups", None)
     reg.keepalive = list(req.handles)
     return reg
 

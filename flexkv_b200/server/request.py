@@ -34,6 +34,7 @@ class RegisterTPClientRequest:
     tp_rank: int = 0
     group_id: int = -1               # layer group of a multi-group cache (window pages: group of the window pool)
     is_swa: bool = False             # the tensors are sliding-window pages ([pages, page bytes] per layer)
+    layer_groups: Optional[List[Any]] = None   # LayerGroupSpec list when the worker discovered the groups itself
 
 
 @dataclass

@@ -42,6 +42,7 @@ class GpuRegistration:
     tp_rank: int = 0                # effective rank inside the host block (cp_rank * tp + tp_rank)
     group_id: int = -1              # layer group of a multi-group cache (-1: the only group)
     is_swa: bool = False            # sliding-window pages (group_id then names the window pool's group)
+    layer_groups: Any = None        # LayerGroupSpec list sent along by a worker that discovered the groups itself
     keepalive: Any = field(default=None, repr=False)   # tensors or opened handles
 
     def as_native(self) -> Dict[str, Any]:

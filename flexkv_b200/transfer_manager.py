@@ -69,7 +69,21 @@ class TransferManager:
         m = self.model_config
         return m.total_clients * m.local_pp_stages * m.effective_tp_size_per_node * (1 + len(swa.sidecar_groups))
 
+    def _adopt_layer_groups(self) -> None:
+        """Layer groups discovered by an engine worker (first list wins) when this side was configured with
+        none. Block counts stay as the planner knows them; only the block size grows."""
+        if self.model_config.layer_groups:
+            return
+        for r in self._pending_regs:
+            groups = getattr(r, "layer_groups", None)
+            if groups:
+                object.__setattr__(self.model_config, "layer_groups", list(groups))
+                flexkv_logger.info("layer groups taken from the GPU registration of rank %d: %s", r.tp_rank,
+                                   [(g.num_layers, g.num_kv_heads, g.head_size, g.compress_ratio) for g in groups])
+                return
+
     def _expected_registrations(self) -> int:
+        self._adopt_layer_groups()
         m = self.model_config
         groups = len(m.layer_groups) if m.layer_groups else 1      # one registration per rank and layer group
         return m.total_clients * m.local_pp_stages * m.effective_tp_size_per_node * groups if self.require_gpu else 0
@@ -93,6 +107,7 @@ class TransferManager:
             with self._reg_cv:
                 while (len(self._pending_regs) < want or len(self._pending_swa) < want_swa) and not self._stop:
                     self._reg_cv.wait(timeout=1.0)
+                    want = self._expected_registrations()      # a registration may have brought the layer groups
                     if not warned and time.monotonic() - t0 > 60:
                         warned = True
                         flexkv_logger.warning("still waiting for GPU registrations: %d of %d arrived (window pages: "

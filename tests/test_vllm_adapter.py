@@ -149,3 +149,48 @@ def test_blocking_waits_events_and_stats():
         assert conn.stats.num_put_requests == 1 and conn.stats.num_get_requests == 1
     finally:
         conn.shutdown()
+
+
+def test_worker_registers_indexer_caches_as_a_second_group_and_the_manager_adopts_it():
+    """Only the worker sees the indexer key caches (layer names with ``.k_cache``): the group list travels with
+    its registration and a manager configured without groups moves both groups from then on."""
+    from flexkv_b200.integration.vllm.vllm_v1_adapter import FlexKVWorkerConnector
+    from flexkv_b200.server.utils import unique_ipc_endpoint
+    shape = KVShape("v", 2, 2, 16, tokens_per_block=T)
+    cfg = FlexKVConfig()
+    cfg.model_config = make_model_config(shape)
+    cfg.cache_config = CacheConfig(tokens_per_block=T, num_cpu_blocks=32)
+    cfg.gpu_register_port = unique_ipc_endpoint("vidx")
+    mgr = KVManager(cfg.model_config, cfg.cache_config, require_gpu=True, gpu_register_port=cfg.gpu_register_port)
+    mgr.start()
+    kv, _ = alloc_paged_cache(shape, 64, "cpu", "vllm", fill="normal", seed=81)
+    g = torch.Generator().manual_seed(4)
+    idx = [torch.randint(0, 256, (64, T, 12), dtype=torch.uint8, generator=g) for _ in range(2)]
+    caches = {"model.layers.0.self_attn.attn": kv[0], "model.layers.0.self_attn.indexer.k_cache": idx[0],
+              "model.layers.1.self_attn.attn": kv[1], "model.layers.1.self_attn.indexer.k_cache": idx[1]}
+    worker = FlexKVWorkerConnector(cfg, dp_client_id=0, tp_rank=0, device_id=0)
+    worker.client.register_to_server = (lambda f: lambda *a, **k: f(*a, mode="same_process", **k))(
+        worker.client.register_to_server)
+    try:
+        worker.register_to_server(caches)
+        mgr.wait_ready(30)
+        groups = mgr.transfer_manager.model_config.layer_groups
+        assert [(x.num_layers, x.num_kv_heads, x.head_size, x.kv_dim) for x in groups] == [(2, 2, 16, 2), (2, 1, 12, 1)]
+        host = mgr.transfer_manager.storage.host
+        assert host.block_bytes == 2 * 2 * T * 2 * 16 * 2 + 2 * T * 12
+        tok = np.arange(5 * T, dtype=np.int64) + 40
+        sl = lambda b: np.repeat(np.asarray(b), T) * T + np.tile(np.arange(T), len(b))   # noqa: E731
+        src, dst = [3, 9, 1, 30, 12], [40, 41, 42, 43, 44]
+        tid = mgr.put_async(tok, sl(src))
+        assert mgr.wait(tid, completely=True)[tid].status.value == "success"
+        want_kv, want_idx = [t[:, src].clone() for t in kv], [t[src].clone() for t in idx]
+        for t in kv:
+            t[:, dst] = 0
+        for t in idx:
+            t[dst] = 0
+        tid = mgr.get_async(tok, sl(dst))
+        assert mgr.wait(tid)[tid].status.value == "success"
+        for l in range(2):
+            assert torch.equal(kv[l][:, dst], want_kv[l]) and torch.equal(idx[l][dst], want_idx[l])
+    finally:
+        mgr.shutdown()
