@@ -236,7 +236,7 @@ class TransferPlan:
     peer_leases: Optional[Tuple[np.ndarray, np.ndarray]] = None   # (ranks, gpu blocks) pinned in the peer directory
     swa_locked: List[Any] = field(default_factory=list)            # (tier engine, node) pairs this plan window-locked
     swa_pending: Dict[int, int] = field(default_factory=dict)      # side op id -> host slot not yet mounted
-    swa_pending_ssd: Dict[int, int] = field(default_factory=dict)  # side op id -> SSD window slot not yet mounted
+    swa_pending_tier: Dict[int, Any] = field(default_factory=dict)  # side op id -> (tier engine, its slot) not yet mounted
     partial_blocks: Optional[int] = None                           # prefetch: blocks (from bstart) that really arrived
 
 
@@ -302,10 +302,11 @@ class GlobalCacheEngine:
             from .swa_cache_engine import SWAOpConstructor
             self.cpu_cache_engine.attach_swa(SWAHostPool(swa_cfg))
             self.swa_ops = SWAOpConstructor(self)
-            ssd_cfg = cache_config.swa.for_cache_tier(DeviceType.SSD)
-            if ssd_cfg is not None and self.ssd_cache_engine is not None:
-                # second window tier: snapshots are written through beside the SSD blocks
-                self.ssd_cache_engine.attach_swa(SWAHostPool(ssd_cfg))
+            # deeper window tiers: snapshots are written through beside the tier's blocks
+            for dev, eng in ((DeviceType.SSD, self.ssd_cache_engine), (DeviceType.REMOTE, self.remote_cache_engine)):
+                tier_cfg = cache_config.swa.for_cache_tier(dev)
+                if tier_cfg is not None and eng is not None:
+                    eng.attach_swa(SWAHostPool(tier_cfg))
         self._metrics = None
         self._evict_log = EvictionLogAggregator()
         for eng in self.cache_engines.values():
@@ -418,11 +419,11 @@ class GlobalCacheEngine:
                 # joint gate: only a prefix that ends where a window snapshot sits can be resumed
                 m = self.cpu_cache_engine.match(seq)
                 swa_src = (self.cpu_cache_engine, m.last_swa_node, int(m.swa_slot), int(m.swa_hit_blocks))
-                ssd = self.ssd_cache_engine
-                if ssd is not None and ssd.swa_enabled and not cpu_only:
-                    ms = ssd.match(seq)
-                    if int(ms.swa_hit_blocks) > swa_src[3]:      # a deeper snapshot sits on the SSD tier
-                        swa_src = (ssd, ms.last_swa_node, int(ms.swa_slot), int(ms.swa_hit_blocks))
+                for tier in (self.ssd_cache_engine, self.remote_cache_engine):
+                    if tier is not None and tier.swa_enabled and not cpu_only:
+                        mt = tier.match(seq)
+                        if int(mt.swa_hit_blocks) > swa_src[3]:      # a deeper snapshot sits on this tier
+                            swa_src = (tier, mt.last_swa_node, int(mt.swa_slot), int(mt.swa_hit_blocks))
                 bend = min(bend, swa_src[3])
                 if bend <= bstart:
                     return self._empty(token_mask)
@@ -441,13 +442,13 @@ class GlobalCacheEngine:
                 src_eng, src_node, src_slot, _ = swa_src
                 host_slot, stage_in = src_slot, None
                 if src_eng is not self.cpu_cache_engine:
-                    # SSD snapshot: staged through a host slot that the plan gives back at its end
+                    # SSD / remote snapshot: staged through a host slot that the plan gives back at its end
                     host_slot = self.cpu_cache_engine.alloc_swa_slot()
                     if host_slot is None:
                         self._discard_plan(plan)
                         return self._empty(token_mask)
-                    stage_in = self.swa_ops.build_swa_op(plan.graph, TransferType.DISK2H, [src_slot], [host_slot],
-                                                         dp_client_id)
+                    hop = TransferType.DISK2H if src_eng is self.ssd_cache_engine else TransferType.REMOTE2H
+                    stage_in = self.swa_ops.build_swa_op(plan.graph, hop, [src_slot], [host_slot], dp_client_id)
                     plan.swa_pending[stage_in.op_id] = host_slot
                 op = self.swa_ops.build_get_chain(plan.graph, host_slot, dp_client_id)
                 if op is not None:
@@ -746,34 +747,38 @@ class GlobalCacheEngine:
                     swa_op = graph.get_op(chain.d2h_id)
                     plan.swa_pending[chain.d2h_id] = slot
 
-                    # write-through to the SSD window tier, onto the SSD node this put created
-                    ssd_slot, disk_op = None, None
-                    if ssd is not None and ssd.swa_enabled and plan.inserted.get(DeviceType.SSD):
-                        ssd_slot = ssd.alloc_swa_slot()
-                        if ssd_slot is not None:
-                            disk_op = self.swa_ops.build_swa_op(graph, TransferType.H2DISK, [slot], [ssd_slot],
-                                                                dp_client_id)
-                            graph.add_dependency(disk_op.op_id, chain.d2h_id)
-                            plan.swa_pending_ssd[disk_op.op_id] = ssd_slot
+                    # write-through to the deeper window tiers, onto the node this put created there
+                    chained = []
+                    for dev, hop in ((DeviceType.SSD, TransferType.H2DISK), (DeviceType.REMOTE, TransferType.H2REMOTE)):
+                        tier = self.cache_engines.get(dev)
+                        if tier is None or not tier.swa_enabled or not plan.inserted.get(dev):
+                            continue
+                        tier_slot = tier.alloc_swa_slot()
+                        if tier_slot is None:
+                            continue
+                        tier_op = self.swa_ops.build_swa_op(graph, hop, [slot], [tier_slot], dp_client_id)
+                        graph.add_dependency(tier_op.op_id, chain.d2h_id)
+                        plan.swa_pending_tier[tier_op.op_id] = (tier, tier_slot)
+                        chained.append((tier, tier_slot, tier_op, plan.inserted[dev][-1]))
 
-                    def _mount(node=cpu_node, slot=slot, op=swa_op, oid=chain.d2h_id, chained=disk_op is not None):
+                    def _mount(node=cpu_node, slot=slot, op=swa_op, oid=chain.d2h_id, chained=bool(chained)):
                         plan.swa_pending.pop(oid, None)
                         if op.transfer_type == TransferType.VIRTUAL or not cpu.index.alive(node):
                             cpu.swa_pool.free(slot)
                         elif cpu.mount_swa(node, slot) and chained:
-                            # the slot feeds the SSD write: it must not be evicted and reused before that ends
+                            # the slot feeds the tier writes: it must not be evicted and reused before they end
                             cpu.index.lock_swa(node)
                             plan.swa_locked.append((cpu, node))
                     plan.op_callback_dict[chain.d2h_id] = _mount
                     plan.finished_ops_ids = list(plan.finished_ops_ids) + [chain.d2h_id]
-                    if disk_op is not None:
-                        def _mount_ssd(node=plan.inserted[DeviceType.SSD][-1], s_=ssd_slot, op=disk_op):
-                            plan.swa_pending_ssd.pop(op.op_id, None)
-                            if op.transfer_type == TransferType.VIRTUAL or not ssd.index.alive(node):
-                                ssd.swa_pool.free(s_)
+                    for tier, tier_slot, tier_op, tier_node in chained:
+                        def _mount_tier(tier=tier, node=tier_node, s_=tier_slot, op=tier_op):
+                            plan.swa_pending_tier.pop(op.op_id, None)
+                            if op.transfer_type == TransferType.VIRTUAL or not tier.index.alive(node):
+                                tier.swa_pool.free(s_)
                             else:
-                                ssd.mount_swa(node, s_)
-                        plan.op_callback_dict[disk_op.op_id] = _mount_ssd
+                                tier.mount_swa(node, s_)
+                        plan.op_callback_dict[tier_op.op_id] = _mount_tier
         plan.skipped_gpu_blocks = cpu_matched
         plan.num_gpu_blocks_to_transfer = need_cpu
         return plan
@@ -864,9 +869,9 @@ class GlobalCacheEngine:
         for slot in plan.swa_pending.values():      # side ops that never completed, staging slots of gets
             cpu.swa_pool.free(slot)
         plan.swa_pending = {}
-        for slot in plan.swa_pending_ssd.values():
-            self.ssd_cache_engine.swa_pool.free(slot)
-        plan.swa_pending_ssd = {}
+        for tier, slot in plan.swa_pending_tier.values():
+            tier.swa_pool.free(slot)
+        plan.swa_pending_tier = {}
 
     def _release_peer(self, plan: TransferPlan) -> None:
         if plan.peer_leases is not None and self.peer_directory is not None:

@@ -6,9 +6,9 @@ side ops to the plan's graph: standard transfer types flagged ``is_swa=True`` wh
 ids are window-pool slot ids on the host side and window page ids on the GPU side, so the
 transfer engine routes them to the window worker (reference:
 flexkv/cache/swa_cache_engine.py:142-239 ``build_get_chain`` / ``build_put_chain``).
-The host tier and (with ``SWAPoolConfig.num_ssd_slots``) the SSD tier carry snapshots: a put
-writes the page through host slot -> SSD slot, a get whose deepest snapshot sits on SSD stages it
-through a temporary host slot. A remote window tier is not built.
+The host tier and, with ``SWAPoolConfig.num_ssd_slots`` / ``num_remote_slots``, the SSD tier and the
+block-addressed remote tier carry snapshots: a put writes the page through host slot -> tier slot, a
+get whose deepest snapshot sits on a deeper tier stages it through a temporary host slot.
 """
 from __future__ import annotations
 

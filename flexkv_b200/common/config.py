@@ -225,7 +225,7 @@ class SWAPoolConfig:
     enabled: bool = False
     num_slots: int = 1024              # host slots
     num_ssd_slots: int = 0             # SSD window tier (0 = none): snapshots written through beside the SSD blocks
-    num_remote_slots: int = 0          # accepted; a remote window tier is not built
+    num_remote_slots: int = 0          # remote window tier (0 = none), for the block-addressed remote tier
     num_swa_layers: int = 61
     bytes_per_token_per_layer: int = 584
     multi_group: bool = False
@@ -257,6 +257,8 @@ class SWAPoolConfig:
             return self
         if name == "SSD" and self.num_ssd_slots > 0:
             return replace(self, num_slots=self.num_ssd_slots, pin_memory=False)
+        if name == "REMOTE" and self.num_remote_slots > 0:
+            return replace(self, num_slots=self.num_remote_slots, pin_memory=False)
         return None
 
 

@@ -222,7 +222,8 @@ class TransferOpGraph:
             if not op.is_swa:
                 continue
             if page_ids is None and (op.gpu_side is not None or
-                                     op.transfer_type in (TransferType.H2DISK, TransferType.DISK2H)):
+                                     op.transfer_type in (TransferType.H2DISK, TransferType.DISK2H, TransferType.H2REMOTE,
+                                                          TransferType.REMOTE2H)):
                 # the whole window chain goes, tier-to-tier hops included: their source never arrives
                 op.transfer_type = TransferType.VIRTUAL
                 op.src_block_ids = op.dst_block_ids = _EMPTY

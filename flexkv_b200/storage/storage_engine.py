@@ -110,6 +110,8 @@ class StorageEngine:
         self.gpu_group_regs: Dict[WorkerKey, Dict[int, Dict[int, GpuRegistration]]] = {}
         self.swa_host: Optional[SwaPool] = None
         self.swa_ssd: Optional[SsdPool] = None
+        self.swa_remote_path: str = ""          # remote window tier: a file of whole slots on the remote mount
+        self.swa_remote_slots: int = 0
         self._cuda_register = torch.cuda.is_available() if cuda_register is None else cuda_register
         self._numa_node = numa_node
         if cache_config.enable_cpu:
@@ -350,6 +352,15 @@ class StorageEngine:
                                            try_direct=True, iouring_entries=self.env.iouring_entries,
                                            num_threads=2)
             self.swa_ssd = SsdPool(engine, [[path]], ranks * rank_slot, cfg.num_ssd_slots, cfg.num_ssd_slots)
+        if cfg.num_remote_slots > 0 and self.cache_config.enable_remote and self.cache_config.remote_cache_path:
+            # remote window tier: one file of whole slots on the remote mount, plain positional IO
+            d = parse_path_list(self.cache_config.remote_cache_path)[0]
+            os.makedirs(d, exist_ok=True)
+            self.swa_remote_path = os.path.join(
+                d, f"{self.cache_config.remote_file_prefix or 'flexkv_remote'}_swa.bin")
+            with open(self.swa_remote_path, "ab") as f:
+                f.truncate(cfg.num_remote_slots * ranks * rank_slot)
+            self.swa_remote_slots = cfg.num_remote_slots
         flexkv_logger.info("window pool: %d slots x %d B (groups of layers x page bytes per rank: %s, %d rank(s))",
                            cfg.num_slots, ranks * rank_slot, geometry, ranks)
 

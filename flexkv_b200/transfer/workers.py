@@ -543,6 +543,8 @@ class SwaWorker(TransferWorker):
         h2d = op.transfer_type == TransferType.H2D
         if op.transfer_type in (TransferType.H2DISK, TransferType.DISK2H):
             return self._disk(op)
+        if op.transfer_type in (TransferType.H2REMOTE, TransferType.REMOTE2H):
+            return self._remote(op)
         if op.transfer_type not in (TransferType.H2D, TransferType.D2H):
             return OpOutcome(False, error=f"window ops on {op.transfer_type.value} are not built")
         slots, pages = (op.src_block_ids, op.dst_block_ids) if h2d else (op.dst_block_ids, op.src_block_ids)
@@ -612,6 +614,42 @@ class SwaWorker(TransferWorker):
                                                st.swa_ssd_layout_dict(), 0, 1)
         return OpOutcome(nfail == 0, num_bytes=int(len(ok) - nfail) * st.swa_ssd.block_bytes,
                          error="" if nfail == 0 else f"{nfail} window slot(s) failed")
+
+
+    def _remote(self, op: TransferOp) -> OpOutcome:
+        """Host window slots <-> slots of the window file on the remote mount (positional reads and writes)."""
+        import ctypes
+        st = self.storage
+        if not st.swa_remote_path or st.swa_host is None:
+            return OpOutcome(False, error="window op on the remote tier but no remote window file is configured")
+        read = op.transfer_type == TransferType.REMOTE2H
+        host, far = (op.dst_block_ids, op.src_block_ids) if read else (op.src_block_ids, op.dst_block_ids)
+        if host.size != far.size or host.size == 0:
+            return OpOutcome(False, error=f"window remote op with {host.size} host and {far.size} remote slots")
+        b = st.swa_host.slot_bytes
+        bad = 0
+        fd = os.open(st.swa_remote_path, os.O_RDWR)
+        try:
+            for h, r in zip(host.tolist(), far.tolist()):
+                if not (0 <= h < st.swa_host.num_slots and 0 <= r < st.swa_remote_slots):
+                    bad += 1
+                    continue
+                view = (ctypes.c_char * b).from_address(st.swa_host.base + h * b)
+                try:
+                    if read:
+                        data = os.pread(fd, b, r * b)
+                        if len(data) != b:
+                            bad += 1
+                            continue
+                        ctypes.memmove(view, data, b)
+                    elif os.pwrite(fd, bytes(view), r * b) != b:
+                        bad += 1
+                except OSError:
+                    bad += 1
+        finally:
+            os.close(fd)
+        return OpOutcome(bad == 0, num_bytes=(int(host.size) - bad) * b,
+                         error="" if bad == 0 else f"{bad} window slot(s) failed")
 
 
 class PeerHostWorker(TransferWorker):

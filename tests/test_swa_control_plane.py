@@ -285,3 +285,55 @@ def test_sidecar_registration_must_match_the_configured_geometry():
             mgr.wait_ready(30)
     finally:
         mgr.shutdown()
+
+
+def test_remote_window_tier_serves_the_snapshot_after_the_host_copy_is_gone(tmp_path):
+    """Same as the SSD window tier, one level further out: block-addressed remote files plus a window file."""
+    shape = KVShape("s", 2, 2, 16, tokens_per_block=T)
+    cfg = CacheConfig(tokens_per_block=T, num_cpu_blocks=32, enable_remote=True, num_remote_blocks=64,
+                      remote_cache_path=str(tmp_path), remote_file_num=2, enable_swa_transfer=True,
+                      swa=SWAPoolConfig(enabled=True, num_slots=4, num_remote_slots=8, num_swa_layers=SWA_LAYERS,
+                                        bytes_per_token_per_layer=PAGE_BYTES // T, evict_ratio=0.25))
+    mgr = KVManager(make_model_config(shape), cfg, require_gpu=True)
+    kv, layout = alloc_paged_cache(shape, 64, "cpu", "vllm", fill="normal", seed=5)
+    mgr.register_gpu_tensors(kv, layout)
+    g = torch.Generator().manual_seed(9)
+    swa = [torch.randint(0, 256, (16, PAGE_BYTES), dtype=torch.uint8, generator=g) for _ in range(SWA_LAYERS)]
+    mgr.register_swa_tensors(swa)
+    mgr.start(); mgr.wait_ready(30)
+    try:
+        gce = mgr.kv_task_engine.cache_engine
+        cpu, rem = gce.cpu_cache_engine, gce.remote_cache_engine
+        tok = np.arange(5 * T, dtype=np.int64) + 900
+        src = np.array([3, 9, 1, 30, 12])
+        tid, mask = mgr.put_match(tok)
+        kinds = sorted((o.transfer_type.value, o.is_swa) for o in mgr.kv_task_engine.tasks[tid].graph.ops()
+                       if o.transfer_type.value != "Virtual")
+        assert kinds == [("D2H", False), ("D2H", True), ("H2REMOTE", False), ("H2REMOTE", True)]
+        mgr.launch(tid, slots(src), swa_slot_mappings=[slots([5])])
+        assert mgr.wait(tid, completely=True)[tid].status.value == "success"
+        assert rem.index.total_swa_slots() == 1 and rem.swa_pool.num_used == 1
+        assert (tmp_path / "flexkv_remote_swa.bin").stat().st_size == 8 * SWA_LAYERS * PAGE_BYTES
+        want_page = [t[5].clone() for t in swa]
+        want_kv = [t[:, src].clone() for t in kv]
+        mgr._clear_cpu_cache()
+        assert cpu.swa_pool.num_used == 0
+        tid, mask = mgr.get_match(tok, swa_aware=True)
+        assert int(mask.sum()) == 5 * T
+        kinds = sorted((o.transfer_type.value, o.is_swa) for o in mgr.kv_task_engine.tasks[tid].graph.ops()
+                       if o.transfer_type.value != "Virtual")
+        assert kinds == [("H2D", False), ("H2D", True), ("REMOTE2H", False), ("REMOTE2H", True)]
+        dst = np.arange(40, 45)
+        for t in kv:
+            t[:, dst] = 0
+        for t in swa:
+            t[11] = 0
+        mgr.launch(tid, slots(dst), swa_slot_mappings=[slots([11])])
+        assert mgr.wait(tid)[tid].status.value == "success"
+        for l in range(2):
+            assert torch.equal(kv[l][:, dst], want_kv[l])
+        for l in range(SWA_LAYERS):
+            assert torch.equal(swa[l][11], want_page[l])
+        assert cpu.swa_pool.num_used == 0
+    finally:
+        mgr.shutdown()
