@@ -53,6 +53,7 @@ def parse_args():
     ap.add_argument("--engine", default="", choices=["", "tma", "simt", "ce", "auto"])
     ap.add_argument("--latency-iters", type=int, default=20)
     ap.add_argument("--skip-e2e", action="store_true")
+    ap.add_argument("--skip-duplex", action="store_true")
     ap.add_argument("--codec", default="bf16_xp", choices=["none", "bf16_xp", "fp8_e4m3"],
                     help="host-tier codec: bf16_xp (default) = lossless exponent packing fused into the copy, every "
                          "restored bit is identical; none = raw bytes; fp8_e4m3 = lossy block-scaled fp8 (a "
@@ -329,6 +330,52 @@ def main() -> None:
                 lat.append(dt)
         p50_ms = max_over_ranks(statistics.median(lat))
 
+    # ------------------------------------------------------------------ both directions at once
+    # PCIe is full duplex: an engine offloads finished requests while it restores others. One D2H op and one
+    # H2D op (disjoint GPU and host blocks) run concurrently on the two workers; reported beside `value`,
+    # which stays the sum of the two directions timed one after the other.
+    duplex = None
+    if args.impl == "ours" and not args.skip_duplex and int(num_cpu_blocks) >= 2 * blocks_per_batch and \
+            args.gpu_blocks >= 2 * blocks_per_batch:
+        import threading
+        r = np.random.default_rng(4242 + rank)
+        cperm = r.permutation(int(num_cpu_blocks))[:2 * blocks_per_batch].astype(np.int64)
+        c_a, c_b = cperm[:blocks_per_batch], cperm[blocks_per_batch:]
+        gperm = r.permutation(args.gpu_blocks)[:2 * blocks_per_batch].astype(np.int64)
+        g_out, g_in = gperm[:blocks_per_batch], gperm[blocks_per_batch:]
+        first = w_d2h.execute(TransferOp(0, TransferType.D2H, g_out, c_a))
+        if not first.success:
+            raise RuntimeError(f"duplex warm-up failed: {first.error}")
+        wall, put_ms, get_ms = [], [], []
+        for i in range(args.warmup + args.steps):
+            res = {}
+
+            def go(name, w, op):
+                res[name] = w.execute(op)
+            ths = [threading.Thread(target=go, args=("put", w_d2h, TransferOp(0, TransferType.D2H, g_out, c_b))),
+                   threading.Thread(target=go, args=("get", w_h2d, TransferOp(0, TransferType.H2D, c_a, g_in)))]
+            torch.cuda.synchronize()
+            barrier()
+            t1 = time.perf_counter()
+            for th in ths:
+                th.start()
+            for th in ths:
+                th.join()
+            dt = (time.perf_counter() - t1) * 1e3
+            if not (res["put"].success and res["get"].success):
+                raise RuntimeError(f"duplex step failed: {res['put'].error} / {res['get'].error}")
+            if i >= args.warmup:
+                wall.append(dt)
+                put_ms.append(res["put"].gpu_ms)
+                get_ms.append(res["get"].gpu_ms)
+            c_a, c_b = c_b, c_a
+        wall_step = max_over_ranks(statistics.median(wall))
+        duplex = {"value": round(2 * batch_bytes * world / (wall_step * 1e-3) / 1e9, 2),
+                  "unit": "GB/s of KV, put and get in flight together (host clock around the pair, all GPUs)",
+                  "ms_per_pair": round(wall_step, 2),
+                  "put_gbs_per_gpu": round(batch_bytes / (max_over_ranks(statistics.median(put_ms)) * 1e-3) / 1e9, 2),
+                  "get_gbs_per_gpu": round(batch_bytes / (max_over_ranks(statistics.median(get_ms)) * 1e-3) / 1e9, 2)}
+
     launches = 2 * args.steps     # one D2H and one H2D kernel per step and rank
     pcie_ratio = 1.0
     st_host = mgr.transfer_manager.storage.host
@@ -350,7 +397,7 @@ def main() -> None:
             "put_gbs_per_gpu": round(put_gbs, 2), "get_gbs_per_gpu": round(get_gbs, 2),
             "region_ms_per_step": round(region_ms / args.steps, 3),
             "p50_get_latency_ms_8k_tokens": None if p50_ms is None else round(p50_ms, 3),
-            "e2e": e2e, "gpu_launches": launches * world, "clocks": clocks,
+            "e2e": e2e, "duplex": duplex, "gpu_launches": launches * world, "clocks": clocks,
             "config": {"model": f"{shape.name} KV, vLLM paged layout", "global_batch": args.requests * world,
                        "seq_len": args.tokens, "parallelism": f"dp{world}", "gpu_blocks": args.gpu_blocks,
                        "host_pool_gib": round(num_cpu_blocks * block_bytes / 2**30, 1),

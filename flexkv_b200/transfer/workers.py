@@ -890,10 +890,12 @@ def build_workers(storage, model_config: ModelConfig, cache_config: CacheConfig
             workers[(key, TransferType.H2D)] = QuantGpuHostWorker(storage, model_config, key, True)
             workers[(key, TransferType.D2H)] = QuantGpuHostWorker(storage, model_config, key, False)
             continue
-        group = build_transfer_group(storage, model_config, key)
         per_rank_block = reg0.num_layers * reg0.kv_dim * reg0.chunk_bytes
         shared = model_config.use_mla or model_config.num_kv_heads == 1
         for h2d in (True, False):
+            # one native group (thread + stream per GPU) per direction: PCIe is full duplex, so an offload and a
+            # restore that are in flight together must not queue behind each other on one stream
+            group = build_transfer_group(storage, model_config, key)
             w = GpuHostWorker(group, h2d, per_rank_block, len(regs) if (h2d or not shared) else 1)
             w.group_layers = reg0.num_layers
             w.max_blocks = max(4096, min(1 << 18, storage.host.num_blocks))
