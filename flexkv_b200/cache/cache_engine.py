@@ -322,7 +322,23 @@ class GlobalCacheEngine:
         self._metrics = collector
         self._update_mempool_metrics()
 
+    checkpoint_valid = False     # an index image written while running is still true to the SSD files
+
+    def checkpoint_ssd_index(self) -> bool:
+        """Writes the SSD index now. The image stays valid only until the tier frees a block (which it is
+        about to overwrite): the first SSD eviction after the call removes the image again, so a restart never
+        mounts an index that names rewritten blocks."""
+        if self.ssd_cache_engine is None or not persist.persist_enabled(self.cache_config):
+            return False
+        with self._cache_tree_lock:
+            ok = persist.save_index(self.cache_config, self.model_config, self.ssd_cache_engine) is not None
+            self.checkpoint_valid = ok
+        return ok
+
     def _on_evict(self, device: DeviceType, blocks: np.ndarray, hashes: np.ndarray) -> None:
+        if device == DeviceType.SSD and self.checkpoint_valid:
+            self.checkpoint_valid = False
+            persist.discard_index(self.cache_config)
         self._evict_log.record(device.name, len(blocks))
         if self._metrics is not None:
             self._metrics.record_eviction(device.name, len(blocks))

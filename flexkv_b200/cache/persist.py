@@ -186,6 +186,14 @@ def load_index(cache_config: CacheConfig, model_config: ModelConfig, engine) -> 
     return n
 
 
+def discard_index(cache_config: CacheConfig) -> None:
+    """Removes a saved image that no longer describes the files (blocks are about to be rewritten)."""
+    try:
+        os.unlink(index_path(cache_config))
+    except OSError:
+        pass
+
+
 def _consume(path: str) -> None:
     try:
         os.replace(path, path + ".mounted")

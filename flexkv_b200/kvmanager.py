@@ -263,6 +263,22 @@ class KVManager:
             return self.dp_client.withdraw_gpu_blocks(_np(gpu_block_ids, np.int64))
         return self.kv_task_engine.withdraw_gpu_blocks(_np(gpu_block_ids, np.int64), dp)
 
+    def checkpoint_ssd_index(self) -> bool:
+        """Writes the SSD tier's size table and index beside its files now (they are written at shutdown
+        anyway when ``ssd_persist`` is on): a crash after this call restarts from this state instead of cold.
+        Blocks still being written are left out, blocks stored later are simply not in the image, and the
+        image is removed again as soon as the tier evicts a block (it would be rewritten). Returns False when
+        the tier does not persist or lives in another process."""
+        from .cache import persist
+        if self.server_client_mode or not persist.persist_enabled(self.cache_config):
+            return False
+        tm, gce = self.transfer_manager, self.kv_task_engine.cache_engine
+        if tm.storage is None or gce.ssd_cache_engine is None:
+            return False
+        with gce._cache_tree_lock:     # noqa: SLF001 - the index must not move between the two files
+            persist.save_size_table(self.cache_config, tm.storage.ssd_size_table)
+            return gce.checkpoint_ssd_index()
+
     def _clear_cpu_cache(self) -> None:
         if self.server_client_mode:
             flexkv_logger.error("clearing the host cache is not supported in server-client mode")

@@ -201,3 +201,35 @@ def test_unsafe_images_give_a_cold_start(tmp_path):
     assert first.ssd_blocks_restored == 6
     second = GlobalCacheEngine(cc, mc)                       # "crash": first never shut down
     assert second.ssd_blocks_restored == 0
+
+
+def test_checkpoint_survives_a_crash_and_is_withdrawn_when_blocks_are_about_to_be_rewritten(tmp_path, monkeypatch):
+    T = SHAPE.tokens_per_block
+    kw = dict(num_cpu_blocks=32, enable_ssd=True, num_ssd_blocks=16, ssd_cache_dir=str(tmp_path), ssd_persist=True)
+    index_file = tmp_path / "flexkv_ssd_cache.index.npz"
+    tok = np.arange(6 * T, dtype=np.int64) + 50
+    mgr, (kv,) = start(SHAPE, "vllm", **kw)
+    want = _put(mgr, kv, tok, np.arange(6))
+    assert mgr.checkpoint_ssd_index() and index_file.exists()
+    # "crash": the process state is dropped without a shutdown (threads are stopped, nothing is saved)
+    monkeypatch.setenv("FLEXKV_KEEP_SSD_FILES", "1")
+    mgr.kv_task_engine.cache_engine._index_saved = True           # what a killed process would not have done:
+    mgr.transfer_manager.storage._ssd_persist = False             # neither the index nor the size table is rewritten
+    mgr.shutdown()
+    assert index_file.exists()
+    mgr, (kv,) = start(SHAPE, "vllm", **kw)
+    try:
+        assert mgr.kv_task_engine.cache_engine.ssd_blocks_restored == 6
+        for t in kv:
+            t.zero_()
+        dst = np.arange(10, 16)
+        tid = mgr.get_async(tok, slots(dst, T))
+        assert mgr.wait(tid)[tid].status.value == "success"
+        assert torch.equal(chunks(kv, "vllm", SHAPE, dst), want)
+        # a new checkpoint, then the 16-block tier has to evict to take 12 more blocks: the image goes
+        assert mgr.checkpoint_ssd_index() and index_file.exists()
+        _put(mgr, kv, np.arange(12 * T, dtype=np.int64) + 5000, np.arange(20, 32))
+        assert not index_file.exists()
+    finally:
+        mgr.shutdown()
+    assert index_file.exists()                                     # the clean shutdown saved the current state
