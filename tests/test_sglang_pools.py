@@ -7,7 +7,7 @@ import numpy as np
 import pytest
 import torch
 
-from flexkv_b200 import CacheConfig
+from flexkv_b200 import CacheConfig, KVManager
 from flexkv_b200.common.config import ModelConfig
 from flexkv_b200.integration.config import FlexKVConfig
 from flexkv_b200.integration.sglang.connector import FlexKVConnector
@@ -143,7 +143,10 @@ def test_connector_round_trip_of_every_part_of_a_split_pool():
     pool = FlexKVConnector.configure_for_pool(cfg, kv, T)
     assert len(cfg.model_config.layer_groups) == 3 and cfg.cache_config.swa.sidecar_groups
     cfg.cache_config.swa.num_slots = 4
-    conn = FlexKVConnector(cfg, page_size=T)
+    # require_gpu: start-up waits for every registration although the "GPU" tensors are host stand-ins here
+    mgr = KVManager(cfg.model_config, cfg.cache_config, require_gpu=True, gpu_register_port=cfg.gpu_register_port)
+    mgr.start()
+    conn = FlexKVConnector(cfg, page_size=T, kv_manager=mgr)
     try:
         conn.register_kv_pool(kv, pool)
         conn.wait_ready(60)
