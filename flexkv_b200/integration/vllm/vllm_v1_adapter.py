@@ -374,9 +374,16 @@ class FlexKVWorkerConnector:
 
     def after_device_wake(self, kv_caches: Optional[Dict[str, torch.Tensor]] = None) -> None:
         """Pass the re-created tensors when the engine allocated a new cache on wake."""
+        indexer = getattr(self, "_indexer", None)
         if kv_caches is not None:
-            self._caches = list(kv_caches.values()) if isinstance(kv_caches, dict) else list(kv_caches)
-        if self._caches is not None:
+            named = kv_caches if isinstance(kv_caches, dict) else {str(i): t for i, t in enumerate(kv_caches)}
+            self._caches = [t for n, t in named.items() if ".k_cache" not in n]
+            if indexer is not None:
+                indexer = self._indexer = [t for n, t in named.items() if ".k_cache" in n]
+        if self._caches is not None and indexer:
+            self.client.resume_gpu_mappings(self._caches, self._layout, group_id=0,
+                                            more_groups=[(indexer, self._idx_layout, 1)])
+        elif self._caches is not None:
             self.client.resume_gpu_mappings(self._caches, self._layout)
 
 

@@ -155,13 +155,13 @@ class KVTPClient:
         self._sock.send(pickle.dumps(req, protocol=pickle.HIGHEST_PROTOCOL))
 
     # ---- sleep / wake (vLLM sleep mode) ----------------------------------------------------
-    def _control(self, action: str, registration=None, timeout: float = 60.0) -> bool:
+    def _control(self, action: str, registration=None, timeout: float = 60.0, more=None) -> bool:
         import os
         import uuid
         ep = f"ipc:///tmp/flexkv_ctl_{os.getpid()}_{uuid.uuid4().hex[:8]}"
         reply = get_zmq_socket(self._ctx, zmq.PULL, ep, bind=True)
         try:
-            req = R.GpuControlRequest(self.dp_client_id, action, ep, registration, timeout)
+            req = R.GpuControlRequest(self.dp_client_id, action, ep, registration, timeout, more or None)
             self._sock.send(pickle.dumps(req, protocol=pickle.HIGHEST_PROTOCOL))
             if not reply.poll(int((timeout + 5) * 1000)):
                 return False
@@ -178,13 +178,23 @@ class KVTPClient:
         return self._control("suspend", None, timeout)
 
     def resume_gpu_mappings(self, kv_caches: Optional[Sequence[torch.Tensor]] = None,
-                            kv_layout: Optional[KVCacheLayout] = None, mode: Optional[str] = None) -> bool:
-        reg = None
+                            kv_layout: Optional[KVCacheLayout] = None, mode: Optional[str] = None,
+                            group_id: int = -1, more_groups: Optional[Sequence[tuple]] = None) -> bool:
+        """Hands over the re-created tensors (omit them when the memory came back at the old addresses). A
+        multi-group cache passes its first group here with its ``group_id`` and the others as
+        ``more_groups = [(tensors, layout, group_id), ...]``."""
+        reg, more = None, []
         if kv_caches is not None:
             self._handles = [TensorSharedHandle.export(t, mode) for t in kv_caches]
             reg = R.RegisterTPClientRequest(self.dp_client_id, self.intra_client_id, self.device_id, self._handles,
-                                            kv_layout, pp_rank=self.pp_rank, tp_rank=self.tp_rank)
-        return self._control("resume", reg)
+                                            kv_layout, pp_rank=self.pp_rank, tp_rank=self.tp_rank, group_id=group_id)
+            for tensors, layout, gid in (more_groups or []):
+                handles = [TensorSharedHandle.export(t, mode) for t in tensors]
+                self._handles = self._handles + handles
+                more.append(R.RegisterTPClientRequest(self.dp_client_id, self.intra_client_id, self.device_id, handles,
+                                                      layout, pp_rank=self.pp_rank, tp_rank=self.tp_rank,
+                                                      group_id=int(gid)))
+        return self._control("resume", reg, more=more)
 
     def shutdown(self) -> None:
         self._sock.close()

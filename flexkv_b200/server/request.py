@@ -47,6 +47,7 @@ class GpuControlRequest:
     reply_endpoint: str = ""
     registration: Optional[RegisterTPClientRequest] = None
     timeout: float = 60.0
+    more_registrations: Optional[List[RegisterTPClientRequest]] = None    # the other groups of a multi-group cache
 
 
 @dataclass

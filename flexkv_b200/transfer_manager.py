@@ -176,13 +176,19 @@ class TransferManager:
                 for key, ranks in self.storage.gpu_regs.items():
                     if key.dp_client_id != req.dp_client_id:
                         continue
-                    for reg in ranks.values():
+                    by_group = self.storage.gpu_group_regs.get(key, {})
+                    every = list(ranks.values()) + [g for per_rank in by_group.values() for g in per_rank.values()]
+                    seen = set()
+                    for reg in every:
                         for h in (reg.keepalive or []):
-                            if hasattr(h, "close"):
+                            if hasattr(h, "close") and id(h) not in seen:
+                                seen.add(id(h))
                                 h.close()
             return ok
         if req.action == "resume":
-            regs = [registration_from_request(req.registration)] if req.registration is not None else []
+            reqs = ([req.registration] if req.registration is not None else []) + \
+                list(getattr(req, "more_registrations", None) or [])
+            regs = [registration_from_request(r) for r in reqs]
             self.resume_gpu_mappings(req.dp_client_id, regs)
             return True
         return False

@@ -192,5 +192,17 @@ def test_worker_registers_indexer_caches_as_a_second_group_and_the_manager_adopt
         assert mgr.wait(tid)[tid].status.value == "success"
         for l in range(2):
             assert torch.equal(kv[l][:, dst], want_kv[l]) and torch.equal(idx[l][dst], want_idx[l])
+        # sleep mode: the engine drops both groups' tensors and comes back with new ones
+        assert worker.before_device_sleep() == 0
+        kv2 = [torch.zeros_like(t) for t in kv]
+        idx2 = [torch.zeros_like(t) for t in idx]
+        worker.after_device_wake({"model.layers.0.self_attn.attn": kv2[0],
+                                  "model.layers.0.self_attn.indexer.k_cache": idx2[0],
+                                  "model.layers.1.self_attn.attn": kv2[1],
+                                  "model.layers.1.self_attn.indexer.k_cache": idx2[1]})
+        tid = mgr.get_async(tok, sl(dst))
+        assert mgr.wait(tid)[tid].status.value == "success"
+        for l in range(2):
+            assert torch.equal(kv2[l][:, dst], want_kv[l]) and torch.equal(idx2[l][dst], want_idx[l])
     finally:
         mgr.shutdown()
