@@ -107,6 +107,15 @@ class FlexKVConfig:
             head = int(_attr(model_config, "head_dim"))
         m.dtype = parse_dtype(_attr(model_config, "dtype", default=torch.bfloat16))
         self._apply_kv_dtype(_attr(server_args, "kv_cache_dtype", default="auto"), head)
+        if m.use_mla and _attr(model_config, "index_head_dim", default=None) is not None and \
+                m.dtype == torch.float8_e4m3fn:
+            # sparse-attention fp8 latent cache: fp8 latent + one fp32 scale per 128 values + bf16 rope part,
+            # all counted in bytes of the 1-byte element (flexkv/integration/config.py:506-518)
+            rank = int(_attr(model_config, "kv_lora_rank", default=512))
+            rope = int(_attr(model_config, "qk_rope_head_dim", default=64))
+            if rank % 128:
+                raise ValueError(f"kv_lora_rank {rank} must be a multiple of 128 for the fp8 latent cache layout")
+            m.head_size = rank + rank // 128 * 4 + rope * torch.bfloat16.itemsize
         self._finish(int(page_size))
 
     # ---- TensorRT-LLM --------------------------------------------------------------

@@ -94,3 +94,18 @@ def test_model_config_parallel_layout():
     m.freeze()
     with pytest.raises(Exception):
         m.num_layers = 1
+
+
+def test_sglang_fp8_latent_cache_with_indexer_has_the_packed_head_width():
+    from types import SimpleNamespace as NS
+    from flexkv_b200.integration.config import FlexKVConfig
+    c = FlexKVConfig()
+    c.post_init_from_sglang_config(NS(kv_cache_dtype="fp8_e4m3"),
+                                   NS(num_hidden_layers=4, is_mla=True, kv_lora_rank=512, qk_rope_head_dim=64,
+                                      index_head_dim=128, dtype=torch.bfloat16), 64)
+    assert c.model_config.dtype == torch.float8_e4m3fn and c.model_config.head_size == 512 + 16 + 128
+    c = FlexKVConfig()
+    c.post_init_from_sglang_config(NS(kv_cache_dtype="auto"),
+                                   NS(num_hidden_layers=4, is_mla=True, kv_lora_rank=512, qk_rope_head_dim=64,
+                                      dtype=torch.bfloat16), 64)
+    assert c.model_config.head_size == 576
