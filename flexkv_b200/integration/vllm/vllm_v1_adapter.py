@@ -310,11 +310,17 @@ def infer_vllm_gpu_layout(kv_caches: Sequence[torch.Tensor], tokens_per_block: i
                           use_mla: bool) -> KVCacheLayout:
     """Tells the two vLLM cache shapes apart by inspecting the real tensor:
     flash-attn ``[2, N, T, H, D]`` vs flashinfer / triton ``[N, 2, T, H, D]``; MLA is
-    ``[N, T, D]`` (flexkv/integration/vllm/vllm_v1_adapter.py:846-905)."""
+    ``[N, T, D]``; packed single-region caches are ``[N, H, T, W]`` (flexkv/integration/vllm/vllm_v1_adapter.py:846-905)."""
     t = kv_caches[0]
     L = len(kv_caches)
     if use_mla or t.dim() == 3:
         return KVCacheLayout(KVCacheLayoutType.LAYERFIRST, L, t.shape[0], tokens_per_block, 1, t.shape[-1], is_mla=True)
+    if t.dim() == 4:
+        # packed caches without a K/V axis: (blocks, H, tokens, 2 * D), or FlashInfer NVFP4 (blocks, 2 * H,
+        # tokens, D packed). One region per block and layer; the chunk moves whole, so the order of heads and
+        # tokens inside it is the engine's business (flexkv/integration/vllm/vllm_v1_adapter.py:852-874)
+        return KVCacheLayout(KVCacheLayoutType.LAYERFIRST, L, t.shape[0], t.shape[2], t.shape[1], t.shape[3],
+                             is_mla=True)
     if t.dim() != 5:
         raise ValueError(f"unsupported vLLM KV cache shape {tuple(t.shape)}")
     if t.shape[0] == 2 and t.shape[1] != 2:

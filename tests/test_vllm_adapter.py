@@ -111,6 +111,9 @@ def test_layout_inference_and_config_mapping():
     c = [torch.empty(10, 16, 576) for _ in range(3)]
     assert infer_vllm_gpu_layout(a, 16, 4, 64, False).type.value == "LAYERFIRST"
     assert infer_vllm_gpu_layout(b, 16, 4, 64, False).type.value == "LAYERBLOCK"
+    packed = [torch.zeros(8, 4, 16, 72, dtype=torch.uint8) for _ in range(3)]      # no K/V axis: one region per block
+    lay = infer_vllm_gpu_layout(packed, 16, 4, 72, False)
+    assert (lay.kv_dim, lay.num_block, lay.tokens_per_block, lay.get_chunk_size()) == (1, 8, 16, 4 * 16 * 72)
     lay = infer_vllm_gpu_layout(c, 16, 1, 576, True)
     assert lay.is_mla and lay.kv_dim == 1 and lay.num_block == 10
     hf = NS(num_hidden_layers=32, num_key_value_heads=8, num_attention_heads=32, hidden_size=4096, head_dim=128)
