@@ -83,6 +83,23 @@ def _block_ids_of(blocks: Any) -> List[int]:
     return list(blocks)
 
 
+def _should_offload(request: Any) -> bool:
+    """A request's KV is offloaded when it finished normally (stop or length), or when it was aborted and the
+    caller asked for the offload with ``offload_kv_on_finish`` (a router that moves the request elsewhere);
+    any other abort leaves nothing behind (flexkv/integration/vllm/vllm_v1_adapter.py:522-532). Request
+    objects that expose no finish reason count as finished normally."""
+    get = getattr(request, "get_finished_reason", None)
+    if get is None:
+        return True
+    reason = get()
+    name = str(getattr(reason, "name", reason)).upper()
+    if name in ("STOP", "LENGTH"):
+        return True
+    if name == "ABORT":
+        return bool(getattr(request, "offload_kv_on_finish", False))
+    return reason is None and not callable(getattr(request, "is_finished", None))
+
+
 class FlexKVSchedulerConnector:
     def __init__(self, flexkv_config: FlexKVConfig, kv_manager: Any = None, dp_client_id: int = 0) -> None:
         self.cfg = flexkv_config
@@ -193,6 +210,8 @@ class FlexKVSchedulerConnector:
         pending = self.req_to_get.pop(rid, None)
         if pending is not None:
             self.to_cancel.append(pending.task_id)
+        if not _should_offload(request):
+            return False, None
         tokens = _tokens_of(request)
         n = ((len(tokens) - 1) // self.T) * self.T
         if n <= 0:

@@ -209,3 +209,27 @@ def test_worker_registers_indexer_caches_as_a_second_group_and_the_manager_adopt
             assert torch.equal(kv2[l][:, dst], want_kv[l]) and torch.equal(idx2[l][dst], want_idx[l])
     finally:
         mgr.shutdown()
+
+
+def test_aborted_requests_offload_only_on_request():
+    """An abort leaves nothing behind unless the caller set ``offload_kv_on_finish``; stop and length finishes
+    offload as before (reference: tests/test_vllm_abort_offload_directive.py)."""
+    conn, kv, mgr = make()
+    try:
+        blocks = [10, 11, 12, 13, 14]
+        tok = np.arange(700, 700 + 4 * T + 1)
+        aborted = req("x", tok, get_finished_reason=lambda: NS(name="ABORT"))
+        assert conn.request_finished(aborted, blocks) == (False, None)
+        assert conn.stats.num_put_requests == 0
+        for reason in ("STOP", "LENGTH"):
+            r = req("ok-" + reason, tok + (1 if reason == "LENGTH" else 0), get_finished_reason=lambda n=reason: NS(name=n))
+            keep, _ = conn.request_finished(r, blocks)
+            assert keep
+        moved = req("y", tok + 7, get_finished_reason=lambda: NS(name="ABORT"), offload_kv_on_finish=True)
+        keep, _ = conn.request_finished(moved, blocks)
+        assert keep
+        conn.launch_tasks()
+        s, _ = drain(conn, want_send={"ok-STOP", "ok-LENGTH", "y"})
+        assert s == {"ok-STOP", "ok-LENGTH", "y"}
+    finally:
+        conn.shutdown()
