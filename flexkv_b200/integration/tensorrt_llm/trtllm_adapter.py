@@ -56,6 +56,13 @@ class FlexKVSchedulerConnector:
         self.core.update_state_after_alloc(v, list(block_ids), task.num_tokens if task else 0)
 
     def request_finished(self, request: Any, cache_block_ids: Sequence[int]) -> bool:
+        """True while a transfer still needs the request's blocks. A request that did not finish normally
+        (cancelled, errored) leaves nothing behind (flexkv/integration/tensorrt_llm/trtllm_adapter.py:291-297)."""
+        def flag(name: str) -> bool:
+            v = getattr(request, name, True)
+            return bool(v() if callable(v) else v)
+        if not (flag("is_finished") and flag("is_finished_normal")):
+            return False
         return self.core.request_finished(_LlmRequestView(request), cache_block_ids)[0]
 
     def build_connector_meta(self, scheduler_output: Any = None) -> Dict[str, Set[str]]:

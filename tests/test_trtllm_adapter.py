@@ -66,3 +66,17 @@ def test_offload_and_restore_through_the_single_pool():
         assert torch.equal(pool[20], saved[20])                       # the block the engine computed is untouched
     finally:
         conn.shutdown()
+
+
+def test_a_request_that_did_not_finish_normally_is_not_offloaded():
+    conn, pool, mgr = make()
+    try:
+        r = llm_request(21, np.arange(900, 900 + 3 * T + 1))
+        r.is_finished = True
+        r.is_finished_normal = False
+        assert conn.request_finished(r, [1, 2, 3, 4]) is False
+        assert conn.core.stats.num_put_requests == 0
+        r.is_finished_normal = True
+        assert conn.request_finished(r, [1, 2, 3, 4]) is True
+    finally:
+        conn.shutdown()
