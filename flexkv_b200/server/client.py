@@ -107,7 +107,20 @@ class KVDPClient:
     def withdraw_gpu_blocks(self, gpu_block_ids) -> List[int]:
         return self._call(R.WithdrawGpuBlocksRequest(gpu_block_ids=gpu_block_ids)).value
 
+    def unregister(self) -> int:
+        """Leaves the shared server (which keeps running for the other clients): tasks of this client that were
+        matched but never launched are cancelled there. Returns how many."""
+        if not self._registered:
+            return 0
+        n = int(self._call(R.UnregisterDPClientRequest(), timeout=10.0).value or 0)
+        self._registered = False
+        return n
+
     def shutdown(self) -> None:
+        try:
+            self.unregister()
+        except Exception:  # noqa: BLE001 - the server may already be gone
+            pass
         self._send.close()
         self._recv.close()
 

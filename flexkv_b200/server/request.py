@@ -127,6 +127,12 @@ class ShutdownRequest(Request):
 
 
 @dataclass
+class UnregisterDPClientRequest(Request):
+    """One data-parallel client leaves; the shared server keeps running for the others
+    (flexkv/server/server.py:486-490)."""
+
+
+@dataclass
 class Response:
     dp_client_id: int
     seq: int = 0

@@ -48,6 +48,7 @@ class KVServer:
             R.PublishGpuBlocksRequest: self._on_publish,
             R.WithdrawGpuBlocksRequest: self._on_withdraw,
             R.ShutdownRequest: self._on_shutdown,
+            R.UnregisterDPClientRequest: self._on_unregister_dp,
         }
 
     # ---- process / thread front ends ---------------------------------------------------
@@ -70,7 +71,10 @@ class KVServer:
         t.start()
         return ServerHandle(thread=t, server=srv, endpoint=recv_endpoint)
 
+    _leaving: list = []
+
     def run(self) -> None:
+        self._leaving = []
         self.engine.start()
         self._running = True
         poller = zmq.Poller()
@@ -94,6 +98,10 @@ class KVServer:
                 rsp = R.Response(req.dp_client_id, req.seq, error=repr(e))
             if rsp is not None:
                 self._reply(rsp)
+            while self._leaving:                       # after the answer went out
+                gone = self._clients.pop(self._leaving.pop(), None)
+                if gone is not None:
+                    gone.close(linger=1000)
         self.engine.shutdown()
         for s in self._clients.values():
             s.close()
@@ -157,6 +165,19 @@ class KVServer:
 
     def _on_withdraw(self, q: R.WithdrawGpuBlocksRequest):
         return R.Response(q.dp_client_id, q.seq, value=self.engine.withdraw_gpu_blocks(q.gpu_block_ids, q.dp_client_id))
+
+    def _on_unregister_dp(self, q: R.UnregisterDPClientRequest):
+        """Detaches one client: its tasks that were matched but never launched give their reservations back, its
+        published GPU blocks leave the peer directory, and its reply socket is closed after this answer."""
+        stale = [tid for tid, t in list(self.engine.tasks.items())
+                 if getattr(t, "dp_id", None) == q.dp_client_id and t.status.name == "UNREADY"]
+        if stale:
+            self.engine.cancel_tasks(stale)
+        pd = self.engine.cache_engine.peer_directory
+        if pd is not None:
+            pd.clear_rank(q.dp_client_id)
+        self._leaving.append(q.dp_client_id)
+        return R.Response(q.dp_client_id, q.seq, value=len(stale))
 
     def _on_shutdown(self, q):
         self._running = False

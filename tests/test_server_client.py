@@ -53,6 +53,15 @@ def test_two_dp_ranks_share_one_server():
         assert int(m0.get_match(tok)[1].sum()) == 0
         with pytest.raises(RuntimeError):
             m0.launch(12345, slots(dst, T))        # server-side errors come back as exceptions
+        # a client that leaves gives back what it had reserved; the server keeps serving the other one
+        tid = m0.put_async(tok, slots(src, T))
+        assert m0.wait(tid, completely=True)[tid].status.value == "success"
+        pending, mask = m1.get_match(tok)
+        assert int(mask.sum()) == 6 * T
+        assert m1.dp_client.unregister() == 1
+        assert m1.dp_client.unregister() == 0                      # already gone
+        assert int(m0.get_match(tok)[1].sum()) == 6 * T
+        assert m1.is_ready()                                       # registers again on its next call
     finally:
         m1.shutdown(); m0.shutdown()
 
