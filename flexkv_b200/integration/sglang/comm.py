@@ -102,10 +102,22 @@ class FlexKVLayerLoadingEvent:
                 except BlockingIOError:
                     break
 
+    finished = True          # nothing registered, nothing being waited for: the set may be handed out again
+    wait_started = False     # a forward pass began consuming this set
+
     def reset_for_new_transfer(self) -> None:
         with self._lock:
             self._drain()
             self._pending = 0
+            self.finished, self.wait_started = False, False
+
+    def mark_reusable(self) -> None:
+        """Returns the set to the ring. The caller has made sure that no restore can still signal it (every
+        launched layerwise task was waited for) - flexkv/integration/sglang/comm.py:672-682."""
+        with self._lock:
+            self._drain()
+            self._pending = 0
+            self.finished, self.wait_started = True, False
 
     def add_transfer(self) -> None:
         with self._lock:
@@ -121,6 +133,7 @@ class FlexKVLayerLoadingEvent:
     def wait(self, layer: int, timeout: float = 240.0) -> None:
         """Blocks until every restore registered on this set has signalled `layer`."""
         need = self._pending
+        self.wait_started = True
         fd = self.fds[layer]
         deadline = time.monotonic() + timeout
         got = 0
@@ -166,6 +179,45 @@ class FlexKVLayerDoneCounter:
         self._task_to_counter[task_id] = producer_id
         self.events[producer_id].add_transfer()
 
+    def expected_transfer_count(self, counter_id: int) -> int:
+        """Checks, without changing anything, that a restore may still be added to set ``counter_id`` and returns
+        how many are registered on it. Followers call it with the leader's choice, so that a rank whose batch
+        boundary differs from the leader's fails loudly instead of waiting on the wrong set
+        (flexkv/integration/sglang/comm.py:798-844)."""
+        if not 0 <= counter_id < self.num_counters:
+            raise ValueError(f"invalid counter id {counter_id}, must be in [0, {self.num_counters})")
+        ev = self.events[counter_id]
+        if ev.wait_started:
+            raise RuntimeError(f"counter {counter_id} is already being consumed by a forward pass")
+        if self._consumer == counter_id and ev.finished:
+            raise RuntimeError(f"counter {counter_id} is marked finished but still selected for consumption")
+        return ev.pending_transfers()
+
+    def register_task_with_explicit_counter_id(self, task_id: int, counter_id: int) -> None:
+        """Follower side of a batched restore: the leader chose the set."""
+        self.expected_transfer_count(counter_id)
+        if task_id in self._task_to_counter:
+            raise RuntimeError(f"task {task_id} is already registered")
+        ev = self.events[counter_id]
+        if ev.finished:
+            ev.reset_for_new_transfer()
+        self._producer = counter_id
+        self.register_task(task_id, counter_id)
+
+    def abort_unregistered_selection(self, producer_id: int) -> None:
+        """Gives back a set the leader selected with ``update_producer`` when nothing was registered on it after
+        all (the plan turned out empty)."""
+        if not 0 <= producer_id < self.num_counters:
+            raise ValueError(f"invalid producer id {producer_id}, must be in [0, {self.num_counters})")
+        ev = self.events[producer_id]
+        if self._consumer == producer_id or ev.wait_started:
+            raise RuntimeError(f"counter {producer_id} is already being consumed")
+        if ev.pending_transfers() != 0:
+            raise RuntimeError(f"counter {producer_id} already has registered transfers")
+        ev.mark_reusable()
+        if self._producer == producer_id:
+            self._producer = (producer_id - 1) % self.num_counters
+
     def rollback_prepared_transfer(self, task_id: int) -> None:
         c = self._task_to_counter.pop(task_id, None)
         if c is not None:
@@ -180,12 +232,12 @@ class FlexKVLayerDoneCounter:
             return
         self.events[self._consumer].wait(layer, timeout)
         if layer == self.num_layers - 1:
-            self.events[self._consumer].reset_for_new_transfer()
+            self.events[self._consumer].mark_reusable()
             self._consumer = -1
 
     def reset(self) -> None:
         for e in self.events:
-            e.reset_for_new_transfer()
+            e.mark_reusable()
         self._producer = self._consumer = -1
         self._task_to_counter.clear()
 

@@ -225,21 +225,26 @@ class FlexKVConnector:
         layer; the forward pass waits in the KV pool's layer hook."""
         ids: List[int] = []
         counter = 0
+        pairs_selected = False
         if self.is_leader:
             pend = [self._pending_loads.pop(r, None) for r in rids]
             pairs = [(p, sm) for p, sm in zip(pend, slot_mappings) if p is not None]
             if pairs:
                 counter = self.layer_counter.update_producer() if self.layer_counter else 0
+                pairs_selected = self.layer_counter is not None
                 sms = [torch.as_tensor(sm).cpu().numpy().astype(np.int64)[:p.matched_tokens] for p, sm in pairs]
                 ids = self.mgr.launch([p.task_id for p, _ in pairs], sms, as_batch=True,
                                       layerwise_transfer=self.layerwise, counter_id=counter)
         manifest = self.comm.broadcast({"ids": ids, "counter": counter})
         if self.layer_counter is not None and manifest["ids"]:
-            if not self.is_leader:
-                self.layer_counter.update_producer()
             for t in manifest["ids"]:
-                self.layer_counter.register_task(t, manifest["counter"])
+                if self.is_leader:
+                    self.layer_counter.register_task(t, manifest["counter"])
+                else:
+                    self.layer_counter.register_task_with_explicit_counter_id(t, manifest["counter"])
             self.layer_counter.set_consumer(manifest["ids"][0])
+        elif self.layer_counter is not None and self.is_leader and pairs_selected:
+            self.layer_counter.abort_unregistered_selection(counter)
         return manifest["ids"]
 
     def drain_launched_loads(self, task_ids: Sequence[int], timeout: float = 60.0) -> bool:

@@ -151,3 +151,36 @@ def test_pipeline_stage_leaders_receive_the_plan(tmp_path):
     p = subprocess.run(cmd, capture_output=True, text=True, timeout=180, env=dict(os.environ, PYTHONPATH=ROOT))
     assert p.returncode == 0, p.stdout[-2000:] + p.stderr[-2000:]
     assert p.stdout.count("PP_OK") == 4
+
+
+def test_layer_done_counter_guards_rank_skewed_batches():
+    """A follower registers on the set the leader chose; a set that a forward pass already consumes, or a task
+    registered twice, is refused; an empty selection goes back to the ring
+    (reference: flexkv/integration/sglang/comm.py:798-925)."""
+    import pytest
+    c = FlexKVLayerDoneCounter(num_layers=2, num_counters=3)
+    try:
+        assert c.expected_transfer_count(1) == 0
+        c.register_task_with_explicit_counter_id(5, 1)             # the leader said: set 1
+        assert c.expected_transfer_count(1) == 1
+        with pytest.raises(RuntimeError):
+            c.register_task_with_explicit_counter_id(5, 1)
+        with pytest.raises(ValueError):
+            c.expected_transfer_count(7)
+        c.set_consumer(5)
+        fds = c.fds_per_counter()[1]
+        for l in range(2):
+            os.write(fds[l], struct.pack("Q", 1))
+        c.wait_until(0, timeout=5)
+        with pytest.raises(RuntimeError):                          # the forward pass is already reading set 1
+            c.register_task_with_explicit_counter_id(6, 1)
+        c.wait_until(1, timeout=5)
+        assert c.events[1].finished and c.expected_transfer_count(1) == 0      # back in the ring
+        p = c.update_producer()
+        c.abort_unregistered_selection(p)                          # the leader's plan turned out empty
+        assert c.events[p].finished and c.update_producer() == p
+        c.register_task(9, p)
+        with pytest.raises(RuntimeError):
+            c.abort_unregistered_selection(p)
+    finally:
+        c.close()
