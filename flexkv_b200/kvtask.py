@@ -82,6 +82,15 @@ class KVTask:
     def is_completed(self) -> bool:
         return self.status in (TaskStatus.COMPLETED, TaskStatus.CANCELLED, TaskStatus.FAILED)
 
+    def shed_heavy_resources(self) -> None:
+        """A finished task is kept until its answer was fetched (or its time-to-live ran out); what it no longer
+        needs - token ids, slot mapping, the op graph, callbacks - goes at once, status and return mask stay
+        (flexkv/kvtask.py:106-113)."""
+        self.graph = None
+        self.token_ids = self.token_mask = self.slot_mapping = None
+        self.op_callback_dict = {}
+        self.op_remap = {}
+
 
 class ExpiringDict(OrderedDict):
     """Insertion-ordered dict that forgets entries older than ``ttl`` seconds or
@@ -405,9 +414,11 @@ class KVTaskEngine:
                 m.failed_gpu_blocks = slot_mapping_to_block_ids(np.asarray(m.slot_mapping, dtype=np.int64),
                                                                 self.cache_config.tokens_per_block)
             log_op(m.task_type.value, "finish", "ok" if success else "failed", task_id=m.task_id)
+            m.shed_heavy_resources()
         if task.children:
             task.status = TaskStatus.COMPLETED if success else TaskStatus.FAILED
             task.task_end_op_finished = True
+            task.shed_heavy_resources()
 
     def _response(self, task: KVTask) -> KVResponse:
         if task.is_completed():

@@ -77,6 +77,10 @@ def test_put_get_lifecycle():
     assert e.try_wait([tid]) == {}                                      # not finished: omitted
     assert e.wait([tid], timeout=0.05)[tid].status == S.TIMEOUT
     h.run(h.graphs[0])
+    e._update_tasks(timeout=0)
+    done = e.tasks[tid]                                                 # finished, answer not fetched yet:
+    assert done.graph is None and done.token_ids is None and done.slot_mapping is None     # the heavy parts are gone
+    assert done.return_mask.sum() == 20
     r = e.wait([tid])[tid]
     assert r.status == S.SUCCESS and r.return_mask.sum() == 20
     assert e.wait([tid])[tid].status == S.NOTFOUND                      # released once returned
