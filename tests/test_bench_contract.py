@@ -25,3 +25,13 @@ def test_entry_module_exposes_build_and_smoke():
     g.build()                                     # a no-op when the content hashes match
     from flexkv_b200 import _native
     assert os.path.dirname(_native.C.__file__) == os.path.join(ROOT, "flexkv_b200")     # in-tree, not site-packages
+
+
+def test_worker_benchmark_runs_on_the_cpu_data_plane(tmp_path):
+    out = subprocess.run([sys.executable, os.path.join(ROOT, "benchmarks", "benchmark_workers.py"), "--device", "cpu",
+                          "--blocks", "8", "--iters", "1", "--warmup", "1", "--ssd-dir", str(tmp_path / "ssd"),
+                          "--out", str(tmp_path / "rows.json")], capture_output=True, text=True, timeout=200)
+    assert out.returncode == 0, out.stdout[-1500:] + out.stderr[-1500:]
+    rows = json.loads((tmp_path / "rows.json").read_text())
+    assert [r["type"] for r in rows] == ["D2H", "H2D", "H2DISK", "DISK2H"]
+    assert all(r["bytes"] == 8 * 2097152 and r["gbs"] > 0 for r in rows)
