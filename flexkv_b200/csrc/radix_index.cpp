@@ -446,6 +446,10 @@ std::vector<int64_t> RadixIndex::reset() {
 
 IndexSnapshot RadixIndex::export_ready() const {
   IndexSnapshot snap;
+  snap.hashes.reserve((size_t)total_blocks_);
+  snap.blocks.reserve((size_t)total_blocks_);
+  snap.parents.reserve((size_t)live_nodes_);
+  snap.sizes.reserve((size_t)live_nodes_);
   // explicit stack of (node, position of its parent in the image); children in key order
   // so that the image of a given tree is deterministic
   std::vector<std::pair<int32_t, int32_t>> stack;
