@@ -129,6 +129,41 @@ def bench_planner(a):
                 requests=a.requests)
 
 
+def bench_warm_restart(a):
+    """Image of a large SSD index: export, import into an empty index, reservation of its blocks."""
+    import io
+    from flexkv_b200 import _native
+    C = _native.C
+    N = 1_000_000
+    idx = C.RadixIndex(T, N, "lru", 0.0, 2)
+    rng = np.random.default_rng(0)
+    prefixes = [rng.integers(1, 2**63, size=128, dtype=np.int64).astype(np.uint64) for _ in range(64)]
+    nxt = 0
+    for i in range(1950):
+        s = np.concatenate([prefixes[i % 64], rng.integers(1, 2**63, size=384, dtype=np.int64).astype(np.uint64)])
+        m = idx.match_prefix(s, len(s), False)
+        need = len(s) - m.num_matched_blocks
+        idx.insert(np.arange(nxt, nxt + need, dtype=np.int64), s, len(s), True, m)
+        nxt += need
+    t_exp, t_imp, t_res = [], [], []
+    for _ in range(a.reps):
+        t0 = time.perf_counter()
+        img = idx.export_ready()
+        t1 = time.perf_counter()
+        other = C.RadixIndex(T, N, "lru", 0.0, 2)
+        n = other.import_snapshot(*img)
+        t2 = time.perf_counter()
+        pool = C.BlockPool(N)
+        pool.reserve(img[3])
+        t3 = time.perf_counter()
+        t_exp.append(t1 - t0); t_imp.append(t2 - t1); t_res.append(t3 - t2)
+    buf = io.BytesIO()
+    np.savez(buf, parents=img[0], sizes=img[1], hashes=img[2], blocks=img[3])
+    return dict(bench="ssd_index_image", blocks=int(n), nodes=int(idx.num_nodes()),
+                export_ms=round(statistics.median(t_exp) * 1e3, 1), import_ms=round(statistics.median(t_imp) * 1e3, 1),
+                reserve_ms=round(statistics.median(t_res) * 1e3, 1), image_mb=round(buf.tell() / 1e6, 1))
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--reps", type=int, default=5)
@@ -136,7 +171,7 @@ def main() -> None:
     ap.add_argument("--requests", type=int, default=200)
     ap.add_argument("--out", default="")
     a = ap.parse_args()
-    rows = [bench_hash(a)] + bench_index(a) + [bench_planner(a)]
+    rows = [bench_hash(a)] + bench_index(a) + [bench_planner(a), bench_warm_restart(a)]
     for r in rows:
         print(json.dumps(r))
     if a.out:
