@@ -138,6 +138,9 @@ class KVTPClient:
             self.tp_rank = intra_client_id
         self._ctx = zmq.Context.instance()
         self._sock = get_zmq_socket(self._ctx, zmq.PUSH, gpu_register_port, bind=False)
+        # a registration must survive a client that is dropped right after sending it (the connection to the
+        # data plane is made asynchronously): queued messages are flushed for up to 10 s after close
+        self._sock.setsockopt(zmq.LINGER, 10000)
         self._handles: List[TensorSharedHandle] = []
 
     def register_to_server(self, kv_caches: Sequence[torch.Tensor], kv_layout: KVCacheLayout,
