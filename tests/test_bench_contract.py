@@ -35,3 +35,10 @@ def test_worker_benchmark_runs_on_the_cpu_data_plane(tmp_path):
     rows = json.loads((tmp_path / "rows.json").read_text())
     assert [r["type"] for r in rows] == ["D2H", "H2D", "H2DISK", "DISK2H"]
     assert all(r["bytes"] == 8 * 2097152 and r["gbs"] > 0 for r in rows)
+
+
+def test_standalone_example_runs_on_the_cpu_data_plane():
+    out = subprocess.run([sys.executable, os.path.join(ROOT, "examples", "standalone_roundtrip.py"), "--device", "cpu",
+                          "--tokens", "128"], capture_output=True, text=True, timeout=200)
+    assert out.returncode == 0, out.stdout[-1500:] + out.stderr[-1500:]
+    assert "bytes identical=True" in out.stdout
