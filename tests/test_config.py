@@ -109,3 +109,16 @@ def test_sglang_fp8_latent_cache_with_indexer_has_the_packed_head_width():
                                    NS(num_hidden_layers=4, is_mla=True, kv_lora_rank=512, qk_rope_head_dim=64,
                                       dtype=torch.bfloat16), 64)
     assert c.model_config.head_size == 576
+
+
+def test_response_helpers_keep_the_reference_names_and_values():
+    import numpy as np
+    from flexkv_b200 import KVResponse, KVResponseStatus
+    assert {s.name: s.value for s in KVResponseStatus} == {
+        "SUCCESS": "success", "NOTFOUND": "not_found", "UNREADY": "unready", "TIMEOUT": "timeout",
+        "CANCELLED": "cancelled", "FAILED": "failed"}
+    r = KVResponse(KVResponseStatus.SUCCESS, 3, [np.array([1, 1, 0], bool), np.array([0, 1], bool)])
+    assert r.ok and r.num_tokens() == 3 and r.get_mask(1).tolist() == [False, True]
+    with pytest.raises(AssertionError):
+        r.get_mask(2)
+    assert not KVResponse(KVResponseStatus.TIMEOUT, 4, None).ok and not KVResponseStatus.TIMEOUT.terminal
