@@ -29,6 +29,9 @@ from flexkv_b200.storage.gpu_layout import register_tensors  # noqa: E402
 C = _native.C
 
 
+HOST_LAYOUT = "blockfirst"
+
+
 def build(shape, ngpu, gpu_blocks, host_blocks, engine_layout, notify, ctas, tile, tp_split, lpb=1):
     regs, caches = [], []
     for d in range(ngpu):
@@ -43,6 +46,10 @@ def build(shape, ngpu, gpu_blocks, host_blocks, engine_layout, notify, ctas, til
                                  numa_node=C.gpu_numa_node(0))
     host = dict(base=region.ptr, layer_stride=shape.kv_dim * chunk, kv_stride=chunk, block_stride=block_bytes,
                 num_blocks=host_blocks)
+    if HOST_LAYOUT == "layerfirst" and not tp_split:
+        # [layer][kv][block][chunk]: one layer of consecutive blocks is one contiguous run of host memory
+        host = dict(base=region.ptr, layer_stride=shape.kv_dim * host_blocks * chunk, kv_stride=host_blocks * chunk,
+                    block_stride=chunk, num_blocks=host_blocks)
     opts = dict(num_layers=shape.num_layers, kv_dim=shape.kv_dim, chunk_bytes=chunk,
                 cpu_tp_stride=block_bytes // slices if tp_split else 0, shared_kv=not tp_split,
                 max_blocks_per_op=max(gpu_blocks, 4096), notify_mode=notify, num_counters=3, layers_per_batch=lpb,
@@ -79,7 +86,7 @@ def scenario_notify(a):
             per_gpu = layers * blocks * chunk
             row = dict(scale=name, notify=notify + ("+fused" if lpb == 0 else ""), gpus=a.gpus, p50_ms=round(p50, 3),
                        gbs_per_gpu=round(per_gpu / p50 / 1e6, 2), bytes_per_gpu=per_gpu,
-                       gpu_ms=round(r.total_ms, 3))
+                       gpu_ms=round(r.total_ms, 3), host_layout=HOST_LAYOUT)
             out.append(row)
             print(json.dumps(row), flush=True)
             del grp
@@ -157,9 +164,13 @@ def main():
     ap.add_argument("--stub-ctas", type=int, default=148)
     ap.add_argument("--layers-per-batch", type=int, default=0, help="0 = one fused launch with per-layer flags")
     ap.add_argument("--out", default="")
+    ap.add_argument("--host-layout", default="blockfirst", choices=["blockfirst", "layerfirst"],
+                    help="host pool layout (FLEXKV_CPU_LAYOUT of a deployment)")
     ap.add_argument("--scales", nargs="*", default=[], help="notify: subset of small medium large")
     ap.add_argument("--modes", nargs="*", default=[], help="notify: subset of hostfunc polling flag flag+fused")
     a = ap.parse_args()
+    global HOST_LAYOUT
+    HOST_LAYOUT = a.host_layout
     rows = scenario_notify(a) if a.scenario == "notify" else scenario_overlap(a)
     if a.out:
         os.makedirs(os.path.dirname(os.path.abspath(a.out)), exist_ok=True)

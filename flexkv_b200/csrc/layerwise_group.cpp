@@ -195,6 +195,7 @@ void LayerwiseGroup::rank_main(int r) {
     check(cudaMemset(rk.dev_flags, 0, (size_t)C * L * sizeof(uint32_t)), "cudaMemset(flags)");
     check(cudaMalloc((void**)&rk.done_counter, (size_t)L * sizeof(uint32_t)), "cudaMalloc(counter)");
     check(cudaMemset(rk.done_counter, 0, (size_t)L * sizeof(uint32_t)), "cudaMemset(counter)");
+    check(cudaMalloc((void**)&rk.dev_ids, 2 * (size_t)opt_.group.max_blocks_per_op * sizeof(int64_t)), "cudaMalloc(ids)");
     check(cudaHostAlloc((void**)&rk.host_flags, (size_t)C * L * sizeof(uint32_t),
                         cudaHostAllocPortable | cudaHostAllocMapped), "cudaHostAlloc(flags)");
     std::memset(rk.host_flags, 0, (size_t)C * L * sizeof(uint32_t));
@@ -231,6 +232,7 @@ void LayerwiseGroup::rank_main(int r) {
   if (rk.ev_begin) cudaEventDestroy(rk.ev_begin);
   if (rk.dev_flags) cudaFree(rk.dev_flags);
   if (rk.done_counter) cudaFree(rk.done_counter);
+  if (rk.dev_ids) cudaFree(rk.dev_ids);
   if (rk.host_flags) cudaFreeHost(rk.host_flags);
   if (rk.status) cudaFreeHost(rk.status);
   if (rk.stream) cudaStreamDestroy(rk.stream);
@@ -249,6 +251,24 @@ void LayerwiseGroup::update_group_gpu_ptrs(int group, int rank, const std::vecto
   mgroups_.at((size_t)group).gpus.at((size_t)rank).ptrs = ptrs;
 }
 
+// Copies a job's block ids from the mapped host ring into device memory, in stream order before the launches
+// that read them. A layer-major walk touches a new 32-id window every few tiles; fetched from host memory each of
+// those reads would wait behind the bulk reads already queued on the link.
+cudaError_t LayerwiseGroup::stage_ids(Rank& rk, const Job& j, const int64_t*& gpu_ids, const int64_t*& cpu_ids) {
+  if (j.n <= 0 || rk.dev_ids == nullptr) return cudaSuccess;
+  const size_t half = (size_t)opt_.group.max_blocks_per_op;
+  cudaError_t err = cudaMemcpyAsync(rk.dev_ids, j.gpu_blocks, (size_t)j.n * sizeof(int64_t), cudaMemcpyHostToDevice,
+                                    rk.stream);
+  if (err == cudaSuccess)
+    err = cudaMemcpyAsync(rk.dev_ids + half, j.cpu_blocks, (size_t)j.n * sizeof(int64_t), cudaMemcpyHostToDevice,
+                          rk.stream);
+  if (err == cudaSuccess) {
+    gpu_ids = rk.dev_ids;
+    cpu_ids = rk.dev_ids + half;
+  }
+  return err;
+}
+
 // Multi-group restore of one rank: model layer by model layer, one launch per member; the last
 // member's launch carries the completion signal of the model layer (same stream, so the earlier
 // members have landed when its last CTA publishes the flag).
@@ -261,6 +281,9 @@ void LayerwiseGroup::run_job_members(int r, const Job& j) {
   uint32_t* hflags = rk.host_flags + (size_t)j.counter * L;
   uint32_t* dflags = rk.dev_flags + (size_t)j.counter * L;
   cudaError_t err = cudaEventRecord(rk.ev_begin, rk.stream);
+  const int64_t* gpu_ids = j.gpu_blocks;
+  const int64_t* cpu_ids = j.cpu_blocks;
+  if (err == cudaSuccess) err = stage_ids(rk, j, gpu_ids, cpu_ids);
   for (int l = 0; l < L && err == cudaSuccess; ++l) {
     const auto& ms = members_[(size_t)l];
     bool signalled = false;
@@ -268,7 +291,7 @@ void LayerwiseGroup::run_job_members(int r, const Job& j) {
       const LayerwiseMemberGroup& g = mgroups_[(size_t)ms[k].group];
       KvCopyParams p;
       bool skip = false;
-      fill_kv_params(g.gpus[(size_t)r], g.host, g.group, r, R, j.gpu_blocks, j.cpu_blocks, j.n, true,
+      fill_kv_params(g.gpus[(size_t)r], g.host, g.group, r, R, gpu_ids, cpu_ids, j.n, true,
                      ms[k].local_layer, 1, 0, p, skip);
       p.status = rk.status;
       if (k + 1 == ms.size()) {
@@ -343,11 +366,14 @@ void LayerwiseGroup::run_job(int r, const Job& j) {
   cudaEvent_t* ev = rk.layer_ev.data() + (size_t)j.counter * L;
   uint32_t* hflags = rk.host_flags + (size_t)j.counter * L;
   cudaError_t err = cudaEventRecord(rk.ev_begin, rk.stream);
+  const int64_t* gpu_ids = j.gpu_blocks;
+  const int64_t* cpu_ids = j.cpu_blocks;
+  if (err == cudaSuccess) err = stage_ids(rk, j, gpu_ids, cpu_ids);
   for (int b = 0; b < batches && err == cudaSuccess; ++b) {
     const int l0 = b * B, l1 = std::min(L, l0 + B);
     KvCopyParams p;
     bool skip = false;
-    fill_kv_params(gpus_[(size_t)r], host_, opt_.group, r, R, j.gpu_blocks, j.cpu_blocks, j.n, true, l0, l1 - l0, 0,
+    fill_kv_params(gpus_[(size_t)r], host_, opt_.group, r, R, gpu_ids, cpu_ids, j.n, true, l0, l1 - l0, 0,
                    p, skip);
     p.status = rk.status;
     p.done_counter = rk.done_counter;

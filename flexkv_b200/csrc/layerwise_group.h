@@ -122,6 +122,8 @@ class LayerwiseGroup {
     uint32_t* dev_flags = nullptr;      // [counters][layers]
     uint32_t* host_flags = nullptr;     // mapped, [counters][layers]
     uint32_t* done_counter = nullptr;   // device scratch, one word per layer, zero between launches
+    int64_t* dev_ids = nullptr;         // [2][max_blocks] device copy of a job's block ids (gpu ids, then host ids):
+                                        // id reads from mapped host memory would queue behind the bulk reads on the link
     int32_t* status = nullptr;          // mapped, kStatusWords
     std::vector<cudaEvent_t> layer_ev;  // [counters][layers]
     cudaEvent_t ev_begin = nullptr;
@@ -140,6 +142,7 @@ class LayerwiseGroup {
   void rank_main(int r);
   void run_job(int r, const Job& j);
   void run_job_members(int r, const Job& j);
+  cudaError_t stage_ids(Rank& rk, const Job& j, const int64_t*& gpu_ids, const int64_t*& cpu_ids);
   void notify(int rank, int counter, int layer_lo, int layer_hi);
   static void CUDART_CB host_fn(void* arg);
 
