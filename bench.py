@@ -61,12 +61,14 @@ def parse_args():
     return ap.parse_args()
 
 
-def reference_unavailable() -> None:
-    # The reference's build aborts offline: its third_party/spdlog, xxHash and prometheus-cpp submodules
-    # are empty and the link line needs libxxhash and liburing, none of which exist on this image.
-    print(json.dumps({"impl": "reference", "unavailable":
-                      "reference does not build offline: setup.py aborts on the empty third_party/spdlog "
-                      "submodule and needs system xxhash/liburing headers that the image lacks"}))
+def run_reference(args) -> None:
+    """The unmodified reference, installed under baseline/_ref, through its own public API; nothing of
+    this repository's package is imported on this path (see baseline/reference_arm.py)."""
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("reference_arm", os.path.join(ROOT, "baseline", "reference_arm.py"))
+    arm = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(arm)
+    arm.run(args, ClockSampler)
 
 
 class ClockSampler:
@@ -123,7 +125,7 @@ class ClockSampler:
 def main() -> None:
     args = parse_args()
     if args.impl == "reference":
-        reference_unavailable()
+        run_reference(args)
         return
 
     import torch
