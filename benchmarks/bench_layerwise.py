@@ -114,17 +114,17 @@ def scenario_overlap(a):
         evs = []
         t0 = time.perf_counter()
         res = {}
+        epoch = grp.begin_restore(counter)     # the value this round's restore will publish to the layer flags
         th = threading.Thread(target=lambda: res.setdefault("r", grp.restore(gpu, cpu, counter)))
         th.start()
         # the model: per layer, wait (in stream order) for the layer's KV, then "compute"
-        time.sleep(0.002)     # let the restore record this round's per-layer events first
         for d in range(a.gpus):
             with torch.cuda.device(d):
                 e0 = torch.cuda.Event(enable_timing=True)
                 e1 = torch.cuda.Event(enable_timing=True)
                 e0.record(streams[d])
                 for l in range(L):
-                    grp.stream_wait_layer(d, counter, l, streams[d].cuda_stream)
+                    grp.stream_wait_layer(d, counter, l, streams[d].cuda_stream, epoch)
                     C.layer_stub(0, 0, busy_ns, 0, 0, 0, a.stub_ctas, streams[d].cuda_stream)
                 e1.record(streams[d])
                 evs.append((e0, e1))

@@ -31,6 +31,7 @@ KvCopyParams kv_params_from_dict(const py::dict& d) {
   auto ptrs = d["gpu_ptrs"].cast<std::vector<uint64_t>>();
   if ((int)ptrs.size() > kMaxGpuPtrs) throw std::invalid_argument("too many gpu tensors");
   for (size_t i = 0; i < ptrs.size(); ++i) p.gpu_ptrs[i] = ptrs[i];
+  p.num_gpu_ptrs = (int32_t)ptrs.size();
   auto geti = [&](const char* k, int64_t dflt) { return d.contains(k) ? d[k].cast<int64_t>() : dflt; };
   p.idx_layer_mul = (int32_t)geti("idx_layer_mul", 1);
   p.idx_kv_mul = (int32_t)geti("idx_kv_mul", 0);
@@ -43,6 +44,7 @@ KvCopyParams kv_params_from_dict(const py::dict& d) {
     auto cp = d["c_ptrs"].cast<std::vector<uint64_t>>();
     if ((int)cp.size() > kMaxGpuPtrs) throw std::invalid_argument("too many peer tensors");
     for (size_t i = 0; i < cp.size(); ++i) p.c_ptrs[i] = cp[i];
+    p.num_c_ptrs = (int32_t)cp.size();
     p.c_use_table = 1;
     p.c_idx_layer_mul = (int32_t)geti("c_idx_layer_mul", 1);
     p.c_idx_kv_mul = (int32_t)geti("c_idx_kv_mul", 0);

@@ -13,8 +13,10 @@ namespace py = pybind11;
 using namespace fkv;
 
 void init_layerwise_bindings(py::module_& m) {
+  m.attr("LAYER_FAILED_SIGNAL") = py::int_(kLayerFailedSignal);
   py::class_<LayerwiseResult>(m, "LayerwiseResult")
       .def_readonly("status", &LayerwiseResult::status)
+      .def_readonly("epoch", &LayerwiseResult::epoch)
       .def_readonly("total_ms", &LayerwiseResult::total_ms)
       .def_readonly("disk_ms", &LayerwiseResult::disk_ms)
       .def_readonly("layer_done_ms", &LayerwiseResult::layer_done_ms);
@@ -97,10 +99,14 @@ void init_layerwise_bindings(py::module_& m) {
       .def("device_flags_ptr", &LayerwiseGroup::device_flags_ptr)
       .def("host_flags_ptr", &LayerwiseGroup::host_flags_ptr)
       .def("epoch_of", &LayerwiseGroup::epoch_of)
-      .def("stream_wait_layer", [](LayerwiseGroup& g, int rank, int counter, int layer, uint64_t stream) {
-             cudaError_t e = g.stream_wait_layer(rank, counter, layer, (cudaStream_t)(uintptr_t)stream);
+      .def("begin_restore", &LayerwiseGroup::begin_restore, py::arg("counter"),
+           "Reserves and returns the epoch the next restore() on this counter publishes.")
+      .def("counter_status", &LayerwiseGroup::counter_status, py::arg("counter"))
+      .def("stream_wait_layer", [](LayerwiseGroup& g, int rank, int counter, int layer, uint64_t stream,
+                                   uint32_t epoch) {
+             cudaError_t e = g.stream_wait_layer(rank, counter, layer, (cudaStream_t)(uintptr_t)stream, epoch);
              if (e != cudaSuccess) throw std::runtime_error(cudaGetErrorString(e));
-           })
+           }, py::arg("rank"), py::arg("counter"), py::arg("layer"), py::arg("stream"), py::arg("epoch") = 0u)
       .def_property_readonly("num_ranks", &LayerwiseGroup::num_ranks)
       .def_property_readonly("num_layers", &LayerwiseGroup::num_layers)
       .def_property_readonly("num_counters", &LayerwiseGroup::num_counters);

@@ -394,10 +394,11 @@ inline bool all_multiple(const KvCopyParams& p, int64_t m) {
 
 }  // namespace
 
-bool kv_copy_tma_eligible(const KvCopyParams& p) { return all_multiple(p, 16); }
+bool kv_copy_tma_eligible(const KvCopyParams& p) { return kv_copy_tables_ok(p) && all_multiple(p, 16); }
 
 cudaError_t launch_kv_copy(const KvCopyParams& p, const KvCopyLaunch& cfg, cudaStream_t stream) {
   if (p.num_pairs <= 0 || p.num_layers <= 0 || p.kv_dim <= 0 || p.chunk_bytes <= 0) return cudaSuccess;
+  if (!kv_copy_tables_ok(p)) return cudaErrorInvalidValue;
   int tile = cfg.tile_bytes > 0 ? cfg.tile_bytes : 16384;
   int engine = cfg.engine;
   if (engine == 0 && !all_multiple(p, 16)) engine = 1;
@@ -447,7 +448,7 @@ cudaError_t launch_kv_copy(const KvCopyParams& p, const KvCopyLaunch& cfg, cudaS
 
 cudaError_t launch_kv_copy_refshape(const KvCopyParams& p, int num_ctas, cudaStream_t stream) {
   if (p.num_pairs <= 0 || p.num_layers <= 0) return cudaSuccess;
-  if (!all_multiple(p, 16)) return cudaErrorInvalidValue;
+  if (!kv_copy_tables_ok(p) || !all_multiple(p, 16)) return cudaErrorInvalidValue;
   kv_copy_refshape_kernel<<<num_ctas > 0 ? num_ctas : 4, 1024, 0, stream>>>(p);
   return cudaGetLastError();
 }

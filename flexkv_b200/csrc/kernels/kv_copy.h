@@ -47,7 +47,10 @@ struct KvCopyParams {
   // reached over NVLink): when c_use_table is set its base is
   // c_ptrs[layer*c_idx_layer_mul + kv*c_idx_kv_mul] instead of cpu_base.
   uint64_t c_ptrs[kMaxGpuPtrs];
-  int32_t c_use_table, c_idx_layer_mul, c_idx_kv_mul, pad0_;
+  int32_t c_use_table, c_idx_layer_mul, c_idx_kv_mul;
+  // how many leading entries of gpu_ptrs / c_ptrs the caller filled: every launch path rejects a call whose
+  // largest table index (last layer, last kv plane) is not below these counts
+  int32_t num_gpu_ptrs, num_c_ptrs, pad0_;
   const int64_t* gpu_blocks;
   const int64_t* cpu_blocks;
   int32_t num_pairs;
@@ -106,5 +109,27 @@ inline int collect_status(volatile int32_t* words) {
 
 // true when every address component allows 16-byte bulk copies
 bool kv_copy_tma_eligible(const KvCopyParams& p);
+
+// True when the tensor tables cover every (layer, kv) the call addresses: index multipliers and the layer
+// range are non-negative, the largest index layer*idx_layer_mul + kv*idx_kv_mul is below the filled count
+// (itself at most kMaxGpuPtrs) and no addressed entry is null; the same for the c_ptrs table when it is in
+// use. A short pointer list after a re-registration or wrong multipliers are refused here, on the host,
+// instead of sending the kernel to a zero or foreign address.
+inline bool kv_copy_tables_ok(const KvCopyParams& p) {
+  if (p.num_layers < 0 || p.layer_start < 0 || p.kv_dim < 0) return false;
+  if (p.num_layers == 0 || p.kv_dim == 0) return true;   // nothing is addressed
+  auto table_ok = [&](const uint64_t* tbl, int32_t filled, int32_t lmul, int32_t kmul) {
+    if (lmul < 0 || kmul < 0 || filled <= 0 || filled > kMaxGpuPtrs) return false;
+    const int64_t last = (int64_t)(p.layer_start + p.num_layers - 1) * lmul + (int64_t)(p.kv_dim - 1) * kmul;
+    if (last >= filled) return false;
+    for (int32_t l = p.layer_start; l < p.layer_start + p.num_layers; ++l)
+      for (int32_t k = 0; k < p.kv_dim; ++k)
+        if (tbl[(int64_t)l * lmul + (int64_t)k * kmul] == 0) return false;
+    return true;
+  };
+  if (!table_ok(p.gpu_ptrs, p.num_gpu_ptrs, p.idx_layer_mul, p.idx_kv_mul)) return false;
+  if (p.c_use_table && !table_ok(p.c_ptrs, p.num_c_ptrs, p.c_idx_layer_mul, p.c_idx_kv_mul)) return false;
+  return true;
+}
 
 }  // namespace fkv

@@ -2,6 +2,7 @@
 // completion counter per layer) lives in a file-scope device array here, so the
 // entry point never allocates.
 #include "kv_copy_noalloc.h"
+#include "layer_sync.h"
 
 #include <cstdio>
 #include <cstring>
@@ -66,24 +67,11 @@ int fkv_layerwise_copy_noalloc(const FkvNoAllocArgs* a, void* stream_v, char* er
     return -1;
   }
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
-  uint32_t* counters = nullptr;
-  int dev = -1;
-  cudaError_t e = counters_for_current_device(&counters, &dev);
-  if (e != cudaSuccess) {
-    (void)cudaGetLastError();
-    set_error(errbuf, errbuf_len, cudaGetErrorString(e));
-    return (int)e;
-  }
-  // the array keeps whatever the previous call left: start from zero
-  e = cudaMemsetAsync(counters, 0, (size_t)a->num_layers * sizeof(uint32_t), stream);
-  if (e != cudaSuccess) {
-    (void)cudaGetLastError();
-    set_error(errbuf, errbuf_len, cudaGetErrorString(e));
-    return (int)e;
-  }
+  // Every argument check comes before the first CUDA call, so a rejected call has queued nothing.
   fkv::KvCopyParams p;
   std::memset(&p, 0, sizeof(p));
   for (int i = 0; i < a->num_gpu_ptrs; ++i) p.gpu_ptrs[i] = a->gpu_ptrs[i];
+  p.num_gpu_ptrs = a->num_gpu_ptrs;
   p.idx_layer_mul = a->idx_layer_mul;
   p.idx_kv_mul = a->idx_kv_mul;
   p.g_layer_stride = a->g_layer_stride;
@@ -105,16 +93,53 @@ int fkv_layerwise_copy_noalloc(const FkvNoAllocArgs* a, void* stream_v, char* er
   p.cpu_num_blocks = a->cpu_num_blocks;
   p.status = a->status;
   p.h2d = 1;
-  p.done_counter = counters;
   p.dev_flags = a->dev_flags;
   p.host_flags = a->host_flags;
   p.epoch = a->epoch;
   p.layer_major = 1;
+  if (!fkv::kv_copy_tables_ok(p)) {
+    char msg[200];
+    snprintf(msg, sizeof(msg), "tensor table too short or holed: layer %d, kv plane %d index entry %lld of %d "
+             "(idx_layer_mul %d, idx_kv_mul %d), and every addressed entry must be non-null",
+             a->num_layers - 1, a->kv_dim - 1,
+             (long long)(a->num_layers - 1) * a->idx_layer_mul + (long long)(a->kv_dim - 1) * a->idx_kv_mul,
+             a->num_gpu_ptrs, a->idx_layer_mul, a->idx_kv_mul);
+    set_error(errbuf, errbuf_len, msg);
+    return -1;
+  }
   if (!fkv::kv_copy_tma_eligible(p)) {
     set_error(errbuf, errbuf_len, "addresses, strides and chunk_bytes must be multiples of 16 bytes");
     return -1;
   }
-  if (a->num_pairs == 0) return 0;
+  cudaError_t e;
+  if (a->num_pairs == 0) {
+    // nothing to copy: release whoever waits on the layer flags, in stream order, as the ordinary path does
+    e = cudaSuccess;
+    if (a->dev_flags) e = fkv::launch_set_flags(a->dev_flags, a->num_layers, a->epoch, stream);
+    if (e == cudaSuccess && a->host_flags) e = fkv::launch_set_flags(a->host_flags, a->num_layers, a->epoch, stream);
+    if (e != cudaSuccess) {
+      (void)cudaGetLastError();
+      set_error(errbuf, errbuf_len, cudaGetErrorString(e));
+      return (int)e;
+    }
+    return 0;
+  }
+  uint32_t* counters = nullptr;
+  int dev = -1;
+  e = counters_for_current_device(&counters, &dev);
+  if (e != cudaSuccess) {
+    (void)cudaGetLastError();
+    set_error(errbuf, errbuf_len, cudaGetErrorString(e));
+    return (int)e;
+  }
+  // the array keeps whatever the previous call left: start from zero
+  e = cudaMemsetAsync(counters, 0, (size_t)a->num_layers * sizeof(uint32_t), stream);
+  if (e != cudaSuccess) {
+    (void)cudaGetLastError();
+    set_error(errbuf, errbuf_len, cudaGetErrorString(e));
+    return (int)e;
+  }
+  p.done_counter = counters;
   fkv::KvCopyLaunch cfg{a->num_ctas > 0 ? a->num_ctas : 8, a->tile_bytes > 0 ? a->tile_bytes : 16384, 0};
   e = fkv::launch_kv_copy(p, cfg, stream);
   if (e != cudaSuccess) {

@@ -28,6 +28,13 @@
 //    the GPU race on it: serialise them (one stream, or an event between them).
 //    The counters are cleared on the stream at the start of every call, so a call
 //    that was cut short cannot poison the next one.
+//  * The tensor table must cover every (layer, kv plane) the call addresses:
+//    (num_layers-1)*idx_layer_mul + (kv_dim-1)*idx_kv_mul < num_gpu_ptrs, no addressed
+//    entry null. A short or holed table is rejected (-1) before anything is queued.
+//  * Arguments are checked before the first CUDA call: a rejected call has put
+//    nothing on the stream and has not touched the shared array.
+//  * num_pairs == 0 copies nothing and publishes `epoch` to every layer's flags in
+//    stream order (two tiny launches), so waiters of an empty restore are released.
 //  * No cudaMalloc, cudaFree or allocating library routine is called.
 #pragma once
 #include <stdint.h>

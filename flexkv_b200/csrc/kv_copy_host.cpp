@@ -14,6 +14,7 @@ namespace fkv {
 
 int host_kv_copy(const KvCopyParams& p, int num_threads) {
   if (p.num_pairs <= 0 || p.num_layers <= 0 || p.kv_dim <= 0 || p.chunk_bytes <= 0) return 0;
+  if (!kv_copy_tables_ok(p)) return KV_ERR_BAD_ARGS;
   std::atomic<int> err{0};
   std::atomic<int64_t> next{0};
   const int64_t total = (int64_t)p.num_pairs * p.num_layers;

@@ -82,6 +82,9 @@ void LayerwiseGroup::start_ranks() {
   if (opt_.num_counters < 1 || opt_.layers_per_batch < -1) throw std::invalid_argument("LayerwiseGroup: bad options");
   const int L = opt_.group.num_layers, R = (int)gpus_.size(), C = opt_.num_counters;
   epochs_.assign((size_t)C, 0);
+  reserved_.assign((size_t)C, 0);
+  counter_status_.reset(new std::atomic<int>[(size_t)C]);
+  for (int i = 0; i < C; ++i) counter_status_[(size_t)i].store(0);
   if (opt_.create_eventfds) {
     eventfds_.assign((size_t)C * R * L, -1);
     for (auto& fd : eventfds_) {
@@ -155,31 +158,76 @@ uint64_t LayerwiseGroup::host_flags_ptr(int rank, int counter) const {
   return (uint64_t)(uintptr_t)(ranks_.at((size_t)rank)->host_flags + (size_t)counter * opt_.group.num_layers);
 }
 
-cudaError_t LayerwiseGroup::stream_wait_layer(int rank, int counter, int layer, cudaStream_t stream) {
+uint32_t LayerwiseGroup::epoch_of(int counter) {
+  std::lock_guard<std::mutex> g(epoch_mu_);
+  return epochs_.at((size_t)counter);
+}
+
+uint32_t LayerwiseGroup::begin_restore(int counter) {
+  if (counter < 0 || counter >= opt_.num_counters) throw std::invalid_argument("LayerwiseGroup: bad counter id");
+  std::lock_guard<std::mutex> g(epoch_mu_);
+  if (!reserved_[(size_t)counter]) {
+    reserved_[(size_t)counter] = 1;
+    ++epochs_[(size_t)counter];
+  }
+  return epochs_[(size_t)counter];
+}
+
+cudaError_t LayerwiseGroup::stream_wait_layer(int rank, int counter, int layer, cudaStream_t stream, uint32_t epoch) {
   Rank& rk = *ranks_.at((size_t)rank);
-  if (opt_.layers_per_batch > 0)
-    return cudaStreamWaitEvent(stream, rk.layer_ev[(size_t)counter * opt_.group.num_layers + layer], 0);
-  // fused launch: no event sits between layers, so the stream waits on the device flag itself
+  if (counter < 0 || counter >= opt_.num_counters || layer < 0 || layer >= opt_.group.num_layers)
+    return cudaErrorInvalidValue;
+  if (epoch == 0) {
+    std::lock_guard<std::mutex> g(epoch_mu_);
+    epoch = epochs_[(size_t)counter];
+  }
+  // Every launch form publishes the device flag, so the wait is on the flag's value: an event wait would bind to
+  // whatever record of the per-layer event was last queued, i.e. to the previous restore when the consumer runs ahead.
   StreamWaitValue32Fn fn = stream_wait_value32();
   if (fn == nullptr) return cudaErrorNotSupported;
   uint32_t* flag = rk.dev_flags + (size_t)counter * opt_.group.num_layers + layer;
-  const CUresult r = fn((CUstream)stream, (CUdeviceptr)(uintptr_t)flag, epochs_[(size_t)counter],
-                        CU_STREAM_WAIT_VALUE_GEQ);
+  const CUresult r = fn((CUstream)stream, (CUdeviceptr)(uintptr_t)flag, epoch, CU_STREAM_WAIT_VALUE_GEQ);
   return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorUnknown;
 }
 
-void LayerwiseGroup::notify(int rank, int counter, int layer_lo, int layer_hi) {
+void LayerwiseGroup::notify(int rank, int counter, int layer_lo, int layer_hi, bool failed) {
   if (eventfds_.empty()) return;
-  const uint64_t one = 1;
+  const uint64_t v = failed ? kLayerFailedSignal : 1;
   for (int l = layer_lo; l < layer_hi; ++l) {
     const int fd = eventfd_of(counter, rank, l);
-    if (fd >= 0) { ssize_t w = write(fd, &one, sizeof(one)); (void)w; }
+    if (fd >= 0) { ssize_t w = write(fd, &v, sizeof(v)); (void)w; }
   }
+}
+
+bool LayerwiseGroup::status_words_set(const volatile int32_t* words) {
+  for (int b = 0; b < kStatusWords; ++b)
+    if (words[b]) return true;
+  return false;
+}
+
+void LayerwiseGroup::release_waiters(int r, const Job& j, int from_layer, int status) {
+  Rank& rk = *ranks_[(size_t)r];
+  const int L = opt_.group.num_layers;
+  counter_status_[(size_t)j.counter].store(status ? status : -1, std::memory_order_release);
+  if (from_layer >= L) return;
+  uint32_t* hflags = rk.host_flags + (size_t)j.counter * L;
+  for (int l = from_layer; l < L; ++l) __atomic_store_n(hflags + l, j.epoch, __ATOMIC_RELEASE);
+  // device flags from the host, on the side stream: the copy stream may hold the failed work
+  if (rk.dev_flags != nullptr && rk.notify_stream != nullptr) {
+    cudaError_t e = cudaMemcpyAsync(rk.dev_flags + (size_t)j.counter * L + from_layer, hflags + from_layer,
+                                    (size_t)(L - from_layer) * sizeof(uint32_t), cudaMemcpyHostToDevice,
+                                    rk.notify_stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(rk.notify_stream);
+    if (e != cudaSuccess) (void)cudaGetLastError();
+  }
+  notify(r, j.counter, from_layer, L, true);
 }
 
 void CUDART_CB LayerwiseGroup::host_fn(void* arg) {
   auto* a = static_cast<HostFnArg*>(arg);
-  a->self->notify(a->rank, a->counter, a->layer_lo, a->layer_hi);
+  // a kernel that gave up has written its status words before it released the layers it did not restore
+  const bool failed = status_words_set(a->self->ranks_[(size_t)a->rank]->status);
+  a->self->notify(a->rank, a->counter, a->layer_lo, a->layer_hi, failed);
 }
 
 void LayerwiseGroup::rank_main(int r) {
@@ -277,6 +325,13 @@ void LayerwiseGroup::run_job_members(int r, const Job& j) {
   const int L = (int)members_.size(), R = (int)gpus_.size();
   rk.res_status = 0;
   rk.res_layer_ms.assign((size_t)L, 0.f);
+  if (j.fail_status) {
+    release_waiters(r, j, 0, j.fail_status);
+    rk.res_status = j.fail_status;
+    rk.res_ms = 0.f;
+    return;
+  }
+  int queued_upto = 0, notified_upto = 0;   // layers whose signal is queued on the side stream / already sent
   cudaEvent_t* ev = rk.layer_ev.data() + (size_t)j.counter * L;
   uint32_t* hflags = rk.host_flags + (size_t)j.counter * L;
   uint32_t* dflags = rk.dev_flags + (size_t)j.counter * L;
@@ -315,11 +370,13 @@ void LayerwiseGroup::run_job_members(int r, const Job& j) {
       HostFnArg* a = fn_args_[((size_t)r * opt_.num_counters + j.counter) * L + l].get();
       err = cudaStreamWaitEvent(rk.notify_stream, ev[l], 0);
       if (err == cudaSuccess) err = cudaLaunchHostFunc(rk.notify_stream, host_fn, a);
+      if (err == cudaSuccess) queued_upto = l + 1;
     }
   }
+  bool kernel_failed = false;
   if (err == cudaSuccess && opt_.notify != NotifyMode::HOSTFUNC) {
     const auto t0 = std::chrono::steady_clock::now();
-    for (int l = 0; l < L && err == cudaSuccess; ++l) {
+    for (int l = 0; l < L && err == cudaSuccess && !kernel_failed; ++l) {
       for (;;) {
         // events in both modes: a host-published flag of an empty layer is set before the stream reaches it
         cudaError_t q = cudaEventQuery(ev[l]);
@@ -327,18 +384,31 @@ void LayerwiseGroup::run_job_members(int r, const Job& j) {
         if (q != cudaErrorNotReady) { err = q; break; }
         if (std::chrono::steady_clock::now() - t0 > std::chrono::seconds(120)) { err = cudaErrorTimeout; break; }
       }
-      if (err == cudaSuccess) notify(r, j.counter, l, l + 1);
+      if (err != cudaSuccess) break;
+      // a kernel that gave up has written its status words before the flags of the layers it did not restore
+      if (status_words_set(rk.status)) { kernel_failed = true; break; }
+      notify(r, j.counter, l, l + 1);
+      notified_upto = l + 1;
     }
   }
   if (err == cudaSuccess) err = cudaStreamSynchronize(rk.stream);
   if (err == cudaSuccess) err = cudaStreamSynchronize(rk.notify_stream);
   if (err != cudaSuccess) {
     (void)cudaGetLastError();
+    (void)cudaStreamSynchronize(rk.notify_stream);   // callbacks already queued run first
+    (void)cudaGetLastError();
     rk.res_status = -(int)err;
     rk.res_ms = 0.f;
+    release_waiters(r, j, std::max(queued_upto, notified_upto), rk.res_status);
     return;
   }
   rk.res_status = collect_status(rk.status);
+  if (rk.res_status != 0) {
+    release_waiters(r, j, std::max(queued_upto, notified_upto), rk.res_status);
+    rk.res_ms = 0.f;
+    return;
+  }
+  counter_status_[(size_t)j.counter].store(0, std::memory_order_release);
   for (int l = 0; l < L; ++l) cudaEventElapsedTime(&rk.res_layer_ms[(size_t)l], rk.ev_begin, ev[l]);
   rk.res_ms = rk.res_layer_ms[(size_t)L - 1];
 }
@@ -363,6 +433,14 @@ void LayerwiseGroup::run_job(int r, const Job& j) {
   const auto t_begin = std::chrono::steady_clock::now();
   rk.res_status = 0;
   rk.res_layer_ms.assign((size_t)L, 0.f);
+  if (j.fail_status) {
+    release_waiters(r, j, 0, j.fail_status);
+    rk.res_status = j.fail_status;
+    rk.res_ms = 0.f;
+    return;
+  }
+  int queued_upto = 0, notified_upto = 0;   // layers whose signal is queued on the side stream / already sent
+  bool kernel_failed = false;
   cudaEvent_t* ev = rk.layer_ev.data() + (size_t)j.counter * L;
   uint32_t* hflags = rk.host_flags + (size_t)j.counter * L;
   cudaError_t err = cudaEventRecord(rk.ev_begin, rk.stream);
@@ -395,6 +473,7 @@ void LayerwiseGroup::run_job(int r, const Job& j) {
       HostFnArg* a = fn_args_[((size_t)r * opt_.num_counters + j.counter) * batches + b].get();
       err = cudaStreamWaitEvent(rk.notify_stream, ev[l1 - 1], 0);
       if (err == cudaSuccess) err = cudaLaunchHostFunc(rk.notify_stream, host_fn, a);
+      if (err == cudaSuccess) queued_upto = l1;
     }
   }
   if (err == cudaSuccess && (opt_.notify != NotifyMode::HOSTFUNC || fused)) {
@@ -416,21 +495,35 @@ void LayerwiseGroup::run_job(int r, const Job& j) {
         if (std::chrono::steady_clock::now() - t0 > std::chrono::seconds(120)) { err = cudaErrorTimeout; break; }
       }
       if (err != cudaSuccess) break;
+      // a kernel that gave up has written its status words before the flags of the layers it did not restore
+      if (status_words_set(rk.status)) { kernel_failed = true; break; }
       notify(r, j.counter, l0, l1);
+      notified_upto = l1;
       if (fused)
         rk.res_layer_ms[(size_t)l0] =
             std::chrono::duration<float, std::milli>(std::chrono::steady_clock::now() - t_begin).count();
     }
   }
+  (void)kernel_failed;
   if (err == cudaSuccess) err = cudaStreamSynchronize(rk.stream);
   if (err == cudaSuccess) err = cudaStreamSynchronize(rk.notify_stream);
   if (err != cudaSuccess) {
     (void)cudaGetLastError();
+    (void)cudaStreamSynchronize(rk.notify_stream);   // callbacks already queued run first
+    (void)cudaGetLastError();
     rk.res_status = -(int)err;
     rk.res_ms = 0.f;
+    release_waiters(r, j, std::max(queued_upto, notified_upto), rk.res_status);
     return;
   }
   rk.res_status = collect_status(rk.status);
+  if (rk.res_status != 0) {
+    // the data of some layers is not what was asked for: whoever is still waiting is released with the failure
+    release_waiters(r, j, std::max(queued_upto, notified_upto), rk.res_status);
+    rk.res_ms = 0.f;
+    return;
+  }
+  counter_status_[(size_t)j.counter].store(0, std::memory_order_release);
   if (!fused) {
     for (int l = 0; l < L; ++l) cudaEventElapsedTime(&rk.res_layer_ms[(size_t)l], rk.ev_begin, ev[l]);
     rk.res_ms = rk.res_layer_ms[(size_t)L - 1];
@@ -446,6 +539,16 @@ LayerwiseResult LayerwiseGroup::restore(const int64_t* gpu_blocks, const int64_t
   if (n > opt_.group.max_blocks_per_op) throw std::invalid_argument("LayerwiseGroup: op exceeds max_blocks_per_op");
   std::lock_guard<std::mutex> api(api_mu_);
   LayerwiseResult res;
+  Job j;
+  j.counter = counter_id;
+  {
+    std::lock_guard<std::mutex> g(epoch_mu_);
+    if (reserved_[(size_t)counter_id]) reserved_[(size_t)counter_id] = 0;
+    else ++epochs_[(size_t)counter_id];
+    j.epoch = epochs_[(size_t)counter_id];
+  }
+  res.epoch = j.epoch;
+  counter_status_[(size_t)counter_id].store(0, std::memory_order_release);
   if (n_disk > 0) {
     if (ssd == nullptr || ssd_layout == nullptr) throw std::invalid_argument("LayerwiseGroup: disk blocks without an SSD engine");
     const auto t0 = std::chrono::steady_clock::now();
@@ -453,19 +556,13 @@ LayerwiseResult LayerwiseGroup::restore(const int64_t* gpu_blocks, const int64_t
     const int64_t nfail = ssd->transfer(reinterpret_cast<uint8_t*>(host_.base), cpu_dst, ssd_src, n_disk, true,
                                         *ssd_layout, 0, ssd_layout->num_layers_total, ok.data());
     res.disk_ms = std::chrono::duration<float, std::milli>(std::chrono::steady_clock::now() - t0).count();
-    if (nfail > 0) {
-      res.status = 1 << 29;  // disk stage failed: nothing is restored, nothing is signalled
-      return res;
-    }
+    if (nfail > 0) j.fail_status = 1 << 29;   // disk stage failed: nothing is copied, every waiter is released
   }
-  if (n > 0) {
+  if (n > 0 && !j.fail_status) {
     std::memcpy(id_ring_, gpu_blocks, (size_t)n * sizeof(int64_t));
     std::memcpy(id_ring_ + opt_.group.max_blocks_per_op, cpu_blocks, (size_t)n * sizeof(int64_t));
   }
-  Job j;
   j.n = n;
-  j.counter = counter_id;
-  j.epoch = ++epochs_[(size_t)counter_id];
   j.gpu_blocks = id_ring_;
   j.cpu_blocks = id_ring_ + opt_.group.max_blocks_per_op;
   {

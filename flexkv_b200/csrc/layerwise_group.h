@@ -46,8 +46,13 @@ struct LayerwiseOptions {
   bool create_eventfds = true;
 };
 
+// Value written to a layer's eventfd when the restore failed (a reader that ignores the value is still
+// released; one that looks at it sees the failure and recomputes). A successful layer writes 1.
+constexpr uint64_t kLayerFailedSignal = 1ull << 32;
+
 struct LayerwiseResult {
   int status = 0;
+  uint32_t epoch = 0;                // the value this restore published to its counter's flags
   float total_ms = 0.f;              // first launch to last completion, max over ranks (CUDA events)
   float disk_ms = 0.f;               // host wall time of the SSD -> host stage
   std::vector<float> layer_done_ms;  // per layer, time since first launch (rank 0)
@@ -91,9 +96,20 @@ class LayerwiseGroup {
   void set_eventfd(int counter, int rank, int layer, int fd);
   uint64_t device_flags_ptr(int rank, int counter) const;  // uint32[num_layers] in device memory
   uint64_t host_flags_ptr(int rank, int counter) const;    // uint32[num_layers] in mapped host memory
-  uint32_t epoch_of(int counter) const { return epochs_[(size_t)counter]; }
-  // makes `stream` (a CUDA stream of rank's device) wait for layer `layer` of the restore in flight on `counter`
-  cudaError_t stream_wait_layer(int rank, int counter, int layer, cudaStream_t stream);
+  uint32_t epoch_of(int counter);
+  // Reserves and returns the epoch that the NEXT restore() on `counter` will publish. A consumer that wants to
+  // queue its waits before (or while) the restore is issued calls this first and hands the value to
+  // stream_wait_layer; restore() then publishes exactly that epoch. Without a reservation restore() takes the
+  // next epoch itself and returns it in LayerwiseResult::epoch.
+  uint32_t begin_restore(int counter);
+  // Makes `stream` (a CUDA stream of rank's device) wait until layer `layer` of the restore that publishes
+  // `epoch` on `counter` has landed (a stream-ordered wait on the device flag, value >= epoch). `epoch` 0
+  // means "the newest epoch handed out for this counter", which is only right once that restore has been
+  // started or reserved. A failed restore releases the waiters too; whether the data is usable is told by
+  // counter_status() / the restore's result, never by the flag alone.
+  cudaError_t stream_wait_layer(int rank, int counter, int layer, cudaStream_t stream, uint32_t epoch = 0);
+  // 0 while the newest restore on `counter` is running or has succeeded, else its failure status
+  int counter_status(int counter) const { return counter_status_[(size_t)counter].load(std::memory_order_acquire); }
   int num_ranks() const { return (int)gpus_.size(); }
   // new tensor addresses after the engine re-created its cache; call with no restore in flight
   void update_gpu_ptrs(int rank, const std::vector<uint64_t>& ptrs);
@@ -107,6 +123,7 @@ class LayerwiseGroup {
     int64_t n;
     int counter;
     uint32_t epoch;
+    int fail_status = 0;        // non-zero: nothing is copied, the waiters are released with this failure
     const int64_t* gpu_blocks;  // in the id ring
     const int64_t* cpu_blocks;
   };
@@ -143,7 +160,11 @@ class LayerwiseGroup {
   void run_job(int r, const Job& j);
   void run_job_members(int r, const Job& j);
   cudaError_t stage_ids(Rank& rk, const Job& j, const int64_t*& gpu_ids, const int64_t*& cpu_ids);
-  void notify(int rank, int counter, int layer_lo, int layer_hi);
+  void notify(int rank, int counter, int layer_lo, int layer_hi, bool failed = false);
+  // failure path of a job: publishes the epoch to the flags of layers [from_layer, L) from the host, fires
+  // their eventfds with kLayerFailedSignal and records the status for counter_status()
+  void release_waiters(int r, const Job& j, int from_layer, int status);
+  static bool status_words_set(const volatile int32_t* words);
   static void CUDART_CB host_fn(void* arg);
 
   std::vector<GpuSide> gpus_;
@@ -154,7 +175,10 @@ class LayerwiseGroup {
   std::vector<std::unique_ptr<Rank>> ranks_;
   std::atomic<bool> stop_{false};
   std::vector<int> eventfds_;       // [counters][ranks][layers]
-  std::vector<uint32_t> epochs_;    // per counter
+  std::vector<uint32_t> epochs_;    // per counter, guarded by epoch_mu_
+  std::vector<uint8_t> reserved_;   // per counter: begin_restore() handed the next epoch out already
+  std::mutex epoch_mu_;
+  std::unique_ptr<std::atomic<int>[]> counter_status_;
   int64_t* id_ring_ = nullptr;      // [2][max_blocks], mapped pinned
   std::mutex api_mu_;               // one restore at a time per group
   std::mutex done_mu_;

@@ -82,6 +82,7 @@ void fill_kv_params(const GpuSide& gs, const HostSide& host, const GroupOptions&
                     int num_layers, uint64_t rotate, KvCopyParams& p, bool& skip) {
   std::memset(&p, 0, sizeof(p));
   for (size_t i = 0; i < gs.ptrs.size(); ++i) p.gpu_ptrs[i] = gs.ptrs[i];
+  p.num_gpu_ptrs = (int32_t)gs.ptrs.size();
   p.idx_layer_mul = gs.idx_layer_mul;
   p.idx_kv_mul = gs.idx_kv_mul;
   p.g_layer_stride = gs.layer_stride;

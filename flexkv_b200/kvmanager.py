@@ -276,6 +276,9 @@ class KVManager:
         if tm.storage is None or gce.ssd_cache_engine is None:
             return False
         with gce._cache_tree_lock:     # noqa: SLF001 - the index must not move between the two files
+            # the index may only name blocks whose bytes are on the disk: with buffered descriptors (no O_DIRECT)
+            # they may still sit in the page cache, and the blocks carry no checksum
+            tm.storage.sync_ssd_files()
             persist.save_size_table(self.cache_config, tm.storage.ssd_size_table)
             return gce.checkpoint_ssd_index()
 

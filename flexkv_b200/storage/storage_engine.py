@@ -279,6 +279,25 @@ class StorageEngine:
                            c.num_ssd_blocks, block_bytes, ndev, files_per_dev, engine.using_iouring,
                            engine.direct_available)
 
+    def sync_ssd_files(self) -> None:
+        """fsync of every SSD block file and of the directories that hold them (a persisted index must not
+        name blocks that only exist in the page cache)."""
+        if self.ssd is None:
+            return
+        try:
+            self.ssd.engine.sync_files()
+        except Exception as e:  # noqa: BLE001
+            flexkv_logger.warning("ssd block files not synced: %s", e)
+        for d in {os.path.dirname(os.path.abspath(f)) for dev in self.ssd.files for f in dev}:
+            try:
+                fd = os.open(d, os.O_RDONLY | os.O_DIRECTORY)
+                try:
+                    os.fsync(fd)
+                finally:
+                    os.close(fd)
+            except OSError:
+                pass
+
     def ssd_layout_dict(self) -> Dict[str, Any]:
         h = self.host
         bf = h.layout.type == KVCacheLayoutType.BLOCKFIRST or h.layout.is_multi_group
@@ -409,6 +428,8 @@ class StorageEngine:
                     pass
         if self.ssd is not None:
             files = [f for d in self.ssd.files for f in d]
+            if getattr(self, "_ssd_persist", False):
+                self.sync_ssd_files()      # the index written after this names only bytes that reached the disk
             self.ssd = None
             if getattr(self, "_ssd_persist", False):
                 from ..cache import persist

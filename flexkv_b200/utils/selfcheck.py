@@ -1,0 +1,200 @@
+"""Byte-exact self checks of the data plane on real GPUs, small enough to run after a benchmark.
+
+Each function builds its own small caches, moves data through the native path under test and
+compares every byte with a PyTorch gather of the same blocks. They return ``True``/``False`` (or
+raise on a launch error); ``bench.py`` prints their results under ``verified`` and the GPU tests
+assert on them, so the multi-GPU paths are proven wherever two or more GPUs are visible.
+
+The scenarios mirror the reference's data-plane correctness suite
+(``tests/test_kv_transfer_correctness.py:515-520,604-610`` TP thread group with MHA slices and the
+shared-KV write modes, ``:1320-1327`` layerwise restore) and add the NVLink peer pull, which the
+reference does not have.
+"""
+from __future__ import annotations
+
+import os
+import struct
+from typing import Dict, Sequence
+
+import numpy as np
+import torch
+
+from .. import CacheConfig, KVManager, _native
+from ..models import KVShape, alloc_paged_cache, make_model_config
+from ..storage.gpu_layout import register_tensors
+
+SHARED_KV_MODES = ("sharded", "all_write", "rank0_only", "layer_parallel", "rank_rotate")
+
+
+def slots_of(blocks, tokens_per_block: int) -> np.ndarray:
+    b = np.asarray(blocks, dtype=np.int64)
+    return np.repeat(b, tokens_per_block) * tokens_per_block + np.tile(np.arange(tokens_per_block), len(b))
+
+
+def manager_roundtrip(mgr: KVManager, kv: Sequence[torch.Tensor], gpu_blocks: int, tokens_per_block: int,
+                      n_blocks: int = 64, seed: int = 4321, vocab: int = 128256, layers=None) -> bool:
+    """put -> get of ``n_blocks`` fresh blocks through the public API into *different* GPU blocks of a
+    vLLM-layout cache, then compare source and destination pages of the given layers."""
+    T = tokens_per_block
+    r = np.random.default_rng(seed)
+    tok = r.integers(0, vocab, size=n_blocks * T, dtype=np.int64)
+    ids = r.permutation(gpu_blocks)[:2 * n_blocks].astype(np.int64)
+    src, dst = ids[:n_blocks], ids[n_blocks:]
+    tid = mgr.put_async(tok, slots_of(src, T))
+    if mgr.wait(tid, timeout=120, completely=True)[tid].status.value != "success":
+        return False
+    tid, mask = mgr.get_match(tok)
+    if int(mask.sum()) != n_blocks * T:
+        return False
+    mgr.launch(tid, slots_of(dst, T))
+    if mgr.wait(tid, timeout=120)[tid].status.value != "success":
+        return False
+    torch.cuda.synchronize(kv[0].device)
+    a = torch.from_numpy(src).to(kv[0].device)
+    b = torch.from_numpy(dst).to(kv[0].device)
+    L = len(kv)
+    for l in (layers if layers is not None else sorted({0, L // 2, L - 1})):
+        t = kv[l]
+        same = torch.equal(t[:, a], t[:, b]) if t.dim() >= 4 and t.shape[0] == 2 else torch.equal(t[a], t[b])
+        if not same:
+            return False
+    return True
+
+
+def tp_group_two_gpus(mode: str = "mha", devices=(0, 1)) -> bool:
+    """TP transfer group on two GPUs: offload into one shared host block, restore into other pages.
+    ``mode`` = "mha" (each rank owns its head slice) or one of the shared-KV write modes."""
+    C = _native.C
+    mla = mode != "mha"
+    shape = KVShape("t", 4, 1 if mla else 4, 128 if mla else 32, use_mla=mla, tokens_per_block=16)
+    caches, regs = [], []
+    for i, d in enumerate(devices):
+        kv, layout = alloc_paged_cache(shape, 48, torch.device("cuda", d), "vllm", tp_size=1 if mla else 2,
+                                       fill="normal", seed=40 if mla else 40 + i)
+        caches.append(kv)
+        regs.append(register_tensors(kv, layout))
+    chunk = regs[0].chunk_bytes
+    slices = 1 if mla else 2
+    K = shape.kv_dim
+    block_bytes = slices * 4 * K * chunk
+    pool = torch.zeros(48, block_bytes, dtype=torch.uint8).pin_memory()
+    host = dict(base=pool.data_ptr(), layer_stride=K * chunk, kv_stride=chunk, block_stride=block_bytes, num_blocks=48)
+    opts = dict(num_layers=4, kv_dim=K, chunk_bytes=chunk, cpu_tp_stride=block_bytes // slices, shared_kv=mla,
+                shared_mode=mode if mla else "sharded", max_blocks_per_op=64)
+    grp = C.TransferGroup([r.as_native() for r in regs], host, opts)
+    g = np.array([3, 40, 11, 7, 25], dtype=np.int64)
+    c = np.array([9, 0, 47, 2, 30], dtype=np.int64)
+    ok = grp.transfer(g, c, False, 0, 4).status == 0
+    gi = [torch.from_numpy(g).to(f"cuda:{d}") for d in devices]
+    for i, cb in enumerate(c):
+        blk = pool[int(cb)]
+        for r in range(slices):
+            want = torch.stack([caches[r][l][gi[r][i]] if mla else caches[r][l][:, gi[r][i]] for l in range(4)])
+            want = want.contiguous().view(torch.uint8).reshape(-1).cpu()
+            per = block_bytes // slices
+            ok = ok and torch.equal(blk[r * per:(r + 1) * per], want)
+    saved = [[t.clone() for t in kv] for kv in caches]
+    for kv in caches:
+        for t in kv:
+            t.zero_()
+    g2 = np.array([1, 2, 3, 4, 5], dtype=np.int64)
+    ok = ok and grp.transfer(g2, c, True, 0, 4).status == 0
+    for di, d in enumerate(devices):
+        src_rank = 0 if mla else di
+        sdev = saved[src_rank][0].device
+        a = torch.from_numpy(g).to(sdev)
+        b = torch.from_numpy(g2).to(f"cuda:{d}")
+        for l in range(4):
+            want = saved[src_rank][l][a] if mla else saved[src_rank][l][:, a]
+            got = caches[di][l][b] if mla else caches[di][l][:, b]
+            ok = ok and torch.equal(got.cpu(), want.cpu())
+    del grp
+    return bool(ok)
+
+
+def peer_pull_two_gpus(devices=(0, 1)) -> bool:
+    """A prefix that lives only in GPU ``devices[0]``'s pages is restored into GPU ``devices[1]`` over
+    NVLink through the manager (planner fragment, peer worker, pull kernel)."""
+    shape = KVShape("pp", 3, 2, 64, tokens_per_block=16)
+    T = 16
+    mgr = KVManager(make_model_config(shape, dp_size=2),
+                    CacheConfig(tokens_per_block=T, num_cpu_blocks=64, enable_p2p_gpu=True), in_process=True)
+    caches = []
+    for i, d in enumerate(devices):
+        kv, layout = alloc_paged_cache(shape, 64, torch.device("cuda", d), "vllm",
+                                       fill="normal" if i == 0 else "zeros", seed=50)
+        mgr.register_gpu_tensors(kv, layout, dp_client_id=i)
+        caches.append(kv)
+    mgr.start()
+    mgr.wait_ready(120)
+    ok = True
+    try:
+        tok = np.arange(10 * T, dtype=np.int64)
+        owner_blocks = np.array([9, 3, 60, 1, 7, 8, 33, 21, 5, 40], dtype=np.int64)
+        ok = ok and mgr.publish_gpu_blocks(tok, slots_of(owner_blocks, T), dp_client_id=0) == 10
+        tid, mask = mgr.kv_task_engine.get_match(tok, None, 1)
+        ok = ok and int(mask.sum()) == 10 * T
+        dst = np.arange(20, 30, dtype=np.int64)
+        mgr.launch(tid, slots_of(dst, T))
+        ok = ok and mgr.wait(tid)[tid].status.value == "success"
+        for l in range(3):
+            got = caches[1][l][:, torch.from_numpy(dst).to(caches[1][l].device)].cpu()
+            want = caches[0][l][:, torch.from_numpy(owner_blocks).to(caches[0][l].device)].cpu()
+            ok = ok and torch.equal(got, want)
+        # the owner's own get does not pull from itself; withdrawn blocks are no longer offered
+        ok = ok and int(mgr.kv_task_engine.get_match(tok, None, 0)[1].sum()) == 0
+        ok = ok and mgr.withdraw_gpu_blocks(owner_blocks[:4], dp_client_id=0) == []
+        ok = ok and int(mgr.kv_task_engine.get_match(tok, None, 1)[1].sum()) == 0
+    finally:
+        mgr.shutdown()
+    return bool(ok)
+
+
+def layerwise_two_ranks(devices=(0, 1)) -> bool:
+    """Layerwise restore on two TP ranks (SGLang layout): every rank's per-layer eventfd fires once
+    and every rank's pages hold its own head slice of the host blocks."""
+    C = _native.C
+    shape = KVShape("l2", 4, 4, 32, tokens_per_block=16)
+    caches, regs = [], []
+    for d in devices:
+        kv, layout = alloc_paged_cache(shape, 32, torch.device("cuda", d), "sglang", tp_size=2, fill="zeros")
+        caches.append(kv)
+        regs.append(register_tensors(kv, layout))
+    chunk = regs[0].chunk_bytes
+    bb = 2 * 4 * 2 * chunk
+    pool = torch.randint(0, 256, (32, bb), dtype=torch.uint8).pin_memory()
+    host = dict(base=pool.data_ptr(), layer_stride=2 * chunk, kv_stride=chunk, block_stride=bb, num_blocks=32)
+    opts = dict(num_layers=4, kv_dim=2, chunk_bytes=chunk, cpu_tp_stride=bb // 2, max_blocks_per_op=64,
+                notify_mode="flag", layers_per_batch=0)
+    grp = C.LayerwiseGroup([r.as_native() for r in regs], host, opts)
+    ids = np.arange(16, dtype=np.int64)
+    rev = ids[::-1].copy()
+    ok = grp.restore(ids, rev, 1).status == 0
+    for rank in range(2):
+        for l in range(4):
+            fd = grp.eventfd_of(1, rank, l)
+            ok = ok and struct.unpack("Q", os.read(fd, 8))[0] == 1
+        for l in range(4):
+            for k in range(2):
+                got = caches[rank][k * 4 + l][:16].contiguous().view(torch.uint8).reshape(16, -1).cpu()
+                base = rank * (bb // 2) + l * 2 * chunk + k * chunk
+                want = pool[torch.from_numpy(rev), base:base + chunk]
+                ok = ok and torch.equal(got, want)
+    del grp
+    return bool(ok)
+
+
+def multi_gpu_checks(devices=(0, 1)) -> Dict[str, bool]:
+    """Every two-GPU scenario above; an exception counts as a failed check and is named."""
+    out: Dict[str, bool] = {}
+    cases = [("tp_group_mha", lambda: tp_group_two_gpus("mha", devices))]
+    cases += [(f"tp_group_{m}", (lambda m=m: tp_group_two_gpus(m, devices))) for m in SHARED_KV_MODES]
+    cases += [("peer_pull_nvlink", lambda: peer_pull_two_gpus(devices)),
+              ("layerwise_two_ranks", lambda: layerwise_two_ranks(devices))]
+    for name, fn in cases:
+        try:
+            out[name] = bool(fn())
+        except Exception as e:  # noqa: BLE001
+            out[name] = False
+            out[name + "_error"] = f"{type(e).__name__}: {e}"[:200]
+    return out

@@ -153,3 +153,68 @@ def test_a_layer_flag_is_never_seen_before_the_layer_bytes(lpb):
         assert status.item() == 0
         got = [int(v) & ((1 << 64) - 1) for v in sums.tolist()]
         assert got == want, (rep, lpb)
+
+
+@pytest.mark.parametrize("lpb", [1, 0])
+def test_consumer_queued_before_the_restore_waits_for_this_restore(lpb):
+    """The model stream runs ahead: its per-layer waits are queued before the restore is issued. With the
+    epoch reserved by begin_restore they bind to THIS restore, not to the previous one's flags."""
+    import threading
+    shape = KVShape("lw", 5, 2, 128, tokens_per_block=16)
+    kv, reg, pool, grp, xfer = _setup(shape, notify="flag", layers_per_batch=lpb)
+    n = 64
+    ids = np.arange(n, dtype=np.int64)
+    assert xfer.transfer(ids, ids, False, 0, shape.num_layers).status == 0
+    want = [t[:, :n].clone() for t in kv]
+    assert grp.restore(ids, ids, 0).status == 0              # a first restore: the flags hold epoch 1
+    for t in kv:
+        t.zero_()
+    model = torch.cuda.Stream()
+    ep = grp.begin_restore(0)
+    assert ep == grp.epoch_of(0) == 2
+    snaps = []
+    with torch.cuda.stream(model):
+        for l in range(shape.num_layers):
+            grp.stream_wait_layer(0, 0, l, model.cuda_stream, ep)
+            snaps.append(kv[l][:, :n].clone())                # what the model would read once released
+    th = threading.Thread(target=lambda: grp.restore(ids, ids, 0))
+    th.start()
+    th.join()
+    model.synchronize()
+    assert grp.epoch_of(0) == 2 and grp.counter_status(0) == 0
+    for l in range(shape.num_layers):
+        assert torch.equal(snaps[l], want[l]), l
+
+
+def test_failed_disk_stage_releases_every_waiter_with_the_failure_signal(tmp_path):
+    """The failure is made on the host (an injected EIO in the SSD engine). Nothing is copied, the result and
+    counter_status carry the error, every layer's eventfd fires with the failure value and a stream parked on
+    a layer flag is released."""
+    shape = KVShape("lw", 4, 2, 64, tokens_per_block=16)
+    kv, reg, pool, grp, xfer = _setup(shape, notify="flag", layers_per_batch=0)
+    chunk = reg.chunk_bytes
+    bb = shape.num_layers * shape.kv_dim * chunk
+    paths = [[str(tmp_path / "blk.bin")]]
+    ssd = C.SsdIoEngine(paths, bb, 16, create=True, try_direct=False, iouring_entries=0, num_threads=2)
+    lay = dict(cpu_layer_stride=shape.kv_dim * chunk, cpu_kv_stride=chunk, cpu_block_stride=bb,
+               ssd_layer_stride=shape.kv_dim * chunk, ssd_kv_stride=chunk, ssd_block_stride=bb, chunk_bytes=chunk,
+               num_layers=shape.num_layers, kv_dim=shape.kv_dim, block_first=True)
+    ids = np.arange(4, dtype=np.int64)
+    ssd.set_fault(3, 0)                                       # every IO fails
+    model = torch.cuda.Stream()
+    ep = grp.begin_restore(1)
+    for l in range(shape.num_layers):
+        grp.stream_wait_layer(0, 1, l, model.cuda_stream, ep)
+    before = [t.clone() for t in kv]
+    r = grp.restore(ids, ids, 1, ssd, lay, ids, ids)
+    assert r.status != 0 and r.epoch == ep
+    assert grp.counter_status(1) != 0
+    model.synchronize()                                       # released, not parked forever
+    fails = [_drain(grp.eventfd_of(1, 0, l)) for l in range(shape.num_layers)]
+    assert fails == [C.LAYER_FAILED_SIGNAL] * shape.num_layers
+    for a, b in zip(before, kv):
+        assert torch.equal(a, b)                              # nothing was copied
+    ssd.set_fault(0, 0)
+    r = grp.restore(ids, ids, 1, ssd, lay, ids, ids)          # the next restore on the counter is clean again
+    assert r.status == 0 and grp.counter_status(1) == 0
+    assert [_drain(grp.eventfd_of(1, 0, l)) for l in range(shape.num_layers)] == [1] * shape.num_layers

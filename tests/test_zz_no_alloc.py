@@ -114,3 +114,33 @@ def test_noalloc_entry_rejects_sizes_beyond_its_array():
     rc = fn(ctypes.byref(a), None, err, len(err))
     assert rc != 0 and b"1024" in err.value
     torch.cuda.synchronize()
+
+
+def test_noalloc_entry_rejects_a_short_tensor_table_and_releases_an_empty_call():
+    fn = _entry()
+    err = ctypes.create_string_buffer(256)
+    dev = torch.device("cuda:0")
+    shape = KVShape("na3", 4, 2, 64, tokens_per_block=16)
+    kv, layout = alloc_paged_cache(shape, 8, dev, "vllm", fill="zeros")
+    reg = register_tensors(kv, layout)
+    chunk = reg.chunk_bytes
+    bb = shape.num_layers * shape.kv_dim * chunk
+    pool = torch.zeros(8, bb, dtype=torch.uint8).pin_memory()
+    host = HostSide(pool.data_ptr(), shape.kv_dim * chunk, chunk, bb, 8)
+    ids = torch.zeros(1, dtype=torch.int64, device=dev)
+    flags = torch.zeros(shape.num_layers, dtype=torch.int32, device=dev)
+    stream = torch.cuda.current_stream()
+    # a table one tensor short of what 4 layers address: refused on the host, nothing launched
+    a = _args(reg, host, ids, ids, flags, new_status(dev), 1, shape.num_layers)
+    a.num_gpu_ptrs = shape.num_layers - 1
+    rc = fn(ctypes.byref(a), ctypes.c_void_p(stream.cuda_stream), err, len(err))
+    assert rc == -1 and b"tensor table" in err.value
+    torch.cuda.synchronize()
+    assert flags.tolist() == [0] * shape.num_layers
+    # an empty restore copies nothing and still publishes every layer's flag, in stream order
+    empty = torch.zeros(0, dtype=torch.int64, device=dev)
+    a = _args(reg, host, empty, empty, flags, new_status(dev), 7, shape.num_layers)
+    rc = fn(ctypes.byref(a), ctypes.c_void_p(stream.cuda_stream), err, len(err))
+    assert rc == 0, err.value
+    torch.cuda.synchronize()
+    assert flags.tolist() == [7] * shape.num_layers
