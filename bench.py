@@ -131,7 +131,9 @@ def kernel_desc(worker, env) -> dict:
         pack = not worker.h2d
         return {"kernel": f"kv_compress_kernel<{'pack' if pack else 'unpack'}> ({worker.codec})"
                 if worker.codec == "bf16_xp" else f"kv_quant_kernel<{'pack' if pack else 'unpack'}> ({worker.codec})",
-                "ctas": int(worker.num_ctas), "threads": 256}
+                "ctas": (int(worker.num_ctas) + 1) // 2 if worker.codec == "bf16_xp" else int(worker.num_ctas),
+                "threads": 256 if worker.codec == "bf16_xp" else 128,
+                "note": "two 128-thread tile pipelines per CTA" if worker.codec == "bf16_xp" else ""}
     ctas = env.transfer_num_cta_h2d if worker.h2d else env.transfer_num_cta_d2h
     eng = env.transfer_engine
     return {"kernel": "kv_copy_bulk_kernel (cp.async.bulk ring)" if eng in ("tma", "auto", "") else f"engine={eng}",

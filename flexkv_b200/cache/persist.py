@@ -75,6 +75,7 @@ def signature(cache_config: CacheConfig, model_config: ModelConfig) -> Dict[str,
         "offload_quant": str(c.offload_quant),
         # inputs of the host codec decision (the codec fixes the bytes of a block)
         "compression": bool(c.enable_compression or env.enable_compression),
+        "codec_format": 2,      # layout of a packed tile (rank-coded exponents); bump when the bytes change
         "layerwise": bool(env.enable_layerwise_transfer),
         "p2p_cpu": bool(c.enable_p2p_cpu),
         "host_layout": str(env.cpu_layout_type),

@@ -13,7 +13,6 @@ namespace py = pybind11;
 using namespace fkv;
 
 void init_layerwise_bindings(py::module_& m) {
-  m.attr("LAYER_FAILED_SIGNAL") = py::int_(kLayerFailedSignal);
   py::class_<LayerwiseResult>(m, "LayerwiseResult")
       .def_readonly("status", &LayerwiseResult::status)
       .def_readonly("epoch", &LayerwiseResult::epoch)

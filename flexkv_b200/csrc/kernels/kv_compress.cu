@@ -1,61 +1,346 @@
 #include "kv_compress.h"
 
+#include "kv_signal.cuh"
 #include "ptx_sm100.cuh"
 
 namespace fkv {
 namespace {
 
-constexpr int kThreads = 256;
+// A CTA runs kGroups independent tile pipelines of kThreads threads each (own stage ring, own scratch, own
+// named barrier): one pipeline keeps a single warp per scheduler and waits out every shared-memory round
+// trip; two per SM overlap each other's latencies, so half as many SMs carry the same link rate.
+constexpr int kThreads = 128;
+constexpr int kGroups = 2;
 constexpr int kWarps = kThreads / 32;
-constexpr int kGroup = 128;
-constexpr int kGroupsPerTile = kCompressTileElems / kGroup;   // 64
-constexpr int kInStages = 5;
-constexpr int kEpoch = 2048;                                  // tile sizes fetched per batch (decompress)
+constexpr int kEpoch = 1024;                                  // tile sizes fetched per batch (decompress)
 constexpr uint64_t kWaitBudgetNs = 2000000000ull;
+constexpr int kTblBatch = 32;                                 // size-table entries written per bulk store (128 bytes)
+constexpr uint32_t kFull = 0xffffffffu;
 
+template <int IN_STAGES>
 struct __align__(16) Smem {
-  uint8_t in[kInStages][kCompressTileSlot];
+  uint8_t in[IN_STAGES][kCompressTileSlot];
   uint8_t out[2][kCompressTileSlot];
 };
 
-__device__ __forceinline__ int bits_for(int range) {   // smallest w with range < 2^w
-  return range == 0 ? 0 : 32 - __clz(range);
+// barrier among the kThreads threads of one pipeline (hardware barrier 1 + group; 0 is __syncthreads')
+__device__ __forceinline__ void group_sync(int grp) {
+  asm volatile("bar.sync %0, %1;" ::"r"(grp + 1), "n"(kThreads) : "memory");
 }
 
-constexpr int kTblBatch = 32;   // size-table entries written per bulk store (128 bytes)
+// Per-tile scratch of the coder (static shared memory).
+struct Scratch {
+  uint32_t hist[kWarps][256];   // per-warp exponent histograms
+  uint32_t cnt[256];            // their sum
+  uint32_t code[256];           // exponent -> code bits (low 24) | code length (high 8)
+  uint8_t nz[256];              // exponents that occur, compacted
+  uint32_t seg[8];              // occurrences per 32-exponent segment
+  uint32_t warp_tot[kWarps];
+};
 
-template <bool COMPRESS>
-__global__ void __launch_bounds__(kThreads, 1)
+// code of the exponent with frequency rank r (see kv_compress.h); LSB first
+__device__ __forceinline__ uint32_t code_of_rank(int r) {
+  if (r < kCodeShortRanks) return (uint32_t)r | (2u << 24);
+  const int n = r - kCodeShortRanks;                       // n ones between the "11" marker and the closing zero
+  return 3u | (((1u << n) - 1u) << 2) | ((uint32_t)(n + 3) << 24);
+}
+__device__ __forceinline__ uint32_t code_escape(int e) {
+  return 3u | (((1u << kCodeEscapeOnes) - 1u) << 2) | ((uint32_t)e << (2 + kCodeEscapeOnes)) |
+         ((uint32_t)(2 + kCodeEscapeOnes + 8) << 24);
+}
+
+__device__ __forceinline__ uint32_t block_exclusive_scan(uint32_t v, Scratch& sc, uint32_t& total, int grp) {
+  const int lane = threadIdx.x & 31, warp = (threadIdx.x >> 5) & (kWarps - 1);
+  uint32_t incl = v;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const uint32_t u = __shfl_up_sync(kFull, incl, o);
+    if (lane >= o) incl += u;
+  }
+  if (lane == 31) sc.warp_tot[warp] = incl;
+  group_sync(grp);
+  uint32_t base = 0;
+  total = 0;
+#pragma unroll
+  for (int w = 0; w < kWarps; ++w) {
+    const uint32_t t = sc.warp_tot[w];
+    if (w < warp) base += t;
+    total += t;
+  }
+  return base + incl - v;
+}
+
+// Packs `elems` bf16 values at `in` into `out`; every thread returns the packed size (a multiple of 16).
+__device__ uint32_t compress_tile(const uint8_t* __restrict__ in, uint8_t* __restrict__ out, int elems, Scratch& sc,
+                                  int grp) {
+  const int tid = threadIdx.x & (kThreads - 1), lane = tid & 31, warp = tid >> 5;
+  const int n_chunks = elems / kCodeChunkVals;
+  const uint32_t* in32 = reinterpret_cast<const uint32_t*>(in);
+  const int off_sm = kCodeHeaderBytes + n_chunks, off_exp = off_sm + elems;
+  constexpr int W = kCodeChunkVals / 2;     // words per chunk
+  for (int i = tid; i < kWarps * 256; i += kThreads) (&sc.hist[0][0])[i] = 0;
+  if (tid < kCodeRanks) out[16 + tid] = 0;
+  // this thread's chunk stays in registers for the three passes over it
+  uint32_t x[W];
+  const bool active = tid < n_chunks;
+  if (active) {
+#pragma unroll
+    for (int k = 0; k < W; ++k) x[k] = in32[k * n_chunks + tid];
+  } else {
+#pragma unroll
+    for (int k = 0; k < W; ++k) x[k] = 0;
+  }
+  group_sync(grp);
+  // 1: exponent histogram over a sample (the first kCodeSampleWords words of every chunk: ranks only steer
+  //    the code lengths, any table decodes) and the sign|mantissa plane
+  if (active) {
+    uint16_t* sm16 = reinterpret_cast<uint16_t*>(out + off_sm);
+#pragma unroll
+    for (int k = 0; k < W; ++k) {
+      if (k < kCodeSampleWords) {
+        atomicAdd(&sc.hist[warp][(x[k] >> 7) & 0xffu], 1u);
+        atomicAdd(&sc.hist[warp][(x[k] >> 23) & 0xffu], 1u);
+      }
+      sm16[k * n_chunks + tid] = (uint16_t)(((x[k] >> 8) & 0x80u) | (x[k] & 0x7fu) |
+                                            ((((x[k] >> 24) & 0x80u) | ((x[k] >> 16) & 0x7fu)) << 8));
+    }
+  }
+  group_sync(grp);
+  // 2: counts, the exponents that occur, their frequency ranks -> code table and symbol table
+  uint32_t c0 = 0, c1 = 0;
+#pragma unroll
+  for (int w = 0; w < kWarps; ++w) { c0 += sc.hist[w][tid]; c1 += sc.hist[w][tid + 128]; }
+  sc.cnt[tid] = c0;
+  sc.cnt[tid + 128] = c1;
+  sc.code[tid] = code_escape(tid);
+  sc.code[tid + 128] = code_escape(tid + 128);
+  const uint32_t b0 = __ballot_sync(kFull, c0 > 0), b1 = __ballot_sync(kFull, c1 > 0);
+  if (lane == 0) { sc.seg[warp] = __popc(b0); sc.seg[4 + warp] = __popc(b1); }
+  group_sync(grp);
+  uint32_t base0 = 0, base1 = 0, n_nz = 0;
+#pragma unroll
+  for (int s = 0; s < 8; ++s) {
+    const uint32_t v = sc.seg[s];
+    if (s < warp) base0 += v;
+    if (s < 4 + warp) base1 += v;
+    n_nz += v;
+  }
+  const uint32_t lt = (1u << lane) - 1u;
+  if (c0 > 0) sc.nz[base0 + __popc(b0 & lt)] = (uint8_t)tid;
+  if (c1 > 0) sc.nz[base1 + __popc(b1 & lt)] = (uint8_t)(tid + 128);
+  group_sync(grp);
+  if (n_nz <= 32) {
+    // the usual case: one warp ranks all occurring exponents through shuffles
+    if (warp == 0) {
+      const int b = lane < (int)n_nz ? sc.nz[lane] : 256;
+      const uint32_t c = lane < (int)n_nz ? sc.cnt[b] : 0u;
+      int r = 0;
+      for (int j = 0; j < (int)n_nz; ++j) {
+        const uint32_t co = __shfl_sync(kFull, c, j);
+        const int bo = __shfl_sync(kFull, b, j);
+        r += (co > c || (co == c && bo < b)) ? 1 : 0;
+      }
+      if (lane < (int)n_nz && r < kCodeRanks) { sc.code[b] = code_of_rank(r); out[16 + r] = (uint8_t)b; }
+    }
+  } else {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const uint32_t c = h ? c1 : c0;
+      const int b = tid + 128 * h;
+      if (c == 0) continue;
+      int r = 0;
+      for (uint32_t i = 0; i < n_nz; ++i) {
+        const int bo = sc.nz[i];
+        const uint32_t co = sc.cnt[bo];
+        r += (co > c || (co == c && bo < b)) ? 1 : 0;
+      }
+      if (r < kCodeRanks) { sc.code[b] = code_of_rank(r); out[16 + r] = (uint8_t)b; }
+    }
+  }
+  group_sync(grp);
+  // 3: coded size of every chunk, their offsets, and whether coding pays at all
+  uint32_t bits = 0;
+  if (active) {
+#pragma unroll
+    for (int k = 0; k < W; ++k)
+      bits += (sc.code[(x[k] >> 7) & 0xffu] >> 24) + (sc.code[(x[k] >> 23) & 0xffu] >> 24);
+    out[kCodeHeaderBytes + tid] = (uint8_t)((bits + 7) >> 3);
+  }
+  const uint32_t nbytes = (bits + 7) >> 3;
+  uint32_t total_exp;
+  const uint32_t myoff = block_exclusive_scan(nbytes, sc, total_exp, grp);
+  const uint32_t coded_total = ((uint32_t)off_exp + total_exp + 15u) & ~15u;
+  const uint32_t raw_total = 16u + (uint32_t)elems * 2u;
+  const bool coded = coded_total < raw_total;
+  if (coded) {
+    // 4a: the prefix codes of this thread's 64 exponents, bytes appended at the chunk's offset
+    if (active) {
+      uint8_t* dst = out + off_exp + myoff;
+      uint64_t acc = 0;
+      int nb = 0;
+#pragma unroll
+      for (int k = 0; k < W; ++k) {
+        const uint32_t ca = sc.code[(x[k] >> 7) & 0xffu], cb = sc.code[(x[k] >> 23) & 0xffu];
+        acc |= (uint64_t)(ca & 0xffffffu) << nb;
+        nb += (int)(ca >> 24);
+        if (nb >= 32) {                              // at most 31 + 23 bits are pending here
+          dst[0] = (uint8_t)acc; dst[1] = (uint8_t)(acc >> 8); dst[2] = (uint8_t)(acc >> 16); dst[3] = (uint8_t)(acc >> 24);
+          dst += 4; acc >>= 32; nb -= 32;
+        }
+        acc |= (uint64_t)(cb & 0xffffffu) << nb;
+        nb += (int)(cb >> 24);
+        if (nb >= 32) {
+          dst[0] = (uint8_t)acc; dst[1] = (uint8_t)(acc >> 8); dst[2] = (uint8_t)(acc >> 16); dst[3] = (uint8_t)(acc >> 24);
+          dst += 4; acc >>= 32; nb -= 32;
+        }
+      }
+      while (nb > 0) { *dst++ = (uint8_t)acc; acc >>= 8; nb -= 8; }
+    }
+    if (tid == 0) {
+      for (uint32_t i = (uint32_t)off_exp + total_exp; i < coded_total; ++i) out[i] = 0;
+      out[0] = 1;
+      out[1] = (uint8_t)(n_nz < (uint32_t)kCodeRanks ? n_nz : (uint32_t)kCodeRanks);
+      *reinterpret_cast<uint16_t*>(out + 2) = (uint16_t)n_chunks;
+      *reinterpret_cast<uint32_t*>(out + 4) = coded_total;
+      *reinterpret_cast<uint32_t*>(out + 8) = (uint32_t)elems;
+      *reinterpret_cast<uint32_t*>(out + 12) = 0;
+    }
+    return coded_total;
+  }
+  // 4b: exponents too spread out for the code to pay: the tile travels raw behind its header
+  const uint4* src = reinterpret_cast<const uint4*>(in);
+  uint4* dstv = reinterpret_cast<uint4*>(out + 16);
+  for (int i = tid; i < elems / 8; i += kThreads) dstv[i] = src[i];
+  if (tid == 0) {
+    out[0] = 0;
+    out[1] = 0;
+    *reinterpret_cast<uint16_t*>(out + 2) = 0;
+    *reinterpret_cast<uint32_t*>(out + 4) = raw_total;
+    *reinterpret_cast<uint32_t*>(out + 8) = (uint32_t)elems;
+    *reinterpret_cast<uint32_t*>(out + 12) = 0;
+  }
+  return raw_total;
+}
+
+// Unpacks a tile of `size` bytes at `in` into `elems` bf16 values at `out`. False (for every thread) when the
+// header or the chunk table does not describe a tile of this shape and size; nothing past the slot is read.
+__device__ bool decompress_tile(const uint8_t* __restrict__ in, uint8_t* __restrict__ out, int elems, uint32_t size,
+                                Scratch& sc, int grp) {
+  const int tid = threadIdx.x & (kThreads - 1);
+  const int mode = in[0];
+  const uint32_t total = *reinterpret_cast<const uint32_t*>(in + 4);
+  const uint32_t elems_h = *reinterpret_cast<const uint32_t*>(in + 8);
+  if (total != size || elems_h != (uint32_t)elems || mode > 1) return false;
+  if (mode == 0) {
+    if (size != 16u + (uint32_t)elems * 2u) return false;
+    const uint4* src = reinterpret_cast<const uint4*>(in + 16);
+    uint4* dst = reinterpret_cast<uint4*>(out);
+    for (int i = tid; i < elems / 8; i += kThreads) dst[i] = src[i];
+    return true;
+  }
+  const int n_chunks = elems / kCodeChunkVals;
+  if (*reinterpret_cast<const uint16_t*>(in + 2) != n_chunks) return false;
+  const int off_sm = kCodeHeaderBytes + n_chunks, off_exp = off_sm + elems;
+  const uint32_t nbytes = tid < n_chunks ? in[kCodeHeaderBytes + tid] : 0u;
+  uint32_t total_exp;
+  const uint32_t myoff = block_exclusive_scan(nbytes, sc, total_exp, grp);
+  if ((uint32_t)off_exp + total_exp > size) return false;       // same value in every thread
+  if (tid < n_chunks) {
+    const uint32_t* in32 = reinterpret_cast<const uint32_t*>(in);
+    const uint16_t* sm16 = reinterpret_cast<const uint16_t*>(in + off_sm);
+    const uint8_t* syms = in + 16;
+    uint32_t* out32 = reinterpret_cast<uint32_t*>(out);
+    const uint32_t B = (uint32_t)off_exp + myoff;
+    uint32_t wi = B >> 2;
+    const int sh = (int)(B & 3u) * 8;
+    uint64_t buf = ((uint64_t)in32[wi] | ((uint64_t)in32[wi + 1] << 32)) >> sh;   // reads stay inside the stage ring
+    int avail = 64 - sh;
+    wi += 2;
+    auto next_exp = [&]() -> uint32_t {
+      const uint32_t v = (uint32_t)buf;
+      const uint32_t c = v & 3u, t = v >> 2;
+      const int n = __ffs((int)~t) - 1;                        // ones that follow the "11" marker
+      const bool esc = n >= kCodeEscapeOnes;
+      const int len = c != 3u ? 2 : (esc ? 2 + kCodeEscapeOnes + 8 : n + 3);
+      const uint32_t e = c != 3u ? syms[c] : (esc ? ((t >> kCodeEscapeOnes) & 0xffu) : syms[kCodeShortRanks + n]);
+      buf >>= len;
+      avail -= len;
+      if (avail < 32) { buf |= (uint64_t)in32[wi++] << avail; avail += 32; }
+      return e;
+    };
+#pragma unroll 2
+    for (int k = 0; k < kCodeChunkVals / 2; ++k) {
+      const int w = k * n_chunks + tid;
+      const uint32_t ea = next_exp(), eb = next_exp();
+      const uint32_t s = sm16[w];
+      const uint32_t lo = ((s & 0x80u) << 8) | (ea << 7) | (s & 0x7fu);
+      const uint32_t hi = ((s & 0x8000u)) | (eb << 7) | ((s >> 8) & 0x7fu);
+      out32[w] = lo | (hi << 16);
+    }
+  }
+  return true;
+}
+
+// static shared state of one pipeline
+template <bool COMPRESS, int IN_STAGES>
+struct __align__(128) GroupState {
+  uint32_t tbl[3][kTblBatch];
+  uint64_t full[IN_STAGES];
+  uint64_t dst[IN_STAGES];
+  uint64_t table_idx[IN_STAGES];
+  int32_t elems[IN_STAGES];
+  uint32_t in_bytes[IN_STAGES];
+  uint32_t sizes[COMPRESS ? 1 : kEpoch];
+  Scratch sc;
+  int abort;
+};
+
+template <bool COMPRESS, int kInStages>
+__global__ void __launch_bounds__(kThreads * kGroups, 1)
 kv_compress_kernel(const __grid_constant__ KvCopyParams p, uint32_t* __restrict__ size_table, int layers_total,
                    int tiles_per_chunk) {
   extern __shared__ __align__(128) uint8_t smem_raw[];
-  Smem& sm = *reinterpret_cast<Smem*>(smem_raw);
-  __shared__ __align__(8) uint64_t full[kInStages];
-  __shared__ uint64_t s_dst[kInStages];
-  __shared__ uint64_t s_table_idx[kInStages];
-  __shared__ __align__(128) uint32_t s_tbl[3][kTblBatch];
-  __shared__ int32_t s_elems[kInStages];
-  __shared__ int32_t s_w[kGroupsPerTile];
-  __shared__ int32_t s_off[kGroupsPerTile + 1];
-  __shared__ uint32_t s_sizes[kEpoch];
-  __shared__ int s_abort;
+  __shared__ GroupState<COMPRESS, kInStages> gstate[kGroups];
+  const int grp = threadIdx.x / kThreads;
+  const int tid = threadIdx.x % kThreads;
+  Smem<kInStages>& sm = reinterpret_cast<Smem<kInStages>*>(smem_raw)[grp];
+  GroupState<COMPRESS, kInStages>& gs = gstate[grp];
+  uint64_t* full = gs.full;
+  uint64_t* s_dst = gs.dst;
+  uint64_t* s_table_idx = gs.table_idx;
+  uint32_t(*s_tbl)[kTblBatch] = gs.tbl;
+  int32_t* s_elems = gs.elems;
+  uint32_t* s_in_bytes = gs.in_bytes;
+  uint32_t* s_sizes = gs.sizes;
+  Scratch& sc = gs.sc;
+  int& s_abort = gs.abort;
+  // every pipeline is a CTA of its own as far as the work split and the completion count go
+  const int64_t vcta = (int64_t)blockIdx.x * kGroups + grp, vgrid = (int64_t)gridDim.x * kGroups;
 
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   if (tid == 0) {
     for (int s = 0; s < kInStages; ++s) ptx::mbar_init(&full[s], 1);
     s_abort = 0;
     ptx::fence_mbar_init();
   }
-  __syncthreads();
+  group_sync(grp);
 
   const int64_t chunk_elems = p.chunk_bytes / 2;
-  const int32_t span = p.num_layers * p.kv_dim * tiles_per_chunk;
-  const int64_t total = (int64_t)span * p.num_pairs;
-  // every CTA owns one contiguous run of tiles: consecutive tiles share their block ids (fetched
-  // once per pair, possibly over PCIe) and their size-table neighbourhood
-  const int64_t per_cta = (total + gridDim.x - 1) / gridDim.x;
-  const int64_t first = (int64_t)blockIdx.x * per_cta, step = 1;
-  const int64_t n_mine = first < total ? (total - first < per_cta ? total - first : per_cta) : 0;
+  const bool by_layer = !COMPRESS && p.layer_major;
+  // tiles of one major unit: a pair (all its layers), or, walking layer by layer, a layer (all its pairs)
+  const int32_t span = (by_layer ? p.num_pairs : p.num_layers) * p.kv_dim * tiles_per_chunk;
+  const int64_t total = (int64_t)span * (by_layer ? p.num_layers : p.num_pairs);
+  // Pair-major: every CTA owns one contiguous run of tiles, so consecutive tiles share their block ids
+  // (fetched once per pair, possibly over PCIe) and their size-table neighbourhood. Layer by layer the CTAs
+  // interleave instead, so that all of them finish a layer at about the same time.
+  // (whole blocks per pipeline when there are enough of them: runs that start inside a block showed up as a
+  // 10-15 % dip in link rate at pipeline counts that do not divide the block count)
+  const int64_t per_cta = !by_layer && p.num_pairs >= 4 * vgrid ? (p.num_pairs + vgrid - 1) / vgrid * span
+                                                                 : (total + vgrid - 1) / vgrid;
+  const int64_t first = by_layer ? vcta : vcta * per_cta;
+  const int64_t step = by_layer ? vgrid : 1;
+  const int64_t n_mine = first >= total ? 0
+                         : by_layer   ? (total - first + step - 1) / step
+                                      : (total - first < per_cta ? total - first : per_cta);
   // thread 0 keeps the ids of the pair it is working on and asks for the next pair's early
   int32_t id_pair = -1;
   int64_t id_g = 0, id_c = 0, nx_g = 0, nx_c = 0;
@@ -70,15 +355,20 @@ kv_compress_kernel(const __grid_constant__ KvCopyParams p, uint32_t* __restrict_
   };
   int err = 0;
   uint32_t phases = 0;
+  int32_t signalled = 0;   // thread 0, layer by layer: layers [0, signalled) already reported by this CTA
+
+  auto layer_rel_of = [&](int64_t it) -> int32_t { return (int32_t)((first + it * step) / span); };
 
   // decodes tile `it` of this CTA; returns false for a pair whose ids are out of range
   auto locate = [&](int64_t it, uint64_t& g, uint64_t& c, uint64_t& tidx, int32_t& elems, bool cached) -> bool {
     const int64_t t = first + it * step;
-    const int32_t pair = (int32_t)(t / span), r = (int32_t)(t % span);
+    const int32_t major = (int32_t)(t / span), r = (int32_t)(t % span);
     const int s_ = r % tiles_per_chunk, q = r / tiles_per_chunk;
-    const int kv = q % p.kv_dim, layer = p.layer_start + q / p.kv_dim;
+    const int kv = q % p.kv_dim;
+    const int32_t pair = by_layer ? q / p.kv_dim : major;
+    const int layer = p.layer_start + (by_layer ? major : q / p.kv_dim);
     int64_t gblk, cblk;
-    if (cached) pair_ids(pair, gblk, cblk);
+    if (cached && !by_layer) pair_ids(pair, gblk, cblk);
     else { gblk = __ldg(p.gpu_blocks + pair); cblk = __ldg(p.cpu_blocks + pair); }
     bool ok = true;
     if (p.gpu_num_blocks > 0 && (gblk < 0 || gblk >= p.gpu_num_blocks)) { err |= KV_ERR_GPU_BLOCK_RANGE; ok = false; }
@@ -108,18 +398,20 @@ kv_compress_kernel(const __grid_constant__ KvCopyParams p, uint32_t* __restrict_
     s_elems[st] = elems;
     if (COMPRESS) {
       s_dst[st] = c;
+      s_in_bytes[st] = (uint32_t)elems * 2;
       ptx::mbar_expect_tx(&full[st], (uint32_t)elems * 2);
       ptx::bulk_g2s(sm.in[st], reinterpret_cast<const void*>(g), (uint32_t)elems * 2, &full[st]);
     } else {
       s_dst[st] = g;
-      uint32_t sz = s_sizes[it % kEpoch];
-      const uint32_t cap = 2u * (uint32_t)(elems / kGroup) + 256u * (uint32_t)(elems / kGroup);
-      if (sz < 16 || sz > cap || (sz & 15u)) {   // a slot that was never written or a corrupt table entry
+      const uint32_t sz = s_sizes[it % kEpoch];
+      const uint32_t cap = 16u + 2u * (uint32_t)elems;
+      if (sz < 32 || sz > cap || (sz & 15u)) {   // a slot that was never written or a corrupt table entry
         err |= KV_ERR_PAYLOAD_OVERFLOW;
         s_elems[st] = 0;
         ptx::mbar_arrive(&full[st]);
         return;
       }
+      s_in_bytes[st] = sz;
       ptx::mbar_expect_tx(&full[st], sz);
       ptx::bulk_g2s(sm.in[st], reinterpret_cast<const void*>(c), sz, &full[st]);
     }
@@ -153,7 +445,7 @@ kv_compress_kernel(const __grid_constant__ KvCopyParams p, uint32_t* __restrict_
     tbl_n = 0;
   };
 
-  if (!COMPRESS) { fetch_sizes(0); __syncthreads(); }
+  if (!COMPRESS) { fetch_sizes(0); group_sync(grp); }
   if (tid == 0)
     for (int64_t it = 0; it < n_mine && it < kInStages - 1; ++it) issue_load(it);
 
@@ -162,124 +454,42 @@ kv_compress_kernel(const __grid_constant__ KvCopyParams p, uint32_t* __restrict_
     if (!COMPRESS) {
       // the prefetch below reaches kInStages-1 tiles ahead: refill the size ring before it crosses into a new epoch
       const int64_t ahead = it + kInStages - 1;
-      if (ahead % kEpoch == 0 && ahead > 0 && ahead < n_mine) { __syncthreads(); fetch_sizes(ahead); __syncthreads(); }
+      if (ahead % kEpoch == 0 && ahead > 0 && ahead < n_mine) { group_sync(grp); fetch_sizes(ahead); group_sync(grp); }
     }
     if (tid == 0) {
+      if (by_layer && p.done_counter) {
+        const int32_t lr = layer_rel_of(it);
+        if (lr > signalled) {
+          // first tile of a later layer: everything this CTA owned in the earlier layers is committed;
+          // wait for those stores to be performed and report the layers
+          ptx::bulk_wait<0>();
+          signal_layers(p, signalled, lr, (unsigned)vgrid);
+          signalled = lr;
+        }
+      }
       if (it + kInStages - 1 < n_mine) issue_load(it + kInStages - 1);
       if (it >= 2) ptx::bulk_wait_read<1>();
     }
-    __syncthreads();
+    group_sync(grp);
     const int ok = ptx::mbar_wait_bounded(&full[st], (phases >> st) & 1u, kWaitBudgetNs) ? 1 : 0;
     phases ^= 1u << st;
-    if (!__syncthreads_and(ok)) {
-      if (tid == 0) s_abort = 1;
-      break;
-    }
+    if (!ok) s_abort = 1;                 // any thread whose wait ran out; the pipeline leaves together
+    group_sync(grp);
+    if (*reinterpret_cast<volatile int*>(&s_abort)) break;
     const int elems = s_elems[st];
-    const int groups = elems / kGroup;
-    const int hdr = (groups * 2 + 15) & ~15;
     uint32_t out_bytes = 0;
-    if (COMPRESS) {
-      const uint16_t* src = reinterpret_cast<const uint16_t*>(sm.in[st]);
-      uint8_t* out = sm.out[ob];
-      // pass 1: exponent range of every group -> header and widths
-      for (int g = warp; g < groups; g += kWarps) {
-        const uint2 raw = *reinterpret_cast<const uint2*>(src + g * kGroup + lane * 4);
-        const int e0 = (raw.x >> 7) & 0xff, e1 = (raw.x >> 23) & 0xff, e2 = (raw.y >> 7) & 0xff, e3 = (raw.y >> 23) & 0xff;
-        int emax = max(max(e0, e1), max(e2, e3)), emin = min(min(e0, e1), min(e2, e3));
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-          emax = max(emax, __shfl_xor_sync(0xffffffffu, emax, o));
-          emin = min(emin, __shfl_xor_sync(0xffffffffu, emin, o));
-        }
-        if (lane == 0) {
-          const int w = bits_for(emax - emin);
-          s_w[g] = w;
-          out[2 * g] = (uint8_t)emax;
-          out[2 * g + 1] = (uint8_t)w;
-        }
+    if (elems > 0) {
+      if (COMPRESS) {
+        out_bytes = compress_tile(sm.in[st], sm.out[ob], elems, sc, grp);
+      } else {
+        if (decompress_tile(sm.in[st], sm.out[ob], elems, s_in_bytes[st], sc, grp)) out_bytes = (uint32_t)elems * 2;
+        else err |= KV_ERR_PAYLOAD_OVERFLOW;   // same verdict in every thread; thread 0 reports it
       }
-      __syncthreads();
-      if (warp == 0) {   // exclusive scan of the group sizes (two groups per lane)
-        const int a = lane * 2 < groups ? kGroup + 16 * s_w[lane * 2] : 0;
-        const int b = lane * 2 + 1 < groups ? kGroup + 16 * s_w[lane * 2 + 1] : 0;
-        int incl = a + b;
-#pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-          const int v = __shfl_up_sync(0xffffffffu, incl, o);
-          if (lane >= o) incl += v;
-        }
-        const int excl = incl - (a + b);
-        s_off[lane * 2] = hdr + excl;
-        s_off[lane * 2 + 1] = hdr + excl + a;
-        if (lane == 31) s_off[kGroupsPerTile] = hdr + incl;
-      }
-      __syncthreads();
-      // pass 2: sign|mantissa bytes and the bit planes of the exponent distances
-      for (int g = warp; g < groups; g += kWarps) {
-        const uint2 raw = *reinterpret_cast<const uint2*>(src + g * kGroup + lane * 4);
-        const uint32_t v0 = raw.x & 0xffffu, v1 = raw.x >> 16, v2 = raw.y & 0xffffu, v3 = raw.y >> 16;
-        const int emax = out[2 * g], w = s_w[g];
-        uint8_t* gp = out + s_off[g];
-        const uint32_t sm4 = (((v0 >> 8) & 0x80u) | (v0 & 0x7fu)) | ((((v1 >> 8) & 0x80u) | (v1 & 0x7fu)) << 8) |
-                             ((((v2 >> 8) & 0x80u) | (v2 & 0x7fu)) << 16) | ((((v3 >> 8) & 0x80u) | (v3 & 0x7fu)) << 24);
-        *reinterpret_cast<uint32_t*>(gp + lane * 4) = sm4;
-        const int d0 = emax - (int)((v0 >> 7) & 0xff), d1 = emax - (int)((v1 >> 7) & 0xff),
-                  d2 = emax - (int)((v2 >> 7) & 0xff), d3 = emax - (int)((v3 >> 7) & 0xff);
-        uint32_t mine = 0;   // lane (b*4 + j) keeps the plane (b, j)
-        for (int b = 0; b < w; ++b) {
-          const uint32_t p0 = __ballot_sync(0xffffffffu, (d0 >> b) & 1), p1 = __ballot_sync(0xffffffffu, (d1 >> b) & 1),
-                         p2 = __ballot_sync(0xffffffffu, (d2 >> b) & 1), p3 = __ballot_sync(0xffffffffu, (d3 >> b) & 1);
-          if ((lane >> 2) == b) mine = (lane & 3) == 0 ? p0 : (lane & 3) == 1 ? p1 : (lane & 3) == 2 ? p2 : p3;
-        }
-        if (lane < 4 * w) *reinterpret_cast<uint32_t*>(gp + kGroup + lane * 4) = mine;
-      }
-      out_bytes = groups ? (uint32_t)s_off[groups] : 0;   // s_off[groups] = header + all group bodies
-    } else {
-      const uint8_t* in = sm.in[st];
-      uint16_t* dst = reinterpret_cast<uint16_t*>(sm.out[ob]);
-      if (tid < groups) s_w[tid] = in[2 * tid + 1] > 8 ? 8 : in[2 * tid + 1];
-      __syncthreads();
-      if (warp == 0) {
-        const int a = lane * 2 < groups ? kGroup + 16 * s_w[lane * 2] : 0;
-        const int b = lane * 2 + 1 < groups ? kGroup + 16 * s_w[lane * 2 + 1] : 0;
-        int incl = a + b;
-#pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-          const int v = __shfl_up_sync(0xffffffffu, incl, o);
-          if (lane >= o) incl += v;
-        }
-        const int excl = incl - (a + b);
-        s_off[lane * 2] = hdr + excl;
-        s_off[lane * 2 + 1] = hdr + excl + a;
-      }
-      __syncthreads();
-      for (int g = warp; g < groups; g += kWarps) {
-        const int emax = in[2 * g], w = s_w[g];
-        const uint8_t* gp = in + s_off[g];
-        const uint32_t sm4 = *reinterpret_cast<const uint32_t*>(gp + lane * 4);
-        int d0 = 0, d1 = 0, d2 = 0, d3 = 0;
-        for (int b = 0; b < w; ++b) {
-          const uint4 pl = *reinterpret_cast<const uint4*>(gp + kGroup + b * 16);   // planes (b, 0..3), broadcast read
-          d0 |= (int)((pl.x >> lane) & 1u) << b;
-          d1 |= (int)((pl.y >> lane) & 1u) << b;
-          d2 |= (int)((pl.z >> lane) & 1u) << b;
-          d3 |= (int)((pl.w >> lane) & 1u) << b;
-        }
-        auto rebuild = [&](uint32_t smb, int d) -> uint32_t {
-          return ((smb & 0x80u) << 8) | ((uint32_t)((emax - d) & 0xff) << 7) | (smb & 0x7fu);
-        };
-        uint2 o;
-        o.x = rebuild(sm4 & 0xffu, d0) | (rebuild((sm4 >> 8) & 0xffu, d1) << 16);
-        o.y = rebuild((sm4 >> 16) & 0xffu, d2) | (rebuild(sm4 >> 24, d3) << 16);
-        *reinterpret_cast<uint2*>(dst + g * kGroup + lane * 4) = o;
-      }
-      out_bytes = (uint32_t)elems * 2;
     }
     ptx::fence_proxy_async_smem();
-    __syncthreads();
+    group_sync(grp);
     if (tid == 0) {
-      if (elems > 0 && out_bytes > 0) {
+      if (out_bytes > 0) {
         ptx::bulk_s2g(reinterpret_cast<void*>(s_dst[st]), sm.out[ob], out_bytes);
         if (COMPRESS) {
           // Table entries of consecutive tiles are consecutive words: collect them and write 128 bytes
@@ -297,9 +507,10 @@ kv_compress_kernel(const __grid_constant__ KvCopyParams p, uint32_t* __restrict_
     if (COMPRESS && tbl_n > 0) { flush_table(); ptx::bulk_commit(); }
     ptx::bulk_wait<0>();
     if (s_abort) err |= KV_ERR_WAIT_EXPIRED;
-    if (err && p.status)
-      for (int b = 0; b < kStatusWords; ++b)
-        if (err & (1 << b)) reinterpret_cast<volatile int32_t*>(p.status)[b] = 1;
+    // the status words are written before any flag of a layer this CTA did not finish is released
+    if (err && p.status) report_status(p.status, err);
+    if (by_layer) signal_layers(p, signalled, p.num_layers, (unsigned)vgrid);
+    else signal_done(p, (unsigned)vgrid);
   }
 }
 
@@ -311,20 +522,29 @@ cudaError_t launch_kv_compress_bf16(const KvCopyParams& p, uint32_t* size_table,
   const int64_t chunk_elems = p.chunk_bytes / 2;
   if ((p.chunk_bytes & 1) || chunk_elems % 1024 != 0 || size_table == nullptr || !kv_copy_tma_eligible(p))
     return cudaErrorInvalidValue;
+  if (p.layer_major && !p.h2d) return cudaErrorInvalidValue;   // per-layer signalling exists for restores only
   const int tiles_per_chunk = (int)compress_tiles_per_chunk(chunk_elems);
   const int64_t total = (int64_t)p.num_pairs * p.num_layers * p.kv_dim * tiles_per_chunk;
-  int ctas = num_ctas > 0 ? num_ctas : 32;
-  if ((int64_t)ctas > total) ctas = (int)total;
-  const int smem = (int)sizeof(Smem) + 128;
+  // `num_ctas` counts 128-thread tile pipelines; two of them share a CTA (and an SM)
+  int64_t pipes = num_ctas > 0 ? num_ctas : 32;
+  if (pipes > total) pipes = total;
+  const int ctas = (int)((pipes + kGroups - 1) / kGroups);
   cudaError_t e;
   if (p.h2d) {
-    e = cudaFuncSetAttribute(kv_compress_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    // host reads need several tiles in flight per pipeline to cover the PCIe round trip
+    constexpr int kIn = 4;
+    const int smem = (int)sizeof(Smem<kIn>) * kGroups + 128;
+    e = cudaFuncSetAttribute(kv_compress_kernel<false, kIn>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return e;
-    kv_compress_kernel<false><<<ctas, kThreads, smem, stream>>>(p, size_table, layers_total, tiles_per_chunk);
+    kv_compress_kernel<false, kIn><<<ctas, kThreads * kGroups, smem, stream>>>(p, size_table, layers_total,
+                                                                               tiles_per_chunk);
   } else {
-    e = cudaFuncSetAttribute(kv_compress_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    constexpr int kIn = 3;
+    const int smem = (int)sizeof(Smem<kIn>) * kGroups + 128;
+    e = cudaFuncSetAttribute(kv_compress_kernel<true, kIn>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return e;
-    kv_compress_kernel<true><<<ctas, kThreads, smem, stream>>>(p, size_table, layers_total, tiles_per_chunk);
+    kv_compress_kernel<true, kIn><<<ctas, kThreads * kGroups, smem, stream>>>(p, size_table, layers_total,
+                                                                              tiles_per_chunk);
   }
   return cudaGetLastError();
 }

@@ -1,24 +1,31 @@
-// Lossless exponent-packing codec for bf16 KV, fused into the paged copy.
+// Lossless exponent coder for bf16 KV, fused into the paged copy.
 //
-// bf16 = sign(1) | exponent(8) | mantissa(7). Inside a group of 128 neighbouring
-// values the exponents span only a few binades, so each group stores its largest
-// exponent once and every value's distance to it in w bits (w = 0..8 chosen per
-// group), next to the untouched sign+mantissa byte. Any bit pattern round-trips
-// exactly (zeros, denormals, NaN, Inf included: they only widen w).
+// bf16 = sign(1) | exponent(8) | mantissa(7). Sign and mantissa of KV values are close to
+// incompressible and travel as one byte per value; the exponents of a tile take only a handful of
+// values with a steep frequency profile, so they are entropy coded with a prefix code over their
+// frequency RANK in the tile. Any bit pattern round-trips exactly (zeros, denormals, NaN, Inf: a rare
+// exponent costs an escape, and a tile whose exponents do not compress travels raw behind its header).
 //
-// GPU->host ("compress"): tile staged from HBM by TMA, packed in shared memory,
-// only the packed bytes are bulk-stored to the host slot and the tile's size goes
-// to a uint32 size table in mapped host memory. Host->GPU is the mirror: sizes are
-// read first, exactly that many bytes cross PCIe. On N(0,1) data the link carries
-// about 0.76 of the raw bytes. The reference reaches the same goal with nvCOMP's
-// ANS coder and a staging kernel (csrc/compression/ans/nvcomp_ans.cu:321-519,
-// csrc/compression/common/staging_transfer.cuh:16-101); the host slot geometry
-// idea is kept: a fixed-size slot per tile, payload in its first `size` bytes.
+// GPU->host ("compress"): tile staged from HBM by TMA, packed in shared memory, only the packed bytes
+// are bulk-stored to the host slot and the tile's size goes to a uint32 size table in mapped host
+// memory. Host->GPU is the mirror: sizes are read first, exactly that many bytes cross PCIe. On N(0,1)
+// data the link carries 0.675 of the raw bytes (the exponent's entropy bounds it at about 0.66). The
+// reference reaches the same goal with nvCOMP's ANS coder and a staging kernel
+// (csrc/compression/ans/nvcomp_ans.cu:321-519, csrc/compression/common/staging_transfer.cuh:16-101);
+// the host slot geometry idea is kept: a fixed-size slot per tile, payload in its first `size` bytes.
 //
-// Tile = 8192 values (16 KiB raw) = 64 groups. Packed tile:
-//   [64 x (e_base u8, w u8)] [group 0: 128 sign|mantissa bytes, w*16 bytes of bit planes] [group 1] ...
-// Bit plane (b, j) of a group is the 32-bit ballot, over the 32 lanes, of bit b of
-// the exponent distance of element 4*lane + j.
+// Tile = up to 8192 values (16 KiB raw), a multiple of 1024. Chunk t of the tile = the 64 values of the
+// 32-bit words t, t + C, t + 2C, ... (C = number of chunks = elems / 64): one thread codes one chunk and
+// neighbouring threads touch neighbouring words. Packed tile, every size a multiple of 16 bytes:
+//   [0]  u8 mode (1 coded, 0 raw)  [1] u8 symbols in use  [2] u16 C  [4] u32 packed size  [8] u32 elems  [12] 0
+//   [16] 16 x u8: the exponent of rank 0..15 (most frequent first, ties by smaller exponent; frequencies are
+//        counted over a sample, the first 8 values of every chunk: the table only steers code lengths)
+//   [32] C x u8: coded bytes of each chunk
+//   [32 + C] elems x u8: sign<<7 | mantissa of every value, in value order
+//   then the chunks' codes back to back, each chunk padded to a byte, the tile padded to 16 bytes.
+// Code of an exponent, bits written LSB first: rank 0..2 -> that rank in 2 bits; rank r = 3..15 -> "11",
+// r-3 one bits, a zero bit; any other exponent -> "11", 13 one bits, the 8 exponent bits (23 bits).
+// Raw tile: the 16-byte header with mode 0, then the values.
 // Host chunk slot = tiles_per_chunk * kCompressTileSlot bytes; chunk elements % 1024 == 0.
 #pragma once
 #include <cstdint>
@@ -29,7 +36,13 @@
 namespace fkv {
 
 constexpr int kCompressTileElems = 8192;
-constexpr int kCompressTileSlot = 2 * kCompressTileElems + 128;   // worst case: every group needs w = 8
+constexpr int kCompressTileSlot = 2 * kCompressTileElems + 128;   // a raw tile (16 + 16384 bytes) fits
+constexpr int kCodeChunkVals = 64;      // values coded by one thread
+constexpr int kCodeHeaderBytes = 32;    // header and symbol table
+constexpr int kCodeRanks = 16;          // exponents with a code of their own
+constexpr int kCodeShortRanks = 3;      // of which this many take 2 bits
+constexpr int kCodeEscapeOnes = kCodeRanks - kCodeShortRanks;   // one bits that announce a literal exponent
+constexpr int kCodeSampleWords = 4;     // the frequency ranks come from the first 4 words (8 values) of every chunk
 
 inline int64_t compress_tiles_per_chunk(int64_t chunk_elems) {
   return (chunk_elems + kCompressTileElems - 1) / kCompressTileElems;
@@ -39,6 +52,8 @@ inline int64_t compress_chunk_slot_bytes(int64_t chunk_elems) {
 }
 
 // p.chunk_bytes = raw bf16 chunk bytes (GPU side); host strides are slot strides.
+// Restores (p.h2d) honour p.layer_major with p.done_counter / dev_flags / host_flags exactly as the plain
+// copy kernel does: tiles are walked layer by layer and each layer's flag is published when it has landed.
 // size_table: mapped-host uint32 array indexed
 //   ((cpu_block * layers_total + layer) * kv_dim + kv) * tiles_per_chunk + tile
 cudaError_t launch_kv_compress_bf16(const KvCopyParams& p, uint32_t* size_table, int layers_total, int num_ctas,

@@ -16,6 +16,7 @@
 // out 16-byte bulk copies (the reference needs an 8-byte path for the same
 // reason: csrc/transfer.cu:34-92) and is the cross-check for engine 0.
 #include "kv_copy.h"
+#include "kv_signal.cuh"
 #include "ptx_sm100.cuh"
 
 namespace fkv {
@@ -23,34 +24,6 @@ namespace {
 
 constexpr uint64_t kWaitBudgetNs = 2000000000ull;  // 2 s per bulk-copy wait
 constexpr uint64_t kSignalBudgetNs = 60000000000ull;  // signaller warp: longer than any restore, still finite
-
-// Error reporting without atomics: `status` is an array of kStatusWords words,
-// one per KvCopyStatus bit, and a CTA that saw error bit b stores 1 to word b.
-// Plain idempotent stores cannot lose a bit when several CTAs report at once,
-// and they work on mapped host memory whether or not the platform offers PCIe
-// atomics. The host ORs the words back into a bit mask.
-__device__ __forceinline__ void report_status(int32_t* status, int err) {
-#pragma unroll
-  for (int b = 0; b < kStatusWords; ++b)
-    if (err & (1 << b)) reinterpret_cast<volatile int32_t*>(status)[b] = 1;
-}
-
-// Last-CTA-out publication of the completion flags (see KvCopyParams). Called by
-// one thread per CTA after all of the CTA's stores are complete.
-__device__ __forceinline__ void signal_done(const KvCopyParams& p) {
-  if (p.done_counter == nullptr) return;
-  ptx::fence_proxy_async_all();  // order the bulk (async proxy) stores before the generic-proxy flag traffic
-  __threadfence();
-  const unsigned prev = atomicAdd(p.done_counter, 1u);
-  if (prev == gridDim.x - 1) {
-    *reinterpret_cast<volatile uint32_t*>(p.done_counter) = 0;
-    __threadfence();
-    for (int l = p.layer_start; l < p.layer_start + p.num_layers; ++l) {
-      if (p.dev_flags) ptx::st_release_gpu(p.dev_flags + l, p.epoch);
-      if (p.host_flags) ptx::st_release_sys(p.host_flags + l, p.epoch);
-    }
-  }
-}
 
 struct TileAddr {
   uint64_t gpu;
@@ -99,26 +72,6 @@ __device__ __forceinline__ bool ids_in_range(const KvCopyParams& p, int64_t g, i
   if (p.gpu_num_blocks > 0 && (g < 0 || g >= p.gpu_num_blocks)) { err |= KV_ERR_GPU_BLOCK_RANGE; ok = false; }
   if (p.cpu_num_blocks > 0 && (c < 0 || c >= p.cpu_num_blocks)) { err |= KV_ERR_CPU_BLOCK_RANGE; ok = false; }
   return ok;
-}
-
-// Per-layer publication for layer-major launches: this CTA has finished (and
-// drained) everything it owns in layers [from, to); the last CTA to say so for
-// a layer resets that layer's counter and publishes the flags.
-__device__ __forceinline__ void signal_layers(const KvCopyParams& p, int from, int to) {
-  if (p.done_counter == nullptr || from >= to) return;
-  // The caller has waited for its bulk stores of these layers (wait_group 0: the writes are performed).
-  // No async-proxy fence here: it would also wait for the loads in flight and drain the pipeline at every
-  // layer boundary; the release below orders the completed stores before the counter and flag updates.
-  __threadfence();
-  for (int l = from; l < to; ++l) {
-    const unsigned prev = atomicAdd(p.done_counter + l, 1u);
-    if (prev == gridDim.x - 1) {
-      reinterpret_cast<volatile uint32_t*>(p.done_counter)[l] = 0;
-      __threadfence();
-      if (p.dev_flags) ptx::st_release_gpu(p.dev_flags + p.layer_start + l, p.epoch);
-      if (p.host_flags) ptx::st_release_sys(p.host_flags + p.layer_start + l, p.epoch);
-    }
-  }
 }
 
 // Layer-major launches run a second warp per CTA whose only job is the per-layer publication: fences, the

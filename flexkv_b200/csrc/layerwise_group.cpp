@@ -190,9 +190,9 @@ cudaError_t LayerwiseGroup::stream_wait_layer(int rank, int counter, int layer, 
   return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorUnknown;
 }
 
-void LayerwiseGroup::notify(int rank, int counter, int layer_lo, int layer_hi, bool failed) {
+void LayerwiseGroup::notify(int rank, int counter, int layer_lo, int layer_hi) {
   if (eventfds_.empty()) return;
-  const uint64_t v = failed ? kLayerFailedSignal : 1;
+  const uint64_t v = 1;
   for (int l = layer_lo; l < layer_hi; ++l) {
     const int fd = eventfd_of(counter, rank, l);
     if (fd >= 0) { ssize_t w = write(fd, &v, sizeof(v)); (void)w; }
@@ -220,14 +220,16 @@ void LayerwiseGroup::release_waiters(int r, const Job& j, int from_layer, int st
     if (e == cudaSuccess) e = cudaStreamSynchronize(rk.notify_stream);
     if (e != cudaSuccess) (void)cudaGetLastError();
   }
-  notify(r, j.counter, from_layer, L, true);
+  notify(r, j.counter, from_layer, L);
 }
 
 void CUDART_CB LayerwiseGroup::host_fn(void* arg) {
   auto* a = static_cast<HostFnArg*>(arg);
-  // a kernel that gave up has written its status words before it released the layers it did not restore
-  const bool failed = status_words_set(a->self->ranks_[(size_t)a->rank]->status);
-  a->self->notify(a->rank, a->counter, a->layer_lo, a->layer_hi, failed);
+  // a kernel that gave up has written its status words before it released the layers it did not restore:
+  // make the failure visible to whoever this wake-up releases
+  if (status_words_set(a->self->ranks_[(size_t)a->rank]->status))
+    a->self->counter_status_[(size_t)a->counter].store(-1, std::memory_order_release);
+  a->self->notify(a->rank, a->counter, a->layer_lo, a->layer_hi);
 }
 
 void LayerwiseGroup::rank_main(int r) {

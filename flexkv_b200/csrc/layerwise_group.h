@@ -46,10 +46,6 @@ struct LayerwiseOptions {
   bool create_eventfds = true;
 };
 
-// Value written to a layer's eventfd when the restore failed (a reader that ignores the value is still
-// released; one that looks at it sees the failure and recomputes). A successful layer writes 1.
-constexpr uint64_t kLayerFailedSignal = 1ull << 32;
-
 struct LayerwiseResult {
   int status = 0;
   uint32_t epoch = 0;                // the value this restore published to its counter's flags
@@ -160,9 +156,10 @@ class LayerwiseGroup {
   void run_job(int r, const Job& j);
   void run_job_members(int r, const Job& j);
   cudaError_t stage_ids(Rank& rk, const Job& j, const int64_t*& gpu_ids, const int64_t*& cpu_ids);
-  void notify(int rank, int counter, int layer_lo, int layer_hi, bool failed = false);
-  // failure path of a job: publishes the epoch to the flags of layers [from_layer, L) from the host, fires
-  // their eventfds with kLayerFailedSignal and records the status for counter_status()
+  void notify(int rank, int counter, int layer_lo, int layer_hi);
+  // failure path of a job: records the status for counter_status(), then publishes the epoch to the flags of
+  // layers [from_layer, L) from the host and fires their eventfds (one unit each, as for a good layer: the
+  // eventfds are semaphores, so the failure is told by counter_status() and the restore's result, not by a value)
   void release_waiters(int r, const Job& j, int from_layer, int status);
   static bool status_words_set(const volatile int32_t* words);
   static void CUDART_CB host_fn(void* arg);

@@ -42,27 +42,99 @@ def kv_compress(reg: GpuRegistration, host: HostSide, size_table: torch.Tensor, 
     return keep
 
 
+CHUNK_VALS = 64
+HEADER_BYTES = 32
+RANKS, SHORT_RANKS, ESCAPE_ONES = 16, 3, 13
+SAMPLE_WORDS = 4
+
+
+def _code_of(rank: int, exponent: int):
+    if rank < SHORT_RANKS:
+        return rank, 2
+    if rank < RANKS:
+        n = rank - SHORT_RANKS
+        return 3 | (((1 << n) - 1) << 2), n + 3
+    return 3 | (((1 << ESCAPE_ONES) - 1) << 2) | (exponent << (2 + ESCAPE_ONES)), 2 + ESCAPE_ONES + 8
+
+
 def reference_compress_tile(x: torch.Tensor) -> torch.Tensor:
-    """Packed bytes (uint8, 1-D) of one tile of bf16 values (numel % 1024 == 0, <= 8192)."""
-    v = x.reshape(-1).view(torch.int16).to(torch.int32) & 0xFFFF
-    G = v.numel() // GROUP
-    v = v.reshape(G, GROUP)
+    """Packed bytes (uint8, 1-D) of one tile of bf16 values (numel % 1024 == 0, <= 8192), computed on the
+    CPU with plain Python integers from the format description alone."""
+    import numpy as np
+    v = x.reshape(-1).view(torch.int16).numpy().view(np.uint16).astype(np.int64)
+    n = v.size
+    C = n // CHUNK_VALS
     e = (v >> 7) & 0xFF
-    emax, emin = e.amax(1), e.amin(1)
-    rng = (emax - emin)
-    w = torch.where(rng == 0, torch.zeros_like(rng), torch.floor(torch.log2(rng.clamp(min=1).float())).int() + 1)
-    hdr = torch.stack([emax, w], 1).to(torch.uint8).reshape(-1)
-    smb = (((v >> 8) & 0x80) | (v & 0x7F)).to(torch.uint8)
-    d = emax[:, None] - e                                  # [G, 128]; element index = 4*lane + j
-    d = d.reshape(G, 32, 4)
-    lanes = torch.arange(32, dtype=torch.int64)
-    out = [hdr]
-    for g in range(G):
-        out.append(smb[g])
-        for b in range(int(w[g])):
-            for j in range(4):
-                bits = ((d[g, :, j] >> b) & 1).to(torch.int64)
-                word = int((bits << lanes).sum().item()) & 0xFFFFFFFF
-                out.append(torch.tensor([word & 0xFF, (word >> 8) & 0xFF, (word >> 16) & 0xFF, (word >> 24) & 0xFF],
-                                        dtype=torch.uint8))
-    return torch.cat(out)
+    # frequencies over the sample the format names: the first SAMPLE_WORDS words of every chunk
+    sample = [2 * (k * C + t) + h for t in range(C) for k in range(SAMPLE_WORDS) for h in range(2)]
+    hist = np.bincount(e[sample], minlength=256)
+    order = sorted((b for b in range(256) if hist[b] > 0), key=lambda b: (-int(hist[b]), b))
+    syms = order[:RANKS]
+    rank = {s: r for r, s in enumerate(syms)}
+    sizes, payload = [], bytearray()
+    for t in range(C):
+        acc, nb = 0, 0
+        for k in range(CHUNK_VALS // 2):
+            w = k * C + t
+            for h in range(2):
+                ex = int(e[2 * w + h])
+                code, ln = _code_of(rank.get(ex, RANKS), ex)
+                acc |= code << nb
+                nb += ln
+        nbytes = (nb + 7) // 8
+        sizes.append(nbytes)
+        payload += acc.to_bytes(nbytes, "little")
+    total = (HEADER_BYTES + C + n + len(payload) + 15) // 16 * 16
+    raw_total = 16 + 2 * n
+    if total >= raw_total:
+        hdr = bytearray(16)
+        hdr[4:8] = raw_total.to_bytes(4, "little")
+        hdr[8:12] = n.to_bytes(4, "little")
+        return torch.frombuffer(bytearray(bytes(hdr) + v.astype(np.uint16).tobytes()), dtype=torch.uint8).clone()
+    out = bytearray(total)
+    out[0], out[1] = 1, len(syms)
+    out[2:4] = C.to_bytes(2, "little")
+    out[4:8] = total.to_bytes(4, "little")
+    out[8:12] = n.to_bytes(4, "little")
+    out[16:16 + len(syms)] = bytes(syms)
+    out[32:32 + C] = bytes(sizes)
+    smb = (((v >> 8) & 0x80) | (v & 0x7F)).astype(np.uint8)
+    out[32 + C:32 + C + n] = smb.tobytes()
+    out[32 + C + n:32 + C + n + len(payload)] = payload
+    return torch.frombuffer(out, dtype=torch.uint8).clone()
+
+
+def reference_decompress_tile(packed: torch.Tensor) -> torch.Tensor:
+    """bf16 values (1-D) of one packed tile, decoded on the CPU from the format description alone."""
+    import numpy as np
+    b = bytes(packed.reshape(-1).numpy().tobytes())
+    mode, total, n = b[0], int.from_bytes(b[4:8], "little"), int.from_bytes(b[8:12], "little")
+    assert total == len(b)
+    if mode == 0:
+        return torch.frombuffer(bytearray(b[16:16 + 2 * n]), dtype=torch.bfloat16).clone()
+    C = int.from_bytes(b[2:4], "little")
+    syms, sizes = b[16:32], b[32:32 + C]
+    smb = np.frombuffer(b[32 + C:32 + C + n], dtype=np.uint8).astype(np.int64)
+    e = np.zeros(n, dtype=np.int64)
+    off = 32 + C + n
+    for t in range(C):
+        acc = int.from_bytes(b[off:off + sizes[t]], "little")
+        off += sizes[t]
+        for k in range(CHUNK_VALS // 2):
+            w = k * C + t
+            for h in range(2):
+                c = acc & 3
+                if c != 3:
+                    ex, ln = syms[c], 2
+                else:
+                    tt, ones = acc >> 2, 0
+                    while (tt >> ones) & 1 and ones < ESCAPE_ONES:
+                        ones += 1
+                    if ones >= ESCAPE_ONES:
+                        ex, ln = (tt >> ESCAPE_ONES) & 0xFF, 2 + ESCAPE_ONES + 8
+                    else:
+                        ex, ln = syms[SHORT_RANKS + ones], ones + 3
+                e[2 * w + h] = ex
+                acc >>= ln
+    v = ((smb & 0x80) << 8) | (e << 7) | (smb & 0x7F)
+    return torch.from_numpy(v.astype(np.uint16).view(np.int16).copy()).view(torch.bfloat16)

@@ -353,8 +353,11 @@ class QuantGpuHostWorker(TransferWorker):
         self.host = host
         self.layer_stride, self.kv_stride, self.tp_stride = host.layer_stride // n, host.kv_stride // n, \
             host.block_bytes // n
-        # measured on B200 (Llama-3-8B blocks): unpacking fills the link with 16 CTAs, packing needs ~48
-        self.num_ctas = int(os.environ.get("FLEXKV_QUANT_NUM_CTA", 32 if h2d else 48))
+        # Tile pipelines per launch (two share an SM in the lossless codec's kernel). Measured on B200 with
+        # Llama-3-8B blocks: 80 pipelines (40 SMs) put both directions on the link's plateau for SM-issued
+        # traffic; the fp8 kernel needs fewer (its CTAs are single pipelines)
+        dflt = 80 if storage.host.quant == "bf16_xp" else (32 if h2d else 48)
+        self.num_ctas = int(os.environ.get("FLEXKV_QUANT_NUM_CTA", dflt))
         self._torch = torch
         self.streams = {r.device_id: torch.cuda.Stream(device=r.device_id) for r in self.regs}
         self.status = {r.device_id: torch.zeros(8, dtype=torch.int32, device=f"cuda:{r.device_id}") for r in self.regs}
