@@ -88,8 +88,16 @@ void init_kernel_bindings(py::module_& m) {
   m.def("kv_fanout", [](py::dict params, int64_t mc_delta, uint64_t mc_flag_ptr, int num_ctas, int tile_bytes,
                         uint64_t stream) {
     KvFanoutParams fp;
+    // "mc_ptrs" (optional): multicast address of every tensor in gpu_ptrs
+    std::vector<uint64_t> mc;
+    if (params.contains("mc_ptrs")) mc = params["mc_ptrs"].cast<std::vector<uint64_t>>();
     fp.base = kv_params_from_dict(params);
     fp.base.h2d = 1;
+    if (!mc.empty()) {
+      if ((int)mc.size() != fp.base.num_gpu_ptrs) throw std::invalid_argument("mc_ptrs must match gpu_ptrs");
+      for (size_t i = 0; i < mc.size(); ++i) fp.base.c_ptrs[i] = mc[i];
+      fp.base.num_c_ptrs = (int32_t)mc.size();
+    }
     fp.mc_delta = mc_delta;
     fp.mc_flag = (uint32_t*)(uintptr_t)mc_flag_ptr;
     throw_on(launch_kv_fanout(fp, num_ctas, tile_bytes, (cudaStream_t)(uintptr_t)stream), "kv_fanout launch");

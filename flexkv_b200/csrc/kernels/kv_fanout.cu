@@ -88,7 +88,9 @@ kv_fanout_kernel(const __grid_constant__ KvFanoutParams fp, int tile_bytes, int 
                              kv * p.g_kv_stride + gblk * p.g_block_stride + p.g_off + off;
           const uint64_t c = p.cpu_base + layer * p.c_layer_stride + kv * p.c_kv_stride + cblk * p.c_block_stride +
                              p.c_off + off;
-          s_dst[st] = g + (uint64_t)fp.mc_delta;
+          // multicast twin of the local address: per-tensor table when given, else one delta for the whole cache
+          const int ti = layer * p.idx_layer_mul + kv * p.idx_kv_mul;
+          s_dst[st] = p.num_c_ptrs > 0 ? p.c_ptrs[ti] + (g - p.gpu_ptrs[ti]) : g + (uint64_t)fp.mc_delta;
           if (!ok) {
             // keep the barrier protocol uniform: publish an empty tile
             s_bytes[st] = 0;
@@ -161,7 +163,13 @@ kv_fanout_kernel(const __grid_constant__ KvFanoutParams fp, int tile_bytes, int 
 cudaError_t launch_kv_fanout(const KvFanoutParams& fp, int num_ctas, int tile_bytes, cudaStream_t stream) {
   const KvCopyParams& p = fp.base;
   if (p.num_pairs <= 0 || p.num_layers <= 0 || p.kv_dim <= 0 || p.chunk_bytes <= 0) return cudaSuccess;
+  if (p.c_use_table) return cudaErrorInvalidValue;           // the host side is a pool, c_ptrs carries multicast bases
   if (!kv_copy_tma_eligible(p) || (fp.mc_delta & 15)) return cudaErrorInvalidValue;
+  if (p.num_c_ptrs > 0) {
+    if (p.num_c_ptrs != p.num_gpu_ptrs) return cudaErrorInvalidValue;
+    for (int i = 0; i < p.num_c_ptrs; ++i)
+      if (p.c_ptrs[i] == 0 || (p.c_ptrs[i] & 15)) return cudaErrorInvalidValue;
+  }
   int tile = tile_bytes > 0 ? (tile_bytes / 16) * 16 : 16384;
   if (tile > 16384) tile = 16384;
   if (tile < 1024) tile = 1024;

@@ -18,6 +18,9 @@ namespace fkv {
 struct KvFanoutParams {
   KvCopyParams base;    // host -> local GPU addressing (h2d = 1); done_counter = device scratch word
   int64_t mc_delta;     // multicast address of a local address a: a + mc_delta
+                        // When base.num_c_ptrs > 0 the delta is not used: base.c_ptrs[i] is the multicast address
+                        // of tensor gpu_ptrs[i], so the tensors may come from several symmetric allocations
+                        // (one multicast object each), e.g. segments kept under a few GiB
   uint32_t* mc_flag;    // multicast address of a per-rank flag word, set to base.epoch after the data; may be null
 };
 

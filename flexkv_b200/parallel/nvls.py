@@ -76,23 +76,72 @@ def alloc_symmetric_kv(payload_bytes: int, device: torch.device, group=None) -> 
     return SymmetricKVBuffer(buf, hdl, payload_bytes)
 
 
-def fanout_restore(sym: SymmetricKVBuffer, reg: GpuRegistration, host: HostSide, gpu_blocks, cpu_blocks, epoch: int,
+class SymmetricKVPool:
+    """Several symmetric buffers used as one cache: every layer tensor lives entirely inside one segment and
+    is reached through that segment's multicast mapping. Segments keep each multicast object small (the
+    default is 2 GiB); the completion flags live in the tail of segment 0."""
+
+    def __init__(self, segments: List[SymmetricKVBuffer], layers_per_segment: int, per_layer_bytes: int) -> None:
+        self.segments = segments
+        self.layers_per_segment = layers_per_segment
+        self.per_layer_bytes = per_layer_bytes
+
+    def layer_tensor(self, layer: int, shape: Sequence[int], dtype: torch.dtype) -> torch.Tensor:
+        seg = self.segments[layer // self.layers_per_segment]
+        return seg.carve((layer % self.layers_per_segment) * self.per_layer_bytes, shape, dtype)
+
+    def mc_of(self, ptr: int) -> int:
+        """multicast address of a local address inside one of the segments"""
+        for seg in self.segments:
+            if seg.local_ptr <= ptr < seg.local_ptr + seg.payload_bytes:
+                return ptr + seg.mc_delta
+        raise ValueError("address outside the symmetric cache")
+
+    # the flag area of segment 0 serves the whole pool
+    @property
+    def flag_mc_ptr(self) -> int:
+        return self.segments[0].flag_mc_ptr
+
+    def flag_tensor(self) -> torch.Tensor:
+        return self.segments[0].flag_tensor()
+
+    @property
+    def mc_delta(self) -> int:
+        return self.segments[0].mc_delta
+
+
+def alloc_symmetric_kv_layers(num_layers: int, per_layer_bytes: int, device: torch.device, group=None,
+                              segment_bytes: int = 2 << 30) -> SymmetricKVPool:
+    """Collective: a symmetric cache of `num_layers` layers of `per_layer_bytes` each, in segments of at most
+    `segment_bytes` (a whole number of layers per segment)."""
+    per_layer_bytes = (per_layer_bytes + 255) // 256 * 256
+    lps = max(1, min(num_layers, segment_bytes // per_layer_bytes))
+    segs = []
+    for l0 in range(0, num_layers, lps):
+        segs.append(alloc_symmetric_kv(min(lps, num_layers - l0) * per_layer_bytes, device, group))
+    return SymmetricKVPool(segs, lps, per_layer_bytes)
+
+
+def fanout_restore(sym, reg: GpuRegistration, host: HostSide, gpu_blocks, cpu_blocks, epoch: int,
                    scratch: torch.Tensor, status: Optional[torch.Tensor] = None, layer_start: int = 0,
                    num_layers: int = -1, num_ctas: int = 8, tile_bytes: int = 16384,
                    stream: Optional[torch.cuda.Stream] = None) -> List[Any]:
     """Issuing rank only: host blocks -> every rank's cache, then flag := epoch on
-    every rank. `scratch` is a zeroed int32 device word reused across calls."""
+    every rank. `sym` is a SymmetricKVBuffer or a SymmetricKVPool; `scratch` is a zeroed int32
+    device word reused across calls."""
     keep: List[Any] = []
     p = make_params(reg, host, gpu_blocks, cpu_blocks, True, layer_start, num_layers,
                     status_ptr=status.data_ptr() if status is not None else 0, keep=keep)
     p["done_counter_ptr"] = scratch.data_ptr()
     p["epoch"] = int(epoch)
+    if isinstance(sym, SymmetricKVPool):
+        p["mc_ptrs"] = [sym.mc_of(int(a)) for a in reg.ptrs]
     s = stream if stream is not None else torch.cuda.current_stream()
     _native.C.kv_fanout(p, sym.mc_delta, sym.flag_mc_ptr, num_ctas, tile_bytes, s.cuda_stream)
     return keep
 
 
-def wait_flag(sym: SymmetricKVBuffer, epoch: int, timeout_s: float = 10.0) -> bool:
+def wait_flag(sym, epoch: int, timeout_s: float = 10.0) -> bool:
     """Receiving ranks: host-side bounded wait for the completion flag."""
     import time
     flag = sym.flag_tensor()

@@ -24,18 +24,21 @@ def main() -> int:
     try:
         from flexkv_b200.common.storage import KVCacheLayout, KVCacheLayoutType
         from flexkv_b200.ops.kv_copy import HostSide, decode_status, new_status
-        from flexkv_b200.parallel.nvls import alloc_symmetric_kv, fanout_restore, wait_flag
+        from flexkv_b200.parallel.nvls import alloc_symmetric_kv_layers, fanout_restore, wait_flag
         from flexkv_b200.storage.gpu_layout import register_tensors
 
         # MLA-shaped latent cache, identical on every rank: L layers of [N, T, 576] bf16
         L, N, T, D = 4, 64, 64, 576
         per_layer = N * T * D * 2
         try:
-            sym = alloc_symmetric_kv(L * per_layer, dev)
+            # two symmetric segments of two layers each: the kernel reaches every tensor through the
+            # multicast mapping of the segment that holds it
+            sym = alloc_symmetric_kv_layers(L, per_layer, dev, segment_bytes=2 * per_layer)
         except RuntimeError as e:
             result.update(ok=True, skipped=str(e))
             return 0
-        kv = [sym.carve(l * per_layer, (N, T, D), torch.bfloat16) for l in range(L)]
+        assert len(sym.segments) == 2
+        kv = [sym.layer_tensor(l, (N, T, D), torch.bfloat16) for l in range(L)]
         layout = KVCacheLayout(KVCacheLayoutType.LAYERFIRST, L, N, T, 1, D, is_mla=True)
         reg = register_tensors(kv, layout)
         chunk = reg.chunk_bytes
