@@ -460,10 +460,17 @@ def main() -> None:
         del kv
         torch.cuda.empty_cache()
         barrier()
+        # One process drives two GPUs here, as a TP group of an engine does. The other ranks wait on the HOST
+        # (a gloo barrier): an NCCL barrier would park a spinning kernel on GPU 1 while rank 0 runs there.
+        host_group = dist.new_group(backend="gloo")
         if rank == 0:
-            # one process drives two GPUs here, as a TP group of an engine does; the other ranks wait
             verified.update(selfcheck.multi_gpu_checks((0, 1)))
+        dist.barrier(group=host_group)
         barrier()
+        # restore + NVSwitch broadcast in one kernel (multimem.st), every rank checks every byte
+        verified[f"nvls_fanout_{world}_ranks"] = selfcheck.nvls_fanout_all_ranks(dev, rank, world)
+        if verified[f"nvls_fanout_{world}_ranks"] is False and rank == 0:
+            verified["nvls_fanout_error"] = selfcheck.last_failure
 
     if rank == 0:
         out = {

@@ -24,6 +24,13 @@ from ..models import KVShape, alloc_paged_cache, make_model_config
 from ..storage.gpu_layout import register_tensors
 
 SHARED_KV_MODES = ("sharded", "all_write", "rank0_only", "layer_parallel", "rank_rotate")
+last_failure = ""      # where the most recent check that returned False went wrong
+
+
+def _fail(why: str) -> bool:
+    global last_failure
+    last_failure = why
+    return False
 
 
 def slots_of(blocks, tokens_per_block: int) -> np.ndarray:
@@ -84,7 +91,10 @@ def tp_group_two_gpus(mode: str = "mha", devices=(0, 1)) -> bool:
     grp = C.TransferGroup([r.as_native() for r in regs], host, opts)
     g = np.array([3, 40, 11, 7, 25], dtype=np.int64)
     c = np.array([9, 0, 47, 2, 30], dtype=np.int64)
-    ok = grp.transfer(g, c, False, 0, 4).status == 0
+    st = grp.transfer(g, c, False, 0, 4).status
+    if st != 0:
+        return _fail(f"{mode}: offload status {st}")
+    ok = True
     gi = [torch.from_numpy(g).to(f"cuda:{d}") for d in devices]
     for i, cb in enumerate(c):
         blk = pool[int(cb)]
@@ -92,13 +102,18 @@ def tp_group_two_gpus(mode: str = "mha", devices=(0, 1)) -> bool:
             want = torch.stack([caches[r][l][gi[r][i]] if mla else caches[r][l][:, gi[r][i]] for l in range(4)])
             want = want.contiguous().view(torch.uint8).reshape(-1).cpu()
             per = block_bytes // slices
-            ok = ok and torch.equal(blk[r * per:(r + 1) * per], want)
+            if not torch.equal(blk[r * per:(r + 1) * per], want):
+                ne = (blk[r * per:(r + 1) * per] != want).nonzero()
+                return _fail(f"{mode}: host block {int(cb)} slice {r} differs after offload: {ne.numel()} bytes, "
+                             f"first at {int(ne[0])} of {per}")
     saved = [[t.clone() for t in kv] for kv in caches]
     for kv in caches:
         for t in kv:
             t.zero_()
     g2 = np.array([1, 2, 3, 4, 5], dtype=np.int64)
-    ok = ok and grp.transfer(g2, c, True, 0, 4).status == 0
+    st = grp.transfer(g2, c, True, 0, 4).status
+    if st != 0:
+        return _fail(f"{mode}: restore status {st}")
     for di, d in enumerate(devices):
         src_rank = 0 if mla else di
         sdev = saved[src_rank][0].device
@@ -107,7 +122,8 @@ def tp_group_two_gpus(mode: str = "mha", devices=(0, 1)) -> bool:
         for l in range(4):
             want = saved[src_rank][l][a] if mla else saved[src_rank][l][:, a]
             got = caches[di][l][b] if mla else caches[di][l][:, b]
-            ok = ok and torch.equal(got.cpu(), want.cpu())
+            if not torch.equal(got.cpu(), want.cpu()):
+                return _fail(f"{mode}: GPU {d} layer {l} differs after restore")
     del grp
     return bool(ok)
 
@@ -184,6 +200,71 @@ def layerwise_two_ranks(devices=(0, 1)) -> bool:
     return bool(ok)
 
 
+def nvls_fanout_all_ranks(device: torch.device, rank: int, world: int, group=None):
+    """Collective over the ranks of an initialised NCCL group (one process per GPU): rank 0 reads host
+    blocks once and `multimem.st` replicates them into every rank's symmetric MLA cache, laid out in two
+    symmetric segments; every rank compares every byte. Returns True / False, or the string
+    "skipped: ..." when the fabric offers no multicast. Every rank walks the same sequence of collectives
+    whatever it finds, and nothing here waits on a peer from inside a kernel."""
+    import torch.distributed as dist
+    from ..common.storage import KVCacheLayout, KVCacheLayoutType
+    from ..ops.kv_copy import HostSide, decode_status, new_status
+    from ..parallel.nvls import alloc_symmetric_kv_layers, fanout_restore, wait_flag
+    L, N, T, D, n = 4, 64, 64, 576, 24
+    per_layer = N * T * D * 2
+    have = torch.ones(1, device=device)
+    sym = None
+    try:
+        sym = alloc_symmetric_kv_layers(L, per_layer, device, group, segment_bytes=2 * per_layer)
+    except Exception as e:  # noqa: BLE001 - no multicast, or an older torch
+        have.zero_()
+        why = f"{type(e).__name__}: {e}"[:120]
+    dist.all_reduce(have, op=dist.ReduceOp.MIN, group=group)
+    if float(have.item()) < 1.0:
+        return "skipped: " + (why if sym is None else "another rank has no multicast mapping")
+    ok = True
+    try:
+        kv = [sym.layer_tensor(l, (N, T, D), torch.bfloat16) for l in range(L)]
+        reg = register_tensors(kv, KVCacheLayout(KVCacheLayoutType.LAYERFIRST, L, N, T, 1, D, is_mla=True))
+        chunk = reg.chunk_bytes
+        g = torch.Generator().manual_seed(5)            # the same host bytes on every rank, to compare against
+        pool = torch.randint(0, 256, (N, L, 1, chunk), dtype=torch.uint8, generator=g).pin_memory()
+        host = HostSide(pool.data_ptr(), chunk, chunk, L * chunk, N)
+        rng = np.random.default_rng(1)
+        gpu_blocks = rng.permutation(N)[:n].astype(np.int64)
+        cpu_blocks = rng.permutation(N)[:n].astype(np.int64)
+        status = new_status(device)
+        scratch = torch.zeros(1, dtype=torch.int32, device=device)
+        for epoch in (1, 2):
+            for t in kv:
+                t.zero_()
+            torch.cuda.synchronize(device)
+            dist.barrier(group=group)
+            if rank == 0:
+                keep = fanout_restore(sym, reg, host, gpu_blocks, cpu_blocks, epoch, scratch, status)
+                torch.cuda.synchronize(device)
+                ok = ok and decode_status(status) == 0
+                del keep
+            ok = wait_flag(sym, epoch, timeout_s=10.0) and ok
+            torch.cuda.synchronize(device)
+            gi = torch.from_numpy(gpu_blocks).to(device)
+            for l in range(L):
+                got = kv[l][gi].contiguous().view(torch.uint8).reshape(n, -1).cpu()
+                ok = ok and torch.equal(got, pool[torch.from_numpy(cpu_blocks), l, 0])
+            untouched = torch.from_numpy(np.setdiff1d(np.arange(N), gpu_blocks)).to(device)
+            ok = ok and int(kv[0][untouched].view(torch.int16).count_nonzero()) == 0
+            dist.barrier(group=group)
+    except Exception as e:  # noqa: BLE001
+        global last_failure
+        last_failure = f"nvls fan-out: {type(e).__name__}: {e}"[:200]
+        ok = False
+    flag = torch.tensor([1.0 if ok else 0.0], device=device)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group)
+    torch.cuda.synchronize(device)
+    dist.barrier(group=group)
+    return bool(flag.item() >= 1.0)
+
+
 def multi_gpu_checks(devices=(0, 1)) -> Dict[str, bool]:
     """Every two-GPU scenario above; an exception counts as a failed check and is named."""
     out: Dict[str, bool] = {}
@@ -194,6 +275,8 @@ def multi_gpu_checks(devices=(0, 1)) -> Dict[str, bool]:
     for name, fn in cases:
         try:
             out[name] = bool(fn())
+            if not out[name]:
+                out[name + "_error"] = last_failure
         except Exception as e:  # noqa: BLE001
             out[name] = False
             out[name + "_error"] = f"{type(e).__name__}: {e}"[:200]
