@@ -31,6 +31,8 @@ def main() -> None:
     ap.add_argument("--peer-share", type=float, default=0.30)
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--out", default="")
+    ap.add_argument("--concurrent", action="store_true",
+                    help="drive every rank from its own thread (all links busy at once) instead of one request at a time")
     a = ap.parse_args()
     N = a.gpus
     shape = get_shape("deepseek-v3")
@@ -66,38 +68,66 @@ def main() -> None:
                 del resident[pid]
         return ids
 
-    t0 = time.perf_counter()
-    peer_req = host_req = 0
-    for i in range(a.requests):
+    import threading
+    state_lock = threading.Lock()          # guards `resident` and the block rings
+    counts = {"peer": 0, "host": 0}
+
+    def serve(i: int) -> None:
+        """request i: restore whatever prefix is cached (a peer's HBM first, then host), offload the rest"""
         rank = i % N
-        n = int(rng.integers(4096, 32769)) // T * T
-        use_peer = N > 1 and rng.random() < a.peer_share and any(r != rank for r, _ in resident.values())
-        if use_peer:
-            pid = rng.choice([p for p, (r, _) in resident.items() if r != rank])
-        else:
-            pid = int(rng.integers(32))
+        r_i = np.random.default_rng([a.seed, i])
+        n = int(r_i.integers(4096, 32769)) // T * T
+        with state_lock:
+            others = [p for p, (r, _) in resident.items() if r != rank]
+            use_peer = N > 1 and r_i.random() < a.peer_share and bool(others)
+            pid = int(r_i.choice(others)) if use_peer else int(r_i.integers(32))
+            nblk = n // T
+            blocks = take_blocks(rank, nblk)
         pre = prefixes[pid][:n]
-        tok = np.concatenate([pre, rng.integers(0, 129280, size=n - len(pre), dtype=np.int64)])
-        nblk = n // T
-        blocks = take_blocks(rank, nblk)
+        tok = np.concatenate([pre, r_i.integers(0, 129280, size=n - len(pre), dtype=np.int64)])
         slot = np.repeat(blocks, T) * T + np.tile(np.arange(T), nblk)
         tid, mask = eng.get_match(tok, None, rank)
         hit = int(mask.sum())
         if hit:
             eng.launch_tasks([tid], [slot[:hit]])
-            r = eng.wait([tid], timeout=120)[tid]
+            r = eng.wait([tid], timeout=300)[tid]
             assert r.status.value == "success", r
-            peer_req += int(use_peer)
-            host_req += int(not use_peer)
+            with state_lock:
+                counts["peer" if use_peer else "host"] += 1
         tid, mask = eng.put_match(tok, None, rank)
         if int(mask.sum()):
             eng.launch_tasks([tid], [slot[mask]])
-            r = eng.wait([tid], timeout=120, completely=True)[tid]
+            r = eng.wait([tid], timeout=300, completely=True)[tid]
             assert r.status.value == "success", r
         # the request's prefix now lives in this rank's GPU blocks
         k = len(pre) // T
         mgr.publish_gpu_blocks(tok[:k * T], slot[:k * T], dp_client_id=rank)
-        resident[pid] = (rank, blocks[:k])
+        with state_lock:
+            resident[pid] = (rank, blocks[:k])
+
+    t0 = time.perf_counter()
+    if a.concurrent and N > 1:
+        # every rank is driven by its own thread, as N engine processes would: all PCIe links and the
+        # NVLink pulls are busy at the same time
+        errs = []
+
+        def rank_loop(rank: int) -> None:
+            try:
+                for i in range(rank, a.requests, N):
+                    serve(i)
+            except Exception as e:  # noqa: BLE001
+                errs.append(f"rank {rank}: {type(e).__name__}: {e}")
+        ths = [threading.Thread(target=rank_loop, args=(r,)) for r in range(N)]
+        for th in ths:
+            th.start()
+        for th in ths:
+            th.join()
+        if errs:
+            raise RuntimeError("; ".join(errs[:3]))
+    else:
+        for i in range(a.requests):
+            serve(i)
+    peer_req, host_req = counts["peer"], counts["host"]
     for d in range(N):
         torch.cuda.synchronize(d)
     wall = time.perf_counter() - t0
@@ -107,6 +137,7 @@ def main() -> None:
         rows[tt] = dict(ops=int(ops), blocks=int(blocks), gib=round(nbytes / 2**30, 2),
                         busy_ms=round(ms, 1), gbs_while_busy=round(nbytes / ms / 1e6, 2) if ms else None)
     out = dict(benchmark="mla_dp_prefix_reuse", gpus=N, codec=a.codec, requests=a.requests, wall_s=round(wall, 2),
+               ranks_driven="concurrently, one thread per rank" if a.concurrent and N > 1 else "one request at a time",
                requests_served_from_peer_gpu=peer_req, requests_served_from_host=host_req, per_type=rows,
                peer_directory=eng.cache_engine.peer_directory.stats if eng.cache_engine.peer_directory else None)
     print(json.dumps(out))

@@ -38,6 +38,14 @@ def main() -> None:
     ap.add_argument("--out", default="")
     a = ap.parse_args()
     rank = int(os.environ.get("LOCAL_RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    if world > 1:
+        # --sessions and the pool sizes name the whole box: every rank serves its share, all ranks at once
+        a.sessions = max(1, a.sessions // world)
+        a.host_gib, a.ssd_gib = a.host_gib / world, a.ssd_gib / world
+        if a.out:
+            root, ext = os.path.splitext(a.out)
+            a.out = f"{root}.rank{rank}{ext}"
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
     shape = get_shape("qwen3-32b-nvfp4")
@@ -112,7 +120,7 @@ def main() -> None:
     rows = {tt: dict(ops=int(v[0]), blocks=int(v[1]), gib=round(v[2] / 2**30, 2), busy_ms=round(v[3], 1),
                      gbs_while_busy=round(v[2] / v[3] / 1e6, 2) if v[3] else None) for tt, v in st.items()}
     gw = next((w for k, w in (mgr.transfer_manager.engine._workers or {}).items() if k[1].value == "DISK2D"), None)
-    out = dict(benchmark="multiturn_nvfp4_ssd", rank=rank, sessions=a.sessions, turns=a.turns, wall_s=round(wall, 2),
+    out = dict(benchmark="multiturn_nvfp4_ssd", rank=rank, ranks=world, sessions=a.sessions, turns=a.turns, wall_s=round(wall, 2),
                block_bytes=bb, hbm_blocks=NB, host_blocks=cfg.num_cpu_blocks, ssd_blocks=n_ssd,
                restored_tokens=restored_tok, recomputed_tokens=recomputed_tok,
                token_hit_rate=round(restored_tok / max(1, restored_tok + recomputed_tok), 4),

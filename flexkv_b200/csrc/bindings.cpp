@@ -8,6 +8,7 @@
 #include <cuda_runtime.h>
 
 #include "hasher.h"
+#include "graph_scheduler.h"
 #include "native_log.h"
 #include "host_mem.h"
 #include "kernels/kv_copy.h"
@@ -27,6 +28,42 @@ void init_dist_bindings(py::module_& m);       // bindings_dist.cpp
 PYBIND11_MODULE(_C, m) {
   m.doc() = "flexkv_b200 native core (sm_100a kernels + C++ control plane)";
   m.attr("MAX_GPU_PTRS") = kMaxGpuPtrs;
+
+  // ------------------------------------------------- transfer-graph scheduler
+  py::class_<GraphScheduler>(m, "GraphScheduler")
+      .def(py::init<>())
+      .def("submit", [](GraphScheduler& g, int64_t graph_id, std::vector<int64_t> op_ids, std::vector<int32_t> flags,
+                        std::vector<std::pair<int64_t, int64_t>> edges) {
+             return g.submit(graph_id, op_ids, flags, edges);
+           }, py::arg("graph_id"), py::arg("op_ids"), py::arg("flags"), py::arg("edges"))
+      .def("set_fanout", &GraphScheduler::set_fanout)
+      .def("op_done", [](GraphScheduler& g, int64_t graph_id, int64_t op_id, bool ok, double ms, int64_t bytes) {
+             SchedDone r = g.op_done(graph_id, op_id, ok, ms, bytes);
+             // (accepted, op finished, op success, ms, bytes, graph finished, graph failed, ready op ids)
+             return py::make_tuple(r.accepted, r.op_finished, r.op_success, r.ms, r.bytes, r.graph_finished,
+                                   r.graph_failed, r.ready);
+           }, py::arg("graph_id"), py::arg("op_id"), py::arg("success"), py::arg("ms") = 0.0, py::arg("bytes") = 0)
+      .def("requeue", &GraphScheduler::requeue)
+      .def("take_ready", &GraphScheduler::take_ready)
+      .def("wait", [](GraphScheduler& g, double timeout_s) {
+             std::vector<SchedCompletion> v;
+             {
+               py::gil_scoped_release rel;
+               v = g.wait(timeout_s);
+             }
+             py::list out;
+             for (const auto& c : v) out.append(py::make_tuple(c.graph_id, c.op_id, c.success, c.ms, c.bytes));
+             return out;
+           }, py::arg("timeout_s"))
+      .def("has_graph", &GraphScheduler::has_graph)
+      .def("graphs_in_flight", &GraphScheduler::graphs_in_flight)
+      .def("stats", [](GraphScheduler& g) {
+             auto s = g.stats();
+             py::dict d;
+             d["ops"] = s.ops; d["failed_ops"] = s.failed_ops; d["graphs"] = s.graphs; d["failed_graphs"] = s.failed_graphs;
+             return d;
+           });
+  m.attr("SCHED_OP_INSTANT") = (int)GraphScheduler::kInstant;
 
   // ------------------------------------------------- native logging / counters
   m.def("configure_cpp_metrics", [](bool enabled) { configure_metrics(enabled); }, py::arg("enabled"));

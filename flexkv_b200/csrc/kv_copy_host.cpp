@@ -4,13 +4,85 @@
 // stand-in for the engine's paged cache.
 #include <algorithm>
 #include <atomic>
+#include <condition_variable>
 #include <cstring>
+#include <functional>
+#include <mutex>
 #include <thread>
 #include <vector>
 
 #include "kernels/kv_copy.h"
 
 namespace fkv {
+
+namespace {
+
+// Persistent helpers for the CPU data plane: an op borrows up to `n - 1` of them and runs the
+// same work function on its own thread too, so a request never pays for thread creation
+// (the reference keeps a per-thread CopyPool for its CPU gather/scatter: csrc/ce_transfer.cu:523-641).
+class CopyPool {
+ public:
+  CopyPool() {
+    const unsigned hw = std::max(2u, std::thread::hardware_concurrency());
+    const int n = (int)std::min(16u, hw) - 1;
+    for (int i = 0; i < n; ++i) threads_.emplace_back([this] { loop(); });
+  }
+  ~CopyPool() {
+    { std::lock_guard<std::mutex> g(mu_); stop_ = true; }
+    cv_.notify_all();
+    for (auto& t : threads_) t.join();
+  }
+  int size() const { return (int)threads_.size() + 1; }
+  // runs `fn` on min(n, size()) threads in total and returns when all of them are done
+  void run(int n, const std::function<void()>& fn) {
+    const int helpers = std::max(0, std::min(n, size()) - 1);
+    if (helpers == 0) { fn(); return; }
+    std::unique_lock<std::mutex> op(op_mu_);     // one parallel op at a time; others wait their turn
+    {
+      std::lock_guard<std::mutex> g(mu_);
+      fn_ = &fn;
+      tickets_ = helpers;
+      running_ = helpers;
+    }
+    cv_.notify_all();
+    fn();
+    std::unique_lock<std::mutex> lk(mu_);
+    done_cv_.wait(lk, [&] { return running_ == 0; });
+    fn_ = nullptr;
+  }
+
+ private:
+  void loop() {
+    for (;;) {
+      const std::function<void()>* fn;
+      {
+        std::unique_lock<std::mutex> lk(mu_);
+        cv_.wait(lk, [&] { return stop_ || tickets_ > 0; });
+        if (stop_) return;
+        --tickets_;
+        fn = fn_;
+      }
+      (*fn)();
+      {
+        std::lock_guard<std::mutex> g(mu_);
+        if (--running_ == 0) done_cv_.notify_all();
+      }
+    }
+  }
+  std::vector<std::thread> threads_;
+  std::mutex mu_, op_mu_;
+  std::condition_variable cv_, done_cv_;
+  const std::function<void()>* fn_ = nullptr;
+  int tickets_ = 0, running_ = 0;
+  bool stop_ = false;
+};
+
+CopyPool& copy_pool() {
+  static CopyPool* pool = new CopyPool();   // lives until exit: no join at static destruction after fork/exit races
+  return *pool;
+}
+
+}  // namespace
 
 int host_kv_copy(const KvCopyParams& p, int num_threads) {
   if (p.num_pairs <= 0 || p.num_layers <= 0 || p.kv_dim <= 0 || p.chunk_bytes <= 0) return 0;
@@ -38,13 +110,10 @@ int host_kv_copy(const KvCopyParams& p, int num_threads) {
       }
     }
   };
-  num_threads = (int)std::max<int64_t>(1, std::min<int64_t>(num_threads, total / 64 + 1));
-  if (num_threads == 1) work();
-  else {
-    std::vector<std::thread> team;
-    for (int t = 0; t < num_threads; ++t) team.emplace_back(work);
-    for (auto& th : team) th.join();
-  }
+  // one helper per 512 KiB of payload, the caller's thread included; small ops run inline
+  const int64_t bytes = total * p.kv_dim * p.chunk_bytes;
+  const int want = (int)std::max<int64_t>(1, std::min<int64_t>(num_threads, bytes / (512 << 10)));
+  copy_pool().run(want, work);
   return err.load();
 }
 

@@ -224,7 +224,7 @@ class HostEmulatedGpuWorker(TransferWorker):
                           cpu_blocks_ptr=cpu.ctypes.data, num_pairs=int(cpu.size), layer_start=op.layer_start,
                           num_layers=nl, kv_dim=reg.kv_dim, chunk_bytes=reg.chunk_bytes,
                           gpu_num_blocks=reg.num_blocks, cpu_num_blocks=self.host.num_blocks, h2d=int(self.h2d))
-            status |= _native.C.host_kv_copy(params, 4)
+            status |= _native.C.host_kv_copy(params, 16)
             nbytes += int(cpu.size) * nl * reg.kv_dim * reg.chunk_bytes
         return OpOutcome(status == 0, num_bytes=nbytes, error="" if status == 0 else f"copy status 0x{status:x}")
 
@@ -313,7 +313,7 @@ class MultiGroupGpuHostWorker(TransferWorker):
                         _native.C.kv_copy(params, self.num_ctas, GLOBAL_CONFIG_FROM_ENV.transfer_tile_bytes, 0,
                                           st.cuda_stream)
                 else:
-                    status |= _native.C.host_kv_copy(params, 4)
+                    status |= _native.C.host_kv_copy(params, 16)
             if self.on_gpu:
                 e1.record(st)
                 evs.append((e0, e1, dev))
@@ -584,7 +584,7 @@ class SwaWorker(TransferWorker):
                               gpu_num_blocks=reg.num_blocks, cpu_num_blocks=pool.num_slots, h2d=int(h2d))
                 nbytes += int(slots.size) * reg.num_layers * reg.chunk_bytes
                 if not self.on_gpu:
-                    status |= _native.C.host_kv_copy(params, 2)
+                    status |= _native.C.host_kv_copy(params, 16)
                     continue
                 params["status_ptr"] = self._status[dev_id].data_ptr()
                 with self._torch.cuda.device(dev_id):

@@ -21,7 +21,9 @@ from .common.debug import flexkv_logger
 from .common.transfer import CompletedOp, TransferOpGraph
 from .storage.gpu_layout import GpuRegistration
 from .storage.storage_engine import StorageEngine
+from .common.config import GLOBAL_CONFIG_FROM_ENV
 from .transfer.engine import TransferEngine
+from .transfer.engine_spec import TransferEngineSpec
 
 
 class TransferManager:
@@ -134,7 +136,9 @@ class TransferManager:
                                        block_bytes=self.storage.host.block_bytes,
                                        num_blocks=self.storage.host.num_blocks, pid=os.getpid(),
                                        codec=self.storage.host.quant))
-            self.engine = TransferEngine(self.storage, self.model_config, self.cache_config)
+            # graph state in the native scheduler (default) or the Python specification of it
+            engine_cls = TransferEngine if GLOBAL_CONFIG_FROM_ENV.native_scheduler else TransferEngineSpec
+            self.engine = engine_cls(self.storage, self.model_config, self.cache_config)
             if self._metrics is not None:
                 self.engine.set_metrics_collector(self._metrics)
             self.engine.start()
