@@ -32,14 +32,21 @@ C = _native.C
 HOST_LAYOUT = "blockfirst"
 
 
-def build(shape, ngpu, gpu_blocks, host_blocks, engine_layout, notify, ctas, tile, tp_split, lpb=1):
+def build(shape, ngpu, gpu_blocks, host_blocks, engine_layout, notify, ctas, tile, tp_split, lpb=1, codec=False,
+          codec_pipelines=64):
+    """``codec``: the host pool holds the lossless bf16 codec's packed form (N(0,1) values packed by the offload
+    kernel before the timed restores); sizes and rates are still counted in raw KV bytes."""
     regs, caches = [], []
     for d in range(ngpu):
         kv, layout = alloc_paged_cache(shape, gpu_blocks, torch.device("cuda", d), engine_layout,
-                                       tp_size=ngpu if tp_split else 1, fill="zeros")
+                                       tp_size=ngpu if tp_split else 1, fill="normal" if codec else "zeros", seed=7 + d)
         regs.append(register_tensors(kv, layout))
         caches.append(kv)
-    chunk = regs[0].chunk_bytes
+    raw_chunk = regs[0].chunk_bytes
+    chunk = raw_chunk
+    if codec:
+        from flexkv_b200.ops.kv_compress import chunk_slot_bytes
+        chunk = chunk_slot_bytes(raw_chunk // 2)          # host slot of one chunk
     slices = ngpu if tp_split else 1
     block_bytes = slices * shape.num_layers * shape.kv_dim * chunk
     region = C.host_region_alloc(host_blocks * block_bytes, cuda_register=True, touch_threads=16,
@@ -50,12 +57,35 @@ def build(shape, ngpu, gpu_blocks, host_blocks, engine_layout, notify, ctas, til
         # [layer][kv][block][chunk]: one layer of consecutive blocks is one contiguous run of host memory
         host = dict(base=region.ptr, layer_stride=shape.kv_dim * host_blocks * chunk, kv_stride=host_blocks * chunk,
                     block_stride=chunk, num_blocks=host_blocks)
-    opts = dict(num_layers=shape.num_layers, kv_dim=shape.kv_dim, chunk_bytes=chunk,
+    opts = dict(num_layers=shape.num_layers, kv_dim=shape.kv_dim, chunk_bytes=raw_chunk,
                 cpu_tp_stride=block_bytes // slices if tp_split else 0, shared_kv=not tp_split,
                 max_blocks_per_op=max(gpu_blocks, 4096), notify_mode=notify, num_counters=3, layers_per_batch=lpb,
                 h2d=dict(num_ctas=ctas, tile_bytes=tile, engine=0))
+    if codec:
+        from flexkv_b200.ops.kv_compress import kv_compress, tiles_per_chunk
+        from flexkv_b200.ops.kv_copy import HostSide, decode_status, new_status
+        L, K, tpc = shape.num_layers, shape.kv_dim, tiles_per_chunk(raw_chunk // 2)
+        per_rank = L * K * tpc
+        table = torch.zeros(host_blocks * slices * per_rank, dtype=torch.int32).pin_memory()
+        ids = np.arange(min(gpu_blocks, host_blocks), dtype=np.int64)
+        for d, reg in enumerate(regs if tp_split else regs[:1]):
+            with torch.cuda.device(d):
+                st = new_status(torch.device("cuda", d))
+                hs = HostSide(region.ptr, host["layer_stride"], host["kv_stride"], block_bytes, host_blocks,
+                              offset=d * (block_bytes // slices) if tp_split else 0)
+                off = d * per_rank if tp_split else 0
+                keep = kv_compress(reg, hs, table[off:], ids, ids, h2d=False, layers_total=slices * L, num_ctas=64,
+                                   status=st)
+                torch.cuda.synchronize(d)
+                assert decode_status(st) == 0
+                del keep
+        used = table[table > 0].double()
+        opts.update(size_table_ptr=table.data_ptr(), size_table_layers=slices * L,
+                    size_table_rank_entries=per_rank if tp_split else 0, codec_pipelines=codec_pipelines)
+        build.packed_ratio = float(used.sum()) / (used.numel() * 2.0 * min(8192, raw_chunk // 2)) if used.numel() else 0
+        build.table = table
     grp = C.LayerwiseGroup([r.as_native() for r in regs], host, opts)
-    return grp, region, caches, chunk, block_bytes
+    return grp, region, caches, raw_chunk, block_bytes
 
 
 def scenario_notify(a):
@@ -98,7 +128,8 @@ def scenario_overlap(a):
     shape = KVShape("llama3-70b", 80, 8, 128, tokens_per_block=16)
     nblocks = a.requests * a.tokens // 16
     grp, region, caches, chunk, bb = build(shape, a.gpus, nblocks, nblocks, "sglang", a.notify, a.ctas or 8,
-                                           a.tile_bytes, tp_split=a.gpus > 1, lpb=a.layers_per_batch)
+                                           a.tile_bytes, tp_split=a.gpus > 1, lpb=a.layers_per_batch, codec=a.codec,
+                                           codec_pipelines=a.codec_pipelines)
     L = shape.num_layers
     rng = np.random.default_rng(0)
     cpu = rng.permutation(nblocks).astype(np.int64)
@@ -140,7 +171,8 @@ def scenario_overlap(a):
     restore_ms = statistics.median(x[0] for x in rows)
     model_ms = statistics.median(x[1] for x in rows)
     per_rank = nblocks * L * shape.kv_dim * chunk
-    row = dict(scenario="overlap", gpus=a.gpus, notify=a.notify, layers_per_batch=a.layers_per_batch, blocks=nblocks, bytes_per_rank=per_rank,
+    row = dict(scenario="overlap", gpus=a.gpus, notify=a.notify,
+               host_pool="bf16_xp packed, %.3f of raw" % build.packed_ratio if a.codec else "raw", layers_per_batch=a.layers_per_batch, blocks=nblocks, bytes_per_rank=per_rank,
                restore_ms=round(restore_ms, 2), restore_gbs_per_gpu=round(per_rank / restore_ms / 1e6, 2),
                restore_gbs_box=round(a.gpus * per_rank / restore_ms / 1e6, 2),
                compute_only_ms=round(L * a.layer_us / 1e3, 2), overlapped_total_ms=round(model_ms, 2),
@@ -164,6 +196,8 @@ def main():
     ap.add_argument("--stub-ctas", type=int, default=148)
     ap.add_argument("--layers-per-batch", type=int, default=0, help="0 = one fused launch with per-layer flags")
     ap.add_argument("--out", default="")
+    ap.add_argument("--codec", action="store_true", help="overlap: host pool in the lossless codec's packed form")
+    ap.add_argument("--codec-pipelines", type=int, default=64)
     ap.add_argument("--host-layout", default="blockfirst", choices=["blockfirst", "layerfirst"],
                     help="host pool layout (FLEXKV_CPU_LAYOUT of a deployment)")
     ap.add_argument("--scales", nargs="*", default=[], help="notify: subset of small medium large")

@@ -308,6 +308,31 @@ PYBIND11_MODULE(_C, m) {
              }
              return py::make_tuple(nfail, ok);
            })
+      .def("transfer_packed", [](SsdIoEngine& e, uint64_t cpu_base, I64Array cpu_blocks, I64Array ssd_blocks,
+                                 bool is_read, py::dict geo,
+                                 py::array_t<int32_t, py::array::c_style | py::array::forcecast> sizes) {
+             if (cpu_blocks.size() != ssd_blocks.size()) throw std::invalid_argument("block id arrays differ in size");
+             SsdIoEngine::PackedGeometry g;
+             g.cpu_block_stride = geo["cpu_block_stride"].cast<int64_t>();
+             g.chunk_slot_bytes = geo["chunk_slot_bytes"].cast<int64_t>();
+             g.tile_slot_bytes = geo["tile_slot_bytes"].cast<int64_t>();
+             g.last_tile_slot_bytes = geo["last_tile_slot_bytes"].cast<int64_t>();
+             g.tiles_per_chunk = geo["tiles_per_chunk"].cast<int32_t>();
+             g.entries = geo["entries"].cast<int32_t>();
+             const int64_t n = (int64_t)cpu_blocks.size();
+             if ((int64_t)sizes.size() != n * g.entries) throw std::invalid_argument("one row of sizes per block");
+             py::array_t<uint8_t> ok((py::ssize_t)n);
+             int64_t nfail;
+             {
+               const int64_t* cb = cpu_blocks.data();
+               const int64_t* sb = ssd_blocks.data();
+               const int32_t* sz = sizes.data();
+               uint8_t* okp = ok.mutable_data();
+               py::gil_scoped_release rel;
+               nfail = e.transfer_packed((uint8_t*)(uintptr_t)cpu_base, cb, sb, n, is_read, g, sz, okp);
+             }
+             return py::make_tuple(nfail, ok);
+           })
       .def("set_fault", [](SsdIoEngine& e, int mode, int64_t nth) { SsdFault f; f.mode = mode; f.nth = nth; e.set_fault(f); })
       .def("sync_files", &SsdIoEngine::sync_files)
       .def_property_readonly("using_iouring", &SsdIoEngine::using_iouring)

@@ -28,6 +28,12 @@ void init_layerwise_bindings(py::module_& m) {
     if (o.contains("layers_per_batch")) lo.layers_per_batch = o["layers_per_batch"].cast<int>();
     if (o.contains("fused_max_bytes")) lo.fused_max_bytes = o["fused_max_bytes"].cast<int64_t>();
     if (o.contains("create_eventfds")) lo.create_eventfds = o["create_eventfds"].cast<bool>();
+    if (o.contains("size_table_ptr")) {
+      lo.size_table = (uint32_t*)(uintptr_t)o["size_table_ptr"].cast<uint64_t>();
+      lo.size_table_layers = o["size_table_layers"].cast<int>();
+      lo.size_table_rank_entries = o.contains("size_table_rank_entries") ? o["size_table_rank_entries"].cast<int64_t>() : 0;
+      if (o.contains("codec_pipelines")) lo.codec_pipelines = o["codec_pipelines"].cast<int>();
+    }
     return lo;
   };
 

@@ -26,7 +26,8 @@
 // Code of an exponent, bits written LSB first: rank 0..2 -> that rank in 2 bits; rank r = 3..15 -> "11",
 // r-3 one bits, a zero bit; any other exponent -> "11", 13 one bits, the 8 exponent bits (23 bits).
 // Raw tile: the 16-byte header with mode 0, then the values.
-// Host chunk slot = tiles_per_chunk * kCompressTileSlot bytes; chunk elements % 1024 == 0.
+// Host chunk slot: kCompressTileSlot bytes per full tile, 2 * elems + 128 for a shorter last tile; tile s of a
+// chunk starts s * kCompressTileSlot bytes into the chunk's slot; chunk elements % 1024 == 0.
 #pragma once
 #include <cstdint>
 #include <cuda_runtime.h>
@@ -48,7 +49,9 @@ inline int64_t compress_tiles_per_chunk(int64_t chunk_elems) {
   return (chunk_elems + kCompressTileElems - 1) / kCompressTileElems;
 }
 inline int64_t compress_chunk_slot_bytes(int64_t chunk_elems) {
-  return compress_tiles_per_chunk(chunk_elems) * kCompressTileSlot;
+  // full tiles take a full slot; the last, shorter tile takes what its own raw form needs (plus the same slack)
+  const int64_t full = chunk_elems / kCompressTileElems, rest = chunk_elems % kCompressTileElems;
+  return full * kCompressTileSlot + (rest ? 2 * rest + 128 : 0);
 }
 
 // p.chunk_bytes = raw bf16 chunk bytes (GPU side); host strides are slot strides.

@@ -1,5 +1,7 @@
 #include "layerwise_group.h"
 
+#include "kernels/kv_compress.h"
+
 #include <cuda.h>
 
 #include <sys/eventfd.h>
@@ -462,7 +464,11 @@ void LayerwiseGroup::run_job(int r, const Job& j) {
     p.epoch = j.epoch;
     p.layer_major = fused ? 1 : 0;
     if (j.n > 0) {
-      err = launch_kv_copy(p, opt_.group.h2d, rk.stream);
+      if (opt_.size_table != nullptr)
+        err = launch_kv_compress_bf16(p, opt_.size_table + (int64_t)r * opt_.size_table_rank_entries,
+                                      opt_.size_table_layers, opt_.codec_pipelines, rk.stream);
+      else
+        err = launch_kv_copy(p, opt_.group.h2d, rk.stream);
     } else {
       // nothing to restore: publish the flags from the host so waiters are released at once
       for (int l = l0; l < l1; ++l) hflags[l] = j.epoch;

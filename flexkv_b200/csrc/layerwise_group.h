@@ -44,6 +44,14 @@ struct LayerwiseOptions {
                               // -1 = decide per restore: fused up to fused_max_bytes, else one launch per layer
   int64_t fused_max_bytes = 64ll << 20;
   bool create_eventfds = true;
+  // Host pool kept in the lossless bf16 codec's packed form (uniform caches only): the restore then runs the
+  // unpacking kernel, layer by layer with the same per-layer flags, and reads only the packed bytes from the host.
+  // size_table: mapped uint32 table of the pool; rank r starts size_table_rank_entries * r entries in and is told
+  // the table holds size_table_layers layers per block (see transfer/compression/size_table.py).
+  uint32_t* size_table = nullptr;
+  int size_table_layers = 0;
+  int64_t size_table_rank_entries = 0;
+  int codec_pipelines = 64;   // 128-thread tile pipelines of the unpacking kernel (two per SM)
 };
 
 struct LayerwiseResult {

@@ -167,6 +167,7 @@ SsdIoEngine::SsdIoEngine(const std::vector<std::vector<std::string>>& files, int
 SsdIoEngine::~SsdIoEngine() {
   for (int fd : fds_buffered_) if (fd >= 0) close(fd);
   for (int fd : fds_direct_) if (fd >= 0) close(fd);
+  if (staging_) free(staging_);
 }
 
 void SsdIoEngine::sync_files() {
@@ -331,6 +332,106 @@ int64_t SsdIoEngine::transfer(uint8_t* cpu_base, const int64_t* cpu_blocks, cons
   }
   for (auto& r : merged) if (!failed[(size_t)r.block_slot]) bytes += r.len;
   (is_read ? bytes_read_ : bytes_written_) += (uint64_t)bytes;
+  return nfail;
+}
+
+// ---------------------------------------------------------------- packed blocks
+
+static constexpr int64_t kPackedBatch = 32;   // blocks gathered per round of IO
+
+int64_t SsdIoEngine::transfer_packed(uint8_t* cpu_base, const int64_t* cpu_blocks, const int64_t* ssd_blocks, int64_t n,
+                                     bool is_read, const PackedGeometry& geo, const int32_t* sizes, uint8_t* ok) {
+  if (n <= 0) return 0;
+  if (geo.entries <= 0 || geo.tiles_per_chunk <= 0 || geo.entries % geo.tiles_per_chunk != 0)
+    throw std::invalid_argument("SsdIoEngine::transfer_packed: bad geometry");
+  std::lock_guard<std::mutex> sg(staging_mu_);
+  if (staging_ == nullptr) {
+    void* p = nullptr;
+    if (posix_memalign(&p, (size_t)kDirectAlign, (size_t)(kPackedBatch * block_bytes_ + kDirectAlign)) != 0)
+      throw std::runtime_error("SsdIoEngine: no memory for the packed staging area");
+    staging_ = static_cast<uint8_t*>(p);
+  }
+  const int64_t cap = capacity_blocks();
+  std::vector<uint8_t> failed((size_t)n, 0);
+  std::vector<int64_t> total((size_t)n, 0);
+  // validate the rows and size every block's run
+  for (int64_t i = 0; i < n; ++i) {
+    if (ssd_blocks[i] < 0 || ssd_blocks[i] >= cap || cpu_blocks[i] < 0) { failed[(size_t)i] = 1; continue; }
+    const int32_t* row = sizes + i * geo.entries;
+    int64_t sum = 0;
+    for (int32_t e = 0; e < geo.entries; ++e) {
+      const bool last = (e % geo.tiles_per_chunk) == geo.tiles_per_chunk - 1;
+      const int64_t slot = last ? geo.last_tile_slot_bytes : geo.tile_slot_bytes;
+      if (row[e] <= 0 || (row[e] & 15) || row[e] > slot) { failed[(size_t)i] = 1; break; }
+      sum += row[e];
+    }
+    if (!failed[(size_t)i] && sum > block_bytes_) failed[(size_t)i] = 1;
+    total[(size_t)i] = sum;
+  }
+  auto tile_ptr = [&](int64_t cpu_block, int32_t e) {
+    return cpu_base + cpu_block * geo.cpu_block_stride + (int64_t)(e / geo.tiles_per_chunk) * geo.chunk_slot_bytes +
+           (int64_t)(e % geo.tiles_per_chunk) * geo.tile_slot_bytes;
+  };
+  int64_t moved = 0;
+  for (int64_t lo = 0; lo < n; lo += kPackedBatch) {
+    const int64_t hi = std::min(n, lo + kPackedBatch);
+    std::vector<IoReq> reqs;
+    for (int64_t i = lo; i < hi; ++i) {
+      if (failed[(size_t)i]) continue;
+      uint8_t* st = staging_ + (i - lo) * block_bytes_;
+      const int64_t len = std::min(block_bytes_, (total[(size_t)i] + kDirectAlign - 1) / kDirectAlign * kDirectAlign);
+      if (!is_read) {
+        const int32_t* row = sizes + i * geo.entries;
+        int64_t off = 0;
+        for (int32_t e = 0; e < geo.entries; ++e) {
+          std::memcpy(st + off, tile_ptr(cpu_blocks[i], e), (size_t)row[e]);
+          off += row[e];
+        }
+        std::memset(st + off, 0, (size_t)(len - off));
+      }
+      int fdi; int64_t base;
+      locate(ssd_blocks[i], fdi, base);
+      IoReq r;
+      r.fd_index = fdi;
+      r.file_off = base;
+      r.mem = st;
+      r.len = len;
+      r.block_slot = (int32_t)i;
+      reqs.push_back(r);
+    }
+    if (reqs.empty()) continue;
+    bool direct = direct_ok_;
+    for (auto& r : reqs)
+      if ((r.file_off % kDirectAlign) || (r.len % kDirectAlign) || ((uintptr_t)r.mem % kDirectAlign)) { direct = false; break; }
+    std::sort(reqs.begin(), reqs.end(), [](const IoReq& a, const IoReq& b) {
+      return a.fd_index != b.fd_index ? a.fd_index < b.fd_index : a.file_off < b.file_off;
+    });
+    {
+      std::lock_guard<std::mutex> g(mu_);
+      if (ring_) run_iouring(reqs, is_read, direct, failed);
+      else run_threads(reqs, is_read, direct, failed);
+    }
+    for (auto& r : reqs) {
+      const int64_t i = r.block_slot;
+      if (failed[(size_t)i]) continue;
+      moved += r.len;
+      if (is_read) {
+        const int32_t* row = sizes + i * geo.entries;
+        const uint8_t* st = r.mem;
+        int64_t off = 0;
+        for (int32_t e = 0; e < geo.entries; ++e) {
+          std::memcpy(tile_ptr(cpu_blocks[i], e), st + off, (size_t)row[e]);
+          off += row[e];
+        }
+      }
+    }
+  }
+  int64_t nfail = 0;
+  for (int64_t i = 0; i < n; ++i) {
+    if (ok) ok[i] = failed[(size_t)i] ? 0 : 1;
+    nfail += failed[(size_t)i];
+  }
+  (is_read ? bytes_read_ : bytes_written_) += (uint64_t)moved;
   return nfail;
 }
 

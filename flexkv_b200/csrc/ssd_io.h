@@ -54,6 +54,25 @@ class SsdIoEngine {
   int64_t transfer(uint8_t* cpu_base, const int64_t* cpu_blocks, const int64_t* ssd_blocks, int64_t n, bool is_read,
                    const SsdLayout& lay, int layer_start, int num_layers, uint8_t* ok);
 
+  // Packed form for host pools kept in the lossless codec's format: a host block is a grid of fixed tile
+  // slots of which only the first sizes[i] bytes are in use. A write gathers the used bytes of a block's tiles
+  // back to back (row order of the size table) and writes that run, rounded up to 4 KiB, at the start of the
+  // block's SSD slot; a read fetches the run and scatters the tiles back into their slots. The SSD slot keeps
+  // its size (block ids map to the same offsets), what shrinks are the bytes that cross the SSD interface.
+  // `sizes` holds n rows of `geo.entries` int32 (host table rows for a write, SSD table rows for a read); a row
+  // with an entry that is 0, not a multiple of 16 or larger than its tile's slot fails that block.
+  // (reference: csrc/compression/common/packed_ssd.cpp:64-250, one 512-aligned IO per block.)
+  struct PackedGeometry {
+    int64_t cpu_block_stride;   // bytes between host blocks
+    int64_t chunk_slot_bytes;   // host slot of one chunk
+    int64_t tile_slot_bytes;    // slot of a full tile; tile t of a chunk starts t * tile_slot_bytes into the chunk slot
+    int32_t tiles_per_chunk;
+    int32_t entries;            // tiles per block = chunks per block * tiles_per_chunk
+    int64_t last_tile_slot_bytes;   // slot of the last tile of a chunk (shorter when the chunk is not a whole number of tiles)
+  };
+  int64_t transfer_packed(uint8_t* cpu_base, const int64_t* cpu_blocks, const int64_t* ssd_blocks, int64_t n,
+                          bool is_read, const PackedGeometry& geo, const int32_t* sizes, uint8_t* ok);
+
   bool using_iouring() const { return ring_ != nullptr; }
   bool direct_available() const { return direct_ok_; }
   int num_devices() const { return (int)num_devices_; }
@@ -80,6 +99,8 @@ class SsdIoEngine {
   SsdFault fault_;
   std::atomic<int64_t> fault_counter_{0};
   std::atomic<uint64_t> bytes_read_{0}, bytes_written_{0};
+  uint8_t* staging_ = nullptr;      // packed IO: page-aligned gather/scatter area, kPackedBatch blocks
+  std::mutex staging_mu_;
 };
 
 }  // namespace fkv

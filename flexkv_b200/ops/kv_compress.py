@@ -20,7 +20,9 @@ def tiles_per_chunk(chunk_elems: int) -> int:
 
 
 def chunk_slot_bytes(chunk_elems: int) -> int:
-    return tiles_per_chunk(chunk_elems) * TILE_SLOT
+    # full tiles take a full slot; the last, shorter tile takes what its own raw form would need
+    full, rest = divmod(chunk_elems, TILE_ELEMS)
+    return full * TILE_SLOT + ((2 * rest + 128) if rest else 0)
 
 
 def size_table_entries(num_blocks: int, num_layers: int, kv_dim: int, chunk_elems: int) -> int:

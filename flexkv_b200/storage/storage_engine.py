@@ -37,7 +37,8 @@ def packed_chunk_bytes(chunk_elems: int, quant: str, itemsize: int) -> int:
     if quant == "bf16_xp":
         if chunk_elems % 1024:
             raise ValueError("the exponent-packing codec needs chunk elements divisible by 1024")
-        return (chunk_elems + COMPRESS_TILE_ELEMS - 1) // COMPRESS_TILE_ELEMS * COMPRESS_TILE_SLOT
+        full, rest = divmod(chunk_elems, COMPRESS_TILE_ELEMS)
+        return full * COMPRESS_TILE_SLOT + ((2 * rest + 128) if rest else 0)
     if quant == "fp8_e4m3":
         if chunk_elems % QUANT_GROUP:
             raise ValueError("fp8 offload needs chunk elements divisible by 128")
@@ -278,6 +279,22 @@ class StorageEngine:
         flexkv_logger.info("ssd pool: %d blocks x %d B over %d dir(s), %d file(s)/dir, io_uring=%s direct=%s",
                            c.num_ssd_blocks, block_bytes, ndev, files_per_dev, engine.using_iouring,
                            engine.direct_available)
+
+    def packed_ssd_geometry(self) -> Optional[Dict[str, int]]:
+        """Tile-slot geometry of a host block for packed SSD IO, or None when the pool is not in the lossless
+        codec's format (or ``FLEXKV_SSD_PACKED=0``): the SSD then moves whole slots."""
+        if self.ssd is None or self.ssd_size_table is None or self.host.size_table is None:
+            return None
+        if os.environ.get("FLEXKV_SSD_PACKED", "1") == "0":
+            return None
+        tpc = int(self.host.tiles_per_chunk)
+        entries = int(self.ssd_size_table.shape[1])
+        # a rank's chunk slot: the block is [rank slice][layer][kv][slot], the table row walks it in that order
+        chunk_slot = int(self.host.chunk_bytes) // max(1, int(getattr(self.host.layout, "tp_slices", 1)))
+        last = chunk_slot - (tpc - 1) * COMPRESS_TILE_SLOT
+        return dict(cpu_block_stride=int(self.host.block_bytes), chunk_slot_bytes=chunk_slot,
+                    tile_slot_bytes=COMPRESS_TILE_SLOT, last_tile_slot_bytes=int(last), tiles_per_chunk=tpc,
+                    entries=entries)
 
     def sync_ssd_files(self) -> None:
         """fsync of every SSD block file and of the directories that hold them (a persisted index must not

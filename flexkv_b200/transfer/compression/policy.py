@@ -56,8 +56,6 @@ def choose_codec(*, requested_quant: str, compression_enabled: bool, dtype, host
         why = f"chunks of {chunk_bytes} B are below {MIN_CHUNK_BYTES} B"
     elif chunk_elems_per_rank % XP_ELEM_MULTIPLE:
         why = f"chunk elements per rank are not a multiple of {XP_ELEM_MULTIPLE}"
-    elif layerwise:
-        why = "layerwise restore is enabled"
     elif peer_host_sharing:
         why = "host blocks are shared with other nodes (the size table is not)"
     if why:

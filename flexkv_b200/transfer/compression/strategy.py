@@ -79,7 +79,8 @@ class ExponentPackStrategy(CompressionStrategy):
     def host_chunk_bytes(self, chunk_elems: int, itemsize: int) -> int:
         if chunk_elems % 1024:
             raise ValueError("the exponent-packing codec needs chunk elements divisible by 1024")
-        return (chunk_elems + self.TILE_ELEMS - 1) // self.TILE_ELEMS * self.TILE_SLOT
+        full, rest = divmod(chunk_elems, self.TILE_ELEMS)
+        return full * self.TILE_SLOT + ((2 * rest + 128) if rest else 0)
 
     def run(self, params, rank_index, num_ctas, stream) -> None:
         if self.size_table is None or self.spec is None:

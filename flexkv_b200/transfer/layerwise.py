@@ -149,6 +149,15 @@ def build_layerwise_group(storage, model_config, key: WorkerKey, notify_mode: Op
                 max_blocks_per_op=max(4096, min(1 << 18, host.num_blocks)),
                 notify_mode=notify_mode or env.layerwise_notify_mode, num_counters=num_counters,
                 layers_per_batch=layers_per_batch, create_eventfds=create_eventfds)
+    if getattr(host, "quant", "none") == "bf16_xp":
+        # packed host pool: the restore unpacks layer by layer and reads only the packed bytes
+        from .compression import build_compressors
+        spec = build_compressors(host, reg0.num_layers, reg0.kv_dim, len(ranks), shared).spec
+        opts.update(size_table_ptr=host.size_table.data_ptr(), size_table_layers=spec.kernel_layers(),
+                    size_table_rank_entries=spec.rank_offset_entries(1) if len(ranks) > 1 else 0,
+                    codec_pipelines=int(os.environ.get("FLEXKV_QUANT_NUM_CTA", 64)))
+    elif getattr(host, "quant", "none") != "none":
+        raise ValueError(f"layerwise restore does not serve host pools in the {host.quant} format")
     return _native.C.LayerwiseGroup([regs[r].as_native() for r in ranks], host_d, opts)
 
 

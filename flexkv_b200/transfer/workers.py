@@ -481,6 +481,21 @@ class SsdWorker(TransferWorker):
             cpu, ssd = op.src_block_ids, op.dst_block_ids
         lay = st.ssd_layout_dict()
         nl = lay["num_layers"] if op.num_layers < 0 else op.num_layers
+        geo = st.packed_ssd_geometry() if (op.layer_start == 0 and nl == lay["num_layers"]) else None
+        if geo is not None:
+            # packed pool: only the used bytes of every tile cross the SSD interface, one run per block
+            cpu = np.ascontiguousarray(cpu, dtype=np.int64)
+            ssd = np.ascontiguousarray(ssd, dtype=np.int64)
+            if self.is_read:
+                rows = st.ssd_size_table[ssd]
+            else:
+                rows = st.host.size_table.view(st.host.num_blocks, -1).numpy()[cpu]
+            before = st.ssd.engine.bytes_read if self.is_read else st.ssd.engine.bytes_written
+            nfail, ok = st.ssd.engine.transfer_packed(st.host.base, cpu, ssd, self.is_read, geo, rows)
+            self._move_size_tables(cpu, ssd, ok)
+            after = st.ssd.engine.bytes_read if self.is_read else st.ssd.engine.bytes_written
+            return OpOutcome(nfail == 0, block_results=tuple(bool(x) for x in ok), num_bytes=int(after - before),
+                             error="" if nfail == 0 else f"{nfail} block(s) failed")
         nfail, ok = st.ssd.engine.transfer(st.host.base, cpu, ssd, self.is_read, lay, op.layer_start, nl)
         self._move_size_tables(cpu, ssd, ok)
         return OpOutcome(nfail == 0, block_results=tuple(bool(x) for x in ok),

@@ -23,11 +23,13 @@ def test_lossless_codec_is_all_or_nothing():
     assert _dec().codec == "bf16_xp"
     assert _dec(compression_enabled=False).codec == "none" and not _dec(compression_enabled=False).reason
     for kw, word in [(dict(dtype=torch.float16), "bf16"), (dict(host_layout_type=KVCacheLayoutType.LAYERFIRST), "BLOCKFIRST"),
-                     (dict(chunk_elems_per_rank=1024), "below"), (dict(chunk_elems_per_rank=16384 + 512), "multiple"),
-                     (dict(layerwise=True), "layerwise")]:
+                     (dict(chunk_elems_per_rank=1024), "below"), (dict(chunk_elems_per_rank=16384 + 512), "multiple")]:
         d = _dec(**kw)
         assert d.codec == "none" and word in d.reason, (kw, d)
     assert "small" in _dec(chunk_elems_per_rank=4096).warning
+    # the layer-by-layer restore has a form of the unpacking kernel; the lossy fp8 format has not
+    assert _dec(layerwise=True).codec == "bf16_xp"
+    assert "layerwise" in _dec(requested_quant="fp8_e4m3", compression_enabled=False, layerwise=True).reason
 
 
 def test_fp8_is_explicit_and_checked():

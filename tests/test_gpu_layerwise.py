@@ -218,3 +218,45 @@ def test_failed_disk_stage_releases_every_waiter_with_the_failure_signal(tmp_pat
     r = grp.restore(ids, ids, 1, ssd, lay, ids, ids)          # the next restore on the counter is clean again
     assert r.status == 0 and grp.counter_status(1) == 0
     assert [_drain(grp.eventfd_of(1, 0, l)) for l in range(shape.num_layers)] == [1] * shape.num_layers
+
+
+@pytest.mark.parametrize("lpb", [0, 2])
+def test_layerwise_restore_from_a_packed_host_pool(lpb):
+    """Host pool in the lossless codec's packed form: the restore unpacks layer by layer (one fused launch
+    with per-layer flags, or one launch per layer batch), signals every layer once and is bit-exact."""
+    from flexkv_b200.ops.kv_compress import chunk_slot_bytes, kv_compress, size_table_entries
+    from flexkv_b200.ops.kv_copy import HostSide, decode_status, new_status
+    dev = torch.device("cuda:0")
+    shape = KVShape("lwc", 4, 8, 128, tokens_per_block=16)           # 16384-element chunks, two tiles each
+    NB, n = 64, 24
+    kv, layout = alloc_paged_cache(shape, NB, dev, "vllm", fill="normal", seed=33)
+    reg = register_tensors(kv, layout)
+    E = reg.chunk_bytes // 2
+    L, K = shape.num_layers, shape.kv_dim
+    slot = chunk_slot_bytes(E)
+    pool = torch.zeros(NB, L, K, slot, dtype=torch.uint8).pin_memory()
+    table = torch.zeros(size_table_entries(NB, L, K, E), dtype=torch.int32).pin_memory()
+    host = HostSide(pool.data_ptr(), K * slot, slot, L * K * slot, NB)
+    rng = np.random.default_rng(4)
+    src = rng.permutation(NB)[:n].astype(np.int64)
+    cpu = rng.permutation(NB)[:n].astype(np.int64)
+    status = new_status(dev)
+    keep = kv_compress(reg, host, table, src, cpu, h2d=False, num_ctas=6, status=status)
+    torch.cuda.synchronize()
+    assert decode_status(status) == 0
+    want = [t[:, torch.from_numpy(src).cuda()].clone() for t in kv]
+    for t in kv:
+        t.zero_()
+    opts = dict(num_layers=L, kv_dim=K, chunk_bytes=reg.chunk_bytes, max_blocks_per_op=NB, notify_mode="flag",
+                num_counters=2, layers_per_batch=lpb, size_table_ptr=table.data_ptr(), size_table_layers=L,
+                codec_pipelines=6)
+    grp = C.LayerwiseGroup([reg.as_native()], dict(base=pool.data_ptr(), layer_stride=K * slot, kv_stride=slot,
+                                                    block_stride=L * K * slot, num_blocks=NB), opts)
+    dst = rng.permutation(NB)[:n].astype(np.int64)
+    r = grp.restore(dst, cpu, 1)
+    assert r.status == 0 and grp.counter_status(1) == 0
+    assert [_drain(grp.eventfd_of(1, 0, l)) for l in range(L)] == [1] * L
+    d = torch.from_numpy(dst).cuda()
+    for l in range(L):
+        assert torch.equal(kv[l][:, d].view(torch.int16), want[l].view(torch.int16)), l
+    del keep

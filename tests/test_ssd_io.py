@@ -109,3 +109,49 @@ def test_host_region_file_backed_is_shared(tmp_path):
     assert list(np.frombuffer(b, dtype=np.uint8)[:4]) == [1, 2, 3, 4]
     assert a.file_backed and not a.registered
     a.free(); b.free()
+
+
+def test_packed_blocks_move_only_their_used_bytes(tmp_path):
+    """Host blocks in the lossless codec's slot format: tile slots of which only the first size bytes are used.
+    A packed write gathers them into one run per block, the read scatters them back; the bytes on the SSD
+    interface are the used bytes rounded up to 4 KiB, and a corrupt size row fails only its block."""
+    tile_slot, last_slot, tpc, chunks = 4096 + 128, 2048 + 128, 2, 3          # chunk = one full and one short tile
+    chunk_slot = tile_slot + last_slot
+    block = 32768                                                               # 4 KiB multiple >= chunks * chunk_slot
+    assert chunks * chunk_slot <= block
+    paths = [[str(tmp_path / "p0.bin"), str(tmp_path / "p1.bin")]]
+    e = C.SsdIoEngine(paths, block, 4, create=True, try_direct=True, iouring_entries=32, num_threads=2)
+    region = C.host_region_alloc(8 * block)
+    buf = np.frombuffer(region, dtype=np.uint8)
+    rng = np.random.default_rng(3)
+    buf[:] = rng.integers(0, 256, size=buf.size, dtype=np.uint8)
+    geo = dict(cpu_block_stride=block, chunk_slot_bytes=chunk_slot, tile_slot_bytes=tile_slot,
+               last_tile_slot_bytes=last_slot, tiles_per_chunk=tpc, entries=chunks * tpc)
+    cpu = np.array([1, 5, 6], dtype=np.int64)
+    ssd = np.array([7, 0, 3], dtype=np.int64)
+    sizes = rng.integers(2, 64, size=(3, chunks * tpc)).astype(np.int32) * 16      # multiples of 16 under every slot
+    want = buf.copy()
+    nfail, ok = e.transfer_packed(region.ptr, cpu, ssd, False, geo, sizes)
+    assert nfail == 0 and ok.all()
+    written = int(sum((int(r.sum()) + 4095) // 4096 * 4096 for r in sizes))
+    assert e.bytes_written == written < 3 * block
+    buf[:] = 0
+    cpu2 = np.array([0, 2, 4], dtype=np.int64)
+    nfail, ok = e.transfer_packed(region.ptr, cpu2, ssd, True, geo, sizes)
+    assert nfail == 0 and e.bytes_read == written
+    for i in range(3):
+        for t in range(chunks * tpc):
+            off = (t // tpc) * chunk_slot + (t % tpc) * tile_slot
+            a = buf[cpu2[i] * block + off:cpu2[i] * block + off + sizes[i, t]]
+            b = want[cpu[i] * block + off:cpu[i] * block + off + sizes[i, t]]
+            assert np.array_equal(a, b), (i, t)
+    # a row with an impossible size fails its block and nothing else
+    bad = sizes.copy()
+    bad[1, 3] = last_slot + 16
+    nfail, ok = e.transfer_packed(region.ptr, cpu, ssd, False, geo, bad)
+    assert nfail == 1 and list(ok) == [1, 0, 1]
+    e.set_fault(3, 0)
+    nfail, ok = e.transfer_packed(region.ptr, cpu2, ssd, True, geo, sizes)
+    assert nfail == 3
+    e.set_fault(0, 0)
+    region.free()
