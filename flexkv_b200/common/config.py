@@ -344,6 +344,9 @@ def load_env_config() -> Namespace:
         server_recv_port=_env("FLEXKV_SERVER_RECV_PORT", "ipc:///tmp/flexkv_server"),
         index_accel=_env("FLEXKV_INDEX_ACCEL", True, bool),
         native_scheduler=_env("FLEXKV_NATIVE_SCHEDULER", True, bool),
+        # "thread": the data plane shares the serving process (default); "process": it runs in a child process
+        transfer_manager_mode=_env("FLEXKV_TRANSFER_MANAGER_MODE", "thread", str),
+        crash_diagnostics=_env("FLEXKV_CRASH_DIAGNOSTICS", False, bool),
         cpu_layout_type=KVCacheLayoutType(_env("FLEXKV_CPU_LAYOUT", "BLOCKFIRST").upper()),
         ssd_layout_type=KVCacheLayoutType(_env("FLEXKV_SSD_LAYOUT", "BLOCKFIRST").upper()),
         remote_layout_type=KVCacheLayoutType(_env("FLEXKV_REMOTE_LAYOUT", "BLOCKFIRST").upper()),

@@ -99,3 +99,28 @@ def debug_timing(name: Optional[str] = None) -> Callable:
                 flexkv_logger.debug("%s took %.3f ms", label, (time.perf_counter() - t0) * 1e3)
         return wrapper
     return deco
+
+
+_crash_diagnostics_installed = False
+
+
+def install_crash_diagnostics(dump_signal: Optional[int] = None) -> bool:
+    """On a fatal signal (SIGSEGV, SIGFPE, SIGABRT, SIGBUS, SIGILL) the interpreter prints the Python stack
+    of every thread before it dies, and ``SIGUSR1`` (or ``dump_signal``) prints them on demand without
+    stopping the process: the first thing wanted from a worker that crashed inside native code or sits
+    in a call that never returns (flexkv/common/debug.py:315-337). Idempotent; returns False when the
+    standard error stream has no file descriptor to write to."""
+    global _crash_diagnostics_installed
+    import faulthandler
+    import signal
+    import sys
+    if _crash_diagnostics_installed:
+        return True
+    try:
+        faulthandler.enable(file=sys.stderr, all_threads=True)
+        sig = signal.SIGUSR1 if dump_signal is None else dump_signal
+        faulthandler.register(sig, file=sys.stderr, all_threads=True, chain=False)
+    except (ValueError, OSError, AttributeError, RuntimeError):
+        return False
+    _crash_diagnostics_installed = True
+    return True

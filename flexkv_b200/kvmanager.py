@@ -33,7 +33,8 @@ class KVManager:
     def __init__(self, model_config: ModelConfig, cache_config: CacheConfig, dp_client_id: int = 0,
                  server_recv_port: Optional[str] = None, gpu_register_port: Optional[str] = None,
                  require_gpu: Optional[bool] = None, in_process: Optional[bool] = None,
-                 remote_transfer_endpoints: Optional[Sequence[Tuple[str, str, str]]] = None) -> None:
+                 remote_transfer_endpoints: Optional[Sequence[Tuple[str, str, str]]] = None,
+                 transfer_manager_mode: Optional[str] = None) -> None:
         env = GLOBAL_CONFIG_FROM_ENV
         self.model_config = model_config
         self.cache_config = cache_config
@@ -72,8 +73,17 @@ class KVManager:
             from .transfer_manager import TransferManager
             if require_gpu is None:
                 require_gpu = torch.cuda.is_available()
-            self.transfer_manager = TransferManager(model_config, cache_config, gpu_register_port,
-                                                    require_gpu=require_gpu)
+            if env.crash_diagnostics:
+                from .common.debug import install_crash_diagnostics
+                install_crash_diagnostics()
+            if (transfer_manager_mode or env.transfer_manager_mode) == "process":
+                # the data plane in a child process (pipe EOF in both directions, SIGTERM-safe unpinning)
+                from .transfer_process import TransferManagerProcessHandle
+                self.transfer_manager = TransferManagerProcessHandle(model_config, cache_config, gpu_register_port,
+                                                                     require_gpu=require_gpu)
+            else:
+                self.transfer_manager = TransferManager(model_config, cache_config, gpu_register_port,
+                                                        require_gpu=require_gpu)
             handles = [self.transfer_manager]
             # other nodes of a TP/PP group: one handle per (command, result, query) endpoint triple; a graph
             # is finished when every node reported it
@@ -94,6 +104,11 @@ class KVManager:
         per group with that group's tensors and layout."""
         if self.server_client_mode:
             raise RuntimeError("in server-client mode GPU tensors are registered through KVTPClient")
+        if hasattr(self.transfer_manager, "register_gpu_tensors"):      # data plane in a child process
+            self.transfer_manager.register_gpu_tensors(tensors, gpu_layout, tp_rank=tp_rank, pp_rank=pp_rank,
+                                                       dp_client_id=self.dp_client_id if dp_client_id is None
+                                                       else dp_client_id, group_id=group_id)
+            return
         from .storage.gpu_layout import register_tensors
         reg = register_tensors(tensors, gpu_layout, tp_rank=tp_rank, pp_rank=pp_rank,
                                dp_client_id=self.dp_client_id if dp_client_id is None else dp_client_id,

@@ -180,8 +180,9 @@ class StorageEngine:
         total = self._host_total_bytes(block_bytes, lay)
         backing = os.environ.get("FLEXKV_HUGEPAGE_FILE", "") if c.use_hugepage_cpu_buffer else ""
         self._owned_backing = ""
-        if c.enable_p2p_cpu and not backing:
-            # other nodes of the box map this pool to pull blocks out of it
+        if (c.enable_p2p_cpu or os.environ.get("FLEXKV_HOST_POOL_SHM", "0") == "1") and not backing:
+            # other nodes of the box map this pool to pull blocks out of it (FLEXKV_HOST_POOL_SHM=1 asks for the
+            # same named shared-memory file without the cross-node index)
             import uuid
             backing = f"/dev/shm/flexkv_host_{os.getpid()}_{uuid.uuid4().hex[:8]}"
             self._owned_backing = backing
