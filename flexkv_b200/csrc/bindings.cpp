@@ -386,6 +386,7 @@ PYBIND11_MODULE(_C, m) {
              t.set_launch(h2d, KvCopyLaunch{ctas, tile, engine});
            })
       .def_property_readonly("ce_ops", &TransferGroup::ce_ops)
+      .def_property_readonly("staged_ops", &TransferGroup::staged_ops)
       .def_property_readonly("num_ranks", &TransferGroup::num_ranks);
 
   init_kernel_bindings(m);

@@ -86,6 +86,7 @@ inline GroupOptions parse_group_options(const py::dict& o) {
   if (o.contains("ring_slots")) g.ring_slots = o["ring_slots"].cast<int>();
   if (o.contains("max_blocks_per_op")) g.max_blocks_per_op = o["max_blocks_per_op"].cast<int64_t>();
   if (o.contains("high_priority_stream")) g.high_priority_stream = o["high_priority_stream"].cast<bool>();
+  if (o.contains("ce_staging_blocks")) g.ce_staging_blocks = o["ce_staging_blocks"].cast<int64_t>();
   if (o.contains("ce_max_copies")) g.ce_policy.max_copies = o["ce_max_copies"].cast<int64_t>();
   if (o.contains("ce_min_bytes_per_copy")) g.ce_policy.min_bytes_per_copy = o["ce_min_bytes_per_copy"].cast<int64_t>();
   return g;

@@ -206,6 +206,20 @@ void TransferGroup::rank_main(int r) {
               if (a.status & (1 << b)) p.status[b] = 1;
             ce_ops_.fetch_add(1, std::memory_order_relaxed);
             done = true;
+          } else if (opt_.ce_staging_blocks > 0 && p.c_block_stride > 0) {
+            // scattered GPU pages, host blocks in a row: gather into device staging, one large copy per piece
+            const int64_t min_run = std::max<int64_t>(1, (opt_.ce_policy.min_bytes_per_copy + p.c_block_stride - 1) /
+                                                             p.c_block_stride);
+            std::vector<CeHostRun> runs;
+            if ((int)gpus_.size() == 1 &&
+                ce_host_runs(p, p.gpu_blocks, p.cpu_blocks, p.num_pairs, opt_.num_layers, min_run, runs)) {
+              KvCopyLaunch kcfg = cfg;
+              kcfg.engine = 0;
+              lerr[i] = ce_copy_staged(p, runs, rk.staging, opt_.ce_staging_blocks, kcfg, rk.stream);
+              ce_ops_.fetch_add(1, std::memory_order_relaxed);
+              staged_ops_.fetch_add(1, std::memory_order_relaxed);
+              done = true;
+            }
           }
         }
         if (!done) {
@@ -232,6 +246,7 @@ void TransferGroup::rank_main(int r) {
       finish(batch[i].ticket, status, ms);
     }
   }
+  ce_staging_free(rk.staging);
   for (int i = 0; i < kInflight; ++i) { cudaEventDestroy(ev0[i]); cudaEventDestroy(ev1[i]); }
   if (rk.status) cudaFreeHost(rk.status);
   if (rk.stream) cudaStreamDestroy(rk.stream);

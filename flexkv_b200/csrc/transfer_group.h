@@ -57,6 +57,8 @@ struct GroupOptions {
   int64_t max_blocks_per_op = 1 << 16;
   bool high_priority_stream = false;
   CePolicy ce_policy;
+  int64_t ce_staging_blocks = 32;   // blocks per staging buffer of the gather + large-copy route (0 = route off);
+                                    // two buffers of this size are allocated per GPU the first time the route runs
 };
 
 // Engine selectors of an op (KvCopyLaunch::engine or a per-op override).
@@ -95,6 +97,7 @@ class TransferGroup {
   void set_launch(bool h2d, KvCopyLaunch cfg);
   int num_ranks() const { return (int)gpus_.size(); }
   uint64_t ce_ops() const { return ce_ops_.load(); }   // ops that went through the copy engines
+  uint64_t staged_ops() const { return staged_ops_.load(); }   // of which through the staging area
   const GroupOptions& options() const { return opt_; }
 
  private:
@@ -116,6 +119,7 @@ class TransferGroup {
     cudaStream_t stream = nullptr;
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
     int32_t* status = nullptr;  // mapped pinned word
+    CeStaging staging;          // device staging of the gather + large-copy route (allocated on first use)
     bool ready = false;
     std::string init_error;
   };
@@ -142,7 +146,7 @@ class TransferGroup {
   std::unordered_map<uint64_t, Pending> pending_;
   uint64_t next_ticket_ = 1;
   uint64_t op_counter_ = 0;
-  std::atomic<uint64_t> ce_ops_{0};
+  std::atomic<uint64_t> ce_ops_{0}, staged_ops_{0};
   mutable std::mutex ptr_mu_;
 };
 

@@ -88,3 +88,49 @@ def test_bad_ids_are_reported_by_the_copy_engine_path():
     r = grp.transfer(g, c, False, 0, 2, ENG["ce"])
     assert r.status == 1
     assert int(pool[7].count_nonzero()) == 0 and int(pool[4].count_nonzero()) > 0
+
+
+def test_scattered_pages_with_host_blocks_in_a_row_go_through_the_staging_area():
+    """GPU pages scattered, host blocks allocated in runs: the gather kernel fills a device staging buffer in
+    host block format and one large copy moves each piece; bytes equal the kernel path in both directions.
+    The staging buffers (4 blocks each here) are reused by several pieces and by both runs."""
+    dev = torch.device("cuda:0")
+    shape = KVShape("t", 3, 2, 128, tokens_per_block=16)          # 8 KiB chunks, 48 KiB blocks
+    NG, NC = 256, 200
+    tensors, layout = alloc_paged_cache(shape, NG, dev, "vllm", fill="normal", seed=5)
+    reg = register_tensors(tensors, layout)
+    chunk = reg.chunk_bytes
+    pool = torch.zeros(NC, shape.num_layers, shape.kv_dim, chunk, dtype=torch.uint8).pin_memory()
+    host = dict(base=pool.data_ptr(), layer_stride=shape.kv_dim * chunk, kv_stride=chunk,
+                block_stride=shape.num_layers * shape.kv_dim * chunk, num_blocks=NC)
+    opts = dict(num_layers=shape.num_layers, kv_dim=shape.kv_dim, chunk_bytes=chunk, max_blocks_per_op=4096,
+                ce_min_bytes_per_copy=96 << 10, ce_staging_blocks=4)     # runs of >= 2 blocks qualify
+    grp = C.TransferGroup([reg.as_native()], host, opts)
+    rng = np.random.default_rng(8)
+    g = rng.permutation(NG)[:30].astype(np.int64)                 # scattered pages
+    c = np.concatenate([np.arange(40, 59), np.arange(120, 131)]).astype(np.int64)   # two host runs: 19 and 11 blocks
+    n0 = grp.staged_ops
+    assert grp.transfer(g, c, False, 0, shape.num_layers, ENG["auto"]).status == 0
+    assert grp.staged_ops == n0 + 1
+    want = pool.clone()
+    pool.zero_()
+    assert grp.transfer(g, c, False, 0, shape.num_layers, ENG["tma"]).status == 0
+    assert torch.equal(pool, want) and int(want.count_nonzero()) > 0
+    # restore through the staging area into other scattered pages
+    saved = [t.clone() for t in tensors]
+    g2 = rng.permutation(NG)[:30].astype(np.int64)
+    assert grp.transfer(g2, c, True, 0, shape.num_layers, ENG["auto"]).status == 0
+    assert grp.staged_ops == n0 + 2
+    a, b = torch.from_numpy(g).to(dev), torch.from_numpy(g2).to(dev)
+    for l in range(shape.num_layers):
+        assert torch.equal(tensors[l][:, b], saved[l][:, a])
+    # a partial-layer op or a stray host block keeps the op on the kernel
+    assert grp.transfer(g, c, False, 0, 2, ENG["auto"]).status == 0
+    c3 = c.copy()
+    c3[5] = 199
+    assert grp.transfer(g, c3, False, 0, shape.num_layers, ENG["auto"]).status == 0
+    assert grp.staged_ops == n0 + 2
+    # a bad page id is refused on the host: the op falls back to the kernel, which reports it
+    gb = g.copy()
+    gb[3] = NG + 5
+    assert grp.transfer(gb, c, False, 0, shape.num_layers, ENG["auto"]).status == 1
