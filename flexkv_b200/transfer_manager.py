@@ -235,6 +235,17 @@ class TransferManager:
 
 # ------------------------------------------------------------------ other nodes / processes
 
+def _remote_main(model_config, cache_config, cmd, res, qry, gpu_register_port, require_gpu) -> None:
+    import signal
+    from .common.debug import install_crash_diagnostics
+    install_crash_diagnostics()
+    signal.signal(signal.SIGINT, signal.SIG_IGN)
+    node = TransferManagerOnRemote(model_config, cache_config, cmd, res, qry, require_gpu=require_gpu,
+                                   gpu_register_port=gpu_register_port)
+    signal.signal(signal.SIGTERM, lambda *_: node._stop.set())      # leave the serve loop, then unpin
+    node.serve_forever()
+
+
 class TransferManagerOnRemote:
     """Runs a TransferManager for this node's GPUs on behalf of a master node: graphs
     arrive on a ZeroMQ PULL socket, completions go back on a PUSH socket, readiness is
@@ -243,9 +254,10 @@ class TransferManagerOnRemote:
     are the master's, applied to the same positions here."""
 
     def __init__(self, model_config: ModelConfig, cache_config: CacheConfig, command_endpoint: str,
-                 result_endpoint: str, query_endpoint: str, require_gpu: bool = True) -> None:
+                 result_endpoint: str, query_endpoint: str, require_gpu: bool = True,
+                 gpu_register_port: Optional[str] = None) -> None:
         import zmq
-        self.tm = TransferManager(model_config, cache_config, require_gpu=require_gpu)
+        self.tm = TransferManager(model_config, cache_config, gpu_register_port, require_gpu=require_gpu)
         self._ctx = zmq.Context.instance()
         self._cmd = self._ctx.socket(zmq.PULL)
         self._cmd.setsockopt(zmq.LINGER, 0)
@@ -260,6 +272,20 @@ class TransferManagerOnRemote:
 
     def register_gpu(self, reg: GpuRegistration) -> None:
         self.tm.register_gpu(reg)
+
+    @staticmethod
+    def create_process(model_config: ModelConfig, cache_config: CacheConfig, command_endpoint: str,
+                       result_endpoint: str, query_endpoint: str, gpu_register_port: Optional[str] = None,
+                       require_gpu: bool = True):
+        """Starts this node's transfer manager in a process of its own (spawn) and returns the process: local
+        engine workers register their tensors at ``gpu_register_port``, the master drives it over the three
+        endpoints (flexkv/transfer_manager.py:529-908 ``TransferManagerOnRemote.create_process``)."""
+        import multiprocessing as mp
+        p = mp.get_context("spawn").Process(target=_remote_main, name="flexkv-remote-transfer-manager", daemon=True,
+                                            args=(model_config, cache_config, command_endpoint, result_endpoint,
+                                                  query_endpoint, gpu_register_port, require_gpu))
+        p.start()
+        return p
 
     def serve_forever(self) -> None:
         import pickle

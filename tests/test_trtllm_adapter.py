@@ -80,3 +80,62 @@ def test_a_request_that_did_not_finish_normally_is_not_offloaded():
         assert conn.request_finished(r, [1, 2, 3, 4]) is True
     finally:
         conn.shutdown()
+
+
+def test_namespace_rule_and_request_wrapper():
+    from flexkv_b200.integration.tensorrt_llm.utils import RequestWrapper, extract_namespace, physical_device_id
+    r = NS(request_id=5, lora_task_id=123, cache_salt_id="session_1", namespace_info="tenant_A| user_1 |",
+           get_tokens=lambda: [[1, 2, 3, 4, 5]], prompt_len=4, num_connector_matched_tokens=2,
+           is_finished=True, is_finished_normal=lambda: False)
+    assert extract_namespace(r) == ["123", "session_1", "tenant_A", "user_1"]
+    assert extract_namespace(NS()) is None and extract_namespace(NS(namespace_info=7)) == ["7"]
+    w = RequestWrapper(r)
+    assert w.req_id == 5 and w.all_token_ids == [1, 2, 3, 4, 5] and w.num_prompt_tokens == 4
+    assert w.np_token_ids.dtype == np.int64 and w.np_token_ids is w.np_token_ids       # converted once
+    assert w.num_new_matched_tokens == 2 and w.is_finished() and not w.is_finished_normal()
+    assert w.namespace_info == ["123", "session_1", "tenant_A", "user_1"]
+    with pytest.raises(ValueError):
+        RequestWrapper(NS(get_tokens=lambda: [[1], [2]])).all_token_ids            # beam search
+    assert physical_device_id(1, "4,6") == 6 and physical_device_id(3, "4,6") == 3 and physical_device_id(2, None) == 2
+    assert physical_device_id(0, "GPU-abc") == 0
+
+
+def test_namespaces_isolate_requests_with_the_same_tokens():
+    conn, pool, mgr = make()
+    try:
+        tok = np.arange(900, 900 + 4 * T)
+        a = NS(py_request_id=21, request_id=None, get_tokens=lambda beam: list(tok), lora_task_id=1,
+               namespace_info="tenant_A")
+        assert conn.request_finished(a, [1, 2, 3, 4]) is True
+        assert "21" in drain(conn, "finished_sending", 21)
+        same = NS(py_request_id=22, request_id=None, get_tokens=lambda beam: list(tok), lora_task_id=1,
+                  namespace_info="tenant_A")
+        other = NS(py_request_id=23, request_id=None, get_tokens=lambda beam: list(tok), lora_task_id=1,
+                   namespace_info="tenant_B")
+        assert conn.get_num_new_matched_tokens(other, 0)[0] == 0           # another tenant sees nothing
+        n, _ = conn.get_num_new_matched_tokens(same, 0)
+        assert n > 0 and conn.tasks["22"].num_new_matched_tokens == n and conn.tasks["22"].match_cost >= 0
+        meta = conn.build_connector_meta()
+        assert isinstance(meta.finished_sending, list) and meta["finished_recving"] == set(meta.finished_recving)
+    finally:
+        conn.shutdown()
+        mgr.shutdown()
+
+
+def test_worker_connector_reports_the_bound_metadata(tmp_path):
+    from flexkv_b200.integration.tensorrt_llm.meta import FlexKVConnectorMetadata
+    from flexkv_b200.integration.tensorrt_llm.trtllm_adapter import FlexKVWorkerConnector
+    shape = KVShape("t", L, H, D, tokens_per_block=T)
+    cfg = FlexKVConfig()
+    cfg.model_config = make_model_config(shape)
+    cfg.cache_config = CacheConfig(tokens_per_block=T, num_cpu_blocks=8)
+    cfg.gpu_register_port = f"ipc://{tmp_path}/reg"
+    w = FlexKVWorkerConnector(flexkv_config=cfg)
+    try:
+        assert w.remote_process is None and w.get_finished() == ([], [])
+        w.bind_connector_meta(FlexKVConnectorMetadata(["3"], ["4", "5"]))
+        assert w.get_finished([9], [9]) == (["3"], ["4", "5"])
+        with pytest.raises(ValueError):
+            w.register_kv_caches(torch.zeros(4, L, 2, 7))
+    finally:
+        w.shutdown()
