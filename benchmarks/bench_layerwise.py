@@ -148,6 +148,9 @@ def scenario_overlap(a):
         epoch = grp.begin_restore(counter)     # the value this round's restore will publish to the layer flags
         th = threading.Thread(target=lambda: res.setdefault("r", grp.restore(gpu, cpu, counter)))
         th.start()
+        # the waits go to the GPU only after the restore's launches are queued: a stream wait ahead of its producer
+        # can block the hardware queue they share
+        assert grp.wait_launched(counter, epoch, 30000), "the restore did not queue its launches"
         # the model: per layer, wait (in stream order) for the layer's KV, then "compute"
         for d in range(a.gpus):
             with torch.cuda.device(d):

@@ -107,6 +107,11 @@ void init_layerwise_bindings(py::module_& m) {
       .def("begin_restore", &LayerwiseGroup::begin_restore, py::arg("counter"),
            "Reserves and returns the epoch the next restore() on this counter publishes.")
       .def("counter_status", &LayerwiseGroup::counter_status, py::arg("counter"))
+      .def("wait_launched", [](LayerwiseGroup& g, int counter, uint32_t epoch, int timeout_ms) {
+             py::gil_scoped_release rel;
+             return g.wait_launched(counter, epoch, timeout_ms);
+           }, py::arg("counter"), py::arg("epoch"), py::arg("timeout_ms") = 10000,
+           "Blocks until every rank has queued the launches of the restore publishing `epoch` (or it failed).")
       .def("stream_wait_layer", [](LayerwiseGroup& g, int rank, int counter, int layer, uint64_t stream,
                                    uint32_t epoch) {
              cudaError_t e = g.stream_wait_layer(rank, counter, layer, (cudaStream_t)(uintptr_t)stream, epoch);

@@ -85,6 +85,7 @@ void LayerwiseGroup::start_ranks() {
   const int L = opt_.group.num_layers, R = (int)gpus_.size(), C = opt_.num_counters;
   epochs_.assign((size_t)C, 0);
   reserved_.assign((size_t)C, 0);
+  launched_.assign((size_t)C * gpus_.size(), 0);
   counter_status_.reset(new std::atomic<int>[(size_t)C]);
   for (int i = 0; i < C; ++i) counter_status_[(size_t)i].store(0);
   if (opt_.create_eventfds) {
@@ -175,6 +176,25 @@ uint32_t LayerwiseGroup::begin_restore(int counter) {
   return epochs_[(size_t)counter];
 }
 
+void LayerwiseGroup::mark_launched(int r, const Job& j) {
+  {
+    std::lock_guard<std::mutex> g(launched_mu_);
+    launched_[(size_t)j.counter * gpus_.size() + (size_t)r] = j.epoch;
+  }
+  launched_cv_.notify_all();
+}
+
+bool LayerwiseGroup::wait_launched(int counter, uint32_t epoch, int timeout_ms) {
+  if (counter < 0 || counter >= opt_.num_counters) throw std::invalid_argument("LayerwiseGroup: bad counter id");
+  std::unique_lock<std::mutex> lk(launched_mu_);
+  const size_t R = gpus_.size();
+  return launched_cv_.wait_for(lk, std::chrono::milliseconds(timeout_ms), [&] {
+    for (size_t r = 0; r < R; ++r)
+      if ((int32_t)(launched_[(size_t)counter * R + r] - epoch) < 0) return false;
+    return true;
+  });
+}
+
 cudaError_t LayerwiseGroup::stream_wait_layer(int rank, int counter, int layer, cudaStream_t stream, uint32_t epoch) {
   Rank& rk = *ranks_.at((size_t)rank);
   if (counter < 0 || counter >= opt_.num_counters || layer < 0 || layer >= opt_.group.num_layers)
@@ -211,6 +231,7 @@ void LayerwiseGroup::release_waiters(int r, const Job& j, int from_layer, int st
   Rank& rk = *ranks_[(size_t)r];
   const int L = opt_.group.num_layers;
   counter_status_[(size_t)j.counter].store(status ? status : -1, std::memory_order_release);
+  mark_launched(r, j);      // nothing more will be queued for this epoch
   if (from_layer >= L) return;
   uint32_t* hflags = rk.host_flags + (size_t)j.counter * L;
   for (int l = from_layer; l < L; ++l) __atomic_store_n(hflags + l, j.epoch, __ATOMIC_RELEASE);
@@ -378,6 +399,7 @@ void LayerwiseGroup::run_job_members(int r, const Job& j) {
     }
   }
   bool kernel_failed = false;
+  mark_launched(r, j);      // every launch of this rank is queued: consumers may queue their stream waits now
   if (err == cudaSuccess && opt_.notify != NotifyMode::HOSTFUNC) {
     const auto t0 = std::chrono::steady_clock::now();
     for (int l = 0; l < L && err == cudaSuccess && !kernel_failed; ++l) {
@@ -484,6 +506,7 @@ void LayerwiseGroup::run_job(int r, const Job& j) {
       if (err == cudaSuccess) queued_upto = l1;
     }
   }
+  mark_launched(r, j);      // every launch of this rank is queued: consumers may queue their stream waits now
   if (err == cudaSuccess && (opt_.notify != NotifyMode::HOSTFUNC || fused)) {
     // retire in order from this thread; a fused launch is watched layer by layer through the mapped flags
     const auto t0 = std::chrono::steady_clock::now();

@@ -106,10 +106,16 @@ class LayerwiseGroup {
   // stream_wait_layer; restore() then publishes exactly that epoch. Without a reservation restore() takes the
   // next epoch itself and returns it in LayerwiseResult::epoch.
   uint32_t begin_restore(int counter);
+  // Blocks (on the host, up to timeout_ms) until every rank has QUEUED all launches of the restore that publishes
+  // `epoch` on `counter`, or until that restore has failed. True when queued. A consumer calls this between
+  // begin_restore() and its stream_wait_layer() calls: a stream wait that reaches the GPU ahead of the producer's
+  // launch can share a hardware queue with it and then nothing behind the wait, the producer included, ever runs.
+  bool wait_launched(int counter, uint32_t epoch, int timeout_ms);
   // Makes `stream` (a CUDA stream of rank's device) wait until layer `layer` of the restore that publishes
   // `epoch` on `counter` has landed (a stream-ordered wait on the device flag, value >= epoch). `epoch` 0
   // means "the newest epoch handed out for this counter", which is only right once that restore has been
-  // started or reserved. A failed restore releases the waiters too; whether the data is usable is told by
+  // started or reserved. Queue it only once wait_launched() has returned true (see there). A failed restore
+  // releases the waiters too; whether the data is usable is told by
   // counter_status() / the restore's result, never by the flag alone.
   cudaError_t stream_wait_layer(int rank, int counter, int layer, cudaStream_t stream, uint32_t epoch = 0);
   // 0 while the newest restore on `counter` is running or has succeeded, else its failure status
@@ -184,6 +190,10 @@ class LayerwiseGroup {
   std::vector<uint8_t> reserved_;   // per counter: begin_restore() handed the next epoch out already
   std::mutex epoch_mu_;
   std::unique_ptr<std::atomic<int>[]> counter_status_;
+  std::mutex launched_mu_;
+  std::condition_variable launched_cv_;
+  std::vector<uint32_t> launched_;  // [counters][ranks]: newest epoch whose launches are all queued (or that failed)
+  void mark_launched(int r, const Job& j);
   int64_t* id_ring_ = nullptr;      // [2][max_blocks], mapped pinned
   std::mutex api_mu_;               // one restore at a time per group
   std::mutex done_mu_;

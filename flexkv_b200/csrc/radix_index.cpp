@@ -670,6 +670,9 @@ std::vector<int64_t> BlockPool::allocate(int64_t n, bool strict) {
     used_[(size_t)id] = 1;
     out[(size_t)i] = id;
   }
+  // Ascending ids: blocks freed together (an evicted sequence) come back as runs of neighbours, and a request
+  // whose host blocks lie in a row can be moved with large copies instead of one per block.
+  std::sort(out.begin(), out.end());
   return out;
 }
 

@@ -156,9 +156,10 @@ def test_a_layer_flag_is_never_seen_before_the_layer_bytes(lpb):
 
 
 @pytest.mark.parametrize("lpb", [1, 0])
-def test_consumer_queued_before_the_restore_waits_for_this_restore(lpb):
-    """The model stream runs ahead: its per-layer waits are queued before the restore is issued. With the
-    epoch reserved by begin_restore they bind to THIS restore, not to the previous one's flags."""
+def test_consumer_waits_bind_to_the_reserved_epoch_not_to_the_previous_restore(lpb):
+    """The model thread reserves the epoch before the restore is issued, waits on the host until the restore's
+    launches are queued, then queues its per-layer stream waits: they bind to THIS restore, not to the previous
+    one's flags (which already hold an older epoch)."""
     import threading
     shape = KVShape("lw", 5, 2, 128, tokens_per_block=16)
     kv, reg, pool, grp, xfer = _setup(shape, notify="flag", layers_per_batch=lpb)
@@ -173,12 +174,14 @@ def test_consumer_queued_before_the_restore_waits_for_this_restore(lpb):
     ep = grp.begin_restore(0)
     assert ep == grp.epoch_of(0) == 2
     snaps = []
+    assert not grp.wait_launched(0, ep, 50)                   # nothing queued yet for this epoch
+    th = threading.Thread(target=lambda: grp.restore(ids, ids, 0))
+    th.start()
+    assert grp.wait_launched(0, ep, 10000)
     with torch.cuda.stream(model):
         for l in range(shape.num_layers):
             grp.stream_wait_layer(0, 0, l, model.cuda_stream, ep)
             snaps.append(kv[l][:, :n].clone())                # what the model would read once released
-    th = threading.Thread(target=lambda: grp.restore(ids, ids, 0))
-    th.start()
     th.join()
     model.synchronize()
     assert grp.epoch_of(0) == 2 and grp.counter_status(0) == 0
@@ -202,13 +205,13 @@ def test_failed_disk_stage_releases_every_waiter_with_the_failure_signal(tmp_pat
     ssd.set_fault(3, 0)                                       # every IO fails
     model = torch.cuda.Stream()
     ep = grp.begin_restore(1)
-    for l in range(shape.num_layers):
-        grp.stream_wait_layer(0, 1, l, model.cuda_stream, ep)
     before = [t.clone() for t in kv]
     r = grp.restore(ids, ids, 1, ssd, lay, ids, ids)
     assert r.status != 0 and r.epoch == ep
-    assert grp.counter_status(1) != 0
-    model.synchronize()                                       # released, not parked forever
+    assert grp.counter_status(1) != 0 and grp.wait_launched(1, ep, 1000)      # a failed restore counts as queued
+    for l in range(shape.num_layers):
+        grp.stream_wait_layer(0, 1, l, model.cuda_stream, ep)
+    model.synchronize()                                       # the flags were released from the host: no hang
     # every layer's eventfd fired once: an engine hook blocked on it wakes up and reads the failure
     # from counter_status() / the failed task
     assert [_drain(grp.eventfd_of(1, 0, l)) for l in range(shape.num_layers)] == [1] * shape.num_layers
