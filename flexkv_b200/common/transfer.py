@@ -244,11 +244,19 @@ class TransferOpGraph:
     # ---- execution ------------------------------------------------------------
     set_swa_gpu_blocks = set_swa_pages      # the reference's name for the same binding step
 
-    def clear_gpu_blocks(self) -> None:
+    _GPU_SIDE_OF = {"D2H": "src", "H2D": "dst", "DISK2D": "dst", "D2DISK": "src", "PEERD2D": "dst"}
+
+    def clear_gpu_blocks(self, force: bool = False) -> None:
         """Forgets the bound GPU side of every late-bound op so that another pipeline stage (whose
-        engine uses its own block ids) can bind the same plan again (flexkv/kvtask.py:438-444)."""
+        engine uses its own block ids) can bind the same plan again (flexkv/kvtask.py:438-444).
+        ``force`` also unbinds ops whose GPU pages were known when the plan was made (a put, a one-call get):
+        which side is the GPU's follows from the op's type, its place in the page list from its binding rule."""
         for op in self._ops.values():
             side = getattr(op, "_late_side", None)
+            if side is None and force and not op.is_swa:
+                side = self._GPU_SIDE_OF.get(op.transfer_type.value)
+                if side is None and isinstance(op, LayerwiseTransferOp):
+                    side = "dst"
             if side is None or op.is_swa:
                 continue
             if side == "src":

@@ -48,8 +48,14 @@ def sglang_gpu_layout(k_buffers: Sequence[torch.Tensor], page_size: int, use_mla
 class FlexKVConnector:
     def __init__(self, flexkv_config: FlexKVConfig, page_size: int, tp_rank: int = 0, tp_size: int = 1,
                  pp_rank: int = 0, pp_size: int = 1, dp_rank: int = 0, cp_rank: int = 0, cp_size: int = 1,
-                 comm: Optional[FlexKVComm] = None, kv_manager: Any = None, register: bool = True) -> None:
+                 comm: Optional[FlexKVComm] = None, kv_manager: Any = None, register: bool = True,
+                 hand_off_slot_mapping: bool = False) -> None:
+        """``hand_off_slot_mapping``: set on ONE rank of every node other than the leader's when the group
+        spans nodes. That node's transfer manager receives the leader's graphs with the GPU side unbound; this
+        rank sends it the pages its node allocated for each task (flexkv/integration/sglang/connector.py:2199-2204)."""
         self.cfg = flexkv_config
+        self.hand_off_slot_mapping = bool(hand_off_slot_mapping)
+        self.any_hand_off: Optional[bool] = None      # agreed over the group at the first load or store
         self.T = page_size
         self.tp_rank, self.tp_size, self.pp_rank, self.dp_rank = tp_rank, tp_size, pp_rank, dp_rank
         self.comm = comm or FlexKVComm(tp_size=tp_size, cp_size=cp_size, pp_size=pp_size)
@@ -85,7 +91,39 @@ class FlexKVConnector:
         layout = layout._replace(num_block=nb)
         tensors = list(k_buffers) + ([] if use_mla else list(v_buffers))
         if self._client is not None:
-            self._client.register_to_server(tensors, layout, group_id=group_id)
+            self._register_with_retry(tensors, layout, group_id)
+
+    def _register_with_retry(self, tensors, layout, group_id: int, max_retries: int = 360, delay_s: float = 1.0) -> None:
+        """The transfer manager of a node other than the leader's may come up after this rank: keep trying for
+        about six minutes (flexkv/integration/sglang/connector.py:1926-1950)."""
+        import time
+        from ...common.debug import flexkv_logger
+        for attempt in range(max_retries):
+            try:
+                self._client.register_to_server(tensors, layout, group_id=group_id)
+                return
+            except Exception as e:  # noqa: BLE001
+                if attempt == max_retries - 1:
+                    raise
+                if attempt % 30 == 0:
+                    flexkv_logger.info("GPU registration retry %d/%d (tp %d pp %d): %s", attempt + 1, max_retries,
+                                       self.tp_rank, self.pp_rank, e)
+                time.sleep(delay_s)
+
+    def _group_hands_off(self) -> bool:
+        if self.any_hand_off is None:
+            self.any_hand_off = bool(self.comm.all_reduce_min(0 if self.hand_off_slot_mapping else 1) == 0)
+        return self.any_hand_off
+
+    def _hand_off(self, task_id: Optional[int], slot_mapping: Any, n_tokens: Optional[int] = None, mask=None) -> None:
+        if not self.hand_off_slot_mapping or self._client is None or task_id is None:
+            return
+        sm = torch.as_tensor(slot_mapping).cpu().numpy().astype(np.int64)
+        if n_tokens is not None:
+            sm = sm[:n_tokens]
+        if mask is not None:
+            sm = sm[np.asarray(mask, dtype=bool)]
+        self._client.set_slot_mapping(int(task_id), sm)
 
     @staticmethod
     def configure_for_pool(flexkv_config: FlexKVConfig, kvcache: Any, page_size: int,
@@ -209,6 +247,15 @@ class FlexKVConnector:
         """Blocking load of the matched tokens into the pages named by `slot_mapping`
         (one entry per matched token). Returns the number of tokens restored."""
         done = 0
+        if self._group_hands_off():
+            # every rank learns the task before the leader launches it, so the other nodes can name their pages
+            plan = None
+            if self.is_leader:
+                pl = self._pending_loads.get(rid)
+                plan = (pl.task_id, pl.matched_tokens) if pl is not None else None
+            plan = self.comm.broadcast(plan)
+            if plan is not None:
+                self._hand_off(plan[0], slot_mapping, n_tokens=plan[1])
         if self.is_leader:
             p = self._pending_loads.pop(rid, None)
             if p is not None:
@@ -259,6 +306,7 @@ class FlexKVConnector:
                  namespace: Optional[List[str]] = None) -> int:
         """Asynchronous offload of the request's full pages; returns the tokens that will move."""
         moved = 0
+        plan = None
         if self.is_leader:
             tok = np.asarray(token_ids, dtype=np.int64)
             aligned = (len(tok) // self.T) * self.T
@@ -271,7 +319,12 @@ class FlexKVConnector:
                 else:
                     self.mgr.launch(tid, sm[mask], swa_slot_mappings=self._window_page(sm))
                     self._stores[rid] = tid
+                    plan = (tid, aligned, np.asarray(mask, dtype=bool))
                 self.stats.record_put(aligned, moved)
+        if self._group_hands_off():
+            plan = self.comm.broadcast(plan)
+            if plan is not None:      # the other nodes' graphs wait for their pages; the order does not matter
+                self._hand_off(plan[0], slot_mapping, n_tokens=plan[1], mask=plan[2])
         return int(self.comm.broadcast(moved))
 
     def check_completed_stores(self) -> List[str]:

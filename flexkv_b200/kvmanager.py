@@ -33,7 +33,7 @@ class KVManager:
     def __init__(self, model_config: ModelConfig, cache_config: CacheConfig, dp_client_id: int = 0,
                  server_recv_port: Optional[str] = None, gpu_register_port: Optional[str] = None,
                  require_gpu: Optional[bool] = None, in_process: Optional[bool] = None,
-                 remote_transfer_endpoints: Optional[Sequence[Tuple[str, str, str]]] = None,
+                 remote_transfer_endpoints: Optional[Sequence[tuple]] = None,
                  transfer_manager_mode: Optional[str] = None) -> None:
         env = GLOBAL_CONFIG_FROM_ENV
         self.model_config = model_config
@@ -87,9 +87,11 @@ class KVManager:
             handles = [self.transfer_manager]
             # other nodes of a TP/PP group: one handle per (command, result, query) endpoint triple; a graph
             # is finished when every node reported it
-            for cmd, res, qry in (remote_transfer_endpoints or []):
+            # a fourth element True: that node numbers its GPU pages itself and sends them per task
+            # (KVTPClient.set_slot_mapping on its ranks); graphs go there with their GPU side unbound
+            for cmd, res, qry, *more in (remote_transfer_endpoints or []):
                 from .transfer_manager import TransferManagerMultiNodeHandle
-                handles.append(TransferManagerMultiNodeHandle(cmd, res, qry))
+                handles.append(TransferManagerMultiNodeHandle(cmd, res, qry, rebind_gpu_blocks=bool(more and more[0])))
             self.kv_task_engine = KVTaskEngine(model_config, cache_config, transfer_handles=handles)
             if env.enable_metrics:
                 from .metrics.collector import get_collector

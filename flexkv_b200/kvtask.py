@@ -175,6 +175,7 @@ class KVTaskEngine:
             handle.complete()
         elif graph.gpu_bound:
             task.status = TaskStatus.READY
+        graph.task_id = tid         # the name other nodes of the group know the task by (slot-mapping hand-off)
         with self._lock:
             self.tasks[tid] = task
             self.graph_to_task[graph.graph_id] = tid
@@ -309,6 +310,7 @@ class KVTaskEngine:
                 t.parent = bid
                 t.status = TaskStatus.RUNNING
                 self.graph_to_task.pop(t.graph.graph_id, None)
+            merged.task_id = bid
             self.tasks[bid] = batch
             self.graph_to_task[merged.graph_id] = bid
         self._launch([batch])

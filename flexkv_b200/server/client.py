@@ -158,6 +158,14 @@ class KVTPClient:
         flexkv_logger.info("sent GPU registration: dp %d rank %d, %d tensors", self.dp_client_id,
                            self.intra_client_id, len(kv_caches))
 
+    def set_slot_mapping(self, task_id: int, slot_mapping) -> None:
+        """Tells the data plane of THIS node which GPU pages this node's ranks use for ``task_id`` (a task
+        planned on the master node of a group that spans nodes; the graph waits there for this message)."""
+        import numpy as np
+        req = R.SlotMappingRequest(int(task_id), np.ascontiguousarray(np.asarray(slot_mapping), dtype=np.int64),
+                                   self.dp_client_id)
+        self._sock.send(pickle.dumps(req, protocol=pickle.HIGHEST_PROTOCOL))
+
     def register_swa_to_server(self, page_tensors: Sequence[torch.Tensor], group_id: int = 0,
                                mode: Optional[str] = None) -> None:
         """Sliding-window pages of this rank (one ``[num_pages, ...]`` tensor per window layer); ``group_id``

@@ -11,7 +11,7 @@ import zmq
 
 from ..common.debug import flexkv_logger
 from ..storage.gpu_layout import GpuRegistration, describe_gpu_tensors
-from .request import GpuControlRequest, RegisterTPClientRequest
+from .request import GpuControlRequest, RegisterTPClientRequest, SlotMappingRequest
 from .utils import get_zmq_socket
 
 
@@ -37,10 +37,12 @@ def registration_from_request(req: RegisterTPClientRequest) -> GpuRegistration:
 
 class RegistrationListener:
     def __init__(self, endpoint: str, on_register: Callable[[GpuRegistration], None],
-                 on_control: Optional[Callable[[GpuControlRequest], bool]] = None) -> None:
+                 on_control: Optional[Callable[[GpuControlRequest], bool]] = None,
+                 on_slot_mapping: Optional[Callable[[SlotMappingRequest], None]] = None) -> None:
         self.endpoint = endpoint
         self.on_register = on_register
         self.on_control = on_control
+        self.on_slot_mapping = on_slot_mapping
         self._ctx = zmq.Context.instance()
         self._sock = get_zmq_socket(self._ctx, zmq.PULL, endpoint, bind=True)
         self._stop = threading.Event()
@@ -64,6 +66,9 @@ class RegistrationListener:
                     self.count += 1
                     flexkv_logger.info("registered GPU tensors of dp client %d rank %d (device %d)",
                                        req.dp_client_id, req.intra_client_id, req.device_id)
+                elif isinstance(req, SlotMappingRequest):
+                    if self.on_slot_mapping is not None:
+                        self.on_slot_mapping(req)
                 elif isinstance(req, GpuControlRequest):
                     ok = False
                     try:

@@ -38,6 +38,16 @@ class RegisterTPClientRequest:
 
 
 @dataclass
+class SlotMappingRequest:
+    """The GPU pages one node's ranks allocated for a task whose graph arrives from the master node with its GPU
+    side unbound: each node of a group that spans nodes has its own block numbering
+    (flexkv/server/client.py:308-334 ``set_slot_mapping``, flexkv/kvtask.py:438-444)."""
+    task_id: int
+    slot_mapping: Any                  # int64 numpy array, one slot per token
+    dp_client_id: int = 0
+
+
+@dataclass
 class GpuControlRequest:
     """Sleep / wake of one engine worker's GPU memory, sent on the registration channel
     (the reference uses a dedicated REP socket: flexkv/transfer_manager.py:167-245).

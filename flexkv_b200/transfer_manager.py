@@ -47,6 +47,10 @@ class TransferManager:
         self._listener = None
         self._metrics = None
         self._stop = False
+        # graphs that arrived with their GPU side unbound, and page lists that arrived before their graph
+        self._bind_lock = threading.Lock()
+        self._await_pages: dict = {}        # task id -> [graphs]
+        self._early_pages: dict = {}        # task id -> slot mapping
 
     # ---- registration -----------------------------------------------------------
     def register_gpu(self, reg: GpuRegistration) -> None:
@@ -96,7 +100,8 @@ class TransferManager:
             return
         if self.gpu_register_port:
             from .server.registration import RegistrationListener
-            self._listener = RegistrationListener(self.gpu_register_port, self.register_gpu, self._on_gpu_control)
+            self._listener = RegistrationListener(self.gpu_register_port, self.register_gpu, self._on_gpu_control,
+                                                  lambda req: self.set_slot_mapping(req.task_id, req.slot_mapping))
             self._listener.start()
         self._init_thread = threading.Thread(target=self._init, name="flexkv-tm-init", daemon=True)
         self._init_thread.start()
@@ -201,11 +206,45 @@ class TransferManager:
         self.submit_batch([graph])
 
     def submit_batch(self, graphs: List[TransferOpGraph]) -> None:
+        ready_graphs = []
+        for g in graphs:
+            tid = getattr(g, "bind_task_id", None)
+            if tid is None or g.gpu_bound:
+                ready_graphs.append(g)
+                continue
+            # planned on another node: the GPU side is bound from this node's own page list
+            with self._bind_lock:
+                pages = self._early_pages.pop(tid, None)
+                if pages is None:
+                    self._await_pages.setdefault(tid, []).append(g)
+                    continue
+            self._bind(g, pages)
+            ready_graphs.append(g)
+        graphs = ready_graphs
+        if not graphs:
+            return
         with self._early_lock:
             if not self._ready.is_set():
                 self._early.extend(graphs)
                 return
         self.engine.submit_batch(graphs)
+
+    def _bind(self, graph: TransferOpGraph, slot_mapping) -> None:
+        import numpy as np
+        T = int(self.cache_config.tokens_per_block)
+        sm = np.asarray(slot_mapping, dtype=np.int64)
+        graph.set_gpu_blocks(sm[::T] // T)
+
+    def set_slot_mapping(self, task_id: int, slot_mapping) -> None:
+        """This node's GPU pages for a task planned elsewhere; releases the graphs that waited for them."""
+        with self._bind_lock:
+            held = self._await_pages.pop(task_id, None)
+            if held is None:
+                self._early_pages[task_id] = slot_mapping
+                return
+        for g in held:
+            self._bind(g, slot_mapping)
+        self.submit_batch(held)
 
     def wait(self, timeout: Optional[float] = None) -> List[CompletedOp]:
         if not self._ready.is_set():
@@ -329,8 +368,12 @@ class TransferManagerMultiNodeHandle:
     TransferManager, so the task layer counts it as one more handle whose completions
     must arrive before a graph is finished (flexkv/transfer_manager.py:1279-1468)."""
 
-    def __init__(self, command_endpoint: str, result_endpoint: str, query_endpoint: str) -> None:
+    def __init__(self, command_endpoint: str, result_endpoint: str, query_endpoint: str,
+                 rebind_gpu_blocks: bool = False) -> None:
         import zmq
+        # rebind_gpu_blocks: the other node numbers its GPU pages itself; graphs go there with their GPU side
+        # cleared and wait for that node's ranks to send the page list of the task (KVTPClient.set_slot_mapping)
+        self.rebind_gpu_blocks = rebind_gpu_blocks
         self._ctx = zmq.Context.instance()
         self._cmd = self._ctx.socket(zmq.PUSH)
         self._cmd.setsockopt(zmq.LINGER, 0)
@@ -368,6 +411,15 @@ class TransferManagerMultiNodeHandle:
 
     def submit_batch(self, graphs: List[TransferOpGraph]) -> None:
         import pickle
+        if self.rebind_gpu_blocks:
+            out = []
+            for g in graphs:
+                c = pickle.loads(pickle.dumps(g))          # this node's own graph keeps its binding
+                if getattr(c, "task_id", None) is not None:
+                    c.clear_gpu_blocks(force=True)
+                    c.bind_task_id = c.task_id
+                out.append(c)
+            graphs = out
         with self._lock:
             self._cmd.send(pickle.dumps(("submit", graphs)))
 
