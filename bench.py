@@ -469,7 +469,10 @@ def main() -> None:
         barrier()
         # restore + NVSwitch broadcast in one kernel (multimem.st), every rank checks every byte
         verified[f"nvls_fanout_{world}_ranks"] = selfcheck.nvls_fanout_all_ranks(dev, rank, world)
-        if verified[f"nvls_fanout_{world}_ranks"] is False and rank == 0:
+        # the same with a cache of deployment size: 61 layers, 4.6 GB per rank, three symmetric segments
+        verified[f"nvls_fanout_{world}_ranks_4p6GB"] = selfcheck.nvls_fanout_all_ranks(dev, rank, world, large=True)
+        if rank == 0 and (verified[f"nvls_fanout_{world}_ranks"] is False or
+                          verified[f"nvls_fanout_{world}_ranks_4p6GB"] is False):
             verified["nvls_fanout_error"] = selfcheck.last_failure
 
     if rank == 0:

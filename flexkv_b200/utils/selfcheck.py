@@ -200,22 +200,25 @@ def layerwise_two_ranks(devices=(0, 1)) -> bool:
     return bool(ok)
 
 
-def nvls_fanout_all_ranks(device: torch.device, rank: int, world: int, group=None):
+def nvls_fanout_all_ranks(device: torch.device, rank: int, world: int, group=None, large: bool = False):
     """Collective over the ranks of an initialised NCCL group (one process per GPU): rank 0 reads host
     blocks once and `multimem.st` replicates them into every rank's symmetric MLA cache, laid out in two
     symmetric segments; every rank compares every byte. Returns True / False, or the string
     "skipped: ..." when the fabric offers no multicast. Every rank walks the same sequence of collectives
-    whatever it finds, and nothing here waits on a peer from inside a kernel."""
+    whatever it finds, and nothing here waits on a peer from inside a kernel. ``large``: a DeepSeek-V3-sized
+    cache (61 layers, 4.6 GB per rank, three symmetric segments) instead of the 19 MB one, so that the
+    multicast mappings are exercised at the size a deployment has."""
     import torch.distributed as dist
     from ..common.storage import KVCacheLayout, KVCacheLayoutType
     from ..ops.kv_copy import HostSide, decode_status, new_status
     from ..parallel.nvls import alloc_symmetric_kv_layers, fanout_restore, wait_flag
-    L, N, T, D, n = 4, 64, 64, 576, 24
+    L, N, T, D, n = (61, 1024, 64, 576, 128) if large else (4, 64, 64, 576, 24)
     per_layer = N * T * D * 2
+    seg_bytes = (2 << 30) if large else 2 * per_layer
     have = torch.ones(1, device=device)
     sym = None
     try:
-        sym = alloc_symmetric_kv_layers(L, per_layer, device, group, segment_bytes=2 * per_layer)
+        sym = alloc_symmetric_kv_layers(L, per_layer, device, group, segment_bytes=seg_bytes)
     except Exception as e:  # noqa: BLE001 - no multicast, or an older torch
         have.zero_()
         why = f"{type(e).__name__}: {e}"[:120]
@@ -228,14 +231,16 @@ def nvls_fanout_all_ranks(device: torch.device, rank: int, world: int, group=Non
         reg = register_tensors(kv, KVCacheLayout(KVCacheLayoutType.LAYERFIRST, L, N, T, 1, D, is_mla=True))
         chunk = reg.chunk_bytes
         g = torch.Generator().manual_seed(5)            # the same host bytes on every rank, to compare against
-        pool = torch.randint(0, 256, (N, L, 1, chunk), dtype=torch.uint8, generator=g).pin_memory()
-        host = HostSide(pool.data_ptr(), chunk, chunk, L * chunk, N)
+        NH = n if large else N                          # host blocks
+        pool = torch.randint(0, 256, (NH, L, 1, chunk), dtype=torch.uint8, generator=g)
+        pool = pool.pin_memory() if rank == 0 else pool  # only the reader's copy is touched by a GPU
+        host = HostSide(pool.data_ptr(), chunk, chunk, L * chunk, NH)
         rng = np.random.default_rng(1)
         gpu_blocks = rng.permutation(N)[:n].astype(np.int64)
-        cpu_blocks = rng.permutation(N)[:n].astype(np.int64)
+        cpu_blocks = rng.permutation(NH)[:n].astype(np.int64)
         status = new_status(device)
         scratch = torch.zeros(1, dtype=torch.int32, device=device)
-        for epoch in (1, 2):
+        for epoch in ((1,) if large else (1, 2)):
             for t in kv:
                 t.zero_()
             torch.cuda.synchronize(device)
@@ -248,14 +253,19 @@ def nvls_fanout_all_ranks(device: torch.device, rank: int, world: int, group=Non
             ok = wait_flag(sym, epoch, timeout_s=10.0) and ok
             torch.cuda.synchronize(device)
             gi = torch.from_numpy(gpu_blocks).to(device)
+            bad_layers = []
             for l in range(L):
                 got = kv[l][gi].contiguous().view(torch.uint8).reshape(n, -1).cpu()
-                ok = ok and torch.equal(got, pool[torch.from_numpy(cpu_blocks), l, 0])
+                if not torch.equal(got, pool[torch.from_numpy(cpu_blocks), l, 0]):
+                    bad_layers.append(l)
+            if bad_layers:
+                global last_failure
+                last_failure = f"nvls fan-out: rank {rank} layers differ: {bad_layers[:8]} ({len(bad_layers)} of {L})"
+                ok = False
             untouched = torch.from_numpy(np.setdiff1d(np.arange(N), gpu_blocks)).to(device)
             ok = ok and int(kv[0][untouched].view(torch.int16).count_nonzero()) == 0
             dist.barrier(group=group)
     except Exception as e:  # noqa: BLE001
-        global last_failure
         last_failure = f"nvls fan-out: {type(e).__name__}: {e}"[:200]
         ok = False
     flag = torch.tensor([1.0 if ok else 0.0], device=device)
