@@ -57,6 +57,9 @@ def parse_args():
     ap.add_argument("--skip-raw", action="store_true", help="do not repeat the run with host_codec none")
     ap.add_argument("--skip-ceiling", action="store_true", help="do not measure the cudaMemcpyAsync ceiling")
     ap.add_argument("--skip-verify", action="store_true", help="do not run the byte checks after the timed region")
+    ap.add_argument("--shared-index", action="store_true",
+                    help="also run the end-to-end flow with ONE KVServer (hosted by rank 0: one index, one host pool, "
+                         "the data plane of every GPU) and one KVDPClient per rank, the dp_size > 1 deployment")
     ap.add_argument("--codec", default="bf16_xp", choices=["none", "bf16_xp", "fp8_e4m3"],
                     help="host-tier codec: bf16_xp (default) = lossless exponent packing fused into the copy, every "
                          "restored bit is identical; none = raw bytes; fp8_e4m3 = lossy block-scaled fp8 (a "
@@ -212,6 +215,42 @@ def main() -> None:
     vocab = 128256
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
 
+    def one_step(mgr, step_seed: int) -> int:
+        """One step through the public API: 32 puts as one batch, then 32 gets of the same tokens as one batch."""
+        r = np.random.default_rng(step_seed)
+        toks = [r.integers(0, vocab, size=args.tokens, dtype=np.int64) for _ in range(args.requests)]
+        g = r.permutation(args.gpu_blocks)[:blocks_per_batch].astype(np.int64)
+        slots = [selfcheck.slots_of(g[i * blocks_per_req:(i + 1) * blocks_per_req], T)
+                 for i in range(args.requests)]
+        ids, moved = [], 0
+        for t in toks:
+            tid, mask = mgr.put_match(t)
+            ids.append(tid)
+        bid = mgr.launch(ids, slots, as_batch=True)
+        res = mgr.wait(bid, timeout=600, completely=True)
+        for rsp in res.values():
+            if rsp.status.value != "success":
+                raise RuntimeError(f"put failed: {rsp.status}")
+            moved += int(sum(m.sum() for m in rsp.return_mask)) if isinstance(rsp.return_mask, list) \
+                else int(rsp.return_mask.sum())
+        g2 = r.permutation(args.gpu_blocks)[:blocks_per_batch].astype(np.int64)
+        slots2 = [selfcheck.slots_of(g2[i * blocks_per_req:(i + 1) * blocks_per_req], T)
+                  for i in range(args.requests)]
+        ids = []
+        for t in toks:
+            tid, mask = mgr.get_match(t)
+            if int(mask.sum()) != args.tokens:
+                raise RuntimeError("get_match did not find the batch that was just put")
+            ids.append(tid)
+        bid = mgr.launch(ids, slots2, as_batch=True)
+        res = mgr.wait(bid, timeout=600)
+        for rsp in res.values():
+            if rsp.status.value != "success":
+                raise RuntimeError(f"get failed: {rsp.status}")
+            moved += int(sum(m.sum() for m in rsp.return_mask)) if isinstance(rsp.return_mask, list) \
+                else int(rsp.return_mask.sum())
+        return moved
+
     def measure(codec: str, with_duplex: bool) -> dict:
         """One manager with the given host codec: the data plane alone (device-timed), the same bytes
         through the public API, the p50 latency of an 8K-token get, and a byte check of a round trip."""
@@ -276,48 +315,13 @@ def main() -> None:
 
         # -------------------------------------------------------------- public API, end to end
         if not args.skip_e2e and args.impl == "ours":
-            def one_step(step_seed: int) -> int:
-                r = np.random.default_rng(step_seed)
-                toks = [r.integers(0, vocab, size=args.tokens, dtype=np.int64) for _ in range(args.requests)]
-                g = r.permutation(args.gpu_blocks)[:blocks_per_batch].astype(np.int64)
-                slots = [selfcheck.slots_of(g[i * blocks_per_req:(i + 1) * blocks_per_req], T)
-                         for i in range(args.requests)]
-                ids, moved = [], 0
-                for t in toks:
-                    tid, mask = mgr.put_match(t)
-                    ids.append(tid)
-                bid = mgr.launch(ids, slots, as_batch=True)
-                res = mgr.wait(bid, timeout=600, completely=True)
-                for rsp in res.values():
-                    if rsp.status.value != "success":
-                        raise RuntimeError(f"put failed: {rsp.status}")
-                    moved += int(sum(m.sum() for m in rsp.return_mask)) if isinstance(rsp.return_mask, list) \
-                        else int(rsp.return_mask.sum())
-                g2 = r.permutation(args.gpu_blocks)[:blocks_per_batch].astype(np.int64)
-                slots2 = [selfcheck.slots_of(g2[i * blocks_per_req:(i + 1) * blocks_per_req], T)
-                          for i in range(args.requests)]
-                ids = []
-                for t in toks:
-                    tid, mask = mgr.get_match(t)
-                    if int(mask.sum()) != args.tokens:
-                        raise RuntimeError("get_match did not find the batch that was just put")
-                    ids.append(tid)
-                bid = mgr.launch(ids, slots2, as_batch=True)
-                res = mgr.wait(bid, timeout=600)
-                for rsp in res.values():
-                    if rsp.status.value != "success":
-                        raise RuntimeError(f"get failed: {rsp.status}")
-                    moved += int(sum(m.sum() for m in rsp.return_mask)) if isinstance(rsp.return_mask, list) \
-                        else int(rsp.return_mask.sum())
-                return moved
-
             for w in range(args.warmup):
-                one_step(10_000 * (rank + 1) + w)
+                one_step(mgr, 10_000 * (rank + 1) + w)
             barrier()
             t0 = time.perf_counter()
             moved = 0
             for s in range(args.steps):
-                moved += one_step(20_000 * (rank + 1) + s)
+                moved += one_step(mgr, 20_000 * (rank + 1) + s)
             barrier()
             wall_ms = max_over_ranks((time.perf_counter() - t0) * 1e3)
             e2e_val = moved * shape.bytes_per_token * world / (wall_ms * 1e-3) / 1e9
@@ -422,6 +426,70 @@ def main() -> None:
     if args.codec != "none" and not args.skip_raw and args.impl == "ours":
         raw_res = measure("none", False)
 
+    # ------------------------------------------------------------------ one server, one index, N clients
+    shared = None
+    if args.shared_index and args.impl == "ours":
+        from flexkv_b200 import KVTPClient
+        host_group = dist.new_group(backend="gloo") if world > 1 else None
+
+        def host_barrier():
+            # ranks wait on the host: rank 0's process runs every GPU's transfers, a device barrier would sit on them
+            if host_group is not None:
+                dist.barrier(group=host_group)
+
+        tag = os.environ.get("MASTER_PORT", str(os.getpid()))
+        ep, reg = f"ipc:///tmp/flexkv_b200_bench_{tag}_srv.sock", f"ipc:///tmp/flexkv_b200_bench_{tag}_reg.sock"
+        # the pool of all ranks in one process; room for every rank's batch and a quarter more
+        shared_blocks = min(num_cpu_blocks * world, world * (blocks_per_batch + blocks_per_batch // 4))
+        cache_cfg = CacheConfig(tokens_per_block=T, num_cpu_blocks=shared_blocks, enable_ssd=False,
+                                enable_compression=args.codec == "bf16_xp",
+                                offload_quant="fp8_e4m3" if args.codec == "fp8_e4m3" else "none")
+        model_dp = make_model_config(shape, dp_size=world)
+        t_setup = time.perf_counter()
+        mgr = None
+        if rank == 0:
+            mgr = KVManager(model_dp, cache_cfg, dp_client_id=0, server_recv_port=ep, gpu_register_port=reg,
+                            in_process=False)
+        host_barrier()
+        if rank != 0:
+            mgr = KVManager(model_dp, cache_cfg, dp_client_id=rank, server_recv_port=ep, gpu_register_port=reg,
+                            in_process=False)
+        tp_client = KVTPClient(reg, dp_client_id=rank, device_id=local_rank)
+        tp_client.register_to_server(kv, layout)
+        mgr.start()
+        mgr.wait_ready(timeout=1800)
+        setup_s = time.perf_counter() - t_setup
+        for w in range(args.warmup):
+            one_step(mgr, 30_000 * (rank + 1) + w)
+        torch.cuda.synchronize()
+        host_barrier()
+        t0 = time.perf_counter()
+        moved = 0
+        for s_ in range(args.steps):
+            moved += one_step(mgr, 40_000 * (rank + 1) + s_)
+        host_barrier()
+        wall_ms = (time.perf_counter() - t0) * 1e3
+        if world > 1:
+            t = torch.tensor([wall_ms], dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX, group=host_group)
+            wall_ms = float(t.item())
+        shared = {"what": "the e2e flow with one KVServer in rank 0's process (shared index, one host pool, every "
+                          "GPU's data plane) and one KVDPClient + KVTPClient per rank over ZeroMQ and CUDA IPC",
+                  "value": round(moved * shape.bytes_per_token * world / (wall_ms * 1e-3) / 1e9, 2), "unit": "GB/s",
+                  "ms_per_step": round(wall_ms / args.steps, 2), "setup_s": round(setup_s, 1),
+                  "host_pool_gib": round(shared_blocks * block_bytes / 2**30, 1),
+                  "over_private_managers_e2e": None if main_res["e2e"] is None else
+                  round(moved * shape.bytes_per_token * world / (wall_ms * 1e-3) / 1e9 / main_res["e2e"]["value"], 3)}
+        host_barrier()
+        if rank != 0:
+            mgr.shutdown()
+        tp_client.shutdown()
+        host_barrier()
+        if rank == 0:
+            mgr.shutdown()
+        del mgr
+        barrier()
+
     # ------------------------------------------------------------------ copy-engine ceiling, all ranks at once
     ceiling = None
     if not args.skip_ceiling:
@@ -492,7 +560,7 @@ def main() -> None:
                 "value": raw_res["value"], "put_gbs_per_gpu": raw_res["put_gbs_per_gpu"],
                 "get_gbs_per_gpu": raw_res["get_gbs_per_gpu"], "e2e": raw_res["e2e"],
                 "p50_get_latency_ms_8k_tokens": raw_res["p50"], "kernels": raw_res["kernels"]},
-            "ceiling": ceiling, "verified": verified,
+            "shared_index": shared, "ceiling": ceiling, "verified": verified,
             "gpu_launches": 2 * args.steps * world, "clocks": main_res["clocks"],
             "config": {"model": f"{shape.name} KV, vLLM paged layout", "global_batch": args.requests * world,
                        "seq_len": args.tokens, "parallelism": f"dp{world}", "gpu_blocks": args.gpu_blocks,

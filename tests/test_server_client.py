@@ -164,3 +164,46 @@ def test_external_server_process(tmp_path, monkeypatch):
             proc.kill()
             out, _ = proc.communicate()
     assert proc.returncode in (0, -15), out[-2000:]
+
+
+def test_batch_launch_over_the_server_returns_per_request_masks():
+    """The flow of the throughput benchmark in server-client mode: several matches, one batched
+    launch, one wait on the batch id whose response lists a mask per request."""
+    shape = KVShape("s", 2, 2, 16, tokens_per_block=4)
+    T = 4
+    model = make_model_config(shape, dp_size=2)
+    cache = CacheConfig(tokens_per_block=T, num_cpu_blocks=32)
+    ep, reg = unique_ipc_endpoint("srv"), unique_ipc_endpoint("reg")
+    m0 = KVManager(model, cache, dp_client_id=0, server_recv_port=ep, gpu_register_port=reg, require_gpu=True)
+    m1 = KVManager(model, cache, dp_client_id=1, server_recv_port=ep, gpu_register_port=reg)
+    caches = []
+    for d in range(2):
+        kv, layout = alloc_paged_cache(shape, 32, "cpu", "vllm", fill="normal", seed=90 + d)
+        KVTPClient(reg, dp_client_id=d, device_id=0, tp_rank=0).register_to_server(kv, layout, mode="same_process")
+        caches.append(kv)
+    m0.start(); m1.start()
+    try:
+        m0.wait_ready(30); m1.wait_ready(30)
+        rng = np.random.default_rng(3)
+        for d, m in enumerate((m0, m1)):
+            toks = [rng.integers(0, 1000, size=3 * T, dtype=np.int64) for _ in range(3)]
+            src = rng.permutation(32)[:9].reshape(3, 3)
+            ids = [m.put_match(t)[0] for t in toks]
+            bid = m.launch(ids, [slots(b, T) for b in src], as_batch=True)
+            res = m.wait(bid, timeout=30, completely=True)
+            assert [r.status.value for r in res.values()] == ["success"]
+            masks = next(iter(res.values())).return_mask
+            assert isinstance(masks, list) and [int(x.sum()) for x in masks] == [3 * T] * 3
+            dst = np.setdiff1d(np.arange(32), src.ravel())[:9].reshape(3, 3)
+            ids = []
+            for t in toks:
+                tid, mask = m.get_match(t)
+                assert int(mask.sum()) == 3 * T
+                ids.append(tid)
+            bid = m.launch(ids, [slots(b, T) for b in dst], as_batch=True)
+            res = m.wait(bid, timeout=30)
+            assert [r.status.value for r in res.values()] == ["success"]
+            for l in range(2):
+                assert torch.equal(caches[d][l][:, dst.ravel()], caches[d][l][:, src.ravel()])
+    finally:
+        m1.shutdown(); m0.shutdown()
