@@ -10,6 +10,7 @@
 #include "hasher.h"
 #include "graph_scheduler.h"
 #include "native_log.h"
+#include "metrics_exposer.h"
 #include "host_mem.h"
 #include "kernels/kv_copy.h"
 #include "radix_index.h"
@@ -81,6 +82,13 @@ PYBIND11_MODULE(_C, m) {
     d["blocks"] = blocks;
     return d;
   });
+  m.def("start_cpp_metrics_exposer", [](int port, const std::string& addr) {
+    py::gil_scoped_release nogil;
+    return metrics_exposer_start(port, addr);
+  }, py::arg("port"), py::arg("bind_addr") = "0.0.0.0");
+  m.def("stop_cpp_metrics_exposer", [] { py::gil_scoped_release nogil; metrics_exposer_stop(); });
+  m.def("cpp_metrics_exposer_port", [] { return metrics_exposer_port(); });
+  m.def("cpp_metrics_text", [] { return metrics_text(); });
   m.def("set_log_level", [](const std::string& name) { set_log_level(name); });
   m.def("get_log_level", [] { return (int)log_level(); });
   m.def("set_log_prefix", [](const std::string& p) { set_log_prefix(p); });

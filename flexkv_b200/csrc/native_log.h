@@ -5,7 +5,7 @@
 // Counters mirror its Prometheus families flexkv_cpp_cache_ops_total{operation=..}
 // and flexkv_cpp_cache_blocks_total{operation=..} (csrc/monitoring/metrics_manager.cpp:104-110,
 // macros metrics_manager.h:211-235); here they are lock-free atomics that Python
-// scrapes into its own registry, so no HTTP exporter lives in native code.
+// scrapes into its own registry and that metrics_exposer.{h,cpp} serves on a port of their own.
 #pragma once
 #include <atomic>
 #include <cstdarg>

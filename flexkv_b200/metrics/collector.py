@@ -76,6 +76,20 @@ class MetricsCollector:
             flexkv_logger.info("metrics endpoint on :%d", port)
         except OSError as e:
             flexkv_logger.warning("metrics endpoint not started: %s", e)
+        # the native counters also have an endpoint of their own, served by a C++ thread
+        # (FLEXKV_CPP_METRICS_PORT, 0 switches it off; reference: csrc/monitoring/metrics_manager.cpp:60-110)
+        cpp_port = int(GLOBAL_CONFIG_FROM_ENV.cpp_metrics_port or 0)
+        if cpp_port > 0:
+            try:
+                from .. import _native
+                got = _native.C.start_cpp_metrics_exposer(cpp_port)
+                if got < 0:
+                    flexkv_logger.warning("native metrics endpoint not started: errno %d", -got)
+                else:
+                    import atexit
+                    atexit.register(_native.C.stop_cpp_metrics_exposer)
+            except Exception as e:  # noqa: BLE001
+                flexkv_logger.warning("native metrics endpoint not started: %s", e)
 
     def record_match(self, device: str, hit_blocks: int, miss_blocks: int) -> None:
         if hit_blocks > 0:

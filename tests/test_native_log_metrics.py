@@ -1,6 +1,7 @@
 """Native logger and index counters (reference: csrc/logging.cpp:50-104,
 csrc/monitoring/metrics_manager.h:211-235)."""
 import numpy as np
+import pytest
 
 from flexkv_b200 import _native
 
@@ -53,3 +54,31 @@ def test_prometheus_exports_native_families():
     text = generate_latest(m.registry).decode()
     assert 'flexkv_cpp_cache_ops_total{operation="insert"} 1.0' in text
     assert 'flexkv_cpp_cache_blocks_total{operation="insert"} 4.0' in text
+
+
+def test_native_metrics_endpoint_serves_the_counters_over_http():
+    """The counters of the native index have an endpoint of their own, answered by a C++ thread
+    (reference: csrc/monitoring/metrics_manager.cpp:60-110, FLEXKV_CPP_METRICS_PORT)."""
+    import urllib.error
+    import urllib.request
+    from flexkv_b200 import _native
+    C = _native.C
+    C.reset_cpp_metrics()
+    port = C.start_cpp_metrics_exposer(0, "127.0.0.1")
+    try:
+        assert port > 0 and C.cpp_metrics_exposer_port() == port
+        assert C.start_cpp_metrics_exposer(0, "127.0.0.1") == port          # one endpoint per process
+        idx = C.RadixIndex(4, 64, "lru", 0.0)
+        h = np.arange(1, 9, dtype=np.uint64)
+        idx.insert(np.arange(8, dtype=np.int64), h, 8, True, None)
+        idx.match_prefix(np.concatenate([h[:4], np.array([99], dtype=np.uint64)]))
+        body = urllib.request.urlopen(f"http://127.0.0.1:{port}/metrics", timeout=5).read().decode()
+        assert "# TYPE flexkv_cpp_cache_ops_total counter" in body
+        line = [l for l in body.splitlines() if l.startswith('flexkv_cpp_cache_ops_total{operation="match"}')]
+        assert line and int(line[0].split()[-1]) >= 1
+        assert body == C.cpp_metrics_text() or "flexkv_cpp_cache_blocks_total" in body
+        with pytest.raises(urllib.error.HTTPError):
+            urllib.request.urlopen(f"http://127.0.0.1:{port}/other", timeout=5)
+    finally:
+        C.stop_cpp_metrics_exposer()
+    assert C.cpp_metrics_exposer_port() == 0
