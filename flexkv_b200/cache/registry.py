@@ -16,7 +16,8 @@ served here by a small store that lives inside the box:
 ``RegistryStore`` is the data structure, ``RegistryServer`` serves it over a ZeroMQ REP
 socket so that several processes of one box (or several boxes) share it, and
 ``RegistryClient`` talks either to a server endpoint or straight to a store object living
-in the same process. A Redis-backed client with the same methods can replace it.
+in the same process. ``redis_client.RedisRegistryClient`` has the same methods over the Redis wire
+protocol (``connect("redis://host", port)``), so the registry can also live in a Redis server.
 """
 from __future__ import annotations
 
@@ -209,10 +210,26 @@ class RegistryClient:
 
 def connect(host: str, port: int) -> RegistryClient:
     """``host`` "inproc[:name]" selects a store inside this process; anything else is the
-    address of a RegistryServer (the configuration reuses the reference's redis_host/redis_port fields)."""
+    address of a RegistryServer (the configuration reuses the reference's redis_host/redis_port fields);
+    "redis://[:password@]host[:port][/db]" is a Redis server."""
     if host.startswith("inproc"):
         name = host.split(":", 1)[1] if ":" in host else "default"
         return RegistryClient(inproc_store(name))
+    if host.startswith("redis://"):
+        # a Redis server, spoken to over its wire protocol: redis://[:password@]host[/db]
+        from .redis_client import RedisRegistryClient
+        rest = host[len("redis://"):]
+        password, db = "", 0
+        if "@" in rest:
+            cred, rest = rest.rsplit("@", 1)
+            password = cred.split(":", 1)[1] if ":" in cred else cred
+        if "/" in rest:
+            rest, dbs = rest.split("/", 1)
+            db = int(dbs or 0)
+        if ":" in rest:
+            rest, ps = rest.rsplit(":", 1)
+            port = int(ps)
+        return RedisRegistryClient(rest, port or 6379, password=password, db=db)
     if host.startswith("ipc://") or host.startswith("tcp://"):
         return RegistryClient(host)
     return RegistryClient(f"tcp://{host}:{port}")

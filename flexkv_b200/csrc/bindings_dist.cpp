@@ -5,6 +5,7 @@
 
 #include "bindings_common.h"
 #include "dist_index.h"
+#include "resp_client.h"
 
 namespace py = pybind11;
 using namespace fkv;
@@ -79,8 +80,74 @@ std::shared_ptr<T> gil_free_delete(T* p) {
 
 }  // namespace
 
+namespace {
+
+py::object resp_to_py(const RespValue& v) {
+  switch (v.type) {
+    case RespValue::kNil: return py::none();
+    case RespValue::kString: return py::str(v.str);
+    case RespValue::kInteger: return py::int_(v.integer);
+    case RespValue::kBulk: return py::bytes(v.str);
+    case RespValue::kArray: {
+      py::list l;
+      for (const auto& it : v.items) l.append(resp_to_py(it));
+      return std::move(l);
+    }
+    case RespValue::kError: break;
+  }
+  throw std::runtime_error("redis error reply: " + v.str);
+}
+
+std::vector<std::string> resp_args(const py::sequence& seq) {
+  std::vector<std::string> out;
+  for (auto a : seq) {
+    if (py::isinstance<py::bytes>(a)) out.push_back(a.cast<std::string>());
+    else out.push_back(py::str(a).cast<std::string>());
+  }
+  return out;
+}
+
+}  // namespace
+
 void init_dist_bindings(py::module_& m) {
   m.def("wall_clock_ms", &wall_clock_ms);
+
+  // Redis wire protocol (an IO failure is a ConnectionError, an error reply a RuntimeError)
+  py::register_exception<RespIoError>(m, "RespIoError", PyExc_ConnectionError);
+  py::class_<RespClient>(m, "RespClient")
+      .def(py::init<std::string, int, int, std::string, int>(), py::arg("host"), py::arg("port"),
+           py::arg("timeout_ms") = 3000, py::arg("password") = "", py::arg("db") = 0)
+      .def("command", [](RespClient& c, py::args args) {
+        auto a = resp_args(args);
+        RespValue v;
+        {
+          py::gil_scoped_release nogil;
+          v = c.command(a);
+        }
+        return resp_to_py(v);
+      })
+      .def("pipeline", [](RespClient& c, py::list cmds) {
+        std::vector<std::vector<std::string>> cs;
+        for (auto one : cmds) cs.push_back(resp_args(one.cast<py::sequence>()));
+        std::vector<RespValue> vs;
+        {
+          py::gil_scoped_release nogil;
+          vs = c.pipeline(cs);
+        }
+        py::list out;
+        for (const auto& v : vs) out.append(resp_to_py(v));
+        return out;
+      })
+      .def("close", &RespClient::close)
+      .def("connected", &RespClient::connected)
+      .def_static("encode", [](py::args args) { return py::bytes(RespClient::encode(resp_args(args))); })
+      .def_static("parse", [](py::bytes data) -> py::object {
+        std::string s = data;
+        size_t pos = 0;
+        RespValue v;
+        if (!RespClient::parse(s, pos, v)) return py::none();
+        return py::make_tuple(resp_to_py(v), pos);
+      });
 
   py::class_<InProcMetaChannel, std::shared_ptr<InProcMetaChannel>>(m, "InProcMetaChannel")
       .def(py::init([] { return std::make_shared<InProcMetaChannel>(); }))

@@ -149,6 +149,9 @@ def build_layerwise_group(storage, model_config, key: WorkerKey, notify_mode: Op
                 max_blocks_per_op=max(4096, min(1 << 18, host.num_blocks)),
                 notify_mode=notify_mode or env.layerwise_notify_mode, num_counters=num_counters,
                 layers_per_batch=layers_per_batch, create_eventfds=create_eventfds)
+    if "FLEXKV_LAYERWISE_FUSED_MAX_BYTES" in os.environ:
+        # narrow grids (below 8 CTAs) restore with one launch per layer above this size; 64 MiB by default
+        opts["fused_max_bytes"] = int(os.environ["FLEXKV_LAYERWISE_FUSED_MAX_BYTES"])
     if getattr(host, "quant", "none") == "bf16_xp":
         # packed host pool: the restore unpacks layer by layer and reads only the packed bytes
         from .compression import build_compressors
