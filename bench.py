@@ -542,6 +542,10 @@ def main() -> None:
         if rank == 0 and (verified[f"nvls_fanout_{world}_ranks"] is False or
                           verified[f"nvls_fanout_{world}_ranks_4p6GB"] is False):
             verified["nvls_fanout_error"] = selfcheck.last_failure
+        # the same kernel as a manager path: rank 0's KVManager restores a prefix into every rank's cache
+        verified[f"nvls_manager_restore_{world}_ranks"] = selfcheck.nvls_manager_restore_all_ranks(dev, rank, world)
+        if rank == 0 and verified[f"nvls_manager_restore_{world}_ranks"] is False:
+            verified["nvls_manager_restore_error"] = selfcheck.last_failure
 
     if rank == 0:
         out = {

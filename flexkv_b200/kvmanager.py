@@ -101,9 +101,16 @@ class KVManager:
 
     # ---- in-process registration (engine worker and manager share the process) --------------
     def register_gpu_tensors(self, tensors: Sequence[torch.Tensor], gpu_layout: KVCacheLayout, tp_rank: int = 0,
-                             pp_rank: int = 0, dp_client_id: Optional[int] = None, group_id: int = -1) -> None:
+                             pp_rank: int = 0, dp_client_id: Optional[int] = None, group_id: int = -1,
+                             multicast=None) -> None:
         """``group_id`` names the layer group of a multi-group cache (``ModelConfig.layer_groups``): call once
-        per group with that group's tensors and layout."""
+        per group with that group's tensors and layout.
+
+        ``multicast``: the ``parallel.nvls.SymmetricKVPool`` (or ``SymmetricKVBuffer``) the tensors were carved
+        from, when the ranks of a shared-KV (MLA) tensor-parallel group allocated their caches as symmetric
+        memory. This ONE registration, made by the rank that lives in the manager's process, then stands for the
+        whole group: a restore reads each host block once and `multimem.st` writes it into every rank's cache
+        (``NvlsFanoutWorker``); an offload reads this rank's copy."""
         if self.server_client_mode:
             raise RuntimeError("in server-client mode GPU tensors are registered through KVTPClient")
         if hasattr(self.transfer_manager, "register_gpu_tensors"):      # data plane in a child process
@@ -115,6 +122,13 @@ class KVManager:
         reg = register_tensors(tensors, gpu_layout, tp_rank=tp_rank, pp_rank=pp_rank,
                                dp_client_id=self.dp_client_id if dp_client_id is None else dp_client_id,
                                group_id=group_id)
+        if multicast is not None:
+            if hasattr(multicast, "mc_of"):
+                reg.mc_ptrs = [int(multicast.mc_of(int(p))) for p in reg.ptrs]
+            else:
+                reg.mc_ptrs = [int(p) + int(multicast.mc_delta) for p in reg.ptrs]
+            reg.mc_flag_ptr = int(multicast.flag_mc_ptr)
+            reg.keepalive = (reg.keepalive, multicast)
         self.transfer_manager.register_gpu(reg)
 
     def register_swa_tensors(self, tensors: Sequence[torch.Tensor], tp_rank: int = 0, pp_rank: int = 0,

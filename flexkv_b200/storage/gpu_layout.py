@@ -43,6 +43,11 @@ class GpuRegistration:
     group_id: int = -1              # layer group of a multi-group cache (-1: the only group)
     is_swa: bool = False            # sliding-window pages (group_id then names the window pool's group)
     layer_groups: Any = None        # LayerGroupSpec list sent along by a worker that discovered the groups itself
+    # NVSwitch multicast: mc_ptrs[i] is the multicast address of tensor ptrs[i] (one store there lands in every
+    # rank's copy of the tensor), mc_flag_ptr the multicast address of the ranks' completion flag. A registration
+    # that carries them stands for all ranks of its shared-KV tensor-parallel group.
+    mc_ptrs: Optional[List[int]] = None
+    mc_flag_ptr: int = 0
     keepalive: Any = field(default=None, repr=False)   # tensors or opened handles
 
     def as_native(self) -> Dict[str, Any]:

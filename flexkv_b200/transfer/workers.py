@@ -406,6 +406,74 @@ class QuantGpuHostWorker(TransferWorker):
                          error="" if status == 0 else f"quant kernel status 0x{status:x}")
 
 
+class NvlsFanoutWorker(TransferWorker):
+    """H2D for a shared-KV tensor-parallel group whose caches are symmetric memory: the issuing rank's kernel
+    reads each host block over PCIe once and `multimem.st` replicates it into every rank's cache through
+    NVSwitch, then raises the ranks' completion flag to the op's epoch (``last_epoch``). The reference reads the
+    same host bytes once per rank (csrc/layerwise.cpp:1142-1165, csrc/tp_transfer_thread_group.cpp:221-323).
+    The op completes after the issuing GPU has finished the launch; ranks in other processes may also wait on
+    the flag (``parallel.nvls.wait_flag``)."""
+
+    def __init__(self, storage, model_config: ModelConfig, key: WorkerKey) -> None:
+        super().__init__()
+        import torch
+        self._torch = torch
+        self.name = "h2d-nvls-fanout"
+        regs = storage.gpu_regs[key]
+        self.reg = regs[sorted(regs)[0]]
+        if len(self.reg.mc_ptrs) != len(self.reg.ptrs) or not self.reg.mc_flag_ptr:
+            raise ValueError("multicast registration needs one multicast address per tensor and a flag address")
+        host = storage.host
+        layer_stride, kv_stride = host.layer_stride, host.kv_stride     # shared KV: every rank reads whole chunks
+        if host.chunk_bytes != self.reg.chunk_bytes:
+            raise ValueError(f"host chunk {host.chunk_bytes} B does not match the GPU chunk {self.reg.chunk_bytes} B")
+        self.host = dict(base=host.base + storage.pp_stage_offset(key.pp_rank), layer_stride=layer_stride,
+                         kv_stride=kv_stride, block_stride=host.block_bytes, num_blocks=host.num_blocks)
+        env = GLOBAL_CONFIG_FROM_ENV
+        self.num_ctas = env.transfer_num_cta_h2d
+        self.tile_bytes = env.transfer_tile_bytes
+        dev = self.reg.device_id
+        self.stream = torch.cuda.Stream(device=dev)
+        self.status = torch.zeros(8, dtype=torch.int32, device=f"cuda:{dev}")
+        self.scratch = torch.zeros(1, dtype=torch.int32, device=f"cuda:{dev}")
+        self.last_epoch = 0
+        self.num_ranks = model_config.effective_tp_size_per_node
+
+    def execute(self, op: TransferOp) -> OpOutcome:
+        torch = self._torch
+        cpu, gpu = op.src_block_ids, op.dst_block_ids
+        if gpu.size != cpu.size:
+            return OpOutcome(False, error=f"unbound GPU blocks: {gpu.size} vs {cpu.size}")
+        reg, h = self.reg, self.host
+        g_ids = torch.from_numpy(np.ascontiguousarray(gpu, dtype=np.int64)).pin_memory()
+        c_ids = torch.from_numpy(np.ascontiguousarray(cpu, dtype=np.int64)).pin_memory()
+        nl = reg.num_layers - op.layer_start if op.num_layers < 0 else op.num_layers
+        self.last_epoch += 1
+        params = dict(gpu_ptrs=[int(p) for p in reg.ptrs], mc_ptrs=[int(p) for p in reg.mc_ptrs],
+                      idx_layer_mul=reg.idx_layer_mul, idx_kv_mul=reg.idx_kv_mul, g_layer_stride=reg.layer_stride,
+                      g_kv_stride=reg.kv_stride, g_block_stride=reg.block_stride, cpu_base=h["base"],
+                      c_layer_stride=h["layer_stride"], c_kv_stride=h["kv_stride"], c_block_stride=h["block_stride"],
+                      c_off=0, gpu_blocks_ptr=g_ids.data_ptr(), cpu_blocks_ptr=c_ids.data_ptr(),
+                      num_pairs=int(cpu.size), layer_start=op.layer_start, num_layers=nl, kv_dim=reg.kv_dim,
+                      chunk_bytes=reg.chunk_bytes, gpu_num_blocks=reg.num_blocks, cpu_num_blocks=h["num_blocks"],
+                      status_ptr=self.status.data_ptr(), h2d=1, done_counter_ptr=self.scratch.data_ptr(),
+                      epoch=self.last_epoch)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with torch.cuda.device(reg.device_id):
+            e0.record(self.stream)
+            _native.C.kv_fanout(params, 0, int(reg.mc_flag_ptr), self.num_ctas, self.tile_bytes,
+                                self.stream.cuda_stream)
+            e1.record(self.stream)
+        e1.synchronize()
+        words = self.status.tolist()
+        status = sum(1 << b for b, w in enumerate(words) if w)
+        if status:
+            self.status.zero_()
+        nbytes = int(cpu.size) * nl * reg.kv_dim * reg.chunk_bytes
+        return OpOutcome(status == 0, gpu_ms=e0.elapsed_time(e1), num_bytes=nbytes * self.num_ranks,
+                         error="" if status == 0 else f"fan-out kernel status 0x{status:x}")
+
+
 # ------------------------------------------------------------------ GPU <-> GPU (NVLink)
 
 class PeerD2DWorker(TransferWorker):
@@ -910,7 +978,10 @@ def build_workers(storage, model_config: ModelConfig, cache_config: CacheConfig
             continue
         per_rank_block = reg0.num_layers * reg0.kv_dim * reg0.chunk_bytes
         shared = model_config.use_mla or model_config.num_kv_heads == 1
-        for h2d in (True, False):
+        fanout = shared and len(regs) == 1 and getattr(reg0, "mc_ptrs", None)
+        if fanout:
+            workers[(key, TransferType.H2D)] = NvlsFanoutWorker(storage, model_config, key)
+        for h2d in ((False,) if fanout else (True, False)):
             # one native group (thread + stream per GPU) per direction: PCIe is full duplex, so an offload and a
             # restore that are in flight together must not queue behind each other on one stream
             group = build_transfer_group(storage, model_config, key)

@@ -94,6 +94,11 @@ class TransferManager:
         groups = len(m.layer_groups) if m.layer_groups else 1      # one registration per rank and layer group
         return m.total_clients * m.local_pp_stages * m.effective_tp_size_per_node * groups if self.require_gpu else 0
 
+    def _registrations_arrived(self) -> int:
+        """A registration with multicast addresses stands for every rank of its tensor-parallel group."""
+        per_group = self.model_config.effective_tp_size_per_node
+        return sum(per_group if getattr(r, "mc_ptrs", None) else 1 for r in self._pending_regs)
+
     # ---- lifecycle ----------------------------------------------------------------
     def start(self) -> None:
         if self._init_thread is not None:
@@ -112,13 +117,13 @@ class TransferManager:
             t0 = time.monotonic()
             warned = False
             with self._reg_cv:
-                while (len(self._pending_regs) < want or len(self._pending_swa) < want_swa) and not self._stop:
+                while (self._registrations_arrived() < want or len(self._pending_swa) < want_swa) and not self._stop:
                     self._reg_cv.wait(timeout=1.0)
                     want = self._expected_registrations()      # a registration may have brought the layer groups
                     if not warned and time.monotonic() - t0 > 60:
                         warned = True
                         flexkv_logger.warning("still waiting for GPU registrations: %d of %d arrived (window pages: "
-                                              "%d of %d)", len(self._pending_regs), want, len(self._pending_swa),
+                                              "%d of %d)", self._registrations_arrived(), want, len(self._pending_swa),
                                               want_swa)
             if self._stop:
                 return

@@ -20,6 +20,7 @@ import numpy as np
 import torch
 
 from .. import CacheConfig, KVManager, _native
+from ..common.transfer import TransferType, WorkerKey
 from ..models import KVShape, alloc_paged_cache, make_model_config
 from ..storage.gpu_layout import register_tensors
 
@@ -268,6 +269,85 @@ def nvls_fanout_all_ranks(device: torch.device, rank: int, world: int, group=Non
     except Exception as e:  # noqa: BLE001
         last_failure = f"nvls fan-out: {type(e).__name__}: {e}"[:200]
         ok = False
+    flag = torch.tensor([1.0 if ok else 0.0], device=device)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group)
+    torch.cuda.synchronize(device)
+    dist.barrier(group=group)
+    return bool(flag.item() >= 1.0)
+
+
+def nvls_manager_restore_all_ranks(device: torch.device, rank: int, world: int, group=None):
+    """Collective over the ranks of an initialised NCCL group: the fan-out as a MANAGER path. Every rank
+    carves an MLA cache out of a symmetric pool; rank 0 owns a KVManager for the tensor-parallel group,
+    registers its tensors with the pool's multicast mapping, offloads a prefix from its own cache and
+    restores it into other pages with ``get_match`` / ``launch`` / ``wait``: one PCIe read, every rank's
+    cache written. Every rank then waits (bounded, on the host) for its flag and compares bytes. Returns
+    True / False or "skipped: ..."; every rank walks the same collectives whatever it finds."""
+    import torch.distributed as dist
+    from ..common.storage import KVCacheLayout, KVCacheLayoutType
+    from ..parallel.nvls import alloc_symmetric_kv_layers, wait_flag
+    global last_failure
+    L, N, T, D, n = 4, 64, 64, 576, 6
+    per_layer = N * T * D * 2
+    have = torch.ones(1, device=device)
+    sym, why = None, ""
+    try:
+        sym = alloc_symmetric_kv_layers(L, per_layer, device, group, segment_bytes=2 * per_layer)
+    except Exception as e:  # noqa: BLE001 - no multicast, or an older torch
+        have.zero_()
+        why = f"{type(e).__name__}: {e}"[:120]
+    dist.all_reduce(have, op=dist.ReduceOp.MIN, group=group)
+    if float(have.item()) < 1.0:
+        return "skipped: " + (why if sym is None else "another rank has no multicast mapping")
+    ok, mgr = True, None
+    try:
+        kv = [sym.layer_tensor(l, (N, T, D), torch.bfloat16) for l in range(L)]
+        g = torch.Generator().manual_seed(11)
+        want = torch.randn(L, n, T, D, generator=g).to(torch.bfloat16)       # the same on every rank
+        src = np.array([3, 40, 11, 7, 25, 60], dtype=np.int64)
+        dst = np.array([1, 2, 50, 4, 5, 33], dtype=np.int64)
+        tok = np.arange(n * T, dtype=np.int64) + 1000
+        if rank == 0:
+            shape = KVShape("mla-fanout", L, 1, D, use_mla=True, tokens_per_block=T)
+            layout = KVCacheLayout(KVCacheLayoutType.LAYERFIRST, L, N, T, 1, D, is_mla=True)
+            mgr = KVManager(make_model_config(shape, tp_size=world), CacheConfig(tokens_per_block=T, num_cpu_blocks=32),
+                            in_process=True)
+            mgr.register_gpu_tensors(kv, layout, multicast=sym)
+            mgr.start()
+            mgr.wait_ready(120)
+            for l in range(L):
+                kv[l][torch.from_numpy(src).to(device)] = want[l].to(device)
+            torch.cuda.synchronize(device)
+            tid = mgr.put_async(tok, slots_of(src, T))
+            ok = mgr.wait(tid, timeout=60, completely=True)[tid].status.value == "success"
+        dist.barrier(group=group)
+        for t in kv:
+            t.zero_()
+        torch.cuda.synchronize(device)
+        dist.barrier(group=group)
+        if rank == 0:
+            tid, mask = mgr.get_match(tok)
+            ok = ok and int(mask.sum()) == n * T
+            mgr.launch(tid, slots_of(dst, T))
+            ok = mgr.wait(tid, timeout=60)[tid].status.value == "success" and ok
+            w = mgr.transfer_manager.engine.worker_for(WorkerKey(0, 0), TransferType.H2D)
+            ok = ok and type(w).__name__ == "NvlsFanoutWorker" and w.last_epoch == 1
+        ok = wait_flag(sym, 1, timeout_s=10.0) and ok
+        torch.cuda.synchronize(device)
+        di = torch.from_numpy(dst).to(device)
+        bad = [l for l in range(L) if not torch.equal(kv[l][di].cpu(), want[l])]
+        if bad:
+            last_failure = f"nvls manager path: rank {rank} layers differ: {bad}"
+            ok = False
+        untouched = torch.from_numpy(np.setdiff1d(np.arange(N), dst)).to(device)
+        ok = ok and int(kv[0][untouched].view(torch.int16).count_nonzero()) == 0
+        dist.barrier(group=group)
+    except Exception as e:  # noqa: BLE001
+        last_failure = f"nvls manager path: {type(e).__name__}: {e}"[:200]
+        ok = False
+    finally:
+        if mgr is not None:
+            mgr.shutdown()
     flag = torch.tensor([1.0 if ok else 0.0], device=device)
     dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group)
     torch.cuda.synchronize(device)

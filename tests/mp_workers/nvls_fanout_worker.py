@@ -74,7 +74,11 @@ def main() -> int:
             untouched = np.setdiff1d(np.arange(N), gpu_blocks)
             assert int(kv[0][torch.from_numpy(untouched).to(dev)].abs().sum()) == 0
             dist.barrier()
-        result.update(ok=True, ms=timings, bytes=n * L * chunk)
+        # the same kernel behind the public API: rank 0's manager restores a prefix into every rank's cache
+        from flexkv_b200.utils import selfcheck
+        mgr_ok = selfcheck.nvls_manager_restore_all_ranks(dev, rank, world)
+        result.update(ok=mgr_ok is True, manager_path=mgr_ok, ms=timings, bytes=n * L * chunk,
+                      why=selfcheck.last_failure)
         return 0
     except Exception as e:  # noqa: BLE001
         result["error"] = repr(e)
