@@ -418,7 +418,27 @@ class StorageEngine:
             return False
         return all(len(r) >= m.effective_tp_size_per_node for r in self.gpu_regs.values())
 
+    def close_gpu_mappings(self) -> None:
+        """Drops this process's view of every registered cache that was opened from a handle (CUDA IPC or
+        virtual-memory handles of another process). The owner may free its cache as soon as the manager is shut
+        down; freeing exported memory that an importer still maps is undefined behaviour in CUDA."""
+        seen = set()
+        regs = [r for ranks in self.gpu_regs.values() for r in ranks.values()]
+        regs += [g for per_rank in self.gpu_group_regs.values() for per in per_rank.values() for g in per.values()]
+        regs += [r for ranks in getattr(self, "swa_regs", {}).values()
+                 for r in (ranks.values() if isinstance(ranks, dict) else ranks)]
+        for reg in regs:
+            keep = getattr(reg, "keepalive", None)
+            for h in (keep if isinstance(keep, (list, tuple)) else [keep]):
+                if h is not None and hasattr(h, "close") and id(h) not in seen:
+                    seen.add(id(h))
+                    try:
+                        h.close()
+                    except Exception:  # noqa: BLE001
+                        pass
+
     def shutdown(self) -> None:
+        self.close_gpu_mappings()
         if self.host is not None:
             try:
                 self.host.region.free()

@@ -226,7 +226,7 @@ def nvls_fanout_all_ranks(device: torch.device, rank: int, world: int, group=Non
     dist.all_reduce(have, op=dist.ReduceOp.MIN, group=group)
     if float(have.item()) < 1.0:
         return "skipped: " + (why if sym is None else "another rank has no multicast mapping")
-    ok = True
+    ok, stage = True, "carve"
     try:
         kv = [sym.layer_tensor(l, (N, T, D), torch.bfloat16) for l in range(L)]
         reg = register_tensors(kv, KVCacheLayout(KVCacheLayoutType.LAYERFIRST, L, N, T, 1, D, is_mla=True))
@@ -242,17 +242,21 @@ def nvls_fanout_all_ranks(device: torch.device, rank: int, world: int, group=Non
         status = new_status(device)
         scratch = torch.zeros(1, dtype=torch.int32, device=device)
         for epoch in ((1,) if large else (1, 2)):
+            stage = f"clear, epoch {epoch}"
             for t in kv:
                 t.zero_()
             torch.cuda.synchronize(device)
             dist.barrier(group=group)
+            stage = f"fan-out kernel, epoch {epoch}"
             if rank == 0:
                 keep = fanout_restore(sym, reg, host, gpu_blocks, cpu_blocks, epoch, scratch, status)
                 torch.cuda.synchronize(device)
                 ok = ok and decode_status(status) == 0
                 del keep
+            stage = f"flag wait, epoch {epoch}"
             ok = wait_flag(sym, epoch, timeout_s=10.0) and ok
             torch.cuda.synchronize(device)
+            stage = f"compare, epoch {epoch}"
             gi = torch.from_numpy(gpu_blocks).to(device)
             bad_layers = []
             for l in range(L):
@@ -267,7 +271,9 @@ def nvls_fanout_all_ranks(device: torch.device, rank: int, world: int, group=Non
             ok = ok and int(kv[0][untouched].view(torch.int16).count_nonzero()) == 0
             dist.barrier(group=group)
     except Exception as e:  # noqa: BLE001
-        last_failure = f"nvls fan-out: {type(e).__name__}: {e}"[:200]
+        last_failure = f"nvls fan-out, rank {rank}, at '{stage}': {type(e).__name__}: {e}"[:240]
+        import sys
+        print(last_failure, file=sys.stderr, flush=True)
         ok = False
     flag = torch.tensor([1.0 if ok else 0.0], device=device)
     dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group)

@@ -152,3 +152,21 @@ def test_injected_worker_failure_surfaces_as_failed():
         assert mgr.get_match(tok)[1].sum() == 5 * T
     finally:
         mgr.shutdown()
+
+
+def test_shutdown_lets_go_of_imported_cache_mappings():
+    """A cache opened from another process's handle is closed when the manager shuts down: its owner may free
+    it right afterwards (freeing exported memory that an importer still maps is undefined in CUDA)."""
+    shape = KVShape("a", 2, 2, 16, tokens_per_block=4)
+    mgr, (kv,) = start(shape, "vllm", num_cpu_blocks=16)
+    closed = []
+
+    class Handle:
+        def close(self):
+            closed.append(id(self))
+
+    h = [Handle(), Handle()]
+    reg = next(iter(mgr.transfer_manager.storage.gpu_regs.values()))[0]
+    reg.keepalive = h + [h[0]]                       # the same handle listed twice is closed once
+    mgr.shutdown()
+    assert sorted(closed) == sorted(id(x) for x in h)
