@@ -535,17 +535,13 @@ def main() -> None:
             verified.update(selfcheck.multi_gpu_checks((0, 1)))
         dist.barrier(group=host_group)
         barrier()
-        # restore + NVSwitch broadcast in one kernel (multimem.st), every rank checks every byte
-        verified[f"nvls_fanout_{world}_ranks"] = selfcheck.nvls_fanout_all_ranks(dev, rank, world)
-        # the same with a cache of deployment size: 61 layers, 4.6 GB per rank, three symmetric segments
-        verified[f"nvls_fanout_{world}_ranks_4p6GB"] = selfcheck.nvls_fanout_all_ranks(dev, rank, world, large=True)
-        if rank == 0 and (verified[f"nvls_fanout_{world}_ranks"] is False or
-                          verified[f"nvls_fanout_{world}_ranks_4p6GB"] is False):
-            verified["nvls_fanout_error"] = selfcheck.last_failure
-        # the same kernel as a manager path: rank 0's KVManager restores a prefix into every rank's cache
-        verified[f"nvls_manager_restore_{world}_ranks"] = selfcheck.nvls_manager_restore_all_ranks(dev, rank, world)
-        if rank == 0 and verified[f"nvls_manager_restore_{world}_ranks"] is False:
-            verified["nvls_manager_restore_error"] = selfcheck.last_failure
+        # restore + NVSwitch broadcast in one kernel (multimem.st) at two cache sizes, and the same kernel behind
+        # KVManager (rank 0 restores a prefix into every rank's cache); every rank checks every byte. They run
+        # as one child process per rank: the multicast mappings then live and end in processes of their own
+        torch.cuda.synchronize()
+        dist.barrier(group=host_group)
+        verified.update(selfcheck.run_nvls_checks_in_children())
+        dist.barrier(group=host_group)
 
     if rank == 0:
         out = {

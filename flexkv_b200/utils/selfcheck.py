@@ -377,3 +377,76 @@ def multi_gpu_checks(devices=(0, 1)) -> Dict[str, bool]:
             out[name] = False
             out[name + "_error"] = f"{type(e).__name__}: {e}"[:200]
     return out
+
+
+def nvls_checks_main(out_path: str) -> int:
+    """Entry point of one rank of a fresh process group (``python -m flexkv_b200.utils.selfcheck --nvls OUT``
+    with RANK / WORLD_SIZE / LOCAL_RANK / MASTER_ADDR / MASTER_PORT set): runs the NVSwitch checks and writes
+    their results as JSON. A benchmark runs them this way, as children, so that the multicast mappings live
+    in processes of their own and end with them."""
+    import json
+    import torch.distributed as dist
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    res: Dict[str, object] = {}
+    try:
+        for name, fn in ((f"nvls_fanout_{world}_ranks", lambda: nvls_fanout_all_ranks(dev, rank, world)),
+                         (f"nvls_fanout_{world}_ranks_4p6GB", lambda: nvls_fanout_all_ranks(dev, rank, world, large=True)),
+                         (f"nvls_manager_restore_{world}_ranks", lambda: nvls_manager_restore_all_ranks(dev, rank, world))):
+            res[name] = fn()
+            if res[name] is False:
+                res[name + "_error"] = last_failure
+    finally:
+        with open(out_path, "w") as f:
+            json.dump(res, f)
+        try:
+            torch.cuda.synchronize()
+            dist.barrier()
+        except Exception:  # noqa: BLE001
+            pass
+        dist.destroy_process_group()
+    return 0
+
+
+def run_nvls_checks_in_children(timeout_s: float = 300.0) -> Dict[str, object]:
+    """Called by every rank of a running job: starts one child per rank (same RANK / WORLD_SIZE / LOCAL_RANK,
+    a rendezvous port of their own), waits for it on the host and returns what the child of this rank wrote.
+    A child that fails or runs out of time gives ``{"nvls_checks": False, "nvls_checks_error": ...}``."""
+    import json
+    import subprocess
+    import sys
+    import tempfile
+    env = {k: v for k, v in os.environ.items() if not k.startswith("TORCHELASTIC")}
+    env["MASTER_PORT"] = str(int(os.environ.get("MASTER_PORT", "29500")) + 17)
+    env["MASTER_ADDR"] = os.environ.get("MASTER_ADDR", "127.0.0.1")
+    root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    env["PYTHONPATH"] = root + os.pathsep + env.get("PYTHONPATH", "")
+    out = os.path.join(tempfile.gettempdir(), f"flexkv_b200_nvls_{os.getpid()}.json")
+    try:
+        proc = subprocess.run([sys.executable, "-m", "flexkv_b200.utils.selfcheck", "--nvls", out], env=env,
+                              capture_output=True, text=True, timeout=timeout_s)
+        if os.path.exists(out):
+            with open(out) as f:
+                res = json.load(f)
+            if proc.returncode != 0:
+                res["nvls_checks_error"] = f"child exit code {proc.returncode}: " + proc.stderr[-300:]
+            return res
+        return {"nvls_checks": False, "nvls_checks_error": f"child exit code {proc.returncode}: " + proc.stderr[-300:]}
+    except subprocess.TimeoutExpired:
+        return {"nvls_checks": False, "nvls_checks_error": f"child still running after {timeout_s:.0f} s (killed)"}
+    finally:
+        try:
+            os.unlink(out)
+        except OSError:
+            pass
+
+
+if __name__ == "__main__":
+    import sys
+    if len(sys.argv) == 3 and sys.argv[1] == "--nvls":
+        sys.exit(nvls_checks_main(sys.argv[2]))
+    sys.exit("usage: python -m flexkv_b200.utils.selfcheck --nvls OUT.json   (one rank of a torch.distributed job)")
+
