@@ -461,6 +461,19 @@ class KVTaskEngine:
                 out[tid] = KVResponse(KVResponseStatus.TIMEOUT, tid, None)
         return out
 
+    def wait_would_return_now(self, task_ids: List[int], completely: bool = False) -> bool:
+        """True when ``wait(task_ids, ...)`` has nothing left to wait for (every task is finished, unknown or not
+        launched). Consumes nothing: a server parks a blocking wait until this holds and serves other clients
+        meanwhile."""
+        self._update_tasks(timeout=0)
+        for tid in task_ids:
+            task = self.tasks.get(tid)
+            if task is None or (task.status in (TaskStatus.UNREADY, TaskStatus.READY) and task.parent < 0):
+                continue
+            if not self._done_for_wait(task, completely):
+                return False
+        return True
+
     def try_wait(self, task_ids: Union[int, List[int]]) -> Dict[int, KVResponse]:
         if isinstance(task_ids, int):
             task_ids = [task_ids]

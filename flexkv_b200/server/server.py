@@ -79,8 +79,12 @@ class KVServer:
         self._running = True
         poller = zmq.Poller()
         poller.register(self._recv, zmq.POLLIN)
+        self._parked = []
         while self._running:
-            if not dict(poller.poll(100)):
+            # a blocking wait of one client must not hold up the others: it is parked and answered from here
+            # once its tasks are done (or its time is up); requests keep being served meanwhile
+            if not dict(poller.poll(1 if self._parked else 100)):
+                self._answer_parked_waits()
                 continue
             try:
                 req = pickle.loads(self._recv.recv())
@@ -98,6 +102,7 @@ class KVServer:
                 rsp = R.Response(req.dp_client_id, req.seq, error=repr(e))
             if rsp is not None:
                 self._reply(rsp)
+            self._answer_parked_waits()
             while self._leaving:                       # after the answer went out
                 gone = self._clients.pop(self._leaving.pop(), None)
                 if gone is not None:
@@ -152,8 +157,28 @@ class KVServer:
         return R.Response(q.dp_client_id, q.seq, value=True)
 
     def _on_wait(self, q: R.WaitRequest):
-        res = self.engine.try_wait(q.task_ids) if q.try_wait else self.engine.wait(q.task_ids, q.timeout, q.completely)
-        return R.Response(q.dp_client_id, q.seq, status=res)
+        if q.try_wait:
+            return R.Response(q.dp_client_id, q.seq, status=self.engine.try_wait(q.task_ids))
+        if not self.engine.wait_would_return_now(q.task_ids, q.completely):
+            self._parked.append((q, time.monotonic() + float(q.timeout)))
+            return None
+        return R.Response(q.dp_client_id, q.seq, status=self.engine.wait(q.task_ids, 0.0, q.completely))
+
+    def _answer_parked_waits(self) -> None:
+        if not self._parked:
+            return
+        still, now = [], time.monotonic()
+        for q, deadline in self._parked:
+            try:
+                if now >= deadline or self.engine.wait_would_return_now(q.task_ids, q.completely):
+                    # unfinished tasks of a wait whose time is up come back as TIMEOUT, as from a blocking wait
+                    self._reply(R.Response(q.dp_client_id, q.seq, status=self.engine.wait(q.task_ids, 0.0, q.completely)))
+                else:
+                    still.append((q, deadline))
+            except Exception as e:  # noqa: BLE001
+                flexkv_logger.exception("parked wait failed")
+                self._reply(R.Response(q.dp_client_id, q.seq, error=repr(e)))
+        self._parked = still
 
     def _on_reset(self, q):
         self.engine.reset_cache()

@@ -207,3 +207,54 @@ def test_batch_launch_over_the_server_returns_per_request_masks():
                 assert torch.equal(caches[d][l][:, dst.ravel()], caches[d][l][:, src.ravel()])
     finally:
         m1.shutdown(); m0.shutdown()
+
+
+def test_blocking_wait_of_one_client_does_not_hold_up_the_others():
+    """The server parks a blocking wait and keeps serving: while rank 0 waits for a slow offload, rank 1's
+    requests are answered at once (one loop serves every data-parallel rank)."""
+    import threading
+    from flexkv_b200.common.transfer import TransferType, WorkerKey
+    shape = KVShape("s", 2, 2, 16, tokens_per_block=4)
+    T = 4
+    model = make_model_config(shape, dp_size=2)
+    cache = CacheConfig(tokens_per_block=T, num_cpu_blocks=32)
+    ep, reg = unique_ipc_endpoint("srv"), unique_ipc_endpoint("reg")
+    m0 = KVManager(model, cache, dp_client_id=0, server_recv_port=ep, gpu_register_port=reg, require_gpu=True)
+    m1 = KVManager(model, cache, dp_client_id=1, server_recv_port=ep, gpu_register_port=reg)
+    for d in range(2):
+        kv, layout = alloc_paged_cache(shape, 32, "cpu", "vllm", fill="normal", seed=50 + d)
+        KVTPClient(reg, dp_client_id=d, device_id=0, tp_rank=0).register_to_server(kv, layout, mode="same_process")
+    m0.start(); m1.start()
+    try:
+        m0.wait_ready(30); m1.wait_ready(30)
+        w = m0.server_handle.server.transfer_manager.engine.worker_for(WorkerKey(0, 0), TransferType.D2H)
+        plain = w.execute
+
+        def slow(op):
+            time.sleep(0.8)
+            return plain(op)
+        w.execute = slow
+        tok = np.arange(4 * T, dtype=np.int64)
+        got = {}
+
+        def offload():
+            tid = m0.put_async(tok, slots([1, 2, 3, 4], T))
+            got["rsp"] = m0.wait(tid, timeout=30, completely=True)[tid]
+            got["t"] = time.monotonic()
+        th = threading.Thread(target=offload)
+        t0 = time.monotonic()
+        th.start()
+        time.sleep(0.1)                                   # rank 0 is inside its wait now
+        for i in range(5):
+            tid, mask = m1.get_match(np.arange(100 + i, 100 + i + 2 * T, dtype=np.int64))
+            assert int(mask.sum()) == 0
+        served = time.monotonic() - t0
+        th.join(30)
+        assert got["rsp"].status.value == "success"
+        assert served < 0.6 < got["t"] - t0, (served, got["t"] - t0)
+        # a wait whose time runs out answers TIMEOUT and leaves the task waitable
+        tid = m0.put_async(np.arange(500, 500 + 2 * T, dtype=np.int64), slots([9, 10], T))
+        assert m0.wait(tid, timeout=0.2, completely=True)[tid].status.value == "timeout"
+        assert m0.wait(tid, timeout=30, completely=True)[tid].status.value == "success"
+    finally:
+        m1.shutdown(); m0.shutdown()
