@@ -139,8 +139,15 @@ def kernel_desc(worker, env) -> dict:
                 "note": "two 128-thread tile pipelines per CTA" if worker.codec == "bf16_xp" else ""}
     ctas = env.transfer_num_cta_h2d if worker.h2d else env.transfer_num_cta_d2h
     eng = env.transfer_engine
-    return {"kernel": "kv_copy_bulk_kernel (cp.async.bulk ring)" if eng in ("tma", "auto", "") else f"engine={eng}",
-            "ctas": int(ctas), "threads": 64, "tile_bytes": int(env.transfer_tile_bytes)}
+    d = {"kernel": "kv_copy_bulk_kernel (cp.async.bulk ring)" if eng in ("tma", "auto", "") else f"engine={eng}",
+         "ctas": int(ctas), "threads": 64, "tile_bytes": int(env.transfer_tile_bytes), "engine": eng}
+    group = getattr(worker, "group", None)
+    if eng in ("auto", "ce") and group is not None and hasattr(group, "ce_ops"):
+        # the router sends an op to the copy engines when its host blocks form runs (gathered into device staging
+        # by the same kernel first when the GPU pages are scattered); everything else stays on the kernel
+        d["ops_through_copy_engines"] = int(group.ce_ops)
+        d["of_which_gathered_into_staging"] = int(group.staged_ops)
+    return d
 
 
 def main() -> None:
@@ -415,6 +422,7 @@ def main() -> None:
         elif host_codec == "fp8_e4m3":
             pcie_ratio = round(0.5 + 1 / 64, 4)
         out["pcie_ratio"] = pcie_ratio
+        out["kernels"] = {"put": kernel_desc(w_d2h, ENV), "get": kernel_desc(w_h2d, ENV)}     # with the final counters
         mgr.shutdown()
         del mgr, w_h2d, w_d2h, group
         import gc

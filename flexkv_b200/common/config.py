@@ -356,7 +356,7 @@ def load_env_config() -> Namespace:
         transfer_num_cta_h2d=_env("FLEXKV_TRANSFER_NUM_CTA_H2D", 8),
         transfer_num_cta_d2h=_env("FLEXKV_TRANSFER_NUM_CTA_D2H", 8),
         transfer_tile_bytes=_env("FLEXKV_TRANSFER_TILE_BYTES", 16384),
-        transfer_engine=_env("FLEXKV_TRANSFER_ENGINE", "tma").lower(),   # tma | simt | ce | auto
+        transfer_engine=_env("FLEXKV_TRANSFER_ENGINE", "auto").lower(),  # tma | simt | ce | auto
         # copy-engine router: the two switches turn on "auto" per direction; the segment
         # threshold is accepted for compatibility (routing here is by bytes per driver call)
         use_ce_transfer_h2d=_env("FLEXKV_USE_CE_TRANSFER_H2D", False, bool),
