@@ -16,6 +16,10 @@ def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gib", type=float, default=4.0)
     ap.add_argument("--iters", type=int, default=5)
+    ap.add_argument("--per-block-kib", type=int, nargs="*", default=[],
+                    help="also copy the same bytes as one cudaMemcpyAsync per block of this size, blocks at random "
+                         "positions on both sides (what a copy-engine path without staging would issue)")
+    ap.add_argument("--streams", type=int, nargs="*", default=[1, 4])
     a = ap.parse_args()
     world = int(os.environ.get("WORLD_SIZE", 1))
     rank = int(os.environ.get("RANK", 0))
@@ -48,6 +52,32 @@ def main() -> None:
             if i >= 3:
                 ms.append(float(t.item()))
         out[name + "_gbs_per_gpu"] = round(n / float(np.median(ms)) / 1e6, 2)
+    # one driver copy per block, blocks scattered on both sides
+    for kib in a.per_block_kib:
+        blk = kib * 1024
+        nb = n // blk
+        rng = np.random.default_rng(7)
+        pg, ph = rng.permutation(nb).tolist(), rng.permutation(nb).tolist()
+        g2d, h2d_ = gpu[:nb * blk].view(nb, blk), host[:nb * blk].view(nb, blk)
+        for ns in a.streams:
+            streams = [torch.cuda.Stream() for _ in range(ns)]
+            for name, (dst, src, pd, ps) in (("d2h", (h2d_, g2d, ph, pg)), ("h2d", (g2d, h2d_, pg, ph))):
+                ms = []
+                for i in range(3):
+                    torch.cuda.synchronize()
+                    e0 = torch.cuda.Event(enable_timing=True)
+                    ends = [torch.cuda.Event(enable_timing=True) for _ in streams]
+                    e0.record()
+                    for k, st in enumerate(streams):
+                        st.wait_event(e0)
+                        with torch.cuda.stream(st):
+                            for j in range(k, nb, ns):
+                                dst[pd[j]].copy_(src[ps[j]], non_blocking=True)
+                            ends[k].record(st)
+                    torch.cuda.synchronize()
+                    if i >= 1:
+                        ms.append(max(e0.elapsed_time(e) for e in ends))
+                out[f"{name}_per_block_{kib}KiB_{ns}streams_gbs"] = round(nb * blk / float(np.median(ms)) / 1e6, 2)
     # both directions at once (a put on one stream, a get on another)
     s1, s2 = torch.cuda.Stream(), torch.cuda.Stream()
     host2 = torch.empty(n, dtype=torch.uint8).pin_memory()
