@@ -34,20 +34,31 @@ struct Scratch {
   uint32_t cnt[256];            // their sum
   uint32_t code[256];           // exponent -> code bits (low 24) | code length (high 8)
   uint8_t nz[256];              // exponents that occur, compacted
+  uint8_t rank[256];            // exponent -> frequency rank (kCodeRanks and above: no code of its own)
   uint32_t seg[8];              // occurrences per 32-exponent segment
   uint32_t warp_tot[kWarps];
+  uint32_t cost[2];             // sampled code bits under mode 1 and mode 2
 };
 
-// code of the exponent with frequency rank r (see kv_compress.h); LSB first
-__device__ __forceinline__ uint32_t code_of_rank(int r) {
-  if (r < kCodeShortRanks) return (uint32_t)r | (2u << 24);
-  const int n = r - kCodeShortRanks;                       // n ones between the "11" marker and the closing zero
-  return 3u | (((1u << n) - 1u) << 2) | ((uint32_t)(n + 3) << 24);
+// code of exponent e with frequency rank r under `mode` (see kv_compress.h): bits (low 24, LSB first) | length << 24
+__device__ __forceinline__ uint32_t code_of(int mode, int r, int e) {
+  if (mode == 1) {
+    if (r < kCodeShortRanks) return (uint32_t)r | (2u << 24);
+    if (r < kCodeRanks) {
+      const int n = r - kCodeShortRanks;                   // n ones between the "11" marker and the closing zero
+      return 3u | (((1u << n) - 1u) << 2) | ((uint32_t)(n + 3) << 24);
+    }
+    return 3u | (((1u << kCodeEscapeOnes) - 1u) << 2) | ((uint32_t)e << (2 + kCodeEscapeOnes)) |
+           ((uint32_t)(2 + kCodeEscapeOnes + 8) << 24);
+  }
+  if (r < kCodeRanks) {
+    const int q = r >> 2;                                  // q ones, a zero, two bits
+    return ((1u << q) - 1u) | ((uint32_t)(r & 3) << (q + 1)) | ((uint32_t)(q + 3) << 24);
+  }
+  return ((1u << kCodeFlatEscapeOnes) - 1u) | ((uint32_t)e << kCodeFlatEscapeOnes) |
+         ((uint32_t)(kCodeFlatEscapeOnes + 8) << 24);
 }
-__device__ __forceinline__ uint32_t code_escape(int e) {
-  return 3u | (((1u << kCodeEscapeOnes) - 1u) << 2) | ((uint32_t)e << (2 + kCodeEscapeOnes)) |
-         ((uint32_t)(2 + kCodeEscapeOnes + 8) << 24);
-}
+__device__ __forceinline__ uint32_t code_len(int mode, int r) { return code_of(mode, r, 0) >> 24; }
 
 __device__ __forceinline__ uint32_t block_exclusive_scan(uint32_t v, Scratch& sc, uint32_t& total, int grp) {
   const int lane = threadIdx.x & 31, warp = (threadIdx.x >> 5) & (kWarps - 1);
@@ -80,6 +91,7 @@ __device__ uint32_t compress_tile(const uint8_t* __restrict__ in, uint8_t* __res
   constexpr int W = kCodeChunkVals / 2;     // words per chunk
   for (int i = tid; i < kWarps * 256; i += kThreads) (&sc.hist[0][0])[i] = 0;
   if (tid < kCodeRanks) out[16 + tid] = 0;
+  if (tid < 2) sc.cost[tid] = 0;
   // this thread's chunk stays in registers for the three passes over it
   uint32_t x[W];
   const bool active = tid < n_chunks;
@@ -97,7 +109,7 @@ __device__ uint32_t compress_tile(const uint8_t* __restrict__ in, uint8_t* __res
     uint16_t* sm16 = reinterpret_cast<uint16_t*>(out + off_sm);
 #pragma unroll
     for (int k = 0; k < W; ++k) {
-      if (k < kCodeSampleWords) {
+      if (k % kCodeSampleStride == 0) {
         atomicAdd(&sc.hist[warp][(x[k] >> 7) & 0xffu], 1u);
         atomicAdd(&sc.hist[warp][(x[k] >> 23) & 0xffu], 1u);
       }
@@ -112,8 +124,8 @@ __device__ uint32_t compress_tile(const uint8_t* __restrict__ in, uint8_t* __res
   for (int w = 0; w < kWarps; ++w) { c0 += sc.hist[w][tid]; c1 += sc.hist[w][tid + 128]; }
   sc.cnt[tid] = c0;
   sc.cnt[tid + 128] = c1;
-  sc.code[tid] = code_escape(tid);
-  sc.code[tid + 128] = code_escape(tid + 128);
+  sc.rank[tid] = 255;
+  sc.rank[tid + 128] = 255;
   const uint32_t b0 = __ballot_sync(kFull, c0 > 0), b1 = __ballot_sync(kFull, c1 > 0);
   if (lane == 0) { sc.seg[warp] = __popc(b0); sc.seg[4 + warp] = __popc(b1); }
   group_sync(grp);
@@ -140,7 +152,18 @@ __device__ uint32_t compress_tile(const uint8_t* __restrict__ in, uint8_t* __res
         const int bo = __shfl_sync(kFull, b, j);
         r += (co > c || (co == c && bo < b)) ? 1 : 0;
       }
-      if (lane < (int)n_nz && r < kCodeRanks) { sc.code[b] = code_of_rank(r); out[16 + r] = (uint8_t)b; }
+      if (lane < (int)n_nz) {
+        sc.rank[b] = (uint8_t)(r < kCodeRanks ? r : kCodeRanks);
+        if (r < kCodeRanks) out[16 + r] = (uint8_t)b;
+      }
+      // what the sample would cost under either code
+      uint32_t a1 = c * code_len(1, r < kCodeRanks ? r : kCodeRanks), a2 = c * code_len(2, r < kCodeRanks ? r : kCodeRanks);
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        a1 += __shfl_xor_sync(kFull, a1, o);
+        a2 += __shfl_xor_sync(kFull, a2, o);
+      }
+      if (lane == 0) { sc.cost[0] = a1; sc.cost[1] = a2; }
     }
   } else {
 #pragma unroll
@@ -154,8 +177,19 @@ __device__ uint32_t compress_tile(const uint8_t* __restrict__ in, uint8_t* __res
         const uint32_t co = sc.cnt[bo];
         r += (co > c || (co == c && bo < b)) ? 1 : 0;
       }
-      if (r < kCodeRanks) { sc.code[b] = code_of_rank(r); out[16 + r] = (uint8_t)b; }
+      sc.rank[b] = (uint8_t)(r < kCodeRanks ? r : kCodeRanks);
+      if (r < kCodeRanks) out[16 + r] = (uint8_t)b;
+      atomicAdd(&sc.cost[0], c * code_len(1, r < kCodeRanks ? r : kCodeRanks));
+      atomicAdd(&sc.cost[1], c * code_len(2, r < kCodeRanks ? r : kCodeRanks));
     }
+  }
+  group_sync(grp);
+  // the code shape that is shorter for the sample; every exponent's code under it
+  const int mode = sc.cost[1] < sc.cost[0] ? 2 : 1;
+  {
+    const int r0 = sc.rank[tid], r1 = sc.rank[tid + 128];
+    sc.code[tid] = code_of(mode, r0 < kCodeRanks ? r0 : kCodeRanks, tid);
+    sc.code[tid + 128] = code_of(mode, r1 < kCodeRanks ? r1 : kCodeRanks, tid + 128);
   }
   group_sync(grp);
   // 3: coded size of every chunk, their offsets, and whether coding pays at all
@@ -183,7 +217,7 @@ __device__ uint32_t compress_tile(const uint8_t* __restrict__ in, uint8_t* __res
         const uint32_t ca = sc.code[(x[k] >> 7) & 0xffu], cb = sc.code[(x[k] >> 23) & 0xffu];
         acc |= (uint64_t)(ca & 0xffffffu) << nb;
         nb += (int)(ca >> 24);
-        if (nb >= 32) {                              // at most 31 + 23 bits are pending here
+        if (nb >= 32) {                              // at most 31 + 23 bits are pending here (mode 2: 31 + 12)
           dst[0] = (uint8_t)acc; dst[1] = (uint8_t)(acc >> 8); dst[2] = (uint8_t)(acc >> 16); dst[3] = (uint8_t)(acc >> 24);
           dst += 4; acc >>= 32; nb -= 32;
         }
@@ -198,7 +232,7 @@ __device__ uint32_t compress_tile(const uint8_t* __restrict__ in, uint8_t* __res
     }
     if (tid == 0) {
       for (uint32_t i = (uint32_t)off_exp + total_exp; i < coded_total; ++i) out[i] = 0;
-      out[0] = 1;
+      out[0] = (uint8_t)mode;
       out[1] = (uint8_t)(n_nz < (uint32_t)kCodeRanks ? n_nz : (uint32_t)kCodeRanks);
       *reinterpret_cast<uint16_t*>(out + 2) = (uint16_t)n_chunks;
       *reinterpret_cast<uint32_t*>(out + 4) = coded_total;
@@ -230,7 +264,7 @@ __device__ bool decompress_tile(const uint8_t* __restrict__ in, uint8_t* __restr
   const int mode = in[0];
   const uint32_t total = *reinterpret_cast<const uint32_t*>(in + 4);
   const uint32_t elems_h = *reinterpret_cast<const uint32_t*>(in + 8);
-  if (total != size || elems_h != (uint32_t)elems || mode > 1) return false;
+  if (total != size || elems_h != (uint32_t)elems || mode > 2) return false;
   if (mode == 0) {
     if (size != 16u + (uint32_t)elems * 2u) return false;
     const uint4* src = reinterpret_cast<const uint4*>(in + 16);
@@ -256,26 +290,49 @@ __device__ bool decompress_tile(const uint8_t* __restrict__ in, uint8_t* __restr
     uint64_t buf = ((uint64_t)in32[wi] | ((uint64_t)in32[wi + 1] << 32)) >> sh;   // reads stay inside the stage ring
     int avail = 64 - sh;
     wi += 2;
-    auto next_exp = [&]() -> uint32_t {
+    auto refill = [&](int len) {
+      buf >>= len;
+      avail -= len;
+      if (avail < 32) { buf |= (uint64_t)in32[wi++] << avail; avail += 32; }
+    };
+    auto next_steep = [&]() -> uint32_t {                        // mode 1
       const uint32_t v = (uint32_t)buf;
       const uint32_t c = v & 3u, t = v >> 2;
       const int n = __ffs((int)~t) - 1;                        // ones that follow the "11" marker
       const bool esc = n >= kCodeEscapeOnes;
       const int len = c != 3u ? 2 : (esc ? 2 + kCodeEscapeOnes + 8 : n + 3);
       const uint32_t e = c != 3u ? syms[c] : (esc ? ((t >> kCodeEscapeOnes) & 0xffu) : syms[kCodeShortRanks + n]);
-      buf >>= len;
-      avail -= len;
-      if (avail < 32) { buf |= (uint64_t)in32[wi++] << avail; avail += 32; }
+      refill(len);
       return e;
     };
-#pragma unroll 2
-    for (int k = 0; k < kCodeChunkVals / 2; ++k) {
+    auto next_flat = [&]() -> uint32_t {                         // mode 2
+      const uint32_t v = (uint32_t)buf;
+      const int q = __ffs((int)(~v | (1u << kCodeFlatEscapeOnes))) - 1;   // leading ones of the code, at most 4
+      const bool esc = q >= kCodeFlatEscapeOnes;
+      const int len = esc ? kCodeFlatEscapeOnes + 8 : q + 3;
+      const uint32_t e = esc ? ((v >> kCodeFlatEscapeOnes) & 0xffu) : syms[(q << 2) | ((v >> (q + 1)) & 3u)];
+      refill(len);
+      return e;
+    };
+    auto emit = [&](int k, uint32_t ea, uint32_t eb) {
       const int w = k * n_chunks + tid;
-      const uint32_t ea = next_exp(), eb = next_exp();
       const uint32_t s = sm16[w];
       const uint32_t lo = ((s & 0x80u) << 8) | (ea << 7) | (s & 0x7fu);
       const uint32_t hi = ((s & 0x8000u)) | (eb << 7) | ((s >> 8) & 0x7fu);
       out32[w] = lo | (hi << 16);
+    };
+    if (mode == 1) {
+#pragma unroll 2
+      for (int k = 0; k < kCodeChunkVals / 2; ++k) {
+        const uint32_t ea = next_steep(), eb = next_steep();
+        emit(k, ea, eb);
+      }
+    } else {
+#pragma unroll 2
+      for (int k = 0; k < kCodeChunkVals / 2; ++k) {
+        const uint32_t ea = next_flat(), eb = next_flat();
+        emit(k, ea, eb);
+      }
     }
   }
   return true;

@@ -47,10 +47,18 @@ def kv_compress(reg: GpuRegistration, host: HostSide, size_table: torch.Tensor, 
 CHUNK_VALS = 64
 HEADER_BYTES = 32
 RANKS, SHORT_RANKS, ESCAPE_ONES = 16, 3, 13
+FLAT_ESCAPE_ONES = 4
 SAMPLE_WORDS = 4
+SAMPLE_STRIDE = CHUNK_VALS // 2 // SAMPLE_WORDS      # words 0, 8, 16, 24 of every chunk are sampled
 
 
-def _code_of(rank: int, exponent: int):
+def _code_of(rank: int, exponent: int, mode: int = 1):
+    """(bits, length) of one exponent, LSB first; rank >= RANKS means no code of its own."""
+    if mode == 2:
+        if rank < RANKS:
+            q = rank >> 2
+            return ((1 << q) - 1) | ((rank & 3) << (q + 1)), q + 3
+        return ((1 << FLAT_ESCAPE_ONES) - 1) | (exponent << FLAT_ESCAPE_ONES), FLAT_ESCAPE_ONES + 8
     if rank < SHORT_RANKS:
         return rank, 2
     if rank < RANKS:
@@ -67,12 +75,15 @@ def reference_compress_tile(x: torch.Tensor) -> torch.Tensor:
     n = v.size
     C = n // CHUNK_VALS
     e = (v >> 7) & 0xFF
-    # frequencies over the sample the format names: the first SAMPLE_WORDS words of every chunk
-    sample = [2 * (k * C + t) + h for t in range(C) for k in range(SAMPLE_WORDS) for h in range(2)]
+    # frequencies over the sample the format names: every SAMPLE_STRIDE-th word of every chunk
+    sample = [2 * (k * C + t) + h for t in range(C) for k in range(0, CHUNK_VALS // 2, SAMPLE_STRIDE) for h in range(2)]
     hist = np.bincount(e[sample], minlength=256)
     order = sorted((b for b in range(256) if hist[b] > 0), key=lambda b: (-int(hist[b]), b))
     syms = order[:RANKS]
     rank = {s: r for r, s in enumerate(syms)}
+    # the code shape that is shorter for the sample (mode 1 on a tie)
+    cost = {m: sum(int(hist[b]) * _code_of(rank.get(b, RANKS), b, m)[1] for b in order) for m in (1, 2)}
+    mode = 2 if cost[2] < cost[1] else 1
     sizes, payload = [], bytearray()
     for t in range(C):
         acc, nb = 0, 0
@@ -80,7 +91,7 @@ def reference_compress_tile(x: torch.Tensor) -> torch.Tensor:
             w = k * C + t
             for h in range(2):
                 ex = int(e[2 * w + h])
-                code, ln = _code_of(rank.get(ex, RANKS), ex)
+                code, ln = _code_of(rank.get(ex, RANKS), ex, mode)
                 acc |= code << nb
                 nb += ln
         nbytes = (nb + 7) // 8
@@ -94,7 +105,7 @@ def reference_compress_tile(x: torch.Tensor) -> torch.Tensor:
         hdr[8:12] = n.to_bytes(4, "little")
         return torch.frombuffer(bytearray(bytes(hdr) + v.astype(np.uint16).tobytes()), dtype=torch.uint8).clone()
     out = bytearray(total)
-    out[0], out[1] = 1, len(syms)
+    out[0], out[1] = mode, len(syms)
     out[2:4] = C.to_bytes(2, "little")
     out[4:8] = total.to_bytes(4, "little")
     out[8:12] = n.to_bytes(4, "little")
@@ -126,7 +137,15 @@ def reference_decompress_tile(packed: torch.Tensor) -> torch.Tensor:
             w = k * C + t
             for h in range(2):
                 c = acc & 3
-                if c != 3:
+                if mode == 2:
+                    q = 0
+                    while (acc >> q) & 1 and q < FLAT_ESCAPE_ONES:
+                        q += 1
+                    if q >= FLAT_ESCAPE_ONES:
+                        ex, ln = (acc >> FLAT_ESCAPE_ONES) & 0xFF, FLAT_ESCAPE_ONES + 8
+                    else:
+                        ex, ln = syms[(q << 2) | ((acc >> (q + 1)) & 3)], q + 3
+                elif c != 3:
                     ex, ln = syms[c], 2
                 else:
                     tt, ones = acc >> 2, 0
