@@ -432,9 +432,10 @@ def main() -> None:
     main_res = measure(args.codec, True, args.steps, args.warmup, args.latency_iters)
     raw_res = None
     if args.codec != "none" and not args.skip_raw and args.impl == "ours":
-        # the side record takes at most two timed steps (three warm-up steps as the timing rules ask), so that
-        # the whole run stays short on boxes whose host side is slow with every GPU busy
-        raw_res = measure("none", False, min(args.steps, 2), min(args.warmup, 3), min(args.latency_iters, 8))
+        # the side record takes at most two timed steps, one from four GPUs up (three warm-up steps as the timing
+        # rules ask), so that the whole run stays short on boxes whose host side is slow with every GPU busy
+        raw_res = measure("none", False, 1 if world >= 4 else min(args.steps, 2), min(args.warmup, 3),
+                          min(args.latency_iters, 4 if world >= 4 else 8))
 
     # ------------------------------------------------------------------ one server, one index, N clients
     shared = None

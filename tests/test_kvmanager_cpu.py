@@ -170,3 +170,20 @@ def test_shutdown_lets_go_of_imported_cache_mappings():
     reg.keepalive = h + [h[0]]                       # the same handle listed twice is closed once
     mgr.shutdown()
     assert sorted(closed) == sorted(id(x) for x in h)
+
+
+def test_multicast_registration_stands_for_its_whole_tp_group():
+    """One registration that carries multicast addresses counts as every rank of a shared-KV tensor-parallel
+    group when the data plane waits for its registrations."""
+    from flexkv_b200.storage.gpu_layout import register_tensors
+    from flexkv_b200.transfer_manager import TransferManager
+    shape = KVShape("m", 2, 1, 64, use_mla=True, tokens_per_block=4)
+    tm = TransferManager(make_model_config(shape, tp_size=4), CacheConfig(tokens_per_block=4, num_cpu_blocks=8),
+                         require_gpu=True)
+    kv, layout = alloc_paged_cache(shape, 8, "cpu", "vllm")
+    reg = register_tensors(kv, layout)
+    tm.register_gpu(reg)
+    assert tm._expected_registrations() == 4 and tm._registrations_arrived() == 1
+    reg.mc_ptrs = [int(p) for p in reg.ptrs]
+    reg.mc_flag_ptr = 1
+    assert tm._registrations_arrived() == 4
