@@ -49,8 +49,8 @@ def mode_pull(a):
     src = rng.permutation(NB)[:n].astype(np.int64)
     dst = rng.permutation(NB)[:n].astype(np.int64)
     rows = []
-    for ctas in a.ctas:
-        copier = _native.C.PeerCopier([r.as_native() for r in regs], L, 1, chunk, num_ctas=ctas, tile_bytes=16384,
+    for ctas, tile in [(c, t) for t in a.tile_bytes for c in a.ctas]:
+        copier = _native.C.PeerCopier([r.as_native() for r in regs], L, 1, chunk, num_ctas=ctas, tile_bytes=tile,
                                       engine=0, max_blocks_per_op=max(4096, n))
         if not copier.can_access(0, 1):
             print(json.dumps({"mode": "pull", "skipped": "no peer access between GPU 0 and 1"}))
@@ -62,7 +62,7 @@ def mode_pull(a):
             if i >= 3:
                 ms.append(r.gpu_ms)
         t = float(np.median(ms))
-        rows.append(dict(mode="pull", path="pull_kernel", ctas=ctas, blocks=n, bytes=total, ms=round(t, 3),
+        rows.append(dict(mode="pull", path="pull_kernel", ctas=ctas, tile_bytes=tile, blocks=n, bytes=total, ms=round(t, 3),
                          gbs=round(total / t / 1e6, 1)))
         print(json.dumps(rows[-1]), flush=True)
         del copier
@@ -284,6 +284,7 @@ def main() -> None:
     ap.add_argument("--baseline-blocks", type=int, default=64)
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--ctas", type=int, nargs="+", default=[8, 32, 64])
+    ap.add_argument("--tile-bytes", type=int, nargs="+", default=[16384], help="pull: tile sizes of the copy kernel")
     ap.add_argument("--out", default="")
     a = ap.parse_args()
     rows = mode_pull(a) if a.mode == "pull" else mode_fanout(a)

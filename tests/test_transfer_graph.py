@@ -103,3 +103,15 @@ def test_merge_requires_bound_graphs():
     g.add_transfer_op(TransferOp(g.graph_id, TransferType.H2D, A(1), A(), gpu_side="dst"))
     with pytest.raises(ValueError):
         merge_to_batch_graph([g])
+
+
+def test_even_tile_bytes_cuts_chunks_without_a_ragged_tile():
+    from flexkv_b200.transfer.workers import even_tile_bytes
+    assert even_tile_bytes(73728) == 24576          # 64 tokens x 576 x bf16 (MLA)
+    assert even_tile_bytes(32768) == 16384
+    assert even_tile_bytes(65536) == 16384
+    assert even_tile_bytes(2048) == 2048
+    assert even_tile_bytes(4680) == 16384           # no 16-byte-aligned even cut: the default tile
+    for c in (73728, 32768, 147456, 9216):
+        t = even_tile_bytes(c)
+        assert c % t == 0 and t % 16 == 0 and t <= 24576
