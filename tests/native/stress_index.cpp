@@ -1,7 +1,10 @@
 // Stand-alone stress of the C++ control plane, built by tests/test_native_sanitizers.py with
 // -fsanitize=address,undefined (memory errors, UB) and with -fsanitize=thread (data races).
-// No Python, no CUDA: radix index, block pool, hasher, lease-aware tree and peer view.
+// No Python, no CUDA: radix index, block pool, hasher, lease-aware tree and peer view, transfer-graph scheduler.
 #include <atomic>
+#include <condition_variable>
+#include <deque>
+#include <mutex>
 #include <cstdio>
 #include <cstdlib>
 #include <random>
@@ -9,6 +12,7 @@
 #include <vector>
 
 #include "dist_index.h"
+#include "graph_scheduler.h"
 #include "hasher.h"
 #include "radix_index.h"
 
@@ -191,6 +195,108 @@ static void threaded_leases() {
   view.shutdown();
 }
 
+// Random DAGs submitted from several threads, executed by several "worker" threads that report through
+// op_done (some ops fail, some are fanned out to two executors, some are requeued once), completions drained
+// by a waiter: every graph must finish exactly once, no op may run twice or after its graph failed for good,
+// and nothing may be left behind.
+static void threaded_scheduler() {
+  GraphScheduler sched;
+  struct Item { int64_t g, op; };
+  std::mutex qmu;
+  std::condition_variable qcv;
+  std::deque<Item> queue;
+  std::atomic<bool> stop{false};
+  std::atomic<int64_t> ran{0}, graph_records{0}, op_records{0}, failed_graphs{0};
+  constexpr int kSubmitters = 3, kGraphsEach = 150, kWorkers = 4;
+  std::vector<std::atomic<int>> runs((size_t)kSubmitters * kGraphsEach * 16);
+  for (auto& r : runs) r = 0;
+  auto push = [&](int64_t g, const std::vector<int64_t>& ops) {
+    std::lock_guard<std::mutex> lk(qmu);
+    for (int64_t o : ops) queue.push_back({g, o});
+    qcv.notify_all();
+  };
+  auto worker = [&](uint64_t seed) {
+    std::mt19937_64 rng(seed);
+    for (;;) {
+      Item it;
+      {
+        std::unique_lock<std::mutex> lk(qmu);
+        qcv.wait(lk, [&] { return stop.load() || !queue.empty(); });
+        if (queue.empty()) return;
+        it = queue.front();
+        queue.pop_front();
+      }
+      const size_t slot = (size_t)it.g * 16 + (size_t)it.op;
+      if ((rng() % 23) == 0 && runs[slot].load() == 0) {     // could not start: back to the ready set, once
+        runs[slot] = -1;
+        CHECK(sched.requeue(it.g, it.op));
+        push(it.g, sched.take_ready(it.g));
+        continue;
+      }
+      const int before = runs[slot].exchange(1);
+      CHECK(before <= 0);                                     // handed out once (after at most one requeue)
+      ++ran;
+      const bool two = (rng() % 5) == 0;
+      if (two) sched.set_fanout(it.g, it.op, 2);
+      const bool ok = (rng() % 17) != 0;
+      SchedDone d = sched.op_done(it.g, it.op, ok, 0.1, 100);
+      CHECK(d.accepted);
+      if (two) {
+        CHECK(!d.op_finished);
+        d = sched.op_done(it.g, it.op, true, 0.2, 100);
+        CHECK(d.accepted && d.op_finished && d.op_success == ok && d.bytes == 200);
+      }
+      push(it.g, d.ready);
+    }
+  };
+  auto submitter = [&](int who) {
+    std::mt19937_64 rng(1000 + (uint64_t)who);
+    for (int k = 0; k < kGraphsEach; ++k) {
+      const int64_t g = (int64_t)who * kGraphsEach + k;
+      const int n = 1 + (int)(rng() % 12);
+      std::vector<int64_t> ids((size_t)n);
+      std::vector<int32_t> flags((size_t)n, 0);
+      std::vector<std::pair<int64_t, int64_t>> edges;
+      for (int i = 0; i < n; ++i) {
+        ids[(size_t)i] = i;
+        if ((rng() % 9) == 0) flags[(size_t)i] = GraphScheduler::kInstant;
+        for (int j = 0; j < i; ++j)
+          if ((rng() % 4) == 0) edges.emplace_back(i, j);     // successor i depends on j < i: acyclic
+      }
+      push(g, sched.submit(g, ids, flags, edges));
+    }
+  };
+  auto waiter = [&] {
+    const int64_t want = (int64_t)kSubmitters * kGraphsEach;
+    while (graph_records.load() < want) {
+      for (const SchedCompletion& c : sched.wait(0.05)) {
+        if (c.op_id < 0) {
+          ++graph_records;
+          if (!c.success) ++failed_graphs;
+        } else {
+          ++op_records;
+        }
+      }
+    }
+  };
+  std::vector<std::thread> th;
+  for (int w = 0; w < kWorkers; ++w) th.emplace_back(worker, 7 + (uint64_t)w);
+  std::thread wt(waiter);
+  std::vector<std::thread> subs;
+  for (int s = 0; s < kSubmitters; ++s) subs.emplace_back(submitter, s);
+  for (auto& t : subs) t.join();
+  wt.join();
+  stop = true;
+  qcv.notify_all();
+  for (auto& t : th) t.join();
+  CHECK(graph_records.load() == (int64_t)kSubmitters * kGraphsEach);
+  CHECK(sched.graphs_in_flight() == 0);
+  const GraphScheduler::Stats st = sched.stats();
+  CHECK(st.graphs == graph_records.load() && st.failed_graphs == failed_graphs.load() && failed_graphs.load() > 0);
+  CHECK(op_records.load() >= ran.load());                     // instant ops have records but were never run
+  CHECK(sched.wait(0.0).empty());
+}
+
 int main(int argc, char** argv) {
   const bool threads_only = argc > 1 && std::string(argv[1]) == "threads";
   if (!threads_only) {
@@ -198,6 +304,7 @@ int main(int argc, char** argv) {
     hashing();
   }
   threaded_leases();
+  threaded_scheduler();
   std::printf("OK\n");
   return 0;
 }

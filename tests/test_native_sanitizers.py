@@ -9,7 +9,7 @@ import pytest
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(os.path.dirname(HERE), "flexkv_b200", "csrc")
-SOURCES = [os.path.join(CSRC, f) for f in ("radix_index.cpp", "dist_index.cpp", "native_log.cpp", "hasher.cpp")] + \
+SOURCES = [os.path.join(CSRC, f) for f in ("radix_index.cpp", "dist_index.cpp", "native_log.cpp", "hasher.cpp", "graph_scheduler.cpp")] + \
     [os.path.join(HERE, "native", "stress_index.cpp")]
 
 
