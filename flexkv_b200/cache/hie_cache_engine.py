@@ -117,7 +117,8 @@ def get_node_registry(cache_config, model_config=None) -> NodeRegistry:
     reg = getattr(cache_config, "_node_registry_obj", None)
     if reg is not None:
         return reg
-    client: RegistryClient = connect(cache_config.redis_host, int(cache_config.redis_port))
+    client: RegistryClient = connect(cache_config.redis_host, int(cache_config.redis_port),
+                                     getattr(cache_config, "redis_password", None))
     pp_rank = getattr(model_config, "pp_rank", 0) if model_config is not None else 0
     pp_size = getattr(model_config, "pp_size", 1) if model_config is not None else 1
     reg = NodeRegistry(client, ip=cache_config.local_ip or "127.0.0.1", pp_rank=pp_rank, pp_size=pp_size,

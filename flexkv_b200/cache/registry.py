@@ -208,7 +208,7 @@ class RegistryClient:
         raise AttributeError(name)
 
 
-def connect(host: str, port: int) -> RegistryClient:
+def connect(host: str, port: int, password: Optional[str] = None) -> RegistryClient:
     """``host`` "inproc[:name]" selects a store inside this process; anything else is the
     address of a RegistryServer (the configuration reuses the reference's redis_host/redis_port fields);
     "redis://[:password@]host[:port][/db]" is a Redis server."""
@@ -219,7 +219,7 @@ def connect(host: str, port: int) -> RegistryClient:
         # a Redis server, spoken to over its wire protocol: redis://[:password@]host[/db]
         from .redis_client import RedisRegistryClient
         rest = host[len("redis://"):]
-        password, db = "", 0
+        password, db = password or "", 0
         if "@" in rest:
             cred, rest = rest.rsplit("@", 1)
             password = cred.split(":", 1)[1] if ":" in cred else cred

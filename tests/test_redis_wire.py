@@ -105,6 +105,7 @@ def test_password_and_database_are_sent_on_connect():
         ok = connect("redis://:s3cret@127.0.0.1/2", s.port)
         assert ok.incr("k") == 1
         assert s.store.commands[:2] == ["AUTH", "SELECT"]
+        assert connect("redis://127.0.0.1", s.port, password="s3cret").incr("k") == 2     # CacheConfig.redis_password
         with pytest.raises(ConnectionError, match="AUTH refused"):
             RedisRegistryClient("127.0.0.1", s.port, password="wrong").ping()
     finally:
