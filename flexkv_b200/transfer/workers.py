@@ -789,26 +789,38 @@ class PeerHostWorker(TransferWorker):
         if nids is None or len(nids) != len(src) or len(src) != len(dst):
             return OpOutcome(False, error="peer host op without owner ids")
         host = self.storage.host
-        mine = host.as_numpy()
         bb = host.block_bytes
-        results = [False] * len(src)
-        i, n = 0, len(src)
+        n = len(src)
+        results = [False] * n
         err = ""
-        while i < n:
-            j = i + 1
-            while j < n and nids[j] == nids[i] and src[j] == src[j - 1] + 1 and dst[j] == dst[j - 1] + 1:
-                j += 1
+        src = np.asarray(src, dtype=np.int64)
+        dst = np.asarray(dst, dtype=np.int64)
+        owners = np.asarray(nids, dtype=np.int64)
+        for nid in np.unique(owners).tolist():
+            sel = np.nonzero(owners == nid)[0]
             try:
-                pool, _, nblk = self._pool_of(int(nids[i]))
-                if src[i] < 0 or src[j - 1] >= nblk:
-                    raise RuntimeError(f"block {int(src[j - 1])} outside node {int(nids[i])}'s pool")
-                mine[int(dst[i]) * bb:int(dst[j - 1] + 1) * bb] = pool[int(src[i]) * bb:int(src[j - 1] + 1) * bb]
-                for k in range(i, j):
+                pool, _, nblk = self._pool_of(int(nid))
+                s_ids = np.ascontiguousarray(src[sel])
+                d_ids = np.ascontiguousarray(dst[sel])
+                if s_ids.min() < 0 or s_ids.max() >= nblk:
+                    raise RuntimeError(f"block {int(s_ids.max())} outside node {nid}'s pool")
+                if d_ids.min() < 0 or d_ids.max() >= host.num_blocks:
+                    raise RuntimeError(f"destination block {int(d_ids.max())} outside the host pool")
+                # the owner's pool plays the paged side of the host copy helper (one tensor, whole blocks as
+                # chunks), so the blocks move on the helper's thread pool instead of one memcpy at a time
+                params = dict(gpu_ptrs=[int(pool.ctypes.data)], idx_layer_mul=0, idx_kv_mul=0, g_layer_stride=0,
+                              g_kv_stride=0, g_block_stride=bb, cpu_base=host.base, c_layer_stride=0, c_kv_stride=0,
+                              c_block_stride=bb, c_off=0, gpu_blocks_ptr=s_ids.ctypes.data,
+                              cpu_blocks_ptr=d_ids.ctypes.data, num_pairs=int(sel.size), layer_start=0, num_layers=1,
+                              kv_dim=1, chunk_bytes=bb, gpu_num_blocks=nblk, cpu_num_blocks=host.num_blocks, h2d=0)
+                status = _native.C.host_kv_copy(params, 16)
+                if status != 0:
+                    raise RuntimeError(f"host copy status 0x{status:x}")
+                for k in sel.tolist():
                     results[k] = True
             except (RuntimeError, OSError, ValueError) as e:
                 err = str(e)
-                self._maps.pop(int(nids[i]), None)
-            i = j
+                self._maps.pop(int(nid), None)
         ok = all(results)
         return OpOutcome(ok, block_results=tuple(results), num_bytes=sum(results) * bb,
                          error="" if ok else f"{n - sum(results)} peer block(s) failed: {err}")
