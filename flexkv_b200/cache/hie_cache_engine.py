@@ -53,7 +53,11 @@ class HierarchyLRCacheEngine(CacheEngine):
             registry.register()
         self.node_id = int(registry.node_id)
         kind = {DeviceType.CPU: "CPUB", DeviceType.SSD: "SSDB"}.get(device_type, "CPUB")
-        self.channel = channel if channel is not None else RegistryMetaChannel(registry.client, kind)
+        if channel is None:
+            # a registry in a Redis server gets the native channel, the in-box registry the Python one
+            native = getattr(registry.client, "native_channel", None)
+            channel = native(kind) if callable(native) else RegistryMetaChannel(registry.client, kind)
+        self.channel = channel
         lease = int(lease_ttl_ms if lease_ttl_ms is not None else env.lease_ttl_ms)
         renew = int(renew_lease_ms if renew_lease_ms is not None else env.renew_lease_ms)
         refresh = int(refresh_interval_ms if refresh_interval_ms is not None else getattr(env, "refresh_batch_ms", 100))

@@ -41,7 +41,15 @@ def _glob_escape(prefix: str) -> str:
 class RedisRegistryClient:
     def __init__(self, host: str, port: int = 6379, password: str = "", db: int = 0, timeout_ms: int = 3000) -> None:
         from .. import _native
+        self._addr = (host, int(port), int(timeout_ms), password or "", int(db))
         self._c = _native.C.RespClient(host, int(port), int(timeout_ms), password or "", int(db))
+
+    def native_channel(self, kind: str = "CPUB"):
+        """The block-record channel of the cross-node index over its own connection, served from native code
+        (the trees' refresh threads then never take the interpreter lock for it)."""
+        from .. import _native
+        host, port, timeout_ms, password, db = self._addr
+        return _native.C.RedisMetaChannel(host, port, kind, timeout_ms, password, db)
 
     def close(self) -> None:
         self._c.close()

@@ -5,6 +5,7 @@
 
 #include "bindings_common.h"
 #include "dist_index.h"
+#include "redis_meta_channel.h"
 #include "resp_client.h"
 
 namespace py = pybind11;
@@ -66,6 +67,7 @@ class PyMetaChannel : public MetaChannel {
 std::shared_ptr<MetaChannel> channel_from_py(const py::object& o) {
   if (o.is_none()) return nullptr;
   if (py::isinstance<InProcMetaChannel>(o)) return o.cast<std::shared_ptr<InProcMetaChannel>>();
+  if (py::isinstance<RedisMetaChannel>(o)) return o.cast<std::shared_ptr<RedisMetaChannel>>();
   return std::make_shared<PyMetaChannel>(o);
 }
 
@@ -147,6 +149,46 @@ void init_dist_bindings(py::module_& m) {
         RespValue v;
         if (!RespClient::parse(s, pos, v)) return py::none();
         return py::make_tuple(resp_to_py(v), pos);
+      });
+
+  // block records in a Redis server, spoken to from native code (no interpreter lock on the refresh path)
+  py::class_<RedisMetaChannel, std::shared_ptr<RedisMetaChannel>>(m, "RedisMetaChannel")
+      .def(py::init([](const std::string& host, int port, const std::string& kind, int timeout_ms,
+                       const std::string& password, int db) {
+             return std::make_shared<RedisMetaChannel>(host, port, kind, timeout_ms, password, db);
+           }), py::arg("host"), py::arg("port"), py::arg("kind") = "CPUB", py::arg("timeout_ms") = 3000,
+           py::arg("password") = "", py::arg("db") = 0)
+      .def("publish", [](RedisMetaChannel& c, uint32_t nid, py::list rows) {
+        std::vector<BlockMeta> v;
+        for (auto row : rows) {
+          py::tuple t = row.cast<py::tuple>();
+          BlockMeta b;
+          b.ph = t[0].cast<uint64_t>(); b.pb = t[1].cast<int64_t>(); b.nid = t[2].cast<uint32_t>();
+          b.hash = t[3].cast<uint64_t>(); b.lt = t[4].cast<int64_t>(); b.state = t[5].cast<int>();
+          v.push_back(b);
+        }
+        py::gil_scoped_release nogil;
+        c.publish(nid, v);
+      })
+      .def("remove", [](RedisMetaChannel& c, uint32_t nid, std::vector<uint64_t> hashes) {
+        py::gil_scoped_release nogil;
+        c.remove(nid, hashes);
+      })
+      .def("list_nodes", [](RedisMetaChannel& c) {
+        py::gil_scoped_release nogil;
+        return c.list_nodes();
+      })
+      .def("load", [](RedisMetaChannel& c, uint32_t nid) {
+        std::vector<BlockMeta> v;
+        {
+          py::gil_scoped_release nogil;
+          v = c.load(nid);
+        }
+        return PyMetaChannel::to_rows(v);
+      })
+      .def("clear_node", [](RedisMetaChannel& c, uint32_t nid) {
+        py::gil_scoped_release nogil;
+        c.clear_node(nid);
       });
 
   py::class_<InProcMetaChannel, std::shared_ptr<InProcMetaChannel>>(m, "InProcMetaChannel")

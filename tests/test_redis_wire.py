@@ -110,3 +110,76 @@ def test_password_and_database_are_sent_on_connect():
             RedisRegistryClient("127.0.0.1", s.port, password="wrong").ping()
     finally:
         s.stop()
+
+
+def test_native_channel_and_python_channel_read_each_other(server):
+    """Block records written from native code and from Python share one schema in the server."""
+    cl = connect("redis://127.0.0.1", server.port)
+    cl.hset("node:1", dict(node_id=1, status="active"), ttl=30)
+    cl.hset("node:2", dict(node_id=2, status="left"), ttl=30)
+    cl.hset("node:3", dict(node_id=3, status="active"), ttl=30)
+    py_ch = RegistryMetaChannel(cl)
+    nat = cl.native_channel("CPUB")
+    rows = [(0, 5, 1, 2**64 - 7, -3, 0), (2**64 - 7, 6, 1, 1234567, 99, 1)] + \
+           [(i, i, 1, 10_000 + i, 5, 0) for i in range(30)]                       # several SCAN pages
+    nat.publish(1, rows)
+    py_ch.publish(3, [(1, 2, 3, 4, 5, 2)])
+    assert nat.list_nodes() == [1, 3] == py_ch.list_nodes()
+    assert sorted(nat.load(1)) == sorted(rows) == sorted(py_ch.load(1))
+    assert nat.load(3) == [(1, 2, 3, 4, 5, 2)]
+    nat.remove(1, [1234567, 10_003])
+    assert len(py_ch.load(1)) == 30 and (2**64 - 7, 6, 1, 1234567, 99, 1) not in py_ch.load(1)
+    nat.clear_node(1)
+    assert nat.load(1) == [] and py_ch.load(3) == [(1, 2, 3, 4, 5, 2)]
+    server.drop_next = True
+    with pytest.raises(ConnectionError):
+        nat.list_nodes()
+    assert nat.list_nodes() == [1, 3]
+
+
+def test_two_nodes_share_prefixes_through_a_redis_registry(server):
+    """The cross-node reuse flow of tests/test_p2p_host.py with the registry in a Redis server: node ids,
+    liveness, node meta and block records all travel over the wire protocol, the block records from native code."""
+    import numpy as np
+    import torch
+    from flexkv_b200 import CacheConfig, KVManager
+    from flexkv_b200.models import KVShape, alloc_paged_cache, make_model_config
+    T = 4
+
+    def slots(blocks):
+        return np.repeat(np.asarray(blocks, dtype=np.int64), T) * T + np.tile(np.arange(T), len(blocks))
+
+    def start(seed):
+        shape = KVShape("p", 2, 2, 16, tokens_per_block=T)
+        cfg = CacheConfig(tokens_per_block=T, num_cpu_blocks=24, enable_p2p_cpu=True, redis_host="redis://127.0.0.1",
+                          redis_port=server.port)
+        mgr = KVManager(make_model_config(shape), cfg, require_gpu=True)
+        kv, layout = alloc_paged_cache(shape, 64, "cpu", "vllm", fill="normal", seed=seed)
+        mgr.register_gpu_tensors(kv, layout)
+        mgr.start(); mgr.wait_ready(30)
+        return mgr, kv
+
+    a, kva = start(1)
+    b, kvb = start(2)
+    try:
+        ea = a.kv_task_engine.cache_engine.cpu_cache_engine
+        eb = b.kv_task_engine.cache_engine.cpu_cache_engine
+        assert type(ea.channel).__name__ == "RedisMetaChannel" and {ea.node_id, eb.node_id} == {1, 2}
+        tok = np.arange(6 * T, dtype=np.int64) + 500
+        src = np.array([5, 6, 7, 20, 21, 3])
+        tid = a.put_async(tok, slots(src))
+        assert a.wait(tid, completely=True)[tid].status.value == "success"
+        ea.refresh(); eb.refresh()
+        assert any(k.startswith(b"CPUB:block:") for k in server.store.d)
+        tid, mask = b.get_match(tok)
+        assert int(mask.sum()) == 6 * T
+        assert sorted(o.transfer_type.value for o in b.kv_task_engine.tasks[tid].graph.ops()) == ["H2D", "PEERH2H"]
+        dst = np.arange(40, 46)
+        b.launch(tid, slots(dst))
+        assert b.wait(tid)[tid].status.value == "success"
+        for l in range(2):
+            assert torch.equal(kvb[l][:, dst], kva[l][:, src])
+    finally:
+        a.shutdown()
+        b.shutdown()
+    assert not any(k.startswith(b"node:") for k in server.store.d)          # both left the registry
