@@ -275,7 +275,14 @@ class GlobalCacheEngine:
         elif cache_config.enable_cpu:
             self.cpu_cache_engine = CacheEngine(DeviceType.CPU, cache_config.num_cpu_blocks, **common)
             self.cache_engines[DeviceType.CPU] = self.cpu_cache_engine
-        if cache_config.enable_ssd:
+        if cache_config.enable_ssd and cache_config.enable_p2p_ssd:
+            # SSD blocks are published too: another node may read them straight out of this node's block files
+            from .hie_cache_engine import HierarchyLRCacheEngine, get_node_registry
+            self.node_registry = self.node_registry or get_node_registry(cache_config, model_config)
+            self.ssd_cache_engine = HierarchyLRCacheEngine(DeviceType.SSD, cache_config.num_ssd_blocks,
+                                                           registry=self.node_registry, **common)
+            self.cache_engines[DeviceType.SSD] = self.ssd_cache_engine
+        elif cache_config.enable_ssd:
             self.ssd_cache_engine = CacheEngine(DeviceType.SSD, cache_config.num_ssd_blocks, **common)
             self.cache_engines[DeviceType.SSD] = self.ssd_cache_engine
         if cache_config.enable_remote and cache_config.num_remote_blocks and \
@@ -538,8 +545,8 @@ class GlobalCacheEngine:
             f3_lo = max(bstart, end)
             f3 = max(0, r_hit - f3_lo)
         # fragment 3 may instead come from another node's host pool when that node holds a longer prefix
-        peer_host_nids = None
-        if self.node_registry is not None and not cpu_only and not use_gds_early:
+        peer_host_nids, peer_is_ssd = None, False
+        if self.node_registry is not None and not cpu_only and not use_gds_early and hasattr(cpu, "match_remote"):
             pm = cpu.match_remote(seq, bend)
             if pm.num_matched_blocks > max(end, f3_lo + f3):
                 f3_lo = max(bstart, end)
@@ -547,6 +554,16 @@ class GlobalCacheEngine:
                 peer_host_nids = pm.node_ids[f3_lo:f3_lo + f3]
                 peer_host_src = pm.physical_blocks[f3_lo:f3_lo + f3]
                 remote_m = None
+        # ... or from another node's SSD tier when that reaches further still (read out of its block files)
+        if self.node_registry is not None and not cpu_only and not use_gds_early and \
+                hasattr(self.ssd_cache_engine, "match_remote"):
+            sm = self.ssd_cache_engine.match_remote(seq, bend)
+            if sm.num_matched_blocks > max(end, f3_lo + f3):
+                f3_lo = max(bstart, end)
+                f3 = sm.num_matched_blocks - f3_lo
+                peer_host_nids = sm.node_ids[f3_lo:f3_lo + f3]
+                peer_host_src = sm.physical_blocks[f3_lo:f3_lo + f3]
+                peer_is_ssd, remote_m = True, None
         if f0 + f1 + f2 + f3 == 0:
             return None
         graph = TransferOpGraph()
@@ -611,7 +628,9 @@ class GlobalCacheEngine:
             hashes3 = seq.block_hashes[f3_lo:f3_lo + f3]
             src3 = remote_m.physical_blocks[f3_lo:f3_lo + f3] if remote_m is not None else np.zeros(f3, dtype=np.int64)
             if peer_host_nids is not None:
-                remote_op = TransferOp(graph.graph_id, TransferType.PEERH2H, peer_host_src, staging3,
+                remote_op = TransferOp(graph.graph_id,
+                                       TransferType.PEERSSD2H if peer_is_ssd else TransferType.PEERH2H,
+                                       peer_host_src, staging3,
                                        dp_client_id=dp_client_id, block_hashes=hashes3,
                                        remote_node_ids=peer_host_nids)
             else:

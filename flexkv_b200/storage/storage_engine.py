@@ -167,7 +167,8 @@ class StorageEngine:
                          compression_enabled=bool(c.enable_compression or self.env.enable_compression),
                          dtype=m.dtype, host_layout_type=lay.type, chunk_elems_per_rank=lay.get_chunk_size() // slices,
                          itemsize=m.dtype.itemsize, layerwise=bool(self.env.enable_layerwise_transfer),
-                         peer_host_sharing=bool(c.enable_p2p_cpu), pipeline_stages=m.local_pp_stages)
+                         peer_host_sharing=bool(c.enable_p2p_cpu or c.enable_p2p_ssd),
+                         pipeline_stages=m.local_pp_stages)
         if d.reason:
             flexkv_logger.warning("host codec refused: %s; every tier runs uncompressed", d.reason)
         if d.warning:

@@ -15,7 +15,7 @@ import queue
 import threading
 import time
 from dataclasses import dataclass
-from typing import Callable, Dict, Optional, Tuple
+from typing import Any, Callable, Dict, Optional, Tuple
 
 import numpy as np
 
@@ -826,6 +826,81 @@ class PeerHostWorker(TransferWorker):
                          error="" if ok else f"{n - sum(results)} peer block(s) failed: {err}")
 
 
+class PeerSsdWorker(TransferWorker):
+    """PEERSSD2H: reads blocks that only another node's SSD tier holds straight out of that node's block files
+    into this node's host pool. The owner published its file list and geometry in the registry; files are
+    opened once per owner through this node's own IO engine (io_uring / O_DIRECT where they allow it). The
+    reference asks the owner over ZeroMQ to stage the block and reads the staging buffer with RDMA
+    (flexkv/transfer/worker.py:2920-3873); on one box, or over a shared mount, the files themselves are
+    reachable. The owner's lease keeps the blocks in place while they are read."""
+
+    name = "peerssd2h"
+
+    def __init__(self, storage, registry) -> None:
+        super().__init__()
+        self.storage, self.registry = storage, registry
+        self._engines: Dict[int, Tuple[Any, int]] = {}
+
+    def _engine_of(self, nid: int):
+        ent = self._engines.get(nid)
+        if ent is not None:
+            return ent
+        import json
+        meta = self.registry.get_node_meta(nid)
+        if not meta or not meta.get("ssd_files"):
+            raise RuntimeError(f"node {nid} has no SSD tier in the registry")
+        st = self.storage
+        mine = json.dumps(st.ssd_layout_dict(), sort_keys=True)
+        if int(meta["ssd_block_bytes"]) != st.ssd.block_bytes or str(meta.get("ssd_layout")) != mine or \
+                meta.get("codec", "none") != st.host.quant:
+            raise RuntimeError(f"node {nid} uses a different SSD block format")
+        files = json.loads(meta["ssd_files"])
+        env = GLOBAL_CONFIG_FROM_ENV
+        eng = _native.C.SsdIoEngine(files, int(meta["ssd_block_bytes"]), int(meta["ssd_blocks_per_file"]),
+                                    create=False, try_direct=True, iouring_entries=env.iouring_entries,
+                                    num_threads=max(2, env.ssd_io_threads // 2))
+        ent = (eng, int(meta["ssd_num_blocks"]))
+        self._engines[nid] = ent
+        return ent
+
+    def execute(self, op: TransferOp) -> OpOutcome:
+        src, dst, nids = op.src_block_ids, op.dst_block_ids, op.remote_node_ids
+        if nids is None or len(nids) != len(src) or len(src) != len(dst):
+            return OpOutcome(False, error="peer SSD op without owner ids")
+        st = self.storage
+        n = len(src)
+        results = [False] * n
+        err = ""
+        src = np.asarray(src, dtype=np.int64)
+        dst = np.asarray(dst, dtype=np.int64)
+        owners = np.asarray(nids, dtype=np.int64)
+        lay = st.ssd_layout_dict()
+        for nid in np.unique(owners).tolist():
+            sel = np.nonzero(owners == nid)[0]
+            try:
+                eng, nblk = self._engine_of(int(nid))
+                s_ids = np.ascontiguousarray(src[sel])
+                d_ids = np.ascontiguousarray(dst[sel])
+                if s_ids.min() < 0 or s_ids.max() >= nblk:
+                    raise RuntimeError(f"block {int(s_ids.max())} outside node {nid}'s SSD tier")
+                if d_ids.min() < 0 or d_ids.max() >= st.host.num_blocks:
+                    raise RuntimeError(f"destination block {int(d_ids.max())} outside the host pool")
+                nfail, ok = eng.transfer(st.host.base, d_ids, s_ids, True, lay, 0, lay["num_layers"])
+                for k, good in zip(sel.tolist(), ok):
+                    results[k] = bool(good)
+                if nfail:
+                    err = f"{nfail} read(s) from node {nid}'s files failed"
+            except (RuntimeError, OSError, ValueError) as e:
+                err = str(e)
+                self._engines.pop(int(nid), None)
+        ok_all = all(results)
+        return OpOutcome(ok_all, block_results=tuple(results), num_bytes=sum(results) * st.host.block_bytes,
+                         error="" if ok_all else f"{n - sum(results)} peer SSD block(s) failed: {err}")
+
+    def close(self) -> None:
+        self._engines.clear()
+
+
 _GDS_PROBE: Optional[Tuple[bool, str]] = None
 
 
@@ -1041,6 +1116,10 @@ def build_workers(storage, model_config: ModelConfig, cache_config: CacheConfig
     if cache_config.enable_p2p_cpu and storage.host is not None:
         from ..cache.hie_cache_engine import get_node_registry
         workers[(WorkerKey(0, 0), TransferType.PEERH2H)] = PeerHostWorker(
+            storage, get_node_registry(cache_config, model_config))
+    if cache_config.enable_p2p_ssd and storage.ssd is not None and storage.host is not None:
+        from ..cache.hie_cache_engine import get_node_registry
+        workers[(WorkerKey(0, 0), TransferType.PEERSSD2H)] = PeerSsdWorker(
             storage, get_node_registry(cache_config, model_config))
     if storage.ssd is not None:
         k0 = WorkerKey(0, 0)

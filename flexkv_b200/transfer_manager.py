@@ -146,6 +146,16 @@ class TransferManager:
                                        block_bytes=self.storage.host.block_bytes,
                                        num_blocks=self.storage.host.num_blocks, pid=os.getpid(),
                                        codec=self.storage.host.quant))
+            if self.cache_config.enable_p2p_ssd and self.storage.ssd is not None:
+                # what a peer needs to read this node's SSD blocks out of their files
+                import json
+                from .cache.hie_cache_engine import get_node_registry
+                reg = get_node_registry(self.cache_config, self.model_config)
+                ssd = self.storage.ssd
+                reg.set_node_meta(dict(ssd_files=json.dumps(ssd.files), ssd_block_bytes=ssd.block_bytes,
+                                       ssd_blocks_per_file=ssd.blocks_per_file, ssd_num_blocks=ssd.num_blocks,
+                                       ssd_layout=json.dumps(self.storage.ssd_layout_dict(), sort_keys=True),
+                                       codec=self.storage.host.quant))
             # graph state in the native scheduler (default) or the Python specification of it
             engine_cls = TransferEngine if GLOBAL_CONFIG_FROM_ENV.native_scheduler else TransferEngineSpec
             self.engine = engine_cls(self.storage, self.model_config, self.cache_config)

@@ -155,3 +155,59 @@ def test_registry_over_zeromq(tmp_path):
             c1._call("no_such_command")
     finally:
         srv.close()
+
+
+def test_node_b_restores_from_node_a_ssd_files(tmp_path):
+    """A prefix that node A holds only on SSD (its host pool is too small to keep it) is read by node B out of
+    A's block files (PEERSSD2H), staged in B's host pool and restored (reference: PEER2CPUTransferWorker's
+    peer-SSD path, flexkv/transfer/worker.py:2920-3873; planner flexkv/cache/cache_engine.py:2963-3060)."""
+    name = uuid.uuid4().hex
+    shape = KVShape("p", 2, 2, 16, tokens_per_block=T)
+
+    def start(seed, sub, cpu_blocks):
+        cfg = CacheConfig(tokens_per_block=T, num_cpu_blocks=cpu_blocks, enable_ssd=True, num_ssd_blocks=64,
+                          ssd_cache_dir=str(tmp_path / sub), enable_p2p_cpu=True, enable_p2p_ssd=True,
+                          redis_host=f"inproc:{name}")
+        mgr = KVManager(make_model_config(shape), cfg, require_gpu=True)
+        kv, layout = alloc_paged_cache(shape, 64, "cpu", "vllm", fill="normal", seed=seed)
+        mgr.register_gpu_tensors(kv, layout)
+        mgr.start(); mgr.wait_ready(30)
+        return mgr, kv
+
+    a, kva = start(1, "a", 12)
+    b, kvb = start(2, "b", 24)
+    try:
+        ga, gb = a.kv_task_engine.cache_engine, b.kv_task_engine.cache_engine
+        tok = np.arange(10 * T, dtype=np.int64) + 7000
+        src = np.array([5, 6, 7, 20, 21, 3, 40, 41, 42, 43])
+        tid = a.put_async(tok, slots(src))
+        assert a.wait(tid, completely=True)[tid].status.value == "success"
+        # push the prefix out of A's 12-block host pool: only the SSD tier keeps it
+        other = np.arange(10 * T, dtype=np.int64) + 90000
+        tid = a.put_async(other, slots(np.arange(50, 60)))
+        assert a.wait(tid, completely=True)[tid].status.value == "success"
+        from flexkv_b200.common.block import SequenceMeta
+        seq = SequenceMeta(tok, T)
+        assert ga.cpu_cache_engine.match(seq).num_ready_matched_blocks < 10
+        assert ga.ssd_cache_engine.match(seq).num_ready_matched_blocks == 10
+        for e in (ga.cpu_cache_engine, ga.ssd_cache_engine, gb.cpu_cache_engine, gb.ssd_cache_engine):
+            e.refresh()
+        assert gb.ssd_cache_engine.match_remote(seq).num_matched_blocks == 10
+        tid, mask = b.get_match(tok)
+        assert int(mask.sum()) == 10 * T
+        kinds = sorted(o.transfer_type.value for o in b.kv_task_engine.tasks[tid].graph.ops())
+        assert "PEERSSD2H" in kinds and "H2D" in kinds, kinds
+        dst = np.arange(20, 30)
+        for t in kvb:
+            t[:, dst] = 0
+        b.launch(tid, slots(dst))
+        assert b.wait(tid, timeout=30)[tid].status.value == "success"
+        for l in range(2):
+            assert torch.equal(kvb[l][:, dst], kva[l][:, src])
+        # adopted by B's host tier: the next get is local
+        tid, mask = b.get_match(tok)
+        assert [o.transfer_type.value for o in b.kv_task_engine.tasks[tid].graph.ops()] == ["H2D"]
+        b.cancel(tid)
+    finally:
+        a.shutdown()
+        b.shutdown()
