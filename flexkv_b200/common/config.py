@@ -321,6 +321,37 @@ class CacheConfig:
             raise ValueError("enable_gds requires enable_ssd")
         if self.offload_quant not in ("none", "fp8_e4m3"):
             raise ValueError(f"unknown offload_quant {self.offload_quant}")
+        if self.enable_nixl and self.enable_ssd and not self.enable_gds:
+            # NIXL's role here (SSD <-> GPU without the host pool) is the GDS worker's
+            self.enable_gds = True
+
+    def settings_without_effect(self) -> List[Tuple[str, str]]:
+        """Fields kept for compatibility with the reference's configuration that do nothing in this build when
+        set away from their defaults, each with the reason; the manager logs them at start-up so that a
+        deployment file written for the reference does not fail silently."""
+        out: List[Tuple[str, str]] = []
+        if self.enable_nixl:
+            out.append(("enable_nixl", "no NIXL library in this build: SSD <-> GPU ops run through the GDS worker "
+                                       "(cuFile when it opens, else a pinned bounce buffer)"
+                        if self.enable_ssd else "needs enable_ssd; no NIXL library in this build"))
+        if self.nixl_extra_config:
+            out.append(("nixl_extra_config", "no NIXL library in this build"))
+        if self.use_hugepage_tmp_buffer or self.num_tmp_cpu_blocks != 500:
+            out.append(("use_hugepage_tmp_buffer / num_tmp_cpu_blocks",
+                        "peer reads land in blocks of the host pool itself; there is no separate staging buffer"))
+        if self.mooncake_config_path or self.mooncake_store_config_path:
+            out.append(("mooncake_config_path / mooncake_store_config_path",
+                        "no Mooncake library in this build: peer reads map the owner's pool or block files, the "
+                        "key-addressed store is remote_config_custom"))
+        if self.enable_3rd_remote:
+            out.append(("enable_3rd_remote", "no PCFS SDK in this build: the remote tier is a block-addressed file "
+                                             "set (remote_cache_path) or a key-addressed store"))
+        if self.distributed_node_id >= 0:
+            out.append(("distributed_node_id", "node ids are allocated by the registry"))
+        if (self.local_zmq_ip, self.local_zmq_port) != ("127.0.0.1", 5555):
+            out.append(("local_zmq_ip / local_zmq_port", "peers are read through their pool and block files, not "
+                                                         "through a per-node ZeroMQ endpoint"))
+        return out
 
 
 def _env(name: str, default: Any, cast=None) -> Any:

@@ -43,6 +43,8 @@ class KVManager:
         self.gpu_register_port = gpu_register_port
         safe = {k: ("***" if "password" in k else v) for k, v in vars(cache_config).items() if not k.startswith("_")}
         flexkv_logger.debug("KVManager config: %s | %s", model_config, safe)
+        for name, why in cache_config.settings_without_effect():
+            flexkv_logger.warning("configuration: %s has no effect here: %s", name, why)
         # `in_process=True` keeps everything in this process even with several DP ranks (one process
         # that sees every GPU, e.g. tests and single-process benchmarks)
         self.server_client_mode = bool(env.server_client_mode or model_config.dp_size > 1

@@ -122,3 +122,16 @@ def test_response_helpers_keep_the_reference_names_and_values():
     with pytest.raises(AssertionError):
         r.get_mask(2)
     assert not KVResponse(KVResponseStatus.TIMEOUT, 4, None).ok and not KVResponseStatus.TIMEOUT.terminal
+
+
+def test_settings_kept_for_compatibility_are_reported_not_ignored_silently():
+    from flexkv_b200.common.config import CacheConfig
+    assert CacheConfig().settings_without_effect() == []
+    c = CacheConfig(enable_ssd=True, enable_nixl=True, num_tmp_cpu_blocks=64, mooncake_config_path="/x.json",
+                    enable_3rd_remote=True, distributed_node_id=3, local_zmq_port=6000)
+    assert c.enable_gds is True                     # NIXL's role (SSD <-> GPU) is served by the GDS worker
+    names = [n for n, _ in c.settings_without_effect()]
+    assert names == ["enable_nixl", "use_hugepage_tmp_buffer / num_tmp_cpu_blocks",
+                     "mooncake_config_path / mooncake_store_config_path", "enable_3rd_remote",
+                     "distributed_node_id", "local_zmq_ip / local_zmq_port"]
+    assert c.enable_kv_sharing and c.enable_remote
