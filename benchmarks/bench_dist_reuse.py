@@ -20,6 +20,8 @@ import numpy as np
 import torch
 
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+# only node B resets in the third round: do not wait long for node A's acknowledgement of that reset
+os.environ.setdefault("FLEXKV_RESET_BARRIER_TIMEOUT_MS", "500")
 from flexkv_b200 import CacheConfig, KVManager  # noqa: E402
 from flexkv_b200.common.transfer import TransferType  # noqa: E402
 from flexkv_b200.models import alloc_paged_cache, get_shape, make_model_config  # noqa: E402

@@ -60,14 +60,16 @@ class HierarchyLRCacheEngine(CacheEngine):
         self.channel = channel
         lease = int(lease_ttl_ms if lease_ttl_ms is not None else env.lease_ttl_ms)
         renew = int(renew_lease_ms if renew_lease_ms is not None else env.renew_lease_ms)
-        refresh = int(refresh_interval_ms if refresh_interval_ms is not None else getattr(env, "refresh_batch_ms", 100))
+        refresh = int(refresh_interval_ms if refresh_interval_ms is not None else 100)
+        # how often the read-only view of the other nodes' blocks is rebuilt (FLEXKV_REBUILD_INTERVAL_MS)
+        rebuild = int(refresh_interval_ms if refresh_interval_ms is not None else getattr(env, "rebuild_interval_ms", 2000))
         safety = int(safety_ttl_ms if safety_ttl_ms is not None else getattr(env, "safety_ttl_ms", 100))
         self.index = _native.C.LocalRadixTree(self.node_id, tokens_per_block, self.num_total_blocks, eviction_policy,
                                               float(hit_reward_seconds), self.channel, lease_ttl_ms=lease,
                                               renew_margin_ms=min(renew, max(1, lease - 1)),
                                               refresh_interval_ms=refresh, safety_ttl_ms=safety,
                                               start_thread=start_threads)
-        self.remote_view = _native.C.DistributedRadixTree(self.node_id, self.channel, refresh_interval_ms=refresh,
+        self.remote_view = _native.C.DistributedRadixTree(self.node_id, self.channel, refresh_interval_ms=rebuild,
                                                           safety_ttl_ms=safety, start_thread=start_threads)
         self.mempool = Mempool(self.num_total_blocks, native=True)
         self.on_evict, self.on_insert = [], []
@@ -94,13 +96,17 @@ class HierarchyLRCacheEngine(CacheEngine):
         self.remote_view.refresh_once()
 
     # ---- lifecycle ----------------------------------------------------------------------
-    def reset(self, barrier_timeout: float = 5.0) -> None:
+    def reset(self, barrier_timeout: Optional[float] = None) -> None:
         """Drops every local block, withdraws the published records and waits until all
-        live nodes acknowledged the same reset epoch."""
+        live nodes acknowledged the same reset epoch (FLEXKV_RESET_BARRIER_TIMEOUT_MS / _POLL_MS)."""
+        env = GLOBAL_CONFIG_FROM_ENV
+        if barrier_timeout is None:
+            barrier_timeout = float(getattr(env, "reset_barrier_timeout_ms", 60000)) / 1e3
         self.index.reset()
         self.mempool.reset()
         self._reset_epoch += 1
-        if not self.registry.reset_barrier(self._reset_epoch, timeout=barrier_timeout):
+        if not self.registry.reset_barrier(self._reset_epoch, timeout=barrier_timeout,
+                                           poll=float(getattr(env, "reset_barrier_poll_ms", 50)) / 1e3):
             flexkv_logger.warning("reset barrier %d timed out; some nodes may still list old blocks",
                                   self._reset_epoch)
         self.remote_view.refresh_once()

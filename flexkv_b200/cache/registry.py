@@ -325,7 +325,7 @@ class NodeRegistry:
         return self.client.hgetall(f"meta:{nid}")
 
     # ---- reset barrier -----------------------------------------------------------------
-    def reset_barrier(self, epoch: int, timeout: float = 10.0) -> bool:
+    def reset_barrier(self, epoch: int, timeout: float = 10.0, poll: float = 0.01) -> bool:
         """Every live node acknowledges reset ``epoch``; returns once all of them did
         (reference: flexkv/cache/hie_cache_engine.py:177-223)."""
         self.client.hset(f"reset:{epoch}", {str(self.node_id): 1}, ttl=max(timeout * 2, 5.0))
@@ -334,7 +334,7 @@ class NodeRegistry:
             acks = self.client.hgetall(f"reset:{epoch}")
             if all(str(n) in acks for n in self.active_nodes()):
                 return True
-            time.sleep(0.01)
+            time.sleep(max(0.001, poll))
         return False
 
 

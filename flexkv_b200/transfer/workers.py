@@ -137,6 +137,8 @@ def build_transfer_group(storage, model_config: ModelConfig, key: WorkerKey, hig
     opts = dict(num_layers=reg0.num_layers, kv_dim=reg0.kv_dim, chunk_bytes=reg0.chunk_bytes,
                 cpu_tp_stride=tp_stride, shared_kv=shared, shared_mode=env.kv_shared_across_ranks_mode,
                 h2d=_launch_cfg(env, True), d2h=_launch_cfg(env, False), high_priority_stream=high_priority,
+                **({"ce_max_copies": int(os.environ["FLEXKV_CE_SEGMENT_THRESHOLD"])}
+                   if os.environ.get("FLEXKV_CE_SEGMENT_THRESHOLD") else {}),
                 max_blocks_per_op=max_blocks_per_op or max(4096, min(1 << 18, host.num_blocks)))
     return _native.C.TransferGroup(gpus, host_d, opts)
 
