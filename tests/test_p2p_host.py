@@ -211,3 +211,40 @@ def test_node_b_restores_from_node_a_ssd_files(tmp_path):
     finally:
         a.shutdown()
         b.shutdown()
+
+
+def test_cluster_wide_reset_withdraws_every_nodes_blocks():
+    """Both nodes reset at the same time: each drops its blocks, withdraws its published records and returns
+    once the other has acknowledged the same epoch; afterwards neither finds the old prefix anywhere
+    (reference: tests/test_hierarchy_reset.py, flexkv/cache/hie_cache_engine.py:177-223)."""
+    import threading
+    name = uuid.uuid4().hex
+    a, kva = start_node(name, 1)
+    b, kvb = start_node(name, 2)
+    try:
+        ea = a.kv_task_engine.cache_engine.cpu_cache_engine
+        eb = b.kv_task_engine.cache_engine.cpu_cache_engine
+        tok = np.arange(6 * T, dtype=np.int64) + 300
+        tid = a.put_async(tok, slots([1, 2, 3, 4, 5, 6]))
+        assert a.wait(tid, completely=True)[tid].status.value == "success"
+        ea.refresh(); eb.refresh()
+        assert int(b.get_match(tok)[1].sum()) == 6 * T
+        t0 = time.monotonic()
+        ths = [threading.Thread(target=m.reset) for m in (a, b)]
+        for t in ths:
+            t.start()
+        for t in ths:
+            t.join(30)
+        assert time.monotonic() - t0 < 10, "the reset barrier ran into its timeout"
+        ea.refresh(); eb.refresh()
+        assert int(a.get_match(tok)[1].sum()) == 0 and int(b.get_match(tok)[1].sum()) == 0
+        assert ea.channel.load(ea.node_id) == [] and eb.match_remote(
+            __import__("flexkv_b200.common.block", fromlist=["SequenceMeta"]).SequenceMeta(tok, T)).num_matched_blocks == 0
+        # the tiers work again afterwards
+        tid = b.put_async(tok, slots([7, 8, 9, 10, 11, 12]))
+        assert b.wait(tid, completely=True)[tid].status.value == "success"
+        eb.refresh(); ea.refresh()                          # B publishes, then A rebuilds its view
+        assert int(a.get_match(tok)[1].sum()) == 6 * T
+    finally:
+        a.shutdown()
+        b.shutdown()
