@@ -12,6 +12,26 @@ import numpy as np
 import torch
 
 
+def _write_combined_host_tensor(n: int) -> torch.Tensor:
+    """n bytes from cudaHostAlloc(portable | write-combined), wrapped as a tensor; never freed (benchmark)."""
+    import ctypes
+    import glob
+    import site
+    libs = []
+    for root in site.getsitepackages() + [os.path.dirname(torch.__file__)]:
+        libs += glob.glob(os.path.join(root, "nvidia", "cuda_runtime", "lib", "libcudart.so*"))
+        libs += glob.glob(os.path.join(root, "lib", "libcudart*.so*"))
+    rt = ctypes.CDLL(libs[0] if libs else "libcudart.so")
+    ptr = ctypes.c_void_p()
+    rc = rt.cudaHostAlloc(ctypes.byref(ptr), ctypes.c_size_t(n), ctypes.c_uint(0x01 | 0x04))
+    if rc != 0 or not ptr.value:
+        raise RuntimeError(f"cudaHostAlloc(write-combined) failed with error {rc}")
+    buf = (ctypes.c_uint8 * n).from_address(ptr.value)
+    t = torch.frombuffer(buf, dtype=torch.uint8)
+    t._keep = buf
+    return t
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gib", type=float, default=4.0)
@@ -20,6 +40,9 @@ def main() -> None:
                     help="also copy the same bytes as one cudaMemcpyAsync per block of this size, blocks at random "
                          "positions on both sides (what a copy-engine path without staging would issue)")
     ap.add_argument("--streams", type=int, nargs="*", default=[1, 4])
+    ap.add_argument("--host-alloc", default="pinned", choices=["pinned", "wc"],
+                    help="wc: the host buffer comes from cudaHostAlloc with the write-combined flag (the CPU does "
+                         "not cache it, so device writes need no snoop of CPU caches)")
     a = ap.parse_args()
     world = int(os.environ.get("WORLD_SIZE", 1))
     rank = int(os.environ.get("RANK", 0))
@@ -31,8 +54,11 @@ def main() -> None:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
     n = int(a.gib * 2**30)
-    host = torch.empty(n, dtype=torch.uint8).pin_memory()
-    host.fill_(1)
+    if a.host_alloc == "wc":
+        host = _write_combined_host_tensor(n)
+    else:
+        host = torch.empty(n, dtype=torch.uint8).pin_memory()
+        host.fill_(1)
     gpu = torch.empty(n, dtype=torch.uint8, device=dev)
     out = {}
     for name, (dst, src) in (("d2h", (host, gpu)), ("h2d", (gpu, host))):
@@ -102,7 +128,8 @@ def main() -> None:
             ms.append(float(t.item()))
     out["bidirectional_gbs_per_gpu_sum"] = round(2 * n / float(np.median(ms)) / 1e6, 2)
     if rank == 0:
-        print(json.dumps(dict(benchmark="memcpy_baseline", gpus=world, gib_per_copy=a.gib, **out)))
+        print(json.dumps(dict(benchmark="memcpy_baseline", gpus=world, gib_per_copy=a.gib, host_alloc=a.host_alloc,
+                         host_is_pinned=bool(host.is_pinned()), **out)))
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()
