@@ -107,9 +107,16 @@ class KVServer:
                 gone = self._clients.pop(self._leaving.pop(), None)
                 if gone is not None:
                     gone.close(linger=1000)
+        # waits still parked get their answer (what has finished, TIMEOUT for the rest) before the sockets close
+        for q, _ in self._parked:
+            try:
+                self._reply(R.Response(q.dp_client_id, q.seq, status=self.engine.wait(q.task_ids, 0.0, q.completely)))
+            except Exception:  # noqa: BLE001
+                pass
+        self._parked = []
         self.engine.shutdown()
         for s in self._clients.values():
-            s.close()
+            s.close(linger=1000)
         self._recv.close()
 
     def _reply(self, rsp: R.Response) -> None:
