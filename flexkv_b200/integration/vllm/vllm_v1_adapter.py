@@ -412,6 +412,33 @@ class FlexKVWorkerConnector:
             self.client.resume_gpu_mappings(self._caches, self._layout)
 
 
+_VLLM_TYPES: Optional[dict] = None
+
+
+class _PlainConnectorMetadata:
+    """Stand-in for the step record where vLLM is not importable (tests with fake engine objects)."""
+
+    def __init__(self, finished_sending=(), finished_recving=()) -> None:
+        self.finished_sending = set(finished_sending)
+        self.finished_recving = set(finished_recving)
+
+    def __getitem__(self, key):
+        return {"finished_sending": self.finished_sending, "finished_recving": self.finished_recving}[key]
+
+
+def _vllm_types() -> dict:
+    """vLLM's own metadata and stats base classes when vLLM is importable (its scheduler and logger check the
+    types of what a connector returns), plain stand-ins otherwise. Resolved once, on first use."""
+    global _VLLM_TYPES
+    if _VLLM_TYPES is None:
+        try:
+            from . import vllm_types as vt
+            _VLLM_TYPES = dict(meta=vt.FlexKVConnectorMetadata, stats=vt.FlexKVConnectorStats)
+        except Exception:  # noqa: BLE001 - no vLLM here
+            _VLLM_TYPES = dict(meta=_PlainConnectorMetadata, stats=None)
+    return _VLLM_TYPES
+
+
 class FlexKVConnectorV1Impl:
     """Role-dispatching object behind vLLM's ``KVConnectorBase_V1`` interface."""
 
@@ -463,7 +490,7 @@ class FlexKVConnectorV1Impl:
     def update_state_after_alloc(self, request: Any, blocks: Any, num_external_tokens: int) -> None:
         self.scheduler.update_state_after_alloc(request, blocks, num_external_tokens)
 
-    def build_connector_meta(self, scheduler_output: Any) -> dict:
+    def build_connector_meta(self, scheduler_output: Any):
         s = self.scheduler
         pre = getattr(scheduler_output, "preempted_req_ids", None)
         if pre:
@@ -471,7 +498,7 @@ class FlexKVConnectorV1Impl:
         s.flush_cancels()
         s.launch_tasks()
         sending, recving = s.query_finished_task()
-        return {"finished_sending": sending, "finished_recving": recving}
+        return _vllm_types()["meta"](sending, recving)
 
     def update_connector_output(self, connector_output: Any) -> None: ...
 
@@ -486,13 +513,15 @@ class FlexKVConnectorV1Impl:
     def get_kv_connector_stats(self) -> Optional[dict]:
         """Counters of the last interval. The worker side returns an empty (non-None) record so that the
         engine keeps polling for finished transfers on steps that schedule no tokens."""
+        cls = _vllm_types()["stats"]
         if not self.is_scheduler:
-            return {}
+            return {} if cls is None else cls(data={})
         st = self.scheduler.stats
-        return dict(num_get_requests=st.num_get_requests, num_get_query_tokens=st.num_get_query_tokens,
+        d = dict(num_get_requests=st.num_get_requests, num_get_query_tokens=st.num_get_query_tokens,
                     num_gpu_matched_tokens=st.num_gpu_matched_tokens,
                     num_flexkv_matched_tokens=st.num_flexkv_matched_tokens, num_put_requests=st.num_put_requests,
                     num_put_unmatched_tokens=st.num_put_unmatched_tokens, num_failed_requests=st.num_failed_requests)
+        return d if cls is None else cls(data=d)
 
     def get_block_ids_with_load_errors(self) -> Set[int]:
         return self.scheduler.get_and_clear_failed_block_ids() if self.scheduler else set()
