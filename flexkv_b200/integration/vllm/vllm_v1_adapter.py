@@ -458,6 +458,7 @@ class FlexKVConnectorV1Impl:
             self.scheduler = None
         self._finished_sending: Set[str] = set()
         self._finished_recving: Set[str] = set()
+        self._previous_scheduled: Set[str] = set()
 
     # worker side: data moves outside the forward pass, so these hooks are no-ops
     def start_load_kv(self, forward_context: Any, **kw: Any) -> None: ...
@@ -493,14 +494,42 @@ class FlexKVConnectorV1Impl:
     def build_connector_meta(self, scheduler_output: Any):
         s = self.scheduler
         pre = getattr(scheduler_output, "preempted_req_ids", None)
+        if pre is None:
+            # engines whose scheduler output does not name the preempted requests: whoever was scheduled in the
+            # last step, is not scheduled now and did not finish was preempted
+            now = {getattr(r, "req_id", None) for r in (getattr(scheduler_output, "scheduled_new_reqs", None) or [])}
+            cached = getattr(scheduler_output, "scheduled_cached_reqs", None)
+            now.update(getattr(cached, "req_ids", None) or [])
+            now.discard(None)
+            done = set(getattr(scheduler_output, "finished_req_ids", None) or [])
+            pre = self._previous_scheduled - now - done
+            self._previous_scheduled = now
         if pre:
             s.handle_preemptions(pre)
         s.flush_cancels()
         s.launch_tasks()
         sending, recving = s.query_finished_task()
+        # finished transfers reach the engine through update_connector_output (below); engines that read the
+        # step record instead get them there as well
+        self._finished_sending |= set(sending)
+        self._finished_recving |= set(recving)
         return _vllm_types()["meta"](sending, recving)
 
-    def update_connector_output(self, connector_output: Any) -> None: ...
+    def update_connector_output(self, connector_output: Any) -> None:
+        """Scheduler side, once per step after the model runner's output came back: the requests whose offload
+        or restore has finished are written into the engine's connector output, which is what releases a
+        finished request's pages and resumes a request that waited for its restore
+        (reference: flexkv/integration/vllm/vllm_v1_adapter.py:1204-1220)."""
+        if not self.is_scheduler or connector_output is None:
+            return
+        sending, recving = self.scheduler.query_finished_task()
+        sending = set(sending) | self._finished_sending
+        recving = set(recving) | self._finished_recving
+        self._finished_sending, self._finished_recving = set(), set()
+        for name, got in (("finished_sending", sending), ("finished_recving", recving)):
+            have = getattr(connector_output, name, None)
+            merged = (set(have) if have else set()) | got
+            setattr(connector_output, name, merged if merged else have)
 
     def request_finished(self, request: Any, block_ids: Sequence[int]) -> Tuple[bool, Optional[dict]]:
         return self.scheduler.request_finished(request, block_ids)

@@ -233,3 +233,36 @@ def test_aborted_requests_offload_only_on_request():
         assert s == {"ok-STOP", "ok-LENGTH", "y"}
     finally:
         conn.shutdown()
+
+
+def test_impl_reports_finished_transfers_through_the_engines_connector_output():
+    """The step loop as vLLM drives it: ``build_connector_meta`` launches, ``update_connector_output`` writes the
+    finished request ids into the engine's own output record (merged with what is already there), and a scheduler
+    output without ``preempted_req_ids`` gets the preempted set from the difference of consecutive steps."""
+    import time
+    from flexkv_b200.integration.vllm.vllm_v1_adapter import FlexKVConnectorV1Impl
+    conn, kv, mgr = make()
+    impl = FlexKVConnectorV1Impl.__new__(FlexKVConnectorV1Impl)
+    impl.is_scheduler, impl.scheduler, impl.worker = True, conn, None
+    impl._finished_sending, impl._finished_recving, impl._previous_scheduled = set(), set(), set()
+    try:
+        tok = np.arange(500, 500 + 5 * T + 1)
+        keep, _ = impl.request_finished(req("a", tok), [1, 2, 3, 4, 5, 6])
+        assert keep
+        step = NS(scheduled_new_reqs=[NS(req_id="x")], scheduled_cached_reqs=NS(req_ids=["y"]), finished_req_ids=set())
+        meta = impl.build_connector_meta(step)                      # launches the put
+        out = NS(finished_sending={"earlier"}, finished_recving=None)
+        t0 = time.time()
+        while "a" not in (out.finished_sending or ()) and time.time() - t0 < 10:
+            impl.update_connector_output(out)
+            time.sleep(0.005)
+        assert out.finished_sending == {"earlier", "a"} and not out.finished_recving
+        assert hasattr(meta, "finished_sending")
+        # next step: "x" is gone without having finished -> treated as preempted; "y" finished
+        seen = []
+        conn.handle_preemptions = lambda ids: seen.append(set(ids))
+        impl.build_connector_meta(NS(scheduled_new_reqs=[], scheduled_cached_reqs=None, finished_req_ids={"y"}))
+        assert seen == [{"x"}]
+        impl.update_connector_output(None)                          # tolerated
+    finally:
+        conn.shutdown()
