@@ -58,7 +58,33 @@ def main() -> None:
                 best, parts = dt, (res["a"], res["b"])
         return best, parts
 
+    # the router's staged route: scattered GPU pages, host blocks in two runs (what a fresh allocation gives): the
+    # kernel gathers into device staging, the copy engines cross the link, one direction per engine
+    g_out.set_launch(False, 8, 16384, 3)
+    g_in.set_launch(True, 8, 16384, 3)
+    gp = rng.permutation(NB)
+    ga, gb = gp[:n].astype(np.int64), gp[n:2 * n].astype(np.int64)
+    ca, cb = np.arange(0, n, dtype=np.int64), np.arange(n, 2 * n, dtype=np.int64)
+
+    def d2h_staged():
+        o = g_out.transfer(ga, ca, False, 0, shape.num_layers)
+        assert o.status == 0, o.status
+        return o.gpu_ms
+
+    def h2d_staged():
+        o = g_in.transfer(gb, cb, True, 0, shape.num_layers)
+        assert o.status == 0, o.status
+        return o.gpu_ms
+    ms, (m_out, m_in) = pair(d2h_staged, h2d_staged)
+    row = dict(engine="router: gather into staging + copy engines (host blocks in runs)", pair_ms=round(ms, 2),
+               both_gbs=round(2 * n * bb / ms / 1e6, 2), d2h_gbs=round(n * bb / m_out / 1e6, 2),
+               h2d_gbs=round(n * bb / m_in / 1e6, 2), staged_ops=[int(g_out.staged_ops), int(g_in.staged_ops)])
+    rows.append(row)
+    print(json.dumps(row), flush=True)
+
     for engine, name in ((0, "tma"), (1, "simt")):
+        if "--staged-only" in sys.argv:
+            break
         for ctas in (4, 8, 16, 32, 64):
             for tile in ((8192, 16384, 32768) if engine == 0 else (16384,)):
                 g_out.set_launch(False, ctas, tile, engine)
@@ -102,7 +128,7 @@ def main() -> None:
     row = dict(engine="copy engines, contiguous", pair_ms=round(best, 2), both_gbs=round(2 * nbytes / best / 1e6, 2))
     rows.append(row)
     print(json.dumps(row), flush=True)
-    if len(sys.argv) > 1:
+    if len(sys.argv) > 1 and not sys.argv[1].startswith("--"):
         os.makedirs(os.path.dirname(os.path.abspath(sys.argv[1])), exist_ok=True)
         with open(sys.argv[1], "w") as f:
             json.dump(rows, f, indent=1)
