@@ -382,25 +382,34 @@ class GlobalCacheEngine:
             self.node_registry = None
 
     def _prepare(self, token_ids: np.ndarray, token_mask: Optional[np.ndarray], slot_mapping: Optional[np.ndarray]
-                 ) -> Tuple[np.ndarray, np.ndarray, int]:
+                 ) -> Tuple[np.ndarray, np.ndarray, int, int, int]:
+        """Validated inputs plus the block range ``[bstart, bend)`` the mask selects. Without a mask (the usual
+        call) the range is the whole aligned prefix and nothing is scanned."""
         if token_ids.ndim != 1:
             raise ValueError("token_ids must be 1-D")
         token_ids = np.ascontiguousarray(token_ids, dtype=np.int64)
+        n = token_ids.shape[0]
+        tpb = self.tokens_per_block
+        aligned = (n // tpb) * tpb
+        if slot_mapping is not None and slot_mapping.ndim != 1:
+            raise ValueError("slot_mapping must be 1-D")
         if token_mask is None:
-            token_mask = np.ones(token_ids.shape[0], dtype=np.bool_)
-        else:
-            token_mask = np.array(token_mask, dtype=np.bool_, copy=True)
+            if slot_mapping is not None and slot_mapping.size != n:
+                raise ValueError(f"slot_mapping has {slot_mapping.size} entries, token_mask selects {n} tokens")
+            token_mask = np.ones(n, dtype=np.bool_)
+            token_mask[aligned:] = False
+            return token_ids, token_mask, aligned, 0, aligned // tpb
+        token_mask = np.array(token_mask, dtype=np.bool_, copy=True)
         if token_mask.shape != token_ids.shape:
             raise ValueError(f"token_mask has {token_mask.size} entries for {token_ids.size} tokens")
         if slot_mapping is not None:
-            if slot_mapping.ndim != 1:
-                raise ValueError("slot_mapping must be 1-D")
-            if slot_mapping.size != int(token_mask.sum()):
+            selected = int(token_mask.sum())
+            if slot_mapping.size != selected:
                 raise ValueError(f"slot_mapping has {slot_mapping.size} entries, token_mask selects "
-                                 f"{int(token_mask.sum())} tokens")
-        aligned = (token_ids.shape[0] // self.tokens_per_block) * self.tokens_per_block
+                                 f"{selected} tokens")
         token_mask[aligned:] = False
-        return token_ids, token_mask, aligned
+        bstart, bend = _block_range(token_mask, tpb)
+        return token_ids, token_mask, aligned, bstart, bend
 
     def _empty(self, token_mask: np.ndarray):
         handle = TransferPlanHandle(lambda: None, lambda: None)
@@ -427,11 +436,10 @@ class GlobalCacheEngine:
             slot_mapping: Optional[np.ndarray], dp_client_id: int = 0, namespace: Optional[List[str]] = None,
             cpu_only: bool = False, prefetch: bool = False, swa_aware: bool = False):
         """Returns ``(graph, return_mask, plan_handle, op_callbacks, task_end_op_id)``."""
-        token_ids, token_mask, aligned = self._prepare(token_ids, token_mask, slot_mapping)
-        if aligned == 0 or not token_mask.any():
+        token_ids, token_mask, aligned, bstart, bend = self._prepare(token_ids, token_mask, slot_mapping)
+        if aligned == 0 or bend <= bstart:
             return self._empty(token_mask)
         tpb = self.tokens_per_block
-        bstart, bend = _block_range(token_mask, tpb)
         gpu_blocks = None
         if slot_mapping is not None:
             gpu_blocks = slot_mapping_to_block_ids(slot_mapping, tpb)[:bend - bstart]
@@ -487,11 +495,10 @@ class GlobalCacheEngine:
 
     def put(self, request_id: int, token_ids: np.ndarray, token_mask: Optional[np.ndarray],
             slot_mapping: Optional[np.ndarray], dp_client_id: int = 0, namespace: Optional[List[str]] = None):
-        token_ids, token_mask, aligned = self._prepare(token_ids, token_mask, slot_mapping)
-        if aligned == 0 or not token_mask.any():
+        token_ids, token_mask, aligned, bstart, bend = self._prepare(token_ids, token_mask, slot_mapping)
+        if aligned == 0 or bend <= bstart:
             return self._empty(token_mask)
         tpb = self.tokens_per_block
-        bstart, bend = _block_range(token_mask, tpb)
         if bstart != 0:
             raise ValueError("put: token_mask must select a prefix of the sequence")
         gpu_blocks = None

@@ -41,7 +41,8 @@ class TransferWorker:
     name = "worker"
 
     def __init__(self) -> None:
-        self._q: "queue.Queue[Optional[TransferOp]]" = queue.Queue()
+        # SimpleQueue: put and get are C calls (no Python-level condition variable on the submit path)
+        self._q: "queue.SimpleQueue[Optional[TransferOp]]" = queue.SimpleQueue()
         self._thread: Optional[threading.Thread] = None
         self._done_cb: Optional[Callable[[TransferOp, OpOutcome], None]] = None
         self.fail_next = 0          # host-side fault injection for tests: fail this many ops
