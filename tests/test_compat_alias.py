@@ -18,6 +18,8 @@ def test_reference_module_paths_resolve_to_the_same_objects():
         "from flexkv.kvmanager import KVManager as KA\n"
         "from flexkv.common.config import CacheConfig as CA\n"
         "import flexkv.integration.sglang.connector as S, flexkv_b200.integration.sglang.connector as S2\n"
+        "from flexkv.integration.tensorrt_llm.trtllm_adapter import FlexKVSchedulerConnector, FlexKVWorkerConnector\n"
+        "from flexkv.server.client import KVTPClient, KVDPClient\n"
         "import sys\n"
         "assert A is B and KA is flexkv_b200.KVManager and CA is flexkv_b200.CacheConfig and S is S2\n"
         "assert flexkv is flexkv_b200 and sys.modules['flexkv.kvmanager'] is sys.modules['flexkv_b200.kvmanager']\n"
