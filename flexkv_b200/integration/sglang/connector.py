@@ -204,10 +204,10 @@ class FlexKVConnector:
         self.layer_counter = FlexKVLayerDoneCounter(L, num_counters=3, world_rank=self.comm.rank)
         if hasattr(kvcache, "register_layer_transfer_counter"):
             kvcache.register_layer_transfer_counter(self.layer_counter)
-        sock = os.environ.get("FLEXKV_LAYERWISE_SOCK", "")
-        if sock:
-            from ...transfer.layerwise import send_eventfds
-            send_eventfds(f"{sock}.{self.dp_rank}", self.tp_rank, self.tp_size, self.layer_counter.fds_per_counter())
+        from ...transfer.layerwise import build_layerwise_eventfd_socket_path, send_eventfds
+        path = build_layerwise_eventfd_socket_path(self.dp_rank, getattr(self, "pp_rank", 0), self.cfg.model_config)
+        if path:
+            send_eventfds(path, self.tp_rank, self.tp_size, self.layer_counter.fds_per_counter())
 
     def wait_ready(self, timeout: float = 600.0) -> None:
         if self.is_leader:

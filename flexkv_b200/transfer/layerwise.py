@@ -32,6 +32,26 @@ HEADER = struct.Struct("iiii")
 ACK = b"\x01"
 
 
+def build_layerwise_eventfd_socket_path(dp_client_id: int, pp_rank: int, model_config) -> Optional[str]:
+    """Where the layerwise worker of (dp client, pipeline stage) listens for the engine ranks' eventfds, or None
+    when no socket is configured (worker and engine share a process). ``FLEXKV_LAYERWISE_EVENTFD_SOCKET`` follows
+    the reference's naming rule: the given path, with ``_pp<rank>`` before the extension when there are several
+    pipeline stages and ``_dp<id>`` when there are several data-parallel clients or instances
+    (flexkv/transfer/layerwise.py:30-48). ``FLEXKV_LAYERWISE_SOCK`` is this package's older form,
+    ``<path>.<dp client id>``."""
+    base = os.environ.get("FLEXKV_LAYERWISE_EVENTFD_SOCKET", "")
+    if base:
+        suffix = ""
+        if getattr(model_config, "pp_size", 1) > 1:
+            suffix += f"_pp{pp_rank}"
+        if getattr(model_config, "instance_num", 1) > 1 or getattr(model_config, "dp_size", 1) > 1:
+            suffix += f"_dp{dp_client_id}"
+        root, ext = os.path.splitext(base)
+        return f"{root}{suffix}{ext}" if suffix else base
+    sock = os.environ.get("FLEXKV_LAYERWISE_SOCK", "")
+    return f"{sock}.{dp_client_id}" if sock else None
+
+
 def send_eventfds(sock_path: str, rank: int, tp_size: int, fds_per_counter: Sequence[Sequence[int]],
                   timeout: float = 30.0) -> None:
     """Engine side: hands this rank's eventfds (``[counter][layer]``) to the worker."""

@@ -1068,10 +1068,10 @@ def build_workers(storage, model_config: ModelConfig, cache_config: CacheConfig
             workers[(key, TransferType.H2D)] = MultiGroupGpuHostWorker(storage, model_config, key, True)
             workers[(key, TransferType.D2H)] = MultiGroupGpuHostWorker(storage, model_config, key, False)
             if GLOBAL_CONFIG_FROM_ENV.enable_layerwise_transfer and reg0.device_id >= 0:
-                from .layerwise import LayerwiseWorker
-                sock = os.environ.get("FLEXKV_LAYERWISE_SOCK", "")
+                from .layerwise import LayerwiseWorker, build_layerwise_eventfd_socket_path
                 workers[(key, TransferType.LAYERWISE)] = LayerwiseWorker(
-                    storage, model_config, key, sock_path=f"{sock}.{key.dp_client_id}" if sock else None)
+                    storage, model_config, key,
+                    sock_path=build_layerwise_eventfd_socket_path(key.dp_client_id, key.pp_rank, model_config))
             continue
         if reg0.device_id < 0:
             workers[(key, TransferType.H2D)] = HostEmulatedGpuWorker(storage, model_config, key, True)
@@ -1095,10 +1095,10 @@ def build_workers(storage, model_config: ModelConfig, cache_config: CacheConfig
             w.max_blocks = max(4096, min(1 << 18, storage.host.num_blocks))
             workers[(key, TransferType.H2D if h2d else TransferType.D2H)] = w
         if GLOBAL_CONFIG_FROM_ENV.enable_layerwise_transfer:
-            from .layerwise import LayerwiseWorker
-            sock = os.environ.get("FLEXKV_LAYERWISE_SOCK", "")
+            from .layerwise import LayerwiseWorker, build_layerwise_eventfd_socket_path
             workers[(key, TransferType.LAYERWISE)] = LayerwiseWorker(
-                storage, model_config, key, sock_path=f"{sock}.{key.dp_client_id}" if sock else None)
+                storage, model_config, key,
+                sock_path=build_layerwise_eventfd_socket_path(key.dp_client_id, key.pp_rank, model_config))
     for key in storage.swa_regs:
         workers[(key, "SWA")] = SwaWorker(storage, model_config, key)
     real = [k for k, regs in storage.gpu_regs.items() if regs[sorted(regs)[0]].device_id >= 0]

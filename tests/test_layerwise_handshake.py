@@ -39,3 +39,18 @@ def test_eventfds_cross_the_socket_and_stay_usable(tmp_path):
         rx.stop()
         for fd in installed.values():
             os.close(fd)
+
+
+def test_socket_path_follows_the_reference_naming_rule(monkeypatch):
+    from types import SimpleNamespace as NS
+    from flexkv_b200.transfer.layerwise import build_layerwise_eventfd_socket_path as path
+    monkeypatch.delenv("FLEXKV_LAYERWISE_SOCK", raising=False)
+    monkeypatch.delenv("FLEXKV_LAYERWISE_EVENTFD_SOCKET", raising=False)
+    one = NS(pp_size=1, dp_size=1, instance_num=1)
+    assert path(0, 0, one) is None                               # same process: no socket
+    monkeypatch.setenv("FLEXKV_LAYERWISE_SOCK", "/tmp/lw")
+    assert path(3, 0, one) == "/tmp/lw.3"
+    monkeypatch.setenv("FLEXKV_LAYERWISE_EVENTFD_SOCKET", "/run/fkv/eventfd.sock")
+    assert path(0, 0, one) == "/run/fkv/eventfd.sock"
+    assert path(2, 1, NS(pp_size=2, dp_size=4, instance_num=1)) == "/run/fkv/eventfd_pp1_dp2.sock"
+    assert path(5, 0, NS(pp_size=1, dp_size=1, instance_num=2)) == "/run/fkv/eventfd_dp5.sock"
