@@ -309,6 +309,7 @@ class CacheConfig:
     mooncake_store_config_path: Optional[str] = None
     _user_cpu_cache_gb: float = 0
     _user_ssd_cache_gb: float = 0
+    _swa_multi_group: Optional[bool] = None       # user switch: False leaves state sidecars out of the window slot
     swa: Optional[SWAPoolConfig] = None
     enable_swa_transfer: bool = False
 
@@ -453,6 +454,21 @@ class UserConfig:
     local_ip: str = "127.0.0.1"
     kv_cache_dtype: Optional[str] = None
     offload_quant: str = "none"
+    # keys a deployment file written for the reference may carry (flexkv/common/config.py:843-880); they are
+    # passed on to CacheConfig, which reports the ones that have no effect in this build
+    enable_nixl: bool = False
+    enable_3rd_remote: bool = False
+    use_mooncake_store_backend: bool = False
+    mooncake_store_config_path: Optional[str] = None
+    mooncake_store_pp_rank: int = 0
+    mooncake_store_pp_size: int = 1
+    mooncake_store_node_layer_start: int = 0
+    mooncake_store_node_layer_end: int = 0
+    mooncake_store_total_layers: int = 0
+    local_zmq_ip: Optional[str] = None
+    local_zmq_port: Optional[int] = None
+    node_ttl_seconds: Optional[int] = None
+    swa_multi_group: Optional[bool] = None
     overrides: Dict[str, Any] = field(default_factory=dict)
 
     def __post_init__(self) -> None:
@@ -558,6 +574,22 @@ def update_default_config_from_user_config(model_config: ModelConfig, cache_conf
     cache_config.redis_port = user_config.redis_port
     cache_config.redis_password = user_config.redis_password
     cache_config.local_ip = user_config.local_ip
+    cache_config.enable_nixl = bool(user_config.enable_nixl)
+    cache_config.enable_3rd_remote = bool(user_config.enable_3rd_remote)
+    cache_config.use_mooncake_store_backend = bool(user_config.use_mooncake_store_backend)
+    if user_config.mooncake_store_config_path:
+        cache_config.mooncake_store_config_path = user_config.mooncake_store_config_path
+    if user_config.local_zmq_ip:
+        cache_config.local_zmq_ip = user_config.local_zmq_ip
+    if user_config.local_zmq_port:
+        cache_config.local_zmq_port = int(user_config.local_zmq_port)
+    if user_config.node_ttl_seconds:
+        cache_config.node_ttl_seconds = int(user_config.node_ttl_seconds)
+    # None / True: compressor-state sidecars travel with the window slot; False keeps the window-only path. The
+    # engine adapter that reads the pool (SGLang) takes the switch from here.
+    cache_config._swa_multi_group = user_config.swa_multi_group
+    if user_config.swa_multi_group is False and cache_config.swa is not None:
+        cache_config.swa.sidecar_groups = []
     cache_config.__post_init__()
     apply_overrides(user_config)
 

@@ -135,6 +135,8 @@ class FlexKVConnector:
         ``include_state=False`` leaves the compressor-state sidecars out of the window slot."""
         import dataclasses
         from ...common.config import recompute_block_counts
+        if include_state is None:
+            include_state = getattr(flexkv_config.cache_config, "_swa_multi_group", None)     # swa_multi_group key
         pool = resolve_kv_pool(kvcache, page_size, include_state)
         specs = layer_group_specs(pool, page_size)
         if specs is not None and flexkv_config.model_config.layer_groups is None:

@@ -135,3 +135,30 @@ def test_settings_kept_for_compatibility_are_reported_not_ignored_silently():
                      "mooncake_config_path / mooncake_store_config_path", "enable_3rd_remote",
                      "distributed_node_id", "local_zmq_ip / local_zmq_port"]
     assert c.enable_kv_sharing and c.enable_remote
+
+
+def test_a_deployment_file_written_for_the_reference_loads(tmp_path):
+    """Every key of the reference's user configuration is accepted; the ones that have no effect here are named
+    by ``settings_without_effect`` instead of failing the start-up."""
+    import json
+    from flexkv_b200.common.config import (CacheConfig, ModelConfig, load_user_config_from_file,
+                                          update_default_config_from_user_config)
+    f = tmp_path / "flexkv.json"
+    f.write_text(json.dumps(dict(cpu_cache_gb=4, ssd_cache_gb=8, ssd_cache_dir=str(tmp_path), enable_gds=False,
+                                 enable_nixl=True, use_hugepage_cpu_buffer=False, enable_p2p_cpu=True,
+                                 enable_p2p_ssd=True, enable_3rd_remote=False, use_mooncake_store_backend=False,
+                                 mooncake_store_config_path="/etc/mc.json", local_zmq_ip="10.0.0.5",
+                                 local_zmq_port=6001, redis_host="10.0.0.9", redis_port=6380, redis_password="x",
+                                 local_ip="10.0.0.5", node_ttl_seconds=45, kv_cache_dtype="bf16",
+                                 swa_multi_group=False)))
+    u = load_user_config_from_file(str(f))
+    assert u.overrides == {}
+    m = ModelConfig(num_layers=4, num_kv_heads=2, head_size=64)
+    c = CacheConfig(tokens_per_block=16)
+    update_default_config_from_user_config(m, c, u)
+    assert c.enable_ssd and c.enable_p2p_ssd and c.enable_gds            # enable_nixl -> the GDS worker
+    assert (c.redis_host, c.redis_port, c.node_ttl_seconds, c.local_zmq_port) == ("10.0.0.9", 6380, 45, 6001)
+    assert c._swa_multi_group is False
+    names = [n for n, _ in c.settings_without_effect()]
+    assert "enable_nixl" in names and "local_zmq_ip / local_zmq_port" in names
+    assert "mooncake_config_path / mooncake_store_config_path" in names
