@@ -57,6 +57,13 @@ class LayerGroupSpec:
     compress_ratio: int = 1           # tokens stored per block = tokens_per_block / ratio
     layer_ids: Optional[List[int]] = None
     name: str = ""
+    layer_indices: Optional[List[int]] = None     # the reference's name for layer_ids; either may be given
+
+    def __post_init__(self) -> None:
+        if self.layer_ids is None and self.layer_indices is not None:
+            self.layer_ids = list(self.layer_indices)
+        elif self.layer_indices is None and self.layer_ids is not None:
+            self.layer_indices = list(self.layer_ids)
 
 
 @dataclass
@@ -202,6 +209,36 @@ class RankInfo:
     instance_id: int = 0
     node_rank: int = 0
     device_id: int = 0
+    # names the SGLang-facing callers of the reference use (flexkv/common/config.py:431-478)
+    attn_cp_rank: int = 0            # mirror of cp_rank
+    pp_start_layer: int = 0
+    pp_end_layer: int = -1
+    local_rank: int = -1             # GPU index on the node; derived from the ranks when negative
+
+    def __post_init__(self) -> None:
+        if self.cp_rank == 0 and self.attn_cp_rank != 0:
+            self.cp_rank = self.attn_cp_rank
+        elif self.attn_cp_rank == 0 and self.cp_rank != 0:
+            self.attn_cp_rank = self.cp_rank
+        elif self.cp_rank != self.attn_cp_rank:
+            raise ValueError(f"cp_rank={self.cp_rank} and attn_cp_rank={self.attn_cp_rank} disagree")
+        if self.local_rank < 0:
+            m = self.model_config
+            nn = max(1, getattr(m, "nnodes", 1))
+            tp_node = max(1, m.tp_size_per_node)
+            cp_node = max(1, getattr(m, "cp_size", 1))
+            pp_node = max(1, m.local_pp_stages)
+            tp_cp = self.cp_rank * tp_node + self.tp_rank % tp_node
+            pp_local = self.pp_rank % pp_node
+            if m.enable_dp_attention:
+                self.local_rank = pp_local * cp_node * tp_node + tp_cp
+            else:
+                dp_node = max(1, m.dp_size // nn) if m.dp_size >= nn else 1
+                self.local_rank = ((self.dp_rank % dp_node) * pp_node + pp_local) * cp_node * tp_node + tp_cp
+
+    @property
+    def attn_tp_rank(self) -> int:
+        return self.tp_rank
 
     @property
     def dp_client_id(self) -> int:
@@ -307,6 +344,11 @@ class CacheConfig:
     mooncake_config_path: Optional[str] = None
     use_mooncake_store_backend: bool = False
     mooncake_store_config_path: Optional[str] = None
+    mooncake_store_pp_rank: int = 0                # accepted for compatibility (no Mooncake library here)
+    mooncake_store_pp_size: int = 1
+    mooncake_store_node_layer_start: int = 0
+    mooncake_store_node_layer_end: int = 0
+    mooncake_store_total_layers: int = 0
     _user_cpu_cache_gb: float = 0
     _user_ssd_cache_gb: float = 0
     _swa_multi_group: Optional[bool] = None       # user switch: False leaves state sidecars out of the window slot
