@@ -90,12 +90,21 @@ class KVDPClient:
     def cancel_tasks(self, task_ids) -> None:
         self._call(R.CancelRequest(task_ids=list(task_ids)))
 
-    def wait(self, task_ids, timeout: float = 20.0, completely: bool = False) -> Dict[int, KVResponse]:
+    def wait(self, task_ids=None, timeout: float = 20.0, completely: bool = False, *, wait_task_ids=None,
+             wait_timeout: Optional[float] = None) -> Dict[int, KVResponse]:
+        """``wait_task_ids`` / ``wait_timeout`` are the reference's names for the first two arguments."""
+        task_ids = wait_task_ids if task_ids is None else task_ids
+        timeout = timeout if wait_timeout is None else float(wait_timeout)
         return self._call(R.WaitRequest(task_ids=list(task_ids), timeout=timeout, completely=completely),
                           timeout=timeout + self.request_timeout).status
 
-    def try_wait(self, task_ids) -> Dict[int, KVResponse]:
+    def try_wait(self, task_ids=None, *, try_wait_task_ids=None) -> Dict[int, KVResponse]:
+        task_ids = try_wait_task_ids if task_ids is None else task_ids
         return self._call(R.WaitRequest(task_ids=list(task_ids), try_wait=True)).status
+
+    def register_to_server(self, model_config=None, client_recv_port: Optional[str] = None) -> None:
+        """The reference's name for joining the server; the reply endpoint is this client's own."""
+        self.start_server_and_register()
 
     def reset(self) -> None:
         self._call(R.ResetRequest())
@@ -144,11 +153,48 @@ class KVTPClient:
         self._handles: List[TensorSharedHandle] = []
 
     def register_to_server(self, kv_caches: Sequence[torch.Tensor], kv_layout: KVCacheLayout,
-                           mode: Optional[str] = None, group_id: int = -1, layer_groups=None) -> None:
+                           mode: Optional[str] = None, group_id: int = -1, layer_groups=None, *,
+                           override_device_id: Optional[int] = None, gpu_layouts=None, handles_per_group=None,
+                           swa_caches=None, swa_layout=None, swa_layer_groups=None, swa_gpu_layouts=None,
+                           swa_handles_per_group=None, resume: bool = False) -> None:
         """``group_id``: layer group of a multi-group cache; call once per group. ``layer_groups``: the
         ``LayerGroupSpec`` list, for engines whose worker only learns the groups from its tensors (the data
         plane adopts the first list it receives when its own configuration names none;
-        flexkv/transfer_manager.py:154-161)."""
+        flexkv/transfer_manager.py:154-161).
+
+        The keyword-only arguments are the one-call form engine integrations written for the reference use
+        (flexkv/server/client.py:366-470): ``handles_per_group[g]`` / ``gpu_layouts[g]`` register every layer
+        group at once, ``swa_caches`` (or ``swa_handles_per_group``: window pages first, then the state
+        sidecars) the sliding-window pool, ``override_device_id`` replaces this client's device id, and
+        ``resume`` re-registers after the engine re-created its tensors (sleep / wake)."""
+        if override_device_id is not None:
+            self.device_id = int(override_device_id)
+        if swa_handles_per_group is not None or swa_gpu_layouts is not None or swa_layer_groups is not None:
+            if swa_handles_per_group is None or swa_gpu_layouts is None or swa_layer_groups is None or not \
+                    (len(swa_handles_per_group) == len(swa_gpu_layouts) == len(swa_layer_groups)):
+                raise ValueError("swa_layer_groups, swa_gpu_layouts and swa_handles_per_group go together, "
+                                 "one entry per group")
+        if handles_per_group is not None:
+            if gpu_layouts is None or len(gpu_layouts) != len(handles_per_group):
+                raise ValueError("handles_per_group needs one gpu layout per group")
+            if resume:
+                first, rest = handles_per_group[0], list(zip(handles_per_group[1:], gpu_layouts[1:],
+                                                            range(1, len(handles_per_group))))
+                if not self.resume_gpu_mappings(first, gpu_layouts[0], mode, 0, rest):
+                    raise RuntimeError("the data plane did not take the re-created tensors")
+            else:
+                for g, (tensors, layout) in enumerate(zip(handles_per_group, gpu_layouts)):
+                    self.register_to_server(tensors, layout, mode, g, layer_groups if g == 0 else None)
+        elif resume:
+            if not self.resume_gpu_mappings(kv_caches, kv_layout, mode, group_id):
+                raise RuntimeError("the data plane did not take the re-created tensors")
+        if swa_handles_per_group is not None:
+            for g, tensors in enumerate(swa_handles_per_group):
+                self.register_swa_to_server(tensors, g, mode)
+        elif swa_caches is not None:
+            self.register_swa_to_server(swa_caches, 0, mode)
+        if handles_per_group is not None or resume:
+            return
         handles = [TensorSharedHandle.export(t, mode) for t in kv_caches]
         self._handles = self._handles + handles if group_id > 0 else handles
         req = R.RegisterTPClientRequest(self.dp_client_id, self.intra_client_id, self.device_id, handles,

@@ -77,3 +77,44 @@ def test_missing_group_registration_is_reported():
             mgr.wait_ready(5)
     finally:
         mgr.shutdown()
+
+
+def test_one_call_registration_of_every_group_through_the_tp_client():
+    """The registration form of engine integrations written for the reference: one ``register_to_server`` call
+    carries every layer group (``handles_per_group`` / ``gpu_layouts``), the spec list travels with it, and an
+    ``override_device_id`` replaces the client's device id (flexkv/server/client.py:366-470)."""
+    from flexkv_b200 import KVTPClient
+    from flexkv_b200.server.utils import unique_ipc_endpoint
+    groups = [LayerGroupSpec(3, 2, 16, kv_dim=2, name="full", layer_indices=[0, 2, 4]),
+              LayerGroupSpec(2, 1, 24, kv_dim=1, compress_ratio=4, name="latent", layer_indices=[1, 3])]
+    assert groups[0].layer_ids == [0, 2, 4]
+    model = ModelConfig(num_layers=5, num_kv_heads=2, head_size=16, dtype=torch.bfloat16)     # groups arrive later
+    reg = unique_ipc_endpoint("reg")
+    mgr = KVManager(model, CacheConfig(tokens_per_block=T, num_cpu_blocks=16), require_gpu=True, gpu_register_port=reg)
+    NB = 32
+    g0, lay0 = _alloc(3, 2, NB, T, 2, 16, torch.bfloat16, "cpu", 1)
+    g1, lay1 = _alloc(2, 1, NB, T // 4, 1, 24, torch.bfloat16, "cpu", 2)
+    mgr.start()
+    client = KVTPClient(reg, dp_client_id=0, device_id=7)
+    client.register_to_server(g0 + g1, lay0, mode="same_process", layer_groups=groups, gpu_layouts=[lay0, lay1],
+                              handles_per_group=[g0, g1], override_device_id=0)
+    assert client.device_id == 0
+    try:
+        mgr.wait_ready(30)
+        assert len(mgr.transfer_manager.model_config.layer_groups) == 2
+        tok = np.arange(4 * T, dtype=np.int64)
+        src, dst = [3, 9, 1, 30], [20, 21, 22, 23]
+        tid = mgr.put_async(tok, slots(src))
+        assert mgr.wait(tid, completely=True)[tid].status.value == "success"
+        want1 = [t[src].clone() for t in g1]
+        for t in g1:
+            t[dst] = 0
+        tid = mgr.get_async(tok, slots(dst))
+        assert mgr.wait(tid)[tid].status.value == "success"
+        for l in range(2):
+            assert torch.equal(g1[l][dst], want1[l])
+        with pytest.raises(ValueError, match="go together"):
+            client.register_to_server(g0, lay0, swa_layer_groups=[1], swa_gpu_layouts=None, swa_handles_per_group=None)
+    finally:
+        client.shutdown()
+        mgr.shutdown()
