@@ -60,7 +60,7 @@ class GroupLayout:
         return self.num_layers * self.layer_stride_bytes
 
 
-@dataclass
+@dataclass(init=False)
 class KVCacheLayout:
     type: KVCacheLayoutType
     num_layer: int
@@ -72,6 +72,26 @@ class KVCacheLayout:
     kv_dim_override: Optional[int] = None
     groups: Optional[List[GroupLayout]] = None   # byte-flat multi-group block (BLOCKFIRST only)
     tp_slices: int = 1                           # multi-group: rank slices per block
+
+    def __init__(self, type: KVCacheLayoutType, num_layer: int, num_block: int, tokens_per_block: int, num_head: int,
+                 head_size: int, is_mla=False, kv_dim_override: Optional[int] = None,
+                 groups: Optional[List[GroupLayout]] = None, tp_slices: int = 1, *, kv_dim: Optional[int] = None,
+                 num_kv_heads: Optional[int] = None) -> None:
+        """Also takes the reference's spelling (flexkv/common/storage.py:31-48): ``kv_dim`` (1 for an MLA latent
+        cache or a packed 4-D cache, 2 for K and V) as a keyword or as the seventh positional argument, and
+        ``num_kv_heads``, which is kept for the caller and not used here."""
+        if not isinstance(is_mla, bool) and isinstance(is_mla, int):       # positional kv_dim of the reference
+            kv_dim, is_mla = int(is_mla), False
+        if kv_dim is not None:
+            kv_dim_override = int(kv_dim)
+            is_mla = bool(is_mla) or (kv_dim_override == 1 and int(num_head) == 1)
+        if kv_dim_override is not None and kv_dim_override == (1 if is_mla else 2):
+            kv_dim_override = None                   # the implied value: keeps equal layouts equal
+        self.type, self.num_layer, self.num_block = type, int(num_layer), int(num_block)
+        self.tokens_per_block, self.num_head, self.head_size = int(tokens_per_block), int(num_head), int(head_size)
+        self.is_mla, self.kv_dim_override, self.groups, self.tp_slices = bool(is_mla), kv_dim_override, groups, tp_slices
+        self.num_kv_heads = num_kv_heads
+        self.__post_init__()
 
     def __post_init__(self) -> None:
         if self.groups is not None and self.type != KVCacheLayoutType.BLOCKFIRST:

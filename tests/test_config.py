@@ -162,3 +162,14 @@ def test_a_deployment_file_written_for_the_reference_loads(tmp_path):
     names = [n for n, _ in c.settings_without_effect()]
     assert "enable_nixl" in names and "local_zmq_ip / local_zmq_port" in names
     assert "mooncake_config_path / mooncake_store_config_path" in names
+
+
+def test_layout_takes_the_reference_spelling():
+    from flexkv_b200.common.storage import KVCacheLayout, KVCacheLayoutType as LT
+    a = KVCacheLayout(type=LT.LAYERFIRST, num_layer=4, num_block=8, tokens_per_block=16, num_head=2, head_size=64, kv_dim=2)
+    assert a.kv_dim == 2 and not a.is_mla and a == KVCacheLayout(LT.LAYERFIRST, 4, 8, 16, 2, 64)
+    mla = KVCacheLayout(LT.LAYERFIRST, 4, 8, 64, 1, 576, 1)                  # kv_dim as the seventh positional
+    assert mla.kv_dim == 1 and mla.is_mla and mla == KVCacheLayout(LT.LAYERFIRST, 4, 8, 64, 1, 576, is_mla=True)
+    packed = KVCacheLayout(LT.LAYERFIRST, 4, 8, 16, 8, 72, kv_dim=1, num_kv_heads=8)   # packed 4-D cache: not MLA
+    assert packed.kv_dim == 1 and not packed.is_mla and packed.num_kv_heads == 8
+    assert packed.div_head(2).num_head == 4 and packed._replace(num_layer=1).kv_dim == 1
