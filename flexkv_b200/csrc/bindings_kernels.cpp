@@ -12,6 +12,7 @@
 #include "kernels/kv_compress.h"
 #include "kernels/kv_hash.h"
 #include "ce_copy.h"
+#include "ptr_table.h"
 #include "ipc.h"
 #include "vmm_handle.h"
 
@@ -25,13 +26,23 @@ static void throw_on(cudaError_t e, const char* what) {
   }
 }
 
-KvCopyParams kv_params_from_dict(const py::dict& d) {
+// `on_host`: the call executes on the CPU (host_kv_copy, planning, checks), so a table beyond the inline
+// limit stays in host memory; otherwise it is uploaded to the current device, where the launch goes.
+KvCopyParams kv_params_from_dict(const py::dict& d, bool on_host = false) {
   KvCopyParams p;
   std::memset(&p, 0, sizeof(p));
   auto ptrs = d["gpu_ptrs"].cast<std::vector<uint64_t>>();
-  if ((int)ptrs.size() > kMaxGpuPtrs) throw std::invalid_argument("too many gpu tensors");
-  for (size_t i = 0; i < ptrs.size(); ++i) p.gpu_ptrs[i] = ptrs[i];
-  p.num_gpu_ptrs = (int32_t)ptrs.size();
+  int device = -1;
+  auto table_device = [&]() {
+    if (on_host) return -1;
+    if (device < 0 && cudaGetDevice(&device) != cudaSuccess) {
+      (void)cudaGetLastError();
+      throw std::runtime_error("no CUDA device for a tensor table of more than " + std::to_string(kMaxGpuPtrs) +
+                               " entries");
+    }
+    return device;
+  };
+  kv_set_gpu_table(p, ptrs, (int)ptrs.size() > kMaxGpuPtrs ? table_device() : -1);
   auto geti = [&](const char* k, int64_t dflt) { return d.contains(k) ? d[k].cast<int64_t>() : dflt; };
   p.idx_layer_mul = (int32_t)geti("idx_layer_mul", 1);
   p.idx_kv_mul = (int32_t)geti("idx_kv_mul", 0);
@@ -42,9 +53,7 @@ KvCopyParams kv_params_from_dict(const py::dict& d) {
   p.cpu_base = d.contains("cpu_base") ? d["cpu_base"].cast<uint64_t>() : 0;
   if (d.contains("c_ptrs")) {
     auto cp = d["c_ptrs"].cast<std::vector<uint64_t>>();
-    if ((int)cp.size() > kMaxGpuPtrs) throw std::invalid_argument("too many peer tensors");
-    for (size_t i = 0; i < cp.size(); ++i) p.c_ptrs[i] = cp[i];
-    p.num_c_ptrs = (int32_t)cp.size();
+    kv_set_c_table(p, cp, (int)cp.size() > kMaxGpuPtrs ? table_device() : -1);
     p.c_use_table = 1;
     p.c_idx_layer_mul = (int32_t)geti("c_idx_layer_mul", 1);
     p.c_idx_kv_mul = (int32_t)geti("c_idx_kv_mul", 0);
@@ -95,8 +104,9 @@ void init_kernel_bindings(py::module_& m) {
     fp.base.h2d = 1;
     if (!mc.empty()) {
       if ((int)mc.size() != fp.base.num_gpu_ptrs) throw std::invalid_argument("mc_ptrs must match gpu_ptrs");
-      for (size_t i = 0; i < mc.size(); ++i) fp.base.c_ptrs[i] = mc[i];
-      fp.base.num_c_ptrs = (int32_t)mc.size();
+      int dev = -1;
+      if ((int)mc.size() > kMaxGpuPtrs) throw_on(cudaGetDevice(&dev), "cudaGetDevice");
+      kv_set_c_table(fp.base, mc, dev);
     }
     fp.mc_delta = mc_delta;
     fp.mc_flag = (uint32_t*)(uintptr_t)mc_flag_ptr;
@@ -169,7 +179,7 @@ void init_kernel_bindings(py::module_& m) {
      py::arg("ns_len") = 0, py::arg("out") = 0, py::arg("out_offsets") = 0, py::arg("stream") = 0);
 
   m.def("host_kv_copy", [](py::dict params, int threads) {
-    KvCopyParams p = kv_params_from_dict(params);
+    KvCopyParams p = kv_params_from_dict(params, true);
     py::gil_scoped_release rel;
     return host_kv_copy(p, threads);
   }, py::arg("params"), py::arg("threads") = 4);
@@ -178,7 +188,7 @@ void init_kernel_bindings(py::module_& m) {
   // [R, 3] array (gpu block, cpu block, length), the chosen path, the number of driver
   // copies that path would issue, and the range-error bits of dropped ids.
   m.def("ce_plan", [](py::dict params, int64_t max_copies, int64_t min_bytes_per_copy) {
-    KvCopyParams p = kv_params_from_dict(params);
+    KvCopyParams p = kv_params_from_dict(params, true);
     CeAnalysis a = ce_analyze(p.gpu_blocks, p.cpu_blocks, p.num_pairs, p.gpu_num_blocks, p.cpu_num_blocks);
     CePolicy pol;
     pol.max_copies = max_copies;
@@ -195,5 +205,7 @@ void init_kernel_bindings(py::module_& m) {
     return py::make_tuple(runs, std::string(names[(int)path]), ce_num_copies(a, p, path), a.status);
   }, py::arg("params"), py::arg("max_copies") = 4096, py::arg("min_bytes_per_copy") = 8 << 20);
 
-  m.def("kv_copy_tma_eligible", [](py::dict params) { return kv_copy_tma_eligible(kv_params_from_dict(params)); });
+  m.def("kv_copy_tma_eligible", [](py::dict params) { return kv_copy_tma_eligible(kv_params_from_dict(params, true)); });
+  m.def("ptr_table_cache_size", &ptr_table_cache_size);
+  m.attr("MAX_GPU_PTRS_EXT") = kMaxGpuPtrsExt;
 }

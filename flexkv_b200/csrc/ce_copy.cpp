@@ -41,11 +41,11 @@ bool block_geometry_matches(const KvCopyParams& p) {
 }
 
 inline uint64_t gpu_addr(const KvCopyParams& p, int layer, int kv, int64_t block) {
-  return p.gpu_ptrs[layer * p.idx_layer_mul + kv * p.idx_kv_mul] + (uint64_t)(layer * p.g_layer_stride) +
+  return kv_gpu_tensor(p, layer * p.idx_layer_mul + kv * p.idx_kv_mul) + (uint64_t)(layer * p.g_layer_stride) +
          (uint64_t)(kv * p.g_kv_stride) + (uint64_t)(block * p.g_block_stride) + (uint64_t)p.g_off;
 }
 inline uint64_t cpu_addr(const KvCopyParams& p, int layer, int kv, int64_t block) {
-  const uint64_t base = p.c_use_table ? p.c_ptrs[layer * p.c_idx_layer_mul + kv * p.c_idx_kv_mul] : p.cpu_base;
+  const uint64_t base = p.c_use_table ? kv_c_tensor(p, layer * p.c_idx_layer_mul + kv * p.c_idx_kv_mul) : p.cpu_base;
   return base + (uint64_t)(layer * p.c_layer_stride) + (uint64_t)(kv * p.c_kv_stride) +
          (uint64_t)(block * p.c_block_stride) + (uint64_t)p.c_off;
 }

@@ -433,7 +433,7 @@ kv_compress_kernel(const __grid_constant__ KvCopyParams p, uint32_t* __restrict_
     const int64_t e0 = (int64_t)s_ * kCompressTileElems;
     const int64_t left = chunk_elems - e0;
     elems = (int32_t)(left < kCompressTileElems ? left : kCompressTileElems);
-    g = p.gpu_ptrs[layer * p.idx_layer_mul + kv * p.idx_kv_mul] + layer * p.g_layer_stride + kv * p.g_kv_stride +
+    g = kv_gpu_tensor(p, layer * p.idx_layer_mul + kv * p.idx_kv_mul) + layer * p.g_layer_stride + kv * p.g_kv_stride +
         gblk * p.g_block_stride + p.g_off + e0 * 2;
     c = p.cpu_base + layer * p.c_layer_stride + kv * p.c_kv_stride + cblk * p.c_block_stride + p.c_off +
         (int64_t)s_ * kCompressTileSlot;

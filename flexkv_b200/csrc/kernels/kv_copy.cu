@@ -60,9 +60,9 @@ __device__ __forceinline__ TileAddr tile_addr(const KvCopyParams& p, const TileP
   const int64_t off = (int64_t)t.s * tile_bytes;
   const int64_t left = p.chunk_bytes - off;
   a.bytes = (uint32_t)(left < tile_bytes ? left : tile_bytes);
-  a.gpu = p.gpu_ptrs[t.layer * p.idx_layer_mul + t.kv * p.idx_kv_mul] + t.layer * p.g_layer_stride +
+  a.gpu = kv_gpu_tensor(p, t.layer * p.idx_layer_mul + t.kv * p.idx_kv_mul) + t.layer * p.g_layer_stride +
           t.kv * p.g_kv_stride + gblk * p.g_block_stride + p.g_off + off;
-  const uint64_t cbase = p.c_use_table ? p.c_ptrs[t.layer * p.c_idx_layer_mul + t.kv * p.c_idx_kv_mul] : p.cpu_base;
+  const uint64_t cbase = p.c_use_table ? kv_c_tensor(p, t.layer * p.c_idx_layer_mul + t.kv * p.c_idx_kv_mul) : p.cpu_base;
   a.cpu = cbase + t.layer * p.c_layer_stride + t.kv * p.c_kv_stride + cblk * p.c_block_stride + p.c_off + off;
   return a;
 }
@@ -299,7 +299,7 @@ __global__ void __launch_bounds__(1024) kv_copy_refshape_kernel(const __grid_con
     const int64_t gblk = p.gpu_blocks[pair];
     const int64_t cblk = p.cpu_blocks[pair];
     for (int kv = 0; kv < p.kv_dim; ++kv) {
-      const uint64_t g = p.gpu_ptrs[layer * p.idx_layer_mul + kv * p.idx_kv_mul] + layer * p.g_layer_stride +
+      const uint64_t g = kv_gpu_tensor(p, layer * p.idx_layer_mul + kv * p.idx_kv_mul) + layer * p.g_layer_stride +
                          kv * p.g_kv_stride + gblk * p.g_block_stride + p.g_off;
       const uint64_t c =
           p.cpu_base + layer * p.c_layer_stride + kv * p.c_kv_stride + cblk * p.c_block_stride + p.c_off;
@@ -335,12 +335,12 @@ inline bool all_multiple(const KvCopyParams& p, int64_t m) {
   const int nptr = p.idx_layer_mul == 0 && p.idx_kv_mul == 0
                        ? 1
                        : (p.layer_start + p.num_layers - 1) * p.idx_layer_mul + (p.kv_dim - 1) * p.idx_kv_mul + 1;
-  for (int i = 0; i < nptr && i < kMaxGpuPtrs; ++i) r = r && (p.gpu_ptrs[i] % (uint64_t)m) == 0;
+  for (int i = 0; i < nptr && i < p.num_gpu_ptrs; ++i) r = r && (kv_gpu_tensor(p, i) % (uint64_t)m) == 0;
   if (p.c_use_table) {
     const int nc = p.c_idx_layer_mul == 0 && p.c_idx_kv_mul == 0
                        ? 1
                        : (p.layer_start + p.num_layers - 1) * p.c_idx_layer_mul + (p.kv_dim - 1) * p.c_idx_kv_mul + 1;
-    for (int i = 0; i < nc && i < kMaxGpuPtrs; ++i) r = r && (p.c_ptrs[i] % (uint64_t)m) == 0;
+    for (int i = 0; i < nc && i < p.num_c_ptrs; ++i) r = r && (kv_c_tensor(p, i) % (uint64_t)m) == 0;
   }
   return r;
 }

@@ -23,7 +23,14 @@
 
 namespace fkv {
 
-constexpr int kMaxGpuPtrs = 256;
+constexpr int kMaxGpuPtrs = 256;      // tensor pointers carried inside the launch parameters
+constexpr int kMaxGpuPtrsExt = 16384; // tensor pointers in a table of its own (gpu_ptrs_ext), for larger registrations
+
+#if defined(__CUDACC__)
+#define FKV_HD __host__ __device__ __forceinline__
+#else
+#define FKV_HD inline
+#endif
 constexpr int kStatusWords = 8;   // status arrays hold one int32 per KvCopyStatus bit
 
 enum KvCopyStatus : int {
@@ -51,6 +58,14 @@ struct KvCopyParams {
   // how many leading entries of gpu_ptrs / c_ptrs the caller filled: every launch path rejects a call whose
   // largest table index (last layer, last kv plane) is not below these counts
   int32_t num_gpu_ptrs, num_c_ptrs, pad0_;
+  // A registration of more than kMaxGpuPtrs tensors (K and V tensors of a model deeper than 128 layers) keeps
+  // its table outside the parameters: `*_ext` is the table as the executing side reads it (device memory for a
+  // kernel, host memory for host_kv_copy), `*_ext_host` the same entries readable by the launching host code
+  // (argument checks, copy-engine planning). Null: the inline arrays above are the table.
+  const uint64_t* gpu_ptrs_ext;
+  const uint64_t* gpu_ptrs_ext_host;
+  const uint64_t* c_ptrs_ext;
+  const uint64_t* c_ptrs_ext_host;
   const int64_t* gpu_blocks;
   const int64_t* cpu_blocks;
   int32_t num_pairs;
@@ -78,6 +93,22 @@ struct KvCopyParams {
   uint32_t epoch;
   int32_t layer_major;
 };
+
+// Entry i of the two tensor tables, wherever they live. Device code reads the device view, host code the host view.
+FKV_HD uint64_t kv_gpu_tensor(const KvCopyParams& p, int i) {
+#if defined(__CUDA_ARCH__)
+  return p.gpu_ptrs_ext ? p.gpu_ptrs_ext[i] : p.gpu_ptrs[i];
+#else
+  return p.gpu_ptrs_ext_host ? p.gpu_ptrs_ext_host[i] : p.gpu_ptrs[i];
+#endif
+}
+FKV_HD uint64_t kv_c_tensor(const KvCopyParams& p, int i) {
+#if defined(__CUDA_ARCH__)
+  return p.c_ptrs_ext ? p.c_ptrs_ext[i] : p.c_ptrs[i];
+#else
+  return p.c_ptrs_ext_host ? p.c_ptrs_ext_host[i] : p.c_ptrs[i];
+#endif
+}
 
 struct KvCopyLaunch {
   int32_t num_ctas;     // persistent CTAs (each one bulk-copy pipeline)
@@ -112,14 +143,18 @@ bool kv_copy_tma_eligible(const KvCopyParams& p);
 
 // True when the tensor tables cover every (layer, kv) the call addresses: index multipliers and the layer
 // range are non-negative, the largest index layer*idx_layer_mul + kv*idx_kv_mul is below the filled count
-// (itself at most kMaxGpuPtrs) and no addressed entry is null; the same for the c_ptrs table when it is in
-// use. A short pointer list after a re-registration or wrong multipliers are refused here, on the host,
-// instead of sending the kernel to a zero or foreign address.
+// (at most kMaxGpuPtrs for the inline arrays, kMaxGpuPtrsExt for a table of its own, which must come with
+// its host view) and no addressed entry is null; the same for the c_ptrs table when it is in use. A short
+// pointer list after a re-registration or wrong multipliers are refused here, on the host, instead of
+// sending the kernel to a zero or foreign address.
 inline bool kv_copy_tables_ok(const KvCopyParams& p) {
   if (p.num_layers < 0 || p.layer_start < 0 || p.kv_dim < 0) return false;
   if (p.num_layers == 0 || p.kv_dim == 0) return true;   // nothing is addressed
-  auto table_ok = [&](const uint64_t* tbl, int32_t filled, int32_t lmul, int32_t kmul) {
-    if (lmul < 0 || kmul < 0 || filled <= 0 || filled > kMaxGpuPtrs) return false;
+  auto table_ok = [&](const uint64_t* inl, const uint64_t* ext, const uint64_t* ext_host, int32_t filled,
+                      int32_t lmul, int32_t kmul) {
+    if ((ext == nullptr) != (ext_host == nullptr)) return false;
+    const uint64_t* tbl = ext_host ? ext_host : inl;
+    if (lmul < 0 || kmul < 0 || filled <= 0 || filled > (ext_host ? kMaxGpuPtrsExt : kMaxGpuPtrs)) return false;
     const int64_t last = (int64_t)(p.layer_start + p.num_layers - 1) * lmul + (int64_t)(p.kv_dim - 1) * kmul;
     if (last >= filled) return false;
     for (int32_t l = p.layer_start; l < p.layer_start + p.num_layers; ++l)
@@ -127,8 +162,11 @@ inline bool kv_copy_tables_ok(const KvCopyParams& p) {
         if (tbl[(int64_t)l * lmul + (int64_t)k * kmul] == 0) return false;
     return true;
   };
-  if (!table_ok(p.gpu_ptrs, p.num_gpu_ptrs, p.idx_layer_mul, p.idx_kv_mul)) return false;
-  if (p.c_use_table && !table_ok(p.c_ptrs, p.num_c_ptrs, p.c_idx_layer_mul, p.c_idx_kv_mul)) return false;
+  if (!table_ok(p.gpu_ptrs, p.gpu_ptrs_ext, p.gpu_ptrs_ext_host, p.num_gpu_ptrs, p.idx_layer_mul, p.idx_kv_mul))
+    return false;
+  if (p.c_use_table &&
+      !table_ok(p.c_ptrs, p.c_ptrs_ext, p.c_ptrs_ext_host, p.num_c_ptrs, p.c_idx_layer_mul, p.c_idx_kv_mul))
+    return false;
   return true;
 }
 

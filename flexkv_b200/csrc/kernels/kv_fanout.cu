@@ -84,13 +84,13 @@ kv_fanout_kernel(const __grid_constant__ KvFanoutParams fp, int tile_bytes, int 
           bool ok = true;
           if (p.gpu_num_blocks > 0 && (gblk < 0 || gblk >= p.gpu_num_blocks)) { err |= KV_ERR_GPU_BLOCK_RANGE; ok = false; }
           if (p.cpu_num_blocks > 0 && (cblk < 0 || cblk >= p.cpu_num_blocks)) { err |= KV_ERR_CPU_BLOCK_RANGE; ok = false; }
-          const uint64_t g = p.gpu_ptrs[layer * p.idx_layer_mul + kv * p.idx_kv_mul] + layer * p.g_layer_stride +
+          const uint64_t g = kv_gpu_tensor(p, layer * p.idx_layer_mul + kv * p.idx_kv_mul) + layer * p.g_layer_stride +
                              kv * p.g_kv_stride + gblk * p.g_block_stride + p.g_off + off;
           const uint64_t c = p.cpu_base + layer * p.c_layer_stride + kv * p.c_kv_stride + cblk * p.c_block_stride +
                              p.c_off + off;
           // multicast twin of the local address: per-tensor table when given, else one delta for the whole cache
           const int ti = layer * p.idx_layer_mul + kv * p.idx_kv_mul;
-          s_dst[st] = p.num_c_ptrs > 0 ? p.c_ptrs[ti] + (g - p.gpu_ptrs[ti]) : g + (uint64_t)fp.mc_delta;
+          s_dst[st] = p.num_c_ptrs > 0 ? kv_c_tensor(p, ti) + (g - kv_gpu_tensor(p, ti)) : g + (uint64_t)fp.mc_delta;
           if (!ok) {
             // keep the barrier protocol uniform: publish an empty tile
             s_bytes[st] = 0;
@@ -168,7 +168,7 @@ cudaError_t launch_kv_fanout(const KvFanoutParams& fp, int num_ctas, int tile_by
   if (p.num_c_ptrs > 0) {
     if (p.num_c_ptrs != p.num_gpu_ptrs) return cudaErrorInvalidValue;
     for (int i = 0; i < p.num_c_ptrs; ++i)
-      if (p.c_ptrs[i] == 0 || (p.c_ptrs[i] & 15)) return cudaErrorInvalidValue;
+      if (kv_c_tensor(p, i) == 0 || (kv_c_tensor(p, i) & 15)) return cudaErrorInvalidValue;
   }
   int tile = tile_bytes > 0 ? (tile_bytes / 16) * 16 : 16384;
   if (tile > 16384) tile = 16384;

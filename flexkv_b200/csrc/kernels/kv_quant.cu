@@ -83,7 +83,7 @@ __global__ void __launch_bounds__(kThreads, 1) kv_quant_fp8_kernel(const __grid_
     const int64_t e0 = (int64_t)s_ * kTileElems;
     const int64_t left = chunk_elems - e0;
     const int32_t elems = (int32_t)(left < kTileElems ? left : kTileElems);
-    const uint64_t g = p.gpu_ptrs[layer * p.idx_layer_mul + kv * p.idx_kv_mul] + layer * p.g_layer_stride +
+    const uint64_t g = kv_gpu_tensor(p, layer * p.idx_layer_mul + kv * p.idx_kv_mul) + layer * p.g_layer_stride +
                        kv * p.g_kv_stride + gblk * p.g_block_stride + p.g_off + e0 * 2;
     const uint64_t c = p.cpu_base + layer * p.c_layer_stride + kv * p.c_kv_stride + cblk * p.c_block_stride + p.c_off;
     const uint64_t c_payload = c + e0, c_scales = c + chunk_elems + (e0 / kQuantGroup) * 4;

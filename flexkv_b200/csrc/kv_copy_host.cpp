@@ -98,11 +98,11 @@ int host_kv_copy(const KvCopyParams& p, int num_threads) {
       if (p.gpu_num_blocks > 0 && (g < 0 || g >= p.gpu_num_blocks)) { err |= KV_ERR_GPU_BLOCK_RANGE; continue; }
       if (p.cpu_num_blocks > 0 && (c < 0 || c >= p.cpu_num_blocks)) { err |= KV_ERR_CPU_BLOCK_RANGE; continue; }
       for (int kv = 0; kv < p.kv_dim; ++kv) {
-        uint8_t* ga = reinterpret_cast<uint8_t*>(p.gpu_ptrs[layer * p.idx_layer_mul + kv * p.idx_kv_mul] +
+        uint8_t* ga = reinterpret_cast<uint8_t*>(kv_gpu_tensor(p, layer * p.idx_layer_mul + kv * p.idx_kv_mul) +
                                                  layer * p.g_layer_stride + kv * p.g_kv_stride +
                                                  g * p.g_block_stride + p.g_off);
         const uint64_t cbase =
-            p.c_use_table ? p.c_ptrs[layer * p.c_idx_layer_mul + kv * p.c_idx_kv_mul] : p.cpu_base;
+            p.c_use_table ? kv_c_tensor(p, layer * p.c_idx_layer_mul + kv * p.c_idx_kv_mul) : p.cpu_base;
         uint8_t* ca = reinterpret_cast<uint8_t*>(cbase + layer * p.c_layer_stride + kv * p.c_kv_stride +
                                                  c * p.c_block_stride + p.c_off);
         if (p.h2d) std::memcpy(ga, ca, (size_t)p.chunk_bytes);

@@ -313,13 +313,13 @@ void LayerwiseGroup::rank_main(int r) {
 }
 
 void LayerwiseGroup::update_gpu_ptrs(int rank, const std::vector<uint64_t>& ptrs) {
-  if ((int)ptrs.size() > kMaxGpuPtrs) throw std::invalid_argument("too many GPU tensors");
+  if ((int)ptrs.size() > kMaxGpuPtrsExt) throw std::invalid_argument("too many GPU tensors");
   std::lock_guard<std::mutex> api(api_mu_);
   gpus_.at((size_t)rank).ptrs = ptrs;
 }
 
 void LayerwiseGroup::update_group_gpu_ptrs(int group, int rank, const std::vector<uint64_t>& ptrs) {
-  if ((int)ptrs.size() > kMaxGpuPtrs) throw std::invalid_argument("too many GPU tensors");
+  if ((int)ptrs.size() > kMaxGpuPtrsExt) throw std::invalid_argument("too many GPU tensors");
   std::lock_guard<std::mutex> api(api_mu_);
   mgroups_.at((size_t)group).gpus.at((size_t)rank).ptrs = ptrs;
 }

@@ -1,4 +1,5 @@
 #include "peer_copier.h"
+#include "ptr_table.h"
 
 #include <cstring>
 #include <stdexcept>
@@ -77,7 +78,7 @@ bool PeerCopier::can_access(int dst_rank, int src_rank) {
 }
 
 void PeerCopier::update_gpu_ptrs(int rank, const std::vector<uint64_t>& ptrs) {
-  if ((int)ptrs.size() > kMaxGpuPtrs) throw std::invalid_argument("too many GPU tensors");
+  if ((int)ptrs.size() > kMaxGpuPtrsExt) throw std::invalid_argument("too many GPU tensors");
   ranks_.at((size_t)rank).ptrs = ptrs;
 }
 
@@ -100,12 +101,10 @@ OpResult PeerCopier::pull(int dst_rank, int src_rank, const int64_t* dst_blocks,
   KvCopyParams p;
   std::memset(&p, 0, sizeof(p));
   // "gpu" side = local destination, "cpu" side = the peer's tensors; direction = peer -> local
-  for (size_t i = 0; i < dg.ptrs.size(); ++i) p.gpu_ptrs[i] = dg.ptrs[i];
-  p.num_gpu_ptrs = (int32_t)dg.ptrs.size();
+  kv_set_gpu_table(p, dg.ptrs, dg.device);
   p.idx_layer_mul = dg.idx_layer_mul; p.idx_kv_mul = dg.idx_kv_mul;
   p.g_layer_stride = dg.layer_stride; p.g_kv_stride = dg.kv_stride; p.g_block_stride = dg.block_stride;
-  for (size_t i = 0; i < sg.ptrs.size(); ++i) p.c_ptrs[i] = sg.ptrs[i];
-  p.num_c_ptrs = (int32_t)sg.ptrs.size();
+  kv_set_c_table(p, sg.ptrs, dg.device);      // the peer's addresses, read by the kernel on the local device
   p.c_use_table = 1;
   p.c_idx_layer_mul = sg.idx_layer_mul; p.c_idx_kv_mul = sg.idx_kv_mul;
   p.c_layer_stride = sg.layer_stride; p.c_kv_stride = sg.kv_stride; p.c_block_stride = sg.block_stride;

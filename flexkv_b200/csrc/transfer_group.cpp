@@ -3,6 +3,7 @@
 #include <climits>
 
 #include "ce_copy.h"
+#include "ptr_table.h"
 
 #include <algorithm>
 #include <cstring>
@@ -32,7 +33,7 @@ TransferGroup::TransferGroup(std::vector<GpuSide> gpus, HostSide host, GroupOpti
     : gpus_(std::move(gpus)), host_(host), opt_(opt) {
   if (gpus_.empty()) throw std::invalid_argument("TransferGroup: no GPUs");
   for (auto& g : gpus_)
-    if ((int)g.ptrs.size() > kMaxGpuPtrs) throw std::invalid_argument("TransferGroup: too many GPU tensors per rank");
+    if ((int)g.ptrs.size() > kMaxGpuPtrsExt) throw std::invalid_argument("TransferGroup: too many GPU tensors per rank");
   if (opt_.shared_kv && opt_.shared_mode == SharedKvMode::SHARDED && (opt_.chunk_bytes % (int64_t)gpus_.size()) != 0)
     throw std::invalid_argument("TransferGroup: sharded shared-KV mode needs chunk_bytes divisible by the group size");
   check(cudaSetDevice(gpus_[0].device), "cudaSetDevice");
@@ -67,7 +68,7 @@ TransferGroup::~TransferGroup() {
 }
 
 void TransferGroup::update_gpu_ptrs(int rank, const std::vector<uint64_t>& ptrs) {
-  if ((int)ptrs.size() > kMaxGpuPtrs) throw std::invalid_argument("too many GPU tensors");
+  if ((int)ptrs.size() > kMaxGpuPtrsExt) throw std::invalid_argument("too many GPU tensors");
   std::lock_guard<std::mutex> g(ptr_mu_);
   gpus_.at((size_t)rank).ptrs = ptrs;
 }
@@ -81,8 +82,7 @@ void fill_kv_params(const GpuSide& gs, const HostSide& host, const GroupOptions&
                     const int64_t* gpu_blocks, const int64_t* cpu_blocks, int64_t n, bool h2d, int layer_start,
                     int num_layers, uint64_t rotate, KvCopyParams& p, bool& skip) {
   std::memset(&p, 0, sizeof(p));
-  for (size_t i = 0; i < gs.ptrs.size(); ++i) p.gpu_ptrs[i] = gs.ptrs[i];
-  p.num_gpu_ptrs = (int32_t)gs.ptrs.size();
+  kv_set_gpu_table(p, gs.ptrs, gs.device);
   p.idx_layer_mul = gs.idx_layer_mul;
   p.idx_kv_mul = gs.idx_kv_mul;
   p.g_layer_stride = gs.layer_stride;

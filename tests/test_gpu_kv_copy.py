@@ -47,6 +47,7 @@ CASES = [
     ("trtllm", False, KVShape("d", 3, 2, 16, tokens_per_block=4)),
     ("vllm", False, KVShape("mla", 3, 1, 576, use_mla=True, tokens_per_block=64)),
     ("vllm", False, KVShape("odd", 2, 1, 585, dtype=torch.uint8, use_mla=True, tokens_per_block=8)),  # 4680 B chunks
+    ("sglang", False, KVShape("deep", 136, 2, 16, tokens_per_block=4)),      # 272 tensors: table in device memory
 ]
 
 

@@ -37,6 +37,8 @@ def _chunks(tensors, engine_layout, shape, blocks):
     ("sglang", KVShape("b", 3, 2, 128, tokens_per_block=16)),
     ("trtllm", KVShape("c", 2, 2, 64, tokens_per_block=8)),
     ("vllm", KVShape("m", 5, 1, 576, use_mla=True, tokens_per_block=64)),
+    # 288 tensors: more than the launch parameters carry, so the tensor table lives in device memory
+    ("sglang", KVShape("deep", 144, 2, 16, tokens_per_block=8)),
 ])
 def test_put_get_roundtrip(engine_layout, shape, tmp_path):
     dev = torch.device("cuda:0")

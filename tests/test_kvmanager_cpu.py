@@ -49,6 +49,7 @@ def start(shape, engine_layout, NB=64, tp=1, **cache_kw):
     ("sglang", KVShape("b", 2, 2, 32, tokens_per_block=8)),
     ("trtllm", KVShape("c", 2, 2, 16, tokens_per_block=4)),
     ("vllm", KVShape("m", 3, 1, 64, use_mla=True, tokens_per_block=4)),
+    ("sglang", KVShape("deep", 130, 2, 8, tokens_per_block=4)),      # 260 tensors: past the inline pointer table
 ])
 def test_roundtrip_host_and_ssd(engine_layout, shape, tmp_path):
     T = shape.tokens_per_block
