@@ -287,7 +287,16 @@ class GlobalCacheEngine:
             self.cache_engines[DeviceType.SSD] = self.ssd_cache_engine
         if cache_config.enable_remote and cache_config.num_remote_blocks and \
                 not cache_config.use_mooncake_store_backend:
-            self.remote_cache_engine = CacheEngine(DeviceType.REMOTE, cache_config.num_remote_blocks, **common)
+            if cache_config.enable_3rd_remote:
+                # a remote file system every node mounts: each node writes files of its own, publishes which
+                # blocks they hold, and reads the other nodes' files (the role PCFS has in the reference:
+                # flexkv/cache/hie_cache_engine.py:561-643, flexkv/cache/cache_engine.py:1024-1033)
+                from .hie_cache_engine import HierarchyLRCacheEngine, get_node_registry
+                self.node_registry = self.node_registry or get_node_registry(cache_config, model_config)
+                self.remote_cache_engine = HierarchyLRCacheEngine(DeviceType.REMOTE, cache_config.num_remote_blocks,
+                                                                  registry=self.node_registry, **common)
+            else:
+                self.remote_cache_engine = CacheEngine(DeviceType.REMOTE, cache_config.num_remote_blocks, **common)
             self.cache_engines[DeviceType.REMOTE] = self.remote_cache_engine
         if not self.cache_engines:
             raise ValueError("at least one cache tier must be enabled")
@@ -552,7 +561,7 @@ class GlobalCacheEngine:
             f3_lo = max(bstart, end)
             f3 = max(0, r_hit - f3_lo)
         # fragment 3 may instead come from another node's host pool when that node holds a longer prefix
-        peer_host_nids, peer_is_ssd = None, False
+        peer_host_nids, peer_is_ssd, peer_is_remote = None, False, False
         if self.node_registry is not None and not cpu_only and not use_gds_early and hasattr(cpu, "match_remote"):
             pm = cpu.match_remote(seq, bend)
             if pm.num_matched_blocks > max(end, f3_lo + f3):
@@ -571,6 +580,16 @@ class GlobalCacheEngine:
                 peer_host_nids = sm.node_ids[f3_lo:f3_lo + f3]
                 peer_host_src = sm.physical_blocks[f3_lo:f3_lo + f3]
                 peer_is_ssd, remote_m = True, None
+        # ... or out of the files another node wrote to the remote file system all nodes mount
+        if self.node_registry is not None and not cpu_only and not use_gds_early and \
+                hasattr(self.remote_cache_engine, "match_remote"):
+            rm = self.remote_cache_engine.match_remote(seq, bend)
+            if rm.num_matched_blocks > max(end, f3_lo + f3):
+                f3_lo = max(bstart, end)
+                f3 = rm.num_matched_blocks - f3_lo
+                peer_host_nids = rm.node_ids[f3_lo:f3_lo + f3]
+                peer_host_src = rm.physical_blocks[f3_lo:f3_lo + f3]
+                peer_is_ssd, peer_is_remote, remote_m = False, True, None
         if f0 + f1 + f2 + f3 == 0:
             return None
         graph = TransferOpGraph()
@@ -636,6 +655,7 @@ class GlobalCacheEngine:
             src3 = remote_m.physical_blocks[f3_lo:f3_lo + f3] if remote_m is not None else np.zeros(f3, dtype=np.int64)
             if peer_host_nids is not None:
                 remote_op = TransferOp(graph.graph_id,
+                                       TransferType.REMOTE2H if peer_is_remote else
                                        TransferType.PEERSSD2H if peer_is_ssd else TransferType.PEERH2H,
                                        peer_host_src, staging3,
                                        dp_client_id=dp_client_id, block_hashes=hashes3,

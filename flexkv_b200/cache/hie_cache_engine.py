@@ -52,7 +52,8 @@ class HierarchyLRCacheEngine(CacheEngine):
         if registry.node_id is None:
             registry.register()
         self.node_id = int(registry.node_id)
-        kind = {DeviceType.CPU: "CPUB", DeviceType.SSD: "SSDB"}.get(device_type, "CPUB")
+        # record families of the three published tiers (the reference names its shared remote tier after PCFS)
+        kind = {DeviceType.CPU: "CPUB", DeviceType.SSD: "SSDB", DeviceType.REMOTE: "PCFSB"}.get(device_type, "CPUB")
         if channel is None:
             # a registry in a Redis server gets the native channel, the in-box registry the Python one
             native = getattr(registry.client, "native_channel", None)

@@ -386,9 +386,9 @@ class CacheConfig:
             out.append(("mooncake_config_path / mooncake_store_config_path",
                         "no Mooncake library in this build: peer reads map the owner's pool or block files, the "
                         "key-addressed store is remote_config_custom"))
-        if self.enable_3rd_remote:
-            out.append(("enable_3rd_remote", "no PCFS SDK in this build: the remote tier is a block-addressed file "
-                                             "set (remote_cache_path) or a key-addressed store"))
+        if self.enable_3rd_remote and self.use_mooncake_store_backend:
+            out.append(("enable_3rd_remote", "a key-addressed store is shared by its keys already; the published "
+                                             "block index applies to the block-addressed file set only"))
         if self.distributed_node_id >= 0:
             out.append(("distributed_node_id", "node ids are allocated by the registry"))
         if (self.local_zmq_ip, self.local_zmq_port) != ("127.0.0.1", 5555):

@@ -167,7 +167,7 @@ class StorageEngine:
                          compression_enabled=bool(c.enable_compression or self.env.enable_compression),
                          dtype=m.dtype, host_layout_type=lay.type, chunk_elems_per_rank=lay.get_chunk_size() // slices,
                          itemsize=m.dtype.itemsize, layerwise=bool(self.env.enable_layerwise_transfer),
-                         peer_host_sharing=bool(c.enable_p2p_cpu or c.enable_p2p_ssd),
+                         peer_host_sharing=bool(c.enable_p2p_cpu or c.enable_p2p_ssd or c.enable_3rd_remote),
                          pipeline_stages=m.local_pp_stages)
         if d.reason:
             flexkv_logger.warning("host codec refused: %s; every tier runs uncompressed", d.reason)

@@ -594,12 +594,65 @@ class RemoteWorker(TransferWorker):
     store). Reports a per-block result list; any failed block fails the op
     (flexkv/transfer/worker.py:1715-1946,3875-4092)."""
 
-    def __init__(self, storage, backend, to_host: bool) -> None:
+    def __init__(self, storage, backend, to_host: bool, registry=None) -> None:
         super().__init__()
         self.storage, self.backend, self.to_host = storage, backend, to_host
         self.name = "remote2h" if to_host else "h2remote"
+        self.registry = registry
+        self._peer_files: Dict[int, Any] = {}
+
+    def _files_of(self, nid: int):
+        """The files node `nid` wrote to the shared remote file system, opened read-only once."""
+        ent = self._peer_files.get(nid)
+        if ent is not None:
+            return ent
+        import json
+        from ..external.remote_store import PeerRemoteFiles
+        meta = self.registry.get_node_meta(nid) if self.registry is not None else None
+        if not meta or not meta.get("remote_files"):
+            raise RuntimeError(f"node {nid} has no remote files in the registry")
+        if int(meta["remote_block_bytes"]) != self.storage.host.block_bytes or \
+                meta.get("codec", "none") != self.storage.host.quant:
+            raise RuntimeError(f"node {nid} uses a different block format")
+        ent = PeerRemoteFiles(json.loads(meta["remote_files"]), int(meta["remote_block_bytes"]),
+                              int(meta["remote_num_blocks"]))
+        self._peer_files[nid] = ent
+        return ent
+
+    def _execute_peer(self, op: TransferOp) -> OpOutcome:
+        """REMOTE2H whose blocks live in other nodes' files (``remote_node_ids`` names the owner per block)."""
+        host = self.storage.host
+        src = np.asarray(op.src_block_ids, dtype=np.int64)
+        dst = np.asarray(op.dst_block_ids, dtype=np.int64)
+        owners = np.asarray(op.remote_node_ids, dtype=np.int64)
+        n = len(src)
+        if len(owners) != n or len(dst) != n:
+            return OpOutcome(False, error="peer remote op without owner ids")
+        results, err = [False] * n, ""
+        for nid in np.unique(owners).tolist():
+            sel = np.nonzero(owners == nid)[0]
+            try:
+                files = self._files_of(int(nid))
+                got = files.get(src[sel].tolist(), [host.block_view(int(b)) for b in dst[sel]])
+                for k, good in zip(sel.tolist(), got):
+                    results[k] = bool(good)
+            except (RuntimeError, OSError, ValueError) as e:
+                err = str(e)
+                self._peer_files.pop(int(nid), None)
+        ok = all(results)
+        if not ok and op.allow_partial and results and results[0]:
+            return OpOutcome(True, block_results=tuple(results), num_bytes=sum(results) * host.block_bytes)
+        return OpOutcome(ok, block_results=tuple(results), num_bytes=sum(results) * host.block_bytes,
+                         error="" if ok else f"{n - sum(results)} block(s) of other nodes' remote files failed: {err}")
+
+    def close(self) -> None:
+        for f in self._peer_files.values():
+            f.close()
+        self._peer_files.clear()
 
     def execute(self, op: TransferOp) -> OpOutcome:
+        if self.to_host and op.remote_node_ids is not None:
+            return self._execute_peer(op)
         host = self.storage.host
         if self.to_host:
             rids, cpu = op.src_block_ids, op.dst_block_ids
@@ -1114,7 +1167,11 @@ def build_workers(storage, model_config: ModelConfig, cache_config: CacheConfig
         from ..external.remote_store import get_backend
         backend = get_backend(cache_config, storage.host.block_bytes)
         if backend is not None:
-            workers[(WorkerKey(0, 0), TransferType.REMOTE2H)] = RemoteWorker(storage, backend, True)
+            registry = None
+            if cache_config.enable_3rd_remote and not backend.key_addressed:
+                from ..cache.hie_cache_engine import get_node_registry
+                registry = get_node_registry(cache_config, model_config)
+            workers[(WorkerKey(0, 0), TransferType.REMOTE2H)] = RemoteWorker(storage, backend, True, registry)
             workers[(WorkerKey(0, 0), TransferType.H2REMOTE)] = RemoteWorker(storage, backend, False)
     if cache_config.enable_p2p_cpu and storage.host is not None:
         from ..cache.hie_cache_engine import get_node_registry

@@ -156,6 +156,17 @@ class TransferManager:
                                        ssd_blocks_per_file=ssd.blocks_per_file, ssd_num_blocks=ssd.num_blocks,
                                        ssd_layout=json.dumps(self.storage.ssd_layout_dict(), sort_keys=True),
                                        codec=self.storage.host.quant))
+            if self.cache_config.enable_3rd_remote and self.cache_config.enable_remote and \
+                    not self.cache_config.use_mooncake_store_backend and self.storage.host is not None:
+                # what a peer needs to read the files this node writes to the shared remote file system
+                import json
+                from .cache.hie_cache_engine import get_node_registry
+                from .external.remote_store import get_backend
+                backend = get_backend(self.cache_config, self.storage.host.block_bytes)
+                if backend is not None and getattr(backend, "files", None):
+                    get_node_registry(self.cache_config, self.model_config).set_node_meta(dict(
+                        remote_files=json.dumps(backend.files), remote_block_bytes=backend.block_bytes,
+                        remote_num_blocks=backend.num_blocks, codec=self.storage.host.quant))
             # graph state in the native scheduler (default) or the Python specification of it
             engine_cls = TransferEngine if GLOBAL_CONFIG_FROM_ENV.native_scheduler else TransferEngineSpec
             self.engine = engine_cls(self.storage, self.model_config, self.cache_config)

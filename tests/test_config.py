@@ -132,9 +132,11 @@ def test_settings_kept_for_compatibility_are_reported_not_ignored_silently():
     assert c.enable_gds is True                     # NIXL's role (SSD <-> GPU) is served by the GDS worker
     names = [n for n, _ in c.settings_without_effect()]
     assert names == ["enable_nixl", "use_hugepage_tmp_buffer / num_tmp_cpu_blocks",
-                     "mooncake_config_path / mooncake_store_config_path", "enable_3rd_remote",
+                     "mooncake_config_path / mooncake_store_config_path",
                      "distributed_node_id", "local_zmq_ip / local_zmq_port"]
-    assert c.enable_kv_sharing and c.enable_remote
+    assert c.enable_kv_sharing and c.enable_remote        # enable_3rd_remote: the shared remote tier is on
+    c = CacheConfig(enable_3rd_remote=True, use_mooncake_store_backend=True)
+    assert [n for n, _ in c.settings_without_effect()] == ["enable_3rd_remote"]
 
 
 def test_a_deployment_file_written_for_the_reference_loads(tmp_path):

@@ -248,3 +248,86 @@ def test_cluster_wide_reset_withdraws_every_nodes_blocks():
     finally:
         a.shutdown()
         b.shutdown()
+
+
+def test_node_b_restores_from_the_files_node_a_wrote_to_the_shared_remote_mount(tmp_path):
+    """enable_3rd_remote: every node writes remote files of its own on a mount all nodes see and publishes which
+    blocks they hold; node B, which never saw the prompt, reads the blocks out of A's files (REMOTE2H with owner
+    ids), adopts them into its host tier and restores them (the role PCFS has in the reference:
+    flexkv/cache/hie_cache_engine.py:239-378,561-643; tests/test_pcfs*.py need its SDK)."""
+    import os
+    name = uuid.uuid4().hex
+    shape = KVShape("p", 2, 2, 16, tokens_per_block=T)
+    shared = tmp_path / "mount"
+
+    def start(seed, cpu_blocks):
+        cfg = CacheConfig(tokens_per_block=T, num_cpu_blocks=cpu_blocks, enable_remote=True, enable_3rd_remote=True,
+                          num_remote_blocks=64, remote_cache_path=str(shared), remote_file_num=2,
+                          remote_file_prefix="kv", redis_host=f"inproc:{name}")
+        mgr = KVManager(make_model_config(shape), cfg, require_gpu=True)
+        kv, layout = alloc_paged_cache(shape, 64, "cpu", "vllm", fill="normal", seed=seed)
+        mgr.register_gpu_tensors(kv, layout)
+        mgr.start(); mgr.wait_ready(30)
+        return mgr, kv
+
+    a, kva = start(1, 12)
+    b, kvb = start(2, 24)
+    try:
+        ga, gb = a.kv_task_engine.cache_engine, b.kv_task_engine.cache_engine
+        names = sorted(os.listdir(shared))
+        assert len(names) == 4 and len({n.rsplit("_", 1)[0] for n in names}) == 2, names   # two files per node
+        tok = np.arange(10 * T, dtype=np.int64) + 7000
+        src = np.array([5, 6, 7, 20, 21, 3, 40, 41, 42, 43])
+        tid = a.put_async(tok, slots(src))
+        assert a.wait(tid, completely=True)[tid].status.value == "success"
+        # push the prefix out of A's 12-block host pool: only its remote files keep it
+        other = np.arange(10 * T, dtype=np.int64) + 90000
+        tid = a.put_async(other, slots(np.arange(50, 60)))
+        assert a.wait(tid, completely=True)[tid].status.value == "success"
+        from flexkv_b200.common.block import SequenceMeta
+        seq = SequenceMeta(tok, T)
+        assert ga.cpu_cache_engine.match(seq).num_ready_matched_blocks < 10
+        assert ga.remote_cache_engine.match(seq).num_ready_matched_blocks == 10
+        ga.remote_cache_engine.refresh(); gb.remote_cache_engine.refresh()
+        assert gb.remote_cache_engine.match_remote(seq).num_matched_blocks == 10
+        assert gb.remote_cache_engine.match(seq).num_matched_blocks == 0           # B itself holds nothing
+        tid, mask = b.get_match(tok)
+        assert int(mask.sum()) == 10 * T
+        ops = list(b.kv_task_engine.tasks[tid].graph.ops())
+        kinds = sorted(o.transfer_type.value for o in ops)
+        assert kinds == ["H2D", "REMOTE2H"], kinds
+        assert next(o for o in ops if o.transfer_type.value == "REMOTE2H").remote_node_ids is not None
+        dst = np.arange(20, 30)
+        for t in kvb:
+            t[:, dst] = 0
+        b.launch(tid, slots(dst))
+        assert b.wait(tid, timeout=30)[tid].status.value == "success"
+        for l in range(2):
+            assert torch.equal(kvb[l][:, dst], kva[l][:, src])
+        # adopted by B's host tier: the next get is local
+        tid, mask = b.get_match(tok)
+        assert [o.transfer_type.value for o in b.kv_task_engine.tasks[tid].graph.ops()] == ["H2D"]
+        b.cancel(tid)
+        # an owner whose files are gone fails the op, it does not hang or return stale bytes
+        tok2 = np.arange(4 * T, dtype=np.int64) + 555000
+        tid = a.put_async(tok2, slots(np.array([1, 2, 3, 4])))
+        assert a.wait(tid, completely=True)[tid].status.value == "success"
+        ga.remote_cache_engine.refresh(); gb.remote_cache_engine.refresh()
+        w = next(w for (k, tt), w in b.kv_task_engine.transfer_handles[0].engine._workers.items()
+                 if getattr(tt, "value", tt) == "REMOTE2H")
+        w.close()
+        meta_key_files = [str(shared / n) for n in names]
+        a_id = ga.node_registry.node_id
+        hidden = [f for f in meta_key_files if f"_n{a_id}_" in f]
+        for f in hidden:
+            os.rename(f, f + ".gone")
+        # A still serves its host copy to itself; B has to go through A's files, which are gone
+        tid, mask = b.get_match(tok2)
+        assert int(mask.sum()) == 4 * T
+        b.launch(tid, slots(np.arange(30, 34)))
+        assert b.wait(tid, timeout=30)[tid].status.value == "failed"
+        for f in hidden:
+            os.rename(f + ".gone", f)
+    finally:
+        a.shutdown()
+        b.shutdown()
