@@ -75,6 +75,7 @@ class RadixTreeIndex:
         self._root.ready = True
         self._stats = dict(hit=0, match=0, miss=0, insert_blocks=0, evict_blocks=0)
         self._swa_lru: List[PyNode] = []       # least recently used first
+        self._swa_armed = False                # a snapshot was mounted at least once
         self._freed_swa: List[int] = []
 
     # ---- helpers ----------------------------------------------------------------
@@ -275,10 +276,28 @@ class RadixTreeIndex:
                 parent = node.parent
                 del parent.children[node.hashes[0]]
                 self._free(node)
+                parent = self._prune_snapshotless_leaves(parent, blocks, hashes)
                 if self._evictable(parent):
                     heapq.heappush(heap, (self._key(parent), id(parent), parent))
         self._stats["evict_blocks"] += len(blocks)
         return np.asarray(blocks, dtype=np.int64), np.asarray(hashes, dtype=np.uint64)
+
+    def _prune_snapshotless_leaves(self, node: PyNode, blocks: List[int], hashes: List[int]) -> PyNode:
+        """Once window snapshots are in use, a leaf without one serves no window-aware request: after a
+        deletion the ancestors that became such leaves (evictable, no snapshot) go too, their blocks are
+        appended beyond what the caller asked for. Returns the first ancestor that stays
+        (reference: flexkv/cache/radixtree.py:726-749)."""
+        if not self._swa_armed:
+            return node
+        while node is not self._root and node.is_leaf() and node.swa_slot < 0 and self._evictable(node):
+            blocks.extend(node.blocks)
+            hashes.extend(node.hashes)
+            self._total_blocks -= node.size()
+            parent = node.parent
+            del parent.children[node.hashes[0]]
+            self._free(node)
+            node = parent
+        return node
 
     def lock(self, h: PyNode) -> None:
         self._check(h).lock_cnt += 1
@@ -417,6 +436,7 @@ class RadixTreeIndex:
         if n.swa_slot >= 0 and n.swa_slot != slot:
             self._freed_swa.append(n.swa_slot)
         n.swa_slot = int(slot)
+        self._swa_armed = True          # stays set across reset(): the deployment uses window snapshots
         self._swa_touch(n)
 
     def has_swa(self, h) -> bool:
@@ -457,8 +477,12 @@ class RadixTreeIndex:
                 hashes.extend(node.hashes)
                 self._total_blocks -= node.size()
                 self._stats["evict_blocks"] += node.size()
-                del node.parent.children[node.hashes[0]]
+                parent = node.parent
+                del parent.children[node.hashes[0]]
                 self._free(node)
+                before = len(blocks)
+                self._prune_snapshotless_leaves(parent, blocks, hashes)
+                self._stats["evict_blocks"] += len(blocks) - before
             else:
                 self._drop_swa(node)
             freed += 1

@@ -369,11 +369,29 @@ EvictResult RadixIndex::evict(int64_t num_blocks) {
     uint64_t head = node.hashes.front();
     free_node(idx);
     remove_child(parent, head);
+    parent = prune_snapshotless_leaves(parent, &out.blocks, &out.hashes);
     if (evictable(parent)) heap.push(parent);
   }
   stat_evict_blocks += (uint64_t)out.blocks.size();
   if (!out.blocks.empty()) count_cache_op(kOpEvict, (uint64_t)out.blocks.size());
   return out;
+}
+
+int32_t RadixIndex::prune_snapshotless_leaves(int32_t idx, std::vector<int64_t>* blocks,
+                                             std::vector<uint64_t>* hashes) {
+  if (!swa_armed_) return idx;
+  while (idx > 0 && nodes_[idx].swa_slot < 0 && evictable(idx)) {
+    Node& n = nodes_[idx];
+    if (blocks) blocks->insert(blocks->end(), n.blocks.begin(), n.blocks.end());
+    if (hashes) hashes->insert(hashes->end(), n.hashes.begin(), n.hashes.end());
+    total_blocks_ -= (int64_t)n.size();
+    const int32_t parent = n.parent;
+    const uint64_t head = n.hashes.front();
+    free_node(idx);
+    remove_child(parent, head);
+    idx = parent;
+  }
+  return idx;
 }
 
 void RadixIndex::lock(NodeHandle h) { ++nodes_[resolve_or_throw(h)].lock_cnt; }
@@ -553,6 +571,7 @@ void RadixIndex::set_swa(NodeHandle h, int32_t slot) {
   Node& n = nodes_[idx];
   if (n.swa_slot >= 0 && n.swa_slot != slot) freed_swa_.push_back(n.swa_slot);
   n.swa_slot = slot;
+  swa_armed_ = true;
   swa_touch(idx);
 }
 
@@ -595,6 +614,11 @@ int64_t RadixIndex::evict_swa(int64_t want, std::vector<int64_t>* freed_full, st
       uint64_t head = n.hashes.front();
       free_node(idx);  // drops the snapshot too
       remove_child(parent, head);
+      if (freed_full) {     // without a place to report the blocks nothing more is deleted
+        const size_t before = freed_full->size();
+        prune_snapshotless_leaves(parent, freed_full, freed_hashes);
+        stat_evict_blocks += freed_full->size() - before;
+      }
     } else {
       drop_swa(idx);
     }

@@ -197,6 +197,12 @@ class RadixIndex {
   uint64_t next_serial_ = 0;
   EvictVeto veto_;
   void drop_swa(int32_t idx);           // frees the node's snapshot, if any
+  // Once window snapshots are in use, a leaf without one serves no window-aware request. After a deletion
+  // the ancestors that became such leaves (evictable, no snapshot) are deleted too; their blocks and hashes are
+  // appended to the output, beyond what the caller asked for. Returns the first ancestor that stays
+  // (reference: flexkv/cache/radixtree.py:726-749).
+  int32_t prune_snapshotless_leaves(int32_t idx, std::vector<int64_t>* blocks, std::vector<uint64_t>* hashes);
+  bool swa_armed_ = false;              // a snapshot was mounted at least once; survives reset()
   void swa_touch(int32_t idx);          // moves the node to the recently-used end
   std::list<int32_t> swa_lru_;          // front = least recently used
   std::vector<int32_t> freed_swa_;

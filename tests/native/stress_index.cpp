@@ -55,7 +55,12 @@ static void single_thread_index(uint64_t seed) {
       int64_t need = (int64_t)h.size() - m.num_matched;
       if (need == 0) continue;
       if (pool.num_free() < need) {
+        // as the planner does: the matched node is locked while room is made, so that the eviction (which may
+        // take ancestors left without a snapshot along) cannot delete what the insert is about to extend
+        const bool guard = m.num_matched > 0;
+        if (guard) idx.lock(m.last_node);
         EvictResult ev = idx.evict(need - pool.num_free());
+        if (guard) idx.unlock(m.last_node);
         pool.recycle(ev.blocks.data(), (int64_t)ev.blocks.size());
         for (int32_t s : idx.drain_freed_swa_slots()) CHECK(s >= 0);
       }

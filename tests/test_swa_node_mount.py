@@ -164,3 +164,100 @@ def test_python_specification_and_native_index_agree_on_random_snapshot_workload
             assert sorted(nat.drain_freed_swa_slots().tolist()) == sorted(py.drain_freed_swa_slots().tolist()), (seed, step)
             assert nat.total_swa_slots() == py.total_swa_slots()
             assert nat.total_cached_blocks() == py._total_blocks
+
+
+INDEXES = [("native", lambda: C.RadixIndex(2, 64, "lru", 0.0))]
+
+
+def _py_index():
+    from flexkv_b200.cache.radixtree import RadixTreeIndex
+    return RadixTreeIndex(2, 64, "lru", 0.0)
+
+
+INDEXES.append(("python", _py_index))
+
+
+def _clock(idx, t):
+    if hasattr(idx, "set_clock_override"):
+        idx.set_clock_override(t)
+    else:
+        idx._clock_override = t
+
+
+@pytest.mark.parametrize("name,make", INDEXES)
+def test_a_real_match_refreshes_the_snapshot_and_a_probe_does_not(name, make):
+    """Snapshot-only eviction takes the least recently used snapshot; a match that updates cache information
+    counts as a use, a probe (update_cache_info=False) does not (reference: tests/test_swa_node_mount.py
+    reuse-promotes / probe-does-not-promote, both index back ends)."""
+    for update, survivor in ((True, "a"), (False, "b")):
+        idx = make()
+        _clock(idx, 100)
+        a = idx.insert(_p(0, 1), _h(1, 2), 2, True, None)
+        idx.set_swa(a, 10)
+        b = idx.insert(_p(2, 3), _h(5, 6), 2, True, None)
+        idx.set_swa(b, 11)
+        _clock(idx, 200)
+        m = idx.match_prefix(_h(1, 2), 2, update)
+        assert m.swa_slot == 10
+        assert idx.evict_swa(1)[2] == 1
+        alive = {"a": idx.alive(a) and idx.has_swa(a), "b": idx.alive(b) and idx.has_swa(b)}
+        assert alive == {"a": survivor == "a", "b": survivor == "b"}, (name, update)
+
+
+@pytest.mark.parametrize("name,make", INDEXES)
+def test_window_locked_nodes_and_the_root_survive_full_eviction(name, make):
+    idx = make()
+    assert len(idx.evict(1)[0]) == 0                       # an empty index has nothing to give
+    n = idx.insert(_p(0, 1), _h(1, 2), 2, True, None)
+    idx.set_swa(n, 5)
+    idx.lock_swa(n)
+    assert len(idx.evict(2)[0]) == 0 and idx.alive(n) and idx.has_swa(n)
+    idx.unlock_swa(n)
+    assert sorted(idx.evict(2)[0].tolist()) == [0, 1] and idx.drain_freed_swa_slots().tolist() == [5]
+
+
+def _fork(idx, snapshot):
+    """root -> A(1,2) -> {a(3,4) [snapshot 901], b(55,66)}"""
+    a = idx.insert(_p(0, 1, 2, 3), _h(1, 2, 3, 4), 4, True, None)
+    if snapshot:
+        idx.set_swa(a, 901)
+    h2 = _h(1, 2, 55, 66)
+    b = idx.insert(_p(8, 9), h2, 4, True, idx.match_prefix(h2))
+    return idx.node_parent(a), a, b
+
+
+@pytest.mark.parametrize("name,make", INDEXES)
+def test_full_eviction_takes_ancestors_left_as_leaves_without_a_snapshot(name, make):
+    """With window snapshots in use, a leaf without one serves no window-aware request: once both children are
+    gone the parent goes too, beyond the number of blocks asked for; a locked parent stays; an index that never
+    saw a snapshot keeps the plain rule (reference: tests/test_swa_node_mount.py:836-893)."""
+    idx = make()
+    A, a, b = _fork(idx, snapshot=True)
+    blocks, hashes = idx.evict(4)
+    assert sorted(blocks.tolist()) == [0, 1, 2, 3, 8, 9] and len(hashes) == 6
+    assert not idx.alive(A) and idx.total_swa_slots() == 0 and idx.drain_freed_swa_slots().tolist() == [901]
+    assert idx.match_prefix(_h(1, 2)).num_matched_blocks == 0
+
+    idx = make()
+    A, a, b = _fork(idx, snapshot=True)
+    idx.lock(A)                                            # the parent's blocks are still referenced
+    blocks, _ = idx.evict(4)
+    assert sorted(blocks.tolist()) == [2, 3, 8, 9] and idx.alive(A) and idx.node_size(A) == 2
+    idx.unlock(A)
+
+    idx = make()                                           # never armed: exactly what was asked for
+    A, a, b = _fork(idx, snapshot=False)
+    blocks, _ = idx.evict(4)
+    assert sorted(blocks.tolist()) == [2, 3, 8, 9] and idx.alive(A)
+    assert idx.match_prefix(_h(1, 2)).num_matched_blocks == 2
+
+
+@pytest.mark.parametrize("name,make", INDEXES)
+def test_snapshot_eviction_of_a_leaf_takes_its_bare_ancestors_along(name, make):
+    idx = make()
+    A = idx.insert(_p(0, 1), _h(1, 2), 2, True, None)
+    leaf = idx.insert(_p(2, 3), _h(1, 2, 3, 4), 4, True, idx.match_prefix(_h(1, 2, 3, 4)))
+    idx.set_swa(leaf, 7)
+    blocks, hashes, freed = idx.evict_swa(1)
+    assert freed == 1 and sorted(blocks.tolist()) == [0, 1, 2, 3] and sorted(hashes.tolist()) == [1, 2, 3, 4]
+    assert not idx.alive(A) and not idx.alive(leaf) and idx.drain_freed_swa_slots().tolist() == [7]
