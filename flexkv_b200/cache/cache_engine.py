@@ -11,6 +11,7 @@ enabled, on SSD; evicting from one tier never writes back to another.
 from __future__ import annotations
 
 import math
+import os
 import threading
 from dataclasses import dataclass, field
 from typing import Any, Callable, Dict, List, Optional, Tuple
@@ -303,6 +304,8 @@ class GlobalCacheEngine:
         if self.cpu_cache_engine is None:
             raise ValueError("the host tier is the staging area of every other tier and must be enabled")
         self.remote_backend = None          # key-addressed store; None = block-addressed index or no remote tier
+        # engines without a prefetch hook may let compute-path gets read the key-addressed store in the graph
+        self._store_in_graph = os.environ.get("FLEXKV_REMOTE_STORE_IN_GRAPH", "0") == "1"
         if cache_config.enable_remote and cache_config.use_mooncake_store_backend:
             from ..external.remote_store import get_backend
             self.set_remote_backend(get_backend(cache_config))
@@ -555,8 +558,12 @@ class GlobalCacheEngine:
         # fragment 3: blocks only the remote tier has, beyond everything local
         f3, f3_lo, remote_m = 0, 0, None
         use_gds_early = bool(self.cache_config.enable_gds) and not prefetch
+        # A key-addressed store sits behind a network: a get on the compute path stays on the local tiers and a
+        # miss is recomputed; only a prefetch pulls from the store, ahead of scheduling
+        # (reference: flexkv/cache/cache_engine.py:885-899 resolve_get_cache_strategy).
+        store_in_graph = self.remote_backend is None or prefetch or self._store_in_graph
         if (self.remote_backend is not None or self.remote_cache_engine is not None) and not cpu_only \
-                and not use_gds_early:
+                and not use_gds_early and store_in_graph:
             r_hit, remote_m = self._remote_hit(seq, bend)
             f3_lo = max(bstart, end)
             f3 = max(0, r_hit - f3_lo)

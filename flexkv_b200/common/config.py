@@ -406,6 +406,16 @@ def _env(name: str, default: Any, cast=None) -> Any:
     return (cast or type(default))(v)
 
 
+def assert_mooncake_prefetch_ready(cache_config, prefetch_enabled: bool) -> None:
+    """With a key-addressed remote store, compute-path gets stay on the local tiers; the store is read by
+    prefetches only. A connector whose prefetch hook is off would never read the store: refuse that
+    combination at start-up (reference: flexkv/common/config.py:17-29)."""
+    if getattr(cache_config, "use_mooncake_store_backend", False) and not prefetch_enabled \
+            and os.environ.get("FLEXKV_REMOTE_STORE_IN_GRAPH", "0") != "1":
+        raise RuntimeError("use_mooncake_store_backend needs the connector's prefetch: the store is read ahead of "
+                           "scheduling, never on the compute path (or set FLEXKV_REMOTE_STORE_IN_GRAPH=1)")
+
+
 def load_env_config() -> Namespace:
     return Namespace(
         instance_num=_env("FLEXKV_INSTANCE_NUM", 1),

@@ -73,6 +73,12 @@ class FlexKVConnector:
         self._pending_loads: Dict[str, _PendingLoad] = {}
         self._stores: Dict[str, int] = {}
         self._prefetch: Dict[str, int] = {}
+        # prefetching pays only where a tier below the host pool exists (flexkv/integration/sglang/connector.py:302-306);
+        # a key-addressed remote store is read by prefetches alone, so it must be on with one
+        cc = flexkv_config.cache_config
+        self.prefetch_enabled = bool(cc.enable_ssd or cc.enable_remote or cc.enable_kv_sharing)
+        from ...common.config import assert_mooncake_prefetch_ready
+        assert_mooncake_prefetch_ready(cc, self.prefetch_enabled)
         self._client = None
         if register:
             from ...server.client import KVTPClient
@@ -348,6 +354,8 @@ class FlexKVConnector:
 
     # ---- prefetch ---------------------------------------------------------------------------
     def prefetch_async(self, rid: str, token_ids: Sequence[int], namespace: Optional[List[str]] = None) -> None:
+        if not self.prefetch_enabled or not rid:
+            return
         if self.is_leader:
             self._prefetch[rid] = self.mgr.prefetch_async(np.asarray(token_ids, dtype=np.int64), namespace=namespace)
 

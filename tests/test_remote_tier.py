@@ -26,7 +26,7 @@ def start(cache_kw):
 
 
 @pytest.mark.parametrize("kind", ["files", "kvstore"])
-def test_remote_write_through_and_restore(tmp_path, kind):
+def test_remote_write_through_and_restore(tmp_path, kind, monkeypatch):
     kw = dict(enable_remote=True, num_remote_blocks=64)
     if kind == "files":
         kw.update(remote_cache_path=str(tmp_path), remote_file_num=3)
@@ -44,6 +44,14 @@ def test_remote_write_through_and_restore(tmp_path, kind):
         for t in kv:
             t.zero_()
         tid, mask = mgr.get_match(tok)
+        if kind == "kvstore":
+            # a store behind a network is never read on the compute path: the get misses (the engine recomputes
+            # or has prefetched); tests/test_mooncake_prefetch_compute_split.py in the reference pins the same
+            assert int(mask.sum()) == 0
+            mgr.cancel(tid)
+            monkeypatch.setenv("FLEXKV_REMOTE_STORE_IN_GRAPH", "1")     # engines without a prefetch hook
+            mgr.kv_task_engine.cache_engine._store_in_graph = True
+            tid, mask = mgr.get_match(tok)
         assert int(mask.sum()) == 8 * T
         kinds = sorted(o.transfer_type.value for o in mgr.kv_task_engine.tasks[tid].graph.ops())
         assert kinds == ["H2D", "REMOTE2H"]
@@ -56,13 +64,19 @@ def test_remote_write_through_and_restore(tmp_path, kind):
         tid, mask = mgr.get_match(tok)
         assert [o.transfer_type.value for o in mgr.kv_task_engine.tasks[tid].graph.ops()] == ["H2D"]
         mgr.cancel(tid)
-        # prefetch pulls remote blocks into the host pool ahead of time
+        # prefetch pulls remote blocks into the host pool ahead of time (from either kind of remote tier,
+        # whatever the compute-path rule says)
+        mgr.kv_task_engine.cache_engine._store_in_graph = False
         mgr._clear_cpu_cache()
         pid = mgr.prefetch_async(tok)
         r = mgr.wait(pid, completely=True)[pid]
         assert r.status.value == "success" and int(r.return_mask.sum()) == 8 * T
         tid, mask = mgr.get_match(tok, cpu_only=True)
         assert int(mask.sum()) == 8 * T
+        mgr.cancel(tid)
+        tid, mask = mgr.get_match(tok)               # and the compute-path get now hits the host tier
+        assert int(mask.sum()) == 8 * T
+        assert [o.transfer_type.value for o in mgr.kv_task_engine.tasks[tid].graph.ops()] == ["H2D"]
         mgr.cancel(tid)
     finally:
         mgr.shutdown()
@@ -72,6 +86,7 @@ def test_injected_remote_failure_fails_the_get_and_rolls_back(monkeypatch):
     monkeypatch.setenv("FLEXKV_MOONCAKE_FAULT_MODE", "tail")
     monkeypatch.setenv("FLEXKV_MOONCAKE_FAULT_OP", "get")
     monkeypatch.setenv("FLEXKV_MOONCAKE_FAULT_TAIL_N", "2")
+    monkeypatch.setenv("FLEXKV_REMOTE_STORE_IN_GRAPH", "1")     # the get itself reads the store in this test
     mgr, kv = start(dict(enable_remote=True, use_mooncake_store_backend=True, mooncake_store_config_path="loopback",
                          remote_config_custom={"store": LoopbackKVStore()}))
     try:
@@ -126,3 +141,15 @@ def test_prefetch_reports_the_longest_prefix_that_arrived(monkeypatch):
             assert torch.equal(kv[l][:, 20:24], saved[l][:, 0:4])
     finally:
         mgr.shutdown()
+
+
+def test_a_key_addressed_store_needs_a_connector_that_prefetches(monkeypatch):
+    from flexkv_b200.common.config import assert_mooncake_prefetch_ready
+    monkeypatch.delenv("FLEXKV_REMOTE_STORE_IN_GRAPH", raising=False)
+    store = CacheConfig(enable_remote=True, use_mooncake_store_backend=True)
+    assert_mooncake_prefetch_ready(store, prefetch_enabled=True)
+    assert_mooncake_prefetch_ready(CacheConfig(), prefetch_enabled=False)        # no store: nothing to gate
+    with pytest.raises(RuntimeError, match="prefetch"):
+        assert_mooncake_prefetch_ready(store, prefetch_enabled=False)
+    monkeypatch.setenv("FLEXKV_REMOTE_STORE_IN_GRAPH", "1")
+    assert_mooncake_prefetch_ready(store, prefetch_enabled=False)
