@@ -753,7 +753,12 @@ class GlobalCacheEngine:
             if need_ssd > 0 and nb - need_ssd < cpu_matched and cpu_m.num_ready_matched_blocks < cpu_matched:
                 need_ssd = 0
         if need_cpu == 0 and need_ssd == 0:
-            return None
+            # Everything is on the local tiers already. If the remote tier misses part of it (an earlier upload
+            # failed or was evicted there) and the host copy is complete and ready, the put becomes an upload
+            # from the host blocks alone, without touching the GPU
+            # (reference scenario: tests/test_mooncake_deferred_put.py:298-317).
+            if cpu_m.num_ready_matched_blocks < nb or not self._remote_lacks(seq, nb):
+                return None
         cpu_new = cpu.take(need_cpu, protected_node=cpu_m.last_node, strict=False) if need_cpu else _EMPTY
         if len(cpu_new) < need_cpu:
             cpu.recycle(cpu_new)
@@ -848,9 +853,19 @@ class GlobalCacheEngine:
                             else:
                                 tier.mount_swa(node, s_)
                         plan.op_callback_dict[tier_op.op_id] = _mount_tier
+        if graph.num_ops == 0:
+            return None                                  # the remote tier could not take the upload either
         plan.skipped_gpu_blocks = cpu_matched
         plan.num_gpu_blocks_to_transfer = need_cpu
         return plan
+
+    def _remote_lacks(self, seq: SequenceMeta, nb: int) -> bool:
+        """True when a remote tier exists and holds fewer than the first `nb` blocks of the sequence."""
+        if self.remote_backend is not None:
+            return self.remote_backend.prefix_hit(seq.block_hashes[:nb]) < nb
+        if self.remote_cache_engine is not None:
+            return self.remote_cache_engine.match(seq, update_cache_info=False).num_matched_blocks < nb
+        return False
 
     def _put_remote(self, seq, nb, cpu_m, cpu_matched, cpu_new, d2h, graph, plan, dp_client_id) -> None:
         """Write-through of the blocks the remote tier lacks (H2REMOTE after the GPU->host copy)."""

@@ -153,3 +153,56 @@ def test_a_key_addressed_store_needs_a_connector_that_prefetches(monkeypatch):
         assert_mooncake_prefetch_ready(store, prefetch_enabled=False)
     monkeypatch.setenv("FLEXKV_REMOTE_STORE_IN_GRAPH", "1")
     assert_mooncake_prefetch_ready(store, prefetch_enabled=False)
+
+
+@pytest.mark.parametrize("kind", ["files", "kvstore"])
+def test_a_put_that_is_local_already_retries_the_upload_the_remote_tier_misses(tmp_path, kind, monkeypatch):
+    """First put: the upload fails (host-side fault injection), the local tiers keep the blocks. Second put of the
+    same tokens: nothing to copy from the GPU, but the remote tier still misses the blocks, so the plan is one
+    H2REMOTE fed by the ready host blocks (reference: tests/test_mooncake_deferred_put.py
+    test_ready_cpu_hit_retries_a_missing_mooncake_upload_without_d2h)."""
+    kw = dict(enable_remote=True, num_remote_blocks=64)
+    if kind == "files":
+        kw.update(remote_cache_path=str(tmp_path), remote_file_num=2)
+    else:
+        kw.update(use_mooncake_store_backend=True, remote_config_custom={"store": LoopbackKVStore()})
+    monkeypatch.setenv("FLEXKV_MOONCAKE_FAULT_MODE", "all")
+    monkeypatch.setenv("FLEXKV_MOONCAKE_FAULT_OP", "put")
+    mgr, kv = start(kw)
+    try:
+        tok = np.arange(5 * T, dtype=np.int64) + 4242
+        src = np.array([3, 9, 1, 30, 12])
+        tid = mgr.put_async(tok, slots(src))
+        r = mgr.wait(tid, completely=True)[tid]              # the GPU->host part ended; the upload failed
+        gce = mgr.kv_task_engine.cache_engine
+        from flexkv_b200.common.block import SequenceMeta
+        seq = SequenceMeta(tok, T)
+        assert gce.cpu_cache_engine.match(seq).num_ready_matched_blocks == 5
+        assert gce._remote_lacks(seq, 5)
+        # the store works again
+        backend = gce.remote_backend or mgr.kv_task_engine.transfer_handles[0].engine._workers[
+            next(k for k in mgr.kv_task_engine.transfer_handles[0].engine._workers
+                 if getattr(k[1], "value", k[1]) == "H2REMOTE")].backend
+        backend.fault.mode = "none"
+        tid, mask = mgr.put_match(tok)
+        ops = [o.transfer_type.value for o in mgr.kv_task_engine.tasks[tid].graph.ops()]
+        assert ops == ["H2REMOTE"], ops
+        assert int(mask.sum()) == 0                          # no GPU block is read
+        mgr.launch(tid, slots(src)[:0])
+        assert mgr.wait(tid, completely=True)[tid].status.value == "success"
+        assert not gce._remote_lacks(seq, 5)
+        tid, mask = mgr.put_match(tok)                       # now there is nothing left to do
+        assert mgr.kv_task_engine.tasks[tid].graph.num_ops == 0
+        mgr.cancel(tid)
+        # and the uploaded bytes are the real ones
+        saved = [t.clone() for t in kv]
+        mgr._clear_cpu_cache()
+        pid = mgr.prefetch_async(tok)
+        assert int(mgr.wait(pid, completely=True)[pid].return_mask.sum()) == 5 * T
+        tid, mask = mgr.get_match(tok)
+        mgr.launch(tid, slots(np.arange(40, 45)))
+        assert mgr.wait(tid)[tid].status.value == "success"
+        for l in range(2):
+            assert torch.equal(kv[l][:, 40:45], saved[l][:, src])
+    finally:
+        mgr.shutdown()
