@@ -45,6 +45,10 @@ def sglang_gpu_layout(k_buffers: Sequence[torch.Tensor], page_size: int, use_mla
     return KVCacheLayout(KVCacheLayoutType.LAYERFIRST, L, tokens // page_size, page_size, t.shape[-2], t.shape[-1])
 
 
+def swa_transfer_enabled_from_env() -> bool:
+    return bool(int(os.environ.get("FLEXKV_ENABLE_SWA_TRANSFER", "1")))
+
+
 class FlexKVConnector:
     def __init__(self, flexkv_config: FlexKVConfig, page_size: int, tp_rank: int = 0, tp_size: int = 1,
                  pp_rank: int = 0, pp_size: int = 1, dp_rank: int = 0, cp_rank: int = 0, cp_size: int = 1,
@@ -153,7 +157,10 @@ class FlexKVConnector:
         swa = window_pool_config(pool, page_size, flexkv_config.cache_config.swa)
         if swa is not None:
             flexkv_config.cache_config.swa = swa
-            flexkv_config.cache_config.enable_swa_transfer = True
+            # the window data plane is on for such a pool unless the deployment switches it off: the geometry stays
+            # configured, snapshots are neither written nor restored and every get falls back to full KV only
+            # (FLEXKV_ENABLE_SWA_TRANSFER, flexkv/integration/config.py:20-21,620-627)
+            flexkv_config.cache_config.enable_swa_transfer = swa_transfer_enabled_from_env()
         return pool
 
     def register_kv_pool(self, kvcache: Any, pool: Optional[ResolvedPool] = None) -> ResolvedPool:

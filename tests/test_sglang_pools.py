@@ -170,3 +170,22 @@ def test_connector_round_trip_of_every_part_of_a_split_pool():
             assert not parts[i][dst[0]].any()
     finally:
         conn.shutdown()
+
+
+def test_window_data_plane_follows_the_deployment_switch(monkeypatch):
+    """A pool with window layers turns the window data plane on unless FLEXKV_ENABLE_SWA_TRANSFER=0; switched
+    off, the geometry stays configured and nothing else forces it back on (reference: tests/test_swa_config_gate.py)."""
+    def configured():
+        cfg = FlexKVConfig()
+        cfg.model_config = ModelConfig(num_layers=4, num_kv_heads=1, head_size=16, dtype=torch.uint8, use_mla=True)
+        cfg.cache_config = CacheConfig(tokens_per_block=T, num_cpu_blocks=16)
+        FlexKVConnector.configure_for_pool(cfg, SplitKV(), T)
+        return cfg.cache_config
+    monkeypatch.delenv("FLEXKV_ENABLE_SWA_TRANSFER", raising=False)
+    cc = configured()
+    assert cc.swa.enabled and cc.enable_swa_transfer is True
+    monkeypatch.setenv("FLEXKV_ENABLE_SWA_TRANSFER", "1")
+    assert configured().enable_swa_transfer is True
+    monkeypatch.setenv("FLEXKV_ENABLE_SWA_TRANSFER", "0")
+    cc = configured()
+    assert cc.swa.enabled and cc.enable_swa_transfer is False
