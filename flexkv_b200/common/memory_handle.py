@@ -49,7 +49,7 @@ _fd_server_path = ""
 
 
 def fd_server_path(pid: int) -> str:
-    return os.path.join(os.environ.get("FLEXKV_VMM_FD_DIR", tempfile.gettempdir()), f"flexkv_vmm_fd_{pid}.sock")
+    return os.path.join(os.environ.get("FLEXKV_VMM_FD_DIR") or os.environ.get("FLEXKV_VMM_FD_SOCK_DIR") or tempfile.gettempdir(), f"flexkv_vmm_fd_{pid}.sock")
 
 
 def _serve_fds(srv: socket.socket) -> None:

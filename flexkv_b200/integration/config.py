@@ -9,7 +9,7 @@ from typing import Any, Optional
 
 import torch
 
-from ..common.config import (NVFP4_NAMES, CacheConfig, ModelConfig, UserConfig, load_user_config_from_env,
+from ..common.config import (GLOBAL_CONFIG_FROM_ENV, NVFP4_NAMES, CacheConfig, ModelConfig, UserConfig, load_user_config_from_env,
                              nvfp4_head_bytes, parse_dtype, update_default_config_from_user_config)
 
 
@@ -61,7 +61,18 @@ class FlexKVConfig:
             m.head_size = head_size
 
     def _finish(self, tokens_per_block: int) -> None:
+        import os
         self.cache_config.tokens_per_block = tokens_per_block
+        # where the transfer managers of a group that spans nodes reach the master's
+        # (FLEXKV_MASTER_HOST / FLEXKV_MASTER_PORTS = command, result, query ports: flexkv/integration/config.py:250-253)
+        if os.getenv("FLEXKV_MASTER_HOST"):
+            self.model_config.master_host = os.environ["FLEXKV_MASTER_HOST"]
+        if os.getenv("FLEXKV_MASTER_PORTS"):
+            ports = tuple(p.strip() for p in os.environ["FLEXKV_MASTER_PORTS"].split(",") if p.strip())
+            if len(ports) != 3:
+                raise ValueError("FLEXKV_MASTER_PORTS needs three comma-separated ports")
+            self.model_config.master_ports = ports
+        self.model_config.instance_num = int(GLOBAL_CONFIG_FROM_ENV.instance_num)
         update_default_config_from_user_config(self.model_config, self.cache_config, self.user_config)
         self.model_config.freeze()
 

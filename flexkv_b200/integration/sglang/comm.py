@@ -85,6 +85,17 @@ class FlexKVComm:
             dist.barrier(group=self.group)
 
 
+def layerwise_wait_timeout_s() -> float:
+    """How long a layer hook waits for its restore before it gives up (FLEXKV_LAYERWISE_WAIT_TIMEOUT_S, 240 s;
+    a value that does not parse keeps the default: flexkv/integration/sglang/comm.py:775-781)."""
+    raw = os.environ.get("FLEXKV_LAYERWISE_WAIT_TIMEOUT_S", "240")
+    try:
+        v = float(raw)
+        return v if v > 0 else 240.0
+    except ValueError:
+        return 240.0
+
+
 class FlexKVLayerLoadingEvent:
     """One set of per-layer eventfds plus the number of restores that will signal it."""
 
@@ -227,9 +238,11 @@ class FlexKVLayerDoneCounter:
         """The forward pass that is about to run consumes the set this task signals."""
         self._consumer = self._task_to_counter.pop(task_id, self._consumer)
 
-    def wait_until(self, layer: int, timeout: float = 240.0) -> None:
+    def wait_until(self, layer: int, timeout: Optional[float] = None) -> None:
         if self._consumer < 0:
             return
+        if timeout is None:
+            timeout = layerwise_wait_timeout_s()
         self.events[self._consumer].wait(layer, timeout)
         if layer == self.num_layers - 1:
             self.events[self._consumer].mark_reusable()

@@ -20,6 +20,7 @@ prompt_token_ids, num_computed_tokens, lora_request, cache_salt ...).
 """
 from __future__ import annotations
 
+import os
 import time
 from dataclasses import dataclass, field
 from typing import Any, Dict, Iterable, List, Optional, Sequence, Set, Tuple
@@ -100,6 +101,9 @@ def _should_offload(request: Any) -> bool:
     return reason is None and not callable(getattr(request, "is_finished", None))
 
 
+SKIP_PUT_FLAG = "/tmp/flexkv_skip_put"
+
+
 class FlexKVSchedulerConnector:
     def __init__(self, flexkv_config: FlexKVConfig, kv_manager: Any = None, dp_client_id: int = 0) -> None:
         self.cfg = flexkv_config
@@ -111,7 +115,14 @@ class FlexKVSchedulerConnector:
                                    gpu_register_port=flexkv_config.gpu_register_port)
             kv_manager.start()
         self.mgr = kv_manager
-        self.stats = FlexKVStats()
+        # operator switches (flexkv/integration/vllm/vllm_v1_adapter.py:261-264,534,1199):
+        #   FLEXKV_NUM_LOG_INTERVAL_REQUESTS  hit-ratio log line every n gets (0 = never)
+        #   FLEXKV_MAYBE_SKIP_PUT=1           offloads are skipped while the file SKIP_PUT_FLAG exists: a running
+        #                                     deployment can be told to stop writing without a restart
+        #   FLEXKV_SYNC_GET=1                 every step waits for the restores it launched (debugging aid)
+        self.stats = FlexKVStats(log_interval=int(os.environ.get("FLEXKV_NUM_LOG_INTERVAL_REQUESTS", "200")))
+        self.maybe_skip_put = os.environ.get("FLEXKV_MAYBE_SKIP_PUT", "0") == "1"
+        self.sync_get = os.environ.get("FLEXKV_SYNC_GET", "0") == "1"
         self.req_to_get: Dict[str, FlexKVTask] = {}          # matched, waiting for allocation / launch
         self.req_to_put: Dict[str, FlexKVTask] = {}
         self.launched_get: Dict[int, FlexKVTask] = {}
@@ -211,6 +222,8 @@ class FlexKVSchedulerConnector:
         if pending is not None:
             self.to_cancel.append(pending.task_id)
         if not _should_offload(request):
+            return False, None
+        if self.maybe_skip_put and os.path.exists(SKIP_PUT_FLAG):
             return False, None
         tokens = _tokens_of(request)
         n = ((len(tokens) - 1) // self.T) * self.T
@@ -509,6 +522,15 @@ class FlexKVConnectorV1Impl:
         s.flush_cancels()
         s.launch_tasks()
         sending, recving = s.query_finished_task()
+        if s.sync_get:
+            # the step does not return before the restores it launched have landed; they are reported as
+            # finished through the same sets as in the asynchronous case
+            deadline = time.monotonic() + 120.0
+            while s.launched_get and time.monotonic() < deadline:
+                time.sleep(0.0005)
+                more_s, more_r = s.query_finished_task()
+                sending |= more_s
+                recving |= more_r
         # finished transfers reach the engine through update_connector_output (below); engines that read the
         # step record instead get them there as well
         self._finished_sending |= set(sending)

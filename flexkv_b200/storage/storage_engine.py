@@ -96,6 +96,16 @@ class SsdPool:
     blocks_per_file: int
 
 
+def host_register_chunk_bytes() -> int:
+    """Chunk size of the host pool's CUDA registration: FLEXKV_HOST_REGISTER_CHUNK_BYTES, or the reference's
+    FLEXKV_CUDAHOST_CHUNK_SIZE_GB (flexkv/transfer/host_buffer.py:58); 0 registers the pool in one call."""
+    v = os.environ.get("FLEXKV_HOST_REGISTER_CHUNK_BYTES")
+    if v is not None:
+        return max(0, int(v))
+    gb = float(os.environ.get("FLEXKV_CUDAHOST_CHUNK_SIZE_GB", "0") or 0)
+    return int(gb * (1 << 30)) if gb > 0 else 0
+
+
 class StorageEngine:
     def __init__(self, model_config: ModelConfig, cache_config: CacheConfig, cuda_register: Optional[bool] = None,
                  numa_node: int = -1) -> None:
@@ -180,6 +190,10 @@ class StorageEngine:
         block_bytes, layer_stride, kv_stride, chunk, lay = self._host_geometry()
         total = self._host_total_bytes(block_bytes, lay)
         backing = os.environ.get("FLEXKV_HUGEPAGE_FILE", "") if c.use_hugepage_cpu_buffer else ""
+        if c.use_hugepage_cpu_buffer and not backing and os.environ.get("FLEXKV_HUGETLBFS_DIR"):
+            # the reference's spelling: a hugetlbfs mount, the pool is a file of its own in it
+            # (flexkv/storage/allocator.py:262)
+            backing = os.path.join(os.environ["FLEXKV_HUGETLBFS_DIR"], f"flexkv_host_{os.getpid()}")
         self._owned_backing = ""
         if (c.enable_p2p_cpu or os.environ.get("FLEXKV_HOST_POOL_SHM", "0") == "1") and not backing:
             # other nodes of the box map this pool to pull blocks out of it (FLEXKV_HOST_POOL_SHM=1 asks for the
@@ -193,8 +207,7 @@ class StorageEngine:
                                                  hugepage_bytes=c.hugepage_size_bytes, numa_node=self._numa_node,
                                                  populate=True, touch_threads=min(16, os.cpu_count() or 4),
                                                  cuda_register=self._cuda_register,
-                                                 register_chunk_bytes=int(os.environ.get(
-                                                     "FLEXKV_HOST_REGISTER_CHUNK_BYTES", 0)),
+                                                 register_chunk_bytes=host_register_chunk_bytes(),
                                                  backing_file=backing)
         except RuntimeError as e:
             raise RuntimeError(f"host pool of {total / 2**30:.1f} GiB could not be allocated: {e}") from e

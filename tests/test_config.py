@@ -175,3 +175,35 @@ def test_layout_takes_the_reference_spelling():
     packed = KVCacheLayout(LT.LAYERFIRST, 4, 8, 16, 8, 72, kv_dim=1, num_kv_heads=8)   # packed 4-D cache: not MLA
     assert packed.kv_dim == 1 and not packed.is_mla and packed.num_kv_heads == 8
     assert packed.div_head(2).num_head == 4 and packed._replace(num_layer=1).kv_dim == 1
+
+
+def test_environment_spellings_of_the_reference_are_understood(monkeypatch):
+    """Deployment scripts written for the reference set these names; each reaches the same knob here."""
+    from types import SimpleNamespace as NS
+    from flexkv_b200.integration.config import FlexKVConfig
+    from flexkv_b200.integration.sglang.comm import layerwise_wait_timeout_s
+    from flexkv_b200.storage.storage_engine import host_register_chunk_bytes
+    from flexkv_b200.common import memory_handle
+    monkeypatch.delenv("FLEXKV_HOST_REGISTER_CHUNK_BYTES", raising=False)
+    assert host_register_chunk_bytes() == 0
+    monkeypatch.setenv("FLEXKV_CUDAHOST_CHUNK_SIZE_GB", "0.5")
+    assert host_register_chunk_bytes() == 1 << 29
+    monkeypatch.setenv("FLEXKV_HOST_REGISTER_CHUNK_BYTES", "4096")
+    assert host_register_chunk_bytes() == 4096
+    assert layerwise_wait_timeout_s() == 240.0
+    monkeypatch.setenv("FLEXKV_LAYERWISE_WAIT_TIMEOUT_S", "12.5")
+    assert layerwise_wait_timeout_s() == 12.5
+    monkeypatch.setenv("FLEXKV_LAYERWISE_WAIT_TIMEOUT_S", "soon")
+    assert layerwise_wait_timeout_s() == 240.0
+    monkeypatch.delenv("FLEXKV_VMM_FD_DIR", raising=False)
+    monkeypatch.setenv("FLEXKV_VMM_FD_SOCK_DIR", "/run/x")
+    assert memory_handle.fd_server_path(77).startswith("/run/x/")
+    monkeypatch.setenv("FLEXKV_MASTER_HOST", "10.0.0.7")
+    monkeypatch.setenv("FLEXKV_MASTER_PORTS", "7001, 7002,7003")
+    cfg = FlexKVConfig()
+    model = NS(num_hidden_layers=2, num_key_value_heads=2, head_dim=16, dtype="bfloat16")
+    cfg.post_init_from_sglang_config(NS(kv_cache_dtype="auto"), model, page_size=16)
+    assert cfg.model_config.master_host == "10.0.0.7" and cfg.model_config.master_ports == ("7001", "7002", "7003")
+    monkeypatch.setenv("FLEXKV_MASTER_PORTS", "7001")
+    with pytest.raises(ValueError, match="three"):
+        FlexKVConfig().post_init_from_sglang_config(NS(kv_cache_dtype="auto"), model, page_size=16)

@@ -266,3 +266,42 @@ def test_impl_reports_finished_transfers_through_the_engines_connector_output():
         impl.update_connector_output(None)                          # tolerated
     finally:
         conn.shutdown()
+
+
+def test_operator_switches_skip_put_flag_and_synchronous_gets(monkeypatch, tmp_path):
+    """FLEXKV_MAYBE_SKIP_PUT: offloads stop while a flag file exists, without a restart. FLEXKV_SYNC_GET: the
+    step that launches a restore returns only after it has landed and reports it in the same step
+    (reference: flexkv/integration/vllm/vllm_v1_adapter.py:264,534,1199)."""
+    from flexkv_b200.integration.vllm import vllm_v1_adapter as A
+    from flexkv_b200.integration.vllm.vllm_v1_adapter import FlexKVConnectorV1Impl
+    flag = tmp_path / "skip_put"
+    monkeypatch.setattr(A, "SKIP_PUT_FLAG", str(flag))
+    monkeypatch.setenv("FLEXKV_MAYBE_SKIP_PUT", "1")
+    monkeypatch.setenv("FLEXKV_SYNC_GET", "1")
+    monkeypatch.setenv("FLEXKV_NUM_LOG_INTERVAL_REQUESTS", "7")
+    conn, kv, mgr = make()
+    assert conn.maybe_skip_put and conn.sync_get and conn.stats.log_interval == 7
+    impl = FlexKVConnectorV1Impl.__new__(FlexKVConnectorV1Impl)
+    impl.is_scheduler, impl.scheduler, impl.worker = True, conn, None
+    impl._finished_sending, impl._finished_recving, impl._previous_scheduled = set(), set(), set()
+    try:
+        tok = np.arange(900, 900 + 4 * T + 1)
+        flag.write_text("")
+        assert conn.request_finished(req("a", tok), [1, 2, 3, 4, 5]) == (False, None)     # writing is paused
+        assert conn.stats.num_put_requests == 0
+        flag.unlink()
+        keep, _ = conn.request_finished(req("a", tok), [1, 2, 3, 4, 5])
+        assert keep
+        conn.launch_tasks()
+        assert drain(conn, want_send={"a"})[0] == {"a"}
+        # synchronous get: finished within the step that launched it
+        r2 = req("b", tok)
+        n, _ = conn.get_num_new_matched_tokens(r2, 0)
+        assert n == 4 * T
+        conn.update_state_after_alloc(r2, NS(get_block_ids=lambda: ([20, 21, 22, 23, 24],)), n)
+        meta = impl.build_connector_meta(NS(preempted_req_ids=set()))
+        assert "b" in meta.finished_recving and not conn.launched_get
+        for l in range(2):
+            assert torch.equal(kv[l][:, [20, 21, 22, 23]], kv[l][:, [1, 2, 3, 4]])
+    finally:
+        conn.shutdown()
