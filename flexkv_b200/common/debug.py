@@ -50,8 +50,14 @@ def log_op(operation: str, act: str, status: str, level: int = logging.DEBUG, **
 class EvictionLogAggregator:
     """Batches eviction events so a storm of small evictions prints one line per interval."""
 
-    def __init__(self, interval_s: float = 5.0) -> None:
-        self.interval_s = interval_s
+    def __init__(self, interval_s: Optional[float] = None) -> None:
+        if interval_s is None:          # FLEXKV_EVICTION_LOG_INTERVAL_S (flexkv/common/debug.py:150-160)
+            try:
+                interval_s = float(os.environ.get("FLEXKV_EVICTION_LOG_INTERVAL_S", "10"))
+            except ValueError:
+                interval_s = 10.0
+            interval_s = max(0.1, interval_s)
+        self.interval_s = float(interval_s)
         self._lock = threading.Lock()
         self._counts: Dict[str, int] = {}
         self._events: Dict[str, int] = {}
