@@ -375,35 +375,64 @@ class FlexKVWorkerConnector:
         self._caches: Optional[List[torch.Tensor]] = None
         self._layout: Optional[KVCacheLayout] = None
 
-    def register_to_server(self, kv_caches: Dict[str, torch.Tensor]) -> None:
-        """Registers the worker's KV tensors. Layers whose name contains ``.k_cache`` are indexer key caches
-        (``[blocks, tokens, dim]`` beside every attention layer): they become a second layer group, and the
-        group list travels with the registration because only the worker sees these tensors
-        (flexkv/integration/vllm/vllm_v1_adapter.py:826-960)."""
-        m, c = self.cfg.model_config, self.cfg.cache_config
+    def _split(self, kv_caches) -> List[Tuple[str, List[torch.Tensor], List[int]]]:
+        """The worker's tensors as ordered groups ``(kind, tensors, layer ids)``. Layers that share one tensor
+        (the same storage under several layer names) count once. Attention caches are grouped by shape and
+        dtype in order of first appearance: a model whose sliding-window layers and full-attention layers have
+        different head counts or head sizes yields one group per shape. Tensors whose layer name contains
+        ``.k_cache`` are indexer key caches and form the last group."""
         named = kv_caches if isinstance(kv_caches, dict) else {str(i): t for i, t in enumerate(kv_caches)}
-        main = [t for n, t in named.items() if ".k_cache" not in n]
-        indexer = [t for n, t in named.items() if ".k_cache" in n]
-        layout = infer_vllm_gpu_layout(main, c.tokens_per_block, m.num_kv_heads // max(1, m.tp_size), m.head_size,
-                                       m.use_mla)
-        self._caches, self._layout = main, layout
-        if not indexer:
-            self.client.register_to_server(main, layout)
+        seen, main, indexer = set(), [], []
+        for name, t in named.items():
+            key = (t.data_ptr(), tuple(t.shape)) if t.numel() else id(t)
+            if key in seen:
+                continue
+            seen.add(key)
+            (indexer if ".k_cache" in name else main).append(t)
+        groups: Dict[Any, Tuple[List[torch.Tensor], List[int]]] = {}
+        for i, t in enumerate(main):
+            ts, ids = groups.setdefault((tuple(t.shape), t.dtype), ([], []))
+            ts.append(t)
+            ids.append(i)
+        out = [("kv", ts, ids) for ts, ids in groups.values()]
+        if indexer:
+            out.append(("indexer", indexer, list(range(len(indexer)))))
+        return out
+
+    def register_to_server(self, kv_caches: Dict[str, torch.Tensor]) -> None:
+        """Registers the worker's KV tensors. One shape: a plain registration. Several shapes (layers with
+        different head geometry, indexer key caches ``[blocks, tokens, dim]`` beside the attention layers): one
+        layer group per shape, and the group list travels with the registration because only the worker sees
+        these tensors (flexkv/integration/vllm/vllm_v1_adapter.py:826-960)."""
+        m, c = self.cfg.model_config, self.cfg.cache_config
+        parts = self._split(kv_caches)
+        regs: List[Tuple[List[torch.Tensor], KVCacheLayout]] = []
+        for kind, ts, _ in parts:
+            if kind == "indexer":
+                t0 = ts[0]
+                if t0.dim() != 3:
+                    raise ValueError(f"indexer caches are [blocks, tokens, dim], got {tuple(t0.shape)}")
+                regs.append((ts, KVCacheLayout(KVCacheLayoutType.LAYERFIRST, len(ts), t0.shape[0], t0.shape[1], 1,
+                                               t0.shape[2], is_mla=True)))
+            else:
+                regs.append((ts, infer_vllm_gpu_layout(ts, c.tokens_per_block, m.num_kv_heads // max(1, m.tp_size),
+                                                       m.head_size, m.use_mla)))
+        self._caches, self._layout = regs[0]
+        self._regs = regs
+        if len(regs) == 1:
+            self.client.register_to_server(*regs[0])
             return
         from ...common.config import LayerGroupSpec
-        t0 = indexer[0]
-        if t0.dim() != 3:
-            raise ValueError(f"indexer caches are [blocks, tokens, dim], got {tuple(t0.shape)}")
-        idx_layout = KVCacheLayout(KVCacheLayoutType.LAYERFIRST, len(indexer), t0.shape[0], t0.shape[1], 1, t0.shape[2],
-                                   is_mla=True)
-        groups = [LayerGroupSpec(num_layers=len(main), num_kv_heads=layout.num_head, head_size=layout.head_size,
-                                 kv_dim=layout.kv_dim, dtype=main[0].dtype, layer_ids=list(range(len(main))), name="kv"),
-                  LayerGroupSpec(num_layers=len(indexer), num_kv_heads=1, head_size=int(t0.shape[2]), kv_dim=1,
-                                 dtype=t0.dtype, compress_ratio=max(1, layout.tokens_per_block // int(t0.shape[1])),
-                                 layer_ids=list(range(len(indexer))), name="indexer")]
-        self._indexer, self._idx_layout, self._groups = indexer, idx_layout, groups
-        self.client.register_to_server(main, layout, group_id=0, layer_groups=groups)
-        self.client.register_to_server(indexer, idx_layout, group_id=1, layer_groups=groups)
+        T = regs[0][1].tokens_per_block
+        groups = []
+        for gi, ((kind, ts, ids), (_, lay)) in enumerate(zip(parts, regs)):
+            groups.append(LayerGroupSpec(
+                num_layers=len(ts), num_kv_heads=lay.num_head, head_size=lay.head_size, kv_dim=lay.kv_dim,
+                dtype=ts[0].dtype, layer_ids=list(ids), name=kind if kind == "indexer" else f"kv{gi}" if gi else "kv",
+                compress_ratio=max(1, T // int(lay.tokens_per_block)) if kind == "indexer" else 1))
+        self._groups = groups
+        for gi, (ts, lay) in enumerate(regs):
+            self.client.register_to_server(ts, lay, group_id=gi, layer_groups=groups)
 
     def before_device_sleep(self) -> int:
         """vLLM sleep mode frees the cache; the data plane must stop touching (and mapping) it first.
@@ -412,17 +441,20 @@ class FlexKVWorkerConnector:
 
     def after_device_wake(self, kv_caches: Optional[Dict[str, torch.Tensor]] = None) -> None:
         """Pass the re-created tensors when the engine allocated a new cache on wake."""
-        indexer = getattr(self, "_indexer", None)
+        regs = getattr(self, "_regs", None)
+        if not regs:
+            return
         if kv_caches is not None:
-            named = kv_caches if isinstance(kv_caches, dict) else {str(i): t for i, t in enumerate(kv_caches)}
-            self._caches = [t for n, t in named.items() if ".k_cache" not in n]
-            if indexer is not None:
-                indexer = self._indexer = [t for n, t in named.items() if ".k_cache" in n]
-        if self._caches is not None and indexer:
-            self.client.resume_gpu_mappings(self._caches, self._layout, group_id=0,
-                                            more_groups=[(indexer, self._idx_layout, 1)])
-        elif self._caches is not None:
-            self.client.resume_gpu_mappings(self._caches, self._layout)
+            parts = self._split(kv_caches)
+            if [len(ts) for _, ts, _ in parts] != [len(ts) for ts, _ in regs]:
+                raise ValueError("the cache that came back after wake has a different set of tensors")
+            regs = self._regs = [(ts, lay) for (_, ts, _), (_, lay) in zip(parts, regs)]
+            self._caches = regs[0][0]
+        if len(regs) == 1:
+            self.client.resume_gpu_mappings(regs[0][0], regs[0][1])
+        else:
+            self.client.resume_gpu_mappings(regs[0][0], regs[0][1], group_id=0,
+                                            more_groups=[(ts, lay, gi) for gi, (ts, lay) in enumerate(regs) if gi])
 
 
 _VLLM_TYPES: Optional[dict] = None

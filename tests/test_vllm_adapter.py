@@ -305,3 +305,61 @@ def test_operator_switches_skip_put_flag_and_synchronous_gets(monkeypatch, tmp_p
             assert torch.equal(kv[l][:, [20, 21, 22, 23]], kv[l][:, [1, 2, 3, 4]])
     finally:
         conn.shutdown()
+
+
+def test_layers_of_different_head_geometry_become_one_group_per_shape():
+    """A hybrid model whose sliding-window layers and full-attention layers have different head counts and head
+    sizes (the reference's Gemma-4 case, docs/gemma4_support.md: 16 x 256 beside 4 x 512, triton layout
+    ``[blocks, 2, tokens, heads, dim]``, some layers sharing one tensor): the worker probes the shapes, registers
+    one layer group per shape, the manager adopts the groups, and a put / get moves every layer."""
+    from flexkv_b200.integration.vllm.vllm_v1_adapter import FlexKVWorkerConnector
+    from flexkv_b200.server.utils import unique_ipc_endpoint
+    shape = KVShape("g", 5, 4, 8, tokens_per_block=T)                 # what the engine config alone would say
+    cfg = FlexKVConfig()
+    cfg.model_config = make_model_config(shape)
+    cfg.cache_config = CacheConfig(tokens_per_block=T, num_cpu_blocks=32)
+    cfg.gpu_register_port = unique_ipc_endpoint("vgem")
+    mgr = KVManager(cfg.model_config, cfg.cache_config, require_gpu=True, gpu_register_port=cfg.gpu_register_port)
+    mgr.start()
+    g = torch.Generator().manual_seed(12)
+    NB = 48
+    swa = [torch.randn(NB, 2, T, 4, 8, generator=g).to(torch.bfloat16) for _ in range(3)]      # sliding-window layers
+    full = [torch.randn(NB, 2, T, 1, 16, generator=g).to(torch.bfloat16) for _ in range(2)]    # full-attention layers
+    caches = {"model.layers.0.attn": swa[0], "model.layers.1.attn": swa[1], "model.layers.2.attn": full[0],
+              "model.layers.3.attn": swa[2], "model.layers.4.attn": full[1],
+              "model.layers.5.attn": full[1]}                          # shares layer 4's tensor
+    worker = FlexKVWorkerConnector(cfg, dp_client_id=0, tp_rank=0, device_id=0)
+    worker.client.register_to_server = (lambda f: lambda *a, **k: f(*a, mode="same_process", **k))(
+        worker.client.register_to_server)
+    try:
+        worker.register_to_server(caches)
+        mgr.wait_ready(30)
+        groups = mgr.transfer_manager.model_config.layer_groups
+        assert [(x.num_layers, x.num_kv_heads, x.head_size, x.kv_dim) for x in groups] == [(3, 4, 8, 2), (2, 1, 16, 2)]
+        assert [list(x.layer_ids) for x in groups] == [[0, 1, 3], [2, 4]]
+        host = mgr.transfer_manager.storage.host
+        assert host.block_bytes == (3 * 2 * T * 4 * 8 + 2 * 2 * T * 1 * 16) * 2
+        tok = np.arange(4 * T, dtype=np.int64) + 77
+        sl = lambda b: np.repeat(np.asarray(b), T) * T + np.tile(np.arange(T), len(b))   # noqa: E731
+        src, dst = [3, 9, 1, 30], [40, 41, 42, 43]
+        tid = mgr.put_async(tok, sl(src))
+        assert mgr.wait(tid, completely=True)[tid].status.value == "success"
+        want = [t[src].clone() for t in swa + full]
+        for t in swa + full:
+            t[dst] = 0
+        tid = mgr.get_async(tok, sl(dst))
+        assert mgr.wait(tid)[tid].status.value == "success"
+        for t, w in zip(swa + full, want):
+            assert torch.equal(t[dst], w)
+        # wake with new tensors of the same shapes
+        assert worker.before_device_sleep() == 0
+        swa2, full2 = [torch.zeros_like(t) for t in swa], [torch.zeros_like(t) for t in full]
+        worker.after_device_wake({"model.layers.0.attn": swa2[0], "model.layers.1.attn": swa2[1],
+                                  "model.layers.2.attn": full2[0], "model.layers.3.attn": swa2[2],
+                                  "model.layers.4.attn": full2[1], "model.layers.5.attn": full2[1]})
+        tid = mgr.get_async(tok, sl(dst))
+        assert mgr.wait(tid)[tid].status.value == "success"
+        for t, w in zip(swa2 + full2, want):
+            assert torch.equal(t[dst], w)
+    finally:
+        mgr.shutdown()
