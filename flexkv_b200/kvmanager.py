@@ -8,6 +8,7 @@ this process. With ``dp_size > 1``, several engine instances or
 """
 from __future__ import annotations
 
+import os
 import time
 from typing import Dict, List, Optional, Sequence, Tuple, Union
 
@@ -78,7 +79,14 @@ class KVManager:
             if env.crash_diagnostics:
                 from .common.debug import install_crash_diagnostics
                 install_crash_diagnostics()
-            if (transfer_manager_mode or env.transfer_manager_mode) == "process":
+            tm_mode = transfer_manager_mode or env.transfer_manager_mode
+            if transfer_manager_mode is None and getattr(model_config, "use_trtllm_subprocess", False) \
+                    and "FLEXKV_TRANSFER_MANAGER_MODE" not in os.environ:
+                # TensorRT-LLM owns MPI in the serving processes: the data plane goes to a child process started
+                # from a fresh interpreter (the reference runs it as a remote-mode subprocess on
+                # FLEXKV_TRT_SUBPROCESS_HOST/PORTS for the same reason: flexkv/kvtask.py:172-199)
+                tm_mode = "process"
+            if tm_mode == "process":
                 # the data plane in a child process (pipe EOF in both directions, SIGTERM-safe unpinning)
                 from .transfer_process import TransferManagerProcessHandle
                 self.transfer_manager = TransferManagerProcessHandle(model_config, cache_config, gpu_register_port,
@@ -199,13 +207,17 @@ class KVManager:
         if self._shut:
             return
         self._shut = True
+        # a constructor that raised half way leaves some of these unset
         if self.server_client_mode:
-            self.dp_client.shutdown()
+            if self.dp_client is not None:
+                self.dp_client.shutdown()
             if self.server_handle is not None:
                 self.server_handle.shutdown()
                 self.server_handle = None
-        else:
+        elif self.kv_task_engine is not None:
             self.kv_task_engine.shutdown()
+        elif self.transfer_manager is not None:
+            self.transfer_manager.shutdown()
 
     # ---- requests -------------------------------------------------------------
     def get_async(self, token_ids, slot_mapping, token_mask=None, namespace: Optional[List[str]] = None) -> int:

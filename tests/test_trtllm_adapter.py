@@ -139,3 +139,39 @@ def test_worker_connector_reports_the_bound_metadata(tmp_path):
             w.register_kv_caches(torch.zeros(4, L, 2, 7))
     finally:
         w.shutdown()
+
+
+def test_a_manager_configured_from_tensorrt_llm_keeps_the_data_plane_out_of_the_serving_process(monkeypatch):
+    """TensorRT-LLM owns MPI in its processes, so a configuration read from it asks for the data plane in a child
+    process; an explicit FLEXKV_TRANSFER_MANAGER_MODE or constructor argument still decides
+    (reference: flexkv/integration/config.py:752, flexkv/kvtask.py:172-199)."""
+    from types import SimpleNamespace as NS
+    from flexkv_b200 import KVManager
+    from flexkv_b200.integration.config import FlexKVConfig
+    import flexkv_b200.transfer_process as tp
+    made = []
+
+    class FakeHandle:
+        def __init__(self, *a, **k):
+            made.append("process")
+
+        def shutdown(self):
+            pass
+
+        def set_metrics_collector(self, c):
+            pass
+
+    monkeypatch.setattr(tp, "TransferManagerProcessHandle", FakeHandle)
+    monkeypatch.delenv("FLEXKV_TRANSFER_MANAGER_MODE", raising=False)
+    cfg = FlexKVConfig()
+    llm = NS(model_config=NS(num_hidden_layers=2, num_key_value_heads=2, num_attention_heads=2, head_dim=16,
+                             hidden_size=32, torch_dtype="bfloat16"),
+             kv_cache_config=NS(dtype="auto", tokens_per_block=T))
+    cfg.post_init_from_trt_config(llm, NS(tp_size=1, pp_size=1))
+    assert cfg.model_config.use_trtllm_subprocess
+    m = KVManager(cfg.model_config, cfg.cache_config, require_gpu=False)
+    assert made == ["process"]
+    m._shut = True
+    m2 = KVManager(cfg.model_config, cfg.cache_config, require_gpu=False, transfer_manager_mode="thread")
+    assert made == ["process"]                       # the explicit choice wins
+    m2.shutdown()
