@@ -56,6 +56,7 @@ PYBIND11_MODULE(_C, m) {
              for (const auto& c : v) out.append(py::make_tuple(c.graph_id, c.op_id, c.success, c.ms, c.bytes));
              return out;
            }, py::arg("timeout_s"))
+      .def("completion_fd", &GraphScheduler::completion_fd)
       .def("has_graph", &GraphScheduler::has_graph)
       .def("graphs_in_flight", &GraphScheduler::graphs_in_flight)
       .def("stats", [](GraphScheduler& g) {

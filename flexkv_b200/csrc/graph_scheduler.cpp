@@ -1,5 +1,8 @@
 #include "graph_scheduler.h"
 
+#include <sys/eventfd.h>
+#include <unistd.h>
+
 #include <algorithm>
 #include <chrono>
 #include <stdexcept>
@@ -66,6 +69,7 @@ void GraphScheduler::complete_locked(int64_t gid, Graph& g, int32_t i, bool succ
     g.failed = true;
   }
   done_.push_back(SchedCompletion{gid, op.id, success, op.ms, op.bytes});
+  signal_locked();
   if (!success || g.failed) return;      // a failed graph hands out nothing more
   for (int32_t s : op.succ) {
     Op& so = g.ops[(size_t)s];
@@ -82,6 +86,7 @@ bool GraphScheduler::maybe_finish_locked(int64_t gid, Graph& g) {
   if (!finished) return false;
   if (g.failed) stats_.failed_graphs++;
   done_.push_back(SchedCompletion{gid, -1, !g.failed, 0.0, 0});
+  signal_locked();
   graphs_.erase(gid);
   cv_.notify_all();
   return true;
@@ -168,7 +173,31 @@ std::vector<SchedCompletion> GraphScheduler::wait(double timeout_s) {
   }
   out.assign(done_.begin(), done_.end());
   done_.clear();
+  if (event_fd_ >= 0) {       // nothing is waiting any more: the descriptor stops being readable
+    uint64_t v;
+    while (::read(event_fd_, &v, sizeof(v)) == (ssize_t)sizeof(v)) {
+    }
+  }
   return out;
+}
+
+void GraphScheduler::signal_locked() {
+  if (event_fd_ < 0) return;
+  const uint64_t one = 1;
+  (void)!::write(event_fd_, &one, sizeof(one));
+}
+
+int GraphScheduler::completion_fd() {
+  std::lock_guard<std::mutex> lk(mu_);
+  if (event_fd_ < 0) {
+    event_fd_ = ::eventfd(0, EFD_NONBLOCK | EFD_CLOEXEC);
+    if (event_fd_ >= 0 && !done_.empty()) signal_locked();
+  }
+  return event_fd_;
+}
+
+GraphScheduler::~GraphScheduler() {
+  if (event_fd_ >= 0) ::close(event_fd_);
 }
 
 bool GraphScheduler::has_graph(int64_t graph_id) {

@@ -68,6 +68,12 @@ class GraphScheduler {
   // Completion records so far; blocks up to timeout_s for the first one (timeout_s < 0: no limit, 0: poll).
   std::vector<SchedCompletion> wait(double timeout_s);
 
+  // A descriptor that is readable exactly while completion records are waiting (an eventfd, created on the first
+  // call, owned by the scheduler): an event loop that also serves sockets polls it instead of calling wait()
+  // on a timer. -1 when the descriptor cannot be created.
+  int completion_fd();
+  ~GraphScheduler();
+
   bool has_graph(int64_t graph_id);
   int64_t graphs_in_flight();
   struct Stats { int64_t ops = 0, failed_ops = 0, graphs = 0, failed_graphs = 0; };
@@ -102,6 +108,8 @@ class GraphScheduler {
   std::condition_variable cv_;
   std::unordered_map<int64_t, Graph> graphs_;
   std::deque<SchedCompletion> done_;
+  int event_fd_ = -1;
+  void signal_locked();     // after a push to done_
   Stats stats_;
 };
 

@@ -358,6 +358,22 @@ class KVTaskEngine:
             for c in h.wait(timeout=per_handle):
                 self._on_completed(c)
 
+    def pump(self, timeout: float) -> None:
+        """Blocks up to ``timeout`` seconds for the next completion of the data plane and applies what arrived.
+        A server calls this between requests while clients wait for tasks."""
+        self._update_tasks(timeout=timeout)
+
+    def completion_fds(self) -> Optional[List[int]]:
+        """One pollable descriptor per transfer handle, or None when some handle has none (a data plane in
+        another process, the Python scheduler): the caller then has to poll on a timer."""
+        fds = []
+        for h in self.transfer_handles:
+            fd = h.completion_fd() if hasattr(h, "completion_fd") else -1
+            if fd < 0:
+                return None
+            fds.append(fd)
+        return fds
+
     def _member_tasks(self, task: KVTask) -> List[KVTask]:
         if not task.children:
             return [task]

@@ -19,6 +19,9 @@ from . import request as R
 from .utils import get_zmq_socket
 
 
+PARKED_PUMP_S = 0.0002     # longest a new request waits behind the completion queue while waits are parked
+
+
 class KVServer:
     def __init__(self, model_config: ModelConfig, cache_config: CacheConfig, recv_endpoint: str,
                  gpu_register_port: Optional[str] = None, require_gpu: Optional[bool] = None) -> None:
@@ -80,12 +83,41 @@ class KVServer:
         poller = zmq.Poller()
         poller.register(self._recv, zmq.POLLIN)
         self._parked = []
+        self._completion_fds: list = []
+        self._probe_fds = 50
         while self._running:
             # a blocking wait of one client must not hold up the others: it is parked and answered from here
             # once its tasks are done (or its time is up); requests keep being served meanwhile
-            if not dict(poller.poll(1 if self._parked else 100)):
-                self._answer_parked_waits()
-                continue
+            # The loop sleeps until a request OR a completion arrives: the data plane's completion queue has a
+            # descriptor the poller can watch. Where it has none (data plane in another process, Python
+            # scheduler) and somebody waits for tasks, look for a request without blocking and else block on the
+            # completion queue for PARKED_PUMP_S at a time.
+            if not self._completion_fds and self._probe_fds > 0:
+                fds = self.engine.completion_fds()
+                if fds:
+                    for fd in fds:
+                        poller.register(fd, zmq.POLLIN)
+                    self._completion_fds = fds
+                elif fds is None or self.engine.is_ready():
+                    self._probe_fds -= 1               # handles without a descriptor: stop asking after a while
+            if self._parked:
+                if self._completion_fds:
+                    next_deadline = min(d for _, d in self._parked)
+                    ms = max(0, min(100, int((next_deadline - time.monotonic()) * 1000) + 1))
+                    ready = dict(poller.poll(ms))
+                    if self._recv not in ready:
+                        self._answer_parked_waits()      # applies the completions, which also empties the descriptor
+                        continue
+                elif not dict(poller.poll(0)):
+                    self.engine.pump(PARKED_PUMP_S)
+                    self._answer_parked_waits()
+                    continue
+            else:
+                ready = dict(poller.poll(100))
+                if self._recv not in ready:
+                    if ready:
+                        self.engine.pump(0.0)    # completions nobody waits for yet: apply them, which empties the descriptor
+                    continue
             try:
                 req = pickle.loads(self._recv.recv())
             except Exception:  # noqa: BLE001

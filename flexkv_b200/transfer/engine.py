@@ -124,6 +124,10 @@ class TransferEngine:
 
     get_completed_graphs_and_ops = wait
 
+    def completion_fd(self) -> int:
+        """Descriptor that is readable while ``wait(0)`` would return records (the native scheduler's eventfd)."""
+        return int(self._sched.completion_fd())
+
     # ---- dispatch ---------------------------------------------------------------
     def _dispatch_op(self, graph: TransferOpGraph, op: TransferOp) -> None:
         """Hands one released op to its worker(s). Called with the lock held."""

@@ -280,6 +280,12 @@ class TransferManager:
                 return []
         return self.engine.wait(timeout)
 
+    def completion_fd(self) -> int:
+        """-1 until the engine runs, or when its scheduler has no descriptor to poll."""
+        if not self._ready.is_set() or not hasattr(self.engine, "completion_fd"):
+            return -1
+        return self.engine.completion_fd()
+
     def shutdown(self) -> None:
         self._stop = True
         with self._reg_cv:

@@ -258,3 +258,53 @@ def test_blocking_wait_of_one_client_does_not_hold_up_the_others():
         assert m0.wait(tid, timeout=30, completely=True)[tid].status.value == "success"
     finally:
         m1.shutdown(); m0.shutdown()
+
+
+def test_server_sleeps_on_requests_and_completions_not_on_a_timer():
+    """While a client waits, the server's loop sleeps until a request or a completion arrives (the data plane's
+    completion queue is a pollable descriptor); completions nobody waits for do not make it spin."""
+    from flexkv_b200 import _native
+    s = _native.C.GraphScheduler()
+    fd = s.completion_fd()
+    assert fd >= 0 and s.completion_fd() == fd
+    import select
+    assert select.select([fd], [], [], 0)[0] == []
+    s.submit(1, [1], [0], [])
+    s.op_done(1, 1, True, 0.1, 8)
+    assert select.select([fd], [], [], 1.0)[0] == [fd]          # readable while records are waiting
+    assert len(s.wait(0.0)) == 2
+    assert select.select([fd], [], [], 0)[0] == []              # and quiet again once they were taken
+
+    shape = KVShape("s", 2, 2, 16, tokens_per_block=4)
+    T = 4
+    model = make_model_config(shape, dp_size=2)
+    cache = CacheConfig(tokens_per_block=T, num_cpu_blocks=32)
+    ep, reg = unique_ipc_endpoint("srvfd"), unique_ipc_endpoint("regfd")
+    m0 = KVManager(model, cache, dp_client_id=0, server_recv_port=ep, gpu_register_port=reg, require_gpu=True)
+    m1 = KVManager(model, cache, dp_client_id=1, server_recv_port=ep, gpu_register_port=reg)
+    for d in range(2):
+        kv, layout = alloc_paged_cache(shape, 32, "cpu", "vllm", fill="normal", seed=7 + d)
+        KVTPClient(reg, dp_client_id=d, device_id=0, tp_rank=0).register_to_server(kv, layout, mode="same_process")
+    m0.start(); m1.start()
+    try:
+        m0.wait_ready(30); m1.wait_ready(30)
+        srv = m0.server_handle.server
+        lat = []
+        for i in range(30):
+            tok = np.arange(6 * T, dtype=np.int64) + 1000 * i
+            tid = m0.put_async(tok, slots([1, 2, 3, 4, 5, 6], T))
+            t0 = time.perf_counter()
+            assert m0.wait(tid, completely=True)[tid].status.value == "success"
+            lat.append(time.perf_counter() - t0)
+        assert srv._completion_fds, "the server never found a descriptor to poll"
+        assert sorted(lat)[len(lat) // 2] < 0.05
+        # puts that nobody waits for: their completions must not leave the loop spinning
+        for i in range(5):
+            m1.put_async(np.arange(6 * T, dtype=np.int64) + 777000 + 1000 * i, slots([7, 8, 9, 10, 11, 12], T))
+        time.sleep(0.3)
+        c0 = time.process_time()
+        time.sleep(0.5)
+        assert time.process_time() - c0 < 0.25, "an idle server burns CPU"
+    finally:
+        m1.shutdown()
+        m0.shutdown()
