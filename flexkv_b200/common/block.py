@@ -28,6 +28,13 @@ def hash_blocks(token_ids: np.ndarray, tokens_per_block: int,
     return _native.C.gen_hashes(tok, tokens_per_block, namespace_prefix(namespace))
 
 
+def format_block_hash(value: Optional[int]) -> str:
+    """Signed or unsigned 64-bit key as fixed-width hex, ``-`` for none (log lines; flexkv/common/block.py:37-41)."""
+    if value is None:
+        return "-"
+    return f"0x{int(value) & ((1 << 64) - 1):016x}"
+
+
 @dataclass
 class SequenceMeta:
     token_ids: np.ndarray
@@ -51,5 +58,19 @@ class SequenceMeta:
     def has_hashes(self) -> bool:
         return self.block_hashes is not None
 
-    def get_hash(self, block_id: int) -> int:
+    def get_hash(self, block_id: int) -> Optional[int]:
+        if block_id >= self.num_blocks:
+            return None
         return int(self.block_hashes[block_id])
+
+    def gen_hashes(self) -> None:
+        """Keys are computed at construction; kept for callers written against the reference."""
+
+    @property
+    def namespace_id(self) -> Optional[int]:
+        """XXH64 of the namespace prefix alone (None without a namespace): one id per tenant / LoRA / salt
+        combination, equal for equal namespaces (flexkv/common/block.py:80-90)."""
+        pre = namespace_prefix(self.namespace)
+        if pre is None:
+            return None
+        return int(_native.C.xxh64(pre, 0))

@@ -71,3 +71,30 @@ def test_batch_hashing_matches_single(native):
 def test_sequence_meta():
     s = SequenceMeta(np.arange(40), 16)
     assert s.num_blocks == 2 and len(s.block_hashes) == 2 and s.token_ids.dtype == np.int64
+
+
+def test_namespace_identity_and_key_formatting(native):
+    """Reference scenarios of tests/test_namespace_isolation.py at the level of SequenceMeta: an empty namespace is
+    no namespace, equal namespaces share an id, prefix-cumulative keys hold inside a namespace, and every element of
+    a multi-part namespace matters."""
+    from flexkv_b200.common.block import format_block_hash
+    assert format_block_hash(None) == "-"
+    assert format_block_hash(1) == "0x0000000000000001" and format_block_hash(-1) == "0xffffffffffffffff"
+    tok = np.arange(1, 9, dtype=np.int64)
+    none, empty = SequenceMeta(tok, 4, None), SequenceMeta(tok, 4, [])
+    named, again = SequenceMeta(tok, 4, ["ns"]), SequenceMeta(tok, 4, ["ns"])
+    assert np.array_equal(none.block_hashes, empty.block_hashes) and none.namespace_id is None and empty.namespace_id is None
+    assert named.namespace_id is not None and named.namespace_id == again.namespace_id
+    assert named.namespace_id != SequenceMeta(tok, 4, ["other"]).namespace_id
+    assert not np.any(named.block_hashes == none.block_hashes)
+    # a longer sequence of the same namespace extends the shorter one's keys
+    longer = SequenceMeta(np.arange(1, 17, dtype=np.int64), 4, ["ns"])
+    assert np.array_equal(longer.block_hashes[:2], named.block_hashes)
+    assert named.get_hash(1) == int(named.block_hashes[1]) and named.get_hash(2) is None
+    # multi-part namespaces: LoRA id, cache salt, user hierarchy
+    full = SequenceMeta(tok, 4, ["lora-1", "salt-a", "org", "user"])
+    for other in (["lora-2", "salt-a", "org", "user"], ["lora-1", "salt-b", "org", "user"],
+                  ["lora-1", "salt-a", "org", "user2"], ["lora-1", "salt-a", "org"]):
+        assert not np.any(full.block_hashes == SequenceMeta(tok, 4, other).block_hashes)
+    named.gen_hashes()          # accepted, keys exist already
+    assert named.has_hashes()
