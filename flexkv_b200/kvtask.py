@@ -131,6 +131,7 @@ class KVTaskEngine:
         self.transfer_handles: List[Any] = list(transfer_handles or [])
         self.tasks: ExpiringDict = ExpiringDict(ttl=GLOBAL_CONFIG_FROM_ENV.task_ttl_seconds)
         self.graph_to_task: Dict[int, int] = {}
+        self._op_reports: Dict[Tuple[int, int], list] = {}     # (graph, op) -> reports so far, several handles only
         self._task_id = 0
         self._lock = threading.RLock()
         self._epoch = 0                      # bumped by reset_cache; stale completions are neutered
@@ -354,9 +355,44 @@ class KVTaskEngine:
     def _update_tasks(self, timeout: float = 0.0) -> None:
         """Drains completions from every transfer handle and advances task state."""
         per_handle = timeout / max(1, len(self.transfer_handles)) if timeout else 0.0
+        if len(self.transfer_handles) == 1:
+            for c in self.transfer_handles[0].wait(timeout=per_handle):
+                self._on_completed(c)
+            return
         for h in self.transfer_handles:
             for c in h.wait(timeout=per_handle):
-                self._on_completed(c)
+                c = c if c.is_graph_completed() else self._join_op_reports(c)
+                if c is not None:
+                    self._on_completed(c)
+
+    def _join_op_reports(self, c: CompletedOp) -> Optional[CompletedOp]:
+        """Several transfer handles (the nodes of a group that spans nodes) each run every op on their own slice
+        of the blocks. An op counts once ALL of them reported it: only then may its callback publish the blocks.
+        Success and per-block results are combined with AND; a handle that reports no per-block list, or one of
+        another length, where another handle reported one fails every block (reference scenarios:
+        tests/test_kvtask_lifecycle.py multi-handle block results)."""
+        key = (c.graph_id, c.op_id)
+        with self._lock:
+            rec = self._op_reports.get(key)
+            if rec is None:
+                rec = self._op_reports[key] = [0, True, [], 0.0, 0]
+            rec[0] += 1
+            rec[1] = rec[1] and bool(c.success)
+            rec[2].append(c.block_results)
+            rec[3] = max(rec[3], float(c.gpu_ms))
+            rec[4] += int(c.num_bytes)
+            if rec[0] < len(self.transfer_handles):
+                return None
+            del self._op_reports[key]
+        lists = rec[2]
+        results = None
+        if any(r is not None for r in lists):
+            n = max(len(r) for r in lists if r is not None)
+            if any(r is None or len(r) != n for r in lists):
+                results = (False,) * n
+            else:
+                results = tuple(all(col) for col in zip(*lists))
+        return CompletedOp(c.graph_id, c.op_id, rec[1], block_results=results, gpu_ms=rec[3], num_bytes=rec[4])
 
     def pump(self, timeout: float) -> None:
         """Blocks up to ``timeout`` seconds for the next completion of the data plane and applies what arrived.
@@ -393,12 +429,15 @@ class KVTaskEngine:
                 if task.handles_pending > 0:
                     return                       # every handle must report before the task ends
                 self.graph_to_task.pop(c.graph_id, None)
+                if self._op_reports:                     # ops of a failed graph that not every handle reported
+                    for key in [k for k in self._op_reports if k[0] == c.graph_id]:
+                        del self._op_reports[key]
                 self._finish_task(task, success=not task.any_failed)
                 return
             if not c.success:
                 task.any_failed = True
                 return
-            # per-op callbacks (mark index nodes ready) run once per op, on the first handle that reports it
+            # per-op callbacks (mark index nodes ready) run once per op, after every handle reported it
             members = self._member_tasks(task)
             if task.children:
                 for m in members:

@@ -213,3 +213,46 @@ def test_reset_cache_neuters_inflight_callbacks():
     assert e.wait([tid], completely=True)[tid].status == S.SUCCESS
     assert cpu.index.is_empty() and cpu.mempool.num_used_blocks == 0     # and did not touch the new index
     assert e.get_match(TOK)[1].sum() == 0
+
+
+def test_ops_of_several_handles_join_before_their_callback_and_block_results_are_anded():
+    """Two transfer handles (two nodes of one group): an op's callback runs after BOTH reported it, per-block
+    results are combined with AND, and a missing or mis-sized list fails every block
+    (reference: tests/test_kvtask_lifecycle.py:223-285)."""
+    from flexkv_b200.common.transfer import CompletedOp
+    from flexkv_b200.kvtask import KVTaskEngine
+
+    class Handle:
+        def __init__(self):
+            self.out = []
+
+        def wait(self, timeout=None):
+            o, self.out = self.out, []
+            return o
+
+    eng = KVTaskEngine.__new__(KVTaskEngine)
+    import threading
+    eng._lock = threading.RLock()
+    eng._op_reports = {}
+    h0, h1 = Handle(), Handle()
+    eng.transfer_handles = [h0, h1]
+    seen = []
+    eng._on_completed = seen.append
+    h0.out = [CompletedOp(41, 73, True, block_results=(True, True, False), gpu_ms=1.0, num_bytes=10)]
+    eng._update_tasks(0)
+    assert seen == []                                         # one node is not the whole group
+    h1.out = [CompletedOp(41, 73, True, block_results=(True, False, True), gpu_ms=2.0, num_bytes=5)]
+    eng._update_tasks(0)
+    assert len(seen) == 1 and seen[0].block_results == (True, False, False) and seen[0].success
+    assert seen[0].gpu_ms == 2.0 and seen[0].num_bytes == 15 and eng._op_reports == {}
+    for second in (None, (True, True)):
+        seen.clear()
+        h0.out = [CompletedOp(43, 76, True, block_results=(True, True, True))]
+        h1.out = [CompletedOp(43, 76, True, block_results=second)]
+        eng._update_tasks(0)
+        assert [c.block_results for c in seen] == [(False, False, False)]
+    seen.clear()
+    h0.out = [CompletedOp(44, 1, True)]
+    h1.out = [CompletedOp(44, 1, False), CompletedOp.graph_done(44, success=False)]
+    eng._update_tasks(0)
+    assert [(c.op_id, c.success, c.block_results) for c in seen] == [(1, False, None), (-1, False, None)]
