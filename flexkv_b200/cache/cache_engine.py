@@ -10,6 +10,7 @@ enabled, on SSD; evicting from one tier never writes back to another.
 """
 from __future__ import annotations
 
+import logging
 import math
 import os
 import threading
@@ -21,7 +22,7 @@ import numpy as np
 from .. import _native
 from ..common.block import SequenceMeta
 from ..common.config import GLOBAL_CONFIG_FROM_ENV, CacheConfig, ModelConfig
-from ..common.debug import EvictionLogAggregator
+from ..common.debug import EvictionLogAggregator, log_op
 from ..common.transfer import DeviceType, TransferOp, TransferOpGraph, TransferType
 from . import persist
 from .mempool import Mempool, NotEnoughSpaceError
@@ -181,6 +182,11 @@ class CacheEngine:
                     for cb in self.on_evict:
                         cb(self.device_type, blocks, hashes)
                     self._drain_swa()
+        if n > self.mempool.num_free_blocks:
+            # the eviction could not make room (everything left is locked, unready or leased): say so at once, the
+            # caller is about to skip an offload or fail a restore (reference: tests/test_operational_logging.py:63-77)
+            log_op("eviction", "batch", "target_miss", level=logging.WARNING, tier=self.device_type.name, wanted=n,
+                   free=self.mempool.num_free_blocks, total=self.num_total_blocks, target_met="false")
         if n > self.mempool.num_free_blocks and strict:
             raise NotEnoughSpaceError(f"{self.device_type.name}: need {n} blocks, "
                                       f"{self.mempool.num_free_blocks} free after eviction")

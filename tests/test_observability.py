@@ -64,3 +64,26 @@ def test_operation_line_format_and_eviction_batching():
     assert agg.flush() is None
     agg = EvictionLogAggregator(interval_s=0.0)
     assert agg.record("CPU", 4) == "operation=evict act=aggregate status=ok detail=CPU:blocks=4,events=1"
+
+
+def test_an_eviction_that_cannot_make_room_warns_at_once(caplog):
+    import logging
+    import numpy as np
+    from flexkv_b200.cache.cache_engine import CacheEngine
+    from flexkv_b200.common.block import SequenceMeta
+    from flexkv_b200.common.transfer import DeviceType
+    e = CacheEngine(DeviceType.CPU, 4, 4)
+    s = SequenceMeta(np.arange(16, dtype=np.int64), 4)
+    node = e.insert(s, e.take(4), is_ready=True)
+    e.lock_node(node)                                   # everything cached is pinned by a running transfer
+    with caplog.at_level(logging.WARNING, logger="flexkv"):
+        got = e.take(2, strict=False)
+    assert len(got) == 0
+    lines = [r.getMessage() for r in caplog.records if "operation=eviction" in r.getMessage()]
+    assert lines and "act=batch status=target_miss" in lines[0] and "tier=CPU" in lines[0] and "wanted=2" in lines[0]
+    assert "target_met=false" in lines[0]
+    e.unlock(node)
+    caplog.clear()
+    with caplog.at_level(logging.WARNING, logger="flexkv"):
+        assert len(e.take(2, strict=False)) == 2       # now the eviction makes room: no warning
+    assert not [r for r in caplog.records if "target_miss" in r.getMessage()]
