@@ -546,7 +546,11 @@ def _coerce(value: Any, like: Any) -> Any:
     if isinstance(like, KVCacheLayoutType):
         return KVCacheLayoutType(str(value).upper())
     if isinstance(like, int) and not isinstance(like, bool):
-        return int(value)
+        try:
+            return int(value)
+        except ValueError:
+            f = float(value)              # sizes in GB may be fractional ("0.5"); anything else raises here
+            return int(f) if f.is_integer() else f
     if isinstance(like, float):
         return float(value)
     return value

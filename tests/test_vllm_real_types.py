@@ -104,3 +104,44 @@ def test_offload_and_restore_through_vllms_own_classes(monkeypatch, tmp_path):
         assert shim.request_finished(r3, [1, 2, 3, 4, 5]) == (False, None)
     finally:
         shim.shutdown()
+
+
+def test_connector_is_built_from_vllms_own_config_objects(monkeypatch, tmp_path):
+    """vLLM's real ModelConfig / ParallelConfig / CacheConfig / KVTransferConfig (a six-layer Llama described by a
+    local config.json, no weights) feed the scheduler-side connector: geometry and tier sizes come out right.
+    (A whole VllmConfig cannot be built without a device; its parts can.)"""
+    import json
+    import os
+    from types import SimpleNamespace as NS
+    try:
+        from vllm.config import CacheConfig as VCache, KVTransferConfig, ModelConfig as VModel, ParallelConfig
+        from vllm.distributed.kv_transfer.kv_connector.v1.base import KVConnectorRole
+    except Exception as e:  # noqa: BLE001
+        pytest.skip(f"vllm config classes not importable: {e!r}")
+    model_dir = tmp_path / "tiny"
+    model_dir.mkdir()
+    (model_dir / "config.json").write_text(json.dumps({
+        "architectures": ["LlamaForCausalLM"], "model_type": "llama", "hidden_size": 256, "intermediate_size": 512,
+        "num_attention_heads": 8, "num_key_value_heads": 4, "num_hidden_layers": 6, "vocab_size": 1000,
+        "max_position_embeddings": 2048, "rms_norm_eps": 1e-5, "torch_dtype": "bfloat16", "head_dim": 32}))
+    try:
+        mc = VModel(model=str(model_dir), tokenizer=str(model_dir), skip_tokenizer_init=True, dtype="bfloat16")
+    except Exception as e:  # noqa: BLE001
+        pytest.skip(f"this vllm cannot build a ModelConfig on a box without a device: {e!r}")
+    vc = NS(model_config=mc, parallel_config=ParallelConfig(), cache_config=VCache(block_size=16),
+            kv_transfer_config=KVTransferConfig(kv_connector="FlexKVConnectorV1", kv_role="kv_both"))
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    monkeypatch.syspath_prepend(os.path.join(root, "compat"))
+    monkeypatch.delenv("FLEXKV_CONFIG_PATH", raising=False)
+    monkeypatch.setenv("FLEXKV_CPU_CACHE_GB", "0.01")                      # fractional sizes are accepted
+    monkeypatch.setenv("FLEXKV_SERVER_RECV_PORT", f"ipc://{tmp_path}/srv")
+    from flexkv.integration.vllm.vllm_v1_adapter import FlexKVConnectorV1Impl
+    impl = FlexKVConnectorV1Impl(vc, KVConnectorRole.SCHEDULER)
+    try:
+        m, c = impl.scheduler.cfg.model_config, impl.scheduler.cfg.cache_config
+        assert (m.num_layers, m.num_kv_heads, m.head_size, m.tp_size, m.use_mla) == (6, 4, 32, 1, False)
+        assert m.dtype == torch.bfloat16 and c.tokens_per_block == 16
+        block_bytes = 6 * 2 * 16 * 4 * 32 * 2
+        assert c.num_cpu_blocks == int(0.01 * (1 << 30)) // block_bytes
+    finally:
+        impl.shutdown()
