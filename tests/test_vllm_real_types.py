@@ -145,3 +145,34 @@ def test_connector_is_built_from_vllms_own_config_objects(monkeypatch, tmp_path)
         assert c.num_cpu_blocks == int(0.01 * (1 << 30)) // block_bytes
     finally:
         impl.shutdown()
+
+
+def test_mla_geometry_is_read_off_vllms_own_model_config(tmp_path):
+    """A DeepSeek-V3-shaped config through vLLM's real ModelConfig: one latent head of kv_lora_rank + rope width,
+    no K/V axis, whatever the tensor-parallel size."""
+    import json
+    from types import SimpleNamespace as NS
+    try:
+        from vllm.config import CacheConfig as VCache, ModelConfig as VModel, ParallelConfig
+    except Exception as e:  # noqa: BLE001
+        pytest.skip(f"vllm config classes not importable: {e!r}")
+    d = tmp_path / "ds"
+    d.mkdir()
+    (d / "config.json").write_text(json.dumps({
+        "architectures": ["DeepseekV3ForCausalLM"], "model_type": "deepseek_v3", "hidden_size": 256,
+        "intermediate_size": 512, "moe_intermediate_size": 128, "num_attention_heads": 8, "num_key_value_heads": 8,
+        "num_hidden_layers": 4, "vocab_size": 1000, "kv_lora_rank": 512, "q_lora_rank": 128, "qk_rope_head_dim": 64,
+        "qk_nope_head_dim": 128, "v_head_dim": 128, "n_routed_experts": 4, "n_shared_experts": 1,
+        "num_experts_per_tok": 2, "first_k_dense_replace": 1, "max_position_embeddings": 2048, "rms_norm_eps": 1e-6,
+        "torch_dtype": "bfloat16"}))
+    try:
+        mc = VModel(model=str(d), tokenizer=str(d), skip_tokenizer_init=True, dtype="bfloat16")
+    except Exception as e:  # noqa: BLE001
+        pytest.skip(f"this vllm cannot build the model config here: {e!r}")
+    assert mc.use_mla
+    cfg = FlexKVConfig()
+    cfg.post_init_from_vllm_config(NS(model_config=mc, parallel_config=ParallelConfig(tensor_parallel_size=2),
+                                      cache_config=VCache(block_size=64)))
+    m = cfg.model_config
+    assert (m.num_layers, m.num_kv_heads, m.head_size, m.kv_dim, m.tp_size, m.use_mla) == (4, 1, 576, 1, 2, True)
+    assert cfg.cache_config.tokens_per_block == 64
