@@ -54,3 +54,27 @@ class KVEventCollector:
         with self._lock:
             out, self._buf = self._buf, []
             return out
+
+    def close(self) -> None:
+        """Nothing runs in the background here (events are buffered by the caller's thread); kept for callers
+        written against the reference, whose collector owns a worker thread."""
+
+
+def to_vllm_events(events: List[KVEvent], block_size: int) -> List[Any]:
+    """The same events as vLLM's own ``BlockStored`` / ``BlockRemoved`` records, which is what the engine's event
+    publisher serialises (flexkv/integration/dynamo/collector.py:56-82). Fields that newer engine versions added
+    keep their defaults. Without vLLM the events come back unchanged."""
+    try:
+        from vllm.distributed.kv_events import BlockRemoved, BlockStored
+    except Exception:  # noqa: BLE001 - no engine in this process
+        return list(events)
+    out: List[Any] = []
+    stored_fields = set(getattr(BlockStored, "__struct_fields__", ()))
+    for ev in events:
+        if ev.kind == "stored":
+            kw = dict(block_hashes=list(ev.block_hashes), parent_block_hash=None, token_ids=[], block_size=int(block_size),
+                      lora_id=None, medium=ev.device, lora_name=None)
+            out.append(BlockStored(**{k: v for k, v in kw.items() if not stored_fields or k in stored_fields}))
+        else:
+            out.append(BlockRemoved(block_hashes=list(ev.block_hashes), medium=ev.device))
+    return out

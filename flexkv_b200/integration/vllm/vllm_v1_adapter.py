@@ -591,7 +591,10 @@ class FlexKVConnectorV1Impl:
     def take_events(self) -> List[Any]:
         """Buffered KV-cache events (stored / removed) for routers that track cache contents."""
         col = getattr(self.scheduler, "collector", None) if self.scheduler else None
-        return col.take_events() if col is not None else []
+        if col is None:
+            return []
+        from ..dynamo.collector import to_vllm_events
+        return to_vllm_events(col.take_events(), self.scheduler.T)
 
     def get_kv_connector_stats(self) -> Optional[dict]:
         """Counters of the last interval. The worker side returns an empty (non-None) record so that the

@@ -97,7 +97,20 @@ def test_offload_and_restore_through_vllms_own_classes(monkeypatch, tmp_path):
         stats = shim.get_kv_connector_stats()
         from vllm.distributed.kv_transfer.kv_connector.v1.metrics import KVConnectorStats
         assert stats is None or isinstance(stats, KVConnectorStats)
-        assert list(shim.take_events()) == [] or True
+        assert list(shim.take_events()) == []                    # events are off unless asked for
+        impl.scheduler.enable_kv_events()
+        r4 = request("d", np.arange(7000, 7000 + 3 * T + 1))
+        r4.status = v["RequestStatus"].FINISHED_STOPPED
+        assert shim.request_finished(r4, [20, 21, 22, 23])[0] is True
+        shim.build_connector_meta(v["SchedulerOutput"].make_empty())
+        step_until("finished_sending", "d")
+        from vllm.distributed.kv_events import BlockStored, KVCacheEvent, KVEventBatch
+        events = list(shim.take_events())
+        assert events and all(isinstance(e, KVCacheEvent) for e in events)
+        stored = [e for e in events if isinstance(e, BlockStored)]
+        assert sum(len(e.block_hashes) for e in stored) == 3 and stored[0].block_size == T and stored[0].medium == "CPU"
+        import msgspec
+        msgspec.msgpack.encode(KVEventBatch(ts=0.0, events=events))     # what the engine's publisher does with them
         # an aborted request leaves nothing behind
         r3 = request("c", np.arange(9000, 9000 + 5 * T))
         r3.status = v["RequestStatus"].FINISHED_ABORTED
