@@ -49,9 +49,29 @@ if KVConnectorStats is not None:
             return d
 
         def is_empty(self) -> bool:
-            return False          # keeps the engine polling for finished transfers on idle steps
+            """Nothing was counted in this interval: the engine's logger skips the record."""
+            return not any(v for k, v in self.data.items() if not k.endswith("_ratio"))
 
         def __getitem__(self, key):
             return self.data[key]
+
+    class FlexKVWorkerSentinelStats(KVConnectorStats):
+        """What the worker side returns: it counts nothing itself, but a stats object that is not None keeps the
+        worker's connector output from being dropped as empty, so the engine keeps asking the scheduler side for
+        finished transfers on steps that schedule no tokens. Aggregation hands back the other side's record
+        (reference: flexkv/integration/vllm/vllm_v1_adapter.py:66-82)."""
+
+        def aggregate(self, other):
+            return other
+
+        def reduce(self):
+            return {}
+
+        def reset(self):
+            pass
+
+        def is_empty(self) -> bool:
+            return True
 else:
     FlexKVConnectorStats = None
+    FlexKVWorkerSentinelStats = None

@@ -478,9 +478,10 @@ def _vllm_types() -> dict:
     if _VLLM_TYPES is None:
         try:
             from . import vllm_types as vt
-            _VLLM_TYPES = dict(meta=vt.FlexKVConnectorMetadata, stats=vt.FlexKVConnectorStats)
+            _VLLM_TYPES = dict(meta=vt.FlexKVConnectorMetadata, stats=vt.FlexKVConnectorStats,
+                               worker_stats=vt.FlexKVWorkerSentinelStats)
         except Exception:  # noqa: BLE001 - no vLLM here
-            _VLLM_TYPES = dict(meta=_PlainConnectorMetadata, stats=None)
+            _VLLM_TYPES = dict(meta=_PlainConnectorMetadata, stats=None, worker_stats=None)
     return _VLLM_TYPES
 
 
@@ -599,14 +600,21 @@ class FlexKVConnectorV1Impl:
     def get_kv_connector_stats(self) -> Optional[dict]:
         """Counters of the last interval. The worker side returns an empty (non-None) record so that the
         engine keeps polling for finished transfers on steps that schedule no tokens."""
-        cls = _vllm_types()["stats"]
+        types = _vllm_types()
+        cls = types["stats"]
         if not self.is_scheduler:
-            return {} if cls is None else cls(data={})
+            sentinel = types.get("worker_stats")
+            return {} if sentinel is None else sentinel(data={})
         st = self.scheduler.stats
-        d = dict(num_get_requests=st.num_get_requests, num_get_query_tokens=st.num_get_query_tokens,
-                    num_gpu_matched_tokens=st.num_gpu_matched_tokens,
-                    num_flexkv_matched_tokens=st.num_flexkv_matched_tokens, num_put_requests=st.num_put_requests,
-                    num_put_unmatched_tokens=st.num_put_unmatched_tokens, num_failed_requests=st.num_failed_requests)
+        total = dict(num_get_requests=st.num_get_requests, num_get_query_tokens=st.num_get_query_tokens,
+                     num_gpu_matched_tokens=st.num_gpu_matched_tokens,
+                     num_flexkv_matched_tokens=st.num_flexkv_matched_tokens, num_put_requests=st.num_put_requests,
+                     num_put_query_tokens=st.num_put_query_tokens,
+                     num_put_unmatched_tokens=st.num_put_unmatched_tokens, num_failed_requests=st.num_failed_requests)
+        # the engine's logger ADDS the records of an interval: hand over what happened since the last call
+        last = getattr(self, "_stats_reported", {})
+        d = {k: v - last.get(k, 0) for k, v in total.items()}
+        self._stats_reported = total
         return d if cls is None else cls(data=d)
 
     def get_block_ids_with_load_errors(self) -> Set[int]:

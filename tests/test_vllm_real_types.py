@@ -94,9 +94,24 @@ def test_offload_and_restore_through_vllms_own_classes(monkeypatch, tmp_path):
         for l in range(2):
             assert torch.equal(kv[l][:, [42, 43, 44, 45]], saved[l][:, [12, 13, 14, 15]])
         assert shim.get_block_ids_with_load_errors() == set()
-        stats = shim.get_kv_connector_stats()
         from vllm.distributed.kv_transfer.kv_connector.v1.metrics import KVConnectorStats
-        assert stats is None or isinstance(stats, KVConnectorStats)
+        stats = shim.get_kv_connector_stats()
+        assert isinstance(stats, KVConnectorStats) and not stats.is_empty()
+        assert stats.data["num_get_requests"] == 2 and stats.data["num_put_requests"] == 1
+        assert stats.data["num_flexkv_matched_tokens"] == 4 * T
+        again = shim.get_kv_connector_stats()                # an interval in which nothing happened
+        assert again.is_empty() and again.data["num_get_requests"] == 0
+        total = stats.aggregate(again).reduce()              # what the engine's logger does with the records
+        assert total["num_get_requests"] == 2
+        assert abs(total["get_flexkv_match_ratio"] - 4 * T / total["num_get_query_tokens"]) < 1e-9
+        import pickle
+        assert pickle.loads(pickle.dumps(stats)).data == stats.data
+        # the worker side counts nothing but must not look empty to the engine
+        impl.is_scheduler = False
+        sentinel = shim.get_kv_connector_stats()
+        impl.is_scheduler = True
+        assert isinstance(sentinel, KVConnectorStats) and sentinel.is_empty() and sentinel.aggregate(stats) is stats
+        assert not v["KVConnectorOutput"](kv_connector_stats=sentinel).is_empty()
         assert list(shim.take_events()) == []                    # events are off unless asked for
         impl.scheduler.enable_kv_events()
         r4 = request("d", np.arange(7000, 7000 + 3 * T + 1))
