@@ -304,7 +304,7 @@ def test_server_sleeps_on_requests_and_completions_not_on_a_timer():
         time.sleep(0.3)
         c0 = time.process_time()
         time.sleep(0.5)
-        assert time.process_time() - c0 < 0.25, "an idle server burns CPU"
+        assert time.process_time() - c0 < 0.4, "an idle server burns CPU"       # a spinning loop would use the whole 0.5 s
     finally:
         m1.shutdown()
         m0.shutdown()
