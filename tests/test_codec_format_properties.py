@@ -36,7 +36,7 @@ def tiles(draw):
     return out
 
 
-@settings(max_examples=40, deadline=None)
+@settings(max_examples=40, deadline=None, derandomize=True)
 @given(tiles())
 def test_any_tile_round_trips_and_never_grows(bits):
     x = _tile(bits)
@@ -60,7 +60,7 @@ def test_any_tile_round_trips_and_never_grows(bits):
         assert list(packed[16:16 + min(len(order), K.RANKS)].numpy()) == order[:K.RANKS]
 
 
-@settings(max_examples=200, deadline=None)
+@settings(max_examples=200, deadline=None, derandomize=True)
 @given(st.lists(st.tuples(st.integers(0, K.RANKS), st.integers(0, 255), st.sampled_from([1, 2])), min_size=1, max_size=40))
 def test_codes_are_prefix_free_and_self_delimiting(seq):
     """A stream of codes of either shape parses back to the same (rank or literal exponent) sequence."""
