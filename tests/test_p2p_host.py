@@ -331,3 +331,38 @@ def test_node_b_restores_from_the_files_node_a_wrote_to_the_shared_remote_mount(
     finally:
         a.shutdown()
         b.shutdown()
+
+
+def test_registry_inspector_lists_nodes_metadata_and_block_records():
+    """`benchmarks/registry_check.py` against the registry of a two-node deployment (in-process store here; the same
+    calls go to a RegistryServer or a Redis server): both nodes alive, their pool files in the metadata, the
+    publisher's host blocks counted."""
+    import importlib.util
+    import os
+    spec = importlib.util.spec_from_file_location(
+        "registry_check", os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "benchmarks",
+                                       "registry_check.py"))
+    rc = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(rc)
+    from flexkv_b200.cache.registry import connect
+    name = uuid.uuid4().hex
+    a, kva = start_node(name, 1)
+    b, kvb = start_node(name, 2)
+    try:
+        tok = np.arange(6 * T, dtype=np.int64) + 4100
+        tid = a.put_async(tok, slots([1, 2, 3, 4, 5, 6]))
+        assert a.wait(tid, completely=True)[tid].status.value == "success"
+        a.kv_task_engine.cache_engine.cpu_cache_engine.refresh()
+        report = rc.inspect(connect(f"inproc:{name}", 0))
+        assert [n["alive"] for n in report["nodes"]] == [True, True]
+        by_id = {n["node_id"]: n for n in report["nodes"]}
+        aid = a.kv_task_engine.cache_engine.node_registry.node_id
+        assert by_id[aid]["blocks"]["host"]["records"] == 6 and len(by_id[aid]["blocks"]["host"]["sample"]) == 2
+        assert sum(n["blocks"]["host"]["records"] for n in report["nodes"]) == 6
+        assert any("pool_file" in m for n in report["nodes"] for m in n["meta"].values())
+        assert report["records_of_unknown_nodes"] == {}
+        text = rc.render(report)
+        assert f"node {aid}: alive" in text and "host: 6 block records" in text
+    finally:
+        a.shutdown()
+        b.shutdown()
