@@ -171,6 +171,17 @@ def test_two_nodes_share_prefixes_through_a_redis_registry(server):
         assert a.wait(tid, completely=True)[tid].status.value == "success"
         ea.refresh(); eb.refresh()
         assert any(k.startswith(b"CPUB:block:") for k in server.store.d)
+        # the registry inspector reads the same deployment over the wire protocol
+        import importlib.util
+        import os
+        spec = importlib.util.spec_from_file_location("registry_check", os.path.join(
+            os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "benchmarks", "registry_check.py"))
+        rc = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(rc)
+        from flexkv_b200.cache.registry import connect
+        report = rc.inspect(connect("redis://127.0.0.1", server.port))
+        assert [n["node_id"] for n in report["nodes"]] == [1, 2] and all(n["alive"] for n in report["nodes"])
+        assert {n["node_id"]: n["blocks"]["host"]["records"] for n in report["nodes"]} == {ea.node_id: 6, eb.node_id: 0}
         tid, mask = b.get_match(tok)
         assert int(mask.sum()) == 6 * T
         assert sorted(o.transfer_type.value for o in b.kv_task_engine.tasks[tid].graph.ops()) == ["H2D", "PEERH2H"]
