@@ -45,6 +45,9 @@ def sglang_gpu_layout(k_buffers: Sequence[torch.Tensor], page_size: int, use_mla
     return KVCacheLayout(KVCacheLayoutType.LAYERFIRST, L, tokens // page_size, page_size, t.shape[-2], t.shape[-1])
 
 
+_UNSET = object()
+
+
 def swa_transfer_enabled_from_env() -> bool:
     return bool(int(os.environ.get("FLEXKV_ENABLE_SWA_TRANSFER", "1")))
 
@@ -77,6 +80,7 @@ class FlexKVConnector:
         self._pending_loads: Dict[str, _PendingLoad] = {}
         self._stores: Dict[str, int] = {}
         self._prefetch: Dict[str, int] = {}
+        self._launched_loads: List[int] = []      # loads started through the single-request layerwise form
         # prefetching pays only where a tier below the host pool exists (flexkv/integration/sglang/connector.py:302-306);
         # a key-addressed remote store is read by prefetches alone, so it must be on with one
         cc = flexkv_config.cache_config
@@ -230,8 +234,80 @@ class FlexKVConnector:
         self.comm.barrier()
 
     # ---- lookup / load -------------------------------------------------------------------
-    def lookup_kv(self, rid: str, token_ids: Sequence[int], num_computed_tokens: int = 0,
-                  namespace: Optional[List[str]] = None) -> int:
+    # ---- two calling conventions ------------------------------------------------------------
+    # The methods below take this package's arguments (request id first, lists for batches) and also the ones
+    # the reference's SGLang integration passes (flexkv/integration/sglang/connector.py:460-466,696-700,956,
+    # 1011-1017, as called from its sglang_flexkv_connector.patch), so that integration drives this connector
+    # unchanged. Which one is meant shows in the arguments; the reference's forms return what its callers read.
+    @property
+    def enable_layerwise(self) -> bool:
+        return bool(self.layerwise)
+
+    def lookup_kv(self, *args: Any, **kw: Any):
+        """``lookup_kv(rid, token_ids, num_computed_tokens=0, namespace=None) -> matched tokens``, or the
+        reference's ``lookup_kv(token_ids, token_mask, rid=None, sglang_req_id=...) -> (task id, matched tokens)``
+        where ``token_mask`` marks the tokens that are not on the GPU yet."""
+        if (args and isinstance(args[0], str)) or ("token_mask" not in kw and "rid" in kw and not args):
+            return self._lookup_kv(*args, **kw)
+        token_ids = args[0] if args else kw["token_ids"]
+        token_mask = args[1] if len(args) > 1 else kw.get("token_mask")
+        rid = args[2] if len(args) > 2 else kw.get("rid")
+        computed = 0
+        if token_mask is not None:
+            m = torch.as_tensor(token_mask).cpu().numpy().astype(bool)
+            computed = int(np.argmax(m)) if m.any() else len(m)
+        key = rid if rid else f"__untracked_{id(token_ids)}"
+        matched = self._lookup_kv(key, token_ids, computed)
+        task_id = -1
+        if self.is_leader and key in self._pending_loads:
+            task_id = self._pending_loads[key].task_id
+        if not rid:
+            self.release_pending(key)              # nobody will come back for it
+        return task_id, matched
+
+    def start_load_kv_layerwise(self, rids: Any, slot_mappings: Any):
+        """Batch form ``(rids, slot_mappings) -> task ids``, or the reference's single-request form
+        ``(rid, slot_mapping) -> (tokens being loaded, counter id)``."""
+        if not isinstance(rids, str):
+            return self._start_load_kv_layerwise(rids, slot_mappings)
+        n = 0
+        if self.is_leader and rids in self._pending_loads:
+            n = self._pending_loads[rids].matched_tokens
+        n = int(self.comm.broadcast(n))
+        ids = self._start_load_kv_layerwise([rids], [slot_mappings])
+        if not ids:
+            return 0, -1
+        producer = self.layer_counter.counter_of(ids[0]) if self.layer_counter is not None and \
+            hasattr(self.layer_counter, "counter_of") else 0
+        self._launched_loads.extend(ids)
+        return n, producer
+
+    def drain_launched_loads(self, task_ids: Any = 100, timeout: float = 60.0):
+        """``(task_ids, timeout) -> bool`` waits for these loads; the reference's ``(threshold=100)`` is a
+        non-blocking sweep over the loads launched through its single-request form, run once that many piled up."""
+        if not isinstance(task_ids, int):
+            return self._drain_launched_loads(task_ids, timeout)
+        if len(self._launched_loads) >= task_ids:
+            if self.is_leader:
+                done = self.mgr.try_wait(list(dict.fromkeys(self._launched_loads)))
+                self._launched_loads = [t for t in self._launched_loads if t not in done]
+            else:
+                self._launched_loads = []
+        return None
+
+    def store_kv(self, rid: str, token_ids: Sequence[int], slot_mapping: Any = None,
+                 namespace: Optional[List[str]] = None, *, kv_indices: Any = None, sglang_req_id: Any = _UNSET):
+        """Returns the tokens that will move; called the reference's way (``kv_indices=`` or ``sglang_req_id=``)
+        it returns the id of the store in flight, -1 when nothing had to be stored."""
+        reference_style = kv_indices is not None or sglang_req_id is not _UNSET
+        moved = self._store_kv(rid, token_ids, slot_mapping if kv_indices is None else kv_indices, namespace)
+        if not reference_style:
+            return moved
+        tid = self._stores.get(rid, -1) if self.is_leader and moved else -1
+        return int(self.comm.broadcast(tid))
+
+    def _lookup_kv(self, rid: str, token_ids: Sequence[int], num_computed_tokens: int = 0,
+                   namespace: Optional[List[str]] = None) -> int:
         """Tokens beyond the GPU-resident prefix that can be restored (same on every rank)."""
         matched = 0
         if self.is_leader:
@@ -282,7 +358,7 @@ class FlexKVConnector:
                     self.stats.record_failed()
         return int(self.comm.broadcast(done))
 
-    def start_load_kv_layerwise(self, rids: Sequence[str], slot_mappings: Sequence[Any]) -> List[int]:
+    def _start_load_kv_layerwise(self, rids: Sequence[str], slot_mappings: Sequence[Any]) -> List[int]:
         """Launches the loads of a batch as ONE layerwise restore that signals per
         layer; the forward pass waits in the KV pool's layer hook."""
         ids: List[int] = []
@@ -309,7 +385,7 @@ class FlexKVConnector:
             self.layer_counter.abort_unregistered_selection(counter)
         return manifest["ids"]
 
-    def drain_launched_loads(self, task_ids: Sequence[int], timeout: float = 60.0) -> bool:
+    def _drain_launched_loads(self, task_ids: Sequence[int], timeout: float = 60.0) -> bool:
         ok = True
         if self.is_leader and task_ids:
             res = self.mgr.wait(list(task_ids), timeout=timeout)
@@ -317,8 +393,8 @@ class FlexKVConnector:
         return bool(self.comm.broadcast(ok))
 
     # ---- store -----------------------------------------------------------------------------
-    def store_kv(self, rid: str, token_ids: Sequence[int], slot_mapping: Any,
-                 namespace: Optional[List[str]] = None) -> int:
+    def _store_kv(self, rid: str, token_ids: Sequence[int], slot_mapping: Any,
+                  namespace: Optional[List[str]] = None) -> int:
         """Asynchronous offload of the request's full pages; returns the tokens that will move."""
         moved = 0
         plan = None
@@ -360,7 +436,8 @@ class FlexKVConnector:
         return bool(self.comm.broadcast(ok))
 
     # ---- prefetch ---------------------------------------------------------------------------
-    def prefetch_async(self, rid: str, token_ids: Sequence[int], namespace: Optional[List[str]] = None) -> None:
+    def prefetch_async(self, rid: str, token_ids: Sequence[int], namespace: Optional[List[str]] = None,
+                       sglang_req_id: Any = None) -> None:
         if not self.prefetch_enabled or not rid:
             return
         if self.is_leader:

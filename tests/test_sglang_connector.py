@@ -184,3 +184,57 @@ def test_layer_done_counter_guards_rank_skewed_batches():
             c.abort_unregistered_selection(p)
     finally:
         c.close()
+
+
+def test_the_reference_integrations_calling_convention_drives_the_same_connector():
+    """The calls of the reference's SGLang patch, argument for argument (flexkv/integration/sglang/
+    sglang_flexkv_connector.patch: lookup with a token mask and keyword request ids, store that returns the id of
+    the store in flight or -1, the argument-less sweep of launched loads, prefetch with the engine's request id)."""
+    shape = KVShape("sg", 2, 2, 16, tokens_per_block=T)
+    cfg = FlexKVConfig()
+    cfg.model_config = make_model_config(shape)
+    cfg.cache_config = CacheConfig(tokens_per_block=T, num_cpu_blocks=32)
+    mgr = KVManager(cfg.model_config, cfg.cache_config, require_gpu=True)
+    kv, layout = alloc_paged_cache(shape, 64, "cpu", "sglang", fill="normal", seed=91)
+    mgr.register_gpu_tensors(kv, layout)
+    mgr.start(); mgr.wait_ready(30)
+    conn = FlexKVConnector(cfg, page_size=T, kv_manager=mgr, register=False)
+    try:
+        assert conn.enable_layerwise is False
+        tok = list(range(700, 700 + 5 * T))
+        pages = np.array([9, 2, 33, 4, 17])
+        indices = torch.from_numpy(np.repeat(pages, T) * T + np.tile(np.arange(T), 5))
+        task_id = conn.store_kv("r1:flexkv-store:0", tok, indices, sglang_req_id="r1")
+        assert isinstance(task_id, int) and task_id >= 0
+        import time
+        t0 = time.time()
+        done = []
+        while not done and time.time() - t0 < 10:
+            done = conn.check_completed_stores()
+            time.sleep(0.002)
+        assert done == ["r1:flexkv-store:0"]
+        assert conn.store_kv("r1:flexkv-store:1", tok, indices, sglang_req_id="r1") == -1     # nothing new to store
+        saved = [t.clone() for t in kv]
+        for t in kv:
+            t.zero_()
+        token_mask = torch.zeros(len(tok), dtype=torch.bool)
+        token_mask[T:] = True                                        # the first page is on the GPU already
+        tid, hit = conn.lookup_kv(tok, token_mask, rid="r2", sglang_req_id="r2")
+        assert tid >= 0 and hit == 4 * T
+        dst = np.array([40, 41, 42, 43])
+        assert conn.retrieve_kv("r2", torch.from_numpy(np.repeat(dst, T) * T + np.tile(np.arange(T), 4))) == 4 * T
+        for i in range(4):
+            assert torch.equal(kv[i][dst], saved[i][pages[1:]])
+        # a lookup nobody tracks holds nothing afterwards
+        tid, hit = conn.lookup_kv(tok, token_mask)
+        assert hit == 4 * T and not conn._pending_loads
+        # a miss, a released hit, the sweep and the prefetch form
+        assert conn.lookup_kv(list(range(9000, 9016)), torch.ones(16, dtype=torch.bool), rid="r3")[1] == 0
+        conn.lookup_kv(tok, token_mask, rid="r4", sglang_req_id="r4")
+        conn.release_pending("r4")
+        assert not conn._pending_loads
+        assert conn.drain_launched_loads() is None
+        conn.prefetch_async("r5", tok, sglang_req_id="r5")
+        conn.cancel_prefetch("r5")
+    finally:
+        conn.shutdown()
