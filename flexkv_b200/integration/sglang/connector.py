@@ -53,13 +53,38 @@ def swa_transfer_enabled_from_env() -> bool:
 
 
 class FlexKVConnector:
-    def __init__(self, flexkv_config: FlexKVConfig, page_size: int, tp_rank: int = 0, tp_size: int = 1,
-                 pp_rank: int = 0, pp_size: int = 1, dp_rank: int = 0, cp_rank: int = 0, cp_size: int = 1,
-                 comm: Optional[FlexKVComm] = None, kv_manager: Any = None, register: bool = True,
-                 hand_off_slot_mapping: bool = False) -> None:
+    def __init__(self, flexkv_config: Optional[FlexKVConfig] = None, page_size: int = 0, tp_rank: int = 0,
+                 tp_size: int = 1, pp_rank: int = 0, pp_size: int = 1, dp_rank: int = 0, cp_rank: int = 0,
+                 cp_size: int = 1, comm: Optional[FlexKVComm] = None, kv_manager: Any = None, register: bool = True,
+                 hand_off_slot_mapping: bool = False, *, sgl_model_config: Any = None, server_args: Any = None,
+                 kvcache: Any = None, attn_cp_rank: Optional[int] = None, pp_group: Any = None,
+                 attn_tp_group: Any = None, attn_cp_group: Any = None) -> None:
         """``hand_off_slot_mapping``: set on ONE rank of every node other than the leader's when the group
         spans nodes. That node's transfer manager receives the leader's graphs with the GPU side unbound; this
-        rank sends it the pages its node allocated for each task (flexkv/integration/sglang/connector.py:2199-2204)."""
+        rank sends it the pages its node allocated for each task (flexkv/integration/sglang/connector.py:2199-2204).
+
+        The keyword-only arguments are the reference's constructor (``sgl_model_config``, ``server_args``,
+        ``kvcache``, ``attn_cp_rank`` and the engine's process groups, as its SGLang patch passes them): the
+        configuration is then read off the engine's objects, group sizes off the groups, the pool geometry off
+        ``kvcache``, and the pool is registered at the end of construction."""
+        pool = None
+        if flexkv_config is None:
+            if sgl_model_config is None:
+                raise TypeError("FlexKVConnector needs a FlexKVConfig, or the engine's model config and server args")
+
+            def size(g: Any) -> int:
+                if g is None:
+                    return 1
+                n = getattr(g, "world_size", None)
+                return int(n if n is not None else g.size())
+            tp_size, cp_size, pp_size = size(attn_tp_group), size(attn_cp_group), size(pp_group)
+            cp_rank = int(attn_cp_rank or 0)
+            flexkv_config = FlexKVConfig.from_env()
+            flexkv_config.post_init_from_sglang_config(server_args, sgl_model_config, int(page_size), tp_size=tp_size,
+                                                       pp_size=pp_size, cp_size=cp_size,
+                                                       dp_size=int(getattr(server_args, "dp_size", 1) or 1))
+            if kvcache is not None:
+                pool = FlexKVConnector.configure_for_pool(flexkv_config, kvcache, int(page_size))
         self.cfg = flexkv_config
         self.hand_off_slot_mapping = bool(hand_off_slot_mapping)
         self.any_hand_off: Optional[bool] = None      # agreed over the group at the first load or store
@@ -94,6 +119,8 @@ class FlexKVConnector:
             self._client = KVTPClient(flexkv_config.gpu_register_port, dp_rank, dev, tp_rank=cp_rank * tp_size + tp_rank,
                                       pp_rank=pp_rank)
         atexit.register(self.shutdown)
+        if kvcache is not None and sgl_model_config is not None and self._client is not None:
+            self.register_kv_pool(kvcache, pool)
 
     # ---- start-up ---------------------------------------------------------------------
     def register_kv_buffers(self, k_buffers: Sequence[torch.Tensor], v_buffers: Optional[Sequence[torch.Tensor]] = None,

@@ -238,3 +238,35 @@ def test_the_reference_integrations_calling_convention_drives_the_same_connector
         conn.cancel_prefetch("r5")
     finally:
         conn.shutdown()
+
+
+def test_the_reference_constructor_reads_the_engines_objects():
+    """``FlexKVConnector(sgl_model_config=, server_args=, page_size=, kvcache=, tp_rank=, ..., attn_tp_group=, ...)``
+    as the reference's SGLang patch builds it: geometry from the engine's model config, group sizes from the
+    engine's groups, dtype from the server arguments."""
+    from types import SimpleNamespace as NS
+    model = NS(num_hidden_layers=2, num_key_value_heads=4, head_dim=16, dtype=torch.bfloat16)
+    args = NS(kv_cache_dtype="auto", dp_size=1)
+    group = NS(world_size=2)                                      # the engine's group coordinator
+    shape = KVShape("sg", 2, 2, 16, tokens_per_block=T)           # 4 KV heads over 2 TP ranks
+    kv, layout = alloc_paged_cache(shape, 64, "cpu", "sglang", fill="zeros")
+    probe = FlexKVConfig()
+    probe.post_init_from_sglang_config(args, model, T, tp_size=2)
+    mgr = KVManager(probe.model_config, CacheConfig(tokens_per_block=T, num_cpu_blocks=16), require_gpu=True)
+    mgr.register_gpu_tensors(kv, layout, tp_rank=0)
+    kv1, _ = alloc_paged_cache(shape, 64, "cpu", "sglang", fill="zeros")
+    mgr.register_gpu_tensors(kv1, layout, tp_rank=1)
+    mgr.start(); mgr.wait_ready(30)
+    conn = FlexKVConnector(sgl_model_config=model, server_args=args, page_size=T, kvcache=None, tp_rank=0, dp_rank=0,
+                           pp_rank=0, attn_cp_rank=0, pp_group=None, attn_tp_group=group, attn_cp_group=None,
+                           kv_manager=mgr, register=False)
+    try:
+        m = conn.cfg.model_config
+        assert (m.num_layers, m.num_kv_heads, m.head_size, m.tp_size, m.cp_size, m.pp_size) == (2, 4, 16, 2, 1, 1)
+        assert conn.T == T and conn.tp_size == 2 and conn.enable_layerwise is False
+        assert conn.lookup_kv(list(range(16)), torch.ones(16, dtype=torch.bool), rid="x") == (-1, 0)
+    finally:
+        conn.shutdown()
+    import pytest
+    with pytest.raises(TypeError):
+        FlexKVConnector(page_size=T)
