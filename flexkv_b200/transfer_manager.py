@@ -57,6 +57,11 @@ class TransferManager:
         if getattr(reg, "is_swa", False):
             self.register_swa(reg)
             return
+        # a caller written against the reference names its rank by ``intra_client_id`` = pp_rank * (tp x cp ranks)
+        # + rank inside the stage (flexkv/common/config.py:511-516); the rank inside the stage is what is kept here
+        width = int(getattr(self.model_config, "effective_tp_size", 0) or 0)
+        if width > 0 and reg.pp_rank > 0 and reg.tp_rank >= width and 0 <= reg.tp_rank - reg.pp_rank * width < width:
+            reg.tp_rank -= reg.pp_rank * width
         with self._reg_cv:
             self._pending_regs.append(reg)
             self._reg_cv.notify_all()

@@ -188,3 +188,20 @@ def test_multicast_registration_stands_for_its_whole_tp_group():
     reg.mc_ptrs = [int(p) for p in reg.ptrs]
     reg.mc_flag_ptr = 1
     assert tm._registrations_arrived() == 4
+
+
+def test_a_rank_named_by_the_references_flat_id_lands_on_its_stage_local_rank():
+    """``KVTPClient(..., pp_rank=1, intra_client_id=pp_rank * ranks_per_stage + rank)`` as the reference's adapters
+    call it: the data plane keeps the rank inside the stage."""
+    from flexkv_b200.storage.gpu_layout import GpuRegistration
+    from flexkv_b200.transfer_manager import TransferManager
+    tm = TransferManager.__new__(TransferManager)
+    import threading
+    tm._reg_cv = threading.Condition()
+    tm._pending_regs = []
+    tm.model_config = make_model_config(KVShape("x", 4, 4, 16, tokens_per_block=4), tp_size=2, pp_size=2)
+    for pp, flat, want in ((0, 1, 1), (1, 2, 0), (1, 3, 1), (1, 1, 1)):
+        reg = GpuRegistration.__new__(GpuRegistration)
+        reg.pp_rank, reg.tp_rank = pp, flat
+        tm.register_gpu(reg)
+        assert tm._pending_regs[-1].tp_rank == want, (pp, flat)
